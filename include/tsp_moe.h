@@ -1,0 +1,194 @@
+/*
+ * tsp_moe.h — C ABI of the B200 (sm_100a) routed-MoE FFN hot path.
+ *
+ * This is the boundary a tokspur maintainer binds in place of the Metal operator methods of
+ * `MetalGraph` (native/include/tokspur/graph.hpp) that `encode_moe`, `encode_moe_mm_many` and
+ * `encode_verify_nax_moe` dispatch to. Each entry point names the reference operator it replaces.
+ *
+ * Conventions
+ *  - Every pointer prefixed `d_` is a DEVICE pointer owned by the caller. Nothing here allocates,
+ *    frees, copies weights or reads results back, unless the entry point says so.
+ *  - `stream` is a `cudaStream_t` passed as an opaque pointer (NULL = the legacy default stream).
+ *    Launches are asynchronous and ordered on that stream.
+ *  - Activations are FP32 rows with a byte stride (the reference's `GpuRowsF32`), ids are uint32.
+ *  - Return value: TSP_OK or a negative TSP_E_* code; `tsp_last_error()` gives the message of the
+ *    last refusal on the calling thread. Host-side contract violations are refused BEFORE any launch
+ *    (the reference throws `FormatError` there).
+ *  - Device-side numerical / index failures never trap: kernels OR bits into the caller's sticky
+ *    error word `d_error` (the reference's buffer index 7, graph.mm:3977) and write zeros for the
+ *    affected rows; the host reads the word once per batch with `tsp_error_word_read`.
+ *  - No CPU fallback exists. On a machine without a usable CUDA device every launch entry point
+ *    returns TSP_E_CUDA.
+ */
+#ifndef TSP_MOE_H
+#define TSP_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TSP_OK 0
+#define TSP_E_ARG (-1)      /* shape / size / alignment / aliasing contract violation */
+#define TSP_E_TYPE (-2)     /* encoding or layout without a kernel */
+#define TSP_E_CUDA (-3)     /* CUDA runtime refused (message holds the CUDA error string) */
+#define TSP_E_DEVICE (-4)   /* sticky device error word was non-zero at read time */
+
+/* Sticky error word bits (same meaning as the reference's kernels, planar_moe_v3.metal:100-105). */
+#define TSP_ERR_NONFINITE 2u /* non-finite scale, input or result */
+#define TSP_ERR_INDEX 4u     /* expert id / route geometry out of range, or an expert named twice by one token */
+#define TSP_ERR_TIMEOUT 8u   /* a bounded in-kernel wait gave up (pipeline barrier) */
+
+/* GGUF tensor type ids (gguf.cpp:21-32). */
+#define TSP_TYPE_F32 0u
+#define TSP_TYPE_Q8_0 8u
+#define TSP_TYPE_Q4_K 12u
+
+/* Weight byte layouts. */
+#define TSP_LAYOUT_GGUF 0u    /* GGUF array-of-blocks rows (144 B / 256 weights Q4_K, 34 B / 32 weights Q8_0) */
+#define TSP_LAYOUT_PLANAR 1u  /* Pack v3 planar expert: planes qs | sm | dm (planar_pack_v3.cpp:601-716) */
+
+/* Router activation (routing.hpp: RouterMode). */
+#define TSP_ROUTER_SOFTMAX 0u
+#define TSP_ROUTER_SIGMOID 1u
+
+/* A set of `experts` equally shaped quantised matrices [rows x cols], row-major, one per expert.
+ *   GGUF layout  : expert e at base + e * expert_stride, rows of cols/block blocks.
+ *   PLANAR layout: expert e at (e < split ? base + e*expert_stride : base_hi + (e-split)*expert_stride),
+ *                  each a complete planar expert. Co-located gate/up pairs (planar_moe_v3.metal:549-553)
+ *                  are described by split = experts/2, expert_stride = 2*planar_expert_bytes, with the up
+ *                  matrix set using base + planar_expert_bytes.
+ * A dense matrix is a set with experts = 1. All bases must be 16-byte aligned. */
+typedef struct tsp_matrix_set {
+    const void* base;
+    const void* base_hi;     /* used only when split < experts */
+    uint64_t expert_stride;  /* bytes between consecutive experts in one half */
+    uint32_t split;          /* first expert id stored under base_hi; == experts when unused */
+    uint32_t experts;
+    uint32_t rows, cols;
+    uint32_t type;           /* TSP_TYPE_Q4_K or TSP_TYPE_Q8_0 */
+    uint32_t layout;         /* TSP_LAYOUT_* */
+} tsp_matrix_set;
+
+/* Per-thread message of the last refused call. Never NULL. */
+const char* tsp_last_error(void);
+
+/* Library / device facts: writes the SM count and returns TSP_OK when a CUDA device is usable. */
+int tsp_device_info(int* sm_count, int* cc_major, int* cc_minor);
+
+/* Sticky error word helpers (graph.mm:3977-3978: checked once per batch at submit).
+ * `tsp_error_word_read` synchronises `stream`, copies the word to *host_word and returns
+ * TSP_E_DEVICE when it is non-zero. `tsp_error_word_reset` zeroes it asynchronously. */
+int tsp_error_word_read(const uint32_t* d_error, void* stream, uint32_t* host_word);
+int tsp_error_word_reset(uint32_t* d_error, void* stream);
+
+/* Bytes per expert of a [rows x cols] matrix in the given type/layout; 0 when unsupported.
+ * (planar: make_expert_spec, planar_pack_v3.cpp:601-650.) */
+uint64_t tsp_expert_bytes(uint32_t type, uint32_t layout, uint32_t rows, uint32_t cols);
+
+/* Test hook: decode one expert of a matrix set to FP32 [rows x cols], bit-identical to the
+ * reference's `dequantize` (numeric.cpp:97-148) / `dequantize_expert_planar_v3` (planar_pack_v3.cpp:760). */
+int tsp_dequant_f32(const tsp_matrix_set* m, uint32_t expert, float* d_out, uint32_t* d_error, void* stream);
+
+/* Replaces `MetalGraph::route` / `prefill_route_batch` / `moe_route_rows` (graph.mm:7929,5957,5863;
+ * CPU: route_reference, routing.cpp:11-40). Per token row: top-`selected` ids by descending logit,
+ * ties to the lower id; weights per `mode`, renormalised over the selection when `normalize_selected`.
+ * d_logits: [tokens] rows of `experts` floats, `logits_stride_bytes` apart. experts <= 4096, selected <= 64. */
+int tsp_moe_route(const float* d_logits, uint64_t logits_stride_bytes, uint32_t tokens, uint32_t experts,
+                  uint32_t selected, uint32_t mode, int normalize_selected,
+                  uint32_t* d_ids, float* d_weights, uint32_t* d_error, void* stream);
+
+/* Replaces `graph_grouped_routes` + `graph_grouped_tasks` (grouped_mpp.metal:12-66; host
+ * grouped_mm_routes, graph.mm:4608). Builds the stable per-expert token permutation:
+ *   d_token_map[e*tokens + j] = token*selected + slot of the j-th (ascending) token routed to e,
+ *   d_counts[e], and d_tasks = {live_tiles, routes, (expert,start)*live_tiles, 0xffffffff padding}
+ *   with tiles of `tile` routes in ascending expert order; d_tasks has tsp_moe_tasks_words() words. */
+int tsp_moe_permute(const uint32_t* d_ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile,
+                    uint32_t* d_token_map, uint32_t* d_counts, uint32_t* d_tasks, uint32_t* d_error, void* stream);
+uint64_t tsp_moe_tasks_words(uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile);
+
+/* Decode-size routed projection with the weight bytes streamed once per tile of routes.
+ * Replaces `planar_moe_gate_up_swiglu_m8` (graph.mm:9134), `routed_gemv`x2 + `swiglu` (moe.cpp:62-66),
+ * and for a dense set (token map NULL) `gemv`/`gemv_rows`/`q8_matvec_many` + `swiglu` of the shared expert.
+ *   h[route][r] = silu(sum_c G_e[r][c] x[token][c]) * (sum_c U_e[r][c] x[token][c]),  route = token*selected+slot
+ * gate/up: matrix sets [hidden x channels] with identical shape/type/layout.
+ * d_x: FP32 rows [tokens x channels]; d_h: FP32 rows [tokens*selected x hidden] (dense: [tokens x hidden]).
+ * d_token_map/d_counts/d_tasks: from tsp_moe_permute with tile == TSP_GEMV_TILE; all NULL for a dense set.
+ * x_is_f16_exact: non-zero promises every x value is exactly representable in binary16 (skips the
+ * low-half correction pass); zero is always safe. */
+#define TSP_GEMV_TILE 8u
+int tsp_moe_gate_up_swiglu(const tsp_matrix_set* gate, const tsp_matrix_set* up,
+                           const float* d_x, uint64_t x_stride_bytes, uint32_t tokens, uint32_t selected,
+                           const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks,
+                           float* d_h, uint64_t h_stride_bytes, int x_is_f16_exact,
+                           uint32_t* d_error, void* stream);
+
+/* Routed (or dense) plain projection y[route][r] = sum_j W_e[r][j] h[route][j].
+ * Replaces `planar_moe_routed_m8`'s down stage (graph.mm:9205), `routed_gemv(broadcast=false)` (moe.cpp:68),
+ * and for a dense set `gemv`/`q8_matvec_many`/`verify_nax_dense_q8` (shared down, vocabulary head).
+ * in_div: input row of a route is route / in_div (1 for down; `selected` to broadcast token rows). */
+int tsp_moe_project(const tsp_matrix_set* w, const float* d_in, uint64_t in_stride_bytes, uint32_t in_div,
+                    uint32_t tokens, uint32_t selected,
+                    const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks,
+                    float* d_out, uint64_t out_stride_bytes, int in_is_f16_exact,
+                    uint32_t* d_error, void* stream);
+
+/* Replaces `gemv(shared_router, rows=1)` + `mixture` / `prefill_mixture_batch` (moe.cpp:79-81,
+ * graph.mm:8023,5975; CPU mixture_reference, routing.cpp:42-61):
+ *   out[t][c] = sigmoid(s_t) * shared[t][c] + sum_{r<selected} w[t][r] * routed[t*selected+r][c]
+ * accumulated in route-rank order starting from the shared term. s_t = dot(d_shared_router, x[t]) when
+ * d_shared_router != NULL (and is stored to d_shared_logit when that is non-NULL), else d_shared_logit[t].
+ * d_out_f16 (optional) receives the same rows rounded to binary16. */
+int tsp_moe_combine(const float* d_routed, uint64_t routed_stride_bytes, const float* d_weights,
+                    const float* d_shared, uint64_t shared_stride_bytes,
+                    const float* d_shared_router, const float* d_x, uint64_t x_stride_bytes,
+                    float* d_shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected,
+                    float* d_out, uint64_t out_stride_bytes, void* d_out_f16, uint64_t out_f16_stride_bytes,
+                    uint32_t* d_error, void* stream);
+
+/* binary16 rows -> FP32 rows (exact) and back (round to nearest even); activation edge of the layer. */
+int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride_bytes, float* d_out, uint64_t out_stride_bytes,
+                        uint32_t rows, uint32_t cols, void* stream);
+
+/* Caller-owned scratch of one MoE layer call, sized for `capacity` token rows.
+ * Mirrors MoeScratch / MoeMmManyScratch (moe.hpp:14-17, moe_mm_many.hpp:50-55). */
+typedef struct tsp_moe_scratch {
+    uint32_t* d_ids;        /* [capacity x selected] */
+    float* d_weights;       /* [capacity x selected] */
+    float* d_hidden;        /* [capacity*selected x hidden]   (MoeScratch.gate after swiglu) */
+    float* d_routed;        /* [capacity*selected x channels] (MoeScratch.down) */
+    float* d_shared_hidden; /* [capacity x hidden] */
+    float* d_shared_out;    /* [capacity x channels] */
+    float* d_shared_logit;  /* [capacity] */
+    float* d_x32;           /* [capacity x channels] staging when the input is binary16 */
+    uint32_t* d_token_map;  /* [experts x capacity] */
+    uint32_t* d_counts;     /* [experts] */
+    uint32_t* d_tasks;      /* tsp_moe_tasks_words(capacity, experts, selected, TSP_GEMV_TILE) */
+    uint32_t capacity;
+} tsp_moe_scratch;
+
+typedef struct tsp_moe_weights {
+    tsp_matrix_set gate, up, down;                      /* routed experts */
+    tsp_matrix_set shared_gate, shared_up, shared_down; /* dense shared expert (experts = 1) */
+    const float* d_shared_router;                       /* F32 [channels]; NULL: gate logit 0 is NOT assumed, see below */
+} tsp_moe_weights;
+
+/* One whole MoE FFN sub-layer for `tokens` <= scratch.capacity rows with router logits supplied:
+ * route -> permute -> gate-up+SwiGLU -> down -> shared expert -> gated combine.
+ * Replaces `encode_moe` after its router GEMV (moe.cpp:37-83) and `encode_verify_nax_moe`
+ * (verify_nax.cpp:436-575) for small batches. x_dtype/out_dtype: 0 = FP32 rows, 1 = binary16 rows.
+ * When d_shared_router is NULL the shared expert is added ungated (gate = 1). */
+int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
+                         const void* d_x, uint64_t x_stride_bytes, uint32_t x_dtype,
+                         const float* d_logits, uint64_t logits_stride_bytes,
+                         uint32_t tokens, uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected,
+                         uint32_t mode, int normalize_selected,
+                         void* d_out, uint64_t out_stride_bytes, uint32_t out_dtype,
+                         uint32_t* d_error, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TSP_MOE_H */

@@ -1,0 +1,313 @@
+"""Parity of the CUDA path, called through the C ABI, with the CPU oracle and with the committed
+outputs of the reference's own CPU code. Bars: ids / permutation tables / dequantised weights bit-exact;
+decode-size projections and whole layers within the reference's own 5e-5 scaled error (ffn_check.cpp:48-55)
+and well inside rel-L2 <= 2e-3."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import fixtures
+import golden_cases
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from tokspur_public_b200 import capi, formats, synth  # noqa: E402
+from tokspur_public_b200 import layer as L  # noqa: E402
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_outputs.npz"))
+DEV = "cuda"
+
+
+def scaled_error(actual, expected):
+    """max |a-e| / max(1, |e|): the reference's own acceptance metric (ffn_check.cpp:48-55)."""
+    return float(np.max(np.abs(actual.astype(np.float64) - expected) / np.maximum(1.0, np.abs(expected))))
+
+
+def rel_l2(actual, expected):
+    return float(np.linalg.norm(actual.astype(np.float64) - expected) / max(np.linalg.norm(expected), 1e-30))
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def err_tensor():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def read_err(e):
+    torch.cuda.synchronize()
+    return int(e.item()) & 0xFFFFFFFF
+
+
+# ------------------------------------------------------------------ dequantised values, bit-exact
+@pytest.mark.parametrize("type_", [8, 12])
+@pytest.mark.parametrize("layout", [formats.GGUF, formats.PLANAR])
+def test_dequant_bit_exact(oracle, type_, layout):
+    cols, rows, E = 512, 16, 2
+    w = fixtures.lcg_weights(type_, cols, rows, E)  # extreme / subnormal scales included
+    data = w if layout == formats.GGUF else formats.pack_planar_experts(type_, w, E, rows, cols)
+    t = dev(data)
+    ms = L.matrix_set(t, type_, layout, rows, cols, E)
+    out = torch.empty(rows * cols, dtype=torch.float32, device=DEV)
+    e = err_tensor()
+    for ex in range(E):
+        capi.call("tsp_dequant_f32", C.byref(ms), ex, out.data_ptr(), e.data_ptr(), L.stream_ptr())
+        got = out.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), oracle.dequantize(type_, w[ex], rows * cols).view(np.uint32))
+        assert np.array_equal(got.view(np.uint32), GOLD[f"dequant_{type_}"][ex].view(np.uint32))
+    assert read_err(e) == 0
+
+
+def test_dequant_flags_nonfinite_scale():
+    w = fixtures.lcg_weights(12, 256, 8, 1).copy()
+    w[0, 0:2] = [0x00, 0x7c]  # d = +inf in the first block
+    t = dev(w)
+    ms = L.matrix_set(t, 12, formats.GGUF, 8, 256, 1)
+    out = torch.empty(8 * 256, dtype=torch.float32, device=DEV)
+    e = err_tensor()
+    capi.call("tsp_dequant_f32", C.byref(ms), 0, out.data_ptr(), e.data_ptr(), L.stream_ptr())
+    assert read_err(e) & capi.ERR_NONFINITE
+
+
+# ------------------------------------------------------------------ routing, bit-exact ids
+def run_route(logits, k, mode, norm):
+    T, E = logits.shape
+    lg = dev(logits.astype(np.float32))
+    ids = torch.zeros(T * k, dtype=torch.int32, device=DEV)
+    w = torch.zeros(T * k, dtype=torch.float32, device=DEV)
+    e = err_tensor()
+    capi.call("tsp_moe_route", lg.data_ptr(), E * 4, T, E, k, mode, int(norm), ids.data_ptr(), w.data_ptr(), e.data_ptr(), L.stream_ptr())
+    return ids.cpu().numpy().view(np.uint32).reshape(T, k), w.cpu().numpy().reshape(T, k), read_err(e)
+
+
+@pytest.mark.parametrize("E,k", [(512, 10), (64, 10), (5, 3), (1000, 64), (4096, 8), (33, 33)])
+def test_route_ids_bit_exact(oracle, E, k):
+    rng = np.random.default_rng(E * 131 + k)
+    T = 37
+    lg = np.round(rng.normal(size=(T, E)) * 3, 1).astype(np.float32)  # coarse grid: many exact ties
+    lg[0, :] = 1.5
+    for mode in (0, 1):
+        for norm in (False, True):
+            ids, w, err = run_route(lg, k, mode, norm)
+            oi, ow = oracle.route_rows(lg.astype(np.float64), k, mode, norm)
+            assert err == 0
+            assert np.array_equal(ids, oi)
+            assert np.max(np.abs(w - ow)) <= 1e-6
+
+
+def test_route_matches_reference_outputs_and_flags_nonfinite():
+    lg = fixtures.lcg_activations(9, 8 * 64).reshape(8, 64).astype(np.float64) * 5
+    lg[3, 10:20] = lg[3, 5]
+    lg32 = lg.astype(np.float32)
+    assert np.array_equal(lg32.astype(np.float64), lg)
+    for mode in (0, 1):
+        for norm in (0, 1):
+            ids, w, err = run_route(lg32, 10, mode, bool(norm))
+            assert err == 0 and np.array_equal(ids, GOLD[f"route_ids_{mode}{norm}"])
+            assert np.max(np.abs(w - GOLD[f"route_w_{mode}{norm}"])) <= 1e-6
+    bad = lg32.copy()
+    bad[2, 7] = np.nan
+    _, _, err = run_route(bad, 10, 0, True)
+    assert err & capi.ERR_NONFINITE
+
+
+# ------------------------------------------------------------------ permutation tables, bit-exact
+def run_permute(ids, E, tile):
+    T, k = ids.shape
+    d_ids = dev(ids.astype(np.uint32).view(np.int32))
+    tm = torch.full((E * T,), -1, dtype=torch.int32, device=DEV)
+    counts = torch.zeros(E, dtype=torch.int32, device=DEV)
+    words = int(capi.lib().tsp_moe_tasks_words(T, E, k, tile))
+    tasks = torch.zeros(words, dtype=torch.int32, device=DEV)
+    e = err_tensor()
+    capi.call("tsp_moe_permute", d_ids.data_ptr(), T, E, k, tile, tm.data_ptr(), counts.data_ptr(), tasks.data_ptr(), e.data_ptr(), L.stream_ptr())
+    return (tm.cpu().numpy().view(np.uint32).reshape(E, T), counts.cpu().numpy().view(np.uint32),
+            tasks.cpu().numpy().view(np.uint32), read_err(e))
+
+
+@pytest.mark.parametrize("T,E,k,tile", [(1, 512, 10, 8), (64, 512, 10, 8), (300, 16, 4, 32), (1000, 512, 10, 32), (5, 600, 64, 8), (129, 7, 7, 8)])
+def test_permutation_bit_exact(oracle, T, E, k, tile):
+    rng = np.random.default_rng(T * 7 + E)
+    bias = synth.zipf_bias(3, E) if T >= 300 else 0  # skewed loads, some experts with no route
+    ids = np.stack([np.argsort(-(rng.normal(size=E) + bias), kind="stable")[:k] for _ in range(T)]).astype(np.uint32)
+    tm, counts, tasks, err = run_permute(ids, E, tile)
+    otm, ocounts = oracle.grouped_routes(ids, E)
+    otasks = oracle.grouped_tasks(ocounts, T, k, tile)
+    assert err == 0
+    assert np.array_equal(counts, ocounts)
+    for e in range(E):
+        assert np.array_equal(tm[e, :counts[e]], otm[e, :counts[e]])
+    assert np.array_equal(tasks, otasks)
+    # size-independent properties: a permutation of all routes, ascending inside each expert
+    flat = np.concatenate([tm[e, :counts[e]] for e in range(E)])
+    assert np.array_equal(np.sort(flat), np.arange(T * k, dtype=np.uint32))
+    assert all(np.all(np.diff(tm[e, :counts[e]].astype(np.int64)) > 0) for e in range(E))
+
+
+def test_permutation_flags_bad_ids():
+    ids = np.array([[1, 1], [0, 2]], dtype=np.uint32)     # an expert named twice by one token
+    assert run_permute(ids, 4, 8)[3] & capi.ERR_INDEX
+    ids = np.array([[1, 9], [0, 2]], dtype=np.uint32)     # id out of range
+    assert run_permute(ids, 4, 8)[3] & capi.ERR_INDEX
+
+
+# ------------------------------------------------------------------ dense projection: BASELINE config 1 and the head shape
+def run_dense_project(type_, layout, wbytes, rows, cols, x, exact=False):
+    data = wbytes if layout == formats.GGUF else formats.pack_planar(type_, wbytes, rows, cols)
+    t = dev(data)
+    ms = L.matrix_set(t, type_, layout, rows, cols, 1)
+    M = x.shape[0]
+    dx = dev(x.astype(np.float32))
+    out = torch.full((M, rows + 8), -7654.25, dtype=torch.float32, device=DEV)  # padded rows: canaries must survive
+    e = err_tensor()
+    capi.call("tsp_moe_project", C.byref(ms), dx.data_ptr(), cols * 4, 1, M, 1, None, None, None, out.data_ptr(), (rows + 8) * 4,
+              int(exact), e.data_ptr(), L.stream_ptr())
+    o = out.cpu().numpy()
+    assert read_err(e) == 0
+    assert np.all(o[:, rows:] == np.float32(-7654.25))
+    return o[:, :rows]
+
+
+@pytest.mark.parametrize("layout", [formats.GGUF, formats.PLANAR])
+@pytest.mark.parametrize("M", [1, 7, 16, 256])
+def test_config1_single_q4k_matmul(oracle, layout, M):
+    """BASELINE config 1: [1024 x 2048] N(0, 0.02) Q4_K weight, binary16 N(0,1) activations, FP32 accumulate."""
+    rows, cols = 1024, 2048
+    w = formats.quantize_q4_k(synth.normal(0, (rows, cols), 0.02)).reshape(-1)
+    x = synth.activations_f16(1, M, cols).astype(np.float32)
+    got = run_dense_project(12, layout, w, rows, cols, x, exact=True)
+    check_rows = range(M) if M <= 16 else (0, 100, 255)
+    for m in check_rows:
+        want = oracle.gemv(12, w, cols, rows, x[m])
+        assert scaled_error(got[m], want) <= 5e-5
+        assert rel_l2(got[m], want) <= 1e-5
+    if M > 16:  # linearity over the batch: row 0 + row 1 projected equals the sum of projections, to FP32 accuracy
+        s = run_dense_project(12, layout, w, rows, cols, (x[0:1] + x[1:2]), exact=False)
+        assert rel_l2(s[0], (got[0] + got[1]).astype(np.float64)) <= 1e-5
+
+
+@pytest.mark.parametrize("type_,layout,rows,cols", [(8, formats.GGUF, 512, 2048), (8, formats.PLANAR, 512, 2048), (8, formats.GGUF, 64, 64),
+                                                    (8, formats.PLANAR, 256, 64), (12, formats.GGUF, 48, 256), (12, formats.PLANAR, 2048, 512),
+                                                    (12, formats.GGUF, 2048, 512), (8, formats.GGUF, 16, 2560)])
+def test_dense_projection_shapes(oracle, type_, layout, rows, cols):
+    w = fixtures.bounded_weights(type_, cols, rows, 1, seed=rows + cols)[0]
+    for M, exact in ((1, False), (3, False), (11, False)):
+        x = fixtures.lcg_activations(M, M * cols).reshape(M, cols) * np.float32(3.7)  # not binary16-exact: needs the low-half pass
+        got = run_dense_project(type_, layout, w, rows, cols, x, exact=exact)
+        for m in range(M):
+            want = oracle.gemv(type_, w, cols, rows, x[m])
+            assert scaled_error(got[m], want) <= 5e-6
+
+
+# ------------------------------------------------------------------ whole layers
+def run_layer(host, layout, x, logits, out_dtype=torch.float32, shared_layout=None):
+    dl = L.DeviceLayer(host, layout, DEV, shared_layout)
+    T = x.shape[0]
+    s = L.Scratch(host.channels, host.hidden, host.experts, host.selected, max(T, 1), DEV)
+    dx = dev(x)
+    out = torch.zeros((T, host.channels), dtype=out_dtype, device=DEV)
+    L.moe_layer_decode(dl, s, dx, dev(logits), out)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), s, dl
+
+
+def host_from_dict(d):
+    return L.HostLayer(d["channels"], d["hidden"], d["experts"], d["selected"], d["expert_type"], d["shared_type"], d["gate"], d["up"],
+                       d["down"], d["shared_gate"], d["shared_up"], d["shared_down"], d["shared_router"])
+
+
+@pytest.mark.parametrize("type_", [8, 12])
+@pytest.mark.parametrize("layout", [formats.GGUF, formats.PLANAR])
+def test_layer_matches_reference_outputs(oracle, type_, layout):
+    """The committed outputs of the reference's own CPU layer, stage by stage as its ffn-check compares them."""
+    d, x, logits = golden_cases.small_layer(type_)
+    host = host_from_dict(d)
+    out, s, _ = run_layer(host, layout, x, logits)
+    assert s.error_word() == 0
+    T, K = x.shape[0], host.selected
+    assert np.array_equal(s.ids.cpu().numpy().view(np.uint32)[:T * K].reshape(T, K), GOLD[f"layer_ids_{type_}"])
+    assert scaled_error(out, GOLD[f"layer_out_{type_}"]) <= 5e-5
+    assert rel_l2(out, GOLD[f"layer_out_{type_}"]) <= 1e-5
+    _, st = oracle.moe_layer(d, x, logits, stages=True)
+    H, Cn = host.hidden, host.channels
+    assert scaled_error(s.weights.cpu().numpy()[:T * K].reshape(T, K), st["weights"]) <= 5e-5
+    assert scaled_error(s.hidden.cpu().numpy()[:T * K * H].reshape(T, K, H), st["activated"]) <= 5e-5
+    assert scaled_error(s.routed.cpu().numpy()[:T * K * Cn].reshape(T, K, Cn), st["routed"]) <= 5e-5
+    assert scaled_error(s.shared_hidden.cpu().numpy()[:T * H].reshape(T, H), st["shared_act"]) <= 5e-5
+    assert scaled_error(s.shared_out.cpu().numpy()[:T * Cn].reshape(T, Cn), st["shared_out"]) <= 5e-5
+    assert scaled_error(s.shared_logit.cpu().numpy()[:T], st["shared_logit"]) <= 5e-5
+
+
+@pytest.mark.parametrize("T", [1, 2, 8, 9, 29, 64])
+@pytest.mark.parametrize("type_,layout", [(12, formats.PLANAR), (12, formats.GGUF), (8, formats.PLANAR)])
+def test_layer_synthetic_quantised(oracle, T, type_, layout):
+    """N(0, 0.02) weights through this build's encoders, binary16 N(0,1) activations in and binary16 out, top-k of 16 experts
+    (so that several tokens share an expert and tiles of more than 8 routes occur)."""
+    Cn, H, E, K = 512, 256, 16, 4
+    host = L.synth_host_layer(11, Cn, H, E, K, expert_type=type_)
+    x16 = synth.activations_f16(5, T, Cn)
+    logits = synth.router_logits(6, T, E)
+    out16, s, _ = run_layer(host, layout, x16, logits, out_dtype=torch.float16)
+    assert s.error_word() == 0
+    want, st = oracle.moe_layer(host.oracle_dict(), x16.astype(np.float32), logits, threads=4, stages=True)
+    assert np.array_equal(s.ids.cpu().numpy().view(np.uint32)[:T * K].reshape(T, K), st["indices"])
+    assert scaled_error(s.routed.cpu().numpy()[:T * K * Cn].reshape(T, K, Cn), st["routed"]) <= 5e-5
+    assert rel_l2(out16.astype(np.float32), want) <= 2e-3      # the benchmark's bar, output rounded to binary16
+    out32, s2, _ = run_layer(host, layout, x16.astype(np.float32), logits)  # FP32 rows in/out: the reference API's dtype
+    assert rel_l2(out32, want) <= 1e-5 and scaled_error(out32, want) <= 5e-5
+
+
+def test_layer_mixed_encodings_reference_shape(oracle):
+    """Q4_K gate/up with a Q8_0 down and Q8_0 shared expert (the reference's planar pairing, planar_moe_v3.metal:1584),
+    channels 256 / hidden 64 as in the reference's small-M fixture (test_planar_pack_v3.cpp:449-628)."""
+    Cn, H, E, K, T = 256, 64, 8, 4, 7
+    g = fixtures.bounded_weights(12, Cn, H, E, 1)
+    u = fixtures.bounded_weights(12, Cn, H, E, 2)
+    d = fixtures.bounded_weights(8, H, Cn, E, 3)
+    sg, su, sd = (fixtures.bounded_weights(8, Cn, H, 1, 4)[0], fixtures.bounded_weights(8, Cn, H, 1, 5)[0],
+                  fixtures.bounded_weights(8, H, Cn, 1, 6)[0])
+    sr = fixtures.lcg_activations(8, Cn) * np.float32(0.1)
+    host = L.HostLayer(Cn, H, E, K, 12, 8, g, u, d, sg, su, sd, sr, down_type=8)
+    x = fixtures.lcg_activations(9, T * Cn).reshape(T, Cn) * np.float32(8)
+    logits = fixtures.lcg_activations(10, T * E).reshape(T, E)
+    out, s, _ = run_layer(host, formats.PLANAR, x, logits)
+    assert s.error_word() == 0
+    ids, w = oracle.route_rows(logits.astype(np.float64), K, 0, True)
+    want = np.zeros((T, Cn))
+    eb, db = formats.gguf_bytes(12, H, Cn), formats.gguf_bytes(8, Cn, H)
+    for t in range(T):
+        xd = x[t].astype(np.float64)
+        routed = []
+        for e in ids[t]:
+            gg, uu = oracle.gemv(12, g[e], Cn, H, xd), oracle.gemv(12, u[e], Cn, H, xd)
+            h = np.array([oracle.silu(a) for a in gg]) * uu
+            routed.append(oracle.gemv(8, d[e], H, Cn, h))
+        gg, uu = oracle.gemv(8, sg, Cn, H, xd), oracle.gemv(8, su, Cn, H, xd)
+        sh = oracle.gemv(8, sd, H, Cn, np.array([oracle.silu(a) for a in gg]) * uu)
+        want[t] = oracle.mixture(np.stack(routed), w[t], sh, float(np.dot(sr.astype(np.float64), xd)))
+    assert eb and db
+    assert np.array_equal(s.ids.cpu().numpy().view(np.uint32)[:T * K].reshape(T, K), ids)
+    assert scaled_error(out, want) <= 5e-5
+
+
+def test_sticky_error_word_and_recovery(oracle):
+    """A non-finite scale in one routed expert sets bit 1 and the graph stays usable (test_moe.cpp:175-185)."""
+    d, x, logits = golden_cases.small_layer(12)
+    host = host_from_dict(d)
+    bad = host_from_dict(dict(d, gate=d["gate"].copy()))
+    routed_expert = int(GOLD["layer_ids_12"][0, 0])
+    bad.gate[routed_expert, 0:2] = [0x00, 0x7e]  # NaN super-scale
+    out, s, _ = run_layer(bad, formats.PLANAR, x, logits)
+    assert s.error_word() & capi.ERR_NONFINITE
+    s.reset_error()
+    assert s.error_word() == 0
+    out, s2, _ = run_layer(host, formats.PLANAR, x, logits)
+    assert s2.error_word() == 0 and scaled_error(out, GOLD["layer_out_12"]) <= 5e-5
+    xbad = x.copy()
+    xbad[1, 3] = np.inf
+    _, s3, _ = run_layer(host, formats.GGUF, xbad, logits)
+    assert s3.error_word() & capi.ERR_NONFINITE

@@ -1,0 +1,280 @@
+// C ABI of the MoE hot path: argument validation (refused before any launch, as the reference's
+// FormatError checks are), then the launches. No entry point allocates, frees or reads results back
+// except tsp_error_word_read, which is the once-per-batch readback of the sticky error word.
+#include <cstdarg>
+#include <cstdio>
+
+#include "tsp_common.cuh"
+
+namespace tsp {
+
+static thread_local char g_message[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_message, sizeof g_message, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    snprintf(g_message, sizeof g_message, "CUDA error %d (%s) at %s", static_cast<int>(e), cudaGetErrorString(e), what);
+    return TSP_E_CUDA;
+}
+
+int sm_count() {
+    static thread_local int cached_device = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev != cached_device) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached = n;
+        cached_device = dev;
+    }
+    return cached;
+}
+
+// launchers implemented in the kernel files
+int launch_route(const float*, uint64_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, float*, uint32_t*, cudaStream_t);
+int launch_permute(const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, uint32_t*, uint32_t*, uint32_t*, cudaStream_t);
+int launch_combine(const float*, uint64_t, const float*, const float*, uint64_t, const float*, const float*, uint64_t, float*,
+                   uint32_t, uint32_t, uint32_t, float*, uint64_t, void*, uint64_t, uint32_t*, cudaStream_t);
+int launch_f16_to_f32(const void*, uint64_t, float*, uint64_t, uint32_t, uint32_t, cudaStream_t);
+int launch_dequant(uint32_t, uint32_t, const uint8_t*, uint64_t, float*, uint32_t*, cudaStream_t);
+int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*, uint64_t, uint32_t, uint32_t,
+                const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t);
+
+static int check_matrix(const tsp_matrix_set* m, const char* name) {
+    TSP_REQUIRE(m != nullptr, "%s: null matrix set", name);
+    if (m->type != TSP_TYPE_Q4_K && m->type != TSP_TYPE_Q8_0) return fail(TSP_E_TYPE, "%s: encoding %u has no kernel", name, m->type);
+    if (m->layout != TSP_LAYOUT_GGUF && m->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "%s: unknown layout %u", name, m->layout);
+    TSP_REQUIRE(m->base && aligned16(m->base), "%s: base must be a 16-byte aligned device pointer", name);
+    TSP_REQUIRE(m->experts >= 1 && m->experts <= 4096, "%s: experts out of range", name);
+    TSP_REQUIRE(m->rows >= 8 && m->rows % 8 == 0 && m->rows <= 1u << 20, "%s: rows must be a multiple of 8", name);
+    const uint32_t block = m->type == TSP_TYPE_Q4_K ? 256u : 32u;
+    TSP_REQUIRE(m->cols >= block && m->cols % block == 0 && m->cols <= 65536, "%s: columns must be a multiple of %u", name, block);
+    const uint64_t bytes = tsp_expert_bytes(m->type, m->layout, m->rows, m->cols);
+    TSP_REQUIRE(bytes != 0, "%s: shape not representable in this layout", name);
+    if (m->experts > 1 || m->split < m->experts) {
+        TSP_REQUIRE(m->expert_stride >= bytes && m->expert_stride % 16 == 0, "%s: expert stride too small or unaligned", name);
+    }
+    if (m->split < m->experts) TSP_REQUIRE(m->base_hi && aligned16(m->base_hi), "%s: base_hi must be a 16-byte aligned device pointer", name);
+    return TSP_OK;
+}
+
+static int check_rows(const void* p, uint64_t stride, uint32_t cols, uint32_t elem, const char* name) {
+    TSP_REQUIRE(p && aligned16(p), "%s: rows must be 16-byte aligned", name);
+    TSP_REQUIRE(stride >= static_cast<uint64_t>(cols) * elem && stride % 16 == 0, "%s: row stride must cover the row and be a multiple of 16", name);
+    return TSP_OK;
+}
+
+static bool overlap(const void* a, uint64_t abytes, const void* b, uint64_t bbytes) {
+    const uintptr_t x = reinterpret_cast<uintptr_t>(a), y = reinterpret_cast<uintptr_t>(b);
+    return x < y + bbytes && y < x + abytes;
+}
+
+}  // namespace tsp
+
+using namespace tsp;
+
+extern "C" {
+
+const char* tsp_last_error(void) { return g_message; }
+
+int tsp_device_info(int* sms, int* major, int* minor) {
+    int dev = 0;
+    TSP_CUDA(cudaGetDevice(&dev));
+    int n = 0, ma = 0, mi = 0;
+    TSP_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    TSP_CUDA(cudaDeviceGetAttribute(&ma, cudaDevAttrComputeCapabilityMajor, dev));
+    TSP_CUDA(cudaDeviceGetAttribute(&mi, cudaDevAttrComputeCapabilityMinor, dev));
+    if (sms) *sms = n;
+    if (major) *major = ma;
+    if (minor) *minor = mi;
+    return TSP_OK;
+}
+
+int tsp_error_word_read(const uint32_t* d_error, void* stream, uint32_t* host_word) {
+    TSP_REQUIRE(d_error && host_word, "error word pointers must not be null");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    TSP_CUDA(cudaMemcpyAsync(host_word, d_error, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    TSP_CUDA(cudaStreamSynchronize(st));
+    if (*host_word) return fail(TSP_E_DEVICE, "device error word 0x%x:%s%s%s", *host_word,
+                                (*host_word & TSP_ERR_NONFINITE) ? " non-finite value" : "",
+                                (*host_word & TSP_ERR_INDEX) ? " bad index/geometry" : "",
+                                (*host_word & TSP_ERR_TIMEOUT) ? " bounded wait expired" : "");
+    return TSP_OK;
+}
+
+int tsp_error_word_reset(uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_error, "error word pointer must not be null");
+    TSP_CUDA(cudaMemsetAsync(d_error, 0, sizeof(uint32_t), static_cast<cudaStream_t>(stream)));
+    return TSP_OK;
+}
+
+uint64_t tsp_expert_bytes(uint32_t type, uint32_t layout, uint32_t rows, uint32_t cols) {
+    if (!rows || !cols) return 0;
+    if (type == TSP_TYPE_Q4_K) {
+        if (cols % 256) return 0;
+        if (layout == TSP_LAYOUT_PLANAR && rows % 4) return 0;
+        return static_cast<uint64_t>(rows) * (cols / 256) * (layout == TSP_LAYOUT_PLANAR ? 148u : 144u);
+    }
+    if (type == TSP_TYPE_Q8_0) {
+        if (cols % 32) return 0;
+        const uint64_t blocks = static_cast<uint64_t>(rows) * (cols / 32);
+        if (layout == TSP_LAYOUT_PLANAR && (rows % 4 || blocks % 8)) return 0;
+        return blocks * 34u;
+    }
+    return 0;
+}
+
+int tsp_dequant_f32(const tsp_matrix_set* m, uint32_t expert, float* d_out, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(m, "dequant")) return rc;
+    TSP_REQUIRE(expert < m->experts, "dequant: expert %u out of range", expert);
+    TSP_REQUIRE(d_out, "dequant: null output");
+    const uint8_t* base = static_cast<const uint8_t*>(expert < m->split ? m->base : m->base_hi);
+    const uint32_t local = expert < m->split ? expert : expert - m->split;
+    const uint64_t blocks = static_cast<uint64_t>(m->rows) * (m->cols / (m->type == TSP_TYPE_Q4_K ? 256 : 32));
+    TSP_REQUIRE(blocks < (1ull << 31), "dequant: matrix too large");
+    return launch_dequant(m->type, m->layout, base + local * m->expert_stride, blocks, d_out, d_error, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_route(const float* d_logits, uint64_t stride, uint32_t tokens, uint32_t experts, uint32_t selected,
+                  uint32_t mode, int normalize, uint32_t* d_ids, float* d_weights, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_logits && d_ids && d_weights, "route: null buffer");
+    TSP_REQUIRE(tokens >= 1, "route: no token rows");
+    TSP_REQUIRE(experts >= 1 && experts <= 4096 && selected >= 1 && selected <= 64 && selected <= experts && mode <= 1,
+                "route: invalid router shape/mode");
+    TSP_REQUIRE(stride >= static_cast<uint64_t>(experts) * 4 && stride % 4 == 0, "route: logits stride too small");
+    return launch_route(d_logits, stride, tokens, experts, selected, mode, normalize, d_ids, d_weights, d_error,
+                        static_cast<cudaStream_t>(stream));
+}
+
+uint64_t tsp_moe_tasks_words(uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile) {
+    if (!tile) return 0;
+    return 2 + 2 * ((static_cast<uint64_t>(tokens) * selected) / tile + experts);
+}
+
+int tsp_moe_permute(const uint32_t* d_ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile,
+                    uint32_t* d_token_map, uint32_t* d_counts, uint32_t* d_tasks, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_ids && d_token_map && d_counts && d_tasks, "permute: null buffer");
+    TSP_REQUIRE(tokens >= 1 && experts >= 1 && experts <= 4096 && selected >= 1 && selected <= 64 && selected <= experts,
+                "permute: invalid shape");
+    TSP_REQUIRE(tile >= 1 && tile <= 1024, "permute: tile out of range");
+    TSP_REQUIRE(static_cast<uint64_t>(tokens) * selected < (1ull << 31), "permute: too many routes");
+    return launch_permute(d_ids, tokens, experts, selected, tile, d_token_map, d_counts, d_tasks, d_error,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_gate_up_swiglu(const tsp_matrix_set* gate, const tsp_matrix_set* up, const float* d_x, uint64_t x_stride,
+                           uint32_t tokens, uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts,
+                           const uint32_t* d_tasks, float* d_h, uint64_t h_stride, int f16_exact, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(gate, "gate")) return rc;
+    if (int rc = check_matrix(up, "up")) return rc;
+    TSP_REQUIRE(gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
+                gate->experts == up->experts && gate->expert_stride == up->expert_stride && gate->split == up->split,
+                "gate/up matrix sets must share shape, encoding, layout and addressing");
+    TSP_REQUIRE(tokens >= 1, "gate-up: no token rows");
+    if (int rc = check_rows(d_x, x_stride, gate->cols, 4, "gate-up input")) return rc;
+    if (int rc = check_rows(d_h, h_stride, gate->rows, 4, "gate-up output")) return rc;
+    const bool routed = d_token_map != nullptr;
+    TSP_REQUIRE(routed == (d_counts != nullptr) && routed == (d_tasks != nullptr), "gate-up: token map, counts and tasks go together");
+    TSP_REQUIRE(routed || gate->experts == 1, "gate-up: an expert set needs the route tables");
+    if (routed) TSP_REQUIRE(selected >= 1 && selected <= 64, "gate-up: selected out of range");
+    const uint64_t out_rows = routed ? static_cast<uint64_t>(tokens) * selected : tokens;
+    TSP_REQUIRE(!overlap(d_x, tokens * x_stride, d_h, out_rows * h_stride), "gate-up: input and output overlap");
+    const int nc = (!routed && tokens > 8) ? 2 : 1;
+    return launch_gemv(gate, up, true, d_x, x_stride, routed ? selected : 1, tokens, d_token_map, d_counts, d_tasks, d_h, h_stride,
+                       f16_exact, nc, d_error, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_project(const tsp_matrix_set* w, const float* d_in, uint64_t in_stride, uint32_t in_div, uint32_t tokens,
+                    uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks,
+                    float* d_out, uint64_t out_stride, int f16_exact, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(w, "project")) return rc;
+    TSP_REQUIRE(tokens >= 1, "project: no token rows");
+    TSP_REQUIRE(w->rows % 16 == 0, "project: rows must be a multiple of 16");
+    if (int rc = check_rows(d_in, in_stride, w->cols, 4, "project input")) return rc;
+    if (int rc = check_rows(d_out, out_stride, w->rows, 4, "project output")) return rc;
+    const bool routed = d_token_map != nullptr;
+    TSP_REQUIRE(routed == (d_counts != nullptr) && routed == (d_tasks != nullptr), "project: token map, counts and tasks go together");
+    TSP_REQUIRE(routed || w->experts == 1, "project: an expert set needs the route tables");
+    if (routed) TSP_REQUIRE(selected >= 1 && selected <= 64 && (in_div == 1 || in_div == selected), "project: selected / in_div out of range");
+    const uint64_t out_rows = routed ? static_cast<uint64_t>(tokens) * selected : tokens;
+    const uint64_t in_rows = routed ? out_rows / (in_div ? in_div : 1) : tokens;
+    TSP_REQUIRE(!overlap(d_in, in_rows * in_stride, d_out, out_rows * out_stride), "project: input and output overlap");
+    const int nc = (!routed && tokens > 8) ? 2 : 1;
+    return launch_gemv(w, nullptr, false, d_in, in_stride, routed ? (in_div ? in_div : 1) : 1, tokens, d_token_map, d_counts, d_tasks,
+                       d_out, out_stride, f16_exact, nc, d_error, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_combine(const float* d_routed, uint64_t routed_stride, const float* d_weights, const float* d_shared,
+                    uint64_t shared_stride, const float* d_shared_router, const float* d_x, uint64_t x_stride,
+                    float* d_shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected, float* d_out,
+                    uint64_t out_stride, void* d_out_f16, uint64_t out_f16_stride, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_routed && d_weights && d_shared && (d_out || d_out_f16), "combine: null buffer");
+    TSP_REQUIRE(tokens >= 1 && channels >= 1 && channels <= 65536 && selected >= 1 && selected <= 64, "combine: mixture shape mismatch");
+    TSP_REQUIRE(routed_stride >= channels * 4ull && shared_stride >= channels * 4ull && routed_stride % 4 == 0 &&
+                shared_stride % 4 == 0, "combine: row stride too small");
+    if (d_out) TSP_REQUIRE(out_stride >= channels * 4ull && out_stride % 4 == 0, "combine: output row stride too small");
+    if (d_shared_router) TSP_REQUIRE(d_x && x_stride >= channels * 4ull && x_stride % 4 == 0, "combine: the shared router needs the input rows");
+    if (d_out_f16) TSP_REQUIRE(out_f16_stride >= channels * 2ull && out_f16_stride % 2 == 0, "combine: binary16 output stride too small");
+    if (d_out) TSP_REQUIRE(!overlap(d_out, tokens * out_stride, d_routed, static_cast<uint64_t>(tokens) * selected * routed_stride) &&
+                           !overlap(d_out, tokens * out_stride, d_shared, tokens * shared_stride), "combine: output overlaps an input");
+    return launch_combine(d_routed, routed_stride, d_weights, d_shared, shared_stride, d_shared_router, d_x, x_stride,
+                          d_shared_logit, tokens, channels, selected, d_out, out_stride, d_out_f16, out_f16_stride, d_error,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride, float* d_out, uint64_t out_stride, uint32_t rows,
+                        uint32_t cols, void* stream) {
+    TSP_REQUIRE(d_in && d_out && rows >= 1 && cols >= 1, "convert: null buffer or empty shape");
+    TSP_REQUIRE(in_stride >= cols * 2ull && in_stride % 2 == 0 && out_stride >= cols * 4ull && out_stride % 4 == 0, "convert: row stride too small");
+    TSP_REQUIRE(rows <= 65535, "convert: too many rows");
+    return launch_f16_to_f32(d_in, in_stride, d_out, out_stride, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, const void* d_x, uint64_t x_stride,
+                         uint32_t x_dtype, const float* d_logits, uint64_t logits_stride, uint32_t tokens,
+                         uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected, uint32_t mode,
+                         int normalize, void* d_out, uint64_t out_stride, uint32_t out_dtype, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(w && s && d_x && d_logits && d_out, "layer: null argument");
+    TSP_REQUIRE(tokens >= 1 && tokens <= s->capacity, "layer: %u token rows exceed the scratch capacity %u", tokens, s->capacity);
+    TSP_REQUIRE(x_dtype <= 1 && out_dtype <= 1, "layer: activation dtype must be 0 (FP32) or 1 (binary16)");
+    TSP_REQUIRE(w->gate.rows == hidden && w->gate.cols == channels && w->gate.experts == experts &&
+                w->down.rows == channels && w->down.cols == hidden && w->down.experts == experts &&
+                w->shared_gate.rows == hidden && w->shared_gate.cols == channels && w->shared_gate.experts == 1 &&
+                w->shared_up.experts == 1 && w->shared_down.rows == channels && w->shared_down.cols == hidden &&
+                w->shared_down.experts == 1, "layer: weight shapes do not match the layer shape");
+    TSP_REQUIRE(s->d_ids && s->d_weights && s->d_hidden && s->d_routed && s->d_shared_hidden && s->d_shared_out &&
+                s->d_token_map && s->d_counts && s->d_tasks, "layer: incomplete scratch");
+    TSP_REQUIRE(x_dtype == 0 || s->d_x32, "layer: binary16 input needs the d_x32 staging rows");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const float* x32 = static_cast<const float*>(d_x);
+    uint64_t x32_stride = x_stride;
+    if (x_dtype == 1) {
+        if (int rc = tsp_rows_f16_to_f32(d_x, x_stride, s->d_x32, channels * 4ull, tokens, channels, st)) return rc;
+        x32 = s->d_x32;
+        x32_stride = channels * 4ull;
+    }
+    const int exact = x_dtype == 1;
+    if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
+    if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GEMV_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
+    if (int rc = tsp_moe_gate_up_swiglu(&w->gate, &w->up, x32, x32_stride, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
+                                        s->d_hidden, hidden * 4ull, exact, d_error, st)) return rc;
+    if (int rc = tsp_moe_project(&w->down, s->d_hidden, hidden * 4ull, 1, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
+                                 s->d_routed, channels * 4ull, 0, d_error, st)) return rc;
+    if (int rc = tsp_moe_gate_up_swiglu(&w->shared_gate, &w->shared_up, x32, x32_stride, tokens, 1, nullptr, nullptr, nullptr,
+                                        s->d_shared_hidden, hidden * 4ull, exact, d_error, st)) return rc;
+    if (int rc = tsp_moe_project(&w->shared_down, s->d_shared_hidden, hidden * 4ull, 1, tokens, 1, nullptr, nullptr, nullptr,
+                                 s->d_shared_out, channels * 4ull, 0, d_error, st)) return rc;
+    // binary16 output rows are written straight from the FP32 mixture; no FP32 copy of the output is kept
+    return tsp_moe_combine(s->d_routed, channels * 4ull, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32,
+                           x32_stride, s->d_shared_logit, tokens, channels, selected,
+                           out_dtype == 0 ? static_cast<float*>(d_out) : nullptr, out_dtype == 0 ? out_stride : 0,
+                           out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
+}
+
+}  // extern "C"

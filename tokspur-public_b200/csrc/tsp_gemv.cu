@@ -1,0 +1,564 @@
+// Decode-size routed / dense projections over block-quantised weights (Q4_K, Q8_0; GGUF rows or
+// Pack v3 planar planes) for sm_100a.
+//
+// Shape of the kernel
+//   * persistent CTAs, one per SM, each owning a contiguous range of work items; an item is one
+//     tile of <= 8*NC routes of one expert x one slab of weight rows over the full K extent;
+//   * one producer warp streams the slab's bytes global -> shared with bulk asynchronous copies
+//     (TMA, untiled form) into a ring of stages guarded by full/empty mbarriers, so the bytes in
+//     flight per SM do not depend on registers or occupancy;
+//   * eight consumer warps dequantise in registers and feed warp-level tensor-core MMAs
+//     (m16n8k16, f16 x f16 -> f32): weight codes enter as *exact* small integers (binary16
+//     subnormals q*2^-24), activations as binary16 high (+ optional low) halves, and the per-group
+//     scales/mins are applied to the FP32 partial sums, so the result carries FP32-level error only;
+//   * every wait is bounded; a timeout sets TSP_ERR_TIMEOUT in the sticky error word.
+//
+// The reduction index inside one 8-wide run of K is permuted identically for weights and
+// activations (order 0,2,1,3,4,6,5,7): a 32-bit word of codes then splits into MMA register
+// pairs with two masks and one shift, with no cross-lane movement.
+#include "tsp_common.cuh"
+
+namespace tsp {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kGemvThreads = (kConsumerWarps + 1) * 32;
+constexpr uint32_t kMaxStages = 6;
+
+struct GemvParams {
+    // weights
+    const uint8_t* a_base; const uint8_t* a_base_hi;   // matrix set A (gate, or the only matrix)
+    const uint8_t* b_base; const uint8_t* b_base_hi;   // matrix set B (up); unused for plain projections
+    uint64_t expert_stride;
+    uint32_t split;        // experts >= split live under *_base_hi
+    uint32_t experts;
+    uint32_t rows;         // rows of ONE matrix (gate-up: hidden units)
+    uint32_t cols;         // K
+    uint32_t nunit;        // K units per row: Q4_K super-blocks of 256, Q8_0 blocks of 32
+    uint64_t sm_off, dm_off;  // planar plane offsets inside one expert
+    // item geometry
+    uint32_t rows_per_item;   // rows of ONE matrix covered by an item (gate-up: hidden units)
+    uint32_t items_per_matrix;
+    uint32_t nrt;             // MMA row tiles per item
+    uint32_t row_bytes;       // bytes copied per row into the quant area (0: one contiguous copy per matrix)
+    uint32_t row_stride;      // shared-memory stride between rows of the quant area
+    uint32_t quant_bytes;     // quant area bytes per stage
+    uint32_t sm_bytes_item;   // planar Q4_K: bytes of the sm plane per matrix per full item
+    uint32_t dm_bytes_item;   // planar: bytes of the dm plane per matrix per full item
+    uint32_t stage_bytes, n_stages;
+    // shared memory carve-up (byte offsets from the dynamic base)
+    uint32_t off_xhi, off_xlo, off_sx, off_red, off_stage;
+    uint32_t x_stride, sx_stride;
+    // activations / routes
+    const float* x; uint64_t x_stride_bytes; uint32_t in_div;
+    const uint32_t* token_map; const uint32_t* counts; const uint32_t* tasks;
+    uint32_t tokens;          // token rows (token_map row length); dense: number of rows
+    float* out; uint64_t out_stride_bytes;
+    int split_lo;
+    uint32_t* error;
+};
+
+__device__ __forceinline__ uint64_t lds64(const uint8_t* p) { return *reinterpret_cast<const uint64_t*>(p); }
+__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+
+__device__ __forceinline__ const uint8_t* expert_ptr(const uint8_t* base, const uint8_t* base_hi, uint32_t e,
+                                                     uint32_t split, uint64_t stride) {
+    return e < split ? base + static_cast<uint64_t>(e) * stride : base_hi + static_cast<uint64_t>(e - split) * stride;
+}
+
+// Work item -> (expert, first route of the tile, routes in the tile)
+struct TileInfo { uint32_t expert, start, count; };
+
+template <int NC>
+__device__ __forceinline__ TileInfo tile_info(const GemvParams& p, uint32_t tile) {
+    TileInfo t;
+    if (p.token_map) {
+        t.expert = p.tasks[2 + 2 * tile];
+        t.start = p.tasks[3 + 2 * tile];
+        const uint32_t c = t.expert < p.experts ? p.counts[t.expert] : 0u;
+        t.count = c > t.start ? min(c - t.start, 8u * NC) : 0u;
+        if (t.expert >= p.experts) { t.expert = 0; t.count = 0; }
+    } else {
+        t.expert = 0;
+        t.start = tile * 8u * NC;
+        t.count = min(p.tokens - t.start, 8u * NC);
+    }
+    return t;
+}
+
+template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + kMaxStages;
+    uint32_t* rids = reinterpret_cast<uint32_t*>(smem + 128);  // route ids of the staged tile, 8*NC entries
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t NS = p.n_stages;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < NS; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kConsumerWarps); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const uint32_t n_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
+    const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.items_per_matrix;
+    const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
+    const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
+    constexpr uint32_t NMAT = GATEUP ? 2 : 1;
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------ producer warp ------------------------------
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (uint32_t item = item0; item < item1 && ok; ++item) {
+            const uint32_t tile = item / p.items_per_matrix, ri = item % p.items_per_matrix;
+            const TileInfo ti = tile_info<NC>(p, tile);
+            const uint32_t r0 = ri * p.rows_per_item;
+            const uint32_t nr = min(p.rows_per_item, p.rows - r0);
+            if (lane == 0) ok = mbar_wait(&empty[stage], phase ^ 1u);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { if (lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT); break; }
+            uint8_t* sbase = smem + p.off_stage + stage * p.stage_bytes;
+            // bytes this fill will deliver
+            uint32_t total = 0;
+            if (p.row_bytes) total += NMAT * nr * p.row_bytes; else total += NMAT * nr * p.nunit * 34u;
+            if (LAYOUT == TSP_LAYOUT_PLANAR) {
+                if (TYPE == TSP_TYPE_Q4_K) total += NMAT * nr * p.nunit * 20u; else total += NMAT * nr * p.nunit * 2u;
+            }
+            if (lane == 0) mbar_arrive_expect_tx(&full[stage], total);
+            __syncwarp();
+#pragma unroll
+            for (uint32_t m = 0; m < NMAT; ++m) {
+                const uint8_t* eb = m == 0 ? expert_ptr(p.a_base, p.a_base_hi, ti.expert, p.split, p.expert_stride)
+                                           : expert_ptr(p.b_base, p.b_base_hi, ti.expert, p.split, p.expert_stride);
+                uint8_t* qdst = sbase + m * p.rows_per_item * p.row_stride;
+                if (p.row_bytes) {
+                    const uint8_t* src = eb + static_cast<uint64_t>(r0) * p.row_bytes;
+                    for (uint32_t r = lane; r < nr; r += 32)
+                        bulk_g2s(qdst + r * p.row_stride, src + static_cast<uint64_t>(r) * p.row_bytes, p.row_bytes, &full[stage]);
+                } else if (lane == 0) {
+                    bulk_g2s(qdst, eb + static_cast<uint64_t>(r0) * p.nunit * 34u, nr * p.nunit * 34u, &full[stage]);
+                }
+                if (LAYOUT == TSP_LAYOUT_PLANAR && lane == 1) {
+                    if (TYPE == TSP_TYPE_Q4_K) {
+                        bulk_g2s(sbase + p.quant_bytes + m * p.sm_bytes_item, eb + p.sm_off + static_cast<uint64_t>(r0) * p.nunit * 16u,
+                                 nr * p.nunit * 16u, &full[stage]);
+                        bulk_g2s(sbase + p.quant_bytes + NMAT * p.sm_bytes_item + m * p.dm_bytes_item,
+                                 eb + p.dm_off + static_cast<uint64_t>(r0) * p.nunit * 4u, nr * p.nunit * 4u, &full[stage]);
+                    } else {
+                        bulk_g2s(sbase + p.quant_bytes + m * p.dm_bytes_item, eb + p.dm_off + static_cast<uint64_t>(r0) * p.nunit * 2u,
+                                 nr * p.nunit * 2u, &full[stage]);
+                    }
+                }
+            }
+            if (++stage == NS) { stage = 0; phase ^= 1u; }
+        }
+        return;
+    }
+
+    // -------------------------------- consumer warps --------------------------------
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t ctid = threadIdx.x;  // 0..255
+    constexpr uint32_t CTHREADS = kConsumerWarps * 32;
+    const uint32_t nrt = p.nrt;
+    const uint32_t kp_count = nrt >= kConsumerWarps ? 1u : kConsumerWarps / nrt;
+    const uint32_t my_kp = nrt >= kConsumerWarps ? 0u : warp / nrt;
+    uint8_t* xhi = smem + p.off_xhi;
+    uint8_t* xlo = smem + p.off_xlo;
+    uint8_t* sxb = smem + p.off_sx;
+    float* red = reinterpret_cast<float*>(smem + p.off_red);
+    uint32_t stage = 0, phase = 0, cur_tile = 0xffffffffu, parity = 0;
+    bool ok = true;
+    TileInfo ti{0, 0, 0};
+    for (uint32_t item = item0; item < item1; ++item) {
+        const uint32_t tile = item / p.items_per_matrix, ri = item % p.items_per_matrix;
+        if (tile != cur_tile) {
+            // ---- stage the tile's activation rows: binary16 hi/lo in permuted order + group sums ----
+            named_bar_sync(1, CTHREADS);
+            ti = tile_info<NC>(p, tile);
+            if (ctid < 8u * NC) {
+                uint32_t rid = 0;
+                if (ctid < ti.count) rid = p.token_map ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + ctid] : ti.start + ctid;
+                rids[ctid] = rid;
+            }
+            named_bar_sync(1, CTHREADS);
+            const uint32_t per_row = p.cols / 8;
+            const uint32_t units = ti.count * per_row;
+            bool bad = false;
+            for (uint32_t base = 0; base < units; base += CTHREADS) {
+                const uint32_t u = base + ctid;
+                const bool active = u < units;
+                float s = 0.f;
+                uint32_t j = 0, k8 = 0;
+                if (active) {
+                    j = u / per_row; k8 = u % per_row;
+                    const uint32_t in_row = rids[j] / p.in_div;
+                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + k8 * 2;
+                    const float4 v0 = src[0], v1 = src[1];
+                    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    __half h[8], l[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        h[i] = __float2half_rn(v[i]);
+                        const float hf = __half2float(h[i]);
+                        bad |= !finite_f32(hf);
+                        l[i] = __float2half_rn(v[i] - hf);
+                        s += v[i];
+                    }
+                    // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
+                    uint4 ph, pl;
+                    ph.x = __half_as_ushort(h[0]) | (uint32_t(__half_as_ushort(h[2])) << 16);
+                    ph.y = __half_as_ushort(h[1]) | (uint32_t(__half_as_ushort(h[3])) << 16);
+                    ph.z = __half_as_ushort(h[4]) | (uint32_t(__half_as_ushort(h[6])) << 16);
+                    ph.w = __half_as_ushort(h[5]) | (uint32_t(__half_as_ushort(h[7])) << 16);
+                    *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) = ph;
+                    if (p.split_lo) {
+                        pl.x = __half_as_ushort(l[0]) | (uint32_t(__half_as_ushort(l[2])) << 16);
+                        pl.y = __half_as_ushort(l[1]) | (uint32_t(__half_as_ushort(l[3])) << 16);
+                        pl.z = __half_as_ushort(l[4]) | (uint32_t(__half_as_ushort(l[6])) << 16);
+                        pl.w = __half_as_ushort(l[5]) | (uint32_t(__half_as_ushort(l[7])) << 16);
+                        *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) = pl;
+                    }
+                }
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                if (active && (k8 & 3u) == 0) {
+                    const uint32_t grp = k8 >> 2;
+                    if (TYPE == TSP_TYPE_Q4_K) {
+                        const __half sh = __float2half_rn(s);
+                        const __half sl = __float2half_rn(s - __half2float(sh));
+                        bad |= !finite_f32(__half2float(sh));
+                        *reinterpret_cast<__half*>(sxb + j * p.sx_stride + grp * 2) = sh;
+                        *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
+                    } else {
+                        bad |= !finite_f32(s);
+                        *reinterpret_cast<float*>(sxb + j * p.sx_stride + grp * 4) = s;
+                    }
+                }
+            }
+            if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
+            named_bar_sync(1, CTHREADS);
+            cur_tile = tile;
+        }
+
+        // ---- wait for the slab ----
+        if (ok) {
+            ok = mbar_wait(&full[stage], phase);
+            if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
+        }
+        const uint8_t* sbase = smem + p.off_stage + stage * p.stage_bytes;
+        const uint32_t r0 = ri * p.rows_per_item;
+
+        for (uint32_t rt = (nrt >= kConsumerWarps ? warp : warp % nrt); rt < nrt; rt += kConsumerWarps) {
+            float total[NC][4];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) { total[c][0] = total[c][1] = total[c][2] = total[c][3] = 0.f; }
+            // shared-memory rows of this lane's two MMA row slots
+            const uint32_t rowA = GATEUP ? rt * 8 + g : rt * 16 + g;
+            const uint32_t rowB = GATEUP ? p.rows_per_item + rt * 8 + g : rt * 16 + 8 + g;
+            const uint8_t* qA = sbase + rowA * p.row_stride;
+            const uint8_t* qB = sbase + rowB * p.row_stride;
+            if (ok) {
+                for (uint32_t b = my_kp; b < p.nunit; b += kp_count) {
+                    if (TYPE == TSP_TYPE_Q4_K) {
+                        // ---- header of the super-block for both rows: d, dmin, sc[8], mn[8] ----
+                        uint32_t dmA, dmB, scA[2], scB[2], mnA[2], mnB[2];
+                        const uint8_t *qsA, *qsB;
+                        if (LAYOUT == TSP_LAYOUT_PLANAR) {
+                            const uint8_t* smp = sbase + p.quant_bytes;
+                            const uint8_t* dmp = smp + NMAT * p.sm_bytes_item;
+                            const uint4 sa = lds128(smp + (rowA * p.nunit + b) * 16);
+                            const uint4 sb = lds128(smp + (rowB * p.nunit + b) * 16);
+                            scA[0] = sa.x; scA[1] = sa.y; mnA[0] = sa.z; mnA[1] = sa.w;
+                            scB[0] = sb.x; scB[1] = sb.y; mnB[0] = sb.z; mnB[1] = sb.w;
+                            dmA = lds32(dmp + (rowA * p.nunit + b) * 4);
+                            dmB = lds32(dmp + (rowB * p.nunit + b) * 4);
+                            qsA = qA + b * 128; qsB = qB + b * 128;
+                        } else {
+                            const uint4 ha = lds128(qA + b * 144), hb = lds128(qB + b * 144);
+                            dmA = ha.x; dmB = hb.x;
+                            scA[0] = ha.y & 0x3f3f3f3fu; mnA[0] = ha.z & 0x3f3f3f3fu;
+                            scA[1] = (ha.w & 0x0f0f0f0fu) | ((ha.y >> 2) & 0x30303030u);
+                            mnA[1] = ((ha.w >> 4) & 0x0f0f0f0fu) | ((ha.z >> 2) & 0x30303030u);
+                            scB[0] = hb.y & 0x3f3f3f3fu; mnB[0] = hb.z & 0x3f3f3f3fu;
+                            scB[1] = (hb.w & 0x0f0f0f0fu) | ((hb.y >> 2) & 0x30303030u);
+                            mnB[1] = ((hb.w >> 4) & 0x0f0f0f0fu) | ((hb.z >> 2) & 0x30303030u);
+                            qsA = qA + b * 144 + 16; qsB = qB + b * 144 + 16;
+                        }
+                        const float dA = half_bits_to_float(dmA & 0xffffu), mA = half_bits_to_float(dmA >> 16);
+                        const float dB = half_bits_to_float(dmB & 0xffffu), mB = half_bits_to_float(dmB >> 16);
+                        // ---- min term: sum_g mn_g * Sx_g on the tensor cores (codes as subnormals, Sx as hi+lo) ----
+                        const uint32_t mnpA = __byte_perm((((t & 2u) ? mnA[1] : mnA[0]) >> (16 * (t & 1))) & 0xffffu, 0u, 0x4140);
+                        const uint32_t mnpB = __byte_perm((((t & 2u) ? mnB[1] : mnB[0]) >> (16 * (t & 1))) & 0xffffu, 0u, 0x4140);
+                        float amin[NC][4];
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            amin[c][0] = amin[c][1] = amin[c][2] = amin[c][3] = 0.f;
+                            const uint32_t sh = lds32(sxb + (c * 8 + g) * p.sx_stride + (b * 8 + 2 * t) * 2);
+                            const uint32_t sl = lds32(sxb + (8u * NC + c * 8 + g) * p.sx_stride + (b * 8 + 2 * t) * 2);
+                            mma_f16_16816(amin[c], mnpA, mnpB, mnpA, mnpB, sh, sl);
+                        }
+                        const float dA24 = dA * 16777216.f, dB24 = dB * 16777216.f;
+                        const float dA20 = dA * 1048576.f, dB20 = dB * 1048576.f;
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const uint64_t wa = lds64(qsA + j * 32 + t * 8), wb = lds64(qsB + j * 32 + t * 8);
+                            const uint32_t a0 = static_cast<uint32_t>(wa), a1 = static_cast<uint32_t>(wa >> 32);
+                            const uint32_t b0 = static_cast<uint32_t>(wb), b1 = static_cast<uint32_t>(wb >> 32);
+                            const uint32_t a0s = a0 >> 8, a1s = a1 >> 8, b0s = b0 >> 8, b1s = b1 >> 8;
+                            const uint32_t sw_a = scA[j >> 1] >> (16 * (j & 1)), sw_b = scB[j >> 1] >> (16 * (j & 1));
+                            const float fAl = dA24 * static_cast<float>(sw_a & 0xffu), fAh = dA20 * static_cast<float>((sw_a >> 8) & 0xffu);
+                            const float fBl = dB24 * static_cast<float>(sw_b & 0xffu), fBh = dB20 * static_cast<float>((sw_b >> 8) & 0xffu);
+#pragma unroll
+                            for (int c = 0; c < NC; ++c) {
+                                const uint8_t* xr = xhi + (c * 8 + g) * p.x_stride + (b * 256 + j * 64 + t * 8) * 2;
+                                const uint4 xl = lds128(xr), xh = lds128(xr + 64);
+                                float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
+                                mma_f16_16816(al, a0 & 0x000f000fu, b0 & 0x000f000fu, a0s & 0x000f000fu, b0s & 0x000f000fu, xl.x, xl.y);
+                                mma_f16_16816(al, a1 & 0x000f000fu, b1 & 0x000f000fu, a1s & 0x000f000fu, b1s & 0x000f000fu, xl.z, xl.w);
+                                mma_f16_16816(ah, a0 & 0x00f000f0u, b0 & 0x00f000f0u, a0s & 0x00f000f0u, b0s & 0x00f000f0u, xh.x, xh.y);
+                                mma_f16_16816(ah, a1 & 0x00f000f0u, b1 & 0x00f000f0u, a1s & 0x00f000f0u, b1s & 0x00f000f0u, xh.z, xh.w);
+                                if (p.split_lo) {
+                                    const uint8_t* xq = xlo + (c * 8 + g) * p.x_stride + (b * 256 + j * 64 + t * 8) * 2;
+                                    const uint4 yl = lds128(xq), yh = lds128(xq + 64);
+                                    mma_f16_16816(al, a0 & 0x000f000fu, b0 & 0x000f000fu, a0s & 0x000f000fu, b0s & 0x000f000fu, yl.x, yl.y);
+                                    mma_f16_16816(al, a1 & 0x000f000fu, b1 & 0x000f000fu, a1s & 0x000f000fu, b1s & 0x000f000fu, yl.z, yl.w);
+                                    mma_f16_16816(ah, a0 & 0x00f000f0u, b0 & 0x00f000f0u, a0s & 0x00f000f0u, b0s & 0x00f000f0u, yh.x, yh.y);
+                                    mma_f16_16816(ah, a1 & 0x00f000f0u, b1 & 0x00f000f0u, a1s & 0x00f000f0u, b1s & 0x00f000f0u, yh.z, yh.w);
+                                }
+                                total[c][0] = fmaf(fAl, al[0], total[c][0]); total[c][1] = fmaf(fAl, al[1], total[c][1]);
+                                total[c][2] = fmaf(fBl, al[2], total[c][2]); total[c][3] = fmaf(fBl, al[3], total[c][3]);
+                                total[c][0] = fmaf(fAh, ah[0], total[c][0]); total[c][1] = fmaf(fAh, ah[1], total[c][1]);
+                                total[c][2] = fmaf(fBh, ah[2], total[c][2]); total[c][3] = fmaf(fBh, ah[3], total[c][3]);
+                            }
+                        }
+                        const float mA24 = -mA * 16777216.f, mB24 = -mB * 16777216.f;
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            total[c][0] = fmaf(mA24, amin[c][0], total[c][0]); total[c][1] = fmaf(mA24, amin[c][1], total[c][1]);
+                            total[c][2] = fmaf(mB24, amin[c][2], total[c][2]); total[c][3] = fmaf(mB24, amin[c][3], total[c][3]);
+                        }
+                    } else {
+                        // ---- Q8_0 block of 32 ----
+                        uint32_t a0, a1, b0, b1, dbA, dbB;
+                        if (LAYOUT == TSP_LAYOUT_PLANAR) {
+                            const uint8_t* dmp = sbase + p.quant_bytes;
+                            const uint64_t wa = lds64(qA + b * 32 + t * 8), wb = lds64(qB + b * 32 + t * 8);
+                            a0 = static_cast<uint32_t>(wa); a1 = static_cast<uint32_t>(wa >> 32);
+                            b0 = static_cast<uint32_t>(wb); b1 = static_cast<uint32_t>(wb >> 32);
+                            dbA = *reinterpret_cast<const uint16_t*>(dmp + (rowA * p.nunit + b) * 2);
+                            dbB = *reinterpret_cast<const uint16_t*>(dmp + (rowB * p.nunit + b) * 2);
+                        } else {
+                            // 34-byte blocks leave the codes only 2-byte aligned: three aligned words + funnel shift
+                            const uint8_t* pa = qA + b * 34 + 2 + t * 8;
+                            const uint8_t* pb = qB + b * 34 + 2 + t * 8;
+                            const uint32_t sa = (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(pa)) & 3u) * 8u;
+                            const uint32_t sb = (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(pb)) & 3u) * 8u;
+                            const uint8_t* pa4 = pa - (sa >> 3);
+                            const uint8_t* pb4 = pb - (sb >> 3);
+                            const uint32_t w0 = lds32(pa4), w1 = lds32(pa4 + 4), w2 = lds32(pa4 + 8);
+                            const uint32_t v0 = lds32(pb4), v1 = lds32(pb4 + 4), v2 = lds32(pb4 + 8);
+                            a0 = __funnelshift_r(w0, w1, sa); a1 = __funnelshift_r(w1, w2, sa);
+                            b0 = __funnelshift_r(v0, v1, sb); b1 = __funnelshift_r(v1, v2, sb);
+                            dbA = *reinterpret_cast<const uint16_t*>(qA + b * 34);
+                            dbB = *reinterpret_cast<const uint16_t*>(qB + b * 34);
+                        }
+                        a0 ^= 0x80808080u; a1 ^= 0x80808080u; b0 ^= 0x80808080u; b1 ^= 0x80808080u;  // code + 128 in [0,255]
+                        const float dA = half_bits_to_float(dbA), dB = half_bits_to_float(dbB);
+                        const float fA = dA * 16777216.f, fB = dB * 16777216.f;
+                        const float oA = -128.f * dA, oB = -128.f * dB;
+                        const uint32_t pa0 = __byte_perm(a0, 0u, 0x4240), pa1 = __byte_perm(a0, 0u, 0x4341);
+                        const uint32_t pa2 = __byte_perm(a1, 0u, 0x4240), pa3 = __byte_perm(a1, 0u, 0x4341);
+                        const uint32_t pb0 = __byte_perm(b0, 0u, 0x4240), pb1 = __byte_perm(b0, 0u, 0x4341);
+                        const uint32_t pb2 = __byte_perm(b1, 0u, 0x4240), pb3 = __byte_perm(b1, 0u, 0x4341);
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            const uint4 xv = lds128(xhi + (c * 8 + g) * p.x_stride + (b * 32 + t * 8) * 2);
+                            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                            mma_f16_16816(acc, pa0, pb0, pa1, pb1, xv.x, xv.y);
+                            mma_f16_16816(acc, pa2, pb2, pa3, pb3, xv.z, xv.w);
+                            if (p.split_lo) {
+                                const uint4 yv = lds128(xlo + (c * 8 + g) * p.x_stride + (b * 32 + t * 8) * 2);
+                                mma_f16_16816(acc, pa0, pb0, pa1, pb1, yv.x, yv.y);
+                                mma_f16_16816(acc, pa2, pb2, pa3, pb3, yv.z, yv.w);
+                            }
+                            const float s0 = *reinterpret_cast<const float*>(sxb + (c * 8 + 2 * t) * p.sx_stride + b * 4);
+                            const float s1 = *reinterpret_cast<const float*>(sxb + (c * 8 + 2 * t + 1) * p.sx_stride + b * 4);
+                            total[c][0] = fmaf(fA, acc[0], fmaf(oA, s0, total[c][0]));
+                            total[c][1] = fmaf(fA, acc[1], fmaf(oA, s1, total[c][1]));
+                            total[c][2] = fmaf(fB, acc[2], fmaf(oB, s0, total[c][2]));
+                            total[c][3] = fmaf(fB, acc[3], fmaf(oB, s1, total[c][3]));
+                        }
+                    }
+                }
+            }
+            // ---- cross-warp reduction over the K parts (only when one row tile is shared by several warps) ----
+            if (kp_count > 1) {
+                float* slot = red + ((parity * kConsumerWarps + warp) * 32 + lane) * (4 * NC);
+                if (my_kp != 0) {
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) *reinterpret_cast<float4*>(slot + 4 * c) = make_float4(total[c][0], total[c][1], total[c][2], total[c][3]);
+                }
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&empty[stage]);
+                named_bar_sync(1, CTHREADS);
+                if (my_kp == 0) {
+                    for (uint32_t kp = 1; kp < kp_count; ++kp) {
+                        const float* other = red + ((parity * kConsumerWarps + kp * nrt + rt) * 32 + lane) * (4 * NC);
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            const float4 v = *reinterpret_cast<const float4*>(other + 4 * c);
+                            total[c][0] += v.x; total[c][1] += v.y; total[c][2] += v.z; total[c][3] += v.w;
+                        }
+                    }
+                }
+            }
+            // ---- epilogue ----
+            if (my_kp == 0 && ok) {
+                bool bad = false;
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const uint32_t j = c * 8 + 2 * t + q;
+                        if (j >= ti.count) continue;
+                        float* orow = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + rids[j] * p.out_stride_bytes);
+                        if (GATEUP) {
+                            const uint32_t hu = r0 + rt * 8 + g;
+                            if (hu < p.rows) {
+                                const float v = stable_silu(total[c][q]) * total[c][2 + q];
+                                bad |= !finite_f32(v);
+                                orow[hu] = v;
+                            }
+                        } else {
+                            const uint32_t r = r0 + rt * 16 + g;
+                            if (r < p.rows) { bad |= !finite_f32(total[c][q]); orow[r] = total[c][q]; }
+                            if (r + 8 < p.rows) { bad |= !finite_f32(total[c][2 + q]); orow[r + 8] = total[c][2 + q]; }
+                        }
+                    }
+                }
+                if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
+            }
+        }
+        if (kp_count == 1) {
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(&empty[stage]);
+        }
+        parity ^= 1u;
+        if (++stage == NS) { stage = 0; phase ^= 1u; }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side: geometry, shared-memory plan, launch
+// ---------------------------------------------------------------------------------------------
+static uint32_t pad_row(uint32_t row_bytes) {
+    // smallest multiple-of-16 pad that puts consecutive rows 32 or 96 bytes apart modulo 128, so the four
+    // row groups of a half-warp's 64-bit loads fall on disjoint banks
+    for (uint32_t pad = 0; pad < 128; pad += 16) {
+        const uint32_t m = (row_bytes + pad) % 128;
+        if (m == 32 || m == 96) return row_bytes + pad;
+    }
+    return row_bytes + 32;
+}
+
+template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC>
+static int launch_one(const GemvParams& p, size_t smem, int grid, cudaStream_t st) {
+    auto kernel = gemv_kernel<TYPE, LAYOUT, GATEUP, NC>;
+    static thread_local size_t configured = 0;
+    if (smem > configured) {
+        TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured = smem;
+    }
+    kernel<<<grid, kGemvThreads, smem, st>>>(p);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const float* x, uint64_t x_stride_bytes,
+                uint32_t in_div, uint32_t tokens, const uint32_t* token_map, const uint32_t* counts, const uint32_t* tasks,
+                float* out, uint64_t out_stride_bytes, int f16_exact, int nc, uint32_t* error, cudaStream_t st) {
+    GemvParams p{};
+    const uint32_t type = a->type, layout = a->layout;
+    p.a_base = static_cast<const uint8_t*>(a->base);
+    p.a_base_hi = static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base);
+    if (gateup) {
+        p.b_base = static_cast<const uint8_t*>(b->base);
+        p.b_base_hi = static_cast<const uint8_t*>(b->base_hi ? b->base_hi : b->base);
+    }
+    p.expert_stride = a->expert_stride;
+    p.split = a->split < a->experts ? a->split : a->experts;
+    p.experts = a->experts;
+    p.rows = a->rows;
+    p.cols = a->cols;
+    const bool q4 = type == TSP_TYPE_Q4_K;
+    p.nunit = q4 ? a->cols / 256 : a->cols / 32;
+    const uint64_t total_units = static_cast<uint64_t>(a->rows) * p.nunit;
+    if (layout == TSP_LAYOUT_PLANAR) {
+        p.sm_off = q4 ? total_units * 128 : 0;
+        p.dm_off = q4 ? total_units * 144 : total_units * 32;
+    }
+    // bytes of one row in the quant area
+    uint32_t row_bytes;
+    if (layout == TSP_LAYOUT_PLANAR) row_bytes = q4 ? p.nunit * 128 : p.nunit * 32;
+    else row_bytes = q4 ? p.nunit * 144 : p.nunit * 34;
+    const bool contiguous = (row_bytes % 16) != 0;  // GGUF Q8_0 rows that are not 16-byte multiples
+    p.row_bytes = contiguous ? 0 : row_bytes;
+    p.row_stride = contiguous ? row_bytes : pad_row(row_bytes);
+    // rows per stage: as many as fit ~40 KB, in MMA tiles of 16 rows
+    const uint32_t per_row_total = p.row_stride + (layout == TSP_LAYOUT_PLANAR ? (q4 ? p.nunit * 20 : p.nunit * 2) : 0);
+    uint32_t stage_rows = 128;
+    while (stage_rows > 16 && stage_rows * per_row_total > 44 * 1024) stage_rows >>= 1;
+    const uint32_t matrix_rows_cap = gateup ? a->rows * 2 : a->rows;
+    while (stage_rows > 16 && stage_rows / 2 >= matrix_rows_cap) stage_rows >>= 1;
+    if (stage_rows * per_row_total > 150 * 1024) return fail(TSP_E_ARG, "matrix rows of %u bytes do not fit a shared-memory stage", row_bytes);
+    p.nrt = stage_rows / 16;
+    p.rows_per_item = gateup ? stage_rows / 2 : stage_rows;
+    p.items_per_matrix = (a->rows + p.rows_per_item - 1) / p.rows_per_item;
+    p.quant_bytes = stage_rows * p.row_stride + 16;  // +16: the unaligned-code path may read one word past the last row
+    p.quant_bytes = (p.quant_bytes + 15u) & ~15u;
+    p.sm_bytes_item = (layout == TSP_LAYOUT_PLANAR && q4) ? p.rows_per_item * p.nunit * 16 : 0;
+    p.dm_bytes_item = layout == TSP_LAYOUT_PLANAR ? p.rows_per_item * p.nunit * (q4 ? 4 : 2) : 0;
+    const uint32_t nmat = gateup ? 2 : 1;
+    p.stage_bytes = p.quant_bytes + nmat * (p.sm_bytes_item + p.dm_bytes_item);
+    p.stage_bytes = (p.stage_bytes + 127u) & ~127u;
+    // activations
+    const uint32_t tok = 8u * static_cast<uint32_t>(nc);
+    p.split_lo = f16_exact ? 0 : 1;
+    p.x_stride = a->cols * 2 + 64;
+    const uint32_t ngroups = a->cols / 32;
+    p.sx_stride = q4 ? ngroups * 2 + 16 : ngroups * 4 + 16;
+    uint32_t off = 256;
+    p.off_xhi = off; off += tok * p.x_stride;
+    p.off_xlo = off; if (p.split_lo) off += tok * p.x_stride;
+    p.off_sx = off; off += (q4 ? 2 : 1) * tok * p.sx_stride;
+    off = (off + 15u) & ~15u;
+    p.off_red = off; off += 2 * kConsumerWarps * 32 * 4 * nc * 4;
+    off = (off + 127u) & ~127u;
+    p.off_stage = off;
+    const uint32_t budget = 227 * 1024;
+    if (off + p.stage_bytes > budget) return fail(TSP_E_ARG, "K extent of %u columns needs more shared memory than one SM has", a->cols);
+    p.n_stages = (budget - off) / p.stage_bytes;
+    if (p.n_stages > kMaxStages) p.n_stages = kMaxStages;
+    const size_t smem = off + static_cast<size_t>(p.n_stages) * p.stage_bytes;
+    p.x = x; p.x_stride_bytes = x_stride_bytes; p.in_div = in_div ? in_div : 1;
+    p.token_map = token_map; p.counts = counts; p.tasks = tasks; p.tokens = tokens;
+    p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;
+    const int grid = sm_count();
+    if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
+
+#define TSP_DISPATCH(T, L)                                                                           \
+    if (type == T && layout == L) {                                                                   \
+        if (gateup) return nc == 1 ? launch_one<T, L, true, 1>(p, smem, grid, st) : launch_one<T, L, true, 2>(p, smem, grid, st); \
+        return nc == 1 ? launch_one<T, L, false, 1>(p, smem, grid, st) : launch_one<T, L, false, 2>(p, smem, grid, st);           \
+    }
+    TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR)
+    TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_GGUF)
+    TSP_DISPATCH(TSP_TYPE_Q8_0, TSP_LAYOUT_PLANAR)
+    TSP_DISPATCH(TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF)
+#undef TSP_DISPATCH
+    return fail(TSP_E_TYPE, "no kernel for encoding %u in layout %u", type, layout);
+}
+
+}  // namespace tsp

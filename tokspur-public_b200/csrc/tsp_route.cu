@@ -1,0 +1,345 @@
+// Router top-k, stable token permutation, gated combine and the activation edge conversions.
+// All integer results (ids, token_map, counts, tasks) are deterministic and independent of
+// scheduling: no atomics decide an order anywhere.
+#include "tsp_common.cuh"
+
+namespace tsp {
+
+// ---------------------------------------------------------------------------------------------
+// route: one warp per token row. Selection order is (logit descending, id ascending), i.e. the
+// total order of route_reference (routing.cpp:15-18). Logits are compared as FP32, which orders
+// exactly as the reference's doubles do because the conversion is exact.
+// Weights are evaluated in double so that they round to the same FP32 as the reference's.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRouteWarps = 4;
+
+__device__ __forceinline__ double softplus_f64(double v) { return fmax(v, 0.0) + log1p(exp(-fabs(v))); }
+__device__ __forceinline__ double sigmoid_f64(double v) {
+    if (v >= 0) return 1.0 / (1.0 + exp(-v));
+    const double p = exp(v);
+    return p / (1.0 + p);
+}
+
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t tokens, uint32_t experts,
+             uint32_t selected, uint32_t mode, int normalize, uint32_t* __restrict__ ids,
+             float* __restrict__ weights, uint32_t* error) {
+    extern __shared__ float route_smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t token = blockIdx.x * kRouteWarps + warp;
+    if (token >= tokens) return;
+    float* row = route_smem + warp * experts;
+    const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + token * stride_bytes);
+    bool bad = false;
+    for (uint32_t e = lane; e < experts; e += 32) {
+        const float v = src[e];
+        bad |= !finite_f32(v);
+        row[e] = v;
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    __syncwarp();
+    uint32_t* out_ids = ids + static_cast<uint64_t>(token) * selected;
+    float* out_w = weights + static_cast<uint64_t>(token) * selected;
+    if (bad) {  // reference: FormatError("nonfinite router logit"); here: flag and publish a harmless row
+        if (lane == 0) raise_error(error, TSP_ERR_NONFINITE);
+        for (uint32_t r = lane; r < selected; r += 32) { out_ids[r] = r; out_w[r] = 0.f; }
+        return;
+    }
+    // full-softmax denominator (only when not renormalising over the selection)
+    double all_sum = 0;
+    float row_max = -INFINITY;
+    for (uint32_t e = lane; e < experts; e += 32) row_max = fmaxf(row_max, row[e]);
+    for (int o = 16; o; o >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, o));
+    if (mode == TSP_ROUTER_SOFTMAX && !normalize) {
+        // ascending-id order of additions as in the reference loop, made deterministic by a serial lane-0 pass
+        if (lane == 0) for (uint32_t e = 0; e < experts; ++e) all_sum += exp(static_cast<double>(row[e]) - static_cast<double>(row_max));
+        all_sum = __shfl_sync(0xffffffffu, all_sum, 0);
+    }
+    double my_act = 0;     // lane r (< 32) keeps activation r; ranks >= 32 are handled by lane r%32 in a second slot
+    double my_act_hi = 0;
+    double sel_sum = 0;
+    for (uint32_t r = 0; r < selected; ++r) {
+        float best = -INFINITY;
+        uint32_t best_id = 0xffffffffu;
+        for (uint32_t e = lane; e < experts; e += 32) {
+            const float v = row[e];
+            if (v > best) { best = v; best_id = e; }  // ascending scan keeps the lowest id on ties
+        }
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+            if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+        }
+        double act;
+        const double l = best, mx = row_max;
+        if (mode == TSP_ROUTER_SOFTMAX) act = exp(l - mx);
+        else if (normalize) act = exp(-softplus_f64(-l) + softplus_f64(-mx));
+        else act = sigmoid_f64(l);
+        sel_sum += act;
+        if ((r & 31u) == lane) { if (r < 32) my_act = act; else my_act_hi = act; }
+        if (lane == 0) { out_ids[r] = best_id; row[best_id] = -INFINITY; }
+        __syncwarp();
+    }
+    double denominator = mode == TSP_ROUTER_SIGMOID ? 1.0 : all_sum;
+    if (normalize) denominator = sel_sum;
+    if (!(denominator > 0) || isinf(denominator)) {
+        if (lane == 0) raise_error(error, TSP_ERR_NONFINITE);
+        denominator = 1.0;
+    }
+    if (lane < selected) out_w[lane] = static_cast<float>(my_act / denominator);
+    if (lane + 32 < selected) out_w[lane + 32] = static_cast<float>(my_act_hi / denominator);
+}
+
+// ---------------------------------------------------------------------------------------------
+// permutation: one block per expert compacts, in ascending token order, the routes that name it.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPermuteThreads = 128;
+
+__global__ void __launch_bounds__(kPermuteThreads)
+grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected,
+                      uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* error) {
+    __shared__ uint32_t totals[kPermuteThreads / 32];
+    const uint32_t expert = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t accumulated = 0;
+    for (uint32_t base = 0; base < tokens; base += kPermuteThreads) {
+        const uint32_t token = base + tid;
+        uint32_t slot = 0xffffffffu, matches = 0;
+        if (token < tokens) {
+            for (uint32_t i = 0; i < selected; ++i) {
+                const uint32_t id = ids[static_cast<uint64_t>(token) * selected + i];
+                if (id >= experts && expert == 0) raise_error(error, TSP_ERR_INDEX);
+                if (id == expert) { slot = i; ++matches; }
+            }
+        }
+        if (matches > 1) raise_error(error, TSP_ERR_INDEX);
+        const bool found = matches == 1;
+        const uint32_t ballot = __ballot_sync(0xffffffffu, found);
+        const uint32_t prefix = __popc(ballot & ((1u << lane) - 1u));
+        if (lane == 0) totals[warp] = __popc(ballot);
+        __syncthreads();
+        uint32_t before = 0, chunk = 0;
+        for (uint32_t i = 0; i < kPermuteThreads / 32; ++i) { if (i < warp) before += totals[i]; chunk += totals[i]; }
+        if (found) token_map[static_cast<uint64_t>(expert) * tokens + accumulated + before + prefix] = token * selected + slot;
+        accumulated += chunk;
+        __syncthreads();
+    }
+    if (tid == 0) counts[expert] = accumulated;
+}
+
+// tasks = {live_tiles, routes, (expert, start) pairs in ascending expert order, 0xffffffff padding}
+__global__ void __launch_bounds__(256)
+grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint32_t experts, uint32_t selected,
+                     uint32_t tile, uint32_t bound, uint32_t* __restrict__ tasks, uint32_t* error) {
+    extern __shared__ uint32_t offsets[];  // experts + 1
+    const uint32_t tid = threadIdx.x;
+    __shared__ uint32_t warp_tiles[8], warp_routes[8];
+    // block-wide exclusive scan of tiles per expert, in chunks of 256 experts
+    uint32_t carry_tiles = 0, carry_routes = 0;
+    for (uint32_t base = 0; base < experts; base += 256) {
+        const uint32_t e = base + tid;
+        uint32_t c = 0, n = 0;
+        if (e < experts) {
+            c = counts[e];
+            if (c > tokens) raise_error(error, TSP_ERR_INDEX);
+            n = (min(c, tokens) + tile - 1) / tile;
+        }
+        uint32_t incl_n = n, incl_c = c;
+        const uint32_t lane = tid & 31, warp = tid >> 5;
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t tn = __shfl_up_sync(0xffffffffu, incl_n, o), tc = __shfl_up_sync(0xffffffffu, incl_c, o);
+            if (lane >= static_cast<uint32_t>(o)) { incl_n += tn; incl_c += tc; }
+        }
+        if (lane == 31) { warp_tiles[warp] = incl_n; warp_routes[warp] = incl_c; }
+        __syncthreads();
+        uint32_t before_n = 0, total_n = 0, total_c = 0;
+        for (uint32_t i = 0; i < 8; ++i) { if (i < warp) before_n += warp_tiles[i]; total_n += warp_tiles[i]; total_c += warp_routes[i]; }
+        if (e < experts) offsets[e] = carry_tiles + before_n + incl_n - n;
+        carry_tiles += total_n;
+        carry_routes += total_c;
+        __syncthreads();
+    }
+    if (tid == 0) {
+        offsets[experts] = carry_tiles;
+        tasks[0] = min(carry_tiles, bound);
+        tasks[1] = carry_routes;
+        if (carry_tiles > bound || carry_routes != tokens * selected) raise_error(error, TSP_ERR_INDEX);
+    }
+    for (uint32_t i = tid; i < bound; i += 256) { tasks[2 + 2 * i] = 0xffffffffu; tasks[3 + 2 * i] = 0xffffffffu; }
+    __syncthreads();
+    for (uint32_t e = tid; e < experts; e += 256) {
+        const uint32_t n = (min(counts[e], tokens) + tile - 1) / tile;
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint32_t at = offsets[e] + i;
+            if (at < bound) { tasks[2 + 2 * at] = e; tasks[3 + 2 * at] = i * tile; }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// combine: one block per token. Optional shared-router dot (FP32 tree sum), then the mixture in
+// route-rank order starting from the gated shared term (routing.cpp:49-58).
+// ---------------------------------------------------------------------------------------------
+constexpr int kCombineThreads = 256;
+
+__global__ void __launch_bounds__(kCombineThreads)
+combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const float* __restrict__ weights,
+               const float* __restrict__ shared, uint64_t shared_stride, const float* __restrict__ shared_router,
+               const float* __restrict__ x, uint64_t x_stride, float* shared_logit, uint32_t channels,
+               uint32_t selected, float* __restrict__ out, uint64_t out_stride, __half* __restrict__ out16,
+               uint64_t out16_stride, uint32_t* error) {
+    __shared__ float partial[kCombineThreads / 32];
+    __shared__ float w_s[64];
+    __shared__ float gate_s;
+    const uint32_t token = blockIdx.x, tid = threadIdx.x;
+    if (tid < selected) w_s[tid] = weights[static_cast<uint64_t>(token) * selected + tid];
+    float gate = 1.f;
+    if (shared_router) {
+        const float* xr = reinterpret_cast<const float*>(reinterpret_cast<const char*>(x) + token * x_stride);
+        float acc = 0.f;
+        for (uint32_t c = tid; c < channels; c += kCombineThreads) acc = fmaf(shared_router[c], xr[c], acc);
+        for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if ((tid & 31) == 0) partial[tid >> 5] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            float s = 0.f;
+            for (int i = 0; i < kCombineThreads / 32; ++i) s += partial[i];
+            if (!finite_f32(s)) raise_error(error, TSP_ERR_NONFINITE);
+            if (shared_logit) shared_logit[token] = s;
+            gate_s = stable_sigmoid(s);
+        }
+        __syncthreads();
+        gate = gate_s;
+    } else {
+        if (shared_logit) gate = stable_sigmoid(shared_logit[token]);
+        __syncthreads();
+    }
+    const float* sh = reinterpret_cast<const float*>(reinterpret_cast<const char*>(shared) + token * shared_stride);
+    float* o = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + token * out_stride);
+    bool bad = false;
+    for (uint32_t c = tid; c < channels; c += kCombineThreads) {
+        float v = gate * sh[c];
+        for (uint32_t r = 0; r < selected; ++r) {
+            const float* y = reinterpret_cast<const float*>(reinterpret_cast<const char*>(routed) +
+                                                            (static_cast<uint64_t>(token) * selected + r) * routed_stride);
+            v = fmaf(w_s[r], y[c], v);
+        }
+        bad |= !finite_f32(v);
+        if (out) o[c] = v;
+        if (out16) reinterpret_cast<__half*>(reinterpret_cast<char*>(out16) + token * out16_stride)[c] = __float2half_rn(v);
+    }
+    if (bad) raise_error(error, TSP_ERR_NONFINITE);
+}
+
+__global__ void rows_f16_to_f32_kernel(const __half* __restrict__ in, uint64_t in_stride, float* __restrict__ out,
+                                       uint64_t out_stride, uint32_t rows, uint32_t cols) {
+    const uint32_t row = blockIdx.y;
+    const __half* src = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(in) + row * in_stride);
+    float* dst = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + row * out_stride);
+    for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) dst[c] = __half2float(src[c]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// dequantise test hook: FP32 fmaf(d*sc, q, -(dmin*mn)) is the exactly rounded reference value
+// because d*sc, (d*sc)*q and dmin*mn are exact in FP32 (at most 21 significant bits).
+// ---------------------------------------------------------------------------------------------
+__global__ void dequant_q4k_kernel(const uint8_t* __restrict__ expert, uint32_t layout, uint64_t total_blocks,
+                                   float* __restrict__ out, uint32_t* error) {
+    const uint64_t blk = blockIdx.x;
+    const uint32_t i = threadIdx.x;  // 0..255
+    const uint32_t g = i >> 5;
+    uint32_t dbits, mbits, sc, mn, q;
+    if (layout == TSP_LAYOUT_GGUF) {
+        const uint8_t* b = expert + blk * 144;
+        dbits = b[0] | (b[1] << 8);
+        mbits = b[2] | (b[3] << 8);
+        if (g < 4) { sc = b[4 + g] & 63u; mn = b[8 + g] & 63u; }
+        else { sc = (b[12 + g - 4] & 15u) | ((b[4 + g - 4] >> 6) << 4); mn = (b[12 + g - 4] >> 4) | ((b[8 + g - 4] >> 6) << 4); }
+        q = (b[16 + (i >> 6) * 32 + (i & 31)] >> (4 * ((i >> 5) & 1))) & 15u;
+    } else {
+        const uint8_t* qs = expert + blk * 128;
+        const uint8_t* sm = expert + total_blocks * 128 + blk * 16;
+        const uint8_t* dm = expert + total_blocks * 144 + blk * 4;
+        dbits = dm[0] | (dm[1] << 8);
+        mbits = dm[2] | (dm[3] << 8);
+        sc = sm[g]; mn = sm[8 + g];
+        if ((sc | mn) & 0xc0u) raise_error(error, TSP_ERR_INDEX);
+        q = (qs[(i >> 6) * 32 + (i & 31)] >> (4 * ((i >> 5) & 1))) & 15u;
+    }
+    const float d = half_bits_to_float(dbits), dmin = half_bits_to_float(mbits);
+    const float v = fmaf(d * static_cast<float>(sc), static_cast<float>(q), -(dmin * static_cast<float>(mn)));
+    if (!finite_f32(v) || !finite_f32(d) || !finite_f32(dmin)) raise_error(error, TSP_ERR_NONFINITE);
+    out[blk * 256 + i] = v;
+}
+
+__global__ void dequant_q8_kernel(const uint8_t* __restrict__ expert, uint32_t layout, uint64_t total_blocks,
+                                  float* __restrict__ out, uint32_t* error) {
+    const uint64_t blk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (blk >= total_blocks) return;
+    const uint32_t i = threadIdx.x & 31;
+    uint32_t dbits;
+    int q;
+    if (layout == TSP_LAYOUT_GGUF) {
+        const uint8_t* b = expert + blk * 34;
+        dbits = b[0] | (b[1] << 8);
+        q = static_cast<int8_t>(b[2 + i]);
+    } else {
+        const uint8_t* dm = expert + total_blocks * 32 + blk * 2;
+        dbits = dm[0] | (dm[1] << 8);
+        q = static_cast<int8_t>(expert[blk * 32 + i]);
+    }
+    const float d = half_bits_to_float(dbits);
+    const float v = d * static_cast<float>(q);
+    if (!finite_f32(v)) raise_error(error, TSP_ERR_NONFINITE);
+    out[blk * 32 + i] = v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host launchers (called by the C ABI layer in tsp_api.cu after validation)
+// ---------------------------------------------------------------------------------------------
+int launch_route(const float* logits, uint64_t stride, uint32_t tokens, uint32_t experts, uint32_t selected,
+                 uint32_t mode, int normalize, uint32_t* ids, float* weights, uint32_t* error, cudaStream_t st) {
+    const uint32_t blocks = (tokens + kRouteWarps - 1) / kRouteWarps;
+    route_kernel<<<blocks, kRouteWarps * 32, kRouteWarps * experts * sizeof(float), st>>>(
+        logits, stride, tokens, experts, selected, mode, normalize, ids, weights, error);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+int launch_permute(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile,
+                   uint32_t* token_map, uint32_t* counts, uint32_t* tasks, uint32_t* error, cudaStream_t st) {
+    grouped_routes_kernel<<<experts, kPermuteThreads, 0, st>>>(ids, tokens, experts, selected, token_map, counts, error);
+    TSP_CUDA(cudaGetLastError());
+    const uint32_t bound = static_cast<uint32_t>((static_cast<uint64_t>(tokens) * selected) / tile + experts);
+    grouped_tasks_kernel<<<1, 256, (experts + 1) * sizeof(uint32_t), st>>>(counts, tokens, experts, selected, tile, bound, tasks, error);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+int launch_combine(const float* routed, uint64_t routed_stride, const float* weights, const float* shared,
+                   uint64_t shared_stride, const float* shared_router, const float* x, uint64_t x_stride,
+                   float* shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected, float* out,
+                   uint64_t out_stride, void* out16, uint64_t out16_stride, uint32_t* error, cudaStream_t st) {
+    combine_kernel<<<tokens, kCombineThreads, 0, st>>>(routed, routed_stride, weights, shared, shared_stride, shared_router,
+                                                       x, x_stride, shared_logit, channels, selected, out, out_stride,
+                                                       static_cast<__half*>(out16), out16_stride, error);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+int launch_f16_to_f32(const void* in, uint64_t in_stride, float* out, uint64_t out_stride, uint32_t rows, uint32_t cols,
+                      cudaStream_t st) {
+    dim3 grid((cols + 1023) / 1024, rows);
+    rows_f16_to_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(in), in_stride, out, out_stride, rows, cols);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+int launch_dequant(uint32_t type, uint32_t layout, const uint8_t* expert, uint64_t total_blocks, float* out,
+                   uint32_t* error, cudaStream_t st) {
+    if (type == TSP_TYPE_Q4_K) dequant_q4k_kernel<<<static_cast<unsigned>(total_blocks), 256, 0, st>>>(expert, layout, total_blocks, out, error);
+    else dequant_q8_kernel<<<static_cast<unsigned>((total_blocks + 7) / 8), 256, 0, st>>>(expert, layout, total_blocks, out, error);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+}  // namespace tsp

@@ -1,0 +1,166 @@
+"""Harness objects over the C ABI: device-resident MoE layer weights, caller-owned scratch and the
+operator calls, mirroring the reference's MoeWeights / MoeScratch / encode_moe (moe.hpp:9-45).
+
+torch supplies device memory and streams only; every computation is a libtsp_moe.so kernel.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import capi, formats
+from .capi import MatrixSet, MoeScratch, MoeWeights
+
+
+def _dev(a: np.ndarray, device) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def matrix_set(t: torch.Tensor, type_: int, layout: int, rows: int, cols: int, experts: int = 1, *, base_hi: torch.Tensor | None = None,
+               split: int | None = None, expert_stride: int | None = None, offset: int = 0) -> MatrixSet:
+    bytes_ = int(capi.lib().tsp_expert_bytes(type_, layout, rows, cols))
+    return MatrixSet(t.data_ptr() + offset, (base_hi.data_ptr() + offset) if base_hi is not None else None,
+                     expert_stride if expert_stride is not None else bytes_, split if split is not None else experts,
+                     experts, rows, cols, type_, layout)
+
+
+@dataclass
+class HostLayer:
+    """One MoE layer's weights as GGUF bytes on the host (the oracle's input)."""
+    channels: int
+    hidden: int
+    experts: int
+    selected: int
+    expert_type: int
+    shared_type: int
+    gate: np.ndarray         # [E, gguf bytes of hidden x channels]
+    up: np.ndarray
+    down: np.ndarray         # [E, gguf bytes of channels x hidden]
+    shared_gate: np.ndarray
+    shared_up: np.ndarray
+    shared_down: np.ndarray
+    shared_router: np.ndarray  # f32 [channels]
+    down_type: int | None = None  # defaults to expert_type
+
+    def oracle_dict(self, mode: int = 0, normalize: bool = True) -> dict:
+        assert self.down_type in (None, self.expert_type), "the oracle layer takes one expert encoding"
+        return dict(channels=self.channels, hidden=self.hidden, experts=self.experts, selected=self.selected,
+                    expert_type=self.expert_type, shared_type=self.shared_type, gate=self.gate, up=self.up, down=self.down,
+                    shared_gate=self.shared_gate, shared_up=self.shared_up, shared_down=self.shared_down,
+                    shared_router=self.shared_router, router=None, mode=mode, normalize=normalize)
+
+
+def synth_host_layer(seed: int, channels: int, hidden: int, experts: int, selected: int, expert_type: int = formats.Q4_K,
+                     shared_type: int | None = None, sigma: float = 0.02) -> HostLayer:
+    """Seeded N(0, sigma) weights quantised with this build's encoders."""
+    from . import synth
+    shared_type = expert_type if shared_type is None else shared_type
+    q = formats.quantize
+
+    def experts_of(s, rows, cols):
+        return np.stack([q(expert_type, synth.normal(s * 100003 + e, (rows, cols), sigma)).reshape(-1) for e in range(experts)])
+
+    return HostLayer(channels, hidden, experts, selected, expert_type, shared_type,
+                     experts_of(seed * 4 + 0, hidden, channels), experts_of(seed * 4 + 1, hidden, channels),
+                     experts_of(seed * 4 + 2, channels, hidden),
+                     q(shared_type, synth.normal(seed * 4 + 3, (hidden, channels), sigma)).reshape(-1),
+                     q(shared_type, synth.normal(seed * 4 + 3 + 7777, (hidden, channels), sigma)).reshape(-1),
+                     q(shared_type, synth.normal(seed * 4 + 3 + 9999, (channels, hidden), sigma)).reshape(-1),
+                     synth.normal(seed * 4 + 3 + 5555, (channels,), sigma))
+
+
+class DeviceLayer:
+    """Device-resident weights of one layer in the chosen layout, plus their matrix-set descriptors."""
+
+    def __init__(self, host: HostLayer, layout: int = formats.PLANAR, device="cuda", shared_layout: int | None = None):
+        C_, H, E = host.channels, host.hidden, host.experts
+        self.host = host
+        self.layout = layout
+        shared_layout = layout if shared_layout is None else shared_layout
+        et, st = host.expert_type, host.shared_type
+        dt = host.down_type or et
+        self.tensors = []
+
+        def keep(t):
+            self.tensors.append(t)
+            return t
+
+        if layout == formats.PLANAR:
+            gp = formats.pack_planar_experts(et, host.gate, E, H, C_)
+            up = formats.pack_planar_experts(et, host.up, E, H, C_)
+            pb = gp.shape[1]
+            if E % 2 == 0:
+                lo, hi = formats.colocate_gate_up(gp, up)
+                tlo, thi = keep(_dev(lo, device)), keep(_dev(hi, device))
+                gate = matrix_set(tlo, et, layout, H, C_, E, base_hi=thi, split=E // 2, expert_stride=2 * pb)
+                upm = matrix_set(tlo, et, layout, H, C_, E, base_hi=thi, split=E // 2, expert_stride=2 * pb, offset=pb)
+            else:
+                tg, tu = keep(_dev(gp, device)), keep(_dev(up, device))
+                gate, upm = matrix_set(tg, et, layout, H, C_, E), matrix_set(tu, et, layout, H, C_, E)
+            td = keep(_dev(formats.pack_planar_experts(dt, host.down, E, C_, H), device))
+        else:
+            tg, tu, td = keep(_dev(host.gate, device)), keep(_dev(host.up, device)), keep(_dev(host.down, device))
+            gate, upm = matrix_set(tg, et, layout, H, C_, E), matrix_set(tu, et, layout, H, C_, E)
+        down = matrix_set(td, dt, layout, C_, H, E)
+
+        def dense(b, rows, cols):
+            data = formats.pack_planar(st, b, rows, cols) if shared_layout == formats.PLANAR else b
+            return matrix_set(keep(_dev(data, device)), st, shared_layout, rows, cols, 1)
+
+        self.shared_router = keep(_dev(host.shared_router.astype(np.float32), device))
+        self.weights = MoeWeights(gate, upm, down, dense(host.shared_gate, H, C_), dense(host.shared_up, H, C_),
+                                  dense(host.shared_down, C_, H), self.shared_router.data_ptr())
+
+
+class Scratch:
+    """Caller-owned scratch for `capacity` token rows (MoeScratch / MoeMmManyScratch)."""
+
+    def __init__(self, channels: int, hidden: int, experts: int, selected: int, capacity: int, device="cuda"):
+        f32, u32 = torch.float32, torch.int32  # int32 storage holds uint32 bit patterns
+        z = lambda n, dt: torch.zeros(max(int(n), 1), dtype=dt, device=device)
+        self.capacity = capacity
+        self.shape = (channels, hidden, experts, selected)
+        self.ids = z(capacity * selected, u32)
+        self.weights = z(capacity * selected, f32)
+        self.hidden = z(capacity * selected * hidden, f32)
+        self.routed = z(capacity * selected * channels, f32)
+        self.shared_hidden = z(capacity * hidden, f32)
+        self.shared_out = z(capacity * channels, f32)
+        self.shared_logit = z(capacity, f32)
+        self.x32 = z(capacity * channels, f32)
+        self.token_map = z(experts * capacity, u32)
+        self.counts = z(experts, u32)
+        self.tasks = z(capacity * selected + 2 * experts + 2, u32)  # covers every tile size >= 2
+        self.error = z(1, u32)
+        self.c = MoeScratch(self.ids.data_ptr(), self.weights.data_ptr(), self.hidden.data_ptr(), self.routed.data_ptr(),
+                            self.shared_hidden.data_ptr(), self.shared_out.data_ptr(), self.shared_logit.data_ptr(),
+                            self.x32.data_ptr(), self.token_map.data_ptr(), self.counts.data_ptr(), self.tasks.data_ptr(), capacity)
+
+    def error_word(self) -> int:
+        w = C.c_uint32(0)
+        rc = capi.lib().tsp_error_word_read(self.error.data_ptr(), stream_ptr(), C.byref(w))
+        if rc not in (0, capi.E_DEVICE):
+            capi.check(rc)
+        return w.value
+
+    def reset_error(self) -> None:
+        capi.call("tsp_error_word_reset", self.error.data_ptr(), stream_ptr())
+
+
+def moe_layer_decode(dl: DeviceLayer, s: Scratch, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor,
+                     mode: int = 0, normalize: bool = True) -> None:
+    """Launch one whole layer on the current stream. x/out: [T, channels] float32 or float16; logits [T, E] float32."""
+    C_, H, E, K = s.shape
+    T = x.shape[0]
+    xd = 1 if x.dtype == torch.float16 else 0
+    od = 1 if out.dtype == torch.float16 else 0
+    capi.call("tsp_moe_layer_decode", C.byref(dl.weights), C.byref(s.c), x.data_ptr(), x.stride(0) * x.element_size(), xd,
+              logits.data_ptr(), logits.stride(0) * 4, T, C_, H, E, K, mode, int(normalize), out.data_ptr(),
+              out.stride(0) * out.element_size(), od, s.error.data_ptr(), stream_ptr())

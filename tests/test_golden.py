@@ -23,7 +23,7 @@ def test_decode_and_gemv_match_reference_outputs(oracle, type_):
 
 
 def test_routes_match_reference_outputs(oracle):
-    lg = fixtures.lcg_activations(9, 8 * 64).reshape(8, 64).astype(np.float64) * 5
+    lg = (fixtures.lcg_activations(9, 8 * 64).reshape(8, 64) * np.float32(5)).astype(np.float64)  # binary32-exact values
     lg[3, 10:20] = lg[3, 5]
     for mode in (0, 1):
         for norm in (0, 1):

@@ -100,7 +100,7 @@ def test_route_ids_bit_exact(oracle, E, k):
 
 
 def test_route_matches_reference_outputs_and_flags_nonfinite():
-    lg = fixtures.lcg_activations(9, 8 * 64).reshape(8, 64).astype(np.float64) * 5
+    lg = (fixtures.lcg_activations(9, 8 * 64).reshape(8, 64) * np.float32(5)).astype(np.float64)  # binary32-exact values
     lg[3, 10:20] = lg[3, 5]
     lg32 = lg.astype(np.float32)
     assert np.array_equal(lg32.astype(np.float64), lg)

@@ -33,7 +33,7 @@ def _digest() -> str:
     for path in sources() + sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")) + \
             [os.path.join(ROOT, "include", "tsp_moe.h")]:
         with open(path, "rb") as f:
-            h.update(path.encode())
+            h.update(os.path.relpath(path, ROOT).encode())
             h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()
@@ -66,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("CUDA build failed")
-    subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-lcudart"], check=True)
+    subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-lcudart"], check=True)
     with open(STAMP, "w") as f:
         f.write(digest)
     return LIB

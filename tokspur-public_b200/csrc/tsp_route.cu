@@ -11,7 +11,7 @@ namespace tsp {
 // exactly as the reference's doubles do because the conversion is exact.
 // Weights are evaluated in double so that they round to the same FP32 as the reference's.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRouteWarps = 4;
+constexpr int kRouteWarps = 4;  // at most; fewer when a row of logits is long, to stay inside 48 KB of shared memory
 
 __device__ __forceinline__ double softplus_f64(double v) { return fmax(v, 0.0) + log1p(exp(-fabs(v))); }
 __device__ __forceinline__ double sigmoid_f64(double v) {
@@ -26,7 +26,7 @@ route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t t
              float* __restrict__ weights, uint32_t* error) {
     extern __shared__ float route_smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t token = blockIdx.x * kRouteWarps + warp;
+    const uint32_t token = blockIdx.x * (blockDim.x >> 5) + warp;
     if (token >= tokens) return;
     float* row = route_smem + warp * experts;
     const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + token * stride_bytes);
@@ -298,8 +298,9 @@ __global__ void dequant_q8_kernel(const uint8_t* __restrict__ expert, uint32_t l
 // ---------------------------------------------------------------------------------------------
 int launch_route(const float* logits, uint64_t stride, uint32_t tokens, uint32_t experts, uint32_t selected,
                  uint32_t mode, int normalize, uint32_t* ids, float* weights, uint32_t* error, cudaStream_t st) {
-    const uint32_t blocks = (tokens + kRouteWarps - 1) / kRouteWarps;
-    route_kernel<<<blocks, kRouteWarps * 32, kRouteWarps * experts * sizeof(float), st>>>(
+    const uint32_t warps = experts > 3072 ? 2 : kRouteWarps;
+    const uint32_t blocks = (tokens + warps - 1) / warps;
+    route_kernel<<<blocks, warps * 32, warps * experts * sizeof(float), st>>>(
         logits, stride, tokens, experts, selected, mode, normalize, ids, weights, error);
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;

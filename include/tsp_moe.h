@@ -148,6 +148,18 @@ int tsp_moe_combine(const float* d_routed, uint64_t routed_stride_bytes, const f
                     float* d_out, uint64_t out_stride_bytes, void* d_out_f16, uint64_t out_f16_stride_bytes,
                     uint32_t* d_error, void* stream);
 
+/* ---- data preparation (device side) ----------------------------------------------------------------
+ * tsp_synth_weights: seeded N(0, sigma) values quantised to GGUF blocks of `type` (Q4_K, Q8_0) or written
+ * as FP32 (type F32, `blocks` = element count), `blocks` blocks starting at stream block `first_block`
+ * (any slice of a tensor can be produced independently). No reference counterpart: the reference has
+ * no quantizer; the benchmark's synthetic weights come from here.
+ * tsp_pack_planar: GGUF rows -> Pack v3 planar experts on the device; replaces `pack_expert_planar_v3`
+ * (planar_pack_v3.cpp:676-716). `planar_expert_stride` lets gate and up experts interleave into the
+ * co-located pair tensors (stride 2 * planar_expert_bytes, up offset by one expert). */
+int tsp_synth_weights(uint32_t type, uint64_t seed, uint64_t first_block, uint64_t blocks, float sigma, void* d_out, void* stream);
+int tsp_pack_planar(uint32_t type, uint32_t rows, uint32_t cols, uint32_t experts, const void* d_gguf, uint64_t gguf_expert_stride,
+                    void* d_planar, uint64_t planar_expert_stride, void* stream);
+
 /* binary16 rows -> FP32 rows (exact) and back (round to nearest even); activation edge of the layer. */
 int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride_bytes, float* d_out, uint64_t out_stride_bytes,
                         uint32_t rows, uint32_t cols, void* stream);

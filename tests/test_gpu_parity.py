@@ -311,3 +311,60 @@ def test_sticky_error_word_and_recovery(oracle):
     xbad[1, 3] = np.inf
     _, s3, _ = run_layer(host, formats.GGUF, xbad, logits)
     assert s3.error_word() & capi.ERR_NONFINITE
+
+
+# ------------------------------------------------------------------ device-side data preparation
+@pytest.mark.parametrize("type_", [8, 12])
+def test_device_generator_and_planar_pack(oracle, type_):
+    """The benchmark's weight generator produces valid blocks with the asked distribution, any slice of a stream equals
+    the same slice generated alone, and the device repack equals the oracle's pack_expert byte for byte."""
+    rows, cols, E = 256, 512, 4
+    sl = L.SynthDeviceLayer(9, cols, rows, E, type_, formats.PLANAR, DEV, keep_gguf=True)
+    host = sl.host_layer(2)
+    dec = oracle.dequantize(type_, host.gate.reshape(-1), E * rows * cols)
+    assert abs(float(dec.std()) - 0.02) < 0.002 and abs(float(dec.mean())) < 0.001
+    spec = oracle.spec(type_, cols, rows)
+    part = L.SynthDeviceLayer(9, cols, rows, E, type_, formats.PLANAR, DEV, keep_gguf=True, expert_range=(2, 4)).host_layer(2)
+    assert np.array_equal(part.gate, host.gate[2:4]) and np.array_equal(part.down, host.down[2:4])
+    lo, hi = sl.tensors[0].cpu().numpy(), sl.tensors[1].cpu().numpy()
+    pb = spec.planar_expert_bytes
+    for e in range(E):
+        base = (lo if e < E // 2 else hi)[2 * (e % (E // 2)) * pb:]
+        assert np.array_equal(base[:pb], oracle.pack_expert(spec, host.gate[e]))
+        assert np.array_equal(base[pb:2 * pb], oracle.pack_expert(spec, host.up[e]))
+    dspec = oracle.spec(type_, rows, cols)
+    pd = sl.tensors[2].cpu().numpy().reshape(E, -1)
+    for e in range(E):
+        assert np.array_equal(pd[e], oracle.pack_expert(dspec, host.down[e]))
+
+
+def test_full_shape_layer_properties(oracle):
+    """BASELINE layer shape (hidden 2048, 512 experts of FFN 512, top-10) at 64 tokens with device-generated weights:
+    ids and permutation against the oracle for all tokens, outputs against the CPU layer on a sample of tokens,
+    and token-order independence (a permuted batch gives the permuted output rows exactly)."""
+    Cn, H, E, K, T = 2048, 512, 512, 10, 64
+    sl = L.SynthDeviceLayer(3, Cn, H, E, 12, formats.PLANAR, DEV, keep_gguf=True)
+    s = L.Scratch(Cn, H, E, K, T, DEV)
+    x16 = synth.activations_f16(21, T, Cn)
+    logits = synth.router_logits(22, T, E)
+    out = torch.zeros((T, Cn), dtype=torch.float16, device=DEV)
+    L.moe_layer_decode(sl, s, dev(x16), dev(logits), out)
+    torch.cuda.synchronize()
+    assert s.error_word() == 0
+    ids = s.ids.cpu().numpy().view(np.uint32)[:T * K].reshape(T, K)
+    oi, _ = oracle.route_rows(logits.astype(np.float64), K)
+    assert np.array_equal(ids, oi)
+    otm, ocounts = oracle.grouped_routes(oi, E)
+    assert np.array_equal(s.counts.cpu().numpy().view(np.uint32), ocounts)
+    tm = s.token_map.cpu().numpy().view(np.uint32).reshape(E, T)
+    assert all(np.array_equal(tm[e, :ocounts[e]], otm[e, :ocounts[e]]) for e in range(E))
+    host = sl.host_layer(K)
+    sample = [0, 17, 63]
+    want = oracle.moe_layer(host.oracle_dict(), x16[sample].astype(np.float32), logits[sample], threads=3)
+    got = out.cpu().numpy()
+    assert rel_l2(got[sample].astype(np.float32), want) <= 2e-3
+    perm = np.random.default_rng(0).permutation(T)
+    out2 = torch.zeros((T, Cn), dtype=torch.float16, device=DEV)
+    L.moe_layer_decode(sl, s, dev(x16[perm]), dev(logits[perm]), out2)
+    torch.cuda.synchronize()
+    assert np.array_equal(out2.cpu().numpy().view(np.uint16), got[perm].view(np.uint16))

@@ -46,6 +46,9 @@ int launch_dequant(uint32_t, uint32_t, const uint8_t*, uint64_t, float*, uint32_
 int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*, uint64_t, uint32_t, uint32_t,
                 const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t);
 
+int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
+int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
+
 static int check_matrix(const tsp_matrix_set* m, const char* name) {
     TSP_REQUIRE(m != nullptr, "%s: null matrix set", name);
     if (m->type != TSP_TYPE_Q4_K && m->type != TSP_TYPE_Q8_0) return fail(TSP_E_TYPE, "%s: encoding %u has no kernel", name, m->type);
@@ -226,6 +229,24 @@ int tsp_moe_combine(const float* d_routed, uint64_t routed_stride, const float* 
     return launch_combine(d_routed, routed_stride, d_weights, d_shared, shared_stride, d_shared_router, d_x, x_stride,
                           d_shared_logit, tokens, channels, selected, d_out, out_stride, d_out_f16, out_f16_stride, d_error,
                           static_cast<cudaStream_t>(stream));
+}
+
+int tsp_synth_weights(uint32_t type, uint64_t seed, uint64_t first_block, uint64_t blocks, float sigma, void* d_out, void* stream) {
+    if (type != TSP_TYPE_Q4_K && type != TSP_TYPE_Q8_0 && type != TSP_TYPE_F32) return fail(TSP_E_TYPE, "synth: encoding %u has no generator", type);
+    TSP_REQUIRE(d_out && blocks >= 1 && blocks < (1ull << 38), "synth: null output or block count out of range");
+    TSP_REQUIRE(sigma > 0.f && sigma < 1e4f, "synth: sigma out of range");
+    return launch_synth(type, seed, first_block, blocks, sigma, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_pack_planar(uint32_t type, uint32_t rows, uint32_t cols, uint32_t experts, const void* d_gguf, uint64_t gguf_stride,
+                    void* d_planar, uint64_t planar_stride, void* stream) {
+    const uint64_t pb = tsp_expert_bytes(type, TSP_LAYOUT_PLANAR, rows, cols), gb = tsp_expert_bytes(type, TSP_LAYOUT_GGUF, rows, cols);
+    if (!pb || !gb) return fail(TSP_E_TYPE, "pack: shape %ux%u of encoding %u has no planar layout", rows, cols, type);
+    TSP_REQUIRE(d_gguf && d_planar && aligned16(d_gguf) && aligned16(d_planar), "pack: buffers must be 16-byte aligned");
+    TSP_REQUIRE(experts >= 1 && gguf_stride >= gb && planar_stride >= pb && planar_stride % 16 == 0 && gguf_stride % 16 == 0,
+                "pack: expert strides too small or unaligned");
+    const uint64_t blocks = static_cast<uint64_t>(rows) * (cols / (type == TSP_TYPE_Q4_K ? 256 : 32));
+    return launch_pack_planar(type, d_gguf, gguf_stride, d_planar, planar_stride, blocks, experts, static_cast<cudaStream_t>(stream));
 }
 
 int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride, float* d_out, uint64_t out_stride, uint32_t rows,

@@ -1,0 +1,144 @@
+// Device-side data preparation: seeded synthetic weights quantised to GGUF Q4_K / Q8_0 blocks, and the
+// GGUF -> Pack v3 planar repack (planar_pack_v3.cpp:676-716 restated per block, one thread per block).
+// The generator stands in for a real model's weights at benchmark scale, where producing ~1 GB per
+// layer on the host would dominate the run. Parity never depends on it: every check decodes the
+// produced bytes with the oracle.
+#include "tsp_common.cuh"
+
+namespace tsp {
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    uint64_t z = x;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// element i of the N(0, sigma) stream `seed`: two counter-based uniforms, Box-Muller
+__device__ __forceinline__ float normal_at(uint64_t key, uint64_t i, float sigma) {
+    const uint64_t a = splitmix64((2 * i) * 0xD1342543DE82EF95ull + key);
+    const uint64_t b = splitmix64((2 * i + 1) * 0xD1342543DE82EF95ull + key);
+    const float u1 = (static_cast<float>(a >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = (static_cast<float>(b >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    return sigma * sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+
+__global__ void synth_q4k_kernel(uint64_t key, uint64_t first_block, uint64_t blocks, float sigma, uint8_t* __restrict__ out) {
+    const uint64_t blk = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (blk >= blocks) return;
+    const uint64_t e0 = (first_block + blk) * 256;
+    float scale[8], minv[8];
+    float max_scale = 0.f, max_min = 0.f;
+    for (int g = 0; g < 8; ++g) {
+        float lo = 0.f, hi = -INFINITY;
+        for (int l = 0; l < 32; ++l) {
+            const float v = normal_at(key, e0 + g * 32 + l, sigma);
+            lo = fminf(lo, v);
+            hi = fmaxf(hi, v);
+        }
+        minv[g] = -lo;
+        scale[g] = (hi + minv[g]) / 15.0f;
+        max_scale = fmaxf(max_scale, scale[g]);
+        max_min = fmaxf(max_min, minv[g]);
+    }
+    const __half dh = __float2half_rn(max_scale / 63.0f), mh = __float2half_rn(max_min / 63.0f);
+    const float d = __half2float(dh), dmin = __half2float(mh);
+    uint8_t sc[8], mn[8];
+    for (int g = 0; g < 8; ++g) {
+        sc[g] = d > 0.f ? static_cast<uint8_t>(fminf(fmaxf(rintf(scale[g] / d), 0.f), 63.f)) : 0;
+        mn[g] = dmin > 0.f ? static_cast<uint8_t>(fminf(fmaxf(rintf(minv[g] / dmin), 0.f), 63.f)) : 0;
+    }
+    uint8_t* b = out + blk * 144;
+    const uint16_t db = __half_as_ushort(dh), mb = __half_as_ushort(mh);
+    b[0] = db & 255; b[1] = db >> 8; b[2] = mb & 255; b[3] = mb >> 8;
+    for (int g = 0; g < 4; ++g) {
+        b[4 + g] = sc[g] | ((sc[g + 4] >> 4) << 6);
+        b[8 + g] = mn[g] | ((mn[g + 4] >> 4) << 6);
+        b[12 + g] = (sc[g + 4] & 15) | ((mn[g + 4] & 15) << 4);
+    }
+    for (int j = 0; j < 4; ++j) {
+        const float dl0 = d * sc[2 * j], ml0 = dmin * mn[2 * j], dl1 = d * sc[2 * j + 1], ml1 = dmin * mn[2 * j + 1];
+        for (int l = 0; l < 32; ++l) {
+            const float v0 = normal_at(key, e0 + (2 * j) * 32 + l, sigma), v1 = normal_at(key, e0 + (2 * j + 1) * 32 + l, sigma);
+            const uint32_t q0 = dl0 > 0.f ? static_cast<uint32_t>(fminf(fmaxf(rintf((v0 + ml0) / dl0), 0.f), 15.f)) : 0u;
+            const uint32_t q1 = dl1 > 0.f ? static_cast<uint32_t>(fminf(fmaxf(rintf((v1 + ml1) / dl1), 0.f), 15.f)) : 0u;
+            b[16 + j * 32 + l] = static_cast<uint8_t>(q0 | (q1 << 4));
+        }
+    }
+}
+
+__global__ void synth_q8_kernel(uint64_t key, uint64_t first_block, uint64_t blocks, float sigma, uint8_t* __restrict__ out) {
+    const uint64_t blk = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (blk >= blocks) return;
+    const uint64_t e0 = (first_block + blk) * 32;
+    float amax = 0.f;
+    for (int l = 0; l < 32; ++l) amax = fmaxf(amax, fabsf(normal_at(key, e0 + l, sigma)));
+    const __half dh = __float2half_rn(amax / 127.0f);
+    const float d = __half2float(dh);
+    uint8_t* b = out + blk * 34;
+    const uint16_t db = __half_as_ushort(dh);
+    b[0] = db & 255; b[1] = db >> 8;
+    for (int l = 0; l < 32; ++l) {
+        const float v = normal_at(key, e0 + l, sigma);
+        const int q = d > 0.f ? static_cast<int>(fminf(fmaxf(rintf(v / d), -127.f), 127.f)) : 0;
+        b[2 + l] = static_cast<uint8_t>(q & 255);
+    }
+}
+
+__global__ void synth_f32_kernel(uint64_t key, uint64_t n, float sigma, float* __restrict__ out) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = normal_at(key, i, sigma);
+}
+
+// one thread per block of one expert; blocks_per_expert = rows * blocks_per_row
+__global__ void pack_planar_kernel(uint32_t type, const uint8_t* __restrict__ gguf, uint64_t gguf_expert_stride,
+                                   uint8_t* __restrict__ planar, uint64_t planar_expert_stride, uint64_t blocks_per_expert,
+                                   uint32_t experts) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= blocks_per_expert * experts) return;
+    const uint64_t e = i / blocks_per_expert, blk = i % blocks_per_expert;
+    uint8_t* dst = planar + e * planar_expert_stride;
+    if (type == TSP_TYPE_Q4_K) {
+        const uint8_t* sb = gguf + e * gguf_expert_stride + blk * 144;
+        const uint4* src = reinterpret_cast<const uint4*>(sb);
+        uint4* q = reinterpret_cast<uint4*>(dst + blk * 128);
+        for (int k = 0; k < 8; ++k) q[k] = src[1 + k];
+        const uint8_t* s12 = sb + 4;
+        uint8_t* sm = dst + blocks_per_expert * 128 + blk * 16;
+        for (int s = 0; s < 4; ++s) {
+            sm[s] = s12[s] & 0x3f;
+            sm[4 + s] = (s12[8 + s] & 0x0f) | ((s12[s] >> 6) << 4);
+            sm[8 + s] = s12[4 + s] & 0x3f;
+            sm[12 + s] = (s12[8 + s] >> 4) | ((s12[4 + s] >> 6) << 4);
+        }
+        *reinterpret_cast<uint32_t*>(dst + blocks_per_expert * 144 + blk * 4) = *reinterpret_cast<const uint32_t*>(sb);
+    } else {
+        const uint8_t* sb = gguf + e * gguf_expert_stride + blk * 34;
+        uint8_t* q = dst + blk * 32;
+        for (int k = 0; k < 32; ++k) q[k] = sb[2 + k];
+        uint8_t* dm = dst + blocks_per_expert * 32 + blk * 2;
+        dm[0] = sb[0]; dm[1] = sb[1];
+    }
+}
+
+int launch_synth(uint32_t type, uint64_t seed, uint64_t first_block, uint64_t blocks, float sigma, void* out, cudaStream_t st) {
+    const uint64_t key = seed * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull;
+    const unsigned grid = static_cast<unsigned>((blocks + 127) / 128);
+    if (type == TSP_TYPE_Q4_K) synth_q4k_kernel<<<grid, 128, 0, st>>>(key, first_block, blocks, sigma, static_cast<uint8_t*>(out));
+    else if (type == TSP_TYPE_Q8_0) synth_q8_kernel<<<grid, 128, 0, st>>>(key, first_block, blocks, sigma, static_cast<uint8_t*>(out));
+    else synth_f32_kernel<<<grid, 128, 0, st>>>(key, blocks, sigma, static_cast<float*>(out));
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+int launch_pack_planar(uint32_t type, const void* gguf, uint64_t gguf_stride, void* planar, uint64_t planar_stride,
+                       uint64_t blocks_per_expert, uint32_t experts, cudaStream_t st) {
+    const uint64_t total = blocks_per_expert * experts;
+    pack_planar_kernel<<<static_cast<unsigned>((total + 127) / 128), 128, 0, st>>>(
+        type, static_cast<const uint8_t*>(gguf), gguf_stride, static_cast<uint8_t*>(planar), planar_stride, blocks_per_expert, experts);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+}  // namespace tsp

@@ -164,3 +164,84 @@ def moe_layer_decode(dl: DeviceLayer, s: Scratch, x: torch.Tensor, logits: torch
     capi.call("tsp_moe_layer_decode", C.byref(dl.weights), C.byref(s.c), x.data_ptr(), x.stride(0) * x.element_size(), xd,
               logits.data_ptr(), logits.stride(0) * 4, T, C_, H, E, K, mode, int(normalize), out.data_ptr(),
               out.stride(0) * out.element_size(), od, s.error.data_ptr(), stream_ptr())
+
+
+class SynthDeviceLayer:
+    """One MoE layer of seeded synthetic weights generated and packed on the device (benchmark scale).
+
+    Seeds: gate/up/down/shared streams are `seed*8 + {0,1,2,3..5}`; the shared-router vector `seed*8 + 6`.
+    `expert_range` restricts the routed experts held to [lo, hi) of the global id space (expert parallelism):
+    the stream position of an expert does not depend on the range, so shards equal slices of the full layer."""
+
+    def __init__(self, seed: int, channels: int, hidden: int, experts: int, expert_type: int = formats.Q4_K,
+                 layout: int = formats.PLANAR, device="cuda", sigma: float = 0.02, expert_range: tuple[int, int] | None = None,
+                 keep_gguf: bool = False):
+        lib = capi.lib()
+        lo, hi = expert_range if expert_range else (0, experts)
+        n = hi - lo
+        self.channels, self.hidden, self.experts_global, self.experts_local, self.first_expert = channels, hidden, experts, n, lo
+        self.type, self.layout = expert_type, layout
+        epb = 256 if expert_type == formats.Q4_K else 32
+        gb = int(lib.tsp_expert_bytes(expert_type, formats.GGUF, hidden, channels))
+        pb = int(lib.tsp_expert_bytes(expert_type, formats.PLANAR, hidden, channels))
+        blocks_per_expert = hidden * channels // epb
+        st = stream_ptr()
+        u8 = lambda nbytes: torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+        def gen(stream_seed, count, first):
+            t = u8(count * gb)
+            capi.call("tsp_synth_weights", expert_type, stream_seed, first * blocks_per_expert, count * blocks_per_expert, sigma, t.data_ptr(), st)
+            return t
+
+        g, u, d = gen(seed * 8 + 0, n, lo), gen(seed * 8 + 1, n, lo), gen(seed * 8 + 2, n, lo)
+        sg, su, sd = gen(seed * 8 + 3, 1, 0), gen(seed * 8 + 4, 1, 0), gen(seed * 8 + 5, 1, 0)
+        self.shared_router = torch.empty(channels, dtype=torch.float32, device=device)
+        capi.call("tsp_synth_weights", capi.TYPE_F32, seed * 8 + 6, 0, channels, sigma, self.shared_router.data_ptr(), st)
+        self.gguf = dict(gate=g, up=u, down=d, shared_gate=sg, shared_up=su, shared_down=sd) if keep_gguf or layout == formats.GGUF else None
+        self.tensors = []
+        if layout == formats.PLANAR:
+            def pack(src, rows, cols, count, dst, dst_off, stride):
+                capi.call("tsp_pack_planar", expert_type, rows, cols, count, src.data_ptr(), gb, dst.data_ptr() + dst_off, stride, st)
+            if n % 2 == 0 and n >= 2:
+                half = n // 2
+                plo, phi = u8(half * 2 * pb), u8(half * 2 * pb)
+                pack(g[: half * gb], hidden, channels, half, plo, 0, 2 * pb)
+                pack(u[: half * gb], hidden, channels, half, plo, pb, 2 * pb)
+                pack(g[half * gb:], hidden, channels, half, phi, 0, 2 * pb)
+                pack(u[half * gb:], hidden, channels, half, phi, pb, 2 * pb)
+                gate = matrix_set(plo, expert_type, layout, hidden, channels, n, base_hi=phi, split=half, expert_stride=2 * pb)
+                up = matrix_set(plo, expert_type, layout, hidden, channels, n, base_hi=phi, split=half, expert_stride=2 * pb, offset=pb)
+                self.tensors += [plo, phi]
+            else:
+                pg, pu = u8(n * pb), u8(n * pb)
+                pack(g, hidden, channels, n, pg, 0, pb)
+                pack(u, hidden, channels, n, pu, 0, pb)
+                gate, up = matrix_set(pg, expert_type, layout, hidden, channels, n), matrix_set(pu, expert_type, layout, hidden, channels, n)
+                self.tensors += [pg, pu]
+            pd = u8(n * pb)
+            pack(d, channels, hidden, n, pd, 0, pb)
+            down = matrix_set(pd, expert_type, layout, channels, hidden, n)
+            psg, psu, psd = u8(pb), u8(pb), u8(pb)
+            pack(sg, hidden, channels, 1, psg, 0, pb)
+            pack(su, hidden, channels, 1, psu, 0, pb)
+            pack(sd, channels, hidden, 1, psd, 0, pb)
+            self.tensors += [pd, psg, psu, psd]
+            shared = [matrix_set(psg, expert_type, layout, hidden, channels), matrix_set(psu, expert_type, layout, hidden, channels),
+                      matrix_set(psd, expert_type, layout, channels, hidden)]
+            torch.cuda.synchronize()
+            if not keep_gguf:
+                del g, u, d, sg, su, sd
+        else:
+            gate, up = matrix_set(g, expert_type, layout, hidden, channels, n), matrix_set(u, expert_type, layout, hidden, channels, n)
+            down = matrix_set(d, expert_type, layout, channels, hidden, n)
+            shared = [matrix_set(sg, expert_type, layout, hidden, channels), matrix_set(su, expert_type, layout, hidden, channels),
+                      matrix_set(sd, expert_type, layout, channels, hidden)]
+        self.weights = MoeWeights(gate, up, down, shared[0], shared[1], shared[2], self.shared_router.data_ptr())
+
+    def host_layer(self, selected: int) -> HostLayer:
+        """GGUF bytes of this layer on the host (needs keep_gguf=True): the CPU baseline's input."""
+        assert self.gguf is not None
+        h = {k: v.cpu().numpy() for k, v in self.gguf.items()}
+        n = self.experts_local
+        return HostLayer(self.channels, self.hidden, n, selected, self.type, self.type, h["gate"].reshape(n, -1), h["up"].reshape(n, -1),
+                         h["down"].reshape(n, -1), h["shared_gate"], h["shared_up"], h["shared_down"], self.shared_router.cpu().numpy())

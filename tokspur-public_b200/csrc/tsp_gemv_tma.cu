@@ -1,0 +1,537 @@
+// Decode-size routed / dense projections over Q4_K weights, second-generation pipeline for sm_100a:
+// tiled TMA (cp.async.bulk.tensor) with the 128-byte shared-memory swizzle, and one private
+// software pipeline per consumer warp.
+//
+//   * A work unit is one group of weight rows (gate-up: 8 hidden units = 8 gate + 8 up rows; plain:
+//     16 or 32 rows) of one expert over one part of K (up to 4 super-blocks of 256 columns).
+//   * The producer warp brings a unit's 4-bit codes with ONE tensor copy per matrix: the tensor map
+//     views the code plane as [128 B of a super-block][row][super-block][expert], so a box of
+//     rows x super-blocks lands in shared memory as 128-byte lines whose 16-byte chunks are XOR-ed
+//     with (row & 7). The eight row groups of a warp-wide 64-bit load then fall on disjoint banks
+//     without any padding, and the copy stays one large request. Scales/mins (planar `sm`, `dm`
+//     planes) come as two small contiguous bulk copies covering the unit's rows over the full K.
+//   * Units are dealt round-robin to the consumer warps; unit u lives in stage u % stages with its
+//     own full/empty mbarrier pair (one arrival each), so warps never synchronise with each other
+//     except where the token tile changes. Each warp therefore always has its next unit in flight
+//     while it computes the current one.
+//   * Arithmetic as in the first-generation kernel: codes enter warp-level MMAs (m16n8k16,
+//     f16 x f16 -> f32) as exact binary16 subnormals, scales are applied to FP32 partial sums.
+//   * Every wait is bounded (TSP_ERR_TIMEOUT).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "tsp_common.cuh"
+
+namespace tsp {
+
+constexpr int kW2 = 8;                       // consumer warps
+constexpr int kThreads2 = kW2 * 32;
+constexpr uint32_t kMaxStages2 = 6;    // per warp
+
+struct Gemv2Params {
+    const uint8_t* base[4];   // planar 1D planes: A_lo, A_hi, B_lo, B_hi expert-0 addresses
+    uint64_t expert_stride;
+    uint32_t split, experts;
+    uint32_t rows, cols, nblk;
+    uint64_t sm_off, dm_off;
+    uint32_t rows_per_unit;   // rows of ONE matrix in a unit (gate-up: 8*nt hidden units; plain: 16*nt rows)
+    uint32_t nt;              // MMA row tiles per unit
+    uint32_t kb, kparts;      // super-blocks per unit, units per row group
+    uint32_t groups;          // row groups per expert
+    uint32_t qs_bytes, sm_bytes, dm_bytes;  // per matrix per stage (qs_bytes: region size, a multiple of 1024)
+    uint32_t box_bytes;       // bytes one tensor copy delivers
+    uint32_t stage_bytes, n_stages;   // n_stages: per warp
+    uint32_t off_xhi, off_xlo, off_sx, off_stage;
+    uint32_t x_stride, sx_stride;
+    const float* x; uint64_t x_stride_bytes; uint32_t in_div;
+    const uint32_t* token_map; const uint32_t* counts; const uint32_t* tasks;
+    uint32_t tokens;
+    float* out; uint64_t out_stride_bytes;
+    int split_lo;
+    uint32_t* error;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+struct Tile2 { uint32_t expert, start, count; };
+
+template <int NC>
+__device__ __forceinline__ Tile2 tile2(const Gemv2Params& p, uint32_t tile) {
+    Tile2 t;
+    if (p.token_map) {
+        t.expert = p.tasks[2 + 2 * tile];
+        t.start = p.tasks[3 + 2 * tile];
+        if (t.expert >= p.experts) { t.expert = 0; t.start = 0; t.count = 0; return t; }
+        const uint32_t c = p.counts[t.expert];
+        t.count = c > t.start ? min(c - t.start, 8u * NC) : 0u;
+    } else {
+        t.expert = 0;
+        t.start = tile * 8u * NC;
+        t.count = min(p.tokens - t.start, 8u * NC);
+    }
+    return t;
+}
+
+// LAYOUT: TSP_LAYOUT_PLANAR (swizzled code boxes + sm/dm planes) or TSP_LAYOUT_GGUF (whole 144-byte blocks, unswizzled)
+//
+// Every warp runs its own pipeline: it owns `stages_per_warp` stages, its lane 0 issues the copies of the
+// unit that will reuse a stage right after the warp has finished reading that stage, and it waits only on
+// the full-barriers of its own stages. Program order inside the warp orders the reads of a stage before the
+// copy that overwrites it, so no empty-barrier is needed and no warp ever waits for another one.
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT>
+__global__ void __launch_bounds__(kThreads2, 1)
+gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_a_hi,
+             const __grid_constant__ CUtensorMap map_b_lo, const __grid_constant__ CUtensorMap map_b_hi, const Gemv2Params p) {
+    extern __shared__ uint8_t smem2_raw[];
+    // the 128-byte swizzle is a function of the shared-memory address: stage bases must sit on 1024-byte boundaries
+    uint8_t* smem2 = smem2_raw + ((1024u - (smem_u32(smem2_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem2);
+    uint32_t* rids = reinterpret_cast<uint32_t*>(smem2 + 512);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t S = p.n_stages;   // stages per warp
+    constexpr uint32_t NMAT = GATEUP ? 2 : 1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < S * kW2; ++s) mbar_init(&full[s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const uint32_t n_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
+    const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.groups;   // item = (tile, row group)
+    const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
+    const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t KP = p.kparts;
+    // this warp's items are item0 + warp + 8n; its unit k is part (k % KP) of item item0 + warp + 8*(k / KP)
+    const uint32_t my_items = item0 + warp < item1 ? (item1 - item0 - warp + kW2 - 1) / kW2 : 0u;
+    const uint32_t my_units = my_items * KP;
+    uint8_t* my_stage0 = smem2 + p.off_stage + warp * S * p.stage_bytes;
+    uint64_t* my_full = full + warp * S;
+
+    // lane 0: issue the copies of unit k into stage k % S
+    uint32_t issue_tile = 0xffffffffu;
+    Tile2 issue_ti{0, 0, 0};
+    auto issue = [&](uint32_t k) {
+        const uint32_t it = item0 + warp + kW2 * (k / KP), kh = k % KP;
+        const uint32_t tile = it / p.groups, grp = it % p.groups;
+        if (tile != issue_tile) { issue_ti = tile2<NC>(p, tile); issue_tile = tile; }
+        const uint32_t r0 = grp * p.rows_per_unit;
+        const uint32_t nr = min(p.rows_per_unit, p.rows - r0);
+        const bool hi = issue_ti.expert >= p.split;
+        const uint32_t el = hi ? issue_ti.expert - p.split : issue_ti.expert;
+        const uint32_t s = k % S;
+        uint8_t* sb = my_stage0 + s * p.stage_bytes;
+        uint32_t bytes = NMAT * p.box_bytes;
+        if (LAYOUT == TSP_LAYOUT_PLANAR) bytes += NMAT * nr * p.nblk * 20u;
+        mbar_arrive_expect_tx(&my_full[s], bytes);
+#pragma unroll
+        for (uint32_t m = 0; m < NMAT; ++m) {
+            const CUtensorMap* map = m == 0 ? (hi ? &map_a_hi : &map_a_lo) : (hi ? &map_b_hi : &map_b_lo);
+            if (LAYOUT == TSP_LAYOUT_PLANAR) {
+                tma_load_4d(sb + m * p.qs_bytes, map, 0, static_cast<int>(r0), static_cast<int>(kh * p.kb), static_cast<int>(el), &my_full[s]);
+                const uint8_t* eb = p.base[m * 2 + (hi ? 1 : 0)] + static_cast<uint64_t>(el) * p.expert_stride;
+                bulk_g2s(sb + NMAT * p.qs_bytes + m * p.sm_bytes, eb + p.sm_off + static_cast<uint64_t>(r0) * p.nblk * 16u, nr * p.nblk * 16u, &my_full[s]);
+                bulk_g2s(sb + NMAT * (p.qs_bytes + p.sm_bytes) + m * p.dm_bytes, eb + p.dm_off + static_cast<uint64_t>(r0) * p.nblk * 4u,
+                         nr * p.nblk * 4u, &my_full[s]);
+            } else {
+                tma_load_4d(sb + m * p.qs_bytes, map, 0, static_cast<int>(kh * p.kb), static_cast<int>(r0), static_cast<int>(el), &my_full[s]);
+            }
+        }
+    };
+    if (lane == 0) for (uint32_t k = 0; k < min(S, my_units); ++k) issue(k);
+
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t ctid = threadIdx.x;
+    constexpr uint32_t CT = kThreads2;
+    uint8_t* xhi = smem2 + p.off_xhi;
+    uint8_t* xlo = smem2 + p.off_xlo;
+    uint8_t* sxb = smem2 + p.off_sx;
+    bool ok = true;
+    // lane constants: byte offset of this lane's 8 code bytes of pair j inside a (swizzled) 128-byte line
+    uint32_t qoff[4];
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) qoff[j] = (((2 * j + (t >> 1)) ^ (LAYOUT == TSP_LAYOUT_PLANAR ? g : 0u)) << 4) + (t & 1u) * 8u;
+    const uint32_t xlane = g * p.x_stride + t * 16;     // this lane's B-fragment offset inside a token-row block
+    const uint32_t sxlane = g * p.sx_stride + t * 4;
+    const uint32_t mn_shift = 16 * (t & 1);
+
+    uint32_t k = 0;   // this warp's next unit
+    uint32_t item = item0;
+    while (item < item1) {
+        // ---- one token tile: the segment of this CTA's items that share it ----
+        const uint32_t tile = item / p.groups;
+        const uint32_t seg_end = min(item1, (tile + 1) * p.groups);
+        __syncthreads();
+        const Tile2 ti = tile2<NC>(p, tile);
+        if (ctid < 8u * NC) {
+            uint32_t rid = 0;
+            if (ctid < ti.count) rid = p.token_map ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + ctid] : ti.start + ctid;
+            rids[ctid] = rid;
+        }
+        __syncthreads();
+        {
+            const uint32_t per_row = p.cols / 8;
+            const uint32_t units = ti.count * per_row;
+            bool bad = false;
+            for (uint32_t base = 0; base < units; base += CT) {
+                const uint32_t u = base + ctid;
+                const bool active = u < units;
+                float s = 0.f;
+                uint32_t j = 0, k8 = 0;
+                if (active) {
+                    j = u / per_row; k8 = u % per_row;
+                    const uint32_t in_row = rids[j] / p.in_div;
+                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + k8 * 2;
+                    const float4 v0 = src[0], v1 = src[1];
+                    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    uint32_t hb[8], lb[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const __half h = __float2half_rn(v[i]);
+                        const float hf = __half2float(h);
+                        bad |= !finite_f32(hf);
+                        hb[i] = __half_as_ushort(h);
+                        lb[i] = __half_as_ushort(__float2half_rn(v[i] - hf));
+                        s += v[i];
+                    }
+                    // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
+                    *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) =
+                        make_uint4(hb[0] | (hb[2] << 16), hb[1] | (hb[3] << 16), hb[4] | (hb[6] << 16), hb[5] | (hb[7] << 16));
+                    if (p.split_lo)
+                        *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) =
+                            make_uint4(lb[0] | (lb[2] << 16), lb[1] | (lb[3] << 16), lb[4] | (lb[6] << 16), lb[5] | (lb[7] << 16));
+                }
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                if (active && (k8 & 3u) == 0) {
+                    const uint32_t grp = k8 >> 2;
+                    const __half sh = __float2half_rn(s);
+                    const __half sl = __float2half_rn(s - __half2float(sh));
+                    bad |= !finite_f32(__half2float(sh));
+                    *reinterpret_cast<__half*>(sxb + j * p.sx_stride + grp * 2) = sh;
+                    *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
+                }
+            }
+            if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
+        }
+        __syncthreads();
+
+        // ---- this warp's row groups of the segment ----
+        for (uint32_t it = item0 + warp + kW2 * (k / KP); it < seg_end; it += kW2) {
+            const uint32_t grp = it % p.groups;
+            const uint32_t r0 = grp * p.rows_per_unit;
+            float total[NT][NC][4];
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int c = 0; c < NC; ++c) total[n][c][0] = total[n][c][1] = total[n][c][2] = total[n][c][3] = 0.f;
+
+            for (uint32_t kh = 0; kh < KP; ++kh, ++k) {
+                const uint32_t s = k % S, ph = (k / S) & 1u;
+                if (ok) {
+                    ok = mbar_wait(&my_full[s], ph);
+                    if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
+                }
+                if (!ok) continue;
+                const uint8_t* sb = my_stage0 + s * p.stage_bytes;
+                const uint32_t R = p.rows_per_unit;
+                const uint32_t kb_here = min(p.kb, p.nblk - kh * p.kb);
+                for (uint32_t bl = 0; bl < kb_here; ++bl) {
+                    const uint32_t b = kh * p.kb + bl;   // super-block index along K
+                    const uint8_t* xb = xhi + xlane + b * 512;
+                    const uint8_t* xq = xlo + xlane + b * 512;
+                    const uint8_t* sxp = sxb + sxlane + b * 16;
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) {
+                        const uint32_t rowA = GATEUP ? n * 8 + g : n * 16 + g;        // row inside matrix A's box
+                        const uint32_t rowB = GATEUP ? n * 8 + g : n * 16 + 8 + g;    // gate-up: same row of matrix B's box
+                        const uint8_t* boxB = GATEUP ? sb + p.qs_bytes : sb;
+                        uint32_t dmA, dmB, scA[2], scB[2], mnA[2], mnB[2];
+                        const uint8_t *lineA, *lineB;
+                        if (LAYOUT == TSP_LAYOUT_PLANAR) {
+                            const uint8_t* smp = sb + NMAT * p.qs_bytes;
+                            const uint8_t* dmp = smp + NMAT * p.sm_bytes;
+                            const uint8_t* smA = smp + (rowA * p.nblk + b) * 16;
+                            const uint8_t* smB = smp + (GATEUP ? p.sm_bytes : 0) + (rowB * p.nblk + b) * 16;
+                            const uint4 sa = *reinterpret_cast<const uint4*>(smA), sv = *reinterpret_cast<const uint4*>(smB);
+                            scA[0] = sa.x; scA[1] = sa.y; mnA[0] = sa.z; mnA[1] = sa.w;
+                            scB[0] = sv.x; scB[1] = sv.y; mnB[0] = sv.z; mnB[1] = sv.w;
+                            dmA = *reinterpret_cast<const uint32_t*>(dmp + (rowA * p.nblk + b) * 4);
+                            dmB = *reinterpret_cast<const uint32_t*>(dmp + (GATEUP ? p.dm_bytes : 0) + (rowB * p.nblk + b) * 4);
+                            lineA = sb + (bl * R + rowA) * 128;   // box order: byte, row, super-block
+                            lineB = boxB + (bl * R + rowB) * 128;
+                        } else {
+                            const uint8_t* blkA = sb + (rowA * p.kb + bl) * 144;   // box order: byte, super-block, row
+                            const uint8_t* blkB = boxB + (rowB * p.kb + bl) * 144;
+                            const uint4 ha = *reinterpret_cast<const uint4*>(blkA), hb = *reinterpret_cast<const uint4*>(blkB);
+                            dmA = ha.x; dmB = hb.x;
+                            scA[0] = ha.y & 0x3f3f3f3fu; mnA[0] = ha.z & 0x3f3f3f3fu;
+                            scA[1] = (ha.w & 0x0f0f0f0fu) | ((ha.y >> 2) & 0x30303030u);
+                            mnA[1] = ((ha.w >> 4) & 0x0f0f0f0fu) | ((ha.z >> 2) & 0x30303030u);
+                            scB[0] = hb.y & 0x3f3f3f3fu; mnB[0] = hb.z & 0x3f3f3f3fu;
+                            scB[1] = (hb.w & 0x0f0f0f0fu) | ((hb.y >> 2) & 0x30303030u);
+                            mnB[1] = ((hb.w >> 4) & 0x0f0f0f0fu) | ((hb.z >> 2) & 0x30303030u);
+                            lineA = blkA + 16; lineB = blkB + 16;
+                        }
+                        const float dA = half_bits_to_float(dmA & 0xffffu), mA = half_bits_to_float(dmA >> 16);
+                        const float dB = half_bits_to_float(dmB & 0xffffu), mB = half_bits_to_float(dmB >> 16);
+                        // ---- min term on the tensor cores: codes as subnormals, group sums as hi + lo ----
+                        const uint32_t mnpA = __byte_perm((((t & 2u) ? mnA[1] : mnA[0]) >> mn_shift) & 0xffffu, 0u, 0x4140);
+                        const uint32_t mnpB = __byte_perm((((t & 2u) ? mnB[1] : mnB[0]) >> mn_shift) & 0xffffu, 0u, 0x4140);
+                        float amin[NC][4];
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            const uint32_t sh = *reinterpret_cast<const uint32_t*>(sxp + c * 8 * p.sx_stride);
+                            const uint32_t sl = *reinterpret_cast<const uint32_t*>(sxp + (8u * NC + c * 8) * p.sx_stride);
+                            mma_f16_16816_zero(amin[c], mnpA, mnpB, mnpA, mnpB, sh, sl);
+                        }
+                        // scale factors: float(sc) through the 2^23 magic number, folded into one FMA each
+                        const float dA24 = dA * 16777216.f, dB24 = dB * 16777216.f;
+                        const float dA20 = dA * 1048576.f, dB20 = dB * 1048576.f;
+                        const float nA24 = -dA24 * 8388608.f, nB24 = -dB24 * 8388608.f, nA20 = -dA20 * 8388608.f, nB20 = -dB20 * 8388608.f;
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const uint64_t wa = *reinterpret_cast<const uint64_t*>(lineA + qoff[j]);
+                            const uint64_t wb = *reinterpret_cast<const uint64_t*>(lineB + qoff[j]);
+                            const uint32_t a0 = static_cast<uint32_t>(wa), a1 = static_cast<uint32_t>(wa >> 32);
+                            const uint32_t b0 = static_cast<uint32_t>(wb), b1 = static_cast<uint32_t>(wb >> 32);
+                            const uint32_t a0s = a0 >> 8, a1s = a1 >> 8, b0s = b0 >> 8, b1s = b1 >> 8;
+                            const uint32_t swa = scA[j >> 1], swb = scB[j >> 1];
+                            const uint32_t selL = (j & 1) ? 0x7442 : 0x7440, selH = (j & 1) ? 0x7443 : 0x7441;   // 0x4B0000ss = 2^23 + ss
+                            const float fAl = fmaf(dA24, __uint_as_float(__byte_perm(swa, 0x4b000000u, selL)), nA24);
+                            const float fAh = fmaf(dA20, __uint_as_float(__byte_perm(swa, 0x4b000000u, selH)), nA20);
+                            const float fBl = fmaf(dB24, __uint_as_float(__byte_perm(swb, 0x4b000000u, selL)), nB24);
+                            const float fBh = fmaf(dB20, __uint_as_float(__byte_perm(swb, 0x4b000000u, selH)), nB20);
+#pragma unroll
+                            for (int c = 0; c < NC; ++c) {
+                                const uint8_t* xr = xb + c * 8 * p.x_stride + j * 128;
+                                const uint4 xl = *reinterpret_cast<const uint4*>(xr), xh = *reinterpret_cast<const uint4*>(xr + 64);
+                                float al[4], ah[4];
+                                mma_f16_16816_zero(al, a0 & 0x000f000fu, b0 & 0x000f000fu, a0s & 0x000f000fu, b0s & 0x000f000fu, xl.x, xl.y);
+                                mma_f16_16816(al, a1 & 0x000f000fu, b1 & 0x000f000fu, a1s & 0x000f000fu, b1s & 0x000f000fu, xl.z, xl.w);
+                                mma_f16_16816_zero(ah, a0 & 0x00f000f0u, b0 & 0x00f000f0u, a0s & 0x00f000f0u, b0s & 0x00f000f0u, xh.x, xh.y);
+                                mma_f16_16816(ah, a1 & 0x00f000f0u, b1 & 0x00f000f0u, a1s & 0x00f000f0u, b1s & 0x00f000f0u, xh.z, xh.w);
+                                if (p.split_lo) {
+                                    const uint8_t* xs = xq + c * 8 * p.x_stride + j * 128;
+                                    const uint4 yl = *reinterpret_cast<const uint4*>(xs), yh = *reinterpret_cast<const uint4*>(xs + 64);
+                                    mma_f16_16816(al, a0 & 0x000f000fu, b0 & 0x000f000fu, a0s & 0x000f000fu, b0s & 0x000f000fu, yl.x, yl.y);
+                                    mma_f16_16816(al, a1 & 0x000f000fu, b1 & 0x000f000fu, a1s & 0x000f000fu, b1s & 0x000f000fu, yl.z, yl.w);
+                                    mma_f16_16816(ah, a0 & 0x00f000f0u, b0 & 0x00f000f0u, a0s & 0x00f000f0u, b0s & 0x00f000f0u, yh.x, yh.y);
+                                    mma_f16_16816(ah, a1 & 0x00f000f0u, b1 & 0x00f000f0u, a1s & 0x00f000f0u, b1s & 0x00f000f0u, yh.z, yh.w);
+                                }
+                                total[n][c][0] = fmaf(fAl, al[0], total[n][c][0]); total[n][c][1] = fmaf(fAl, al[1], total[n][c][1]);
+                                total[n][c][2] = fmaf(fBl, al[2], total[n][c][2]); total[n][c][3] = fmaf(fBl, al[3], total[n][c][3]);
+                                total[n][c][0] = fmaf(fAh, ah[0], total[n][c][0]); total[n][c][1] = fmaf(fAh, ah[1], total[n][c][1]);
+                                total[n][c][2] = fmaf(fBh, ah[2], total[n][c][2]); total[n][c][3] = fmaf(fBh, ah[3], total[n][c][3]);
+                            }
+                        }
+                        const float mA24 = -mA * 16777216.f, mB24 = -mB * 16777216.f;
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            total[n][c][0] = fmaf(mA24, amin[c][0], total[n][c][0]); total[n][c][1] = fmaf(mA24, amin[c][1], total[n][c][1]);
+                            total[n][c][2] = fmaf(mB24, amin[c][2], total[n][c][2]); total[n][c][3] = fmaf(mB24, amin[c][3], total[n][c][3]);
+                        }
+                    }
+                }
+                // the stage is free again: bring in the unit that will use it next
+                __syncwarp();
+                if (lane == 0 && k + S < my_units) issue(k + S);
+            }
+            // ---- epilogue: this warp owns its rows' complete sums ----
+            if (ok) {
+                bool bad = false;
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int c = 0; c < NC; ++c)
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const uint32_t j = c * 8 + 2 * t + q;
+                            if (j >= ti.count) continue;
+                            float* orow = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + rids[j] * p.out_stride_bytes);
+                            if (GATEUP) {
+                                const uint32_t hu = r0 + n * 8 + g;
+                                if (hu < p.rows) {
+                                    const float v = stable_silu(total[n][c][q]) * total[n][c][2 + q];
+                                    bad |= !finite_f32(v);
+                                    orow[hu] = v;
+                                }
+                            } else {
+                                const uint32_t r = r0 + n * 16 + g;
+                                if (r < p.rows) { bad |= !finite_f32(total[n][c][q]); orow[r] = total[n][c][q]; }
+                                if (r + 8 < p.rows) { bad |= !finite_f32(total[n][c][2 + q]); orow[r + 8] = total[n][c][2 + q]; }
+                            }
+                        }
+                if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
+            }
+        }
+        item = seg_end;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* base; uint64_t stride; uint32_t layout, rows, nblk, experts, box_rows, box_kb;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && stride == o.stride && layout == o.layout && rows == o.rows && nblk == o.nblk && experts == o.experts &&
+               box_rows == o.box_rows && box_kb == o.box_kb;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.base) * 1000003u ^ k.stride;
+        for (uint32_t v : {k.layout, k.rows, k.nblk, k.experts, k.box_rows, k.box_kb}) h = h * 1000003u ^ v;
+        return h;
+    }
+};
+
+// Tensor maps depend only on (address, shape, box); weights are immutable imports, so they are encoded once and kept.
+static int get_map(const MapKey& k, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(k);
+    if (it != cache.end()) { *out = it->second; return TSP_OK; }
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(TSP_E_CUDA, "the CUDA driver does not export cuTensorMapEncodeTiled");
+    CUtensorMap m;
+    cuuint64_t dims[4], strides[3];
+    cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+    CUtensorMapSwizzle swz;
+    if (k.layout == TSP_LAYOUT_PLANAR) {   // [128 B][row][super-block][expert]
+        dims[0] = 128; dims[1] = k.rows; dims[2] = k.nblk; dims[3] = k.experts;
+        strides[0] = static_cast<cuuint64_t>(k.nblk) * 128; strides[1] = 128; strides[2] = k.stride;
+        box[0] = 128; box[1] = k.box_rows; box[2] = k.box_kb; box[3] = 1;
+        swz = CU_TENSOR_MAP_SWIZZLE_128B;
+    } else {                               // [144 B][super-block][row][expert]
+        dims[0] = 144; dims[1] = k.nblk; dims[2] = k.rows; dims[3] = k.experts;
+        strides[0] = 144; strides[1] = static_cast<cuuint64_t>(k.nblk) * 144; strides[2] = k.stride;
+        box[0] = 144; box[1] = k.box_kb; box[2] = k.box_rows; box[3] = 1;
+        swz = CU_TENSOR_MAP_SWIZZLE_NONE;
+    }
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(k.base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TSP_E_CUDA, "cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(k, m);
+    *out = m;
+    return TSP_OK;
+}
+
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT>
+static int launch2(const CUtensorMap* maps, const Gemv2Params& p, size_t smem, int grid, cudaStream_t st) {
+    auto kernel = gemv2_kernel<LAYOUT, GATEUP, NC, NT>;
+    static thread_local size_t configured = 0;
+    if (smem > configured) {
+        TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured = smem;
+    }
+    kernel<<<grid, kThreads2, smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+// Returns TSP_OK after launching, or 1 when this pipeline does not cover the shape (the caller then uses the
+// first-generation kernel), or a negative error.
+int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const float* x, uint64_t x_stride_bytes,
+                        uint32_t in_div, uint32_t tokens, const uint32_t* token_map, const uint32_t* counts, const uint32_t* tasks,
+                        float* out, uint64_t out_stride_bytes, int f16_exact, int nc, uint32_t* error, cudaStream_t st) {
+    if (a->type != TSP_TYPE_Q4_K) return 1;
+    const uint32_t nblk = a->cols / 256;
+    if (a->rows % (gateup ? 8 : 16)) return 1;
+    Gemv2Params p{};
+    const bool planar = a->layout == TSP_LAYOUT_PLANAR;
+    p.split = a->split < a->experts ? a->split : a->experts;
+    p.experts = a->experts;
+    p.expert_stride = a->expert_stride;
+    p.rows = a->rows; p.cols = a->cols; p.nblk = nblk;
+    const uint64_t total_units = static_cast<uint64_t>(a->rows) * nblk;
+    p.sm_off = total_units * 128; p.dm_off = total_units * 144;
+    p.base[0] = static_cast<const uint8_t*>(a->base);
+    p.base[1] = static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base);
+    if (gateup) {
+        p.base[2] = static_cast<const uint8_t*>(b->base);
+        p.base[3] = static_cast<const uint8_t*>(b->base_hi ? b->base_hi : b->base);
+    }
+    // unit geometry: K in parts of at most 4 super-blocks; plain projections with a short K take two row tiles per unit
+    p.kb = nblk <= 4 ? nblk : 4;
+    p.kparts = (nblk + p.kb - 1) / p.kb;
+    p.nt = (!gateup && p.kparts == 1 && nblk <= 2 && a->rows % 32 == 0) ? 2 : 1;
+    p.rows_per_unit = (gateup ? 8 : 16) * p.nt;
+    p.groups = a->rows / p.rows_per_unit;
+    const uint32_t nmat = gateup ? 2 : 1;
+    p.box_bytes = p.rows_per_unit * p.kb * (planar ? 128 : 144);
+    p.qs_bytes = (p.box_bytes + 1023u) & ~1023u;
+    p.sm_bytes = planar ? p.rows_per_unit * nblk * 16 : 0;
+    p.dm_bytes = planar ? p.rows_per_unit * nblk * 4 : 0;
+    p.stage_bytes = (nmat * (p.qs_bytes + p.sm_bytes + p.dm_bytes) + 1023u) & ~1023u;
+    const uint32_t tok = 8u * static_cast<uint32_t>(nc);
+    p.split_lo = f16_exact ? 0 : 1;
+    p.x_stride = a->cols * 2 + 64;
+    p.sx_stride = (a->cols / 32) * 2 + 16;
+    uint32_t off = 1024;
+    p.off_xhi = off; off += tok * p.x_stride;
+    p.off_xlo = off; if (p.split_lo) off += tok * p.x_stride;
+    p.off_sx = off; off += 2 * tok * p.sx_stride;
+    off = (off + 1023u) & ~1023u;
+    p.off_stage = off;
+    const uint32_t budget = 226 * 1024;   // 1 KB of the 227 KB is kept for aligning the dynamic base
+    if (off + 2 * kW2 * p.stage_bytes > budget) return 1;   // too little room for a double-buffered pipeline per warp
+    p.n_stages = (budget - off) / (kW2 * p.stage_bytes);     // stages per warp
+    if (p.n_stages > kMaxStages2) p.n_stages = kMaxStages2;
+    const size_t smem = off + static_cast<size_t>(p.n_stages) * kW2 * p.stage_bytes + 1024;
+    p.x = x; p.x_stride_bytes = x_stride_bytes; p.in_div = in_div ? in_div : 1;
+    p.token_map = token_map; p.counts = counts; p.tasks = tasks; p.tokens = tokens;
+    p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;
+
+    CUtensorMap maps[4];
+    const uint32_t n_lo = p.split, n_hi = a->experts - p.split;
+    for (int m = 0; m < 4; ++m) {
+        if (!gateup && m >= 2) { maps[m] = maps[0]; continue; }
+        const bool hi = m & 1;
+        if (hi && n_hi == 0) { maps[m] = maps[m - 1]; continue; }
+        MapKey k{p.base[m], a->experts > 1 ? a->expert_stride : tsp_expert_bytes(a->type, a->layout, a->rows, a->cols), a->layout, a->rows, nblk,
+                 hi ? n_hi : n_lo, p.rows_per_unit, p.kb};
+        if (k.stride % 16) return 1;
+        if (int rc = get_map(k, &maps[m])) return rc;
+    }
+    const int grid = sm_count();
+    if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
+#define TSP_D2(L)                                                                                              \
+    if (a->layout == L) {                                                                                       \
+        if (gateup) return nc == 1 ? launch2<L, true, 1, 1>(maps, p, smem, grid, st) : launch2<L, true, 2, 1>(maps, p, smem, grid, st); \
+        if (p.nt == 2) return nc == 1 ? launch2<L, false, 1, 2>(maps, p, smem, grid, st) : launch2<L, false, 2, 2>(maps, p, smem, grid, st); \
+        return nc == 1 ? launch2<L, false, 1, 1>(maps, p, smem, grid, st) : launch2<L, false, 2, 1>(maps, p, smem, grid, st);           \
+    }
+    TSP_D2(TSP_LAYOUT_PLANAR)
+    TSP_D2(TSP_LAYOUT_GGUF)
+#undef TSP_D2
+    return 1;
+}
+
+}  // namespace tsp

@@ -26,8 +26,7 @@
 
 namespace tsp {
 
-constexpr int kW2 = 8;                       // consumer warps
-constexpr int kThreads2 = kW2 * 32;
+constexpr int kW2 = 8;                       // pipelines per CTA (one warp each, or a pair of warps each)
 constexpr uint32_t kMaxStages2 = 6;    // per warp
 
 struct Gemv2Params {
@@ -43,7 +42,7 @@ struct Gemv2Params {
     uint32_t qs_bytes, sm_bytes, dm_bytes;  // per matrix per stage (qs_bytes: region size, a multiple of 1024)
     uint32_t box_bytes;       // bytes one tensor copy delivers
     uint32_t stage_bytes, n_stages;   // n_stages: per warp
-    uint32_t off_xhi, off_xlo, off_sx, off_stage;
+    uint32_t off_xhi, off_xlo, off_sx, off_red, off_stage;
     uint32_t x_stride, sx_stride;
     const float* x; uint64_t x_stride_bytes; uint32_t in_div;
     const uint32_t* token_map; const uint32_t* counts; const uint32_t* tasks;
@@ -85,8 +84,12 @@ __device__ __forceinline__ Tile2 tile2(const Gemv2Params& p, uint32_t tile) {
 // unit that will reuse a stage right after the warp has finished reading that stage, and it waits only on
 // the full-barriers of its own stages. Program order inside the warp orders the reads of a stage before the
 // copy that overwrites it, so no empty-barrier is needed and no warp ever waits for another one.
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT>
-__global__ void __launch_bounds__(kThreads2, 1)
+//
+// PAIR: two warps share each pipeline and split its super-blocks between them (16 warps per SM instead of 8, for
+// latency hiding); they meet at a 64-thread named barrier once per unit, where the second warp also hands its
+// partial sums to the first at the end of a row group.
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR>
+__global__ void __launch_bounds__(kW2 * 32 * (PAIR ? 2 : 1), 1)
 gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_a_hi,
              const __grid_constant__ CUtensorMap map_b_lo, const __grid_constant__ CUtensorMap map_b_hi, const Gemv2Params p) {
     extern __shared__ uint8_t smem2_raw[];
@@ -94,8 +97,11 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
     uint8_t* smem2 = smem2_raw + ((1024u - (smem_u32(smem2_raw) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem2);
     uint32_t* rids = reinterpret_cast<uint32_t*>(smem2 + 512);
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t S = p.n_stages;   // stages per warp
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = PAIR ? threadIdx.x >> 6 : threadIdx.x >> 5;   // pipeline index
+    const uint32_t half = PAIR ? (threadIdx.x >> 5) & 1u : 0u;          // which warp of the pair
+    constexpr uint32_t NH = PAIR ? 2 : 1;
+    const uint32_t S = p.n_stages;   // stages per pipeline
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
 
     if (threadIdx.x == 0) {
@@ -145,11 +151,13 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
             }
         }
     };
-    if (lane == 0) for (uint32_t k = 0; k < min(S, my_units); ++k) issue(k);
+    if (lane == 0 && half == 0) for (uint32_t k = 0; k < min(S, my_units); ++k) issue(k);
 
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t ctid = threadIdx.x;
-    constexpr uint32_t CT = kThreads2;
+    constexpr uint32_t CT = kW2 * 32 * NH;
+    float* red = reinterpret_cast<float*>(smem2 + p.off_red);
+    uint32_t red_parity = 0;
     uint8_t* xhi = smem2 + p.off_xhi;
     uint8_t* xlo = smem2 + p.off_xlo;
     uint8_t* sxb = smem2 + p.off_sx;
@@ -239,11 +247,10 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                     ok = mbar_wait(&my_full[s], ph);
                     if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
                 }
-                if (!ok) continue;
                 const uint8_t* sb = my_stage0 + s * p.stage_bytes;
                 const uint32_t R = p.rows_per_unit;
-                const uint32_t kb_here = min(p.kb, p.nblk - kh * p.kb);
-                for (uint32_t bl = 0; bl < kb_here; ++bl) {
+                const uint32_t kb_here = ok ? min(p.kb, p.nblk - kh * p.kb) : 0u;
+                for (uint32_t bl = half; bl < kb_here; bl += NH) {
                     const uint32_t b = kh * p.kb + bl;   // super-block index along K
                     const uint8_t* xb = xhi + xlane + b * 512;
                     const uint8_t* xq = xlo + xlane + b * 512;
@@ -341,11 +348,36 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                     }
                 }
                 // the stage is free again: bring in the unit that will use it next
-                __syncwarp();
-                if (lane == 0 && k + S < my_units) issue(k + S);
+                if (PAIR) {
+                    if (half == 1 && kh + 1 == KP) {   // hand the partial sums of this row group to the first warp
+                        float* slot = red + ((red_parity * kW2 + warp) * 32 + lane) * (NT * NC * 4);
+#pragma unroll
+                        for (int n = 0; n < NT; ++n)
+#pragma unroll
+                            for (int c = 0; c < NC; ++c)
+                                *reinterpret_cast<float4*>(slot + (n * NC + c) * 4) = make_float4(total[n][c][0], total[n][c][1], total[n][c][2], total[n][c][3]);
+                    }
+                    named_bar_sync(1 + warp, 64);
+                } else {
+                    __syncwarp();
+                }
+                if (lane == 0 && half == 0 && k + S < my_units) issue(k + S);
+            }
+            if (PAIR) {
+                if (half == 0) {
+                    const float* slot = red + ((red_parity * kW2 + warp) * 32 + lane) * (NT * NC * 4);
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            const float4 v = *reinterpret_cast<const float4*>(slot + (n * NC + c) * 4);
+                            total[n][c][0] += v.x; total[n][c][1] += v.y; total[n][c][2] += v.z; total[n][c][3] += v.w;
+                        }
+                }
+                red_parity ^= 1u;
             }
             // ---- epilogue: this warp owns its rows' complete sums ----
-            if (ok) {
+            if (ok && half == 0) {
                 bool bad = false;
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
@@ -443,15 +475,15 @@ static int get_map(const MapKey& k, CUtensorMap* out) {
     return TSP_OK;
 }
 
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT>
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR>
 static int launch2(const CUtensorMap* maps, const Gemv2Params& p, size_t smem, int grid, cudaStream_t st) {
-    auto kernel = gemv2_kernel<LAYOUT, GATEUP, NC, NT>;
+    auto kernel = gemv2_kernel<LAYOUT, GATEUP, NC, NT, PAIR>;
     static thread_local size_t configured = 0;
     if (smem > configured) {
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    kernel<<<grid, kThreads2, smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+    kernel<<<grid, kW2 * 32 * (PAIR ? 2 : 1), smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -498,6 +530,9 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     p.off_xhi = off; off += tok * p.x_stride;
     p.off_xlo = off; if (p.split_lo) off += tok * p.x_stride;
     p.off_sx = off; off += 2 * tok * p.sx_stride;
+    off = (off + 15u) & ~15u;
+    const bool pair = nc == 1 && p.kb >= 2;   // two warps per pipeline when a unit has super-blocks to split
+    p.off_red = off; if (pair) off += 2 * kW2 * 32 * p.nt * nc * 16;
     off = (off + 1023u) & ~1023u;
     p.off_stage = off;
     const uint32_t budget = 226 * 1024;   // 1 KB of the 227 KB is kept for aligning the dynamic base
@@ -524,9 +559,16 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
 #define TSP_D2(L)                                                                                              \
     if (a->layout == L) {                                                                                       \
-        if (gateup) return nc == 1 ? launch2<L, true, 1, 1>(maps, p, smem, grid, st) : launch2<L, true, 2, 1>(maps, p, smem, grid, st); \
-        if (p.nt == 2) return nc == 1 ? launch2<L, false, 1, 2>(maps, p, smem, grid, st) : launch2<L, false, 2, 2>(maps, p, smem, grid, st); \
-        return nc == 1 ? launch2<L, false, 1, 1>(maps, p, smem, grid, st) : launch2<L, false, 2, 1>(maps, p, smem, grid, st);           \
+        if (gateup) {                                                                                           \
+            if (nc == 2) return launch2<L, true, 2, 1, false>(maps, p, smem, grid, st);                          \
+            return pair ? launch2<L, true, 1, 1, true>(maps, p, smem, grid, st) : launch2<L, true, 1, 1, false>(maps, p, smem, grid, st); \
+        }                                                                                                       \
+        if (p.nt == 2) {                                                                                        \
+            if (nc == 2) return launch2<L, false, 2, 2, false>(maps, p, smem, grid, st);                         \
+            return pair ? launch2<L, false, 1, 2, true>(maps, p, smem, grid, st) : launch2<L, false, 1, 2, false>(maps, p, smem, grid, st); \
+        }                                                                                                       \
+        if (nc == 2) return launch2<L, false, 2, 1, false>(maps, p, smem, grid, st);                             \
+        return pair ? launch2<L, false, 1, 1, true>(maps, p, smem, grid, st) : launch2<L, false, 1, 1, false>(maps, p, smem, grid, st); \
     }
     TSP_D2(TSP_LAYOUT_PLANAR)
     TSP_D2(TSP_LAYOUT_GGUF)

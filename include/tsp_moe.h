@@ -200,6 +200,34 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
                          void* d_out, uint64_t out_stride_bytes, uint32_t out_dtype,
                          uint32_t* d_error, void* stream);
 
+/* No counterpart in the reference (its graph always works out of caller-allocated buffers).
+ *
+ * The same layer as tsp_moe_layer_decode, for callers that have nowhere to get scratch from: code that runs
+ * where device allocation is forbidden or unavailable -- inside a host callback or another library's plugin
+ * hook, under an allocator the embedding application owns exclusively, or late in a process whose memory
+ * pool is already fully handed out. The caller passes only weights, inputs and outputs; every intermediate
+ * buffer lives in one array of TSP_STATIC_SCRATCH_BYTES that is part of the library image, so each GPU that
+ * loads the library gives up that much memory until the process exits.
+ *
+ *  - Limit: the layer shape and token count must fit the array; tsp_moe_layer_decode_static_bytes() tells what
+ *    a call needs (0 for an invalid shape). At hidden 2048 / FFN 512 / 512 experts / top-10 that is 32 token
+ *    rows. Anything larger is refused with TSP_E_ARG and a message naming both sizes; nothing is launched.
+ *  - The first call on each device looks up the array's device address (with that device current). Make that
+ *    first call during start-up, before any stream capture begins.
+ *  - No cudaMalloc / cudaFree / allocating library routine is called, on the first call or later.
+ *  - All calls on one device share the one array, which simply keeps what the last call left there; nothing in
+ *    it needs clearing between calls. Two calls whose kernels overlap on the GPU (different streams, or
+ *    different host threads) would overwrite each other's intermediates: keep calls on one device ordered. */
+#define TSP_STATIC_SCRATCH_BYTES (4ull << 20)
+uint64_t tsp_moe_layer_decode_static_bytes(uint32_t tokens, uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected);
+int tsp_moe_layer_decode_static(const tsp_moe_weights* w,
+                                const void* d_x, uint64_t x_stride_bytes, uint32_t x_dtype,
+                                const float* d_logits, uint64_t logits_stride_bytes,
+                                uint32_t tokens, uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected,
+                                uint32_t mode, int normalize_selected,
+                                void* d_out, uint64_t out_stride_bytes, uint32_t out_dtype,
+                                uint32_t* d_error, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -298,4 +298,87 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
                            out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Entry point that needs no caller scratch and performs no device allocation.
+// ---------------------------------------------------------------------------------------------
+// All intermediate buffers of one layer call live in this array. Every device that loads the library
+// carries it from load until process exit.
+static __device__ __align__(256) unsigned char g_static_scratch[TSP_STATIC_SCRATCH_BYTES];
+
+namespace {
+// The array's name is only a host-side handle; kernels need its device address, which is looked up once per
+// device (with that device current) and remembered here.
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_addr[kMaxDevices] = {};
+
+struct StaticPlan {
+    uint64_t ids, weights, hidden, routed, shared_hidden, shared_out, shared_logit, x32, token_map, counts, tasks, total;
+};
+
+StaticPlan plan_static(uint32_t tokens, uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected) {
+    StaticPlan pl{};
+    uint64_t at = 0;
+    auto take = [&](uint64_t bytes) { const uint64_t here = at; at += (bytes + 255) & ~uint64_t(255); return here; };
+    const uint64_t T = tokens, K = selected;
+    pl.ids = take(T * K * 4);
+    pl.weights = take(T * K * 4);
+    pl.hidden = take(T * K * hidden * 4);
+    pl.routed = take(T * K * channels * 4);
+    pl.shared_hidden = take(T * hidden * 4);
+    pl.shared_out = take(T * channels * 4);
+    pl.shared_logit = take(T * 4);
+    pl.x32 = take(T * channels * 4);
+    pl.token_map = take(uint64_t(experts) * T * 4);
+    pl.counts = take(uint64_t(experts) * 4);
+    pl.tasks = take(tsp_moe_tasks_words(tokens, experts, selected, TSP_GEMV_TILE) * 4);
+    pl.total = at;
+    return pl;
+}
+}  // namespace
+
+uint64_t tsp_moe_layer_decode_static_bytes(uint32_t tokens, uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected) {
+    if (!tokens || !channels || !hidden || !experts || !selected || selected > 64) return 0;
+    return plan_static(tokens, channels, hidden, experts, selected).total;
+}
+
+int tsp_moe_layer_decode_static(const tsp_moe_weights* w, const void* d_x, uint64_t x_stride, uint32_t x_dtype,
+                                const float* d_logits, uint64_t logits_stride, uint32_t tokens, uint32_t channels,
+                                uint32_t hidden, uint32_t experts, uint32_t selected, uint32_t mode, int normalize,
+                                void* d_out, uint64_t out_stride, uint32_t out_dtype, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(tokens >= 1 && channels >= 1 && hidden >= 1 && experts >= 1 && selected >= 1 && selected <= 64 && experts <= 4096,
+                "static layer: invalid layer shape");
+    const StaticPlan pl = plan_static(tokens, channels, hidden, experts, selected);
+    if (pl.total > TSP_STATIC_SCRATCH_BYTES)
+        return fail(TSP_E_ARG, "static layer: %u tokens of this layer shape need %llu bytes of scratch, the built-in array holds %llu; "
+                               "use tsp_moe_layer_decode with caller scratch", tokens, static_cast<unsigned long long>(pl.total),
+                    static_cast<unsigned long long>(TSP_STATIC_SCRATCH_BYTES));
+    int dev = 0;
+    TSP_CUDA(cudaGetDevice(&dev));
+    TSP_REQUIRE(dev >= 0 && dev < kMaxDevices, "static layer: device ordinal %d out of range", dev);
+    if (!g_static_scratch_addr[dev]) {   // first call on this device: resolve the array's device address
+        unsigned char* addr = nullptr;
+        TSP_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_static_scratch));
+        TSP_REQUIRE(addr != nullptr, "static layer: the scratch array has no device address");
+        g_static_scratch_addr[dev] = addr;
+    }
+    unsigned char* base = g_static_scratch_addr[dev];
+    tsp_moe_scratch s{};
+    s.d_ids = reinterpret_cast<uint32_t*>(base + pl.ids);
+    s.d_weights = reinterpret_cast<float*>(base + pl.weights);
+    s.d_hidden = reinterpret_cast<float*>(base + pl.hidden);
+    s.d_routed = reinterpret_cast<float*>(base + pl.routed);
+    s.d_shared_hidden = reinterpret_cast<float*>(base + pl.shared_hidden);
+    s.d_shared_out = reinterpret_cast<float*>(base + pl.shared_out);
+    s.d_shared_logit = reinterpret_cast<float*>(base + pl.shared_logit);
+    s.d_x32 = reinterpret_cast<float*>(base + pl.x32);
+    s.d_token_map = reinterpret_cast<uint32_t*>(base + pl.token_map);
+    s.d_counts = reinterpret_cast<uint32_t*>(base + pl.counts);
+    s.d_tasks = reinterpret_cast<uint32_t*>(base + pl.tasks);
+    s.capacity = tokens;
+    // Nothing in the scratch has to start at zero: every region is fully written by the launch that produces it
+    // before any launch reads it, so the previous call's contents are simply overwritten.
+    return tsp_moe_layer_decode(w, &s, d_x, x_stride, x_dtype, d_logits, logits_stride, tokens, channels, hidden, experts, selected,
+                                mode, normalize, d_out, out_stride, out_dtype, d_error, stream);
+}
+
 }  // extern "C"

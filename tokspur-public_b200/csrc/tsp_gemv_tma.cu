@@ -28,6 +28,7 @@ namespace tsp {
 
 constexpr int kW2 = 8;                       // pipelines per CTA (one warp each, or a pair of warps each)
 constexpr uint32_t kMaxStages2 = 6;    // per warp
+constexpr uint32_t kTableTiles = 32;   // token tiles whose routing data a CTA caches in shared memory
 
 struct Gemv2Params {
     const uint8_t* base[4];   // planar 1D planes: A_lo, A_hi, B_lo, B_hi expert-0 addresses
@@ -88,7 +89,8 @@ __device__ __forceinline__ Tile2 tile2(const Gemv2Params& p, uint32_t tile) {
 // PAIR: two warps share each pipeline and split its super-blocks between them (16 warps per SM instead of 8, for
 // latency hiding); they meet at a 64-thread named barrier once per unit, where the second warp also hands its
 // partial sums to the first at the end of a row group.
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR>
+// KBT: super-blocks per unit fixed at compile time (the loop over them is then fully unrolled), or 0 for the run-time value.
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR, int KBT>
 __global__ void __launch_bounds__(kW2 * 32 * (PAIR ? 2 : 1), 1)
 gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_a_hi,
              const __grid_constant__ CUtensorMap map_b_lo, const __grid_constant__ CUtensorMap map_b_hi, const Gemv2Params p) {
@@ -115,24 +117,52 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
     const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
     const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
     const uint32_t KP = p.kparts;
+    // Tile table: the (expert, first route, route count) and route ids of the first kTableTiles token tiles this CTA touches,
+    // fetched once and in parallel, so that the dependent global loads behind them are not paid again at every tile change.
+    uint32_t* tt = reinterpret_cast<uint32_t*>(smem2 + 1024);          // [kTableTiles][4]
+    uint32_t* trid = reinterpret_cast<uint32_t*>(smem2 + 1024 + 512);  // [kTableTiles][16]
+    const uint32_t t0 = item0 / p.groups;
+    for (uint32_t i = threadIdx.x; i < kTableTiles * 16; i += blockDim.x) {
+        const uint32_t tl = i >> 4, slot = i & 15u, tile = t0 + tl;
+        if (tile < n_tiles && item0 < item1) {
+            const Tile2 ti = tile2<NC>(p, tile);
+            if (slot == 0) { tt[tl * 4] = ti.expert; tt[tl * 4 + 1] = ti.start; tt[tl * 4 + 2] = ti.count; }
+            uint32_t rid = 0;
+            if (slot < ti.count) rid = p.token_map ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + slot] : ti.start + slot;
+            trid[i] = rid;
+        }
+    }
+    __syncthreads();
+    auto get_tile = [&](uint32_t tile) {
+        const uint32_t tl = tile - t0;
+        if (tl < kTableTiles) return Tile2{tt[tl * 4], tt[tl * 4 + 1], tt[tl * 4 + 2]};
+        return tile2<NC>(p, tile);
+    };
     // this warp's items are item0 + warp + 8n; its unit k is part (k % KP) of item item0 + warp + 8*(k / KP)
     const uint32_t my_items = item0 + warp < item1 ? (item1 - item0 - warp + kW2 - 1) / kW2 : 0u;
     const uint32_t my_units = my_items * KP;
     uint8_t* my_stage0 = smem2 + p.off_stage + warp * S * p.stage_bytes;
     uint64_t* my_full = full + warp * S;
 
-    // lane 0: issue the copies of unit k into stage k % S
-    uint32_t issue_tile = 0xffffffffu;
+    // lane 0: issue the copies of this pipeline's next unit (units are issued strictly in order, so the stage, K part,
+    // row group and tile advance incrementally; nothing here divides)
+    uint32_t iss_tile = (item0 + warp) / p.groups, iss_grp = (item0 + warp) % p.groups, iss_kh = 0, iss_s = 0, issued = 0;
+    uint32_t iss_ti_tile = 0xffffffffu;
     Tile2 issue_ti{0, 0, 0};
-    auto issue = [&](uint32_t k) {
-        const uint32_t it = item0 + warp + kW2 * (k / KP), kh = k % KP;
-        const uint32_t tile = it / p.groups, grp = it % p.groups;
-        if (tile != issue_tile) { issue_ti = tile2<NC>(p, tile); issue_tile = tile; }
-        const uint32_t r0 = grp * p.rows_per_unit;
+    auto issue_next = [&]() {
+        if (iss_tile != iss_ti_tile) { issue_ti = get_tile(iss_tile); iss_ti_tile = iss_tile; }
+        const uint32_t kh = iss_kh, s = iss_s;
+        const uint32_t r0 = iss_grp * p.rows_per_unit;
         const uint32_t nr = min(p.rows_per_unit, p.rows - r0);
         const bool hi = issue_ti.expert >= p.split;
         const uint32_t el = hi ? issue_ti.expert - p.split : issue_ti.expert;
-        const uint32_t s = k % S;
+        ++issued;
+        if (++iss_s == S) iss_s = 0;
+        if (++iss_kh == KP) {
+            iss_kh = 0;
+            iss_grp += kW2;
+            while (iss_grp >= p.groups) { iss_grp -= p.groups; ++iss_tile; }
+        }
         uint8_t* sb = my_stage0 + s * p.stage_bytes;
         uint32_t bytes = NMAT * p.box_bytes;
         if (LAYOUT == TSP_LAYOUT_PLANAR) bytes += NMAT * nr * p.nblk * 20u;
@@ -151,7 +181,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
             }
         }
     };
-    if (lane == 0 && half == 0) for (uint32_t k = 0; k < min(S, my_units); ++k) issue(k);
+    if (lane == 0 && half == 0) while (issued < min(S, my_units)) issue_next();
 
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t ctid = threadIdx.x;
@@ -170,20 +200,26 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
     const uint32_t sxlane = g * p.sx_stride + t * 4;
     const uint32_t mn_shift = 16 * (t & 1);
 
-    uint32_t k = 0;   // this warp's next unit
+    uint32_t my_it = item0 + warp;                  // this pipeline's next item
+    uint32_t my_grp = (item0 + warp) % p.groups;    // its row group
+    uint32_t cs = 0, cph = 0;                       // stage and phase of this pipeline's next unit
     uint32_t item = item0;
     while (item < item1) {
         // ---- one token tile: the segment of this CTA's items that share it ----
         const uint32_t tile = item / p.groups;
         const uint32_t seg_end = min(item1, (tile + 1) * p.groups);
-        __syncthreads();
-        const Tile2 ti = tile2<NC>(p, tile);
-        if (ctid < 8u * NC) {
-            uint32_t rid = 0;
-            if (ctid < ti.count) rid = p.token_map ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + ctid] : ti.start + ctid;
-            rids[ctid] = rid;
+        __syncthreads();   // every warp is done with the previous tile's activations
+        const Tile2 ti = get_tile(tile);
+        const uint32_t* cur_rids = trid + (tile - t0) * 16;
+        if (tile - t0 >= kTableTiles) {   // beyond the cached window: fetch this tile's route ids now
+            if (ctid < 8u * NC) {
+                uint32_t rid = 0;
+                if (ctid < ti.count) rid = p.token_map ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + ctid] : ti.start + ctid;
+                rids[ctid] = rid;
+            }
+            cur_rids = rids;
+            __syncthreads();
         }
-        __syncthreads();
         {
             const uint32_t per_row = p.cols / 8;
             const uint32_t units = ti.count * per_row;
@@ -195,7 +231,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                 uint32_t j = 0, k8 = 0;
                 if (active) {
                     j = u / per_row; k8 = u % per_row;
-                    const uint32_t in_row = rids[j] / p.in_div;
+                    const uint32_t in_row = cur_rids[j] / p.in_div;
                     const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + k8 * 2;
                     const float4 v0 = src[0], v1 = src[1];
                     const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -232,26 +268,31 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
         __syncthreads();
 
         // ---- this warp's row groups of the segment ----
-        for (uint32_t it = item0 + warp + kW2 * (k / KP); it < seg_end; it += kW2) {
-            const uint32_t grp = it % p.groups;
-            const uint32_t r0 = grp * p.rows_per_unit;
+        for (; my_it < seg_end; my_it += kW2) {
+            const uint32_t r0 = my_grp * p.rows_per_unit;
+            my_grp += kW2;
+            while (my_grp >= p.groups) my_grp -= p.groups;
             float total[NT][NC][4];
 #pragma unroll
             for (int n = 0; n < NT; ++n)
 #pragma unroll
                 for (int c = 0; c < NC; ++c) total[n][c][0] = total[n][c][1] = total[n][c][2] = total[n][c][3] = 0.f;
 
-            for (uint32_t kh = 0; kh < KP; ++kh, ++k) {
-                const uint32_t s = k % S, ph = (k / S) & 1u;
+            for (uint32_t kh = 0; kh < KP; ++kh) {
+                const uint32_t s = cs, ph = cph;
+                if (++cs == S) { cs = 0; cph ^= 1u; }
                 if (ok) {
                     ok = mbar_wait(&my_full[s], ph);
                     if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
                 }
                 const uint8_t* sb = my_stage0 + s * p.stage_bytes;
                 const uint32_t R = p.rows_per_unit;
-                const uint32_t kb_here = ok ? min(p.kb, p.nblk - kh * p.kb) : 0u;
-                for (uint32_t bl = half; bl < kb_here; bl += NH) {
-                    const uint32_t b = kh * p.kb + bl;   // super-block index along K
+                const uint32_t KB = KBT ? KBT : p.kb;
+                const uint32_t kb_here = !ok ? 0u : (KBT ? KBT : min(p.kb, p.nblk - kh * p.kb));
+#pragma unroll
+                for (uint32_t bl = half; bl < (KBT ? KBT : kb_here); bl += NH) {
+                    if (KBT && !ok) break;
+                    const uint32_t b = kh * KB + bl;   // super-block index along K
                     const uint8_t* xb = xhi + xlane + b * 512;
                     const uint8_t* xq = xlo + xlane + b * 512;
                     const uint8_t* sxp = sxb + sxlane + b * 16;
@@ -275,8 +316,8 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                             lineA = sb + (bl * R + rowA) * 128;   // box order: byte, row, super-block
                             lineB = boxB + (bl * R + rowB) * 128;
                         } else {
-                            const uint8_t* blkA = sb + (rowA * p.kb + bl) * 144;   // box order: byte, super-block, row
-                            const uint8_t* blkB = boxB + (rowB * p.kb + bl) * 144;
+                            const uint8_t* blkA = sb + (rowA * KB + bl) * 144;   // box order: byte, super-block, row
+                            const uint8_t* blkB = boxB + (rowB * KB + bl) * 144;
                             const uint4 ha = *reinterpret_cast<const uint4*>(blkA), hb = *reinterpret_cast<const uint4*>(blkB);
                             dmA = ha.x; dmB = hb.x;
                             scA[0] = ha.y & 0x3f3f3f3fu; mnA[0] = ha.z & 0x3f3f3f3fu;
@@ -361,7 +402,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                 } else {
                     __syncwarp();
                 }
-                if (lane == 0 && half == 0 && k + S < my_units) issue(k + S);
+                if (lane == 0 && half == 0 && issued < my_units) issue_next();
             }
             if (PAIR) {
                 if (half == 0) {
@@ -387,7 +428,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                         for (int q = 0; q < 2; ++q) {
                             const uint32_t j = c * 8 + 2 * t + q;
                             if (j >= ti.count) continue;
-                            float* orow = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + rids[j] * p.out_stride_bytes);
+                            float* orow = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + cur_rids[j] * p.out_stride_bytes);
                             if (GATEUP) {
                                 const uint32_t hu = r0 + n * 8 + g;
                                 if (hu < p.rows) {
@@ -475,9 +516,9 @@ static int get_map(const MapKey& k, CUtensorMap* out) {
     return TSP_OK;
 }
 
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR>
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR, int KBT>
 static int launch2(const CUtensorMap* maps, const Gemv2Params& p, size_t smem, int grid, cudaStream_t st) {
-    auto kernel = gemv2_kernel<LAYOUT, GATEUP, NC, NT, PAIR>;
+    auto kernel = gemv2_kernel<LAYOUT, GATEUP, NC, NT, PAIR, KBT>;
     static thread_local size_t configured = 0;
     if (smem > configured) {
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -526,12 +567,12 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     p.split_lo = f16_exact ? 0 : 1;
     p.x_stride = a->cols * 2 + 64;
     p.sx_stride = (a->cols / 32) * 2 + 16;
-    uint32_t off = 1024;
+    uint32_t off = 4096;   // barriers, fallback route ids, tile table
     p.off_xhi = off; off += tok * p.x_stride;
     p.off_xlo = off; if (p.split_lo) off += tok * p.x_stride;
     p.off_sx = off; off += 2 * tok * p.sx_stride;
     off = (off + 15u) & ~15u;
-    const bool pair = nc == 1 && p.kb >= 2;   // two warps per pipeline when a unit has super-blocks to split
+    const bool pair = false;   // paired warps (two per pipeline) measured no faster than one warp per pipeline; kept in the kernel, not dispatched
     p.off_red = off; if (pair) off += 2 * kW2 * 32 * p.nt * nc * 16;
     off = (off + 1023u) & ~1023u;
     p.off_stage = off;
@@ -557,22 +598,29 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     }
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
-#define TSP_D2(L)                                                                                              \
-    if (a->layout == L) {                                                                                       \
-        if (gateup) {                                                                                           \
-            if (nc == 2) return launch2<L, true, 2, 1, false>(maps, p, smem, grid, st);                          \
-            return pair ? launch2<L, true, 1, 1, true>(maps, p, smem, grid, st) : launch2<L, true, 1, 1, false>(maps, p, smem, grid, st); \
-        }                                                                                                       \
-        if (p.nt == 2) {                                                                                        \
-            if (nc == 2) return launch2<L, false, 2, 2, false>(maps, p, smem, grid, st);                         \
-            return pair ? launch2<L, false, 1, 2, true>(maps, p, smem, grid, st) : launch2<L, false, 1, 2, false>(maps, p, smem, grid, st); \
-        }                                                                                                       \
-        if (nc == 2) return launch2<L, false, 2, 1, false>(maps, p, smem, grid, st);                             \
-        return pair ? launch2<L, false, 1, 1, true>(maps, p, smem, grid, st) : launch2<L, false, 1, 1, false>(maps, p, smem, grid, st); \
+    // compile-time super-block count for the common shapes of the planar layout (K a multiple of 1024, or K = 512)
+    const int kbt = (planar && nblk % p.kb == 0 && (p.kb == 4 || (p.kb == 2 && p.nt == 2))) ? static_cast<int>(p.kb) : 0;
+#define TSP_D3(L, G, NCV, NTV, K) return launch2<L, G, NCV, NTV, false, K>(maps, p, smem, grid, st)
+#define TSP_D2(L, SPEC)                                                                 \
+    if (a->layout == L) {                                                                \
+        if (gateup) {                                                                    \
+            if (SPEC && kbt == 4) { if (nc == 1) TSP_D3(L, true, 1, 1, 4); TSP_D3(L, true, 2, 1, 4); } \
+            if (nc == 1) TSP_D3(L, true, 1, 1, 0);                                       \
+            TSP_D3(L, true, 2, 1, 0);                                                    \
+        }                                                                                \
+        if (p.nt == 2) {                                                                 \
+            if (SPEC && kbt == 2) { if (nc == 1) TSP_D3(L, false, 1, 2, 2); TSP_D3(L, false, 2, 2, 2); } \
+            if (nc == 1) TSP_D3(L, false, 1, 2, 0);                                      \
+            TSP_D3(L, false, 2, 2, 0);                                                   \
+        }                                                                                \
+        if (SPEC && kbt == 4) { if (nc == 1) TSP_D3(L, false, 1, 1, 4); TSP_D3(L, false, 2, 1, 4); } \
+        if (nc == 1) TSP_D3(L, false, 1, 1, 0);                                          \
+        TSP_D3(L, false, 2, 1, 0);                                                       \
     }
-    TSP_D2(TSP_LAYOUT_PLANAR)
-    TSP_D2(TSP_LAYOUT_GGUF)
+    TSP_D2(TSP_LAYOUT_PLANAR, true)
+    TSP_D2(TSP_LAYOUT_GGUF, false)
 #undef TSP_D2
+#undef TSP_D3
     return 1;
 }
 

@@ -257,7 +257,7 @@ def run_ours(args):
                        "l2_policy": "inputs larger than L2: each step streams ~650 MB of distinct expert weights"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2},
-            "gpu_launches": 9 * args.steps, "clocks": clk, "roofline": roofline, "cpu_baseline": cpu,
+            "gpu_launches": 7 * args.steps, "clocks": clk, "roofline": roofline, "cpu_baseline": cpu,
             "extra": {"layer_hbm_gbs": layer_bytes / (ms * 1e-3) / 1e9, "layer_hbm_frac": layer_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
                       "layer_algorithmic_bytes": layer_bytes, "unique_experts": U, "stage_ms": stages, "parity_rel_l2_vs_cpu": parity,
                       "layer_tflops": T * (SELECTED + 1) * FLOPS_PER_ROUTE / (ms * 1e-3) / 1e12}}

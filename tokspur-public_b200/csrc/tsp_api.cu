@@ -44,7 +44,7 @@ int launch_combine(const float*, uint64_t, const float*, const float*, uint64_t,
 int launch_f16_to_f32(const void*, uint64_t, float*, uint64_t, uint32_t, uint32_t, cudaStream_t);
 int launch_dequant(uint32_t, uint32_t, const uint8_t*, uint64_t, float*, uint32_t*, cudaStream_t);
 int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*, uint64_t, uint32_t, uint32_t,
-                const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t);
+                const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t, const GemvShared* = nullptr);
 
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
@@ -283,14 +283,43 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
     const int exact = x_dtype == 1;
     if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
     if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GEMV_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
-    if (int rc = tsp_moe_gate_up_swiglu(&w->gate, &w->up, x32, x32_stride, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
-                                        s->d_hidden, hidden * 4ull, exact, d_error, st)) return rc;
-    if (int rc = tsp_moe_project(&w->down, s->d_hidden, hidden * 4ull, 1, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
-                                 s->d_routed, channels * 4ull, 0, d_error, st)) return rc;
-    if (int rc = tsp_moe_gate_up_swiglu(&w->shared_gate, &w->shared_up, x32, x32_stride, tokens, 1, nullptr, nullptr, nullptr,
-                                        s->d_shared_hidden, hidden * 4ull, exact, d_error, st)) return rc;
-    if (int rc = tsp_moe_project(&w->shared_down, s->d_shared_hidden, hidden * 4ull, 1, tokens, 1, nullptr, nullptr, nullptr,
-                                 s->d_shared_out, channels * 4ull, 0, d_error, st)) return rc;
+    // Routed and shared experts in one launch each when the shared expert looks like a routed one (same shape, encoding and
+    // layout, Q4_K); otherwise (launch_gemv answers 1) the shared expert gets its own two launches.
+    bool fused_gate_up = false, fused_down = false;
+    const bool same_shape = w->shared_gate.type == w->gate.type && w->shared_gate.layout == w->gate.layout &&
+                            w->shared_up.type == w->gate.type && w->shared_up.layout == w->gate.layout &&
+                            w->shared_up.rows == hidden && w->shared_up.cols == channels &&
+                            w->shared_down.type == w->down.type && w->shared_down.layout == w->down.layout;
+    if (same_shape && check_matrix(&w->gate, "gate") == TSP_OK && check_matrix(&w->up, "up") == TSP_OK &&
+        check_matrix(&w->shared_gate, "shared gate") == TSP_OK && check_matrix(&w->shared_up, "shared up") == TSP_OK &&
+        w->gate.type == w->up.type && w->gate.layout == w->up.layout && w->up.rows == hidden && w->up.cols == channels &&
+        w->up.experts == experts && w->gate.expert_stride == w->up.expert_stride && w->gate.split == w->up.split &&
+        aligned16(x32) && x32_stride % 16 == 0) {
+        const GemvShared sh{&w->shared_gate, &w->shared_up, x32, x32_stride, s->d_shared_hidden, hidden * 4ull};
+        const int rc = launch_gemv(&w->gate, &w->up, true, x32, x32_stride, selected, tokens, s->d_token_map, s->d_counts, s->d_tasks,
+                                   s->d_hidden, hidden * 4ull, exact, 1, d_error, st, &sh);
+        if (rc < 0) return rc;
+        fused_gate_up = rc == 0;
+    }
+    if (!fused_gate_up) {
+        if (int rc = tsp_moe_gate_up_swiglu(&w->gate, &w->up, x32, x32_stride, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
+                                            s->d_hidden, hidden * 4ull, exact, d_error, st)) return rc;
+        if (int rc = tsp_moe_gate_up_swiglu(&w->shared_gate, &w->shared_up, x32, x32_stride, tokens, 1, nullptr, nullptr, nullptr,
+                                            s->d_shared_hidden, hidden * 4ull, exact, d_error, st)) return rc;
+    }
+    if (same_shape && channels % 16 == 0 && check_matrix(&w->down, "down") == TSP_OK && check_matrix(&w->shared_down, "shared down") == TSP_OK) {
+        const GemvShared sh{&w->shared_down, nullptr, s->d_shared_hidden, hidden * 4ull, s->d_shared_out, channels * 4ull};
+        const int rc = launch_gemv(&w->down, nullptr, false, s->d_hidden, hidden * 4ull, 1, tokens, s->d_token_map, s->d_counts, s->d_tasks,
+                                   s->d_routed, channels * 4ull, 0, 1, d_error, st, &sh);
+        if (rc < 0) return rc;
+        fused_down = rc == 0;
+    }
+    if (!fused_down) {
+        if (int rc = tsp_moe_project(&w->down, s->d_hidden, hidden * 4ull, 1, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
+                                     s->d_routed, channels * 4ull, 0, d_error, st)) return rc;
+        if (int rc = tsp_moe_project(&w->shared_down, s->d_shared_hidden, hidden * 4ull, 1, tokens, 1, nullptr, nullptr, nullptr,
+                                     s->d_shared_out, channels * 4ull, 0, d_error, st)) return rc;
+    }
     // binary16 output rows are written straight from the FP32 mixture; no FP32 copy of the output is kept
     return tsp_moe_combine(s->d_routed, channels * 4ull, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32,
                            x32_stride, s->d_shared_logit, tokens, channels, selected,

@@ -19,6 +19,14 @@ int cuda_fail(cudaError_t e, const char* what);
 #define TSP_CUDA(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return ::tsp::cuda_fail(e_, #expr); } while (0)
 int sm_count();  // SM count of the current device (cached), 0 when no device is usable
 
+// A dense expert (experts == 1 sets with the routed experts' shape, encoding and layout) that a routed projection launch
+// also processes, for every token row: input rows `x`, output rows `out`. b is used by gate-up launches only.
+struct GemvShared {
+    const tsp_matrix_set* a; const tsp_matrix_set* b;
+    const float* x; uint64_t x_stride_bytes;
+    float* out; uint64_t out_stride_bytes;
+};
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------------------------

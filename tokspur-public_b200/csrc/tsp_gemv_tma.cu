@@ -51,6 +51,12 @@ struct Gemv2Params {
     float* out; uint64_t out_stride_bytes;
     int split_lo;
     uint32_t* error;
+    // optional dense "shared" expert processed by the same launch after the routed tiles (sh_tiles == 0: none):
+    // same shape/encoding/layout as the routed experts, every token row as input, its own output rows
+    const uint8_t* sh_base[2];
+    const float* sh_x; uint64_t sh_x_stride_bytes;
+    float* sh_out; uint64_t sh_out_stride_bytes;
+    uint32_t sh_tiles;
 };
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
@@ -62,9 +68,16 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
 
 struct Tile2 { uint32_t expert, start, count; };
 
+// A tile of the shared expert carries the expert id p.experts (one past the routed ids) and identity route ids.
 template <int NC>
-__device__ __forceinline__ Tile2 tile2(const Gemv2Params& p, uint32_t tile) {
+__device__ __forceinline__ Tile2 tile2(const Gemv2Params& p, uint32_t tile, uint32_t routed_tiles) {
     Tile2 t;
+    if (tile >= routed_tiles && p.sh_tiles) {
+        t.expert = p.experts;
+        t.start = (tile - routed_tiles) * 8u * NC;
+        t.count = min(p.tokens - t.start, 8u * NC);
+        return t;
+    }
     if (p.token_map) {
         t.expert = p.tasks[2 + 2 * tile];
         t.start = p.tasks[3 + 2 * tile];
@@ -90,10 +103,12 @@ __device__ __forceinline__ Tile2 tile2(const Gemv2Params& p, uint32_t tile) {
 // latency hiding); they meet at a 64-thread named barrier once per unit, where the second warp also hands its
 // partial sums to the first at the end of a row group.
 // KBT: super-blocks per unit fixed at compile time (the loop over them is then fully unrolled), or 0 for the run-time value.
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR, int KBT>
+// SPLIT: also run the low-half pass of the activations (needed unless every activation is exactly a binary16 value).
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR, int KBT, bool SPLIT>
 __global__ void __launch_bounds__(kW2 * 32 * (PAIR ? 2 : 1), 1)
 gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_a_hi,
-             const __grid_constant__ CUtensorMap map_b_lo, const __grid_constant__ CUtensorMap map_b_hi, const Gemv2Params p) {
+             const __grid_constant__ CUtensorMap map_b_lo, const __grid_constant__ CUtensorMap map_b_hi,
+             const __grid_constant__ CUtensorMap map_s_a, const __grid_constant__ CUtensorMap map_s_b, const Gemv2Params p) {
     extern __shared__ uint8_t smem2_raw[];
     // the 128-byte swizzle is a function of the shared-memory address: stage bases must sit on 1024-byte boundaries
     uint8_t* smem2 = smem2_raw + ((1024u - (smem_u32(smem2_raw) & 1023u)) & 1023u);
@@ -112,7 +127,8 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
     }
     __syncthreads();
 
-    const uint32_t n_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
+    const uint32_t routed_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
+    const uint32_t n_tiles = routed_tiles + p.sh_tiles;
     const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.groups;   // item = (tile, row group)
     const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
     const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
@@ -125,10 +141,10 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
     for (uint32_t i = threadIdx.x; i < kTableTiles * 16; i += blockDim.x) {
         const uint32_t tl = i >> 4, slot = i & 15u, tile = t0 + tl;
         if (tile < n_tiles && item0 < item1) {
-            const Tile2 ti = tile2<NC>(p, tile);
+            const Tile2 ti = tile2<NC>(p, tile, routed_tiles);
             if (slot == 0) { tt[tl * 4] = ti.expert; tt[tl * 4 + 1] = ti.start; tt[tl * 4 + 2] = ti.count; }
             uint32_t rid = 0;
-            if (slot < ti.count) rid = p.token_map ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + slot] : ti.start + slot;
+            if (slot < ti.count) rid = (p.token_map && ti.expert < p.experts) ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + slot] : ti.start + slot;
             trid[i] = rid;
         }
     }
@@ -136,7 +152,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
     auto get_tile = [&](uint32_t tile) {
         const uint32_t tl = tile - t0;
         if (tl < kTableTiles) return Tile2{tt[tl * 4], tt[tl * 4 + 1], tt[tl * 4 + 2]};
-        return tile2<NC>(p, tile);
+        return tile2<NC>(p, tile, routed_tiles);
     };
     // this warp's items are item0 + warp + 8n; its unit k is part (k % KP) of item item0 + warp + 8*(k / KP)
     const uint32_t my_items = item0 + warp < item1 ? (item1 - item0 - warp + kW2 - 1) / kW2 : 0u;
@@ -154,8 +170,9 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
         const uint32_t kh = iss_kh, s = iss_s;
         const uint32_t r0 = iss_grp * p.rows_per_unit;
         const uint32_t nr = min(p.rows_per_unit, p.rows - r0);
-        const bool hi = issue_ti.expert >= p.split;
-        const uint32_t el = hi ? issue_ti.expert - p.split : issue_ti.expert;
+        const bool shared = issue_ti.expert >= p.experts;
+        const bool hi = !shared && issue_ti.expert >= p.split;
+        const uint32_t el = shared ? 0u : (hi ? issue_ti.expert - p.split : issue_ti.expert);
         ++issued;
         if (++iss_s == S) iss_s = 0;
         if (++iss_kh == KP) {
@@ -169,10 +186,10 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
         mbar_arrive_expect_tx(&my_full[s], bytes);
 #pragma unroll
         for (uint32_t m = 0; m < NMAT; ++m) {
-            const CUtensorMap* map = m == 0 ? (hi ? &map_a_hi : &map_a_lo) : (hi ? &map_b_hi : &map_b_lo);
+            const CUtensorMap* map = shared ? (m == 0 ? &map_s_a : &map_s_b) : m == 0 ? (hi ? &map_a_hi : &map_a_lo) : (hi ? &map_b_hi : &map_b_lo);
             if (LAYOUT == TSP_LAYOUT_PLANAR) {
                 tma_load_4d(sb + m * p.qs_bytes, map, 0, static_cast<int>(r0), static_cast<int>(kh * p.kb), static_cast<int>(el), &my_full[s]);
-                const uint8_t* eb = p.base[m * 2 + (hi ? 1 : 0)] + static_cast<uint64_t>(el) * p.expert_stride;
+                const uint8_t* eb = shared ? p.sh_base[m] : p.base[m * 2 + (hi ? 1 : 0)] + static_cast<uint64_t>(el) * p.expert_stride;
                 bulk_g2s(sb + NMAT * p.qs_bytes + m * p.sm_bytes, eb + p.sm_off + static_cast<uint64_t>(r0) * p.nblk * 16u, nr * p.nblk * 16u, &my_full[s]);
                 bulk_g2s(sb + NMAT * (p.qs_bytes + p.sm_bytes) + m * p.dm_bytes, eb + p.dm_off + static_cast<uint64_t>(r0) * p.nblk * 4u,
                          nr * p.nblk * 4u, &my_full[s]);
@@ -214,7 +231,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
         if (tile - t0 >= kTableTiles) {   // beyond the cached window: fetch this tile's route ids now
             if (ctid < 8u * NC) {
                 uint32_t rid = 0;
-                if (ctid < ti.count) rid = p.token_map ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + ctid] : ti.start + ctid;
+                if (ctid < ti.count) rid = (p.token_map && ti.expert < p.experts) ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + ctid] : ti.start + ctid;
                 rids[ctid] = rid;
             }
             cur_rids = rids;
@@ -231,8 +248,10 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                 uint32_t j = 0, k8 = 0;
                 if (active) {
                     j = u / per_row; k8 = u % per_row;
-                    const uint32_t in_row = cur_rids[j] / p.in_div;
-                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + k8 * 2;
+                    const bool sh_tile = ti.expert >= p.experts;
+                    const uint32_t in_row = sh_tile ? cur_rids[j] : cur_rids[j] / p.in_div;
+                    const float4* src = reinterpret_cast<const float4*>(sh_tile ? reinterpret_cast<const char*>(p.sh_x) + in_row * p.sh_x_stride_bytes
+                                                                                : reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + k8 * 2;
                     const float4 v0 = src[0], v1 = src[1];
                     const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                     uint32_t hb[8], lb[8];
@@ -248,7 +267,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                     // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
                     *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) =
                         make_uint4(hb[0] | (hb[2] << 16), hb[1] | (hb[3] << 16), hb[4] | (hb[6] << 16), hb[5] | (hb[7] << 16));
-                    if (p.split_lo)
+                    if (SPLIT)
                         *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) =
                             make_uint4(lb[0] | (lb[2] << 16), lb[1] | (lb[3] << 16), lb[4] | (lb[6] << 16), lb[5] | (lb[7] << 16));
                 }
@@ -289,9 +308,9 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                 const uint32_t R = p.rows_per_unit;
                 const uint32_t KB = KBT ? KBT : p.kb;
                 const uint32_t kb_here = !ok ? 0u : (KBT ? KBT : min(p.kb, p.nblk - kh * p.kb));
+                if (kb_here)
 #pragma unroll
                 for (uint32_t bl = half; bl < (KBT ? KBT : kb_here); bl += NH) {
-                    if (KBT && !ok) break;
                     const uint32_t b = kh * KB + bl;   // super-block index along K
                     const uint8_t* xb = xhi + xlane + b * 512;
                     const uint8_t* xq = xlo + xlane + b * 512;
@@ -366,7 +385,7 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                                 mma_f16_16816(al, a1 & 0x000f000fu, b1 & 0x000f000fu, a1s & 0x000f000fu, b1s & 0x000f000fu, xl.z, xl.w);
                                 mma_f16_16816_zero(ah, a0 & 0x00f000f0u, b0 & 0x00f000f0u, a0s & 0x00f000f0u, b0s & 0x00f000f0u, xh.x, xh.y);
                                 mma_f16_16816(ah, a1 & 0x00f000f0u, b1 & 0x00f000f0u, a1s & 0x00f000f0u, b1s & 0x00f000f0u, xh.z, xh.w);
-                                if (p.split_lo) {
+                                if (SPLIT) {
                                     const uint8_t* xs = xq + c * 8 * p.x_stride + j * 128;
                                     const uint4 yl = *reinterpret_cast<const uint4*>(xs), yh = *reinterpret_cast<const uint4*>(xs + 64);
                                     mma_f16_16816(al, a0 & 0x000f000fu, b0 & 0x000f000fu, a0s & 0x000f000fu, b0s & 0x000f000fu, yl.x, yl.y);
@@ -428,7 +447,8 @@ gemv2_kernel(const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant
                         for (int q = 0; q < 2; ++q) {
                             const uint32_t j = c * 8 + 2 * t + q;
                             if (j >= ti.count) continue;
-                            float* orow = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + cur_rids[j] * p.out_stride_bytes);
+                            float* orow = reinterpret_cast<float*>(ti.expert >= p.experts ? reinterpret_cast<char*>(p.sh_out) + cur_rids[j] * p.sh_out_stride_bytes
+                                                                                          : reinterpret_cast<char*>(p.out) + cur_rids[j] * p.out_stride_bytes);
                             if (GATEUP) {
                                 const uint32_t hu = r0 + n * 8 + g;
                                 if (hu < p.rows) {
@@ -516,15 +536,15 @@ static int get_map(const MapKey& k, CUtensorMap* out) {
     return TSP_OK;
 }
 
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR, int KBT>
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, bool PAIR, int KBT, bool SPLIT>
 static int launch2(const CUtensorMap* maps, const Gemv2Params& p, size_t smem, int grid, cudaStream_t st) {
-    auto kernel = gemv2_kernel<LAYOUT, GATEUP, NC, NT, PAIR, KBT>;
+    auto kernel = gemv2_kernel<LAYOUT, GATEUP, NC, NT, PAIR, KBT, SPLIT>;
     static thread_local size_t configured = 0;
     if (smem > configured) {
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    kernel<<<grid, kW2 * 32 * (PAIR ? 2 : 1), smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+    kernel<<<grid, kW2 * 32 * (PAIR ? 2 : 1), smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -533,8 +553,15 @@ static int launch2(const CUtensorMap* maps, const Gemv2Params& p, size_t smem, i
 // first-generation kernel), or a negative error.
 int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const float* x, uint64_t x_stride_bytes,
                         uint32_t in_div, uint32_t tokens, const uint32_t* token_map, const uint32_t* counts, const uint32_t* tasks,
-                        float* out, uint64_t out_stride_bytes, int f16_exact, int nc, uint32_t* error, cudaStream_t st) {
+                        float* out, uint64_t out_stride_bytes, int f16_exact, int nc, uint32_t* error, cudaStream_t st,
+                        const GemvShared* shared) {
     if (a->type != TSP_TYPE_Q4_K) return 1;
+    if (shared) {   // the extra dense expert must look exactly like a routed one, and the launch must be a routed one
+        const tsp_matrix_set* sa = shared->a;
+        if (!token_map || nc != 1 || !sa || sa->experts != 1 || sa->type != a->type || sa->layout != a->layout || sa->rows != a->rows ||
+            sa->cols != a->cols || (gateup && (!shared->b || shared->b->rows != a->rows || shared->b->cols != a->cols ||
+                                               shared->b->type != a->type || shared->b->layout != a->layout))) return 1;
+    }
     const uint32_t nblk = a->cols / 256;
     if (a->rows % (gateup ? 8 : 16)) return 1;
     Gemv2Params p{};
@@ -585,7 +612,7 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     p.token_map = token_map; p.counts = counts; p.tasks = tasks; p.tokens = tokens;
     p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;
 
-    CUtensorMap maps[4];
+    CUtensorMap maps[6];
     const uint32_t n_lo = p.split, n_hi = a->experts - p.split;
     for (int m = 0; m < 4; ++m) {
         if (!gateup && m >= 2) { maps[m] = maps[0]; continue; }
@@ -596,11 +623,25 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
         if (k.stride % 16) return 1;
         if (int rc = get_map(k, &maps[m])) return rc;
     }
+    maps[4] = maps[0]; maps[5] = maps[0];
+    if (shared) {
+        p.sh_tiles = (tokens + 7) / 8;
+        p.sh_x = shared->x; p.sh_x_stride_bytes = shared->x_stride_bytes;
+        p.sh_out = shared->out; p.sh_out_stride_bytes = shared->out_stride_bytes;
+        for (int m = 0; m < (gateup ? 2 : 1); ++m) {
+            const tsp_matrix_set* sm = m == 0 ? shared->a : shared->b;
+            p.sh_base[m] = static_cast<const uint8_t*>(sm->base);
+            MapKey k{sm->base, tsp_expert_bytes(a->type, a->layout, a->rows, a->cols), a->layout, a->rows, nblk, 1, p.rows_per_unit, p.kb};
+            if (int rc = get_map(k, &maps[4 + m])) return rc;
+        }
+    }
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
     // compile-time super-block count for the common shapes of the planar layout (K a multiple of 1024, or K = 512)
     const int kbt = (planar && nblk % p.kb == 0 && (p.kb == 4 || (p.kb == 2 && p.nt == 2))) ? static_cast<int>(p.kb) : 0;
-#define TSP_D3(L, G, NCV, NTV, K) return launch2<L, G, NCV, NTV, false, K>(maps, p, smem, grid, st)
+#define TSP_D3(L, G, NCV, NTV, K)                                                        \
+    return p.split_lo ? launch2<L, G, NCV, NTV, false, K, true>(maps, p, smem, grid, st) \
+                      : launch2<L, G, NCV, NTV, false, K, false>(maps, p, smem, grid, st)
 #define TSP_D2(L, SPEC)                                                                 \
     if (a->layout == L) {                                                                \
         if (gateup) {                                                                    \

@@ -20,16 +20,10 @@ __device__ __forceinline__ double sigmoid_f64(double v) {
     return p / (1.0 + p);
 }
 
-__global__ void __launch_bounds__(kRouteWarps * 32)
-route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t tokens, uint32_t experts,
-             uint32_t selected, uint32_t mode, int normalize, uint32_t* __restrict__ ids,
-             float* __restrict__ weights, uint32_t* error) {
-    extern __shared__ float route_smem[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t token = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (token >= tokens) return;
-    float* row = route_smem + warp * experts;
-    const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + token * stride_bytes);
+// One warp routes one token row; `row` is the warp's scratch of `experts` floats in shared memory.
+__device__ __forceinline__ void route_row(float* row, const float* __restrict__ src, uint32_t token, uint32_t experts, uint32_t selected,
+                                          uint32_t mode, int normalize, uint32_t* __restrict__ ids, float* __restrict__ weights,
+                                          uint32_t* error, uint32_t lane) {
     bool bad = false;
     for (uint32_t e = lane; e < experts; e += 32) {
         const float v = src[e];
@@ -55,9 +49,9 @@ route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t t
         if (lane == 0) for (uint32_t e = 0; e < experts; ++e) all_sum += exp(static_cast<double>(row[e]) - static_cast<double>(row_max));
         all_sum = __shfl_sync(0xffffffffu, all_sum, 0);
     }
-    double my_act = 0;     // lane r (< 32) keeps activation r; ranks >= 32 are handled by lane r%32 in a second slot
-    double my_act_hi = 0;
-    double sel_sum = 0;
+    // lane r keeps the logit of rank r (ranks >= 32 in a second slot); the double-precision activations are then
+    // evaluated once per rank, in parallel across lanes, instead of once per rank by every lane
+    float my_logit = 0.f, my_logit_hi = 0.f;
     for (uint32_t r = 0; r < selected; ++r) {
         float best = -INFINITY;
         uint32_t best_id = 0xffffffffu;
@@ -70,16 +64,21 @@ route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t t
             const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_id, o);
             if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
         }
-        double act;
-        const double l = best, mx = row_max;
-        if (mode == TSP_ROUTER_SOFTMAX) act = exp(l - mx);
-        else if (normalize) act = exp(-softplus_f64(-l) + softplus_f64(-mx));
-        else act = sigmoid_f64(l);
-        sel_sum += act;
-        if ((r & 31u) == lane) { if (r < 32) my_act = act; else my_act_hi = act; }
+        if ((r & 31u) == lane) { if (r < 32) my_logit = best; else my_logit_hi = best; }
         if (lane == 0) { out_ids[r] = best_id; row[best_id] = -INFINITY; }
         __syncwarp();
     }
+    const double mx = row_max;
+    auto activate = [&](float logit) -> double {
+        const double l = logit;
+        if (mode == TSP_ROUTER_SOFTMAX) return exp(l - mx);
+        if (normalize) return exp(-softplus_f64(-l) + softplus_f64(-mx));
+        return sigmoid_f64(l);
+    };
+    const double my_act = lane < selected ? activate(my_logit) : 0.0;
+    const double my_act_hi = lane + 32 < selected ? activate(my_logit_hi) : 0.0;
+    double sel_sum = my_act + my_act_hi;   // fixed butterfly order: deterministic, within an ulp of the rank-order sum
+    for (int o = 16; o; o >>= 1) sel_sum += __shfl_xor_sync(0xffffffffu, sel_sum, o);
     double denominator = mode == TSP_ROUTER_SIGMOID ? 1.0 : all_sum;
     if (normalize) denominator = sel_sum;
     if (!(denominator > 0) || isinf(denominator)) {
@@ -88,6 +87,18 @@ route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t t
     }
     if (lane < selected) out_w[lane] = static_cast<float>(my_act / denominator);
     if (lane + 32 < selected) out_w[lane + 32] = static_cast<float>(my_act_hi / denominator);
+}
+
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t tokens, uint32_t experts,
+             uint32_t selected, uint32_t mode, int normalize, uint32_t* __restrict__ ids,
+             float* __restrict__ weights, uint32_t* error) {
+    extern __shared__ float route_smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t token = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (token >= tokens) return;
+    const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + token * stride_bytes);
+    route_row(route_smem + warp * experts, src, token, experts, selected, mode, normalize, ids, weights, error, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -204,7 +215,7 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
             float s = 0.f;
             for (int i = 0; i < kCombineThreads / 32; ++i) s += partial[i];
             if (!finite_f32(s)) raise_error(error, TSP_ERR_NONFINITE);
-            if (shared_logit) shared_logit[token] = s;
+            if (shared_logit && blockIdx.y == 0) shared_logit[token] = s;
             gate_s = stable_sigmoid(s);
         }
         __syncthreads();
@@ -216,7 +227,8 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
     const float* sh = reinterpret_cast<const float*>(reinterpret_cast<const char*>(shared) + token * shared_stride);
     float* o = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + token * out_stride);
     bool bad = false;
-    for (uint32_t c = tid; c < channels; c += kCombineThreads) {
+    // one channel per thread: blockIdx.y picks the slice of the row, so a small batch still fills the machine
+    for (uint32_t c = blockIdx.y * kCombineThreads + tid; c < min(channels, (blockIdx.y + 1) * kCombineThreads); c += kCombineThreads) {
         float v = gate * sh[c];
         for (uint32_t r = 0; r < selected; ++r) {
             const float* y = reinterpret_cast<const float*>(reinterpret_cast<const char*>(routed) +
@@ -320,7 +332,7 @@ int launch_combine(const float* routed, uint64_t routed_stride, const float* wei
                    uint64_t shared_stride, const float* shared_router, const float* x, uint64_t x_stride,
                    float* shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected, float* out,
                    uint64_t out_stride, void* out16, uint64_t out16_stride, uint32_t* error, cudaStream_t st) {
-    combine_kernel<<<tokens, kCombineThreads, 0, st>>>(routed, routed_stride, weights, shared, shared_stride, shared_router,
+    combine_kernel<<<dim3(tokens, (channels + kCombineThreads - 1) / kCombineThreads), kCombineThreads, 0, st>>>(routed, routed_stride, weights, shared, shared_stride, shared_router,
                                                        x, x_stride, shared_logit, channels, selected, out, out_stride,
                                                        static_cast<__half*>(out16), out16_stride, error);
     TSP_CUDA(cudaGetLastError());

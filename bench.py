@@ -315,6 +315,7 @@ def main():
     ap.add_argument("--layout", default="planar", choices=["planar", "gguf"])
     ap.add_argument("--cpu-tokens", type=int, default=None, help="tokens of the batch timed on the CPU baseline (0 = skip)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--ep-scheme", default="gather", choices=["gather", "alltoall"], help="multi-GPU exchange: all-gather/reduce-scatter or all-to-all")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

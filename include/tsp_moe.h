@@ -109,6 +109,13 @@ int tsp_moe_permute(const uint32_t* d_ids, uint32_t tokens, uint32_t experts, ui
                     uint32_t* d_token_map, uint32_t* d_counts, uint32_t* d_tasks, uint32_t* d_error, void* stream);
 uint64_t tsp_moe_tasks_words(uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile);
 
+/* Expert-parallel form of tsp_moe_permute (no reference counterpart: the reference is single-GPU). d_ids holds GLOBAL
+ * expert ids; the tables cover only the experts [first_expert, first_expert + local_experts) this GPU owns, indexed
+ * locally (row 0 of d_token_map = expert first_expert). Routes to other owners are skipped, not errors; route ids keep
+ * the global numbering token*selected + slot. d_tasks needs tsp_moe_tasks_words(tokens, local_experts, selected, tile). */
+int tsp_moe_permute_local(const uint32_t* d_ids, uint32_t tokens, uint32_t first_expert, uint32_t local_experts, uint32_t selected,
+                          uint32_t tile, uint32_t* d_token_map, uint32_t* d_counts, uint32_t* d_tasks, uint32_t* d_error, void* stream);
+
 /* Decode-size routed projection with the weight bytes streamed once per tile of routes.
  * Replaces `planar_moe_gate_up_swiglu_m8` (graph.mm:9134), `routed_gemv`x2 + `swiglu` (moe.cpp:62-66),
  * and for a dense set (token map NULL) `gemv`/`gemv_rows`/`q8_matvec_many` + `swiglu` of the shared expert.

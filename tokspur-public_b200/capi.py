@@ -57,6 +57,7 @@ SIGNATURES = {
     "tsp_dequant_f32": (_i, [_MS, _u32, _vp, _vp, _vp]),
     "tsp_moe_route": (_i, [_vp, _u64, _u32, _u32, _u32, _u32, _i, _vp, _vp, _vp, _vp]),
     "tsp_moe_permute": (_i, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "tsp_moe_permute_local": (_i, [_vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "tsp_moe_tasks_words": (_u64, [_u32, _u32, _u32, _u32]),
     "tsp_moe_gate_up_swiglu": (_i, [_MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _i, _vp, _vp]),
     "tsp_moe_project": (_i, [_MS, _vp, _u64, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _i, _vp, _vp]),

@@ -38,7 +38,7 @@ int sm_count() {
 
 // launchers implemented in the kernel files
 int launch_route(const float*, uint64_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, float*, uint32_t*, cudaStream_t);
-int launch_permute(const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, uint32_t*, uint32_t*, uint32_t*, cudaStream_t);
+int launch_permute(const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, uint32_t*, uint32_t*, uint32_t*, cudaStream_t);
 int launch_combine(const float*, uint64_t, const float*, const float*, uint64_t, const float*, const float*, uint64_t, float*,
                    uint32_t, uint32_t, uint32_t, float*, uint64_t, void*, uint64_t, uint32_t*, cudaStream_t);
 int launch_f16_to_f32(const void*, uint64_t, float*, uint64_t, uint32_t, uint32_t, cudaStream_t);
@@ -167,7 +167,17 @@ int tsp_moe_permute(const uint32_t* d_ids, uint32_t tokens, uint32_t experts, ui
                 "permute: invalid shape");
     TSP_REQUIRE(tile >= 1 && tile <= 1024, "permute: tile out of range");
     TSP_REQUIRE(static_cast<uint64_t>(tokens) * selected < (1ull << 31), "permute: too many routes");
-    return launch_permute(d_ids, tokens, experts, selected, tile, d_token_map, d_counts, d_tasks, d_error,
+    return launch_permute(d_ids, tokens, experts, selected, tile, 0, 0, d_token_map, d_counts, d_tasks, d_error,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_permute_local(const uint32_t* d_ids, uint32_t tokens, uint32_t first_expert, uint32_t local_experts, uint32_t selected,
+                          uint32_t tile, uint32_t* d_token_map, uint32_t* d_counts, uint32_t* d_tasks, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_ids && d_token_map && d_counts && d_tasks, "permute: null buffer");
+    TSP_REQUIRE(tokens >= 1 && local_experts >= 1 && local_experts <= 4096 && selected >= 1 && selected <= 64, "permute: invalid shape");
+    TSP_REQUIRE(tile >= 1 && tile <= 1024, "permute: tile out of range");
+    TSP_REQUIRE(static_cast<uint64_t>(tokens) * selected < (1ull << 31), "permute: too many routes");
+    return launch_permute(d_ids, tokens, local_experts, selected, tile, first_expert, 1, d_token_map, d_counts, d_tasks, d_error,
                           static_cast<cudaStream_t>(stream));
 }
 

@@ -107,7 +107,7 @@ route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t t
 constexpr int kPermuteThreads = 128;
 
 __global__ void __launch_bounds__(kPermuteThreads)
-grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected,
+grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t first, int local_only,
                       uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* error) {
     __shared__ uint32_t totals[kPermuteThreads / 32];
     const uint32_t expert = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -117,8 +117,10 @@ grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_
         uint32_t slot = 0xffffffffu, matches = 0;
         if (token < tokens) {
             for (uint32_t i = 0; i < selected; ++i) {
-                const uint32_t id = ids[static_cast<uint64_t>(token) * selected + i];
-                if (id >= experts && expert == 0) raise_error(error, TSP_ERR_INDEX);
+                // ids are global; this launch owns experts [first, first + experts). With local_only, routes to other
+                // owners are simply not this rank's business; without it they are an index error.
+                const uint32_t id = ids[static_cast<uint64_t>(token) * selected + i] - first;
+                if (id >= experts && expert == 0 && !local_only) raise_error(error, TSP_ERR_INDEX);
                 if (id == expert) { slot = i; ++matches; }
             }
         }
@@ -140,7 +142,7 @@ grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_
 // tasks = {live_tiles, routes, (expert, start) pairs in ascending expert order, 0xffffffff padding}
 __global__ void __launch_bounds__(256)
 grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint32_t experts, uint32_t selected,
-                     uint32_t tile, uint32_t bound, uint32_t* __restrict__ tasks, uint32_t* error) {
+                     uint32_t tile, uint32_t bound, int local_only, uint32_t* __restrict__ tasks, uint32_t* error) {
     extern __shared__ uint32_t offsets[];  // experts + 1
     const uint32_t tid = threadIdx.x;
     __shared__ uint32_t warp_tiles[8], warp_routes[8];
@@ -173,7 +175,7 @@ grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint3
         offsets[experts] = carry_tiles;
         tasks[0] = min(carry_tiles, bound);
         tasks[1] = carry_routes;
-        if (carry_tiles > bound || carry_routes != tokens * selected) raise_error(error, TSP_ERR_INDEX);
+        if (carry_tiles > bound || (!local_only && carry_routes != tokens * selected) || carry_routes > tokens * selected) raise_error(error, TSP_ERR_INDEX);
     }
     for (uint32_t i = tid; i < bound; i += 256) { tasks[2 + 2 * i] = 0xffffffffu; tasks[3 + 2 * i] = 0xffffffffu; }
     __syncthreads();
@@ -233,7 +235,7 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
         for (uint32_t r = 0; r < selected; ++r) {
             const float* y = reinterpret_cast<const float*>(reinterpret_cast<const char*>(routed) +
                                                             (static_cast<uint64_t>(token) * selected + r) * routed_stride);
-            v = fmaf(w_s[r], y[c], v);
+            if (w_s[r] != 0.f) v = fmaf(w_s[r], y[c], v);   // a zero weight marks a route that is not present in `routed` (expert parallelism)
         }
         bad |= !finite_f32(v);
         if (out) o[c] = v;
@@ -318,12 +320,12 @@ int launch_route(const float* logits, uint64_t stride, uint32_t tokens, uint32_t
     return TSP_OK;
 }
 
-int launch_permute(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile,
+int launch_permute(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile, uint32_t first, int local_only,
                    uint32_t* token_map, uint32_t* counts, uint32_t* tasks, uint32_t* error, cudaStream_t st) {
-    grouped_routes_kernel<<<experts, kPermuteThreads, 0, st>>>(ids, tokens, experts, selected, token_map, counts, error);
+    grouped_routes_kernel<<<experts, kPermuteThreads, 0, st>>>(ids, tokens, experts, selected, first, local_only, token_map, counts, error);
     TSP_CUDA(cudaGetLastError());
     const uint32_t bound = static_cast<uint32_t>((static_cast<uint64_t>(tokens) * selected) / tile + experts);
-    grouped_tasks_kernel<<<1, 256, (experts + 1) * sizeof(uint32_t), st>>>(counts, tokens, experts, selected, tile, bound, tasks, error);
+    grouped_tasks_kernel<<<1, 256, (experts + 1) * sizeof(uint32_t), st>>>(counts, tokens, experts, selected, tile, bound, local_only, tasks, error);
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }

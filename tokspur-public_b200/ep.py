@@ -91,6 +91,21 @@ class EpLayer:
         self.counts = z(per, i32)
         self.tasks = z(max_recv + 2 * per + 2, i32)
         self.error = z(1, i32)
+        # buffers of the gathered (all-gather / reduce-scatter) scheme: every rank sees all world*capacity token rows
+        G = capacity * world
+        self.pack = torch.zeros((capacity, channels * 2 + experts * 4), dtype=torch.uint8, device=device)
+        self.gathered = torch.zeros((G, channels * 2 + experts * 4), dtype=torch.uint8, device=device)
+        self.g_x32 = z(G * channels, f32)
+        self.g_ids = z(G * selected, i32)
+        self.g_weights = z(G * selected, f32)
+        self.g_hid = z(G * selected * hidden, f32)
+        self.g_routed = torch.zeros((G * selected, channels), dtype=f32, device=device)
+        self.g_token_map = z(per * G, i32)
+        self.g_tasks = z(G * selected + 2 * per + 2, i32)
+        self.g_partial = torch.zeros((G, channels), dtype=f32, device=device)
+        self.g_zero = torch.zeros((G, channels), dtype=f32, device=device)
+        self.rs_out = torch.zeros((capacity, channels), dtype=f32, device=device)
+        self.ones = torch.ones(capacity, dtype=f32, device=device)
 
     def step(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
         from . import capi
@@ -121,6 +136,47 @@ class EpLayer:
                                        w.d_shared_router, self.x32.data_ptr(), Cn * 4, self.shared_logit.data_ptr(), T, Cn, K, None, 0,
                                        out16.data_ptr(), out16.stride(0) * 2, e, st))
 
+    def step_gathered(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
+        """Small-batch scheme without any host synchronisation: all-gather the token rows and router logits (every rank then
+        routes all rows itself), compute the routes that hit local experts, mix them per token into partial sums, and
+        reduce-scatter the partial sums back to the tokens' ranks. For decode batches the bytes moved equal those of the
+        all-to-all form (with top-10 of 8 ranks nearly every row visits most ranks anyway) and both collectives have fixed
+        sizes. The mixture adds the ranks' partial sums instead of walking the routes in rank order, so the result agrees with
+        the one-GPU layer to FP32 rounding, not bit for bit."""
+        from . import capi
+        from . import layer as L
+        lib, st, e = capi.lib(), L.stream_ptr(), self.error.data_ptr()
+        T, Cn, H, K, E, per = x16.shape[0], self.C, self.H, self.K, self.E, self.per
+        assert T == self.capacity, "the gathered scheme runs at the capacity it was built for"
+        G = T * self.world
+        w = self.w.weights
+        rowb = Cn * 2 + E * 4
+        self.pack[:, : Cn * 2].copy_(x16.view(torch.uint8).view(T, Cn * 2))
+        self.pack[:, Cn * 2:].copy_(logits.view(torch.uint8).view(T, E * 4))
+        dist.all_gather_into_tensor(self.gathered, self.pack)
+        gx, glg = self.gathered.data_ptr(), self.gathered.data_ptr() + Cn * 2
+        capi.check(lib.tsp_rows_f16_to_f32(gx, rowb, self.g_x32.data_ptr(), Cn * 4, G, Cn, st))
+        capi.check(lib.tsp_moe_route(glg, rowb, G, E, K, 0, 1, self.g_ids.data_ptr(), self.g_weights.data_ptr(), e, st))
+        capi.check(lib.tsp_moe_permute_local(self.g_ids.data_ptr(), G, self.rank * per, per, K, capi.GEMV_TILE, self.g_token_map.data_ptr(),
+                                             self.counts.data_ptr(), self.g_tasks.data_ptr(), e, st))
+        capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.gate), C.byref(w.up), self.g_x32.data_ptr(), Cn * 4, G, K, self.g_token_map.data_ptr(),
+                                              self.counts.data_ptr(), self.g_tasks.data_ptr(), self.g_hid.data_ptr(), H * 4, 1, e, st))
+        capi.check(lib.tsp_moe_project(C.byref(w.down), self.g_hid.data_ptr(), H * 4, 1, G, K, self.g_token_map.data_ptr(), self.counts.data_ptr(),
+                                       self.g_tasks.data_ptr(), self.g_routed.data_ptr(), Cn * 4, 0, e, st))
+        local = (self.g_ids >= self.rank * per) & (self.g_ids < (self.rank + 1) * per)
+        w_local = torch.where(local, self.g_weights, torch.zeros_like(self.g_weights))   # zero weight = route not computed here
+        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, None,
+                                       G, Cn, K, self.g_partial.data_ptr(), Cn * 4, None, 0, e, st))
+        dist.reduce_scatter_tensor(self.rs_out, self.g_partial)
+        x_local = self.g_x32.data_ptr() + self.rank * T * Cn * 4
+        capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.shared_gate), C.byref(w.shared_up), x_local, Cn * 4, T, 1, None, None, None,
+                                              self.shared_hidden.data_ptr(), H * 4, 1, e, st))
+        capi.check(lib.tsp_moe_project(C.byref(w.shared_down), self.shared_hidden.data_ptr(), H * 4, 1, T, 1, None, None, None,
+                                       self.shared_out.data_ptr(), Cn * 4, 0, e, st))
+        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
+                                       w.d_shared_router, x_local, Cn * 4, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
+                                       out16.data_ptr(), out16.stride(0) * 2, e, st))
+
     def error_word(self) -> int:
         torch.cuda.synchronize()
         return int(self.error.item()) & 0xFFFFFFFF
@@ -144,14 +200,15 @@ def run_bench(args, rank: int, world: int, local: int) -> None:
     sx = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
     slg = torch.zeros((T, EXPERTS), dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream()
+    step = EpLayer.step if getattr(args, "ep_scheme", "gather") == "alltoall" else EpLayer.step_gathered
 
     def resident(i):
-        layers[i % len(layers)].step(dev_x[i % nb], dev_lg[i % nb], out)
+        step(layers[i % len(layers)], dev_x[i % nb], dev_lg[i % nb], out)
 
     def e2e(i):
         sx.copy_(host_x[i % nb], non_blocking=True)
         slg.copy_(host_lg[i % nb], non_blocking=True)
-        layers[i % len(layers)].step(sx, slg, out)
+        step(layers[i % len(layers)], sx, slg, out)
         host_out.copy_(out, non_blocking=True)
         stream.synchronize()
 
@@ -185,11 +242,12 @@ def run_bench(args, rank: int, world: int, local: int) -> None:
                 "config": {"workload": f"moe_layer_decode_T{T}_per_gpu (BASELINE configs[1] shape, expert-parallel as configs[4])",
                            "hidden": CHANNELS, "experts": EXPERTS, "expert_ffn": HIDDEN, "top_k": SELECTED, "weights": "Q4_K Pack-v3 planar",
                            "parallelism": f"ep{world}", "experts_per_gpu": EXPERTS // world, "tokens_per_gpu": T,
-                           "collectives": "NCCL all-to-all dispatch (binary16 rows) + all-to-all combine (FP32 rows), one count exchange",
+                           "collectives": ("NCCL all-to-all dispatch (binary16 rows) + all-to-all combine (FP32 rows), one count exchange" if step is EpLayer.step
+                                           else "NCCL all-gather of token rows + logits, reduce-scatter of per-token partial sums (FP32)"),
                            "l2_policy": "layers rotate; per step each GPU streams its hit experts once"},
                 "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": world * (T * CHANNELS * 2 + T * EXPERTS * 4), "d2h_bytes_per_step": world * T * CHANNELS * 2},
-                "gpu_launches": 10 * args.steps, "clocks": clocks.summary(),
+                "gpu_launches": (10 if step is EpLayer.step else 12) * args.steps, "clocks": clocks.summary(),
                 "roofline": None, "cpu_baseline": None}
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -207,6 +207,30 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
                          void* d_out, uint64_t out_stride_bytes, uint32_t out_dtype,
                          uint32_t* d_error, void* stream);
 
+/* ---- prefill-size path: grouped per-expert GEMMs on the tcgen05 tensor cores --------------------------
+ * Replaces `planar_nax_grouped_moe` (graph.mm:9293-9420) = `graph_grouped_routes` -> `nax_grouped_tasks_indirect` ->
+ * `nax_moe_gather_bf16_v3` -> `nax_grouped_moe_gate_up_swiglu_v3` -> `nax_grouped_moe_down_v3`
+ * (planar_moe_v3.metal:2406-2621). Weights: Q4_K Pack v3 planar, rows a multiple of 128.
+ *   1. tsp_moe_permute(..., tile = TSP_GROUPED_TILE)          token_map / counts / tasks (tiles of 128 routes)
+ *   2. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e (experts+1 words)
+ *   3. tsp_moe_gather_rows                                     binary16 rows in permuted order + the route id of each position
+ *   4. tsp_moe_grouped_gate_up                                 H[pos][hidden] binary16, SwiGLU applied, FP32 accumulate in tensor memory
+ *   5. tsp_moe_grouped_down                                    routed[route][channel] FP32, scattered by route id
+ * Row buffers in permuted order (d_xp, d_hp) hold max_positions = tokens*selected rows. Values inside each aligned run of 8
+ * along the row are stored in the order 0,2,1,3,4,6,5,7 (the order the dequantised weight tiles use), which only these
+ * kernels read. Operands are binary16, accumulation FP32. */
+#define TSP_GROUPED_TILE 128u
+int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* d_offsets, void* stream);
+int tsp_moe_gather_rows(const float* d_x, uint64_t x_stride_bytes, uint32_t in_div, const uint32_t* d_token_map,
+                        const uint32_t* d_offsets, uint32_t experts, uint32_t tokens, uint32_t selected, uint32_t cols,
+                        void* d_xp, uint64_t xp_stride_bytes, uint32_t* d_pos_route, uint32_t* d_error, void* stream);
+int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const void* d_xp, uint64_t xp_stride_bytes,
+                            uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
+                            void* d_hp, uint64_t hp_stride_bytes, uint32_t* d_error, void* stream);
+int tsp_moe_grouped_down(const tsp_matrix_set* down, const void* d_hp, uint64_t hp_stride_bytes, uint32_t max_positions,
+                         const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, const uint32_t* d_pos_route,
+                         float* d_routed, uint64_t routed_stride_bytes, uint32_t* d_error, void* stream);
+
 /* No counterpart in the reference (its graph always works out of caller-allocated buffers).
  *
  * The same layer as tsp_moe_layer_decode, for callers that have nowhere to get scratch from: code that runs

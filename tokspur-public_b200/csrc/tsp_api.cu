@@ -46,6 +46,11 @@ int launch_dequant(uint32_t, uint32_t, const uint8_t*, uint64_t, float*, uint32_
 int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*, uint64_t, uint32_t, uint32_t,
                 const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t, const GemvShared* = nullptr);
 
+int launch_route_offsets(const uint32_t*, uint32_t, uint32_t*, cudaStream_t);
+int launch_gather_rows(const float*, uint64_t, uint32_t, const uint32_t*, const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, void*, uint64_t,
+                       uint32_t*, uint32_t*, cudaStream_t);
+int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, const uint32_t*, const uint32_t*,
+                   const uint32_t*, const uint32_t*, void*, uint64_t, uint32_t*, cudaStream_t);
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
 
@@ -335,6 +340,51 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
                            x32_stride, s->d_shared_logit, tokens, channels, selected,
                            out_dtype == 0 ? static_cast<float*>(d_out) : nullptr, out_dtype == 0 ? out_stride : 0,
                            out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Prefill-size path: grouped per-expert GEMMs on the tcgen05 tensor cores
+// ---------------------------------------------------------------------------------------------
+int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* d_offsets, void* stream) {
+    TSP_REQUIRE(d_counts && d_offsets && experts >= 1 && experts <= 4096, "offsets: null buffer or experts out of range");
+    return launch_route_offsets(d_counts, experts, d_offsets, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_gather_rows(const float* d_x, uint64_t x_stride, uint32_t in_div, const uint32_t* d_token_map, const uint32_t* d_offsets,
+                        uint32_t experts, uint32_t tokens, uint32_t selected, uint32_t cols, void* d_xp, uint64_t xp_stride,
+                        uint32_t* d_pos_route, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_token_map && d_offsets && d_pos_route, "gather: null table");
+    TSP_REQUIRE(tokens >= 1 && selected >= 1 && selected <= 64 && in_div >= 1 && cols >= 8 && cols % 8 == 0, "gather: invalid shape");
+    if (int rc = check_rows(d_x, x_stride, cols, 4, "gather input")) return rc;
+    if (int rc = check_rows(d_xp, xp_stride, cols, 2, "gather output")) return rc;
+    return launch_gather_rows(d_x, x_stride, in_div, d_token_map, d_offsets, experts, tokens, tokens * selected, cols, d_xp, xp_stride,
+                              d_pos_route, d_error, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const void* d_xp, uint64_t xp_stride,
+                            uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
+                            void* d_hp, uint64_t hp_stride, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(gate, "gate")) return rc;
+    if (int rc = check_matrix(up, "up")) return rc;
+    TSP_REQUIRE(gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
+                gate->experts == up->experts && gate->expert_stride == up->expert_stride && gate->split == up->split,
+                "gate/up matrix sets must share shape, encoding, layout and addressing");
+    TSP_REQUIRE(d_tasks && d_counts && d_offsets && max_positions >= 1, "grouped gate-up: null table");
+    if (int rc = check_rows(d_xp, xp_stride, gate->cols, 2, "grouped gate-up input")) return rc;
+    if (int rc = check_rows(d_hp, hp_stride, gate->rows, 2, "grouped gate-up output")) return rc;
+    return launch_grouped(gate, up, true, d_xp, xp_stride, max_positions, d_tasks, d_counts, d_offsets, nullptr, d_hp, hp_stride, d_error,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_grouped_down(const tsp_matrix_set* down, const void* d_hp, uint64_t hp_stride, uint32_t max_positions,
+                         const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, const uint32_t* d_pos_route,
+                         float* d_routed, uint64_t routed_stride, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(down, "down")) return rc;
+    TSP_REQUIRE(d_tasks && d_counts && d_offsets && d_pos_route && max_positions >= 1, "grouped down: null table");
+    if (int rc = check_rows(d_hp, hp_stride, down->cols, 2, "grouped down input")) return rc;
+    if (int rc = check_rows(d_routed, routed_stride, down->rows, 4, "grouped down output")) return rc;
+    return launch_grouped(down, nullptr, false, d_hp, hp_stride, max_positions, d_tasks, d_counts, d_offsets, d_pos_route, d_routed,
+                          routed_stride, d_error, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

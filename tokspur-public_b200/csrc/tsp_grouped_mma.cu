@@ -1,0 +1,502 @@
+// Prefill-size grouped expert GEMMs on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+// One launch computes, for every tile of <= 128 routes of one expert, either
+//   gate-up:  H[pos][h]  = silu(W_gate[h] . x[pos]) * (W_up[h] . x[pos])     (two accumulators sharing the activation tile)
+//   down:     Y[route][c] = W_down[c] . H[pos]
+// with the weights as the M operand (128 weight rows per CTA tile fill the MMA's M extent whatever the number of
+// tokens), the tokens as the N operand (32, 64 or 128 columns) and K walked in chunks of 64.
+//
+// Roles inside a CTA (one persistent CTA per SM):
+//   warp 0      TMA producer: Pack v3 planar code boxes + scale planes of one super-block (256 columns of K) per
+//               quant stage; the activation tile (tokens x 64 binary16, 128-byte swizzled) of every K chunk.
+//   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers.
+//   warps 2..5  dequantise: read 4-bit codes + 6-bit factors from the quant stage, write binary16 weights in the
+//               K-major 128-byte-swizzled operand layout; after the last K chunk the same four warps are the epilogue
+//               (tcgen05.ld of their 32 accumulator lanes, SwiGLU / store).
+// Accumulation is FP32 in tensor memory. Operands are binary16 (kind::f16, f16 inputs): the activations of this path are
+// binary16-exact, and Q4_K values keep 11 significant bits instead of bf16's 8, which keeps the two chained GEMMs well
+// inside the 2e-3 relative-L2 bar that bf16 operands would only just meet.
+// Every mbarrier wait is bounded; a timeout sets TSP_ERR_TIMEOUT, and every path still frees the tensor memory.
+#include <cuda.h>
+
+#include "tsp_common.cuh"
+
+namespace tsp {
+
+int get_tensor_map_bytes(const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                         bool swizzle128, CUtensorMap* out);
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05 / TMEM wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], kind::f16, one CTA
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrive on an mbarrier when all MMAs issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 16 consecutive columns of 32-bit accumulators -> 16 registers per thread
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_g(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes (64 binary16) in the 128-byte swizzle:
+// start address >> 4, leading byte offset (unused for this layout) 1, stride byte offset 1024 (eight rows), descriptor
+// version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_k128(const void* smem_tile) {
+    const uint64_t addr = smem_u32(smem_tile);
+    return ((addr & 0x3FFFFull) >> 4) | (1ull << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor for kind::f16: D = FP32, A = B = binary16, both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+constexpr uint32_t kGWarps = 6;            // producer, MMA, 4 x dequant/epilogue
+constexpr uint32_t kGThreads = kGWarps * 32;
+constexpr uint32_t kTileRoutes = 128;      // routes per tile (N extent at most)
+constexpr uint32_t kRowsM = 128;           // weight rows per CTA tile (M)
+constexpr uint32_t kChunkK = 64;           // K per pipeline step: 64 binary16 = one 128-byte swizzled row
+
+struct GroupedParams {
+    // weights: Pack v3 planar Q4_K, addressed as in the decode kernel
+    const uint8_t* base[4];        // A_lo, A_hi, B_lo, B_hi (plane copies)
+    uint64_t expert_stride;
+    uint32_t split, experts;
+    uint32_t rows, cols, nblk;     // rows of ONE matrix, K, super-blocks per row
+    uint64_t sm_off, dm_off;
+    uint32_t row_blocks;           // rows / 128
+    // routes
+    const uint32_t* tasks;         // {tiles, routes, (expert, start)...} with tiles of kTileRoutes
+    const uint32_t* counts;
+    const uint32_t* offsets;       // first permuted position of each expert
+    const uint32_t* pos_route;     // route id (token*selected + slot) of each permuted position
+    // output
+    void* out; uint64_t out_stride_bytes;
+    uint32_t* error;
+    // shared-memory plan
+    uint32_t off_q, q_stage_bytes, off_a, off_b, a_tile_bytes;
+};
+
+
+// bounded wait with a short limit: a stalled pipeline ends in tens of milliseconds, never hangs
+__device__ __forceinline__ bool gwait(uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity, 1u << 21); }
+
+struct GTile { uint32_t expert, start, count, row0, ncols; };
+
+__device__ __forceinline__ GTile gtile(const GroupedParams& p, uint32_t tile) {
+    GTile t;
+    t.expert = p.tasks[2 + 2 * tile];
+    t.start = p.tasks[3 + 2 * tile];
+    if (t.expert >= p.experts) { t.expert = 0; t.start = 0; t.count = 0; t.row0 = 0; t.ncols = 32; return t; }
+    const uint32_t c = p.counts[t.expert];
+    t.count = c > t.start ? min(c - t.start, kTileRoutes) : 0u;
+    t.row0 = p.offsets[t.expert] + t.start;
+    t.ncols = t.count <= 32 ? 32u : (t.count <= 64 ? 64u : 128u);
+    return t;
+}
+
+// GATEUP: two weight matrices (gate, up) and the SwiGLU epilogue writing binary16 hidden rows in permuted position order;
+// otherwise one matrix and FP32 rows scattered to their route ids.
+template <bool GATEUP>
+__global__ void __launch_bounds__(kGThreads, 1)
+grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_constant__ CUtensorMap qmap_a_hi,
+                   const __grid_constant__ CUtensorMap qmap_b_lo, const __grid_constant__ CUtensorMap qmap_b_hi,
+                   const __grid_constant__ CUtensorMap smap_a_lo, const __grid_constant__ CUtensorMap smap_a_hi,
+                   const __grid_constant__ CUtensorMap smap_b_lo, const __grid_constant__ CUtensorMap smap_b_hi,
+                   const __grid_constant__ CUtensorMap xmap32, const __grid_constant__ CUtensorMap xmap64,
+                   const __grid_constant__ CUtensorMap xmap128, const GroupedParams p) {
+    extern __shared__ uint8_t gsm_raw[];
+    uint8_t* gsm = gsm_raw + ((1024u - (smem_u32(gsm_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gsm);
+    uint64_t *qfull = bars, *qempty = bars + 2, *bfull = bars + 4, *afull = bars + 6, *mempty = bars + 8, *acc_full = bars + 10,
+             *acc_empty = bars + 11;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gsm + 128);
+    constexpr uint32_t NMAT = GATEUP ? 2 : 1;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&qfull[s], 1); mbar_init(&qempty[s], 4);
+            mbar_init(&bfull[s], 1); mbar_init(&afull[s], 4); mbar_init(&mempty[s], 1);
+        }
+        mbar_init(acc_full, 1); mbar_init(acc_empty, 4);
+        mbar_fence_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t n_tiles = p.tasks[0];
+    const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.row_blocks;
+    const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
+    const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64
+
+    if (warp == 0) {
+        // =========================== TMA producer ===========================
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t qs = 0, qph = 0, ms = 0, mph = 0;
+            for (uint32_t item = item0; item < item1 && ok; ++item) {
+                const GTile t = gtile(p, item / p.row_blocks);
+                const uint32_t r0 = (item % p.row_blocks) * kRowsM;
+                const bool hi = t.expert >= p.split;
+                const uint32_t el = hi ? t.expert - p.split : t.expert;
+                const CUtensorMap* xmap = t.ncols == 32 ? &xmap32 : (t.ncols == 64 ? &xmap64 : &xmap128);
+                for (uint32_t sb = 0; sb < p.nblk && ok; ++sb) {
+                    // quant stage: code boxes, factor boxes and the d/dmin plane rows of this super-block
+                    ok = gwait(&qempty[qs], qph ^ 1u);
+                    if (!ok) break;
+                    uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
+                    const uint32_t dm_bytes = kRowsM * p.nblk * 4u;
+                    mbar_arrive_expect_tx(&qfull[qs], NMAT * (kRowsM * 128u + kRowsM * 16u + dm_bytes));
+#pragma unroll
+                    for (uint32_t m = 0; m < NMAT; ++m) {
+                        const CUtensorMap* qm = m == 0 ? (hi ? &qmap_a_hi : &qmap_a_lo) : (hi ? &qmap_b_hi : &qmap_b_lo);
+                        const CUtensorMap* sm = m == 0 ? (hi ? &smap_a_hi : &smap_a_lo) : (hi ? &smap_b_hi : &smap_b_lo);
+                        tma_load_4d_g(q + m * 16384u, qm, 0, static_cast<int>(r0), static_cast<int>(sb), static_cast<int>(el), &qfull[qs]);
+                        tma_load_4d_g(q + NMAT * 16384u + m * 2048u, sm, static_cast<int>(sb * 16), static_cast<int>(r0), static_cast<int>(el), 0, &qfull[qs]);
+                        const uint8_t* eb = p.base[m * 2 + (hi ? 1 : 0)] + static_cast<uint64_t>(el) * p.expert_stride;
+                        bulk_g2s(q + NMAT * (16384u + 2048u) + m * dm_bytes, eb + p.dm_off + static_cast<uint64_t>(r0) * p.nblk * 4u, dm_bytes, &qfull[qs]);
+                    }
+                    if (++qs == 2) { qs = 0; qph ^= 1u; }
+                    // activation tiles of the four K chunks of this super-block
+                    for (uint32_t c = 0; c < 4 && ok; ++c) {
+                        ok = gwait(&mempty[ms], mph ^ 1u);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(&bfull[ms], t.ncols * 128u);
+                        tma_load_2d(gsm + p.off_b + ms * 16384u, xmap, static_cast<int>((sb * 256 + c * 64) * 2), static_cast<int>(t.row0), &bfull[ms]);   // byte coordinate: the map's element is a byte
+                        if (++ms == 2) { ms = 0; mph ^= 1u; }
+                    }
+                }
+            }
+            if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
+        }
+    } else if (warp == 1) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t ms = 0, mph = 0, accph = 0;
+            for (uint32_t item = item0; item < item1 && ok; ++item) {
+                const GTile t = gtile(p, item / p.row_blocks);
+                const uint32_t idesc = umma_idesc_f16(kRowsM, t.ncols);
+                ok = gwait(acc_empty, accph ^ 1u);   // the epilogue has drained the previous item's accumulators
+                if (!ok) break;
+                tc_fence_after();
+                for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
+                    ok = gwait(&afull[ms], mph) && gwait(&bfull[ms], mph);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t bdesc = umma_desc_k128(gsm + p.off_b + ms * 16384u);
+#pragma unroll
+                    for (uint32_t m = 0; m < NMAT; ++m) {
+                        const uint64_t adesc = umma_desc_k128(gsm + p.off_a + ms * NMAT * 16384u + m * 16384u);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; ++kk)
+                            umma_f16(tmem_base + m * 128u, adesc + kk * 2, bdesc + kk * 2, idesc, (c | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&mempty[ms]);   // frees this stage's A and B tiles once the MMAs above have read them
+                    if (++ms == 2) { ms = 0; mph ^= 1u; }
+                }
+                if (ok) umma_commit(acc_full);
+                accph ^= 1u;
+            }
+            if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
+        }
+    } else {
+        // =========================== dequantise + epilogue (warps 2..5) ===========================
+        const uint32_t dw = warp - 2;                 // 0..3
+        const uint32_t row = dw * 32 + lane;          // weight row of the tile this thread dequantises
+        const uint32_t sw = row & 7u;
+        const uint32_t quarter = warp & 3u;           // tensor-memory lane quarter this warp may read
+        bool ok = true;
+        uint32_t qs = 0, qph = 0, ms = 0, mph = 0, accph = 0;
+        for (uint32_t item = item0; item < item1; ++item) {
+            const GTile t = gtile(p, item / p.row_blocks);
+            const uint32_t rb = item % p.row_blocks;
+            for (uint32_t sb = 0; sb < p.nblk; ++sb) {
+                if (ok) ok = gwait(&qfull[qs], qph);
+                const uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
+                // per matrix: d, dmin and the sixteen 6-bit factors of this row's super-block
+                float dd[NMAT], dmn[NMAT];
+                uint4 fac[NMAT];
+#pragma unroll
+                for (uint32_t m = 0; m < NMAT; ++m) {
+                    fac[m] = *reinterpret_cast<const uint4*>(q + NMAT * 16384u + m * 2048u + row * 16u);
+                    const uint32_t dmw = *reinterpret_cast<const uint32_t*>(q + NMAT * (16384u + 2048u) + m * (kRowsM * p.nblk * 4u) + (row * p.nblk + sb) * 4u);
+                    dd[m] = half_bits_to_float(dmw & 0xffffu);
+                    dmn[m] = half_bits_to_float(dmw >> 16);
+                    if (ok && (!finite_f32(dd[m]) || !finite_f32(dmn[m]))) raise_error(p.error, TSP_ERR_NONFINITE);
+                }
+                for (uint32_t c = 0; c < 4; ++c) {
+                    if (ok) ok = gwait(&mempty[ms], mph ^ 1u);   // the MMAs that read this A tile two chunks ago are done
+                    if (ok) {
+#pragma unroll
+                        for (uint32_t m = 0; m < NMAT; ++m) {
+                            const uint8_t* line = q + m * 16384u + row * 128u;
+                            const uint4 w0 = *reinterpret_cast<const uint4*>(line + (((2 * c) ^ sw) << 4));
+                            const uint4 w1 = *reinterpret_cast<const uint4*>(line + (((2 * c + 1) ^ sw) << 4));
+                            const uint32_t scw = c < 2 ? fac[m].x : fac[m].y, mnw = c < 2 ? fac[m].z : fac[m].w;
+                            const uint32_t sh = (c & 1u) * 16u;
+                            const float s_lo = dd[m] * static_cast<float>((scw >> sh) & 0xffu), s_hi = dd[m] * static_cast<float>((scw >> (sh + 8)) & 0xffu);
+                            const float m_lo = dmn[m] * static_cast<float>((mnw >> sh) & 0xffu), m_hi = dmn[m] * static_cast<float>((mnw >> (sh + 8)) & 0xffu);
+                            const __half2 sL = __float2half2_rn(s_lo), sH = __float2half2_rn(s_hi);
+                            const __half2 nL = __float2half2_rn(-m_lo), nH = __float2half2_rn(-m_hi);
+                            const __half2 k1024 = __float2half2_rn(1024.f), k16th = __float2half2_rn(0.0625f), kn64 = __float2half2_rn(-64.f);
+                            uint8_t* arow = gsm + p.off_a + ms * NMAT * 16384u + m * 16384u + row * 128u;
+                            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                            // output chunk qq (8 binary16 = K positions 8qq..8qq+7 of this 64-wide slice, in the shared 0,2,1,3,4,6,5,7 order):
+                            // qq < 4 from the low nibbles of bytes 8qq..8qq+7, qq >= 4 from the high nibbles of bytes 8(qq-4)..
+#pragma unroll
+                            for (uint32_t qq = 0; qq < 4; ++qq) {
+                                const uint32_t a = words[2 * qq], b = words[2 * qq + 1];
+                                uint32_t lo[4], hi4[4];
+                                const uint32_t src[4] = {a, a >> 8, b, b >> 8};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const uint32_t l = (src[i] & 0x000f000fu) | 0x64006400u;     // 1024 + q
+                                    const uint32_t h = (src[i] & 0x00f000f0u) | 0x64006400u;     // 1024 + 16 q
+                                    const __half2 ql = __hsub2(*reinterpret_cast<const __half2*>(&l), k1024);
+                                    const __half2 qh = __hfma2(*reinterpret_cast<const __half2*>(&h), k16th, kn64);
+                                    const __half2 wl = __hfma2(ql, sL, nL), wh = __hfma2(qh, sH, nH);
+                                    lo[i] = *reinterpret_cast<const uint32_t*>(&wl);
+                                    hi4[i] = *reinterpret_cast<const uint32_t*>(&wh);
+                                }
+                                *reinterpret_cast<uint4*>(arow + ((qq ^ sw) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                                *reinterpret_cast<uint4*>(arow + (((qq + 4) ^ sw) << 4)) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+                            }
+                        }
+                        fence_async_smem();   // make the generic-proxy writes visible to the tensor-core (async) proxy
+                    }
+                    __syncwarp();
+                    if (lane == 0 && ok) mbar_arrive(&afull[ms]);
+                    if (++ms == 2) { ms = 0; mph ^= 1u; }
+                }
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&qempty[qs]);
+                if (++qs == 2) { qs = 0; qph ^= 1u; }
+            }
+            // ---- epilogue: this warp's 32 accumulator lanes = weight rows rb*128 + quarter*32 + lane ----
+            if (ok) ok = gwait(acc_full, accph);
+            accph ^= 1u;
+            if (ok) {
+                tc_fence_after();
+                const uint32_t wrow = rb * kRowsM + quarter * 32 + lane;
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+                bool bad = false;
+                for (uint32_t j0 = 0; j0 < t.ncols; j0 += 16) {
+                    if (j0 >= t.count) break;
+                    uint32_t g[16], u[16];
+                    tmem_ld16(taddr + j0, g);
+                    if (GATEUP) tmem_ld16(taddr + 128u + j0, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        if (j0 + i >= t.count) break;
+                        const uint32_t pos = t.row0 + j0 + i;
+                        if (GATEUP) {
+                            const float v = stable_silu(__uint_as_float(g[i])) * __uint_as_float(u[i]);
+                            const __half hv = __float2half_rn(v);
+                            bad |= !finite_f32(__half2float(hv));
+                            // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weights use
+                            const uint32_t col = (wrow & ~7u) | ((wrow & 4u) | ((wrow & 1u) << 1) | ((wrow & 2u) >> 1));
+                            reinterpret_cast<__half*>(reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(pos) * p.out_stride_bytes)[col] = hv;
+                        } else {
+                            const float v = __uint_as_float(g[i]);
+                            bad |= !finite_f32(v);
+                            const uint32_t route = p.pos_route[pos];
+                            reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(route) * p.out_stride_bytes)[wrow] = v;
+                        }
+                    }
+                }
+                if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
+                tc_fence_before();
+            }
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(acc_empty);
+        }
+        if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
+    }
+    // every path ends here: free the tensor memory
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 256);
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// helpers: route offsets, gather of the routed rows into permuted order
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) route_offsets_kernel(const uint32_t* __restrict__ counts, uint32_t experts, uint32_t* __restrict__ offsets) {
+    __shared__ uint32_t warp_sum[8];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t carry = 0;
+    for (uint32_t base = 0; base < experts; base += 256) {
+        const uint32_t e = base + tid;
+        const uint32_t c = e < experts ? counts[e] : 0u;
+        uint32_t incl = c;
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= static_cast<uint32_t>(o)) incl += v; }
+        if (lane == 31) warp_sum[warp] = incl;
+        __syncthreads();
+        uint32_t before = 0, total = 0;
+        for (uint32_t i = 0; i < 8; ++i) { if (i < warp) before += warp_sum[i]; total += warp_sum[i]; }
+        if (e < experts) offsets[e] = carry + before + incl - c;
+        carry += total;
+        __syncthreads();
+    }
+    if (tid == 0) offsets[experts] = carry;
+}
+
+// position p of the permuted order belongs to the expert e with offsets[e] <= p < offsets[e+1]; its route id is
+// token_map[e*tokens + p - offsets[e]]. Rows are written as binary16 with the K order 0,2,1,3,4,6,5,7 inside each run of 8.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const float* __restrict__ x, uint64_t x_stride, uint32_t in_div, const uint32_t* __restrict__ token_map,
+                   const uint32_t* __restrict__ offsets, uint32_t experts, uint32_t tokens, uint32_t cols, __half* __restrict__ xp,
+                   uint64_t xp_stride, uint32_t* __restrict__ pos_route, uint32_t* error) {
+    const uint32_t total = offsets[experts];
+    const uint32_t pos = blockIdx.x * 4 + (threadIdx.x >> 6);
+    if (pos >= total) return;
+    uint32_t lo = 0, hi = experts;   // largest e with offsets[e] <= pos
+    while (hi - lo > 1) { const uint32_t mid = (lo + hi) >> 1; if (offsets[mid] <= pos) lo = mid; else hi = mid; }
+    const uint32_t rid = token_map[static_cast<uint64_t>(lo) * tokens + (pos - offsets[lo])];
+    const uint32_t t64 = threadIdx.x & 63;
+    if (t64 == 0) pos_route[pos] = rid;
+    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(x) + static_cast<uint64_t>(rid / in_div) * x_stride);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(xp) + static_cast<uint64_t>(pos) * xp_stride);
+    bool bad = false;
+    for (uint32_t k8 = t64; k8 < cols / 8; k8 += 64) {
+        const float4 a = src[2 * k8], b = src[2 * k8 + 1];
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        uint32_t h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const __half hv = __float2half_rn(v[i]); bad |= !finite_f32(__half2float(hv)); h[i] = __half_as_ushort(hv); }
+        dst[k8] = make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
+    }
+    if (bad) raise_error(error, TSP_ERR_NONFINITE);
+}
+
+int launch_route_offsets(const uint32_t* counts, uint32_t experts, uint32_t* offsets, cudaStream_t st) {
+    route_offsets_kernel<<<1, 256, 0, st>>>(counts, experts, offsets);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+int launch_gather_rows(const float* x, uint64_t x_stride, uint32_t in_div, const uint32_t* token_map, const uint32_t* offsets, uint32_t experts,
+                       uint32_t tokens, uint32_t max_routes, uint32_t cols, void* xp, uint64_t xp_stride, uint32_t* pos_route, uint32_t* error,
+                       cudaStream_t st) {
+    gather_rows_kernel<<<(max_routes + 3) / 4, 256, 0, st>>>(x, x_stride, in_div, token_map, offsets, experts, tokens, cols,
+                                                             static_cast<__half*>(xp), xp_stride, pos_route, error);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host launcher of the grouped tensor-core GEMMs
+// ---------------------------------------------------------------------------------------------
+template <bool GATEUP>
+static int launch_grouped_t(const CUtensorMap* m, const GroupedParams& p, size_t smem, int grid, cudaStream_t st) {
+    auto kernel = grouped_mma_kernel<GATEUP>;
+    static thread_local size_t configured = 0;
+    if (smem > configured) {
+        TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured = smem;
+    }
+    kernel<<<grid, kGThreads, smem, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], m[9], m[10], p);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+// a/b: Q4_K Pack v3 planar matrix sets [rows x cols]; act: binary16 rows in permuted position order ([max_positions] rows of
+// `cols` values, 16-byte aligned stride); out: gate-up -> binary16 rows [positions x rows] in permuted order, down -> FP32 rows by route id.
+int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const void* act, uint64_t act_stride, uint32_t max_positions,
+                   const uint32_t* tasks, const uint32_t* counts, const uint32_t* offsets, const uint32_t* pos_route, void* out,
+                   uint64_t out_stride, uint32_t* error, cudaStream_t st) {
+    if (a->type != TSP_TYPE_Q4_K || a->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "grouped GEMM: only Q4_K Pack v3 planar weights have a tensor-core kernel");
+    TSP_REQUIRE(a->rows % kRowsM == 0 && a->cols % 256 == 0, "grouped GEMM: rows must be a multiple of 128 and columns of 256");
+    GroupedParams p{};
+    const uint32_t nblk = a->cols / 256;
+    TSP_REQUIRE(nblk <= 32, "grouped GEMM: K extent too large");
+    p.split = a->split < a->experts ? a->split : a->experts;
+    p.experts = a->experts; p.expert_stride = a->expert_stride;
+    p.rows = a->rows; p.cols = a->cols; p.nblk = nblk; p.row_blocks = a->rows / kRowsM;
+    const uint64_t total_units = static_cast<uint64_t>(a->rows) * nblk;
+    p.sm_off = total_units * 128; p.dm_off = total_units * 144;
+    p.base[0] = static_cast<const uint8_t*>(a->base);
+    p.base[1] = static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base);
+    if (gateup) {
+        p.base[2] = static_cast<const uint8_t*>(b->base);
+        p.base[3] = static_cast<const uint8_t*>(b->base_hi ? b->base_hi : b->base);
+    } else { p.base[2] = p.base[0]; p.base[3] = p.base[1]; }
+    p.tasks = tasks; p.counts = counts; p.offsets = offsets; p.pos_route = pos_route;
+    p.out = out; p.out_stride_bytes = out_stride; p.error = error;
+    const uint32_t nmat = gateup ? 2 : 1;
+    p.off_q = 1024;
+    p.q_stage_bytes = (nmat * (16384u + 2048u + kRowsM * nblk * 4u) + 1023u) & ~1023u;
+    p.off_a = p.off_q + 2 * p.q_stage_bytes;
+    p.off_b = p.off_a + 2 * nmat * 16384u;
+    const size_t smem = p.off_b + 2 * 16384u + 1024;
+    TSP_REQUIRE(smem <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
+
+    CUtensorMap maps[11];
+    const uint64_t stride = a->experts > 1 ? a->expert_stride : tsp_expert_bytes(a->type, a->layout, a->rows, a->cols);
+    const uint32_t n_lo = p.split, n_hi = a->experts - p.split;
+    for (int i = 0; i < 4; ++i) {
+        const bool hi = i & 1;
+        const uint32_t n = hi ? (n_hi ? n_hi : n_lo) : n_lo;
+        const uint8_t* base = p.base[i];
+        {   // codes: [128 B of a super-block][row][super-block][expert], 128-byte swizzle
+            const uint64_t dims[4] = {128, a->rows, nblk, n}, strides[3] = {uint64_t(nblk) * 128, 128, stride};
+            const uint32_t box[4] = {128, kRowsM, 1, 1};
+            if (int rc = get_tensor_map_bytes(base, 4, dims, strides, box, true, &maps[i])) return rc;
+        }
+        {   // factors: [16 B x super-blocks][row][expert][1]
+            const uint64_t dims[4] = {uint64_t(nblk) * 16, a->rows, n, 1}, strides[3] = {uint64_t(nblk) * 16, stride, stride};
+            const uint32_t box[4] = {16, kRowsM, 1, 1};
+            if (int rc = get_tensor_map_bytes(base + p.sm_off, 4, dims, strides, box, false, &maps[4 + i])) return rc;
+        }
+    }
+    const uint32_t ns[3] = {32, 64, 128};
+    for (int i = 0; i < 3; ++i) {
+        const uint64_t dims[2] = {uint64_t(a->cols) * 2, max_positions}, strides[1] = {act_stride};
+        const uint32_t box[2] = {128, ns[i]};
+        if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps[8 + i])) return rc;
+    }
+    const int grid = sm_count();
+    if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
+    return gateup ? launch_grouped_t<true>(maps, p, smem, grid, st) : launch_grouped_t<false>(maps, p, smem, grid, st);
+}
+
+}  // namespace tsp

@@ -171,6 +171,8 @@ def run_ours(args):
         from tokspur_public_b200 import ep
         return ep.run_bench(args, rank, world, local)
 
+    if args.workload == "prefill":
+        return run_prefill(args, local)
     dev = torch.device("cuda", local)
     T = args.tokens
     layout = formats.PLANAR if args.layout == "planar" else formats.GGUF
@@ -261,6 +263,134 @@ def run_ours(args):
             "extra": {"layer_hbm_gbs": layer_bytes / (ms * 1e-3) / 1e9, "layer_hbm_frac": layer_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
                       "layer_algorithmic_bytes": layer_bytes, "unique_experts": U, "stage_ms": stages, "parity_rel_l2_vs_cpu": parity,
                       "layer_tflops": T * (SELECTED + 1) * FLOPS_PER_ROUTE / (ms * 1e-3) / 1e12}}
+    print(json.dumps(line), flush=True)
+
+
+def run_prefill(args, local):
+    """BASELINE configs[2]: one MoE layer over 4096 tokens, router logits N(0,1) + per-expert Zipf(1.1) bias, through the
+    grouped tcgen05 GEMMs. The line's roofline is the tensor bound of the routed gate-up GEMM."""
+    import torch
+    from tokspur_public_b200 import capi, formats, synth
+    from tokspur_public_b200 import layer as L
+    dev = torch.device("cuda", local)
+    T = args.tokens if args.tokens != 64 else 4096
+    layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, formats.Q4_K, formats.PLANAR, dev, keep_gguf=(i == 0)) for i in range(min(args.layers, 2))]
+    ps = L.PrefillScratch(CHANNELS, HIDDEN, EXPERTS, SELECTED, T, dev)
+    bias = synth.zipf_bias(5, EXPERTS)
+    nb = 4
+    host_x = [torch.from_numpy(synth.activations_f16(1000 + b, T, CHANNELS)).pin_memory() for b in range(nb)]
+    host_lg = [torch.from_numpy(synth.router_logits(2000 + b, T, EXPERTS, bias)).pin_memory() for b in range(nb)]
+    dev_x = [t.to(dev) for t in host_x]
+    dev_lg = [t.to(dev) for t in host_lg]
+    x32 = torch.zeros((T, CHANNELS), dtype=torch.float32, device=dev)
+    out = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
+    host_out = torch.zeros((T, CHANNELS), dtype=torch.float16).pin_memory()
+    sx, slg = torch.zeros_like(dev_x[0]), torch.zeros_like(dev_lg[0])
+    lib = capi.lib()
+    stream = torch.cuda.current_stream()
+
+    def layer_call(i, x, lg):
+        capi.check(lib.tsp_rows_f16_to_f32(x.data_ptr(), CHANNELS * 2, x32.data_ptr(), CHANNELS * 4, T, CHANNELS, L.stream_ptr()))
+        L.moe_layer_prefill(layers[i % len(layers)], ps, x32, lg, out)
+
+    def resident(i):
+        layer_call(i, dev_x[i % nb], dev_lg[i % nb])
+
+    def e2e(i):
+        sx.copy_(host_x[i % nb], non_blocking=True)
+        slg.copy_(host_lg[i % nb], non_blocking=True)
+        layer_call(i, sx, slg)
+        host_out.copy_(out, non_blocking=True)
+        stream.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def stage_pass(steps):
+        """CUDA-event time of each launch of the prefill layer."""
+        s, st = ps.base, L.stream_ptr()
+        names = ["convert", "route", "permute", "offsets", "gather", "gate_up", "down", "shared", "combine"]
+        acc = dict.fromkeys(names, 0.0)
+        C4, E, K = CHANNELS * 4, EXPERTS, SELECTED
+        for i in range(steps):
+            w = layers[i % len(layers)].weights
+            x, lg = dev_x[i % nb], dev_lg[i % nb]
+            e = s.error.data_ptr()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+            ev[0].record()
+            capi.check(lib.tsp_rows_f16_to_f32(x.data_ptr(), CHANNELS * 2, x32.data_ptr(), C4, T, CHANNELS, st)); ev[1].record()
+            capi.check(lib.tsp_moe_route(lg.data_ptr(), E * 4, T, E, K, 0, 1, s.ids.data_ptr(), s.weights.data_ptr(), e, st)); ev[2].record()
+            capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, E, K, 128, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), e, st)); ev[3].record()
+            capi.check(lib.tsp_moe_route_offsets(s.counts.data_ptr(), E, ps.offsets.data_ptr(), st)); ev[4].record()
+            capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), C4, K, s.token_map.data_ptr(), ps.offsets.data_ptr(), E, T, K, CHANNELS,
+                                               ps.xp.data_ptr(), CHANNELS * 2, ps.pos_route.data_ptr(), e, st)); ev[5].record()
+            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), ps.xp.data_ptr(), CHANNELS * 2, T * K, ps.tasks.data_ptr(),
+                                                   s.counts.data_ptr(), ps.offsets.data_ptr(), ps.hp.data_ptr(), HIDDEN * 2, e, st)); ev[6].record()
+            capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), ps.hp.data_ptr(), HIDDEN * 2, T * K, ps.tasks.data_ptr(), s.counts.data_ptr(),
+                                                ps.offsets.data_ptr(), ps.pos_route.data_ptr(), s.routed.data_ptr(), C4, e, st)); ev[7].record()
+            capi.check(lib.tsp_moe_permute(ps.ids0.data_ptr(), T, 1, 1, 128, ps.s_token_map.data_ptr(), ps.s_counts.data_ptr(), ps.s_tasks.data_ptr(), e, st))
+            capi.check(lib.tsp_moe_route_offsets(ps.s_counts.data_ptr(), 1, ps.s_offsets.data_ptr(), st))
+            capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), C4, 1, ps.s_token_map.data_ptr(), ps.s_offsets.data_ptr(), 1, T, 1, CHANNELS,
+                                               ps.s_xp.data_ptr(), CHANNELS * 2, ps.s_pos.data_ptr(), e, st))
+            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.shared_gate), C.byref(w.shared_up), ps.s_xp.data_ptr(), CHANNELS * 2, T, ps.s_tasks.data_ptr(),
+                                                   ps.s_counts.data_ptr(), ps.s_offsets.data_ptr(), ps.s_hp.data_ptr(), HIDDEN * 2, e, st))
+            capi.check(lib.tsp_moe_grouped_down(C.byref(w.shared_down), ps.s_hp.data_ptr(), HIDDEN * 2, T, ps.s_tasks.data_ptr(), ps.s_counts.data_ptr(),
+                                                ps.s_offsets.data_ptr(), ps.s_pos.data_ptr(), s.shared_out.data_ptr(), C4, e, st)); ev[8].record()
+            capi.check(lib.tsp_moe_combine(s.routed.data_ptr(), C4, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
+                                           x32.data_ptr(), C4, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), CHANNELS * 2, e, st)); ev[9].record()
+            torch.cuda.synchronize()
+            for k_, n in enumerate(names):
+                acc[n] += ev[k_].elapsed_time(ev[k_ + 1])
+        return {n + "_ms": acc[n] / steps for n in names}
+
+    with ClockSampler(local) as clocks:
+        ms = timed(resident, args.steps, args.warmup)
+        ms_e2e = timed(e2e, args.steps, args.warmup)
+        stages = stage_pass(max(2, min(args.steps, 5)))
+    assert ps.base.error_word() == 0, "device error word set during the benchmark"
+    _, tf_peak, peak_kind = peaks()
+    gu_flops = T * SELECTED * 2 * (2 * HIDDEN * CHANNELS)
+    achieved = gu_flops / (stages["gate_up_ms"] * 1e-3) / 1e12
+    cpu = parity = None
+    if args.cpu_tokens != 0:
+        orc, kind = cpu_oracle()
+        cores = os.cpu_count() or 1
+        sample = min(args.cpu_tokens or 64, T)
+        idx = np.unique(np.linspace(0, T - 1, sample).astype(int))
+        host = layers[0].host_layer(SELECTED)
+        xs, ls = host_x[0].numpy()[idx].astype(np.float32), host_lg[0].numpy()[idx]
+        t0 = time.perf_counter()
+        want = orc.moe_layer(host.oracle_dict(), xs, ls, threads=min(cores, len(idx)))
+        dt = time.perf_counter() - t0
+        cpu = {"value": len(idx) / dt, "unit": "tokens/s", "cores": min(cores, len(idx)), "kind": kind,
+               "sample": f"{len(idx)} evenly spaced tokens of the {T}-token batch, one layer, threads over tokens, {dt:.1f} s"}
+        layer_call(0, dev_x[0], dev_lg[0])
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()[idx].astype(np.float64)
+        parity = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    line = {"metric": "moe_q4k_expert_gemm_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"moe_layer_prefill_T{T} (BASELINE configs[2])", "hidden": CHANNELS, "experts": EXPERTS, "expert_ffn": HIDDEN,
+                       "top_k": SELECTED, "weights": "Q4_K Pack-v3 planar", "router": "N(0,1) + Zipf(1.1) per-expert bias",
+                       "l2_policy": "inputs larger than L2: 0.93 GB of weights and 0.5 GB of intermediates per step"},
+            "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2},
+            "gpu_launches": 15 * args.steps, "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "kernel": "grouped_mma_kernel<gate-up> (routed experts, tcgen05)", "achieved": achieved, "peak": tf_peak,
+                         "unit": "TFLOP/s", "frac": achieved / tf_peak, "peak_kind": peak_kind, "traffic": None,
+                         "algorithmic_flops_per_launch": gu_flops, "launch_ms": stages["gate_up_ms"]},
+            "cpu_baseline": cpu,
+            "extra": {"layer_tflops": T * (SELECTED + 1) * FLOPS_PER_ROUTE / (ms * 1e-3) / 1e12, "stage_ms": stages, "parity_rel_l2_vs_cpu": parity}}
     print(json.dumps(line), flush=True)
 
 

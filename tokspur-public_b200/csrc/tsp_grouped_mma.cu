@@ -82,7 +82,8 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-constexpr uint32_t kGWarps = 6;            // producer, MMA, 4 x dequant/epilogue
+constexpr uint32_t kGWarps = 7;            // weight producer, MMA, 4 x dequant/epilogue, activation producer
+constexpr uint32_t kMaxBStages = 8;
 constexpr uint32_t kGThreads = kGWarps * 32;
 constexpr uint32_t kTileRoutes = 128;      // routes per tile (N extent at most)
 constexpr uint32_t kRowsM = 128;           // weight rows per CTA tile (M)
@@ -105,7 +106,7 @@ struct GroupedParams {
     void* out; uint64_t out_stride_bytes;
     uint32_t* error;
     // shared-memory plan
-    uint32_t off_q, q_stage_bytes, off_a, off_b, a_tile_bytes;
+    uint32_t off_q, q_stage_bytes, off_a, off_b, a_tile_bytes, nb_stages;
 };
 
 
@@ -139,17 +140,21 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
     extern __shared__ uint8_t gsm_raw[];
     uint8_t* gsm = gsm_raw + ((1024u - (smem_u32(gsm_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(gsm);
-    uint64_t *qfull = bars, *qempty = bars + 2, *bfull = bars + 4, *afull = bars + 6, *mempty = bars + 8, *acc_full = bars + 10,
-             *acc_empty = bars + 11;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gsm + 128);
+    // two rings: dequantised weight tiles (2 stages, filled by the dequant warps) and activation tiles (nb_stages, filled by TMA);
+    // the activation ring is deep because its loads see full memory latency while a weight tile is produced on chip
+    uint64_t *qfull = bars, *qempty = bars + 2, *afull = bars + 4, *aempty = bars + 6, *bfull = bars + 8, *bempty = bars + 8 + kMaxBStages,
+             *acc_full = bars + 8 + 2 * kMaxBStages, *acc_empty = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gsm + 512);
+    const uint32_t NB = p.nb_stages;
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
             mbar_init(&qfull[s], 1); mbar_init(&qempty[s], 4);
-            mbar_init(&bfull[s], 1); mbar_init(&afull[s], 4); mbar_init(&mempty[s], 1);
+            mbar_init(&afull[s], 4); mbar_init(&aempty[s], 1);
         }
+        for (uint32_t s = 0; s < NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], 1); }
         mbar_init(acc_full, 1); mbar_init(acc_empty, 4);
         mbar_fence_init();
     }
@@ -169,13 +174,13 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
         // =========================== TMA producer ===========================
         if (lane == 0) {
             bool ok = true;
-            uint32_t qs = 0, qph = 0, ms = 0, mph = 0;
+            uint32_t qs = 0, qph = 0, cur_tile = 0xffffffffu;
+            GTile t{};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
-                const GTile t = gtile(p, item / p.row_blocks);
+                if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
                 const uint32_t r0 = (item % p.row_blocks) * kRowsM;
                 const bool hi = t.expert >= p.split;
                 const uint32_t el = hi ? t.expert - p.split : t.expert;
-                const CUtensorMap* xmap = t.ncols == 32 ? &xmap32 : (t.ncols == 64 ? &xmap64 : &xmap128);
                 for (uint32_t sb = 0; sb < p.nblk && ok; ++sb) {
                     // quant stage: code boxes, factor boxes and the d/dmin plane rows of this super-block
                     ok = gwait(&qempty[qs], qph ^ 1u);
@@ -193,14 +198,26 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                         bulk_g2s(q + NMAT * (16384u + 2048u) + m * dm_bytes, eb + p.dm_off + static_cast<uint64_t>(r0) * p.nblk * 4u, dm_bytes, &qfull[qs]);
                     }
                     if (++qs == 2) { qs = 0; qph ^= 1u; }
-                    // activation tiles of the four K chunks of this super-block
-                    for (uint32_t c = 0; c < 4 && ok; ++c) {
-                        ok = gwait(&mempty[ms], mph ^ 1u);
-                        if (!ok) break;
-                        mbar_arrive_expect_tx(&bfull[ms], t.ncols * 128u);
-                        tma_load_2d(gsm + p.off_b + ms * 16384u, xmap, static_cast<int>((sb * 256 + c * 64) * 2), static_cast<int>(t.row0), &bfull[ms]);   // byte coordinate: the map's element is a byte
-                        if (++ms == 2) { ms = 0; mph ^= 1u; }
-                    }
+                }
+            }
+            if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
+        }
+    } else if (warp == 6) {
+        // =========================== activation-tile producer ===========================
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t bs = 0, bph = 0, cur_tile = 0xffffffffu;
+            GTile t{};
+            for (uint32_t item = item0; item < item1 && ok; ++item) {
+                if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
+                const CUtensorMap* xmap = t.ncols == 32 ? &xmap32 : (t.ncols == 64 ? &xmap64 : &xmap128);
+                for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
+                    ok = gwait(&bempty[bs], bph ^ 1u);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&bfull[bs], t.ncols * 128u);
+                    // byte coordinate: the map's element is a byte
+                    tma_load_2d(gsm + p.off_b + bs * 16384u, xmap, static_cast<int>(c * 128), static_cast<int>(t.row0), &bfull[bs]);
+                    if (++bs == NB) { bs = 0; bph ^= 1u; }
                 }
             }
             if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
@@ -209,18 +226,19 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
         // =========================== MMA issuer ===========================
         if (lane == 0) {
             bool ok = true;
-            uint32_t ms = 0, mph = 0, accph = 0;
+            uint32_t ms = 0, mph = 0, bs = 0, bph = 0, accph = 0, cur_tile = 0xffffffffu;
+            GTile t{};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
-                const GTile t = gtile(p, item / p.row_blocks);
+                if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
                 const uint32_t idesc = umma_idesc_f16(kRowsM, t.ncols);
                 ok = gwait(acc_empty, accph ^ 1u);   // the epilogue has drained the previous item's accumulators
                 if (!ok) break;
                 tc_fence_after();
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
-                    ok = gwait(&afull[ms], mph) && gwait(&bfull[ms], mph);
+                    ok = gwait(&afull[ms], mph) && gwait(&bfull[bs], bph);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t bdesc = umma_desc_k128(gsm + p.off_b + ms * 16384u);
+                    const uint64_t bdesc = umma_desc_k128(gsm + p.off_b + bs * 16384u);
 #pragma unroll
                     for (uint32_t m = 0; m < NMAT; ++m) {
                         const uint64_t adesc = umma_desc_k128(gsm + p.off_a + ms * NMAT * 16384u + m * 16384u);
@@ -228,24 +246,27 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                         for (uint32_t kk = 0; kk < 4; ++kk)
                             umma_f16(tmem_base + m * 128u, adesc + kk * 2, bdesc + kk * 2, idesc, (c | kk) != 0 ? 1u : 0u);
                     }
-                    umma_commit(&mempty[ms]);   // frees this stage's A and B tiles once the MMAs above have read them
+                    umma_commit(&aempty[ms]);   // both rings' stages are free once the MMAs above have read them
+                    umma_commit(&bempty[bs]);
                     if (++ms == 2) { ms = 0; mph ^= 1u; }
+                    if (++bs == NB) { bs = 0; bph ^= 1u; }
                 }
                 if (ok) umma_commit(acc_full);
                 accph ^= 1u;
             }
             if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
         }
-    } else {
+    } else if (warp >= 2 && warp <= 5) {
         // =========================== dequantise + epilogue (warps 2..5) ===========================
         const uint32_t dw = warp - 2;                 // 0..3
         const uint32_t row = dw * 32 + lane;          // weight row of the tile this thread dequantises
         const uint32_t sw = row & 7u;
         const uint32_t quarter = warp & 3u;           // tensor-memory lane quarter this warp may read
         bool ok = true;
-        uint32_t qs = 0, qph = 0, ms = 0, mph = 0, accph = 0;
+        uint32_t qs = 0, qph = 0, ms = 0, mph = 0, accph = 0, cur_tile = 0xffffffffu;
+        GTile t{};
         for (uint32_t item = item0; item < item1; ++item) {
-            const GTile t = gtile(p, item / p.row_blocks);
+            if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
             const uint32_t rb = item % p.row_blocks;
             for (uint32_t sb = 0; sb < p.nblk; ++sb) {
                 if (ok) ok = gwait(&qfull[qs], qph);
@@ -262,7 +283,7 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                     if (ok && (!finite_f32(dd[m]) || !finite_f32(dmn[m]))) raise_error(p.error, TSP_ERR_NONFINITE);
                 }
                 for (uint32_t c = 0; c < 4; ++c) {
-                    if (ok) ok = gwait(&mempty[ms], mph ^ 1u);   // the MMAs that read this A tile two chunks ago are done
+                    if (ok) ok = gwait(&aempty[ms], mph ^ 1u);   // the MMAs that read this A tile two chunks ago are done
                     if (ok) {
 #pragma unroll
                         for (uint32_t m = 0; m < NMAT; ++m) {
@@ -310,35 +331,48 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                 if (++qs == 2) { qs = 0; qph ^= 1u; }
             }
             // ---- epilogue: this warp's 32 accumulator lanes = weight rows rb*128 + quarter*32 + lane ----
+            // route ids of the tile's positions, fetched before the wait so their latency hides behind the last MMAs:
+            // lane l keeps positions l, 32+l, 64+l, 96+l of the tile
+            uint32_t rt[4] = {0, 0, 0, 0};
+            if (!GATEUP) {
+#pragma unroll
+                for (uint32_t qd = 0; qd < 4; ++qd)
+                    if (qd * 32 + lane < t.count) rt[qd] = p.pos_route[t.row0 + qd * 32 + lane];
+            }
             if (ok) ok = gwait(acc_full, accph);
             accph ^= 1u;
             if (ok) {
                 tc_fence_after();
                 const uint32_t wrow = rb * kRowsM + quarter * 32 + lane;
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+                // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weight tiles use
+                const uint32_t hcol = (wrow & ~7u) | ((wrow & 4u) | ((wrow & 1u) << 1) | ((wrow & 2u) >> 1));
+                char* hrow = reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(t.row0) * p.out_stride_bytes + (GATEUP ? hcol * 2 : 0);
                 bool bad = false;
-                for (uint32_t j0 = 0; j0 < t.ncols; j0 += 16) {
-                    if (j0 >= t.count) break;
+                for (uint32_t j0 = 0; j0 < t.ncols && j0 < t.count; j0 += 16) {
                     uint32_t g[16], u[16];
+                    const uint32_t rq = j0 < 32 ? rt[0] : (j0 < 64 ? rt[1] : (j0 < 96 ? rt[2] : rt[3]));   // this lane's route id in the 32-wide group of j0
                     tmem_ld16(taddr + j0, g);
                     if (GATEUP) tmem_ld16(taddr + 128u + j0, u);
                     tmem_ld_wait();
 #pragma unroll
                     for (uint32_t i = 0; i < 16; ++i) {
-                        if (j0 + i >= t.count) break;
-                        const uint32_t pos = t.row0 + j0 + i;
+                        const uint32_t j = j0 + i;
                         if (GATEUP) {
-                            const float v = stable_silu(__uint_as_float(g[i])) * __uint_as_float(u[i]);
-                            const __half hv = __float2half_rn(v);
-                            bad |= !finite_f32(__half2float(hv));
-                            // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weights use
-                            const uint32_t col = (wrow & ~7u) | ((wrow & 4u) | ((wrow & 1u) << 1) | ((wrow & 2u) >> 1));
-                            reinterpret_cast<__half*>(reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(pos) * p.out_stride_bytes)[col] = hv;
+                            if (j < t.count) {
+                                const float gv = __uint_as_float(g[i]);
+                                const float v = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[i]);   // silu(g) * u
+                                const __half hv = __float2half_rn(v);
+                                bad |= !finite_f32(__half2float(hv));
+                                *reinterpret_cast<__half*>(hrow + static_cast<uint64_t>(j) * p.out_stride_bytes) = hv;
+                            }
                         } else {
-                            const float v = __uint_as_float(g[i]);
-                            bad |= !finite_f32(v);
-                            const uint32_t route = p.pos_route[pos];
-                            reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(route) * p.out_stride_bytes)[wrow] = v;
+                            const uint32_t route = __shfl_sync(0xffffffffu, rq, j & 31u);
+                            if (j < t.count) {
+                                const float v = __uint_as_float(g[i]);
+                                bad |= !finite_f32(v);
+                                reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(route) * p.out_stride_bytes)[wrow] = v;
+                            }
                         }
                     }
                 }
@@ -467,8 +501,10 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     p.q_stage_bytes = (nmat * (16384u + 2048u + kRowsM * nblk * 4u) + 1023u) & ~1023u;
     p.off_a = p.off_q + 2 * p.q_stage_bytes;
     p.off_b = p.off_a + 2 * nmat * 16384u;
-    const size_t smem = p.off_b + 2 * 16384u + 1024;
-    TSP_REQUIRE(smem <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
+    TSP_REQUIRE(p.off_b + 2 * 16384u + 1024 <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
+    p.nb_stages = (227 * 1024 - 1024 - p.off_b) / 16384u;
+    if (p.nb_stages > kMaxBStages) p.nb_stages = kMaxBStages;
+    const size_t smem = p.off_b + p.nb_stages * 16384u + 1024;
 
     CUtensorMap maps[11];
     const uint64_t stride = a->experts > 1 ? a->expert_stride : tsp_expert_bytes(a->type, a->layout, a->rows, a->cols);

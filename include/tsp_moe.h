@@ -167,6 +167,11 @@ int tsp_synth_weights(uint32_t type, uint64_t seed, uint64_t first_block, uint64
 int tsp_pack_planar(uint32_t type, uint32_t rows, uint32_t cols, uint32_t experts, const void* d_gguf, uint64_t gguf_expert_stride,
                     void* d_planar, uint64_t planar_expert_stride, void* stream);
 
+/* Replaces `gemv(type 0)` / `gemv_rows` / `moe_router_f32_batch` on F32 matrices (graph.mm:4182, 4271, 5729): the router and
+ * shared-router projections, out[t][r] = sum_c W[r][c] x[t][c], W row-major F32 [rows x cols], FP32 accumulation. */
+int tsp_gemv_f32(const float* d_w, uint32_t rows, uint32_t cols, const float* d_x, uint64_t x_stride_bytes, uint32_t tokens,
+                 float* d_out, uint64_t out_stride_bytes, uint32_t* d_error, void* stream);
+
 /* binary16 rows -> FP32 rows (exact) and back (round to nearest even); activation edge of the layer. */
 int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride_bytes, float* d_out, uint64_t out_stride_bytes,
                         uint32_t rows, uint32_t cols, void* stream);

@@ -64,6 +64,7 @@ SIGNATURES = {
     "tsp_moe_combine": (_i, [_vp, _u64, _vp, _vp, _u64, _vp, _vp, _u64, _vp, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp, _vp]),
     "tsp_synth_weights": (_i, [_u32, _u64, _u64, _u64, C.c_float, _vp, _vp]),
     "tsp_pack_planar": (_i, [_u32, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),
+    "tsp_gemv_f32": (_i, [_vp, _u32, _u32, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
     "tsp_rows_f16_to_f32": (_i, [_vp, _u64, _vp, _u64, _u32, _u32, _vp]),
     "tsp_moe_layer_decode": (_i, [C.POINTER(MoeWeights), C.POINTER(MoeScratch), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32,
                                   _u32, _u32, _u32, _i, _vp, _u64, _u32, _vp, _vp]),

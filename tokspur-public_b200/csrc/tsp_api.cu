@@ -51,6 +51,7 @@ int launch_gather_rows(const float*, uint64_t, uint32_t, const uint32_t*, const 
                        uint32_t*, uint32_t*, cudaStream_t);
 int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, const uint32_t*, const uint32_t*,
                    const uint32_t*, const uint32_t*, void*, uint64_t, uint32_t*, cudaStream_t);
+int launch_gemv_f32(const float*, uint32_t, uint32_t, const float*, uint64_t, uint32_t, float*, uint64_t, uint32_t*, cudaStream_t);
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
 
@@ -262,6 +263,14 @@ int tsp_pack_planar(uint32_t type, uint32_t rows, uint32_t cols, uint32_t expert
                 "pack: expert strides too small or unaligned");
     const uint64_t blocks = static_cast<uint64_t>(rows) * (cols / (type == TSP_TYPE_Q4_K ? 256 : 32));
     return launch_pack_planar(type, d_gguf, gguf_stride, d_planar, planar_stride, blocks, experts, static_cast<cudaStream_t>(stream));
+}
+
+int tsp_gemv_f32(const float* d_w, uint32_t rows, uint32_t cols, const float* d_x, uint64_t x_stride, uint32_t tokens, float* d_out,
+                 uint64_t out_stride, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_w && d_x && d_out, "gemv: null buffer");
+    TSP_REQUIRE(rows >= 1 && cols >= 1 && tokens >= 1 && static_cast<uint64_t>(rows) * tokens < (1ull << 28), "GEMV shape mismatch");
+    TSP_REQUIRE(x_stride >= cols * 4ull && x_stride % 4 == 0 && out_stride >= rows * 4ull && out_stride % 4 == 0, "gemv: row stride too small");
+    return launch_gemv_f32(d_w, rows, cols, d_x, x_stride, tokens, d_out, out_stride, d_error, static_cast<cudaStream_t>(stream));
 }
 
 int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride, float* d_out, uint64_t out_stride, uint32_t rows,

@@ -244,6 +244,34 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
     if (bad) raise_error(error, TSP_ERR_NONFINITE);
 }
 
+// ---------------------------------------------------------------------------------------------
+// F32 matrix-vector product for the router projections: one warp per (matrix row, token), FP32 FMA + tree sum.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gemv_f32_kernel(const float* __restrict__ w, uint32_t rows, uint32_t cols, const float* __restrict__ x, uint64_t x_stride, uint32_t tokens,
+                float* __restrict__ out, uint64_t out_stride, uint32_t* error) {
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= rows * tokens) return;
+    const uint32_t token = warp / rows, row = warp % rows;
+    const float* wr = w + static_cast<uint64_t>(row) * cols;
+    const float* xr = reinterpret_cast<const float*>(reinterpret_cast<const char*>(x) + token * x_stride);
+    float acc = 0.f;
+    for (uint32_t c = lane; c < cols; c += 32) acc = fmaf(wr[c], xr[c], acc);
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        if (!finite_f32(acc)) raise_error(error, TSP_ERR_NONFINITE);
+        reinterpret_cast<float*>(reinterpret_cast<char*>(out) + token * out_stride)[row] = acc;
+    }
+}
+
+int launch_gemv_f32(const float* w, uint32_t rows, uint32_t cols, const float* x, uint64_t x_stride, uint32_t tokens, float* out,
+                    uint64_t out_stride, uint32_t* error, cudaStream_t st) {
+    const uint64_t warps = static_cast<uint64_t>(rows) * tokens;
+    gemv_f32_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(w, rows, cols, x, x_stride, tokens, out, out_stride, error);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
 __global__ void rows_f16_to_f32_kernel(const __half* __restrict__ in, uint64_t in_stride, float* __restrict__ out,
                                        uint64_t out_stride, uint32_t rows, uint32_t cols) {
     const uint32_t row = blockIdx.y;

@@ -1,0 +1,99 @@
+// CUDA-backed execution context with the ownership and batch rules of the reference's graph
+// (native/include/tokspur/graph.hpp:427-495, 709-717): buffers are opaque checked capabilities, allocation / upload /
+// read / release happen only between batches, weights are immutable registered imports, encode calls never allocate
+// or read back, one host thread owns the graph, and a batch's device-side failures surface once, at submit().
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <optional>
+#include <span>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "tsp_moe.h"
+
+namespace tokspur_b200 {
+
+class FormatError : public std::runtime_error {
+public:
+    using std::runtime_error::runtime_error;
+};
+
+// Opaque, checked capability: a released or foreign view is never silently rebound. Offsets/lengths are bytes.
+struct GpuView {
+    uint64_t owner = 0;
+    size_t slot = 0;
+    uint64_t offset = 0;
+    uint64_t bytes = 0;
+};
+struct GpuRowsF32 {
+    GpuView view;
+    uint32_t rows = 0, columns = 0;
+    uint64_t stride_bytes = 0;
+};
+struct PlanarMatrixShape {
+    uint32_t source_type = 0;  // 8 (Q8_0), 12 (Q4_K)
+    uint32_t kind = 0;         // PlanarKind: 2/3 q4k co-located gate/up, 6/7 q8 co-located, 9 q8 planar, 10 q4k planar (this build's down extension)
+    uint32_t columns = 0, rows = 0, experts = 0;
+};
+enum class RouterMode : uint32_t { softmax, sigmoid };
+struct BatchResult { uint64_t dispatches = 0; double wall_ms = 0, gpu_ms = 0; };
+
+class CudaGraph {
+public:
+    explicit CudaGraph(int device, uint64_t byte_budget);
+    ~CudaGraph();
+    CudaGraph(const CudaGraph&) = delete;
+    CudaGraph& operator=(const CudaGraph&) = delete;
+
+    [[nodiscard]] GpuView zeros(uint64_t bytes, std::string label);
+    [[nodiscard]] GpuView upload(std::span<const std::byte> data, std::string label, bool immutable = true);
+    [[nodiscard]] GpuView slice(GpuView buffer, uint64_t offset, uint64_t bytes) const;
+    void write(GpuView destination, std::span<const std::byte> data);
+    [[nodiscard]] std::vector<std::byte> read(GpuView source) const;
+    void release(GpuView full_buffer);
+    [[nodiscard]] uint64_t live_bytes() const noexcept { return live_bytes_; }
+    [[nodiscard]] uint64_t allocations() const noexcept { return allocations_; }
+
+    // Lossless Pack v3 planar registration (graph.mm:9021-9059): immutable, 16-byte aligned, size == planar bytes * experts.
+    void register_planar_matrix(GpuView matrix, PlanarMatrixShape shape);
+    [[nodiscard]] std::optional<PlanarMatrixShape> planar_matrix_shape(GpuView matrix) const;
+
+    void begin();
+    void abort();                          // discards an unsubmitted batch
+    [[nodiscard]] BatchResult submit();    // waits once, checks the sticky error word, throws FormatError if it is set
+
+    // operators (each is one or two launches through the C ABI; all require an open batch)
+    void gemv_f32(GpuView matrix, GpuView input, GpuView output, uint32_t columns, uint32_t rows);   // gemv(type 0)
+    void route(GpuView logits, GpuView indices, GpuView weights, uint32_t selected, RouterMode mode, bool normalize_selected);
+
+    // raw access for the composed encoders in moe.cpp
+    [[nodiscard]] void* device_pointer(GpuView view, bool for_write = false) const;
+    [[nodiscard]] uint32_t* error_word() const noexcept { return error_; }
+    [[nodiscard]] void* stream() const noexcept { return stream_; }
+    void count_dispatches(uint64_t n) { require_batch(); dispatches_ += n; }
+    void require_batch() const;
+
+private:
+    struct Buffer { void* ptr = nullptr; uint64_t bytes = 0; bool immutable = false; bool live = false; std::string label; };
+    struct Planar { size_t slot; uint64_t offset; PlanarMatrixShape shape; };
+    const Buffer& checked(GpuView view) const;
+    void require_idle() const;
+    void check(int rc) const;
+
+    uint64_t owner_;
+    int device_;
+    uint64_t budget_, live_bytes_ = 0, allocations_ = 0;
+    std::vector<Buffer> buffers_;
+    std::vector<Planar> planar_;
+    uint32_t* error_ = nullptr;
+    void* stream_ = nullptr;
+    void *ev0_ = nullptr, *ev1_ = nullptr;
+    bool in_batch_ = false, frozen_ = false;
+    uint64_t dispatches_ = 0;
+    double batch_start_ = 0;
+};
+
+}  // namespace tokspur_b200

@@ -1,0 +1,34 @@
+// MoE FFN sub-layer encoders with the reference's entry points (native/include/tokspur/moe.hpp:9-45): same descriptor
+// structs, same argument meaning, same refusal behaviour (FormatError before anything is encoded).
+#pragma once
+
+#include <array>
+
+#include "tokspur_b200/graph.hpp"
+
+namespace tokspur_b200 {
+
+struct GpuMatrix { GpuView view; uint32_t encoding; };
+struct MoeShape { uint32_t channels, hidden, experts, selected; };
+struct MoeWeights {
+    GpuMatrix router, gate, up, down, shared_gate, shared_up, shared_down, shared_router;
+};
+// The reference's ten views plus the three permutation tables its prefill scratch carries (moe_mm_many.hpp:50-55).
+struct MoeScratch {
+    GpuView logits, indices, weights, gate, up, down, shared_gate, shared_up, shared_down, shared_logit;
+    GpuView token_map, counts, tasks;
+    [[nodiscard]] std::array<GpuView, 13> views() const;
+};
+
+MoeScratch allocate_moe_scratch(CudaGraph& graph, MoeShape shape);
+void release_moe_scratch(CudaGraph& graph, const MoeScratch& scratch);
+
+// True when gate/up are registered co-located planar pairs and down a registered planar set of matching shape (moe.hpp:22-35).
+[[nodiscard]] bool is_planar_moe(const CudaGraph& g, const MoeWeights& w, MoeShape s);
+
+// One token row: F32 router projection, top-k, routed gate-up + SwiGLU and down, shared expert, gated mixture.
+// Neither allocates, reads back nor commits; `input`/`output` are FP32 rows of `channels` values.
+void encode_moe(CudaGraph& graph, const MoeWeights& weights, const MoeScratch& scratch, GpuView input, GpuView output,
+                MoeShape shape, RouterMode mode, bool normalize_selected);
+
+}  // namespace tokspur_b200

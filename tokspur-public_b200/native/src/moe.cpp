@@ -1,0 +1,108 @@
+// encode_moe over the CUDA graph: the reference's composition (native/src/moe.cpp:37-83) with the routed / shared expert
+// stages and the mixture forwarded to the C ABI's layer entry point. Shape and extent checks happen before anything is encoded.
+#include "tokspur_b200/moe.hpp"
+
+namespace tokspur_b200 {
+namespace {
+void shape_check(MoeShape s) {
+    if (!s.channels || s.channels > 65536 || !s.hidden || s.hidden > 65536 || !s.experts || s.experts > 4096 || !s.selected ||
+        s.selected > 64 || s.selected > s.experts) throw FormatError("invalid mixture shape");
+}
+
+// matrix set of `experts` matrices [rows x cols] behind one view: GGUF rows, or a registered planar tensor
+tsp_matrix_set matrix_set(const CudaGraph& g, GpuMatrix m, uint32_t rows, uint32_t cols, uint32_t experts) {
+    tsp_matrix_set s{};
+    s.base = g.device_pointer(m.view);
+    s.rows = rows; s.cols = cols; s.experts = experts; s.split = experts; s.type = m.encoding;
+    const auto planar = g.planar_matrix_shape(m.view);
+    s.layout = planar ? TSP_LAYOUT_PLANAR : TSP_LAYOUT_GGUF;
+    s.expert_stride = tsp_expert_bytes(s.type, s.layout, rows, cols);
+    if (!s.expert_stride || m.view.bytes != s.expert_stride * experts) throw FormatError("weight view does not match the layer shape");
+    return s;
+}
+}
+
+std::array<GpuView, 13> MoeScratch::views() const {
+    return {logits, indices, weights, gate, up, down, shared_gate, shared_up, shared_down, shared_logit, token_map, counts, tasks};
+}
+
+MoeScratch allocate_moe_scratch(CudaGraph& graph, MoeShape s) {
+    shape_check(s);
+    const uint64_t tasks_words = tsp_moe_tasks_words(1, s.experts, s.selected, TSP_GEMV_TILE);
+    const std::array<uint64_t, 13> counts{s.experts, s.selected, s.selected, uint64_t(s.hidden) * s.selected, uint64_t(s.hidden) * s.selected,
+                                          uint64_t(s.channels) * s.selected, s.hidden, s.hidden, s.channels, 1, s.experts, s.experts, tasks_words};
+    std::array<GpuView, 13> v{};
+    size_t made = 0;
+    try {
+        for (; made < counts.size(); ++made) v[made] = graph.zeros(counts[made] * 4, "mixture scratch");
+    } catch (...) {
+        for (size_t i = 0; i < made; ++i) graph.release(v[i]);
+        throw;
+    }
+    return {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12]};
+}
+
+void release_moe_scratch(CudaGraph& graph, const MoeScratch& scratch) {
+    for (const auto view : scratch.views()) graph.release(view);
+}
+
+bool is_planar_moe(const CudaGraph& g, const MoeWeights& w, MoeShape s) {
+    const auto lo = g.planar_matrix_shape(w.gate.view), hi = g.planar_matrix_shape(w.up.view), dn = g.planar_matrix_shape(w.down.view);
+    if (!lo || !hi || !dn) return false;
+    return (lo->kind == 2u || lo->kind == 6u) && (hi->kind == 3u || hi->kind == 7u) && (dn->kind == 9u || dn->kind == 10u) &&
+           lo->source_type == w.gate.encoding && hi->source_type == w.up.encoding && dn->source_type == w.down.encoding &&
+           lo->source_type == hi->source_type && lo->columns == s.channels && lo->rows == s.hidden && lo->experts == s.experts &&
+           hi->columns == s.channels && hi->rows == s.hidden && hi->experts == s.experts && dn->columns == s.hidden &&
+           dn->rows == s.channels && dn->experts == s.experts;
+}
+
+void encode_moe(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView input, GpuView output, MoeShape shape,
+                RouterMode mode, bool normalize_selected) {
+    shape_check(shape);
+    if (input.bytes != uint64_t(shape.channels) * 4 || output.bytes != uint64_t(shape.channels) * 4) throw FormatError("mixture shape mismatch");
+    if (w.router.encoding != 0 || w.shared_router.encoding != 0) throw FormatError("router projections must be F32");
+    tsp_moe_weights tw{};
+    if (is_planar_moe(g, w, shape)) {
+        // co-located pairs: the "gate" tensor holds experts [0, E/2) as [gate_e, up_e], the "up" tensor experts [E/2, E)
+        const uint64_t pb = tsp_expert_bytes(w.gate.encoding, TSP_LAYOUT_PLANAR, shape.hidden, shape.channels);
+        const auto lo = static_cast<const char*>(g.device_pointer(w.gate.view)), hi = static_cast<const char*>(g.device_pointer(w.up.view));
+        tw.gate = {lo, hi, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, w.gate.encoding, TSP_LAYOUT_PLANAR};
+        tw.up = {lo + pb, hi + pb, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, w.up.encoding, TSP_LAYOUT_PLANAR};
+    } else {
+        tw.gate = matrix_set(g, w.gate, shape.hidden, shape.channels, shape.experts);
+        tw.up = matrix_set(g, w.up, shape.hidden, shape.channels, shape.experts);
+    }
+    tw.down = matrix_set(g, w.down, shape.channels, shape.hidden, shape.experts);
+    tw.shared_gate = matrix_set(g, w.shared_gate, shape.hidden, shape.channels, 1);
+    tw.shared_up = matrix_set(g, w.shared_up, shape.hidden, shape.channels, 1);
+    tw.shared_down = matrix_set(g, w.shared_down, shape.channels, shape.hidden, 1);
+    tw.d_shared_router = static_cast<const float*>(g.device_pointer(w.shared_router.view));
+    if (w.shared_router.view.bytes != uint64_t(shape.channels) * 4) throw FormatError("shared router shape mismatch");
+
+    tsp_moe_scratch ts{};
+    ts.d_ids = static_cast<uint32_t*>(g.device_pointer(s.indices, true));
+    ts.d_weights = static_cast<float*>(g.device_pointer(s.weights, true));
+    ts.d_hidden = static_cast<float*>(g.device_pointer(s.gate, true));
+    ts.d_routed = static_cast<float*>(g.device_pointer(s.down, true));
+    ts.d_shared_hidden = static_cast<float*>(g.device_pointer(s.shared_gate, true));
+    ts.d_shared_out = static_cast<float*>(g.device_pointer(s.shared_down, true));
+    ts.d_shared_logit = static_cast<float*>(g.device_pointer(s.shared_logit, true));
+    ts.d_token_map = static_cast<uint32_t*>(g.device_pointer(s.token_map, true));
+    ts.d_counts = static_cast<uint32_t*>(g.device_pointer(s.counts, true));
+    ts.d_tasks = static_cast<uint32_t*>(g.device_pointer(s.tasks, true));
+    ts.capacity = 1;
+    if (s.token_map.bytes < uint64_t(shape.experts) * 4 || s.counts.bytes < uint64_t(shape.experts) * 4 ||
+        s.tasks.bytes < tsp_moe_tasks_words(1, shape.experts, shape.selected, TSP_GEMV_TILE) * 4 ||
+        s.gate.bytes < uint64_t(shape.hidden) * shape.selected * 4 || s.down.bytes < uint64_t(shape.channels) * shape.selected * 4)
+        throw FormatError("mixture scratch too small");
+
+    g.gemv_f32(w.router.view, input, s.logits, shape.channels, shape.experts);
+    const int rc = tsp_moe_layer_decode(&tw, &ts, g.device_pointer(input), uint64_t(shape.channels) * 4, 0,
+                                        static_cast<const float*>(g.device_pointer(s.logits)), uint64_t(shape.experts) * 4, 1, shape.channels,
+                                        shape.hidden, shape.experts, shape.selected, uint32_t(mode), normalize_selected,
+                                        g.device_pointer(output, true), uint64_t(shape.channels) * 4, 0, g.error_word(), g.stream());
+    if (rc != TSP_OK) throw FormatError(tsp_last_error());
+    g.count_dispatches(6);   // route, routes+tasks (2), gate-up, down, combine (the shared expert rides in the routed launches)
+}
+
+}  // namespace tokspur_b200

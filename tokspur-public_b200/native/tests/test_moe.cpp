@@ -1,0 +1,178 @@
+// encode_moe on the CUDA graph against the CPU oracle, in the style of the reference's native/tests/test_moe.cpp:
+// generated weights, route ids bit-equal, every stage within 5e-5 scaled error, refusals before encoding, sticky-error
+// recovery, allocation invariants. The oracle (oracle/tsp_oracle.h) is test infrastructure and is linked only here.
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <iostream>
+#include <vector>
+
+#include "tokspur_b200/moe.hpp"
+#include "tsp_oracle.h"
+
+using namespace tokspur_b200;
+namespace {
+size_t checks = 0;
+double worst = 0;
+void require(bool v, const char* message) { ++checks; if (!v) throw std::runtime_error(message); }
+void refuses(const std::function<void()>& action, const char* message) {
+    ++checks;
+    try { action(); } catch (const FormatError&) { return; }
+    throw std::runtime_error(message);
+}
+template <class T> std::vector<T> read(CudaGraph& g, GpuView v) {
+    const auto bytes = g.read(v);
+    std::vector<T> out(bytes.size() / sizeof(T));
+    std::memcpy(out.data(), bytes.data(), bytes.size());
+    return out;
+}
+void close(const std::vector<float>& actual, const double* expected, size_t n, double tolerance = 5e-5) {
+    require(actual.size() >= n, "result shape mismatch");
+    for (size_t i = 0; i < n; ++i) {
+        const double e = std::abs(actual[i] - expected[i]) / std::max(1.0, std::abs(expected[i]));
+        worst = std::max(worst, e);
+        require(std::isfinite(actual[i]) && e <= tolerance, "MoE numerical tolerance exceeded");
+    }
+}
+// the reference's "bounded nonzero quant domain" generator (native/tests/test_moe_mm_many_gpu.cpp:30-47), Q4_K and Q8_0
+std::vector<uint8_t> generated(uint32_t type, uint32_t k, uint32_t r, uint32_t e, uint32_t seed) {
+    const uint32_t epb = type == 8 ? 32 : 256, bpb = type == 8 ? 34 : 144;
+    std::vector<uint8_t> raw(uint64_t(k / epb) * bpb * r * e);
+    uint32_t rng = seed;
+    for (size_t at = 0; at < raw.size(); at += bpb) {
+        for (uint32_t i = 0; i < bpb; ++i) { rng = rng * 1664525u + 1013904223u; raw[at + i] = uint8_t(rng >> 24); }
+        raw[at] = 1; raw[at + 1] = 0x0c;
+        if (type == 8) { for (unsigned i = 0; i < 32; ++i) { rng = rng * 1664525u + 1013904223u; raw[at + 2 + i] = uint8_t(int(rng % 31) - 15); } }
+        else {
+            raw[at + 2] = 1; raw[at + 3] = 4;
+            for (unsigned i = 0; i < 8; ++i) raw[at + 4 + i] = 1;
+            for (unsigned i = 8; i < 12; ++i) raw[at + 4 + i] = 0x11;
+            for (unsigned i = 0; i < 128; ++i) raw[at + 16 + i] &= 0x77;
+        }
+    }
+    return raw;
+}
+std::vector<float> activations(uint32_t seed, size_t n, float scale) {
+    std::vector<float> out(n);
+    uint32_t rng = seed;
+    for (auto& x : out) { rng = rng * 1664525u + 1013904223u; x = scale * float(int(rng % 1993) - 996) / 997; }
+    return out;
+}
+std::span<const std::byte> bytes(const std::vector<uint8_t>& v) { return {reinterpret_cast<const std::byte*>(v.data()), v.size()}; }
+template <class T> std::span<const std::byte> bytes_of(const std::vector<T>& v) { return {reinterpret_cast<const std::byte*>(v.data()), v.size() * sizeof(T)}; }
+
+std::vector<uint8_t> planar(uint32_t type, const std::vector<uint8_t>& gguf, uint32_t cols, uint32_t rows, uint32_t experts) {
+    tso_planar_spec spec;
+    require(tso_make_expert_spec(type, cols, rows, &spec) == TSO_OK, "planar spec");
+    std::vector<uint8_t> out(spec.planar_expert_bytes * experts);
+    for (uint32_t e = 0; e < experts; ++e)
+        require(tso_pack_expert_planar(&spec, gguf.data() + e * spec.source_expert_bytes, out.data() + e * spec.planar_expert_bytes) == TSO_OK, "pack");
+    return out;
+}
+
+void layer(CudaGraph& g, uint32_t type, bool use_planar, MoeShape shape, uint32_t seed) {
+    const uint32_t C = shape.channels, H = shape.hidden, E = shape.experts, K = shape.selected;
+    const auto gate = generated(type, C, H, E, seed + 1), up = generated(type, C, H, E, seed + 2), down = generated(type, H, C, E, seed + 3);
+    const auto sgate = generated(type, C, H, 1, seed + 4), sup = generated(type, C, H, 1, seed + 5), sdown = generated(type, H, C, 1, seed + 6);
+    const auto router = activations(seed + 7, size_t(E) * C, 0.25f), srouter = activations(seed + 8, C, 0.125f);
+    MoeWeights w{};
+    w.router = {g.upload(bytes_of(router), "router"), 0};
+    w.shared_router = {g.upload(bytes_of(srouter), "shared router"), 0};
+    w.shared_gate = {g.upload(bytes(sgate), "sg"), type}; w.shared_up = {g.upload(bytes(sup), "su"), type}; w.shared_down = {g.upload(bytes(sdown), "sd"), type};
+    if (use_planar) {
+        // co-located pairs: lo = experts [0, E/2) as [gate_e, up_e], hi = the rest (planar_pack_v3.cpp:1076-1093)
+        const auto pg = planar(type, gate, C, H, E), pu = planar(type, up, C, H, E);
+        const size_t pb = pg.size() / E;
+        std::vector<uint8_t> lo(pb * E), hi(pb * E);
+        for (uint32_t e = 0; e < E; ++e) {
+            auto& dst = e < E / 2 ? lo : hi;
+            const size_t at = size_t(e % (E / 2)) * 2 * pb;
+            std::memcpy(dst.data() + at, pg.data() + e * pb, pb);
+            std::memcpy(dst.data() + at + pb, pu.data() + e * pb, pb);
+        }
+        w.gate = {g.upload(bytes(lo), "pair lo"), type}; w.up = {g.upload(bytes(hi), "pair hi"), type};
+        w.down = {g.upload(bytes(planar(type, down, H, C, E)), "down planar"), type};
+        const uint32_t gk = type == 12 ? 2 : 6, dk = type == 12 ? 10 : 9;
+        g.register_planar_matrix(w.gate.view, {type, gk, C, H, E});
+        g.register_planar_matrix(w.up.view, {type, gk + 1, C, H, E});
+        g.register_planar_matrix(w.down.view, {type, dk, H, C, E});
+        require(is_planar_moe(g, w, shape), "registered pairs are recognised as a planar MoE");
+    } else {
+        w.gate = {g.upload(bytes(gate), "gate"), type}; w.up = {g.upload(bytes(up), "up"), type}; w.down = {g.upload(bytes(down), "down"), type};
+        require(!is_planar_moe(g, w, shape), "raw GGUF tensors are not planar");
+    }
+    const auto scratch = allocate_moe_scratch(g, shape);
+    const auto input = g.zeros(C * 4, "input"), output = g.zeros(C * 4, "output");
+    const auto allocations = g.allocations();
+
+    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1};
+    for (uint32_t token = 0; token < 3; ++token) {
+        const auto x = activations(100 + token + seed, C, 8.f);
+        std::vector<double> expected(C), ew(K), act(size_t(K) * H), routed(size_t(K) * C), sact(H), sout(C);
+        std::vector<uint32_t> eids(K);
+        double slog = 0;
+        tso_layer_stages st{eids.data(), ew.data(), act.data(), routed.data(), sact.data(), sout.data(), &slog};
+        require(tso_moe_layer(&L, x.data(), nullptr, 1, expected.data(), &st, 1) == TSO_OK, "oracle layer");
+        g.write(input, bytes_of(x));
+        for (int run = 0; run < 2; ++run) {
+            g.begin();
+            encode_moe(g, w, scratch, input, output, shape, RouterMode::softmax, true);
+            const auto batch = g.submit();
+            require(batch.dispatches >= 7 && g.allocations() == allocations, "dispatch / allocation invariant");
+            require(read<uint32_t>(g, scratch.indices) == eids, "route ids differ");
+            close(read<float>(g, scratch.weights), ew.data(), K);
+            close(read<float>(g, scratch.gate), act.data(), act.size());
+            close(read<float>(g, scratch.down), routed.data(), routed.size());
+            close(read<float>(g, scratch.shared_gate), sact.data(), H);
+            close(read<float>(g, scratch.shared_down), sout.data(), C);
+            close(read<float>(g, output), expected.data(), C);
+        }
+    }
+    // refusals happen before anything is encoded; the batch is then discarded and the graph stays usable
+    g.begin();
+    refuses([&] { encode_moe(g, w, scratch, g.slice(input, 0, C * 2), output, shape, RouterMode::softmax, true); }, "short input accepted");
+    refuses([&] { encode_moe(g, w, scratch, input, output, {C, H, E, E + 1}, RouterMode::softmax, true); }, "selected > experts accepted");
+    g.abort();
+    refuses([&] { encode_moe(g, w, scratch, input, output, shape, RouterMode::softmax, true); }, "encode outside a batch accepted");
+    // sticky error word: a non-finite input is reported at submit, and the next batch is clean again
+    auto bad = activations(5, C, 1.f);
+    bad[3] = std::numeric_limits<float>::infinity();
+    g.write(input, bytes_of(bad));
+    g.begin();
+    encode_moe(g, w, scratch, input, output, shape, RouterMode::softmax, true);
+    refuses([&] { (void)g.submit(); }, "non-finite input was not reported at submit");
+    const auto x = activations(100 + seed, C, 8.f);
+    g.write(input, bytes_of(x));
+    g.begin();
+    encode_moe(g, w, scratch, input, output, shape, RouterMode::softmax, true);
+    (void)g.submit();
+    release_moe_scratch(g, scratch);
+}
+}  // namespace
+
+int main() {
+    try {
+        CudaGraph g(0, uint64_t(2) << 30);
+        refuses([&] { (void)g.zeros(uint64_t(3) << 30, "too large"); }, "allocation beyond the budget accepted");
+        layer(g, 12, true, {256, 256, 8, 4}, 1);
+        std::cout << "MoE checks passed so far: " << checks << " (worst scaled error " << worst << ")\n";
+    } catch (const std::exception& e) {
+        std::cerr << "MoE check failed after " << checks << " checks: " << e.what() << '\n';
+        return 1;
+    }
+    // planar registration is frozen after the first batch of a graph, so every weight form gets its own graph
+    const struct { uint32_t type; bool planar; MoeShape shape; } cases[] = {
+        {12, false, {256, 256, 8, 4}}, {8, true, {256, 64, 8, 4}}, {8, false, {64, 64, 6, 3}}, {12, true, {512, 256, 16, 10}}};
+    uint32_t seed = 50;
+    for (const auto& c : cases) {
+        try {
+            CudaGraph g(0, uint64_t(2) << 30);
+            layer(g, c.type, c.planar, c.shape, seed += 10);
+        } catch (const std::exception& e) {
+            std::cerr << "MoE check failed (type " << c.type << ", planar " << c.planar << ") after " << checks << " checks: " << e.what() << '\n';
+            return 1;
+        }
+    }
+    std::cout << "MoE encode checks passed: " << checks << " (worst scaled error " << worst << ")\n";
+    return 0;
+}

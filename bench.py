@@ -153,6 +153,9 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------------
+NCU_GATE_UP_DRAM_BYTES_PER_EXPERT = 457.6e6 / 359
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -226,7 +229,10 @@ def run_ours(args):
     layer_bytes = (U + 1) * (GGUF_EXPERT_GATE_UP + GGUF_EXPERT_DOWN) + T * (CHANNELS * 2 * 2) + T * EXPERTS * 4
     achieved = gu_bytes / (stages["gate_up_ms"] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "gemv_kernel<Q4_K, gate-up+SwiGLU> (routed experts)", "achieved": achieved, "peak": hbm_peak,
-                "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (359 experts hit: 457.6 MB) scaled to the
+                # experts this run's batches hit; traffic grows with the experts touched, the activations stay in L2
+                "traffic": NCU_GATE_UP_DRAM_BYTES_PER_EXPERT * U, "traffic_source": "ncu capture scaled by experts hit",
                 "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": stages["gate_up_ms"]}
 
     # CPU baseline on the same first layer and batch 0, and an in-run parity figure

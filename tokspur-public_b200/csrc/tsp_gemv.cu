@@ -482,9 +482,9 @@ static int launch_one(const GemvParams& p, size_t smem, int grid, cudaStream_t s
 int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const float* x, uint64_t x_stride_bytes,
                 uint32_t in_div, uint32_t tokens, const uint32_t* token_map, const uint32_t* counts, const uint32_t* tasks,
                 float* out, uint64_t out_stride_bytes, int f16_exact, int nc, uint32_t* error, cudaStream_t st, const GemvShared* shared) {
-    // `shared` (an extra dense expert in the same launch) is served by the tensor-copy pipeline only: return 1 = not done
+    // `shared` (an extra dense expert in the same launch) is served by the second-generation pipeline only: return 1 = not done
     if (shared && a->type != TSP_TYPE_Q4_K) return 1;
-    if (a->type == TSP_TYPE_Q4_K) {   // the tensor-copy pipeline covers Q4_K; shapes it declines (return 1) fall through
+    if (a->type == TSP_TYPE_Q4_K) {   // the second-generation pipeline covers Q4_K; shapes it declines (return 1) fall through
         const int rc = launch_gemv_q4k_tma(a, b, gateup, x, x_stride_bytes, in_div, tokens, token_map, counts, tasks, out,
                                            out_stride_bytes, f16_exact, nc, error, st, shared);
         if (rc <= 0 || shared) return rc;

@@ -225,14 +225,15 @@ def run_ours(args):
 
     hbm_peak, _, peak_kind = peaks()
     U = stages["unique_experts"]
-    gu_bytes = U * GGUF_EXPERT_GATE_UP + T * CHANNELS * 4 + T * SELECTED * HIDDEN * 4
+    # the launch covers the routed experts that were hit plus the shared expert; activations in (binary16), hidden rows out (FP32)
+    gu_bytes = (U + 1) * GGUF_EXPERT_GATE_UP + T * CHANNELS * 2 + T * (SELECTED + 1) * HIDDEN * 4
     layer_bytes = (U + 1) * (GGUF_EXPERT_GATE_UP + GGUF_EXPERT_DOWN) + T * (CHANNELS * 2 * 2) + T * EXPERTS * 4
     achieved = gu_bytes / (stages["gate_up_ms"] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel<Q4_K, gate-up+SwiGLU> (routed experts)", "achieved": achieved, "peak": hbm_peak,
+    roofline = {"bound": "hbm", "kernel": "gemv3_kernel<planar, gate-up+SwiGLU> (routed experts + shared expert, one launch)", "achieved": achieved, "peak": hbm_peak,
                 "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (359 experts hit: 457.6 MB) scaled to the
                 # experts this run's batches hit; traffic grows with the experts touched, the activations stay in L2
-                "traffic": NCU_GATE_UP_DRAM_BYTES_PER_EXPERT * U, "traffic_source": "ncu capture scaled by experts hit",
+                "traffic": NCU_GATE_UP_DRAM_BYTES_PER_EXPERT * (U + 1), "traffic_source": "ncu capture scaled by experts hit",
                 "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": stages["gate_up_ms"]}
 
     # CPU baseline on the same first layer and batch 0, and an in-run parity figure
@@ -405,7 +406,7 @@ def stage_times(L, capi, layers, s, dev_x, dev_lg, out, steps, warmup, T):
     import torch
     lib = capi.lib()
     st = L.stream_ptr()
-    names = ["convert", "route", "permute", "gate_up", "down", "shared_gate_up", "shared_down", "combine"]
+    names = ["convert", "route", "permute", "gate_up", "down", "combine"]
     acc = {n: 0.0 for n in names}
     uniq = 0.0
     C4, H4 = CHANNELS * 4, HIDDEN * 4
@@ -419,17 +420,17 @@ def stage_times(L, capi, layers, s, dev_x, dev_lg, out, steps, warmup, T):
         capi.check(lib.tsp_moe_route(lg.data_ptr(), EXPERTS * 4, T, EXPERTS, SELECTED, 0, 1, s.ids.data_ptr(), s.weights.data_ptr(), e, st)); ev[2].record()
         capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, EXPERTS, SELECTED, capi.GEMV_TILE, s.token_map.data_ptr(), s.counts.data_ptr(),
                                        s.tasks.data_ptr(), e, st)); ev[3].record()
-        capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.gate), C.byref(w.up), s.x32.data_ptr(), C4, T, SELECTED, s.token_map.data_ptr(),
-                                              s.counts.data_ptr(), s.tasks.data_ptr(), s.hidden.data_ptr(), H4, 1, e, st)); ev[4].record()
-        capi.check(lib.tsp_moe_project(C.byref(w.down), s.hidden.data_ptr(), H4, 1, T, SELECTED, s.token_map.data_ptr(), s.counts.data_ptr(),
-                                       s.tasks.data_ptr(), s.routed.data_ptr(), C4, 0, e, st)); ev[5].record()
-        capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.shared_gate), C.byref(w.shared_up), s.x32.data_ptr(), C4, T, 1, None, None, None,
-                                              s.shared_hidden.data_ptr(), H4, 1, e, st)); ev[6].record()
-        capi.check(lib.tsp_moe_project(C.byref(w.shared_down), s.shared_hidden.data_ptr(), H4, 1, T, 1, None, None, None,
-                                       s.shared_out.data_ptr(), C4, 0, e, st)); ev[7].record()
+        # the routed experts and the shared expert in one launch each, exactly as tsp_moe_layer_decode issues them
+        capi.check(lib.tsp_moe_gate_up_swiglu_shared(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up),
+                                                     s.x32.data_ptr(), C4, x.data_ptr(), CHANNELS * 2, T, SELECTED, s.token_map.data_ptr(),
+                                                     s.counts.data_ptr(), s.tasks.data_ptr(), s.hidden.data_ptr(), H4,
+                                                     s.shared_hidden.data_ptr(), H4, 1, e, st)); ev[4].record()
+        capi.check(lib.tsp_moe_project_shared(C.byref(w.down), C.byref(w.shared_down), s.hidden.data_ptr(), H4, s.shared_hidden.data_ptr(), H4,
+                                              T, SELECTED, s.token_map.data_ptr(), s.counts.data_ptr(), s.tasks.data_ptr(),
+                                              s.routed.data_ptr(), C4, s.shared_out.data_ptr(), C4, e, st)); ev[5].record()
         capi.check(lib.tsp_moe_combine(s.routed.data_ptr(), C4, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
                                        s.x32.data_ptr(), C4, s.shared_logit.data_ptr(), T, CHANNELS, SELECTED, None, 0, out.data_ptr(),
-                                       CHANNELS * 2, e, st)); ev[8].record()
+                                       CHANNELS * 2, e, st)); ev[6].record()
         torch.cuda.synchronize()
         if i >= warmup:
             for k, n in enumerate(names):

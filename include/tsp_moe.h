@@ -142,6 +142,24 @@ int tsp_moe_project(const tsp_matrix_set* w, const float* d_in, uint64_t in_stri
                     float* d_out, uint64_t out_stride_bytes, int in_is_f16_exact,
                     uint32_t* d_error, void* stream);
 
+/* The two projections above for the routed experts AND the layer's dense shared expert in one launch each, as the decode
+ * layer runs them: `encode_moe` issues the routed projections (moe.cpp:62-68) and the shared expert's `gemv`s
+ * (moe.cpp:70-77) back to back on the same input rows. When the shared expert has the routed experts' shape, encoding
+ * and layout (Q4_K), its token tiles are appended to the routed tiles of the same launch; otherwise these entries fall
+ * back to two launches.
+ * d_x16 (optional, may be NULL): the same token rows as binary16, [tokens x channels]; used instead of d_x when
+ * x_is_f16_exact is set, so that staging the rows needs no conversion.
+ * d_shared_h: FP32 rows [tokens x hidden]; d_shared_in / d_shared_out: the shared expert's hidden rows and output rows. */
+int tsp_moe_gate_up_swiglu_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                                  const tsp_matrix_set* shared_up, const float* d_x, uint64_t x_stride_bytes, const void* d_x16,
+                                  uint64_t x16_stride_bytes, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                                  const uint32_t* d_counts, const uint32_t* d_tasks, float* d_h, uint64_t h_stride_bytes,
+                                  float* d_shared_h, uint64_t shared_h_stride_bytes, int x_is_f16_exact, uint32_t* d_error, void* stream);
+int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared_w, const float* d_in, uint64_t in_stride_bytes,
+                           const float* d_shared_in, uint64_t shared_in_stride_bytes, uint32_t tokens, uint32_t selected,
+                           const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, float* d_out,
+                           uint64_t out_stride_bytes, float* d_shared_out, uint64_t shared_out_stride_bytes, uint32_t* d_error, void* stream);
+
 /* Replaces `gemv(shared_router, rows=1)` + `mixture` / `prefill_mixture_batch` (moe.cpp:79-81,
  * graph.mm:8023,5975; CPU mixture_reference, routing.cpp:42-61):
  *   out[t][c] = sigmoid(s_t) * shared[t][c] + sum_{r<selected} w[t][r] * routed[t*selected+r][c]

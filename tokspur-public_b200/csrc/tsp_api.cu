@@ -281,6 +281,58 @@ int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride, float* d_out, uint
     return launch_f16_to_f32(d_in, in_stride, d_out, out_stride, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
+// Routed experts and the layer's dense shared expert in one launch when the shared expert looks like a routed one (same
+// shape, encoding and layout, Q4_K); otherwise the shared expert gets a launch of its own.
+int tsp_moe_gate_up_swiglu_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                                  const tsp_matrix_set* shared_up, const float* d_x, uint64_t x_stride, const void* d_x16,
+                                  uint64_t x16_stride, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                                  const uint32_t* d_counts, const uint32_t* d_tasks, float* d_h, uint64_t h_stride, float* d_shared_h,
+                                  uint64_t shared_h_stride, int x_is_f16_exact, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(gate && up && shared_gate && shared_up && d_token_map && d_counts && d_tasks && d_shared_h, "gate-up with shared expert: null argument");
+    const bool same_shape = shared_gate->type == gate->type && shared_gate->layout == gate->layout && shared_up->type == gate->type &&
+                            shared_up->layout == gate->layout && shared_gate->rows == gate->rows && shared_gate->cols == gate->cols &&
+                            shared_up->rows == gate->rows && shared_up->cols == gate->cols && shared_gate->experts == 1 && shared_up->experts == 1;
+    if (same_shape && check_matrix(gate, "gate") == TSP_OK && check_matrix(up, "up") == TSP_OK && check_matrix(shared_gate, "shared gate") == TSP_OK &&
+        check_matrix(shared_up, "shared up") == TSP_OK && gate->type == up->type && gate->layout == up->layout && up->rows == gate->rows &&
+        up->cols == gate->cols && up->experts == gate->experts && gate->expert_stride == up->expert_stride && gate->split == up->split &&
+        tokens >= 1 && selected >= 1 && selected <= 64 && check_rows(d_x, x_stride, gate->cols, 4, "gate-up input") == TSP_OK &&
+        check_rows(d_h, h_stride, gate->rows, 4, "gate-up output") == TSP_OK &&
+        check_rows(d_shared_h, shared_h_stride, gate->rows, 4, "shared gate-up output") == TSP_OK && aligned16(d_x) && x_stride % 16 == 0 &&
+        (!d_x16 || check_rows(d_x16, x16_stride, gate->cols, 2, "binary16 input") == TSP_OK)) {
+        GemvShared sh{shared_gate, shared_up, d_x, x_stride, d_shared_h, shared_h_stride};
+        if (d_x16 && x_is_f16_exact) { sh.x16 = d_x16; sh.x16_stride_bytes = x16_stride; }   // the binary16 rows themselves: staged without conversion
+        const int rc = launch_gemv(gate, up, true, d_x, x_stride, selected, tokens, d_token_map, d_counts, d_tasks, d_h, h_stride,
+                                   x_is_f16_exact, 1, d_error, static_cast<cudaStream_t>(stream), &sh);
+        if (rc <= 0) return rc;
+    }
+    if (int rc = tsp_moe_gate_up_swiglu(gate, up, d_x, x_stride, tokens, selected, d_token_map, d_counts, d_tasks, d_h, h_stride, x_is_f16_exact,
+                                        d_error, stream)) return rc;
+    return tsp_moe_gate_up_swiglu(shared_gate, shared_up, d_x, x_stride, tokens, 1, nullptr, nullptr, nullptr, d_shared_h, shared_h_stride,
+                                  x_is_f16_exact, d_error, stream);
+}
+
+int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared_w, const float* d_in, uint64_t in_stride,
+                           const float* d_shared_in, uint64_t shared_in_stride, uint32_t tokens, uint32_t selected,
+                           const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, float* d_out, uint64_t out_stride,
+                           float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(w && shared_w && d_token_map && d_counts && d_tasks && d_shared_in && d_shared_out, "project with shared expert: null argument");
+    const bool same_shape = shared_w->type == w->type && shared_w->layout == w->layout && shared_w->rows == w->rows && shared_w->cols == w->cols &&
+                            shared_w->experts == 1;
+    if (same_shape && w->rows % 16 == 0 && check_matrix(w, "project") == TSP_OK && check_matrix(shared_w, "shared project") == TSP_OK &&
+        tokens >= 1 && selected >= 1 && selected <= 64 && check_rows(d_in, in_stride, w->cols, 4, "project input") == TSP_OK &&
+        check_rows(d_shared_in, shared_in_stride, w->cols, 4, "shared project input") == TSP_OK &&
+        check_rows(d_out, out_stride, w->rows, 4, "project output") == TSP_OK &&
+        check_rows(d_shared_out, shared_out_stride, w->rows, 4, "shared project output") == TSP_OK) {
+        const GemvShared sh{shared_w, nullptr, d_shared_in, shared_in_stride, d_shared_out, shared_out_stride};
+        const int rc = launch_gemv(w, nullptr, false, d_in, in_stride, 1, tokens, d_token_map, d_counts, d_tasks, d_out, out_stride, 0, 1, d_error,
+                                   static_cast<cudaStream_t>(stream), &sh);
+        if (rc <= 0) return rc;
+    }
+    if (int rc = tsp_moe_project(w, d_in, in_stride, 1, tokens, selected, d_token_map, d_counts, d_tasks, d_out, out_stride, 0, d_error, stream)) return rc;
+    return tsp_moe_project(shared_w, d_shared_in, shared_in_stride, 1, tokens, 1, nullptr, nullptr, nullptr, d_shared_out, shared_out_stride, 0,
+                           d_error, stream);
+}
+
 int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, const void* d_x, uint64_t x_stride,
                          uint32_t x_dtype, const float* d_logits, uint64_t logits_stride, uint32_t tokens,
                          uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected, uint32_t mode,
@@ -307,43 +359,12 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
     const int exact = x_dtype == 1;
     if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
     if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GEMV_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
-    // Routed and shared experts in one launch each when the shared expert looks like a routed one (same shape, encoding and
-    // layout, Q4_K); otherwise (launch_gemv answers 1) the shared expert gets its own two launches.
-    bool fused_gate_up = false, fused_down = false;
-    const bool same_shape = w->shared_gate.type == w->gate.type && w->shared_gate.layout == w->gate.layout &&
-                            w->shared_up.type == w->gate.type && w->shared_up.layout == w->gate.layout &&
-                            w->shared_up.rows == hidden && w->shared_up.cols == channels &&
-                            w->shared_down.type == w->down.type && w->shared_down.layout == w->down.layout;
-    if (same_shape && check_matrix(&w->gate, "gate") == TSP_OK && check_matrix(&w->up, "up") == TSP_OK &&
-        check_matrix(&w->shared_gate, "shared gate") == TSP_OK && check_matrix(&w->shared_up, "shared up") == TSP_OK &&
-        w->gate.type == w->up.type && w->gate.layout == w->up.layout && w->up.rows == hidden && w->up.cols == channels &&
-        w->up.experts == experts && w->gate.expert_stride == w->up.expert_stride && w->gate.split == w->up.split &&
-        aligned16(x32) && x32_stride % 16 == 0) {
-        const GemvShared sh{&w->shared_gate, &w->shared_up, x32, x32_stride, s->d_shared_hidden, hidden * 4ull};
-        const int rc = launch_gemv(&w->gate, &w->up, true, x32, x32_stride, selected, tokens, s->d_token_map, s->d_counts, s->d_tasks,
-                                   s->d_hidden, hidden * 4ull, exact, 1, d_error, st, &sh);
-        if (rc < 0) return rc;
-        fused_gate_up = rc == 0;
-    }
-    if (!fused_gate_up) {
-        if (int rc = tsp_moe_gate_up_swiglu(&w->gate, &w->up, x32, x32_stride, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
-                                            s->d_hidden, hidden * 4ull, exact, d_error, st)) return rc;
-        if (int rc = tsp_moe_gate_up_swiglu(&w->shared_gate, &w->shared_up, x32, x32_stride, tokens, 1, nullptr, nullptr, nullptr,
-                                            s->d_shared_hidden, hidden * 4ull, exact, d_error, st)) return rc;
-    }
-    if (same_shape && channels % 16 == 0 && check_matrix(&w->down, "down") == TSP_OK && check_matrix(&w->shared_down, "shared down") == TSP_OK) {
-        const GemvShared sh{&w->shared_down, nullptr, s->d_shared_hidden, hidden * 4ull, s->d_shared_out, channels * 4ull};
-        const int rc = launch_gemv(&w->down, nullptr, false, s->d_hidden, hidden * 4ull, 1, tokens, s->d_token_map, s->d_counts, s->d_tasks,
-                                   s->d_routed, channels * 4ull, 0, 1, d_error, st, &sh);
-        if (rc < 0) return rc;
-        fused_down = rc == 0;
-    }
-    if (!fused_down) {
-        if (int rc = tsp_moe_project(&w->down, s->d_hidden, hidden * 4ull, 1, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
-                                     s->d_routed, channels * 4ull, 0, d_error, st)) return rc;
-        if (int rc = tsp_moe_project(&w->shared_down, s->d_shared_hidden, hidden * 4ull, 1, tokens, 1, nullptr, nullptr, nullptr,
-                                     s->d_shared_out, channels * 4ull, 0, d_error, st)) return rc;
-    }
+    if (int rc = tsp_moe_gate_up_swiglu_shared(&w->gate, &w->up, &w->shared_gate, &w->shared_up, x32, x32_stride, x_dtype == 1 ? d_x : nullptr,
+                                               x_dtype == 1 ? x_stride : 0, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks, s->d_hidden,
+                                               hidden * 4ull, s->d_shared_hidden, hidden * 4ull, exact, d_error, stream)) return rc;
+    if (int rc = tsp_moe_project_shared(&w->down, &w->shared_down, s->d_hidden, hidden * 4ull, s->d_shared_hidden, hidden * 4ull, tokens, selected,
+                                        s->d_token_map, s->d_counts, s->d_tasks, s->d_routed, channels * 4ull, s->d_shared_out, channels * 4ull,
+                                        d_error, stream)) return rc;
     // binary16 output rows are written straight from the FP32 mixture; no FP32 copy of the output is kept
     return tsp_moe_combine(s->d_routed, channels * 4ull, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32,
                            x32_stride, s->d_shared_logit, tokens, channels, selected,

@@ -25,6 +25,8 @@ struct GemvShared {
     const tsp_matrix_set* a; const tsp_matrix_set* b;
     const float* x; uint64_t x_stride_bytes;
     float* out; uint64_t out_stride_bytes;
+    // optional: the token rows as binary16 (exactly the values of `x`); both the routed and the dense tiles then read these
+    const void* x16 = nullptr; uint64_t x16_stride_bytes = 0;
 };
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

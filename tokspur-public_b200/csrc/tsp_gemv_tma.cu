@@ -60,6 +60,7 @@ struct Gemv3Params {
     uint32_t off_xhi, off_xlo, off_sx, off_warp;
     uint32_t x_stride, sx_stride;
     const float* x; uint64_t x_stride_bytes; uint32_t in_div;
+    const uint8_t* x16; uint64_t x16_stride_bytes;   // optional binary16 copy of the token rows (routed and shared tiles read it instead)
     const uint32_t* token_map; const uint32_t* counts; const uint32_t* tasks;
     uint32_t tokens;
     float* out; uint64_t out_stride_bytes;
@@ -263,6 +264,15 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
     const uint32_t sxlane = g * p.sx_stride + t * 4;
     const uint32_t mn_shift = 16 * (t & 1);
 
+    // Activation chunks of the CTA's NEXT token tile, loaded into registers while the current tile is computed, so that
+    // the tile change pays no global-load latency (PF chunks per thread: enough for 2 token rows of 2048 columns).
+    // Only the binary16 source is fetched ahead (16 bytes per chunk).
+    constexpr int PF = 2;
+    uint4 pf[PF];
+    uint32_t pf_tile = 0xffffffffu;
+#pragma unroll
+    for (int i = 0; i < PF; ++i) pf[i] = make_uint4(0, 0, 0, 0);
+
     uint32_t my_it = item0 + warp;                  // this ring's next item
     uint32_t my_grp = (item0 + warp) % p.groups;    // its row group
     uint32_t cs = 0, cph = 0, ch = 0;               // stage, phase and header buffer of this ring's next unit / item
@@ -291,63 +301,140 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
             const uint32_t per_row = p.cols / 8;
             const uint32_t units = ti.count * per_row;
             const bool sh_tile = ti.expert >= p.experts;
-            const char* xsrc = sh_tile ? reinterpret_cast<const char*>(p.sh_x) : reinterpret_cast<const char*>(p.x);
-            const uint64_t xsrc_stride = sh_tile ? p.sh_x_stride_bytes : p.x_stride_bytes;
             bool bad = false;
-            for (uint32_t base = 0; base < units; base += 4 * CT) {
-                float4 va[4], vb[4];
-                uint32_t jj[4], kk[4];
+            if (p.x16) {
+                // binary16 rows: no conversion, only the reordering inside each run of 8 and the group sums; the first PF
+                // chunks of a thread were fetched ahead while the previous tile was computed
+                const bool fetched = pf_tile == tile;
+                for (uint32_t base = 0; base < units; base += 4 * CT) {
+                    uint4 vv[4];
+                    uint32_t jj[4], kk[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t u = base + i * CT + ctid;
-                    jj[i] = 0xffffffffu; kk[i] = 0;
-                    va[i] = vb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (u < units) {
-                        jj[i] = u / per_row; kk[i] = u - jj[i] * per_row;
-                        const float4* src = reinterpret_cast<const float4*>(xsrc + cur_rins[jj[i]] * xsrc_stride) + kk[i] * 2;
-                        va[i] = src[0]; vb[i] = src[1];
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t u = base + i * CT + ctid;
+                        jj[i] = 0xffffffffu; kk[i] = 0;
+                        vv[i] = make_uint4(0, 0, 0, 0);
+                        if (u < units) {
+                            jj[i] = u / per_row; kk[i] = u - jj[i] * per_row;
+                            if (i < PF && base == 0 && fetched) vv[i] = pf[i < PF ? i : 0];
+                            else vv[i] = *(reinterpret_cast<const uint4*>(p.x16 + cur_rins[jj[i]] * p.x16_stride_bytes) + kk[i]);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (base + i * CT >= units) break;   // uniform: no thread has work in this slot
+                        const bool active = jj[i] != 0xffffffffu;
+                        const uint32_t j = jj[i], k8 = kk[i];
+                        const uint32_t w[4] = {vv[i].x, vv[i].y, vv[i].z, vv[i].w};
+                        float s = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                            s += f.x + f.y;
+                            bad |= (w[e] & 0x7c00u) == 0x7c00u || (w[e] & 0x7c000000u) == 0x7c000000u;
+                        }
+                        if (active) {
+                            // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
+                            *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) =
+                                make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[0], w[1], 0x7632), __byte_perm(w[2], w[3], 0x5410), __byte_perm(w[2], w[3], 0x7632));
+                            if (SPLIT) *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) = make_uint4(0, 0, 0, 0);
+                        }
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        if (active && (k8 & 3u) == 0) {
+                            const uint32_t grp = k8 >> 2;
+                            const __half sh = __float2half_rn(s);
+                            const __half sl = __float2half_rn(s - __half2float(sh));
+                            bad |= !finite_f32(__half2float(sh));
+                            *reinterpret_cast<__half*>(sxb + j * p.sx_stride + grp * 2) = sh;
+                            *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
+                        }
                     }
                 }
+                // fetch ahead for the next tile of this CTA (its routing data must be in the cached window)
+                pf_tile = 0xffffffffu;
+                if (seg_end < item1 && tile + 1 - t0 < kTableTiles) {
+                    const Tile3 tn = get_tile(tile + 1);
+                    const uint32_t* nrins = tin + (tile + 1 - t0) * 16;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    if (base + i * CT >= units) break;   // uniform: no thread has work in this slot
-                    const bool active = jj[i] != 0xffffffffu;
-                    const uint32_t j = jj[i], k8 = kk[i];
-                    const float v[8] = {va[i].x, va[i].y, va[i].z, va[i].w, vb[i].x, vb[i].y, vb[i].z, vb[i].w};
-                    float s = 0.f;
-                    uint32_t hb[8], lb[8];
+                    for (int i = 0; i < PF; ++i) {
+                        const uint32_t u = i * CT + ctid;
+                        if (u < tn.count * per_row) {
+                            const uint32_t jn = u / per_row, kn = u - jn * per_row;
+                            pf[i] = *(reinterpret_cast<const uint4*>(p.x16 + nrins[jn] * p.x16_stride_bytes) + kn);
+                        }
+                    }
+                    pf_tile = tile + 1;
+                }
+            } else {
+                const char* xsrc = sh_tile ? reinterpret_cast<const char*>(p.sh_x) : reinterpret_cast<const char*>(p.x);
+                const uint64_t xsrc_stride = sh_tile ? p.sh_x_stride_bytes : p.x_stride_bytes;
+                for (uint32_t base = 0; base < units; base += 4 * CT) {
+                    float4 va[4], vb[4];
+                    uint32_t jj[4], kk[4];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const __half h = __float2half_rn(v[e]);
-                        const float hf = __half2float(h);
-                        bad |= !finite_f32(hf);
-                        hb[e] = __half_as_ushort(h);
-                        lb[e] = __half_as_ushort(__float2half_rn(v[e] - hf));
-                        s += v[e];
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t u = base + i * CT + ctid;
+                        jj[i] = 0xffffffffu; kk[i] = 0;
+                        va[i] = vb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (u < units) {
+                            jj[i] = u / per_row; kk[i] = u - jj[i] * per_row;
+                            const float4* src = reinterpret_cast<const float4*>(xsrc + cur_rins[jj[i]] * xsrc_stride) + kk[i] * 2;
+                            va[i] = src[0]; vb[i] = src[1];
+                        }
                     }
-                    if (active) {
-                        // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
-                        *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) =
-                            make_uint4(hb[0] | (hb[2] << 16), hb[1] | (hb[3] << 16), hb[4] | (hb[6] << 16), hb[5] | (hb[7] << 16));
-                        if (SPLIT)
-                            *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) =
-                                make_uint4(lb[0] | (lb[2] << 16), lb[1] | (lb[3] << 16), lb[4] | (lb[6] << 16), lb[5] | (lb[7] << 16));
-                    }
-                    s += __shfl_xor_sync(0xffffffffu, s, 1);
-                    s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    if (active && (k8 & 3u) == 0) {
-                        const uint32_t grp = k8 >> 2;
-                        const __half sh = __float2half_rn(s);
-                        const __half sl = __float2half_rn(s - __half2float(sh));
-                        bad |= !finite_f32(__half2float(sh));
-                        *reinterpret_cast<__half*>(sxb + j * p.sx_stride + grp * 2) = sh;
-                        *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (base + i * CT >= units) break;   // uniform: no thread has work in this slot
+                        const bool active = jj[i] != 0xffffffffu;
+                        const uint32_t j = jj[i], k8 = kk[i];
+                        const float v[8] = {va[i].x, va[i].y, va[i].z, va[i].w, vb[i].x, vb[i].y, vb[i].z, vb[i].w};
+                        float s = 0.f;
+                        uint32_t hb[8], lb[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const __half h = __float2half_rn(v[e]);
+                            const float hf = __half2float(h);
+                            bad |= !finite_f32(hf);
+                            hb[e] = __half_as_ushort(h);
+                            lb[e] = __half_as_ushort(__float2half_rn(v[e] - hf));
+                            s += v[e];
+                        }
+                        if (active) {
+                            // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
+                            *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) =
+                                make_uint4(hb[0] | (hb[2] << 16), hb[1] | (hb[3] << 16), hb[4] | (hb[6] << 16), hb[5] | (hb[7] << 16));
+                            if (SPLIT)
+                                *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) =
+                                    make_uint4(lb[0] | (lb[2] << 16), lb[1] | (lb[3] << 16), lb[4] | (lb[6] << 16), lb[5] | (lb[7] << 16));
+                        }
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        if (active && (k8 & 3u) == 0) {
+                            const uint32_t grp = k8 >> 2;
+                            const __half sh = __float2half_rn(s);
+                            const __half sl = __float2half_rn(s - __half2float(sh));
+                            bad |= !finite_f32(__half2float(sh));
+                            *reinterpret_cast<__half*>(sxb + j * p.sx_stride + grp * 2) = sh;
+                            *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
+                        }
                     }
                 }
             }
             if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
         }
         named_bar_sync(1, CT);
+        // this lane's output rows (tokens 2t, 2t+1 of each column block) for the whole tile
+        float* orow[NC][2];
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const uint32_t j = c * 8 + 2 * t + q;
+                orow[c][q] = j >= ti.count ? nullptr
+                             : reinterpret_cast<float*>(ti.expert >= p.experts ? reinterpret_cast<char*>(p.sh_out) + cur_rids[j] * p.sh_out_stride_bytes
+                                                                               : reinterpret_cast<char*>(p.out) + cur_rids[j] * p.out_stride_bytes);
+            }
 
         // ---- this warp's row groups of the segment ----
         for (; my_it < seg_end; my_it += kW3) {
@@ -483,21 +570,15 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                     for (int c = 0; c < NC; ++c)
 #pragma unroll
                         for (int q = 0; q < 2; ++q) {
-                            const uint32_t j = c * 8 + 2 * t + q;
-                            if (j >= ti.count) continue;
-                            float* orow = reinterpret_cast<float*>(ti.expert >= p.experts ? reinterpret_cast<char*>(p.sh_out) + cur_rids[j] * p.sh_out_stride_bytes
-                                                                                          : reinterpret_cast<char*>(p.out) + cur_rids[j] * p.out_stride_bytes);
+                            float* o = orow[c][q];
                             if (GATEUP) {
-                                const uint32_t hu = r0 + n * 8 + g;
-                                if (hu < p.rows) {
-                                    const float v = fast_silu(total[n][c][q]) * total[n][c][2 + q];
-                                    bad |= !finite_f32(v);
-                                    orow[hu] = v;
-                                }
-                            } else {
+                                const float v = fast_silu(total[n][c][q]) * total[n][c][2 + q];
+                                if (o) { bad |= !finite_f32(v); o[r0 + n * 8 + g] = v; }
+                            } else if (o) {
                                 const uint32_t r = r0 + n * 16 + g;
-                                if (r < p.rows) { bad |= !finite_f32(total[n][c][q]); orow[r] = total[n][c][q]; }
-                                if (r + 8 < p.rows) { bad |= !finite_f32(total[n][c][2 + q]); orow[r + 8] = total[n][c][2 + q]; }
+                                bad |= !finite_f32(total[n][c][q]) | !finite_f32(total[n][c][2 + q]);
+                                o[r] = total[n][c][q];
+                                o[r + 8] = total[n][c][2 + q];
                             }
                         }
                 if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
@@ -579,7 +660,7 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     const uint32_t nt = (!gateup && nblk <= 2 && a->rows % 32 == 0) ? 2 : 1;
     const uint32_t R = (gateup ? 8 : 16) * nt;
     const uint32_t nmat = gateup ? 2 : 1;
-    const uint32_t kb = (nblk % 2 == 0 && nblk >= 4) ? 2 : 1;
+    const uint32_t kb = (nblk % 4 == 0 && nblk >= 8) ? 4 : (nblk % 2 == 0 && nblk >= 4) ? 2 : 1;
     if (R * nblk > 2048) return 1;   // header boxes are limited to 256 lines
     p.upi = nblk / kb;
     p.groups = a->rows / R;
@@ -656,6 +737,9 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
         p.sh_tiles = (tokens + 7) / 8;
         p.sh_x = shared->x; p.sh_x_stride_bytes = shared->x_stride_bytes;
         p.sh_out = shared->out; p.sh_out_stride_bytes = shared->out_stride_bytes;
+        if (shared->x16 && f16_exact && reinterpret_cast<uintptr_t>(shared->x16) % 16 == 0 && shared->x16_stride_bytes % 16 == 0) {
+            p.x16 = static_cast<const uint8_t*>(shared->x16); p.x16_stride_bytes = shared->x16_stride_bytes;
+        }
         const uint8_t* sa = static_cast<const uint8_t*>(shared->a->base);
         const uint8_t* sb = gateup ? static_cast<const uint8_t*>(shared->b->base) : nullptr;
         if (reinterpret_cast<uintptr_t>(sa) % 16 || reinterpret_cast<uintptr_t>(sb) % 16) return 1;
@@ -672,7 +756,7 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     return split_lo ? launch3<L, G, NCV, NTV, K, true>(maps, p, smem, grid, st)    \
                     : launch3<L, G, NCV, NTV, K, false>(maps, p, smem, grid, st)
 #define TSP_D3(L, G, NCV, NTV)                                                     \
-    do { if (kb == 2) { TSP_D4(L, G, NCV, NTV, 2); } else { TSP_D4(L, G, NCV, NTV, 1); } } while (0)
+    do { if (kb == 4) { TSP_D4(L, G, NCV, NTV, 4); } else if (kb == 2) { TSP_D4(L, G, NCV, NTV, 2); } else { TSP_D4(L, G, NCV, NTV, 1); } } while (0)
 #define TSP_D2(L)                                                                  \
     if (a->layout == L) {                                                          \
         if (gateup) { if (nc == 1) TSP_D3(L, true, 1, 1); TSP_D3(L, true, 2, 1); } \

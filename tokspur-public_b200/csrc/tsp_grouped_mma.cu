@@ -7,12 +7,14 @@
 // tokens), the tokens as the N operand (32, 64 or 128 columns) and K walked in chunks of 64.
 //
 // Roles inside a CTA (one persistent CTA per SM):
-//   warp 0      TMA producer: Pack v3 planar code boxes + scale planes of one super-block (256 columns of K) per
-//               quant stage; the activation tile (tokens x 64 binary16, 128-byte swizzled) of every K chunk.
+//   warp 0      TMA producer of the quantised planes: Pack v3 planar code boxes + 6-bit factor boxes of one super-block
+//               (256 columns of K) per quant stage, gate and up in one copy each; the (d, dmin) pairs once per item.
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers.
-//   warps 2..5  dequantise: read 4-bit codes + 6-bit factors from the quant stage, write binary16 weights in the
-//               K-major 128-byte-swizzled operand layout; after the last K chunk the same four warps are the epilogue
-//               (tcgen05.ld of their 32 accumulator lanes, SwiGLU / store).
+//   warps 2..9  dequantise (two warps per SM sub-partition, a thread per half row of a K chunk): read 4-bit codes +
+//               6-bit factors from the quant stage, write binary16 weights in the K-major 128-byte-swizzled operand layout.
+//   warp 10     TMA producer of the activation tiles (tokens x 64 binary16, 128-byte swizzled) of every K chunk.
+//   warps 11..14 epilogue: tcgen05.ld of their 32 accumulator lanes, SwiGLU / store. The accumulators are double-buffered
+//               in tensor memory (2 x 256 columns), so the epilogue of an item runs under the MMAs of the next one.
 // Accumulation is FP32 in tensor memory. Operands are binary16 (kind::f16, f16 inputs): the activations of this path are
 // binary16-exact, and Q4_K values keep 11 significant bits instead of bf16's 8, which keeps the two chained GEMMs well
 // inside the 2e-3 relative-L2 bar that bf16 operands would only just meet.
@@ -58,6 +60,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr));
 }
+// 32 lanes x 32 consecutive columns -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -82,21 +93,24 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-constexpr uint32_t kGWarps = 7;            // weight producer, MMA, 4 x dequant/epilogue, activation producer
+constexpr uint32_t kDqWarps = 8;           // dequantise warps: two per SM sub-partition, each thread half a row of a K chunk
+constexpr uint32_t kEpWarps = 4;           // epilogue warps: one per tensor-memory lane quarter
+constexpr uint32_t kGWarps = 3 + kDqWarps + kEpWarps; // weight producer, MMA, dequant warps, activation producer, epilogue warps
 constexpr uint32_t kMaxBStages = 8;
 constexpr uint32_t kGThreads = kGWarps * 32;
 constexpr uint32_t kTileRoutes = 128;      // routes per tile (N extent at most)
 constexpr uint32_t kRowsM = 128;           // weight rows per CTA tile (M)
 constexpr uint32_t kChunkK = 64;           // K per pipeline step: 64 binary16 = one 128-byte swizzled row
 
+// Tensor maps of one launch: codes (low ids, high ids; second matrix low, high), factors (same four), (d, dmin) pairs (same four),
+// activation tiles of 32 / 64 / 128 token rows.
+struct alignas(64) GroupedMaps { CUtensorMap q[4], f[4], d[4], x[3]; };
+
 struct GroupedParams {
-    // weights: Pack v3 planar Q4_K, addressed as in the decode kernel
-    const uint8_t* base[4];        // A_lo, A_hi, B_lo, B_hi (plane copies)
-    uint64_t expert_stride;
     uint32_t split, experts;
     uint32_t rows, cols, nblk;     // rows of ONE matrix, K, super-blocks per row
-    uint64_t sm_off, dm_off;
     uint32_t row_blocks;           // rows / 128
+    uint32_t merged;               // both matrices of an expert arrive with one copy per plane
     // routes
     const uint32_t* tasks;         // {tiles, routes, (expert, start)...} with tiles of kTileRoutes
     const uint32_t* counts;
@@ -106,9 +120,8 @@ struct GroupedParams {
     void* out; uint64_t out_stride_bytes;
     uint32_t* error;
     // shared-memory plan
-    uint32_t off_q, q_stage_bytes, off_a, off_b, a_tile_bytes, nb_stages;
+    uint32_t off_q, q_stage_bytes, off_d, d_stage_bytes, dm_mat_bytes, off_a, off_b, nb_stages;
 };
-
 
 // bounded wait with a short limit: a stalled pipeline ends in tens of milliseconds, never hangs
 __device__ __forceinline__ bool gwait(uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity, 1u << 21); }
@@ -127,23 +140,24 @@ __device__ __forceinline__ GTile gtile(const GroupedParams& p, uint32_t tile) {
     return t;
 }
 
+__device__ __forceinline__ void tma_load_5d_g(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+                 : "memory");
+}
+
 // GATEUP: two weight matrices (gate, up) and the SwiGLU epilogue writing binary16 hidden rows in permuted position order;
 // otherwise one matrix and FP32 rows scattered to their route ids.
 template <bool GATEUP>
-__global__ void __launch_bounds__(kGThreads, 1)
-grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_constant__ CUtensorMap qmap_a_hi,
-                   const __grid_constant__ CUtensorMap qmap_b_lo, const __grid_constant__ CUtensorMap qmap_b_hi,
-                   const __grid_constant__ CUtensorMap smap_a_lo, const __grid_constant__ CUtensorMap smap_a_hi,
-                   const __grid_constant__ CUtensorMap smap_b_lo, const __grid_constant__ CUtensorMap smap_b_hi,
-                   const __grid_constant__ CUtensorMap xmap32, const __grid_constant__ CUtensorMap xmap64,
-                   const __grid_constant__ CUtensorMap xmap128, const GroupedParams p) {
+__global__ void __launch_bounds__(kGThreads, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
     extern __shared__ uint8_t gsm_raw[];
     uint8_t* gsm = gsm_raw + ((1024u - (smem_u32(gsm_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(gsm);
-    // two rings: dequantised weight tiles (2 stages, filled by the dequant warps) and activation tiles (nb_stages, filled by TMA);
-    // the activation ring is deep because its loads see full memory latency while a weight tile is produced on chip
-    uint64_t *qfull = bars, *qempty = bars + 2, *afull = bars + 4, *aempty = bars + 6, *bfull = bars + 8, *bempty = bars + 8 + kMaxBStages,
-             *acc_full = bars + 8 + 2 * kMaxBStages, *acc_empty = acc_full + 1;
+    // rings: quantised super-blocks (2 stages, TMA), the (d, dmin) pairs of an item (2 stages, TMA), dequantised weight tiles
+    // (2 stages, filled by the dequant warps) and activation tiles (nb_stages, TMA); the activation ring is deep because its
+    // loads see full memory latency while a weight tile is produced on chip
+    uint64_t *qfull = bars, *qempty = bars + 2, *afull = bars + 4, *aempty = bars + 6, *dfull = bars + 8, *dempty = bars + 10,
+             *bfull = bars + 12, *bempty = bars + 12 + kMaxBStages, *acc_full = bars + 12 + 2 * kMaxBStages, *acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gsm + 512);
     const uint32_t NB = p.nb_stages;
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
@@ -151,14 +165,15 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&qfull[s], 1); mbar_init(&qempty[s], 4);
-            mbar_init(&afull[s], 4); mbar_init(&aempty[s], 1);
+            mbar_init(&qfull[s], 1); mbar_init(&qempty[s], kDqWarps);
+            mbar_init(&afull[s], kDqWarps); mbar_init(&aempty[s], 1);
+            mbar_init(&dfull[s], 1); mbar_init(&dempty[s], kDqWarps);
         }
         for (uint32_t s = 0; s < NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], 1); }
-        mbar_init(acc_full, 1); mbar_init(acc_empty, 4);
+        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kEpWarps); }
         mbar_fence_init();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }   // two accumulator sets of 256 columns: the epilogue of an item overlaps the MMAs of the next
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -169,40 +184,43 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
     const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
     const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
     const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64
+    const uint32_t ncopy = (NMAT == 1 || p.merged) ? 1u : NMAT;
 
     if (warp == 0) {
-        // =========================== TMA producer ===========================
+        // =========================== TMA producer of the quantised planes ===========================
         if (lane == 0) {
             bool ok = true;
-            uint32_t qs = 0, qph = 0, cur_tile = 0xffffffffu;
+            uint32_t qs = 0, qph = 0, ds = 0, dph = 0, cur_tile = 0xffffffffu;
             GTile t{};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
                 if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
-                const uint32_t r0 = (item % p.row_blocks) * kRowsM;
+                const int r0 = static_cast<int>((item % p.row_blocks) * kRowsM);
                 const bool hi = t.expert >= p.split;
-                const uint32_t el = hi ? t.expert - p.split : t.expert;
+                const int el = static_cast<int>(hi ? t.expert - p.split : t.expert);
+                // the (d, dmin) pairs of the item's rows over the whole K
+                ok = gwait(&dempty[ds], dph ^ 1u);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&dfull[ds], NMAT * p.dm_mat_bytes);
+                for (uint32_t m = 0; m < ncopy; ++m)
+                    tma_load_4d_g(gsm + p.off_d + ds * p.d_stage_bytes + m * p.dm_mat_bytes, &maps.d[2 * m + (hi ? 1 : 0)], 0,
+                                  static_cast<int>((item % p.row_blocks) * 2 * p.nblk), 0, el, &dfull[ds]);
+                if (++ds == 2) { ds = 0; dph ^= 1u; }
                 for (uint32_t sb = 0; sb < p.nblk && ok; ++sb) {
-                    // quant stage: code boxes, factor boxes and the d/dmin plane rows of this super-block
+                    // quant stage: code boxes and factor boxes of this super-block
                     ok = gwait(&qempty[qs], qph ^ 1u);
                     if (!ok) break;
                     uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
-                    const uint32_t dm_bytes = kRowsM * p.nblk * 4u;
-                    mbar_arrive_expect_tx(&qfull[qs], NMAT * (kRowsM * 128u + kRowsM * 16u + dm_bytes));
-#pragma unroll
-                    for (uint32_t m = 0; m < NMAT; ++m) {
-                        const CUtensorMap* qm = m == 0 ? (hi ? &qmap_a_hi : &qmap_a_lo) : (hi ? &qmap_b_hi : &qmap_b_lo);
-                        const CUtensorMap* sm = m == 0 ? (hi ? &smap_a_hi : &smap_a_lo) : (hi ? &smap_b_hi : &smap_b_lo);
-                        tma_load_4d_g(q + m * 16384u, qm, 0, static_cast<int>(r0), static_cast<int>(sb), static_cast<int>(el), &qfull[qs]);
-                        tma_load_4d_g(q + NMAT * 16384u + m * 2048u, sm, static_cast<int>(sb * 16), static_cast<int>(r0), static_cast<int>(el), 0, &qfull[qs]);
-                        const uint8_t* eb = p.base[m * 2 + (hi ? 1 : 0)] + static_cast<uint64_t>(el) * p.expert_stride;
-                        bulk_g2s(q + NMAT * (16384u + 2048u) + m * dm_bytes, eb + p.dm_off + static_cast<uint64_t>(r0) * p.nblk * 4u, dm_bytes, &qfull[qs]);
+                    mbar_arrive_expect_tx(&qfull[qs], NMAT * (kRowsM * 128u + kRowsM * 16u));
+                    for (uint32_t m = 0; m < ncopy; ++m) {
+                        tma_load_5d_g(q + m * 16384u, &maps.q[2 * m + (hi ? 1 : 0)], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
+                        tma_load_4d_g(q + NMAT * 16384u + m * 2048u, &maps.f[2 * m + (hi ? 1 : 0)], static_cast<int>(sb * 16), r0, 0, el, &qfull[qs]);
                     }
                     if (++qs == 2) { qs = 0; qph ^= 1u; }
                 }
             }
             if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
         }
-    } else if (warp == 6) {
+    } else if (warp == 2 + kDqWarps) {
         // =========================== activation-tile producer ===========================
         if (lane == 0) {
             bool ok = true;
@@ -210,7 +228,7 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
             GTile t{};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
                 if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
-                const CUtensorMap* xmap = t.ncols == 32 ? &xmap32 : (t.ncols == 64 ? &xmap64 : &xmap128);
+                const CUtensorMap* xmap = t.ncols == 32 ? &maps.x[0] : (t.ncols == 64 ? &maps.x[1] : &maps.x[2]);
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
                     ok = gwait(&bempty[bs], bph ^ 1u);
                     if (!ok) break;
@@ -226,12 +244,12 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
         // =========================== MMA issuer ===========================
         if (lane == 0) {
             bool ok = true;
-            uint32_t ms = 0, mph = 0, bs = 0, bph = 0, accph = 0, cur_tile = 0xffffffffu;
+            uint32_t ms = 0, mph = 0, bs = 0, bph = 0, ab = 0, accph = 0, cur_tile = 0xffffffffu;
             GTile t{};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
                 if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
                 const uint32_t idesc = umma_idesc_f16(kRowsM, t.ncols);
-                ok = gwait(acc_empty, accph ^ 1u);   // the epilogue has drained the previous item's accumulators
+                ok = gwait(&acc_empty[ab], accph ^ 1u);   // the epilogue has drained this accumulator set (used two items ago)
                 if (!ok) break;
                 tc_fence_after();
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
@@ -244,30 +262,29 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                         const uint64_t adesc = umma_desc_k128(gsm + p.off_a + ms * NMAT * 16384u + m * 16384u);
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; ++kk)
-                            umma_f16(tmem_base + m * 128u, adesc + kk * 2, bdesc + kk * 2, idesc, (c | kk) != 0 ? 1u : 0u);
+                            umma_f16(tmem_base + ab * 256u + m * 128u, adesc + kk * 2, bdesc + kk * 2, idesc, (c | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(&aempty[ms]);   // both rings' stages are free once the MMAs above have read them
                     umma_commit(&bempty[bs]);
                     if (++ms == 2) { ms = 0; mph ^= 1u; }
                     if (++bs == NB) { bs = 0; bph ^= 1u; }
                 }
-                if (ok) umma_commit(acc_full);
-                accph ^= 1u;
+                if (ok) umma_commit(&acc_full[ab]);
+                if (++ab == 2) { ab = 0; accph ^= 1u; }
             }
             if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
         }
-    } else if (warp >= 2 && warp <= 5) {
-        // =========================== dequantise + epilogue (warps 2..5) ===========================
-        const uint32_t dw = warp - 2;                 // 0..3
-        const uint32_t row = dw * 32 + lane;          // weight row of the tile this thread dequantises
+    } else if (warp < 2 + kDqWarps) {
+        // =========================== dequantise (warps 2 .. 2 + kDqWarps - 1) ===========================
+        const uint32_t dw = warp - 2;                         // 0..7
+        const uint32_t row = (dw & 3u) * 32 + lane;           // weight row of the tile this thread dequantises ...
+        const uint32_t kh = dw >> 2;                          // ... and which half of every 64-wide K chunk (code bytes 16 kh .. 16 kh + 15)
         const uint32_t sw = row & 7u;
-        const uint32_t quarter = warp & 3u;           // tensor-memory lane quarter this warp may read
         bool ok = true;
-        uint32_t qs = 0, qph = 0, ms = 0, mph = 0, accph = 0, cur_tile = 0xffffffffu;
-        GTile t{};
+        uint32_t qs = 0, qph = 0, ms = 0, mph = 0, ds = 0, dph = 0;
         for (uint32_t item = item0; item < item1; ++item) {
-            if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
-            const uint32_t rb = item % p.row_blocks;
+            if (ok) ok = gwait(&dfull[ds], dph);
+            const uint8_t* dmp = gsm + p.off_d + ds * p.d_stage_bytes;
             for (uint32_t sb = 0; sb < p.nblk; ++sb) {
                 if (ok) ok = gwait(&qfull[qs], qph);
                 const uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
@@ -277,7 +294,7 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
 #pragma unroll
                 for (uint32_t m = 0; m < NMAT; ++m) {
                     fac[m] = *reinterpret_cast<const uint4*>(q + NMAT * 16384u + m * 2048u + row * 16u);
-                    const uint32_t dmw = *reinterpret_cast<const uint32_t*>(q + NMAT * (16384u + 2048u) + m * (kRowsM * p.nblk * 4u) + (row * p.nblk + sb) * 4u);
+                    const uint32_t dmw = *reinterpret_cast<const uint32_t*>(dmp + m * p.dm_mat_bytes + (row * p.nblk + sb) * 4u);
                     dd[m] = half_bits_to_float(dmw & 0xffffu);
                     dmn[m] = half_bits_to_float(dmw >> 16);
                     if (ok && (!finite_f32(dd[m]) || !finite_f32(dmn[m]))) raise_error(p.error, TSP_ERR_NONFINITE);
@@ -288,8 +305,7 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
 #pragma unroll
                         for (uint32_t m = 0; m < NMAT; ++m) {
                             const uint8_t* line = q + m * 16384u + row * 128u;
-                            const uint4 w0 = *reinterpret_cast<const uint4*>(line + (((2 * c) ^ sw) << 4));
-                            const uint4 w1 = *reinterpret_cast<const uint4*>(line + (((2 * c + 1) ^ sw) << 4));
+                            const uint4 w0 = *reinterpret_cast<const uint4*>(line + (((2 * c + kh) ^ sw) << 4));
                             const uint32_t scw = c < 2 ? fac[m].x : fac[m].y, mnw = c < 2 ? fac[m].z : fac[m].w;
                             const uint32_t sh = (c & 1u) * 16u;
                             const float s_lo = dd[m] * static_cast<float>((scw >> sh) & 0xffu), s_hi = dd[m] * static_cast<float>((scw >> (sh + 8)) & 0xffu);
@@ -298,12 +314,14 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                             const __half2 nL = __float2half2_rn(-m_lo), nH = __float2half2_rn(-m_hi);
                             const __half2 k1024 = __float2half2_rn(1024.f), k16th = __float2half2_rn(0.0625f), kn64 = __float2half2_rn(-64.f);
                             uint8_t* arow = gsm + p.off_a + ms * NMAT * 16384u + m * 16384u + row * 128u;
-                            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                            const uint32_t words[4] = {w0.x, w0.y, w0.z, w0.w};
                             // output chunk qq (8 binary16 = K positions 8qq..8qq+7 of this 64-wide slice, in the shared 0,2,1,3,4,6,5,7 order):
-                            // qq < 4 from the low nibbles of bytes 8qq..8qq+7, qq >= 4 from the high nibbles of bytes 8(qq-4)..
+                            // qq < 4 from the low nibbles of code bytes 8qq..8qq+7, qq >= 4 from the high nibbles of bytes 8(qq-4)..; this
+                            // thread has bytes 16 kh .. 16 kh + 15, i.e. qq = 2 kh, 2 kh + 1 and their high-nibble partners
 #pragma unroll
-                            for (uint32_t qq = 0; qq < 4; ++qq) {
-                                const uint32_t a = words[2 * qq], b = words[2 * qq + 1];
+                            for (uint32_t q2 = 0; q2 < 2; ++q2) {
+                                const uint32_t qq = 2 * kh + q2;
+                                const uint32_t a = words[2 * q2], b = words[2 * q2 + 1];
                                 uint32_t lo[4], hi4[4];
                                 const uint32_t src[4] = {a, a >> 8, b, b >> 8};
 #pragma unroll
@@ -330,38 +348,51 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                 if (lane == 0 && ok) mbar_arrive(&qempty[qs]);
                 if (++qs == 2) { qs = 0; qph ^= 1u; }
             }
-            // ---- epilogue: this warp's 32 accumulator lanes = weight rows rb*128 + quarter*32 + lane ----
-            // route ids of the tile's positions, fetched before the wait so their latency hides behind the last MMAs:
-            // lane l keeps positions l, 32+l, 64+l, 96+l of the tile
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(&dempty[ds]);
+            if (++ds == 2) { ds = 0; dph ^= 1u; }
+        }
+        if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
+    } else {
+        // =========================== epilogue (the last kEpWarps warps) ===========================
+        const uint32_t quarter = warp & 3u;                   // tensor-memory lane quarter this warp may read
+        bool ok = true;
+        uint32_t ab = 0, accph = 0, cur_tile = 0xffffffffu;
+        GTile t{};
+        for (uint32_t item = item0; item < item1; ++item) {
+            if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
+            const uint32_t rb = item % p.row_blocks;
+            // this warp's 32 accumulator lanes = weight rows rb*128 + quarter*32 + lane, all token columns
+            // route ids of the tile's positions, fetched before the wait so their latency hides behind the MMAs:
+            // lane l keeps positions l, 32 + l, 64 + l, 96 + l
             uint32_t rt[4] = {0, 0, 0, 0};
             if (!GATEUP) {
 #pragma unroll
                 for (uint32_t qd = 0; qd < 4; ++qd)
                     if (qd * 32 + lane < t.count) rt[qd] = p.pos_route[t.row0 + qd * 32 + lane];
             }
-            if (ok) ok = gwait(acc_full, accph);
-            accph ^= 1u;
+            if (ok) ok = gwait(&acc_full[ab], accph);
             if (ok) {
                 tc_fence_after();
                 const uint32_t wrow = rb * kRowsM + quarter * 32 + lane;
-                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * 256u;
                 // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weight tiles use
                 const uint32_t hcol = (wrow & ~7u) | ((wrow & 4u) | ((wrow & 1u) << 1) | ((wrow & 2u) >> 1));
                 char* hrow = reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(t.row0) * p.out_stride_bytes + (GATEUP ? hcol * 2 : 0);
                 bool bad = false;
-                for (uint32_t j0 = 0; j0 < t.ncols && j0 < t.count; j0 += 16) {
-                    uint32_t g[16], u[16];
+                for (uint32_t j0 = 0; j0 < t.ncols && j0 < t.count; j0 += 32) {
+                    uint32_t g[32], u[GATEUP ? 32 : 1];
                     const uint32_t rq = j0 < 32 ? rt[0] : (j0 < 64 ? rt[1] : (j0 < 96 ? rt[2] : rt[3]));   // this lane's route id in the 32-wide group of j0
-                    tmem_ld16(taddr + j0, g);
-                    if (GATEUP) tmem_ld16(taddr + 128u + j0, u);
+                    tmem_ld32(taddr + j0, g);
+                    if constexpr (GATEUP) tmem_ld32(taddr + 128u + j0, u);
                     tmem_ld_wait();
 #pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i) {
+                    for (uint32_t i = 0; i < 32; ++i) {
                         const uint32_t j = j0 + i;
                         if (GATEUP) {
                             if (j < t.count) {
                                 const float gv = __uint_as_float(g[i]);
-                                const float v = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[i]);   // silu(g) * u
+                                const float v = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[GATEUP ? i : 0]);   // silu(g) * u
                                 const __half hv = __float2half_rn(v);
                                 bad |= !finite_f32(__half2float(hv));
                                 *reinterpret_cast<__half*>(hrow + static_cast<uint64_t>(j) * p.out_stride_bytes) = hv;
@@ -380,14 +411,15 @@ grouped_mma_kernel(const __grid_constant__ CUtensorMap qmap_a_lo, const __grid_c
                 tc_fence_before();
             }
             __syncwarp();
-            if (lane == 0 && ok) mbar_arrive(acc_empty);
+            if (lane == 0 && ok) mbar_arrive(&acc_empty[ab]);
+            if (++ab == 2) { ab = 0; accph ^= 1u; }
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     }
     // every path ends here: free the tensor memory
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 256);
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
 
@@ -461,14 +493,14 @@ int launch_gather_rows(const float* x, uint64_t x_stride, uint32_t in_div, const
 // host launcher of the grouped tensor-core GEMMs
 // ---------------------------------------------------------------------------------------------
 template <bool GATEUP>
-static int launch_grouped_t(const CUtensorMap* m, const GroupedParams& p, size_t smem, int grid, cudaStream_t st) {
+static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t smem, int grid, cudaStream_t st) {
     auto kernel = grouped_mma_kernel<GATEUP>;
     static thread_local size_t configured = 0;
     if (smem > configured) {
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    kernel<<<grid, kGThreads, smem, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], m[9], m[10], p);
+    kernel<<<grid, kGThreads, smem, st>>>(m, p);
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -484,51 +516,73 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     const uint32_t nblk = a->cols / 256;
     TSP_REQUIRE(nblk <= 32, "grouped GEMM: K extent too large");
     p.split = a->split < a->experts ? a->split : a->experts;
-    p.experts = a->experts; p.expert_stride = a->expert_stride;
+    p.experts = a->experts;
     p.rows = a->rows; p.cols = a->cols; p.nblk = nblk; p.row_blocks = a->rows / kRowsM;
     const uint64_t total_units = static_cast<uint64_t>(a->rows) * nblk;
-    p.sm_off = total_units * 128; p.dm_off = total_units * 144;
-    p.base[0] = static_cast<const uint8_t*>(a->base);
-    p.base[1] = static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base);
+    const uint64_t sm_off = total_units * 128, dm_off = total_units * 144;
+    const uint8_t* base[4] = {static_cast<const uint8_t*>(a->base), static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base), nullptr, nullptr};
     if (gateup) {
-        p.base[2] = static_cast<const uint8_t*>(b->base);
-        p.base[3] = static_cast<const uint8_t*>(b->base_hi ? b->base_hi : b->base);
-    } else { p.base[2] = p.base[0]; p.base[3] = p.base[1]; }
+        base[2] = static_cast<const uint8_t*>(b->base);
+        base[3] = static_cast<const uint8_t*>(b->base_hi ? b->base_hi : b->base);
+    }
+    for (int i = 0; i < (gateup ? 4 : 2); ++i) TSP_REQUIRE(reinterpret_cast<uintptr_t>(base[i]) % 16 == 0, "grouped GEMM: expert images must be 16-byte aligned");
     p.tasks = tasks; p.counts = counts; p.offsets = offsets; p.pos_route = pos_route;
     p.out = out; p.out_stride_bytes = out_stride; p.error = error;
     const uint32_t nmat = gateup ? 2 : 1;
+    p.dm_mat_bytes = kRowsM * nblk * 4u;
     p.off_q = 1024;
-    p.q_stage_bytes = (nmat * (16384u + 2048u + kRowsM * nblk * 4u) + 1023u) & ~1023u;
-    p.off_a = p.off_q + 2 * p.q_stage_bytes;
+    p.q_stage_bytes = nmat * (16384u + 2048u);
+    p.off_d = p.off_q + 2 * p.q_stage_bytes;
+    p.d_stage_bytes = (nmat * p.dm_mat_bytes + 1023u) & ~1023u;
+    p.off_a = p.off_d + 2 * p.d_stage_bytes;
     p.off_b = p.off_a + 2 * nmat * 16384u;
     TSP_REQUIRE(p.off_b + 2 * 16384u + 1024 <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
     p.nb_stages = (227 * 1024 - 1024 - p.off_b) / 16384u;
     if (p.nb_stages > kMaxBStages) p.nb_stages = kMaxBStages;
     const size_t smem = p.off_b + p.nb_stages * 16384u + 1024;
 
-    CUtensorMap maps[11];
-    const uint64_t stride = a->experts > 1 ? a->expert_stride : tsp_expert_bytes(a->type, a->layout, a->rows, a->cols);
+    // gate and up of an expert at one constant distance: one copy per plane brings both
+    auto mergeable = [](const uint8_t* first, const uint8_t* second, uint64_t* delta) {
+        if (second <= first) return false;
+        *delta = static_cast<uint64_t>(second - first);
+        return *delta % 16 == 0 && *delta < (1ull << 40);
+    };
+    uint64_t delta = 0, delta_hi = 0;
+    p.merged = gateup && mergeable(base[0], base[2], &delta) && mergeable(base[1], base[3], &delta_hi) && delta == delta_hi;
+    const uint32_t mats = p.merged ? 2 : 1;
+    const uint64_t ds = p.merged ? delta : 16;
+    GroupedMaps maps;
+    const uint64_t stride = a->experts > 1 ? a->expert_stride : 16;
+    TSP_REQUIRE(stride % 16 == 0, "grouped GEMM: expert stride must be a multiple of 16");
     const uint32_t n_lo = p.split, n_hi = a->experts - p.split;
-    for (int i = 0; i < 4; ++i) {
+    for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t m = i >> 1;
         const bool hi = i & 1;
-        const uint32_t n = hi ? (n_hi ? n_hi : n_lo) : n_lo;
-        const uint8_t* base = p.base[i];
-        {   // codes: [128 B of a super-block][row][super-block][expert], 128-byte swizzle
-            const uint64_t dims[4] = {128, a->rows, nblk, n}, strides[3] = {uint64_t(nblk) * 128, 128, stride};
-            const uint32_t box[4] = {128, kRowsM, 1, 1};
-            if (int rc = get_tensor_map_bytes(base, 4, dims, strides, box, true, &maps[i])) return rc;
+        if (m == 1 && (!gateup || p.merged)) { maps.q[i] = maps.q[i - 2]; maps.f[i] = maps.f[i - 2]; maps.d[i] = maps.d[i - 2]; continue; }
+        if (hi && n_hi == 0) { maps.q[i] = maps.q[i - 1]; maps.f[i] = maps.f[i - 1]; maps.d[i] = maps.d[i - 1]; continue; }
+        const uint32_t n = hi ? n_hi : (n_lo ? n_lo : 1);
+        const uint8_t* bp = base[i];
+        {   // codes: [128 B of a super-block][row][super-block][matrix][expert], 128-byte swizzle
+            const uint64_t dims[5] = {128, a->rows, nblk, mats, n}, strides[4] = {uint64_t(nblk) * 128, 128, ds, stride};
+            const uint32_t box[5] = {128, kRowsM, 1, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp, 5, dims, strides, box, true, &maps.q[i])) return rc;
         }
-        {   // factors: [16 B x super-blocks][row][expert][1]
-            const uint64_t dims[4] = {uint64_t(nblk) * 16, a->rows, n, 1}, strides[3] = {uint64_t(nblk) * 16, stride, stride};
-            const uint32_t box[4] = {16, kRowsM, 1, 1};
-            if (int rc = get_tensor_map_bytes(base + p.sm_off, 4, dims, strides, box, false, &maps[4 + i])) return rc;
+        {   // factors: [16 B x super-blocks][row][matrix][expert]
+            const uint64_t dims[4] = {uint64_t(nblk) * 16, a->rows, mats, n}, strides[3] = {uint64_t(nblk) * 16, ds, stride};
+            const uint32_t box[4] = {16, kRowsM, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp + sm_off, 4, dims, strides, box, false, &maps.f[i])) return rc;
+        }
+        {   // (d, dmin) pairs: the plane in lines of 256 bytes, [256 B][line][matrix][expert]; a row block of 128 rows is 2 * nblk lines
+            const uint64_t dims[4] = {256, total_units * 4 / 256, mats, n}, strides[3] = {256, ds, stride};
+            const uint32_t box[4] = {256, 2 * nblk, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp + dm_off, 4, dims, strides, box, false, &maps.d[i])) return rc;
         }
     }
     const uint32_t ns[3] = {32, 64, 128};
     for (int i = 0; i < 3; ++i) {
         const uint64_t dims[2] = {uint64_t(a->cols) * 2, max_positions}, strides[1] = {act_stride};
         const uint32_t box[2] = {128, ns[i]};
-        if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps[8 + i])) return rc;
+        if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[i])) return rc;
     }
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");

@@ -229,8 +229,10 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
     const float* sh = reinterpret_cast<const float*>(reinterpret_cast<const char*>(shared) + token * shared_stride);
     float* o = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + token * out_stride);
     bool bad = false;
-    // one channel per thread: blockIdx.y picks the slice of the row, so a small batch still fills the machine
-    for (uint32_t c = blockIdx.y * kCombineThreads + tid; c < min(channels, (blockIdx.y + 1) * kCombineThreads); c += kCombineThreads) {
+    // gridDim.y slices of the row per token, so that a small batch still fills the machine while a large one does not repeat
+    // the gate's dot product more often than needed
+    const uint32_t per_slice = (channels + gridDim.y - 1) / gridDim.y;
+    for (uint32_t c = blockIdx.y * per_slice + tid; c < min(channels, (blockIdx.y + 1) * per_slice); c += kCombineThreads) {
         float v = gate * sh[c];
         for (uint32_t r = 0; r < selected; ++r) {
             const float* y = reinterpret_cast<const float*>(reinterpret_cast<const char*>(routed) +
@@ -362,7 +364,11 @@ int launch_combine(const float* routed, uint64_t routed_stride, const float* wei
                    uint64_t shared_stride, const float* shared_router, const float* x, uint64_t x_stride,
                    float* shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected, float* out,
                    uint64_t out_stride, void* out16, uint64_t out16_stride, uint32_t* error, cudaStream_t st) {
-    combine_kernel<<<dim3(tokens, (channels + kCombineThreads - 1) / kCombineThreads), kCombineThreads, 0, st>>>(routed, routed_stride, weights, shared, shared_stride, shared_router,
+    // about four CTAs per SM in total: 8 slices of a 2048-wide row at 64 tokens, one slice from a few hundred tokens on
+    uint32_t slices = (channels + kCombineThreads - 1) / kCombineThreads;
+    const uint32_t want = (4u * 148u + tokens - 1) / tokens;
+    if (slices > want) slices = want;
+    combine_kernel<<<dim3(tokens, slices), kCombineThreads, 0, st>>>(routed, routed_stride, weights, shared, shared_stride, shared_router,
                                                        x, x_stride, shared_logit, channels, selected, out, out_stride,
                                                        static_cast<__half*>(out16), out16_stride, error);
     TSP_CUDA(cudaGetLastError());

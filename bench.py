@@ -176,6 +176,8 @@ def run_ours(args):
 
     if args.workload == "prefill":
         return run_prefill(args, local)
+    if args.workload == "head":
+        return run_head(args, local)
     dev = torch.device("cuda", local)
     T = args.tokens
     layout = formats.PLANAR if args.layout == "planar" else formats.GGUF
@@ -297,8 +299,7 @@ def run_prefill(args, local):
     stream = torch.cuda.current_stream()
 
     def layer_call(i, x, lg):
-        capi.check(lib.tsp_rows_f16_to_f32(x.data_ptr(), CHANNELS * 2, x32.data_ptr(), CHANNELS * 4, T, CHANNELS, L.stream_ptr()))
-        L.moe_layer_prefill(layers[i % len(layers)], ps, x32, lg, out)
+        L.moe_layer_prefill(layers[i % len(layers)], ps, x, lg, out)   # tsp_moe_layer_prefill: binary16 rows in and out
 
     def resident(i):
         layer_call(i, dev_x[i % nb], dev_lg[i % nb])
@@ -392,12 +393,100 @@ def run_prefill(args, local):
                        "l2_policy": "inputs larger than L2: 0.93 GB of weights and 0.5 GB of intermediates per step"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2},
-            "gpu_launches": 15 * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": 16 * args.steps, "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "kernel": "grouped_mma_kernel<gate-up> (routed experts, tcgen05)", "achieved": achieved, "peak": tf_peak,
                          "unit": "TFLOP/s", "frac": achieved / tf_peak, "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_flops_per_launch": gu_flops, "launch_ms": stages["gate_up_ms"]},
             "cpu_baseline": cpu,
             "extra": {"layer_tflops": T * (SELECTED + 1) * FLOPS_PER_ROUTE / (ms * 1e-3) / 1e12, "stage_ms": stages, "parity_rel_l2_vs_cpu": parity}}
+    print(json.dumps(line), flush=True)
+
+
+def run_head(args, local):
+    """BASELINE configs[3]: the dense Q8_0 vocabulary head [151936 x 2048] on a batch of draft-token hidden states (M <= 16)."""
+    import torch
+    from tokspur_public_b200 import capi, formats, synth
+    from tokspur_public_b200 import layer as L
+    dev = torch.device("cuda", local)
+    VOCAB, M = 151936, min(max(args.tokens, 1), 16) if args.tokens != 64 else 16
+    bpr = CHANNELS // 32                      # Q8_0 blocks per row
+    row_bytes = bpr * 34
+    lib, st = capi.lib(), L.stream_ptr()
+    nw = 2                                     # two independently seeded matrices rotate (each 330 MB, larger than L2)
+    mats, sets = [], []
+    for i in range(nw):
+        t = torch.empty(VOCAB * row_bytes, dtype=torch.uint8, device=dev)
+        capi.call("tsp_synth_weights", formats.Q8_0, 900 + i, 0, VOCAB * bpr, 0.02, t.data_ptr(), st)
+        mats.append(t)
+        sets.append(L.matrix_set(t, formats.Q8_0, formats.GGUF, VOCAB, CHANNELS))
+    nb = 4
+    host_x = [torch.from_numpy(synth.activations_f16(3000 + b, M, CHANNELS).astype(np.float32)).pin_memory() for b in range(nb)]
+    dev_x = [t.to(dev) for t in host_x]
+    sx = torch.zeros_like(dev_x[0])
+    out = torch.zeros((M, VOCAB), dtype=torch.float32, device=dev)
+    host_out = torch.zeros((M, VOCAB), dtype=torch.float32).pin_memory()
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def project(i, x):
+        capi.check(lib.tsp_moe_project(C.byref(sets[i % nw]), x.data_ptr(), CHANNELS * 4, 1, M, 1, None, None, None, out.data_ptr(), VOCAB * 4, 1,
+                                       err.data_ptr(), st))
+
+    def resident(i):
+        project(i, dev_x[i % nb])
+
+    def e2e(i):
+        sx.copy_(host_x[i % nb], non_blocking=True)
+        project(i, sx)
+        host_out.copy_(out, non_blocking=True)
+        stream.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    with ClockSampler(local) as clocks:
+        ms = timed(resident, args.steps, args.warmup)
+        ms_e2e = timed(e2e, args.steps, args.warmup)
+    assert int(err.item()) == 0, "device error word set during the benchmark"
+    hbm_peak, _, peak_kind = peaks()
+    bytes_launch = VOCAB * row_bytes + M * CHANNELS * 4 + M * VOCAB * 4
+    achieved = bytes_launch / (ms * 1e-3) / 1e9
+    cpu = parity = None
+    if args.cpu_tokens != 0:
+        orc, kind = cpu_oracle()
+        rows = 4096                                  # the first 4096 vocabulary rows of matrix 0, every token of batch 0
+        wbytes = mats[0][: rows * row_bytes].cpu().numpy()
+        xs = host_x[0].numpy()
+        t0 = time.perf_counter()
+        want = np.stack([orc.gemv(formats.Q8_0, wbytes, CHANNELS, rows, xs[m]) for m in range(M)])
+        dt = time.perf_counter() - t0
+        cpu = {"value": M / (dt * VOCAB / rows), "unit": "tokens/s", "cores": 1, "kind": kind,
+               "sample": f"{rows} of the {VOCAB} vocabulary rows for all {M} tokens, one thread, {dt:.1f} s, scaled to the whole matrix"}
+        project(0, dev_x[0])
+        torch.cuda.synchronize()
+        got = out[:, :rows].cpu().numpy().astype(np.float64)
+        parity = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    line = {"metric": "moe_q4k_expert_gemm_tokens_per_s", "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"q8_0_vocabulary_head_M{M} (BASELINE configs[3])", "vocab": VOCAB, "hidden": CHANNELS, "weights": "Q8_0 GGUF blocks",
+                       "l2_policy": "inputs larger than L2: two 330 MB matrices rotate"},
+            "e2e": {"value": M / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": M * CHANNELS * 4,
+                    "d2h_bytes_per_step": M * VOCAB * 4},
+            "gpu_launches": args.steps, "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q8_0> (dense head)", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None, "algorithmic_bytes_per_launch": bytes_launch,
+                         "launch_ms": ms},
+            "cpu_baseline": cpu, "extra": {"parity_rel_l2_vs_cpu": parity}}
     print(json.dumps(line), flush=True)
 
 
@@ -451,7 +540,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4, help="independently seeded weight sets rotated over")
     ap.add_argument("--layout", default="planar", choices=["planar", "gguf"])
     ap.add_argument("--cpu-tokens", type=int, default=None, help="tokens of the batch timed on the CPU baseline (0 = skip)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "head"])
     ap.add_argument("--ep-scheme", default="gather", choices=["gather", "alltoall"], help="multi-GPU exchange: all-gather/reduce-scatter or all-to-all")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -254,6 +254,38 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const void* d_hp, uint64_t 
                          const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, const uint32_t* d_pos_route,
                          float* d_routed, uint64_t routed_stride_bytes, uint32_t* d_error, void* stream);
 
+/* One whole MoE FFN sub-layer at prefill size: route -> permute (tiles of TSP_GROUPED_TILE) -> offsets -> gather ->
+ * grouped gate-up + SwiGLU -> grouped down -> shared expert (as a one-expert set over every token row, same kernels) ->
+ * gated mixture. Replaces `encode_moe_mm_many` after its router projection (moe_mm_many.cpp:126-220) on the
+ * `planar_nax_grouped_moe` path (graph.mm:9293-9420). Weights: Q4_K Pack v3 planar, hidden and channels multiples of 128,
+ * channels and hidden multiples of 256. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
+ * Caller-owned scratch, all device memory, nothing has to start at zero:
+ *   base: as for the decode layer, except d_tasks sized tsp_moe_tasks_words(capacity, experts, selected, TSP_GROUPED_TILE);
+ *         d_hidden and d_shared_hidden are not used and may be NULL;
+ *   d_xp / d_hp: binary16 rows in permuted position order, [capacity*selected x channels] / [capacity*selected x hidden];
+ *   d_offsets [experts + 1], d_pos_route [capacity*selected];
+ *   shared expert: d_ids0 [capacity], d_s_token_map [capacity], d_s_counts [1], d_s_offsets [2], d_s_pos [capacity],
+ *   d_s_tasks [tsp_moe_tasks_words(capacity, 1, 1, TSP_GROUPED_TILE)], d_s_xp [capacity x channels], d_s_hp [capacity x hidden]. */
+typedef struct tsp_moe_prefill_scratch {
+    tsp_moe_scratch base;
+    void* d_xp;
+    void* d_hp;
+    uint32_t* d_offsets;
+    uint32_t* d_pos_route;
+    uint32_t* d_ids0;
+    uint32_t* d_s_token_map;
+    uint32_t* d_s_counts;
+    uint32_t* d_s_offsets;
+    uint32_t* d_s_pos;
+    uint32_t* d_s_tasks;
+    void* d_s_xp;
+    void* d_s_hp;
+} tsp_moe_prefill_scratch;
+int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratch* s, const void* d_x, uint64_t x_stride_bytes,
+                          uint32_t x_dtype, const float* d_logits, uint64_t logits_stride_bytes, uint32_t tokens,
+                          uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected, uint32_t mode,
+                          int normalize, void* d_out, uint64_t out_stride_bytes, uint32_t out_dtype, uint32_t* d_error, void* stream);
+
 /* No counterpart in the reference (its graph always works out of caller-allocated buffers).
  *
  * The same layer as tsp_moe_layer_decode, for callers that have nowhere to get scratch from: code that runs

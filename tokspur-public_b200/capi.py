@@ -40,6 +40,12 @@ class MoeScratch(C.Structure):
                 ("capacity", C.c_uint32)]
 
 
+class MoePrefillScratch(C.Structure):
+    _fields_ = [("base", MoeScratch), ("d_xp", C.c_void_p), ("d_hp", C.c_void_p), ("d_offsets", C.c_void_p), ("d_pos_route", C.c_void_p),
+                ("d_ids0", C.c_void_p), ("d_s_token_map", C.c_void_p), ("d_s_counts", C.c_void_p), ("d_s_offsets", C.c_void_p),
+                ("d_s_pos", C.c_void_p), ("d_s_tasks", C.c_void_p), ("d_s_xp", C.c_void_p), ("d_s_hp", C.c_void_p)]
+
+
 class MoeWeights(C.Structure):
     _fields_ = [("gate", MatrixSet), ("up", MatrixSet), ("down", MatrixSet), ("shared_gate", MatrixSet),
                 ("shared_up", MatrixSet), ("shared_down", MatrixSet), ("d_shared_router", C.c_void_p)]
@@ -70,6 +76,8 @@ SIGNATURES = {
     "tsp_rows_f16_to_f32": (_i, [_vp, _u64, _vp, _u64, _u32, _u32, _vp]),
     "tsp_moe_layer_decode": (_i, [C.POINTER(MoeWeights), C.POINTER(MoeScratch), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32,
                                   _u32, _u32, _u32, _i, _vp, _u64, _u32, _vp, _vp]),
+    "tsp_moe_layer_prefill": (_i, [C.POINTER(MoeWeights), C.POINTER(MoePrefillScratch), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32,
+                                   _u32, _u32, _u32, _i, _vp, _u64, _u32, _vp, _vp]),
     "tsp_moe_route_offsets": (_i, [_vp, _u32, _vp, _vp]),
     "tsp_moe_gather_rows": (_i, [_vp, _u64, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp, _vp, _vp]),
     "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),

@@ -455,6 +455,57 @@ StaticPlan plan_static(uint32_t tokens, uint32_t channels, uint32_t hidden, uint
 }
 }  // namespace
 
+int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratch* ps, const void* d_x, uint64_t x_stride,
+                          uint32_t x_dtype, const float* d_logits, uint64_t logits_stride, uint32_t tokens, uint32_t channels,
+                          uint32_t hidden, uint32_t experts, uint32_t selected, uint32_t mode, int normalize, void* d_out,
+                          uint64_t out_stride, uint32_t out_dtype, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(w && ps && d_x && d_logits && d_out, "prefill layer: null argument");
+    const tsp_moe_scratch* s = &ps->base;
+    TSP_REQUIRE(tokens >= 1 && tokens <= s->capacity, "prefill layer: %u token rows exceed the scratch capacity %u", tokens, s->capacity);
+    TSP_REQUIRE(x_dtype <= 1 && out_dtype <= 1, "prefill layer: activation dtype must be 0 (FP32) or 1 (binary16)");
+    TSP_REQUIRE(selected >= 1 && selected <= 64, "prefill layer: selected out of range");
+    TSP_REQUIRE(w->gate.rows == hidden && w->gate.cols == channels && w->gate.experts == experts &&
+                w->down.rows == channels && w->down.cols == hidden && w->down.experts == experts &&
+                w->shared_gate.rows == hidden && w->shared_gate.cols == channels && w->shared_gate.experts == 1 &&
+                w->shared_up.experts == 1 && w->shared_down.rows == channels && w->shared_down.cols == hidden &&
+                w->shared_down.experts == 1, "prefill layer: weight shapes do not match the layer shape");
+    TSP_REQUIRE(s->d_ids && s->d_weights && s->d_routed && s->d_shared_out && s->d_token_map && s->d_counts && s->d_tasks && ps->d_xp &&
+                ps->d_hp && ps->d_offsets && ps->d_pos_route && ps->d_ids0 && ps->d_s_token_map && ps->d_s_counts && ps->d_s_offsets &&
+                ps->d_s_pos && ps->d_s_tasks && ps->d_s_xp && ps->d_s_hp, "prefill layer: incomplete scratch");
+    TSP_REQUIRE(x_dtype == 0 || s->d_x32, "prefill layer: binary16 input needs the d_x32 staging rows");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const float* x32 = static_cast<const float*>(d_x);
+    uint64_t x32_stride = x_stride;
+    if (x_dtype == 1) {
+        if (int rc = tsp_rows_f16_to_f32(d_x, x_stride, s->d_x32, channels * 4ull, tokens, channels, st)) return rc;
+        x32 = s->d_x32;
+        x32_stride = channels * 4ull;
+    }
+    const uint32_t routes = tokens * selected;
+    if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
+    if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GROUPED_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
+    if (int rc = tsp_moe_route_offsets(s->d_counts, experts, ps->d_offsets, st)) return rc;
+    if (int rc = tsp_moe_gather_rows(x32, x32_stride, selected, s->d_token_map, ps->d_offsets, experts, tokens, selected, channels, ps->d_xp,
+                                     channels * 2ull, ps->d_pos_route, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, ps->d_xp, channels * 2ull, routes, s->d_tasks, s->d_counts, ps->d_offsets, ps->d_hp,
+                                         hidden * 2ull, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_down(&w->down, ps->d_hp, hidden * 2ull, routes, s->d_tasks, s->d_counts, ps->d_offsets, ps->d_pos_route,
+                                      s->d_routed, channels * 4ull, d_error, st)) return rc;
+    // the dense shared expert through the same kernels: one expert, every token row routed to it
+    TSP_CUDA(cudaMemsetAsync(ps->d_ids0, 0, tokens * sizeof(uint32_t), st));
+    if (int rc = tsp_moe_permute(ps->d_ids0, tokens, 1, 1, TSP_GROUPED_TILE, ps->d_s_token_map, ps->d_s_counts, ps->d_s_tasks, d_error, st)) return rc;
+    if (int rc = tsp_moe_route_offsets(ps->d_s_counts, 1, ps->d_s_offsets, st)) return rc;
+    if (int rc = tsp_moe_gather_rows(x32, x32_stride, 1, ps->d_s_token_map, ps->d_s_offsets, 1, tokens, 1, channels, ps->d_s_xp, channels * 2ull,
+                                     ps->d_s_pos, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_gate_up(&w->shared_gate, &w->shared_up, ps->d_s_xp, channels * 2ull, tokens, ps->d_s_tasks, ps->d_s_counts,
+                                         ps->d_s_offsets, ps->d_s_hp, hidden * 2ull, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_down(&w->shared_down, ps->d_s_hp, hidden * 2ull, tokens, ps->d_s_tasks, ps->d_s_counts, ps->d_s_offsets, ps->d_s_pos,
+                                      s->d_shared_out, channels * 4ull, d_error, st)) return rc;
+    return tsp_moe_combine(s->d_routed, channels * 4ull, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32, x32_stride,
+                           s->d_shared_logit, tokens, channels, selected, out_dtype == 0 ? static_cast<float*>(d_out) : nullptr,
+                           out_dtype == 0 ? out_stride : 0, out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
+}
+
 uint64_t tsp_moe_layer_decode_static_bytes(uint32_t tokens, uint32_t channels, uint32_t hidden, uint32_t experts, uint32_t selected) {
     if (!tokens || !channels || !hidden || !experts || !selected || selected > 64) return 0;
     return plan_static(tokens, channels, hidden, experts, selected).total;

@@ -266,36 +266,21 @@ class PrefillScratch:
         self.s_tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, 1, 1, 128)), i32)
         self.s_xp = torch.zeros((capacity, channels), dtype=f16, device=device)
         self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)
+        base = capi.MoeScratch.from_buffer_copy(self.base.c)
+        base.d_tasks = self.tasks.data_ptr()     # tiles of 128 routes
+        self.c = capi.MoePrefillScratch(base, self.xp.data_ptr(), self.hp.data_ptr(), self.offsets.data_ptr(), self.pos_route.data_ptr(),
+                                        self.ids0.data_ptr(), self.s_token_map.data_ptr(), self.s_counts.data_ptr(), self.s_offsets.data_ptr(),
+                                        self.s_pos.data_ptr(), self.s_tasks.data_ptr(), self.s_xp.data_ptr(), self.s_hp.data_ptr())
 
 
-def moe_layer_prefill(dl, ps: PrefillScratch, x32: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, mode: int = 0, normalize: bool = True) -> None:
-    """One MoE layer for a prefill-size batch through the grouped tcgen05 GEMMs. x32: [T, channels] float32 rows; out float32 or float16."""
-    lib, st = capi.lib(), stream_ptr()
+def moe_layer_prefill(dl, ps: PrefillScratch, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, mode: int = 0, normalize: bool = True) -> None:
+    """One MoE layer for a prefill-size batch through the grouped tcgen05 GEMMs (tsp_moe_layer_prefill).
+    x: [T, channels] float32 or float16 rows; out float32 or float16."""
     s = ps.base
     C_, H, E, K = s.shape
-    T = x32.shape[0]
-    w, e = dl.weights, s.error.data_ptr()
-    C4, R = C_ * 4, T * K
-    capi.check(lib.tsp_moe_route(logits.data_ptr(), logits.stride(0) * 4, T, E, K, mode, int(normalize), s.ids.data_ptr(), s.weights.data_ptr(), e, st))
-    capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, E, K, 128, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), e, st))
-    capi.check(lib.tsp_moe_route_offsets(s.counts.data_ptr(), E, ps.offsets.data_ptr(), st))
-    capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), x32.stride(0) * 4, K, s.token_map.data_ptr(), ps.offsets.data_ptr(), E, T, K, C_,
-                                       ps.xp.data_ptr(), C_ * 2, ps.pos_route.data_ptr(), e, st))
-    capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), ps.xp.data_ptr(), C_ * 2, R, ps.tasks.data_ptr(), s.counts.data_ptr(),
-                                           ps.offsets.data_ptr(), ps.hp.data_ptr(), H * 2, e, st))
-    capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), ps.hp.data_ptr(), H * 2, R, ps.tasks.data_ptr(), s.counts.data_ptr(), ps.offsets.data_ptr(),
-                                        ps.pos_route.data_ptr(), s.routed.data_ptr(), C4, e, st))
-    # shared expert: one expert, every token row
-    capi.check(lib.tsp_moe_permute(ps.ids0.data_ptr(), T, 1, 1, 128, ps.s_token_map.data_ptr(), ps.s_counts.data_ptr(), ps.s_tasks.data_ptr(), e, st))
-    capi.check(lib.tsp_moe_route_offsets(ps.s_counts.data_ptr(), 1, ps.s_offsets.data_ptr(), st))
-    capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), x32.stride(0) * 4, 1, ps.s_token_map.data_ptr(), ps.s_offsets.data_ptr(), 1, T, 1, C_,
-                                       ps.s_xp.data_ptr(), C_ * 2, ps.s_pos.data_ptr(), e, st))
-    capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.shared_gate), C.byref(w.shared_up), ps.s_xp.data_ptr(), C_ * 2, T, ps.s_tasks.data_ptr(),
-                                           ps.s_counts.data_ptr(), ps.s_offsets.data_ptr(), ps.s_hp.data_ptr(), H * 2, e, st))
-    capi.check(lib.tsp_moe_grouped_down(C.byref(w.shared_down), ps.s_hp.data_ptr(), H * 2, T, ps.s_tasks.data_ptr(), ps.s_counts.data_ptr(),
-                                        ps.s_offsets.data_ptr(), ps.s_pos.data_ptr(), s.shared_out.data_ptr(), C4, e, st))
-    o32 = out.data_ptr() if out.dtype == torch.float32 else None
-    o16 = out.data_ptr() if out.dtype == torch.float16 else None
-    capi.check(lib.tsp_moe_combine(s.routed.data_ptr(), C4, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
-                                   x32.data_ptr(), x32.stride(0) * 4, s.shared_logit.data_ptr(), T, C_, K, o32, C4 if o32 else 0,
-                                   o16, C_ * 2 if o16 else 0, e, st))
+    T = x.shape[0]
+    xd = 1 if x.dtype == torch.float16 else 0
+    od = 1 if out.dtype == torch.float16 else 0
+    capi.call("tsp_moe_layer_prefill", C.byref(dl.weights), C.byref(ps.c), x.data_ptr(), x.stride(0) * x.element_size(), xd, logits.data_ptr(),
+              logits.stride(0) * 4, T, C_, H, E, K, mode, int(normalize), out.data_ptr(), out.stride(0) * out.element_size(), od,
+              s.error.data_ptr(), stream_ptr())

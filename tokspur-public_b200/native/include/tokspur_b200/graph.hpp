@@ -67,6 +67,9 @@ public:
 
     // operators (each is one or two launches through the C ABI; all require an open batch)
     void gemv_f32(GpuView matrix, GpuView input, GpuView output, uint32_t columns, uint32_t rows);   // gemv(type 0)
+    // the same projection for `tokens` strided input rows (moe_router_f32_batch): output rows of `rows` values at out_stride_bytes
+    void gemv_f32_rows(GpuView matrix, GpuView input, uint64_t in_stride_bytes, uint32_t tokens, GpuView output, uint64_t out_stride_bytes,
+                       uint32_t columns, uint32_t rows);
     void route(GpuView logits, GpuView indices, GpuView weights, uint32_t selected, RouterMode mode, bool normalize_selected);
 
     // raw access for the composed encoders in moe.cpp

@@ -1,0 +1,39 @@
+// Prefill-size MoE FFN encoder with the reference's entry points (native/include/tokspur/moe_mm_many.hpp:52-66): caller-owned
+// scratch for `capacity` token rows, strided FP32 row batches in and out, encode only. Longer batches are walked in chunks
+// of `capacity` rows, as the reference does (moe_mm_many.cpp:133-143).
+#pragma once
+
+#include <array>
+
+#include "tokspur_b200/moe.hpp"
+
+namespace tokspur_b200 {
+
+
+constexpr size_t kMoeMmManyViews = 21;
+struct MoeMmManyBytes {
+    std::array<uint64_t, kMoeMmManyViews> views{};
+    uint64_t total = 0;
+};
+struct MoeMmManyScratch {
+    // router logits and routing results of the rows, FP32 route outputs, shared expert output and gate logit
+    GpuView logits, indices, weights, routed, shared_out, shared_logit;
+    // stable per-expert permutation (tiles of 128 routes), first position of every expert, route id of every position
+    GpuView token_map, counts, tasks, offsets, pos_route;
+    // binary16 rows in permuted position order: gathered inputs, hidden rows
+    GpuView xp, hp;
+    // the dense shared expert as a one-expert set over every row
+    GpuView ids0, s_token_map, s_counts, s_offsets, s_pos, s_tasks, s_xp, s_hp;
+    uint32_t capacity = 0;
+    [[nodiscard]] std::array<GpuView, kMoeMmManyViews> views() const;
+};
+MoeMmManyBytes moe_mm_many_bytes(MoeShape shape, uint32_t capacity);
+MoeMmManyScratch allocate_moe_mm_many_scratch(CudaGraph& graph, MoeShape shape, uint32_t capacity);
+void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scratch);
+
+// Encode only. The caller owns allocation, the batch and the committed state. Weights must be the registered planar tensors
+// (is_planar_moe) with a Q4_K planar shared expert; anything else is refused before the first launch.
+void encode_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, const MoeMmManyScratch& scratch, GpuRowsF32 input, GpuRowsF32 output,
+                        MoeShape shape, RouterMode mode, bool normalize_selected);
+
+}  // namespace tokspur_b200

@@ -166,6 +166,18 @@ void CudaGraph::gemv_f32(GpuView matrix, GpuView input, GpuView output, uint32_t
     ++dispatches_;
 }
 
+void CudaGraph::gemv_f32_rows(GpuView matrix, GpuView input, uint64_t in_stride_bytes, uint32_t tokens, GpuView output, uint64_t out_stride_bytes,
+                              uint32_t columns, uint32_t rows) {
+    require_batch();
+    if (!tokens || matrix.bytes != uint64_t(columns) * rows * 4 || in_stride_bytes < uint64_t(columns) * 4 || out_stride_bytes < uint64_t(rows) * 4 ||
+        input.bytes < uint64_t(tokens - 1) * in_stride_bytes + uint64_t(columns) * 4 ||
+        output.bytes < uint64_t(tokens - 1) * out_stride_bytes + uint64_t(rows) * 4)
+        throw FormatError("GEMV shape mismatch");
+    check(tsp_gemv_f32(static_cast<const float*>(device_pointer(matrix)), rows, columns, static_cast<const float*>(device_pointer(input)),
+                       in_stride_bytes, tokens, static_cast<float*>(device_pointer(output, true)), out_stride_bytes, error_, stream_));
+    ++dispatches_;
+}
+
 void CudaGraph::route(GpuView logits, GpuView indices, GpuView weights, uint32_t selected, RouterMode mode, bool normalize_selected) {
     require_batch();
     const uint32_t experts = static_cast<uint32_t>(logits.bytes / 4);

@@ -1,0 +1,112 @@
+// encode_moe_mm_many over the CUDA graph: the reference's composition (native/src/moe_mm_many.cpp:126-220) with everything
+// after the router projection forwarded to the C ABI's prefill layer entry point (grouped tcgen05 GEMMs).
+#include "tokspur_b200/moe_mm_many.hpp"
+
+#include <algorithm>
+
+namespace tokspur_b200 {
+namespace {
+void need(bool ok, const char* what) { if (!ok) throw FormatError(what); }
+}
+
+std::array<GpuView, kMoeMmManyViews> MoeMmManyScratch::views() const {
+    return {logits, indices, weights, routed, shared_out, shared_logit, token_map, counts, tasks, offsets, pos_route, xp, hp,
+            ids0, s_token_map, s_counts, s_offsets, s_pos, s_tasks, s_xp, s_hp};
+}
+
+MoeMmManyBytes moe_mm_many_bytes(MoeShape s, uint32_t capacity) {
+    need(s.channels && s.hidden && s.experts && s.selected && s.selected <= 64 && s.selected <= s.experts && capacity, "tiled MoE shape/capacity");
+    const uint64_t n = capacity, r = n * s.selected;
+    MoeMmManyBytes b;
+    b.views = {n * s.experts * 4, r * 4, r * 4, r * s.channels * 4, n * s.channels * 4, n * 4,
+               uint64_t(s.experts) * n * 4, uint64_t(s.experts) * 4, tsp_moe_tasks_words(capacity, s.experts, s.selected, TSP_GROUPED_TILE) * 4,
+               (uint64_t(s.experts) + 1) * 4, r * 4, r * s.channels * 2, r * s.hidden * 2,
+               n * 4, n * 4, 4, 8, n * 4, tsp_moe_tasks_words(capacity, 1, 1, TSP_GROUPED_TILE) * 4, n * s.channels * 2, n * s.hidden * 2};
+    for (const auto v : b.views) b.total += v;
+    return b;
+}
+
+MoeMmManyScratch allocate_moe_mm_many_scratch(CudaGraph& graph, MoeShape shape, uint32_t capacity) {
+    const auto bytes = moe_mm_many_bytes(shape, capacity);
+    std::array<GpuView, kMoeMmManyViews> v{};
+    size_t made = 0;
+    try {
+        for (; made < v.size(); ++made) v[made] = graph.zeros(bytes.views[made], "tiled mixture scratch");
+    } catch (...) {
+        for (size_t i = 0; i < made; ++i) graph.release(v[i]);
+        throw;
+    }
+    return {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12], v[13], v[14], v[15], v[16], v[17], v[18], v[19], v[20], capacity};
+}
+
+void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scratch) {
+    for (const auto view : scratch.views()) graph.release(view);
+}
+
+void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratch& s, GpuRowsF32 input, GpuRowsF32 output, MoeShape shape,
+                        RouterMode mode, bool normalize_selected) {
+    need(s.capacity > 0 && input.rows > 0 && input.rows == output.rows && input.columns == shape.channels && output.columns == shape.channels &&
+         uint32_t(mode) <= 1, "tiled MoE active rows/router mode");
+    for (const auto r : {input, output})
+        need(r.stride_bytes >= uint64_t(shape.channels) * 4 && r.stride_bytes % 16 == 0 &&
+             r.view.bytes >= uint64_t(r.rows - 1) * r.stride_bytes + uint64_t(shape.channels) * 4, "tiled MoE strided row extent");
+    if (input.rows > s.capacity) {   // longer batches: chunks of `capacity` rows
+        for (uint32_t r0 = 0; r0 < input.rows; r0 += s.capacity) {
+            const uint32_t n = std::min(s.capacity, input.rows - r0);
+            const uint64_t span_in = uint64_t(n - 1) * input.stride_bytes + uint64_t(input.columns) * 4;
+            const uint64_t span_out = uint64_t(n - 1) * output.stride_bytes + uint64_t(output.columns) * 4;
+            encode_moe_mm_many(g, w, s, {g.slice(input.view, uint64_t(r0) * input.stride_bytes, span_in), n, input.columns, input.stride_bytes},
+                               {g.slice(output.view, uint64_t(r0) * output.stride_bytes, span_out), n, output.columns, output.stride_bytes}, shape,
+                               mode, normalize_selected);
+        }
+        return;
+    }
+    const auto bytes = moe_mm_many_bytes(shape, s.capacity);
+    const auto all = s.views();
+    for (size_t i = 0; i < all.size(); ++i) need(all[i].bytes == bytes.views[i], "tiled MoE scratch capacity extent");
+    need(w.router.encoding == 0 && w.shared_router.encoding == 0, "router projections must be F32");
+    need(is_planar_moe(g, w, shape), "tiled MoE needs the registered planar expert tensors");
+    need(w.router.view.bytes == uint64_t(shape.channels) * shape.experts * 4 && w.shared_router.view.bytes == uint64_t(shape.channels) * 4,
+         "router shape mismatch");
+    const uint32_t type = w.gate.encoding;
+    const uint64_t pb = tsp_expert_bytes(type, TSP_LAYOUT_PLANAR, shape.hidden, shape.channels);
+    const uint64_t pd = tsp_expert_bytes(w.down.encoding, TSP_LAYOUT_PLANAR, shape.channels, shape.hidden);
+    need(pb && pd && shape.experts % 2 == 0, "tiled MoE weight extent");
+    auto dense = [&](GpuMatrix m, uint32_t rows, uint32_t cols) {
+        const auto shp = g.planar_matrix_shape(m.view);
+        need(shp.has_value() && m.view.bytes == tsp_expert_bytes(m.encoding, TSP_LAYOUT_PLANAR, rows, cols), "tiled MoE shared expert must be a registered planar matrix");
+        return tsp_matrix_set{g.device_pointer(m.view), nullptr, m.view.bytes, 1, 1, rows, cols, m.encoding, TSP_LAYOUT_PLANAR};
+    };
+    tsp_moe_weights tw{};
+    const auto lo = static_cast<const char*>(g.device_pointer(w.gate.view)), hi = static_cast<const char*>(g.device_pointer(w.up.view));
+    tw.gate = {lo, hi, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, type, TSP_LAYOUT_PLANAR};
+    tw.up = {lo + pb, hi + pb, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, type, TSP_LAYOUT_PLANAR};
+    tw.down = {g.device_pointer(w.down.view), nullptr, pd, shape.experts, shape.experts, shape.channels, shape.hidden, w.down.encoding, TSP_LAYOUT_PLANAR};
+    need(w.down.view.bytes == pd * shape.experts, "tiled MoE down extent");
+    tw.shared_gate = dense(w.shared_gate, shape.hidden, shape.channels);
+    tw.shared_up = dense(w.shared_up, shape.hidden, shape.channels);
+    tw.shared_down = dense(w.shared_down, shape.channels, shape.hidden);
+    tw.d_shared_router = static_cast<const float*>(g.device_pointer(w.shared_router.view));
+
+    auto u32p = [&](GpuView v) { return static_cast<uint32_t*>(g.device_pointer(v, true)); };
+    auto f32p = [&](GpuView v) { return static_cast<float*>(g.device_pointer(v, true)); };
+    tsp_moe_prefill_scratch ps{};
+    ps.base.d_ids = u32p(s.indices); ps.base.d_weights = f32p(s.weights); ps.base.d_routed = f32p(s.routed);
+    ps.base.d_shared_out = f32p(s.shared_out); ps.base.d_shared_logit = f32p(s.shared_logit);
+    ps.base.d_token_map = u32p(s.token_map); ps.base.d_counts = u32p(s.counts); ps.base.d_tasks = u32p(s.tasks);
+    ps.base.capacity = s.capacity;
+    ps.d_xp = g.device_pointer(s.xp, true); ps.d_hp = g.device_pointer(s.hp, true);
+    ps.d_offsets = u32p(s.offsets); ps.d_pos_route = u32p(s.pos_route); ps.d_ids0 = u32p(s.ids0);
+    ps.d_s_token_map = u32p(s.s_token_map); ps.d_s_counts = u32p(s.s_counts); ps.d_s_offsets = u32p(s.s_offsets); ps.d_s_pos = u32p(s.s_pos);
+    ps.d_s_tasks = u32p(s.s_tasks); ps.d_s_xp = g.device_pointer(s.s_xp, true); ps.d_s_hp = g.device_pointer(s.s_hp, true);
+
+    const uint32_t n = input.rows;
+    g.gemv_f32_rows(w.router.view, input.view, input.stride_bytes, n, s.logits, uint64_t(shape.experts) * 4, shape.channels, shape.experts);
+    const int rc = tsp_moe_layer_prefill(&tw, &ps, g.device_pointer(input.view), input.stride_bytes, 0, static_cast<const float*>(g.device_pointer(s.logits)),
+                                         uint64_t(shape.experts) * 4, n, shape.channels, shape.hidden, shape.experts, shape.selected, uint32_t(mode),
+                                         normalize_selected, g.device_pointer(output.view, true), output.stride_bytes, 0, g.error_word(), g.stream());
+    if (rc != TSP_OK) throw FormatError(tsp_last_error());
+    g.count_dispatches(15);   // route, routes+tasks, offsets, gather, gate-up, down, the same six for the shared expert, mixture
+}
+
+}  // namespace tokspur_b200

@@ -1,4 +1,4 @@
-// encode_moe on the CUDA graph against the CPU oracle, in the style of the reference's native/tests/test_moe.cpp:
+// encode_moe and encode_moe_mm_many on the CUDA graph against the CPU oracle, in the style of the reference's native/tests/test_moe.cpp:
 // generated weights, route ids bit-equal, every stage within 5e-5 scaled error, refusals before encoding, sticky-error
 // recovery, allocation invariants. The oracle (oracle/tsp_oracle.h) is test infrastructure and is linked only here.
 #include <cmath>
@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "tokspur_b200/moe.hpp"
+#include "tokspur_b200/moe_mm_many.hpp"
 #include "tsp_oracle.h"
 
 using namespace tokspur_b200;
@@ -148,6 +149,77 @@ void layer(CudaGraph& g, uint32_t type, bool use_planar, MoeShape shape, uint32_
     (void)g.submit();
     release_moe_scratch(g, scratch);
 }
+// encode_moe_mm_many (grouped tensor-core GEMMs): strided row batches longer than the scratch capacity, against the oracle.
+// Operands are binary16 there, so the layer bar is the relative L2 error of 2e-3, not the decode path's 5e-5.
+void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32_t seed) {
+    const uint32_t type = 12, C = shape.channels, H = shape.hidden, E = shape.experts, K = shape.selected;
+    const auto gate = generated(type, C, H, E, seed + 1), up = generated(type, C, H, E, seed + 2), down = generated(type, H, C, E, seed + 3);
+    const auto sgate = generated(type, C, H, 1, seed + 4), sup = generated(type, C, H, 1, seed + 5), sdown = generated(type, H, C, 1, seed + 6);
+    const auto router = activations(seed + 7, size_t(E) * C, 0.25f), srouter = activations(seed + 8, C, 0.125f);
+    MoeWeights w{};
+    w.router = {g.upload(bytes_of(router), "router"), 0};
+    w.shared_router = {g.upload(bytes_of(srouter), "shared router"), 0};
+    const auto pg = planar(type, gate, C, H, E), pu = planar(type, up, C, H, E);
+    const size_t pb = pg.size() / E;
+    std::vector<uint8_t> lo(pb * E), hi(pb * E);
+    for (uint32_t e = 0; e < E; ++e) {
+        auto& dst = e < E / 2 ? lo : hi;
+        const size_t at = size_t(e % (E / 2)) * 2 * pb;
+        std::memcpy(dst.data() + at, pg.data() + e * pb, pb);
+        std::memcpy(dst.data() + at + pb, pu.data() + e * pb, pb);
+    }
+    w.gate = {g.upload(bytes(lo), "pair lo"), type}; w.up = {g.upload(bytes(hi), "pair hi"), type};
+    w.down = {g.upload(bytes(planar(type, down, H, C, E)), "down planar"), type};
+    w.shared_gate = {g.upload(bytes(planar(type, sgate, C, H, 1)), "sg planar"), type};
+    w.shared_up = {g.upload(bytes(planar(type, sup, C, H, 1)), "su planar"), type};
+    w.shared_down = {g.upload(bytes(planar(type, sdown, H, C, 1)), "sd planar"), type};
+    g.register_planar_matrix(w.gate.view, {type, 2, C, H, E});
+    g.register_planar_matrix(w.up.view, {type, 3, C, H, E});
+    g.register_planar_matrix(w.down.view, {type, 10, H, C, E});
+    g.register_planar_matrix(w.shared_gate.view, {type, 10, C, H, 1});
+    g.register_planar_matrix(w.shared_up.view, {type, 10, C, H, 1});
+    g.register_planar_matrix(w.shared_down.view, {type, 10, H, C, 1});
+    const auto scratch = allocate_moe_mm_many_scratch(g, shape, capacity);
+    const uint64_t in_stride = uint64_t(C) * 4 + 32, out_stride = uint64_t(C) * 4 + 16;
+    const auto input = g.zeros(in_stride * rows, "rows in"), output = g.zeros(out_stride * rows, "rows out");
+    const auto allocations = g.allocations();
+
+    // activations that binary16 holds exactly, as on the prefill path (multiples of 1/64 below 16)
+    std::vector<float> x(size_t(rows) * C);
+    uint32_t rng = seed * 77u + 5u;
+    for (auto& v : x) { rng = rng * 1664525u + 1013904223u; v = float(int(rng % 1025) - 512) / 64.f; }
+    std::vector<uint8_t> staged(in_stride * rows, 0);
+    for (uint32_t r = 0; r < rows; ++r) std::memcpy(staged.data() + r * in_stride, x.data() + size_t(r) * C, size_t(C) * 4);
+    g.write(input, bytes(staged));
+    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1};
+    std::vector<double> expected(size_t(rows) * C);
+    require(tso_moe_layer(&L, x.data(), nullptr, rows, expected.data(), nullptr, 4) == TSO_OK, "oracle layer");
+    for (int run = 0; run < 2; ++run) {
+        g.begin();
+        encode_moe_mm_many(g, w, scratch, {input, rows, C, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true);
+        const auto batch = g.submit();
+        require(batch.dispatches >= 16 && g.allocations() == allocations, "dispatch / allocation invariant");
+        const auto raw = g.read(output);
+        double num = 0, den = 0;
+        for (uint32_t r = 0; r < rows; ++r)
+            for (uint32_t c = 0; c < C; ++c) {
+                float v;
+                std::memcpy(&v, raw.data() + r * out_stride + size_t(c) * 4, 4);
+                const double e = expected[size_t(r) * C + c];
+                require(std::isfinite(v), "non-finite row value");
+                num += (v - e) * (v - e); den += e * e;
+            }
+        const double rel = std::sqrt(num / den);
+        std::cout << "  encode_moe_mm_many rows " << rows << " capacity " << capacity << ": relative L2 error " << rel << "\n";
+        require(rel <= 2e-3, "tiled MoE relative L2 tolerance exceeded");
+    }
+    g.begin();
+    refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows, C - 1, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true); }, "column mismatch accepted");
+    refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows, C, in_stride - 4}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true); }, "unaligned stride accepted");
+    refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows + 1, C, in_stride}, {output, rows + 1, C, out_stride}, shape, RouterMode::softmax, true); }, "rows beyond the views accepted");
+    g.abort();
+    release_moe_mm_many_scratch(g, scratch);
+}
 }  // namespace
 
 int main() {
@@ -172,6 +244,15 @@ int main() {
             std::cerr << "MoE check failed (type " << c.type << ", planar " << c.planar << ") after " << checks << " checks: " << e.what() << '\n';
             return 1;
         }
+    }
+    try {
+        CudaGraph g(0, uint64_t(2) << 30);
+        many(g, {512, 256, 16, 4}, 40, 24, 300);   // two chunks: 24 + 16 rows
+        CudaGraph g2(0, uint64_t(2) << 30);
+        many(g2, {512, 256, 8, 2}, 200, 256, 400); // one chunk, tiles of more than 32 routes
+    } catch (const std::exception& e) {
+        std::cerr << "tiled MoE check failed after " << checks << " checks: " << e.what() << '\n';
+        return 1;
     }
     std::cout << "MoE encode checks passed: " << checks << " (worst scaled error " << worst << ")\n";
     return 0;

@@ -307,9 +307,12 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_mma_kernel(const __grid_
                             const uint8_t* line = q + m * 16384u + row * 128u;
                             const uint4 w0 = *reinterpret_cast<const uint4*>(line + (((2 * c + kh) ^ sw) << 4));
                             const uint32_t scw = c < 2 ? fac[m].x : fac[m].y, mnw = c < 2 ? fac[m].z : fac[m].w;
-                            const uint32_t sh = (c & 1u) * 16u;
-                            const float s_lo = dd[m] * static_cast<float>((scw >> sh) & 0xffu), s_hi = dd[m] * static_cast<float>((scw >> (sh + 8)) & 0xffu);
-                            const float m_lo = dmn[m] * static_cast<float>((mnw >> sh) & 0xffu), m_hi = dmn[m] * static_cast<float>((mnw >> (sh + 8)) & 0xffu);
+                            // factor byte -> float through the 2^23 magic number (0x4B0000bb = 2^23 + bb), folded into one FMA each
+                            const uint32_t selL = 0x7440u + 2u * (c & 1u), selH = selL + 1u;
+                            const float s_lo = fmaf(dd[m], __uint_as_float(__byte_perm(scw, 0x4b000000u, selL)), dd[m] * -8388608.f);
+                            const float s_hi = fmaf(dd[m], __uint_as_float(__byte_perm(scw, 0x4b000000u, selH)), dd[m] * -8388608.f);
+                            const float m_lo = fmaf(dmn[m], __uint_as_float(__byte_perm(mnw, 0x4b000000u, selL)), dmn[m] * -8388608.f);
+                            const float m_hi = fmaf(dmn[m], __uint_as_float(__byte_perm(mnw, 0x4b000000u, selH)), dmn[m] * -8388608.f);
                             const __half2 sL = __float2half2_rn(s_lo), sH = __float2half2_rn(s_hi);
                             const __half2 nL = __float2half2_rn(-m_lo), nH = __float2half2_rn(-m_hi);
                             const __half2 k1024 = __float2half2_rn(1024.f), k16th = __float2half2_rn(0.0625f), kn64 = __float2half2_rn(-64.f);

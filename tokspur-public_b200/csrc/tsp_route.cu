@@ -199,7 +199,7 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
                const float* __restrict__ shared, uint64_t shared_stride, const float* __restrict__ shared_router,
                const float* __restrict__ x, uint64_t x_stride, float* shared_logit, uint32_t channels,
                uint32_t selected, float* __restrict__ out, uint64_t out_stride, __half* __restrict__ out16,
-               uint64_t out16_stride, uint32_t* error) {
+               uint64_t out16_stride, int vec4, uint32_t* error) {
     __shared__ float partial[kCombineThreads / 32];
     __shared__ float w_s[64];
     __shared__ float gate_s;
@@ -230,18 +230,38 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
     float* o = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + token * out_stride);
     bool bad = false;
     // gridDim.y slices of the row per token, so that a small batch still fills the machine while a large one does not repeat
-    // the gate's dot product more often than needed
-    const uint32_t per_slice = (channels + gridDim.y - 1) / gridDim.y;
-    for (uint32_t c = blockIdx.y * per_slice + tid; c < min(channels, (blockIdx.y + 1) * per_slice); c += kCombineThreads) {
-        float v = gate * sh[c];
-        for (uint32_t r = 0; r < selected; ++r) {
-            const float* y = reinterpret_cast<const float*>(reinterpret_cast<const char*>(routed) +
-                                                            (static_cast<uint64_t>(token) * selected + r) * routed_stride);
-            if (w_s[r] != 0.f) v = fmaf(w_s[r], y[c], v);   // a zero weight marks a route that is not present in `routed` (expert parallelism)
+    // the gate's dot product more often than needed; four channels per thread (rows are 16-byte aligned)
+    const uint32_t per_slice = ((channels + gridDim.y - 1) / gridDim.y + 3u) & ~3u;
+    const uint32_t c_end = min(channels, (blockIdx.y + 1) * per_slice);
+    const char* y0 = reinterpret_cast<const char*>(routed) + static_cast<uint64_t>(token) * selected * routed_stride;
+    for (uint32_t c = blockIdx.y * per_slice + tid * 4; c < c_end; c += kCombineThreads * 4) {
+        if (vec4 && c + 4 <= c_end) {
+            const float4 s4 = *reinterpret_cast<const float4*>(sh + c);
+            float v[4] = {gate * s4.x, gate * s4.y, gate * s4.z, gate * s4.w};
+            for (uint32_t r = 0; r < selected; ++r) {
+                const float wr = w_s[r];
+                if (wr != 0.f) {   // a zero weight marks a route that is not present in `routed` (expert parallelism)
+                    const float4 y = *reinterpret_cast<const float4*>(y0 + r * routed_stride + c * 4ull);
+                    v[0] = fmaf(wr, y.x, v[0]); v[1] = fmaf(wr, y.y, v[1]); v[2] = fmaf(wr, y.z, v[2]); v[3] = fmaf(wr, y.w, v[3]);
+                }
+            }
+            bad |= !finite_f32(v[0]) | !finite_f32(v[1]) | !finite_f32(v[2]) | !finite_f32(v[3]);
+            if (out) *reinterpret_cast<float4*>(o + c) = make_float4(v[0], v[1], v[2], v[3]);
+            if (out16) {
+                const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                *reinterpret_cast<uint2*>(reinterpret_cast<char*>(out16) + token * out16_stride + c * 2ull) =
+                    make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+            }
+        } else {
+            for (uint32_t cc = c; cc < min(c + 4, c_end); ++cc) {   // a row tail shorter than four channels, or rows that are not 16-byte aligned
+                float v = gate * sh[cc];
+                for (uint32_t r = 0; r < selected; ++r)
+                    if (w_s[r] != 0.f) v = fmaf(w_s[r], reinterpret_cast<const float*>(y0 + r * routed_stride)[cc], v);
+                bad |= !finite_f32(v);
+                if (out) o[cc] = v;
+                if (out16) reinterpret_cast<__half*>(reinterpret_cast<char*>(out16) + token * out16_stride)[cc] = __float2half_rn(v);
+            }
         }
-        bad |= !finite_f32(v);
-        if (out) o[c] = v;
-        if (out16) reinterpret_cast<__half*>(reinterpret_cast<char*>(out16) + token * out16_stride)[c] = __float2half_rn(v);
     }
     if (bad) raise_error(error, TSP_ERR_NONFINITE);
 }
@@ -368,9 +388,12 @@ int launch_combine(const float* routed, uint64_t routed_stride, const float* wei
     uint32_t slices = (channels + kCombineThreads - 1) / kCombineThreads;
     const uint32_t want = (4u * 148u + tokens - 1) / tokens;
     if (slices > want) slices = want;
+    auto a16 = [](const void* p, uint64_t stride) { return (reinterpret_cast<uintptr_t>(p) | stride) % 16 == 0; };
+    const int vec4 = a16(routed, routed_stride) && a16(shared, shared_stride) && (!out || a16(out, out_stride)) &&
+                     (!out16 || (reinterpret_cast<uintptr_t>(out16) | out16_stride) % 8 == 0);
     combine_kernel<<<dim3(tokens, slices), kCombineThreads, 0, st>>>(routed, routed_stride, weights, shared, shared_stride, shared_router,
                                                        x, x_stride, shared_logit, channels, selected, out, out_stride,
-                                                       static_cast<__half*>(out16), out16_stride, error);
+                                                       static_cast<__half*>(out16), out16_stride, vec4, error);
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }

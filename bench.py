@@ -153,7 +153,7 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------------
-NCU_GATE_UP_DRAM_BYTES_PER_EXPERT = 457.6e6 / 359
+NCU_GATE_UP_DRAM_BYTES_PER_EXPERT = 457.2e6 / 361   # 360 routed experts + the shared expert in the captured launch
 
 
 def run_ours(args):
@@ -233,7 +233,7 @@ def run_ours(args):
     achieved = gu_bytes / (stages["gate_up_ms"] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "gemv3_kernel<planar, gate-up+SwiGLU> (routed experts + shared expert, one launch)", "achieved": achieved, "peak": hbm_peak,
                 "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (359 experts hit: 457.6 MB) scaled to the
+                # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (361 experts: 457.2 MB) scaled to the
                 # experts this run's batches hit; traffic grows with the experts touched, the activations stay in L2
                 "traffic": NCU_GATE_UP_DRAM_BYTES_PER_EXPERT * (U + 1), "traffic_source": "ncu capture scaled by experts hit",
                 "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": stages["gate_up_ms"]}

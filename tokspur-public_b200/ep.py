@@ -65,7 +65,7 @@ def combine(plan: RoutePlan, outputs: torch.Tensor, routed: torch.Tensor, group=
 # --------------------------------------------------------------------------------------------------
 class EpLayer:
     def __init__(self, seed: int, channels: int, hidden: int, experts: int, selected: int, rank: int, world: int, device, capacity: int,
-                 expert_type: int = 12, layout: int = 1):
+                 expert_type: int = 12, layout: int = 1, prefill: bool = False):
         from . import layer as L
         assert experts % world == 0
         self.rank, self.world, self.C, self.H, self.E, self.K = rank, world, channels, hidden, experts, selected
@@ -106,6 +106,22 @@ class EpLayer:
         self.g_zero = torch.zeros((G, channels), dtype=f32, device=device)
         self.rs_out = torch.zeros((capacity, channels), dtype=f32, device=device)
         self.ones = torch.ones(capacity, dtype=f32, device=device)
+        if prefill:
+            # prefill-size gathered scheme: the local experts' routes of all world*capacity rows through the grouped tensor-core
+            # GEMMs (permuted binary16 rows), the shared expert of the local rows through the same kernels
+            from . import capi
+            f16 = torch.float16
+            R = G * selected
+            self.p_tasks = z(int(capi.lib().tsp_moe_tasks_words(G, per, selected, 128)), i32)
+            self.p_offsets = z(per + 1, i32)
+            self.p_pos_route = z(R, i32)
+            self.p_xp = torch.zeros((R, channels), dtype=f16, device=device)
+            self.p_hp = torch.zeros((R, hidden), dtype=f16, device=device)
+            self.s_ids0 = z(capacity, i32)
+            self.s_token_map, self.s_counts, self.s_offsets, self.s_pos = z(capacity, i32), z(1, i32), z(2, i32), z(capacity, i32)
+            self.s_tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, 1, 1, 128)), i32)
+            self.s_xp = torch.zeros((capacity, channels), dtype=f16, device=device)
+            self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)
 
     def step(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
         from . import capi
@@ -177,6 +193,53 @@ class EpLayer:
                                        w.d_shared_router, x_local, Cn * 4, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
                                        out16.data_ptr(), out16.stride(0) * 2, e, st))
 
+    def step_gathered_prefill(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
+        """The gathered scheme at prefill size: all-gather rows + logits, route everything on every rank, run the routes that hit
+        local experts through the grouped tcgen05 GEMMs (tiles of 128 routes), mix them per token into partial sums,
+        reduce-scatter the partial sums, then add the local rows' shared expert. No host synchronisation, fixed-size collectives."""
+        from . import capi
+        from . import layer as L
+        lib, st, e = capi.lib(), L.stream_ptr(), self.error.data_ptr()
+        T, Cn, H, K, E, per = x16.shape[0], self.C, self.H, self.K, self.E, self.per
+        assert T == self.capacity, "the gathered scheme runs at the capacity it was built for"
+        G = T * self.world
+        R = G * K
+        w = self.w.weights
+        rowb = Cn * 2 + E * 4
+        self.pack[:, : Cn * 2].copy_(x16.view(torch.uint8).view(T, Cn * 2))
+        self.pack[:, Cn * 2:].copy_(logits.view(torch.uint8).view(T, E * 4))
+        dist.all_gather_into_tensor(self.gathered, self.pack)
+        gx, glg = self.gathered.data_ptr(), self.gathered.data_ptr() + Cn * 2
+        capi.check(lib.tsp_rows_f16_to_f32(gx, rowb, self.g_x32.data_ptr(), Cn * 4, G, Cn, st))
+        capi.check(lib.tsp_moe_route(glg, rowb, G, E, K, 0, 1, self.g_ids.data_ptr(), self.g_weights.data_ptr(), e, st))
+        capi.check(lib.tsp_moe_permute_local(self.g_ids.data_ptr(), G, self.rank * per, per, K, 128, self.g_token_map.data_ptr(),
+                                             self.counts.data_ptr(), self.p_tasks.data_ptr(), e, st))
+        capi.check(lib.tsp_moe_route_offsets(self.counts.data_ptr(), per, self.p_offsets.data_ptr(), st))
+        capi.check(lib.tsp_moe_gather_rows(self.g_x32.data_ptr(), Cn * 4, K, self.g_token_map.data_ptr(), self.p_offsets.data_ptr(), per, G, K, Cn,
+                                           self.p_xp.data_ptr(), Cn * 2, self.p_pos_route.data_ptr(), e, st))
+        capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), self.p_xp.data_ptr(), Cn * 2, R, self.p_tasks.data_ptr(),
+                                               self.counts.data_ptr(), self.p_offsets.data_ptr(), self.p_hp.data_ptr(), H * 2, e, st))
+        capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), self.p_hp.data_ptr(), H * 2, R, self.p_tasks.data_ptr(), self.counts.data_ptr(),
+                                            self.p_offsets.data_ptr(), self.p_pos_route.data_ptr(), self.g_routed.data_ptr(), Cn * 4, e, st))
+        local = (self.g_ids >= self.rank * per) & (self.g_ids < (self.rank + 1) * per)
+        w_local = torch.where(local, self.g_weights, torch.zeros_like(self.g_weights))   # zero weight = route not computed here
+        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, None,
+                                       G, Cn, K, self.g_partial.data_ptr(), Cn * 4, None, 0, e, st))
+        dist.reduce_scatter_tensor(self.rs_out, self.g_partial)
+        x_local = self.g_x32.data_ptr() + self.rank * T * Cn * 4
+        capi.check(lib.tsp_moe_permute(self.s_ids0.data_ptr(), T, 1, 1, 128, self.s_token_map.data_ptr(), self.s_counts.data_ptr(),
+                                       self.s_tasks.data_ptr(), e, st))
+        capi.check(lib.tsp_moe_route_offsets(self.s_counts.data_ptr(), 1, self.s_offsets.data_ptr(), st))
+        capi.check(lib.tsp_moe_gather_rows(x_local, Cn * 4, 1, self.s_token_map.data_ptr(), self.s_offsets.data_ptr(), 1, T, 1, Cn,
+                                           self.s_xp.data_ptr(), Cn * 2, self.s_pos.data_ptr(), e, st))
+        capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.shared_gate), C.byref(w.shared_up), self.s_xp.data_ptr(), Cn * 2, T, self.s_tasks.data_ptr(),
+                                               self.s_counts.data_ptr(), self.s_offsets.data_ptr(), self.s_hp.data_ptr(), H * 2, e, st))
+        capi.check(lib.tsp_moe_grouped_down(C.byref(w.shared_down), self.s_hp.data_ptr(), H * 2, T, self.s_tasks.data_ptr(), self.s_counts.data_ptr(),
+                                            self.s_offsets.data_ptr(), self.s_pos.data_ptr(), self.shared_out.data_ptr(), Cn * 4, e, st))
+        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
+                                       w.d_shared_router, x_local, Cn * 4, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
+                                       out16.data_ptr(), out16.stride(0) * 2, e, st))
+
     def error_word(self) -> int:
         torch.cuda.synchronize()
         return int(self.error.item()) & 0xFFFFFFFF
@@ -188,11 +251,14 @@ def run_bench(args, rank: int, world: int, local: int) -> None:
     from . import synth
     from bench import CHANNELS, HIDDEN, EXPERTS, SELECTED, ClockSampler
     dev = torch.device("cuda", local)
-    T = args.tokens
-    layers = [EpLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, SELECTED, rank, world, dev, T) for i in range(args.layers)]
-    nb = 8
+    prefill = getattr(args, "workload", "decode") == "prefill"
+    T = 4096 if prefill and args.tokens == 64 else args.tokens
+    layers = [EpLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, SELECTED, rank, world, dev, T, prefill=prefill) for i in range(2 if prefill else args.layers)]
+    nb = 2 if prefill else 8
+    bias = synth.zipf_bias(5, EXPERTS) if prefill else None
     host_x = [torch.from_numpy(synth.activations_f16(1000 + rank * 64 + b, T, CHANNELS)).pin_memory() for b in range(nb)]
-    host_lg = [torch.from_numpy(synth.router_logits(2000 + rank * 64 + b, T, EXPERTS)).pin_memory() for b in range(nb)]
+    host_lg = [torch.from_numpy(synth.router_logits(2000 + rank * 64 + b, T, EXPERTS, bias) if prefill else synth.router_logits(2000 + rank * 64 + b, T, EXPERTS)).pin_memory()
+               for b in range(nb)]
     dev_x = [t.to(dev) for t in host_x]
     dev_lg = [t.to(dev) for t in host_lg]
     out = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
@@ -201,6 +267,8 @@ def run_bench(args, rank: int, world: int, local: int) -> None:
     slg = torch.zeros((T, EXPERTS), dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream()
     step = EpLayer.step if getattr(args, "ep_scheme", "gather") == "alltoall" else EpLayer.step_gathered
+    if prefill:
+        step = EpLayer.step_gathered_prefill
 
     def resident(i):
         step(layers[i % len(layers)], dev_x[i % nb], dev_lg[i % nb], out)
@@ -239,7 +307,8 @@ def run_bench(args, rank: int, world: int, local: int) -> None:
         line = {"metric": "moe_q4k_expert_gemm_tokens_per_s", "value": total / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"moe_layer_decode_T{T}_per_gpu (BASELINE configs[1] shape, expert-parallel as configs[4])",
+                "config": {"workload": (f"moe_layer_prefill_T{T}_per_gpu (BASELINE configs[2] shape and router, expert-parallel as configs[4])" if prefill
+                                        else f"moe_layer_decode_T{T}_per_gpu (BASELINE configs[1] shape, expert-parallel as configs[4])"),
                            "hidden": CHANNELS, "experts": EXPERTS, "expert_ffn": HIDDEN, "top_k": SELECTED, "weights": "Q4_K Pack-v3 planar",
                            "parallelism": f"ep{world}", "experts_per_gpu": EXPERTS // world, "tokens_per_gpu": T,
                            "collectives": ("NCCL all-to-all dispatch (binary16 rows) + all-to-all combine (FP32 rows), one count exchange" if step is EpLayer.step
@@ -247,7 +316,7 @@ def run_bench(args, rank: int, world: int, local: int) -> None:
                            "l2_policy": "layers rotate; per step each GPU streams its hit experts once"},
                 "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": world * (T * CHANNELS * 2 + T * EXPERTS * 4), "d2h_bytes_per_step": world * T * CHANNELS * 2},
-                "gpu_launches": (10 if step is EpLayer.step else 12) * args.steps, "clocks": clocks.summary(),
+                "gpu_launches": (19 if prefill else 10 if step is EpLayer.step else 12) * args.steps, "clocks": clocks.summary(),
                 "roofline": None, "cpu_baseline": None}
         print(json.dumps(line), flush=True)
     dist.barrier()

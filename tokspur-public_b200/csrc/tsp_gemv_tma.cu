@@ -119,7 +119,7 @@ __device__ __forceinline__ Tile3 tile3(const Gemv3Params& p, uint32_t tile, uint
 // KB: super-blocks per unit. SPLIT: also run the low-half pass of the activations (needed unless every
 // activation is exactly a binary16 value).
 template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, int KB, bool SPLIT>
-__global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_constant__ Gemv3Maps maps, const __grid_constant__ Gemv3Params p) {
+__global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_constant__ Gemv3Maps maps, const Gemv3Params p) {
     extern __shared__ uint8_t smem3_raw[];
     // the 128-byte swizzle is a function of the shared-memory address: box bases must sit on 1024-byte boundaries
     uint8_t* smem3 = smem3_raw + ((1024u - (smem_u32(smem3_raw) & 1023u)) & 1023u);
@@ -141,12 +141,6 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
         for (uint32_t s = 0; s < S * kW3; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_fence_init();
     }
-    // A copy of the parameters in shared memory for the code that runs only at tile changes: its parameter reads
-    // would otherwise miss the constant cache every time (the inner loops keep theirs in registers).
-    static_assert(sizeof(Gemv3Params) <= 384, "parameter copy does not fit its shared-memory slot");
-    const Gemv3Params& sp = *reinterpret_cast<const Gemv3Params*>(smem3 + 5760);
-    if (threadIdx.x < sizeof(Gemv3Params) / 4)
-        reinterpret_cast<uint32_t*>(smem3 + 5760)[threadIdx.x] = reinterpret_cast<const uint32_t*>(&p)[threadIdx.x];
 
     const uint32_t routed_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
     const uint32_t n_tiles = routed_tiles + p.sh_tiles;
@@ -285,8 +279,8 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
     uint32_t item = item0;
     while (item < item1) {
         // ---- one token tile: the segment of this CTA's items that share it ----
-        const uint32_t tile = item / sp.groups;
-        const uint32_t seg_end = min(item1, (tile + 1) * sp.groups);
+        const uint32_t tile = item / p.groups;
+        const uint32_t seg_end = min(item1, (tile + 1) * p.groups);
         named_bar_sync(1, CT);   // every consumer warp is done with the previous tile's activations
         const Tile3 ti = get_tile(tile);
         const uint32_t* cur_rids = trid + (tile - t0) * 16;
@@ -294,9 +288,9 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
         if (tile - t0 >= kTableTiles) {   // beyond the cached window: fetch this tile's route ids now
             if (ctid < 8u * NC) {
                 uint32_t rid = 0;
-                if (ctid < ti.count) rid = (sp.token_map && ti.expert < sp.experts) ? sp.token_map[static_cast<uint64_t>(ti.expert) * sp.tokens + ti.start + ctid] : ti.start + ctid;
+                if (ctid < ti.count) rid = (p.token_map && ti.expert < p.experts) ? p.token_map[static_cast<uint64_t>(ti.expert) * p.tokens + ti.start + ctid] : ti.start + ctid;
                 rids[ctid] = rid;
-                rins[ctid] = ti.expert < sp.experts ? rid / sp.in_div : rid;
+                rins[ctid] = ti.expert < p.experts ? rid / p.in_div : rid;
             }
             cur_rids = rids;
             cur_rins = rins;
@@ -304,11 +298,11 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
         }
         {
             // Stage the tile's activation rows: 8-column chunks, four per thread in flight so that their global loads overlap.
-            const uint32_t per_row = sp.cols / 8;
+            const uint32_t per_row = p.cols / 8;
             const uint32_t units = ti.count * per_row;
-            const bool sh_tile = ti.expert >= sp.experts;
+            const bool sh_tile = ti.expert >= p.experts;
             bool bad = false;
-            if (sp.x16) {
+            if (p.x16) {
                 // binary16 rows: no conversion, only the reordering inside each run of 8 and the group sums; the first PF
                 // chunks of a thread were fetched ahead while the previous tile was computed
                 const bool fetched = pf_tile == tile;
@@ -323,7 +317,7 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                         if (u < units) {
                             jj[i] = u / per_row; kk[i] = u - jj[i] * per_row;
                             if (i < PF && base == 0 && fetched) vv[i] = pf[i < PF ? i : 0];
-                            else vv[i] = *(reinterpret_cast<const uint4*>(sp.x16 + cur_rins[jj[i]] * sp.x16_stride_bytes) + kk[i]);
+                            else vv[i] = *(reinterpret_cast<const uint4*>(p.x16 + cur_rins[jj[i]] * p.x16_stride_bytes) + kk[i]);
                         }
                     }
 #pragma unroll
@@ -341,9 +335,9 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                         }
                         if (active) {
                             // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
-                            *reinterpret_cast<uint4*>(xhi + j * sp.x_stride + k8 * 16) =
+                            *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) =
                                 make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[0], w[1], 0x7632), __byte_perm(w[2], w[3], 0x5410), __byte_perm(w[2], w[3], 0x7632));
-                            if (SPLIT) *reinterpret_cast<uint4*>(xlo + j * sp.x_stride + k8 * 16) = make_uint4(0, 0, 0, 0);
+                            if (SPLIT) *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) = make_uint4(0, 0, 0, 0);
                         }
                         s += __shfl_xor_sync(0xffffffffu, s, 1);
                         s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -352,8 +346,8 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                             const __half sh = __float2half_rn(s);
                             const __half sl = __float2half_rn(s - __half2float(sh));
                             bad |= !finite_f32(__half2float(sh));
-                            *reinterpret_cast<__half*>(sxb + j * sp.sx_stride + grp * 2) = sh;
-                            *reinterpret_cast<__half*>(sxb + (8u * NC + j) * sp.sx_stride + grp * 2) = sl;
+                            *reinterpret_cast<__half*>(sxb + j * p.sx_stride + grp * 2) = sh;
+                            *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
                         }
                     }
                 }
@@ -367,14 +361,14 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                         const uint32_t u = i * CT + ctid;
                         if (u < tn.count * per_row) {
                             const uint32_t jn = u / per_row, kn = u - jn * per_row;
-                            pf[i] = *(reinterpret_cast<const uint4*>(sp.x16 + nrins[jn] * sp.x16_stride_bytes) + kn);
+                            pf[i] = *(reinterpret_cast<const uint4*>(p.x16 + nrins[jn] * p.x16_stride_bytes) + kn);
                         }
                     }
                     pf_tile = tile + 1;
                 }
             } else {
-                const char* xsrc = sh_tile ? reinterpret_cast<const char*>(sp.sh_x) : reinterpret_cast<const char*>(sp.x);
-                const uint64_t xsrc_stride = sh_tile ? sp.sh_x_stride_bytes : sp.x_stride_bytes;
+                const char* xsrc = sh_tile ? reinterpret_cast<const char*>(p.sh_x) : reinterpret_cast<const char*>(p.x);
+                const uint64_t xsrc_stride = sh_tile ? p.sh_x_stride_bytes : p.x_stride_bytes;
                 for (uint32_t base = 0; base < units; base += 4 * CT) {
                     float4 va[4], vb[4];
                     uint32_t jj[4], kk[4];
@@ -408,10 +402,10 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                         }
                         if (active) {
                             // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
-                            *reinterpret_cast<uint4*>(xhi + j * sp.x_stride + k8 * 16) =
+                            *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) =
                                 make_uint4(hb[0] | (hb[2] << 16), hb[1] | (hb[3] << 16), hb[4] | (hb[6] << 16), hb[5] | (hb[7] << 16));
                             if (SPLIT)
-                                *reinterpret_cast<uint4*>(xlo + j * sp.x_stride + k8 * 16) =
+                                *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) =
                                     make_uint4(lb[0] | (lb[2] << 16), lb[1] | (lb[3] << 16), lb[4] | (lb[6] << 16), lb[5] | (lb[7] << 16));
                         }
                         s += __shfl_xor_sync(0xffffffffu, s, 1);
@@ -421,13 +415,13 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                             const __half sh = __float2half_rn(s);
                             const __half sl = __float2half_rn(s - __half2float(sh));
                             bad |= !finite_f32(__half2float(sh));
-                            *reinterpret_cast<__half*>(sxb + j * sp.sx_stride + grp * 2) = sh;
-                            *reinterpret_cast<__half*>(sxb + (8u * NC + j) * sp.sx_stride + grp * 2) = sl;
+                            *reinterpret_cast<__half*>(sxb + j * p.sx_stride + grp * 2) = sh;
+                            *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
                         }
                     }
                 }
             }
-            if (bad) raise_error(sp.error, TSP_ERR_NONFINITE);
+            if (bad) raise_error(p.error, TSP_ERR_NONFINITE);
         }
         named_bar_sync(1, CT);
         // this lane's output rows (tokens 2t, 2t+1 of each column block) for the whole tile
@@ -438,8 +432,8 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
             for (int q = 0; q < 2; ++q) {
                 const uint32_t j = c * 8 + 2 * t + q;
                 orow[c][q] = j >= ti.count ? nullptr
-                             : reinterpret_cast<float*>(ti.expert >= sp.experts ? reinterpret_cast<char*>(sp.sh_out) + cur_rids[j] * sp.sh_out_stride_bytes
-                                                                               : reinterpret_cast<char*>(sp.out) + cur_rids[j] * sp.out_stride_bytes);
+                             : reinterpret_cast<float*>(ti.expert >= p.experts ? reinterpret_cast<char*>(p.sh_out) + cur_rids[j] * p.sh_out_stride_bytes
+                                                                               : reinterpret_cast<char*>(p.out) + cur_rids[j] * p.out_stride_bytes);
             }
 
         // ---- this warp's row groups of the segment ----

@@ -13,7 +13,7 @@
 //   warps 2..9  dequantise (two warps per SM sub-partition, a thread per half row of a K chunk): read 4-bit codes +
 //               6-bit factors from the quant stage, write binary16 weights in the K-major 128-byte-swizzled operand layout.
 //   warp 10     TMA producer of the activation tiles (tokens x 64 binary16, 128-byte swizzled) of every K chunk.
-//   warps 11..14 epilogue: tcgen05.ld of their 32 accumulator lanes, SwiGLU / store. The accumulators are double-buffered
+//   warps 11..   epilogue (4 warps for gate-up, 8 for down): tcgen05.ld of their 32 accumulator lanes, SwiGLU / store. The accumulators are double-buffered
 //               in tensor memory (2 x 256 columns), so the epilogue of an item runs under the MMAs of the next one.
 // Accumulation is FP32 in tensor memory. Operands are binary16 (kind::f16, f16 inputs): the activations of this path are
 // binary16-exact, and Q4_K values keep 11 significant bits instead of bf16's 8, which keeps the two chained GEMMs well
@@ -94,10 +94,11 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
 }
 
 constexpr uint32_t kDqWarps = 8;           // dequantise warps: two per SM sub-partition, each thread half a row of a K chunk
-constexpr uint32_t kEpWarps = 4;           // epilogue warps: one per tensor-memory lane quarter
-constexpr uint32_t kGWarps = 3 + kDqWarps + kEpWarps; // weight producer, MMA, dequant warps, activation producer, epilogue warps
+// epilogue warps: one per tensor-memory lane quarter for gate-up; two for down, whose items are short (8 K chunks) and
+// whose epilogue (FP32 rows scattered to their route ids) would otherwise hold up the MMAs
+__host__ __device__ constexpr uint32_t ep_warps(bool gateup) { return gateup ? 4u : 8u; }
+__host__ __device__ constexpr uint32_t g_warps(bool gateup) { return 3 + kDqWarps + ep_warps(gateup); }   // weight producer, MMA, dequant warps, activation producer, epilogue warps
 constexpr uint32_t kMaxBStages = 8;
-constexpr uint32_t kGThreads = kGWarps * 32;
 constexpr uint32_t kTileRoutes = 128;      // routes per tile (N extent at most)
 constexpr uint32_t kRowsM = 128;           // weight rows per CTA tile (M)
 constexpr uint32_t kChunkK = 64;           // K per pipeline step: 64 binary16 = one 128-byte swizzled row
@@ -149,7 +150,7 @@ __device__ __forceinline__ void tma_load_5d_g(void* smem_dst, const CUtensorMap*
 // GATEUP: two weight matrices (gate, up) and the SwiGLU epilogue writing binary16 hidden rows in permuted position order;
 // otherwise one matrix and FP32 rows scattered to their route ids.
 template <bool GATEUP>
-__global__ void __launch_bounds__(kGThreads, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
+__global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
     extern __shared__ uint8_t gsm_raw[];
     uint8_t* gsm = gsm_raw + ((1024u - (smem_u32(gsm_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(gsm);
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_mma_kernel(const __grid_
             mbar_init(&dfull[s], 1); mbar_init(&dempty[s], kDqWarps);
         }
         for (uint32_t s = 0; s < NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kEpWarps); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], ep_warps(GATEUP)); }
         mbar_fence_init();
     }
     if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }   // two accumulator sets of 256 columns: the epilogue of an item overlaps the MMAs of the next
@@ -357,8 +358,10 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_mma_kernel(const __grid_
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else {
-        // =========================== epilogue (the last kEpWarps warps) ===========================
+        // =========================== epilogue (the last ep_warps warps) ===========================
         const uint32_t quarter = warp & 3u;                   // tensor-memory lane quarter this warp may read
+        constexpr uint32_t EH = ep_warps(GATEUP) / 4;         // warps per quarter: they take the 32-column batches in turn
+        const uint32_t ehalf = (warp - (3 + kDqWarps)) >> 2;
         bool ok = true;
         uint32_t ab = 0, accph = 0, cur_tile = 0xffffffffu;
         GTile t{};
@@ -383,7 +386,7 @@ __global__ void __launch_bounds__(kGThreads, 1) grouped_mma_kernel(const __grid_
                 const uint32_t hcol = (wrow & ~7u) | ((wrow & 4u) | ((wrow & 1u) << 1) | ((wrow & 2u) >> 1));
                 char* hrow = reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(t.row0) * p.out_stride_bytes + (GATEUP ? hcol * 2 : 0);
                 bool bad = false;
-                for (uint32_t j0 = 0; j0 < t.ncols && j0 < t.count; j0 += 32) {
+                for (uint32_t j0 = ehalf * 32; j0 < t.ncols && j0 < t.count; j0 += 32 * EH) {
                     uint32_t g[32], u[GATEUP ? 32 : 1];
                     const uint32_t rq = j0 < 32 ? rt[0] : (j0 < 64 ? rt[1] : (j0 < 96 ? rt[2] : rt[3]));   // this lane's route id in the 32-wide group of j0
                     tmem_ld32(taddr + j0, g);
@@ -503,7 +506,7 @@ static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    kernel<<<grid, kGThreads, smem, st>>>(m, p);
+    kernel<<<grid, g_warps(GATEUP) * 32, smem, st>>>(m, p);
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }

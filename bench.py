@@ -192,16 +192,24 @@ def run_ours(args):
     dev_lg = [t.to(dev) for t in host_lg]
     out = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
     host_out = torch.zeros((T, CHANNELS), dtype=torch.float16).pin_memory()
-    stage_x = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
-    stage_lg = torch.zeros((T, EXPERTS), dtype=torch.float32, device=dev)
+    # end-to-end arm: a step's token rows and router logits travel as ONE pinned buffer and one host->device copy
+    xb, lb = T * CHANNELS * 2, T * EXPERTS * 4
+    host_pack = []
+    for b_ in range(nb):
+        hp = torch.empty(xb + lb, dtype=torch.uint8).pin_memory()
+        hp[:xb].copy_(host_x[b_].view(torch.uint8).view(-1))
+        hp[xb:].copy_(host_lg[b_].view(torch.uint8).view(-1))
+        host_pack.append(hp)
+    stage = torch.zeros(xb + lb, dtype=torch.uint8, device=dev)
+    stage_x = stage[:xb].view(torch.float16).view(T, CHANNELS)
+    stage_lg = stage[xb:].view(torch.float32).view(T, EXPERTS)
     stream = torch.cuda.current_stream()
 
     def step_resident(i):
         L.moe_layer_decode(layers[i % len(layers)], scratch, dev_x[i % nb], dev_lg[i % nb], out)
 
     def step_e2e(i):
-        stage_x.copy_(host_x[i % nb], non_blocking=True)
-        stage_lg.copy_(host_lg[i % nb], non_blocking=True)
+        stage.copy_(host_pack[i % nb], non_blocking=True)
         L.moe_layer_decode(layers[i % len(layers)], scratch, stage_x, stage_lg, out)
         host_out.copy_(out, non_blocking=True)
         stream.synchronize()
@@ -326,7 +334,7 @@ def run_prefill(args, local):
     def stage_pass(steps):
         """CUDA-event time of each launch of the prefill layer."""
         s, st = ps.base, L.stream_ptr()
-        names = ["convert", "route", "permute", "offsets", "gather", "gate_up", "down", "shared", "combine"]
+        names = ["convert", "route", "permute", "offsets", "gather", "gate_up", "down", "combine"]
         acc = dict.fromkeys(names, 0.0)
         C4, E, K = CHANNELS * 4, EXPERTS, SELECTED
         for i in range(steps):
@@ -340,21 +348,18 @@ def run_prefill(args, local):
             capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, E, K, 128, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), e, st)); ev[3].record()
             capi.check(lib.tsp_moe_route_offsets(s.counts.data_ptr(), E, ps.offsets.data_ptr(), st)); ev[4].record()
             capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), C4, K, s.token_map.data_ptr(), ps.offsets.data_ptr(), E, T, K, CHANNELS,
-                                               ps.xp.data_ptr(), CHANNELS * 2, ps.pos_route.data_ptr(), e, st)); ev[5].record()
-            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), ps.xp.data_ptr(), CHANNELS * 2, T * K, ps.tasks.data_ptr(),
-                                                   s.counts.data_ptr(), ps.offsets.data_ptr(), ps.hp.data_ptr(), HIDDEN * 2, e, st)); ev[6].record()
-            capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), ps.hp.data_ptr(), HIDDEN * 2, T * K, ps.tasks.data_ptr(), s.counts.data_ptr(),
-                                                ps.offsets.data_ptr(), ps.pos_route.data_ptr(), s.routed.data_ptr(), C4, e, st)); ev[7].record()
-            capi.check(lib.tsp_moe_permute(ps.ids0.data_ptr(), T, 1, 1, 128, ps.s_token_map.data_ptr(), ps.s_counts.data_ptr(), ps.s_tasks.data_ptr(), e, st))
-            capi.check(lib.tsp_moe_route_offsets(ps.s_counts.data_ptr(), 1, ps.s_offsets.data_ptr(), st))
-            capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), C4, 1, ps.s_token_map.data_ptr(), ps.s_offsets.data_ptr(), 1, T, 1, CHANNELS,
-                                               ps.s_xp.data_ptr(), CHANNELS * 2, ps.s_pos.data_ptr(), e, st))
-            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.shared_gate), C.byref(w.shared_up), ps.s_xp.data_ptr(), CHANNELS * 2, T, ps.s_tasks.data_ptr(),
-                                                   ps.s_counts.data_ptr(), ps.s_offsets.data_ptr(), ps.s_hp.data_ptr(), HIDDEN * 2, e, st))
-            capi.check(lib.tsp_moe_grouped_down(C.byref(w.shared_down), ps.s_hp.data_ptr(), HIDDEN * 2, T, ps.s_tasks.data_ptr(), ps.s_counts.data_ptr(),
-                                                ps.s_offsets.data_ptr(), ps.s_pos.data_ptr(), s.shared_out.data_ptr(), C4, e, st)); ev[8].record()
+                                               ps.xp.data_ptr(), CHANNELS * 2, ps.pos_route.data_ptr(), e, st))
+            capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), C4, 1, None, None, 1, T, 1, CHANNELS, ps.s_xp.data_ptr(), CHANNELS * 2, None, e, st)); ev[5].record()
+            # routed experts + shared expert in one launch each, exactly as tsp_moe_layer_prefill issues them
+            capi.check(lib.tsp_moe_grouped_gate_up_shared(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up), ps.xp.data_ptr(),
+                                                          CHANNELS * 2, T * K, ps.tasks.data_ptr(), s.counts.data_ptr(), ps.offsets.data_ptr(),
+                                                          ps.hp.data_ptr(), HIDDEN * 2, ps.s_xp.data_ptr(), CHANNELS * 2, T, ps.s_hp.data_ptr(),
+                                                          HIDDEN * 2, e, st)); ev[6].record()
+            capi.check(lib.tsp_moe_grouped_down_shared(C.byref(w.down), C.byref(w.shared_down), ps.hp.data_ptr(), HIDDEN * 2, T * K, ps.tasks.data_ptr(),
+                                                       s.counts.data_ptr(), ps.offsets.data_ptr(), ps.pos_route.data_ptr(), s.routed.data_ptr(), C4,
+                                                       ps.s_hp.data_ptr(), HIDDEN * 2, T, s.shared_out.data_ptr(), C4, e, st)); ev[7].record()
             capi.check(lib.tsp_moe_combine(s.routed.data_ptr(), C4, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
-                                           x32.data_ptr(), C4, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), CHANNELS * 2, e, st)); ev[9].record()
+                                           x32.data_ptr(), C4, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), CHANNELS * 2, e, st)); ev[8].record()
             torch.cuda.synchronize()
             for k_, n in enumerate(names):
                 acc[n] += ev[k_].elapsed_time(ev[k_ + 1])
@@ -366,7 +371,7 @@ def run_prefill(args, local):
         stages = stage_pass(max(2, min(args.steps, 5)))
     assert ps.base.error_word() == 0, "device error word set during the benchmark"
     _, tf_peak, peak_kind = peaks()
-    gu_flops = T * SELECTED * 2 * (2 * HIDDEN * CHANNELS)
+    gu_flops = T * (SELECTED + 1) * 2 * (2 * HIDDEN * CHANNELS)   # the launch carries the routed experts and the shared expert
     achieved = gu_flops / (stages["gate_up_ms"] * 1e-3) / 1e12
     cpu = parity = None
     if args.cpu_tokens != 0:
@@ -393,8 +398,8 @@ def run_prefill(args, local):
                        "l2_policy": "inputs larger than L2: 0.93 GB of weights and 0.5 GB of intermediates per step"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2},
-            "gpu_launches": 16 * args.steps, "clocks": clocks.summary(),
-            "roofline": {"bound": "tensor", "kernel": "grouped_mma_kernel<gate-up> (routed experts, tcgen05)", "achieved": achieved, "peak": tf_peak,
+            "gpu_launches": 11 * args.steps, "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "kernel": "grouped_mma_kernel<gate-up> (routed experts + shared expert, tcgen05)", "achieved": achieved, "peak": tf_peak,
                          "unit": "TFLOP/s", "frac": achieved / tf_peak, "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_flops_per_launch": gu_flops, "launch_ms": stages["gate_up_ms"]},
             "cpu_baseline": cpu,

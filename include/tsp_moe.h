@@ -241,7 +241,9 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
  *   5. tsp_moe_grouped_down                                    routed[route][channel] FP32, scattered by route id
  * Row buffers in permuted order (d_xp, d_hp) hold max_positions = tokens*selected rows. Values inside each aligned run of 8
  * along the row are stored in the order 0,2,1,3,4,6,5,7 (the order the dequantised weight tiles use), which only these
- * kernels read. Operands are binary16, accumulation FP32. */
+ * kernels read. Operands are binary16, accumulation FP32.
+ * tsp_moe_gather_rows with d_token_map = d_offsets = NULL (then selected = in_div = 1, d_pos_route may be NULL) converts the
+ * `tokens` rows in place order: the input rows of a dense expert. */
 #define TSP_GROUPED_TILE 128u
 int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* d_offsets, void* stream);
 int tsp_moe_gather_rows(const float* d_x, uint64_t x_stride_bytes, uint32_t in_div, const uint32_t* d_token_map,
@@ -254,30 +256,39 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const void* d_hp, uint64_t 
                          const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, const uint32_t* d_pos_route,
                          float* d_routed, uint64_t routed_stride_bytes, uint32_t* d_error, void* stream);
 
+/* The two grouped GEMMs with the layer's dense shared expert in the same launch: its token tiles (every one of `tokens`
+ * rows in row order; position = token = route id) follow the routed tiles, as `encode_moe_mm_many` runs the shared
+ * expert's dense projections right after the routed ones (moe_mm_many.cpp:189-214). The shared matrix sets must have the
+ * routed experts' shape, encoding and layout. d_s_xp: binary16 rows [tokens x channels] in the K order of
+ * tsp_moe_gather_rows (call it with NULL tables); d_s_hp: binary16 rows [tokens x hidden]; d_shared_out: FP32 [tokens x channels]. */
+int tsp_moe_grouped_gate_up_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                                   const tsp_matrix_set* shared_up, const void* d_xp, uint64_t xp_stride_bytes, uint32_t max_positions,
+                                   const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, void* d_hp,
+                                   uint64_t hp_stride_bytes, const void* d_s_xp, uint64_t s_xp_stride_bytes, uint32_t tokens, void* d_s_hp,
+                                   uint64_t s_hp_stride_bytes, uint32_t* d_error, void* stream);
+int tsp_moe_grouped_down_shared(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride_bytes,
+                                uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
+                                const uint32_t* d_pos_route, float* d_routed, uint64_t routed_stride_bytes, const void* d_s_hp,
+                                uint64_t s_hp_stride_bytes, uint32_t tokens, float* d_shared_out, uint64_t shared_out_stride_bytes,
+                                uint32_t* d_error, void* stream);
+
 /* One whole MoE FFN sub-layer at prefill size: route -> permute (tiles of TSP_GROUPED_TILE) -> offsets -> gather ->
- * grouped gate-up + SwiGLU -> grouped down -> shared expert (as a one-expert set over every token row, same kernels) ->
- * gated mixture. Replaces `encode_moe_mm_many` after its router projection (moe_mm_many.cpp:126-220) on the
- * `planar_nax_grouped_moe` path (graph.mm:9293-9420). Weights: Q4_K Pack v3 planar, hidden and channels multiples of 128,
- * channels and hidden multiples of 256. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
+ * grouped gate-up + SwiGLU -> grouped down (the dense shared expert rides in both launches) -> gated mixture.
+ * Replaces `encode_moe_mm_many` after its router projection (moe_mm_many.cpp:126-220) on the `planar_nax_grouped_moe`
+ * path (graph.mm:9293-9420). Weights: Q4_K Pack v3 planar, hidden and channels multiples of 256; the shared expert in the
+ * same form. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
  * Caller-owned scratch, all device memory, nothing has to start at zero:
  *   base: as for the decode layer, except d_tasks sized tsp_moe_tasks_words(capacity, experts, selected, TSP_GROUPED_TILE);
  *         d_hidden and d_shared_hidden are not used and may be NULL;
  *   d_xp / d_hp: binary16 rows in permuted position order, [capacity*selected x channels] / [capacity*selected x hidden];
  *   d_offsets [experts + 1], d_pos_route [capacity*selected];
- *   shared expert: d_ids0 [capacity], d_s_token_map [capacity], d_s_counts [1], d_s_offsets [2], d_s_pos [capacity],
- *   d_s_tasks [tsp_moe_tasks_words(capacity, 1, 1, TSP_GROUPED_TILE)], d_s_xp [capacity x channels], d_s_hp [capacity x hidden]. */
+ *   d_s_xp / d_s_hp: the shared expert's binary16 input and hidden rows in row order, [capacity x channels] / [capacity x hidden]. */
 typedef struct tsp_moe_prefill_scratch {
     tsp_moe_scratch base;
     void* d_xp;
     void* d_hp;
     uint32_t* d_offsets;
     uint32_t* d_pos_route;
-    uint32_t* d_ids0;
-    uint32_t* d_s_token_map;
-    uint32_t* d_s_counts;
-    uint32_t* d_s_offsets;
-    uint32_t* d_s_pos;
-    uint32_t* d_s_tasks;
     void* d_s_xp;
     void* d_s_hp;
 } tsp_moe_prefill_scratch;

@@ -42,8 +42,7 @@ class MoeScratch(C.Structure):
 
 class MoePrefillScratch(C.Structure):
     _fields_ = [("base", MoeScratch), ("d_xp", C.c_void_p), ("d_hp", C.c_void_p), ("d_offsets", C.c_void_p), ("d_pos_route", C.c_void_p),
-                ("d_ids0", C.c_void_p), ("d_s_token_map", C.c_void_p), ("d_s_counts", C.c_void_p), ("d_s_offsets", C.c_void_p),
-                ("d_s_pos", C.c_void_p), ("d_s_tasks", C.c_void_p), ("d_s_xp", C.c_void_p), ("d_s_hp", C.c_void_p)]
+                ("d_s_xp", C.c_void_p), ("d_s_hp", C.c_void_p)]
 
 
 class MoeWeights(C.Structure):
@@ -82,6 +81,8 @@ SIGNATURES = {
     "tsp_moe_gather_rows": (_i, [_vp, _u64, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp, _vp, _vp]),
     "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
     "tsp_moe_grouped_down": (_i, [_MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
+    "tsp_moe_grouped_gate_up_shared": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
+    "tsp_moe_grouped_down_shared": (_i, [_MS, _MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
     "tsp_moe_layer_decode_static_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
     "tsp_moe_layer_decode_static": (_i, [C.POINTER(MoeWeights), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u32, _i,
                                          _vp, _u64, _u32, _vp, _vp]),

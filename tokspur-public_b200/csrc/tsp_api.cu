@@ -50,7 +50,7 @@ int launch_route_offsets(const uint32_t*, uint32_t, uint32_t*, cudaStream_t);
 int launch_gather_rows(const float*, uint64_t, uint32_t, const uint32_t*, const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, void*, uint64_t,
                        uint32_t*, uint32_t*, cudaStream_t);
 int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, const uint32_t*, const uint32_t*,
-                   const uint32_t*, const uint32_t*, void*, uint64_t, uint32_t*, cudaStream_t);
+                   const uint32_t*, const uint32_t*, void*, uint64_t, uint32_t*, cudaStream_t, const GroupedShared* = nullptr);
 int launch_gemv_f32(const float*, uint32_t, uint32_t, const float*, uint64_t, uint32_t, float*, uint64_t, uint32_t*, cudaStream_t);
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
@@ -383,7 +383,8 @@ int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* 
 int tsp_moe_gather_rows(const float* d_x, uint64_t x_stride, uint32_t in_div, const uint32_t* d_token_map, const uint32_t* d_offsets,
                         uint32_t experts, uint32_t tokens, uint32_t selected, uint32_t cols, void* d_xp, uint64_t xp_stride,
                         uint32_t* d_pos_route, uint32_t* d_error, void* stream) {
-    TSP_REQUIRE(d_token_map && d_offsets && d_pos_route, "gather: null table");
+    TSP_REQUIRE((d_token_map != nullptr) == (d_offsets != nullptr), "gather: token map and offsets go together");
+    TSP_REQUIRE(d_token_map ? d_pos_route != nullptr : (selected == 1 && in_div == 1), "gather: a routed gather needs the position table; a dense one has selected = in_div = 1");
     TSP_REQUIRE(tokens >= 1 && selected >= 1 && selected <= 64 && in_div >= 1 && cols >= 8 && cols % 8 == 0, "gather: invalid shape");
     if (int rc = check_rows(d_x, x_stride, cols, 4, "gather input")) return rc;
     if (int rc = check_rows(d_xp, xp_stride, cols, 2, "gather output")) return rc;
@@ -415,6 +416,52 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const void* d_hp, uint64_t 
     if (int rc = check_rows(d_routed, routed_stride, down->rows, 4, "grouped down output")) return rc;
     return launch_grouped(down, nullptr, false, d_hp, hp_stride, max_positions, d_tasks, d_counts, d_offsets, d_pos_route, d_routed,
                           routed_stride, d_error, static_cast<cudaStream_t>(stream));
+}
+
+// The grouped GEMMs with the layer's dense shared expert in the same launch (its token tiles follow the routed tiles).
+static int check_shared_set(const tsp_matrix_set* s, const tsp_matrix_set* like, const char* name) {
+    if (int rc = check_matrix(s, name)) return rc;
+    TSP_REQUIRE(s->experts == 1 && s->type == like->type && s->layout == like->layout && s->rows == like->rows && s->cols == like->cols,
+                "%s: the shared expert must have the routed experts' shape, encoding and layout", name);
+    return TSP_OK;
+}
+
+int tsp_moe_grouped_gate_up_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                                   const tsp_matrix_set* shared_up, const void* d_xp, uint64_t xp_stride, uint32_t max_positions,
+                                   const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, void* d_hp, uint64_t hp_stride,
+                                   const void* d_s_xp, uint64_t s_xp_stride, uint32_t tokens, void* d_s_hp, uint64_t s_hp_stride,
+                                   uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(gate, "gate")) return rc;
+    if (int rc = check_matrix(up, "up")) return rc;
+    TSP_REQUIRE(gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
+                gate->experts == up->experts && gate->expert_stride == up->expert_stride && gate->split == up->split,
+                "gate/up matrix sets must share shape, encoding, layout and addressing");
+    if (int rc = check_shared_set(shared_gate, gate, "shared gate")) return rc;
+    if (int rc = check_shared_set(shared_up, gate, "shared up")) return rc;
+    TSP_REQUIRE(d_tasks && d_counts && d_offsets && max_positions >= 1 && tokens >= 1, "grouped gate-up: null table");
+    if (int rc = check_rows(d_xp, xp_stride, gate->cols, 2, "grouped gate-up input")) return rc;
+    if (int rc = check_rows(d_hp, hp_stride, gate->rows, 2, "grouped gate-up output")) return rc;
+    if (int rc = check_rows(d_s_xp, s_xp_stride, gate->cols, 2, "shared gate-up input")) return rc;
+    if (int rc = check_rows(d_s_hp, s_hp_stride, gate->rows, 2, "shared gate-up output")) return rc;
+    const GroupedShared sh{shared_gate, shared_up, d_s_xp, s_xp_stride, tokens, d_s_hp, s_hp_stride};
+    return launch_grouped(gate, up, true, d_xp, xp_stride, max_positions, d_tasks, d_counts, d_offsets, nullptr, d_hp, hp_stride, d_error,
+                          static_cast<cudaStream_t>(stream), &sh);
+}
+
+int tsp_moe_grouped_down_shared(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride,
+                                uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
+                                const uint32_t* d_pos_route, float* d_routed, uint64_t routed_stride, const void* d_s_hp, uint64_t s_hp_stride,
+                                uint32_t tokens, float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(down, "down")) return rc;
+    if (int rc = check_shared_set(shared_down, down, "shared down")) return rc;
+    TSP_REQUIRE(d_tasks && d_counts && d_offsets && d_pos_route && max_positions >= 1 && tokens >= 1, "grouped down: null table");
+    if (int rc = check_rows(d_hp, hp_stride, down->cols, 2, "grouped down input")) return rc;
+    if (int rc = check_rows(d_routed, routed_stride, down->rows, 4, "grouped down output")) return rc;
+    if (int rc = check_rows(d_s_hp, s_hp_stride, down->cols, 2, "shared down input")) return rc;
+    if (int rc = check_rows(d_shared_out, shared_out_stride, down->rows, 4, "shared down output")) return rc;
+    const GroupedShared sh{shared_down, nullptr, d_s_hp, s_hp_stride, tokens, d_shared_out, shared_out_stride};
+    return launch_grouped(down, nullptr, false, d_hp, hp_stride, max_positions, d_tasks, d_counts, d_offsets, d_pos_route, d_routed,
+                          routed_stride, d_error, static_cast<cudaStream_t>(stream), &sh);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -470,8 +517,7 @@ int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratc
                 w->shared_up.experts == 1 && w->shared_down.rows == channels && w->shared_down.cols == hidden &&
                 w->shared_down.experts == 1, "prefill layer: weight shapes do not match the layer shape");
     TSP_REQUIRE(s->d_ids && s->d_weights && s->d_routed && s->d_shared_out && s->d_token_map && s->d_counts && s->d_tasks && ps->d_xp &&
-                ps->d_hp && ps->d_offsets && ps->d_pos_route && ps->d_ids0 && ps->d_s_token_map && ps->d_s_counts && ps->d_s_offsets &&
-                ps->d_s_pos && ps->d_s_tasks && ps->d_s_xp && ps->d_s_hp, "prefill layer: incomplete scratch");
+                ps->d_hp && ps->d_offsets && ps->d_pos_route && ps->d_s_xp && ps->d_s_hp, "prefill layer: incomplete scratch");
     TSP_REQUIRE(x_dtype == 0 || s->d_x32, "prefill layer: binary16 input needs the d_x32 staging rows");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const float* x32 = static_cast<const float*>(d_x);
@@ -487,20 +533,15 @@ int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratc
     if (int rc = tsp_moe_route_offsets(s->d_counts, experts, ps->d_offsets, st)) return rc;
     if (int rc = tsp_moe_gather_rows(x32, x32_stride, selected, s->d_token_map, ps->d_offsets, experts, tokens, selected, channels, ps->d_xp,
                                      channels * 2ull, ps->d_pos_route, d_error, st)) return rc;
-    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, ps->d_xp, channels * 2ull, routes, s->d_tasks, s->d_counts, ps->d_offsets, ps->d_hp,
-                                         hidden * 2ull, d_error, st)) return rc;
-    if (int rc = tsp_moe_grouped_down(&w->down, ps->d_hp, hidden * 2ull, routes, s->d_tasks, s->d_counts, ps->d_offsets, ps->d_pos_route,
-                                      s->d_routed, channels * 4ull, d_error, st)) return rc;
-    // the dense shared expert through the same kernels: one expert, every token row routed to it
-    TSP_CUDA(cudaMemsetAsync(ps->d_ids0, 0, tokens * sizeof(uint32_t), st));
-    if (int rc = tsp_moe_permute(ps->d_ids0, tokens, 1, 1, TSP_GROUPED_TILE, ps->d_s_token_map, ps->d_s_counts, ps->d_s_tasks, d_error, st)) return rc;
-    if (int rc = tsp_moe_route_offsets(ps->d_s_counts, 1, ps->d_s_offsets, st)) return rc;
-    if (int rc = tsp_moe_gather_rows(x32, x32_stride, 1, ps->d_s_token_map, ps->d_s_offsets, 1, tokens, 1, channels, ps->d_s_xp, channels * 2ull,
-                                     ps->d_s_pos, d_error, st)) return rc;
-    if (int rc = tsp_moe_grouped_gate_up(&w->shared_gate, &w->shared_up, ps->d_s_xp, channels * 2ull, tokens, ps->d_s_tasks, ps->d_s_counts,
-                                         ps->d_s_offsets, ps->d_s_hp, hidden * 2ull, d_error, st)) return rc;
-    if (int rc = tsp_moe_grouped_down(&w->shared_down, ps->d_s_hp, hidden * 2ull, tokens, ps->d_s_tasks, ps->d_s_counts, ps->d_s_offsets, ps->d_s_pos,
-                                      s->d_shared_out, channels * 4ull, d_error, st)) return rc;
+    // the dense shared expert rides in the routed launches: its rows need no tables, only the binary16 copy in the K order
+    // the tensor-core tiles use
+    if (int rc = tsp_moe_gather_rows(x32, x32_stride, 1, nullptr, nullptr, 1, tokens, 1, channels, ps->d_s_xp, channels * 2ull, nullptr, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_gate_up_shared(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xp, channels * 2ull, routes, s->d_tasks,
+                                                s->d_counts, ps->d_offsets, ps->d_hp, hidden * 2ull, ps->d_s_xp, channels * 2ull, tokens, ps->d_s_hp,
+                                                hidden * 2ull, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_down_shared(&w->down, &w->shared_down, ps->d_hp, hidden * 2ull, routes, s->d_tasks, s->d_counts, ps->d_offsets,
+                                             ps->d_pos_route, s->d_routed, channels * 4ull, ps->d_s_hp, hidden * 2ull, tokens, s->d_shared_out,
+                                             channels * 4ull, d_error, st)) return rc;
     return tsp_moe_combine(s->d_routed, channels * 4ull, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32, x32_stride,
                            s->d_shared_logit, tokens, channels, selected, out_dtype == 0 ? static_cast<float*>(d_out) : nullptr,
                            out_dtype == 0 ? out_stride : 0, out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);

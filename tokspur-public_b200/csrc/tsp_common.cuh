@@ -19,6 +19,18 @@ int cuda_fail(cudaError_t e, const char* what);
 #define TSP_CUDA(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return ::tsp::cuda_fail(e_, #expr); } while (0)
 int sm_count();  // SM count of the current device (cached), 0 when no device is usable
 
+// kernel<<<grid, block, smem, stream>>>(args...) with programmatic stream serialisation allowed (see pdl_wait below)
+template <typename... Params, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // A dense expert (experts == 1 sets with the routed experts' shape, encoding and layout) that a routed projection launch
 // also processes, for every token row: input rows `x`, output rows `out`. b is used by gate-up launches only.
 struct GemvShared {
@@ -27,6 +39,14 @@ struct GemvShared {
     float* out; uint64_t out_stride_bytes;
     // optional: the token rows as binary16 (exactly the values of `x`); both the routed and the dense tiles then read these
     const void* x16 = nullptr; uint64_t x16_stride_bytes = 0;
+};
+
+// the layer's dense shared expert riding in a routed launch: one-expert matrix sets of the routed experts' shape, binary16
+// activation rows of all `tokens` rows in row order, output rows in row order
+struct GroupedShared {
+    const tsp_matrix_set* a; const tsp_matrix_set* b;
+    const void* act; uint64_t act_stride; uint32_t tokens;
+    void* out; uint64_t out_stride;
 };
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -83,6 +103,16 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Every kernel of the layer is launched with programmatic stream serialisation allowed: its launch is processed while the
+// previous kernel of the stream still runs, which hides the launch latency between the layer's short kernels. The
+// contract kept by every kernel here: `pdl_launch_dependents()` first (the next kernel may then be scheduled once all CTAs
+// of this one have started), set-up that touches no global memory, then `pdl_wait()` on every path before the first
+// global access; the wait returns when the previous kernel has completed and its writes are visible, so the chain of
+// kernels stays transitively ordered.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- named barrier among a subset of warps ---------------------------------------------------
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {

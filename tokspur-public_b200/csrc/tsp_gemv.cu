@@ -88,6 +88,7 @@ __device__ __forceinline__ TileInfo tile_info(const GemvParams& p, uint32_t tile
 
 template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
+    pdl_launch_dependents();
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();   // everything above touched shared memory only
 
     const uint32_t n_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
     const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.items_per_matrix;
@@ -474,8 +476,7 @@ static int launch_one(const GemvParams& p, size_t smem, int grid, cudaStream_t s
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    kernel<<<grid, kGemvThreads, smem, st>>>(p);
-    TSP_CUDA(cudaGetLastError());
+    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGemvThreads), smem, st, p));
     return TSP_OK;
 }
 

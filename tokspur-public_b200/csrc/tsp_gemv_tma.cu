@@ -120,6 +120,7 @@ __device__ __forceinline__ Tile3 tile3(const Gemv3Params& p, uint32_t tile, uint
 // activation is exactly a binary16 value).
 template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, int KB, bool SPLIT>
 __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_constant__ Gemv3Maps maps, const Gemv3Params p) {
+    pdl_launch_dependents();
     extern __shared__ uint8_t smem3_raw[];
     // the 128-byte swizzle is a function of the shared-memory address: box bases must sit on 1024-byte boundaries
     uint8_t* smem3 = smem3_raw + ((1024u - (smem_u32(smem3_raw) & 1023u)) & 1023u);
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
         for (uint32_t s = 0; s < S * kW3; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_fence_init();
     }
+    pdl_wait();   // everything above touched shared memory only
 
     const uint32_t routed_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
     const uint32_t n_tiles = routed_tiles + p.sh_tiles;
@@ -599,8 +601,7 @@ static int launch3(const Gemv3Maps& maps, const Gemv3Params& p, size_t smem, int
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    kernel<<<grid, kThreads3, smem, st>>>(maps, p);
-    TSP_CUDA(cudaGetLastError());
+    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads3), smem, st, maps, p));
     return TSP_OK;
 }
 

@@ -105,13 +105,18 @@ constexpr uint32_t kChunkK = 64;           // K per pipeline step: 64 binary16 =
 
 // Tensor maps of one launch: codes (low ids, high ids; second matrix low, high), factors (same four), (d, dmin) pairs (same four),
 // activation tiles of 32 / 64 / 128 token rows.
-struct alignas(64) GroupedMaps { CUtensorMap q[4], f[4], d[4], x[3]; };
+// Indices 4, 5 of q / f / d and 3..5 of x belong to the optional dense shared expert of the layer (sh_tiles != 0).
+struct alignas(64) GroupedMaps { CUtensorMap q[6], f[6], d[6], x[6]; };
 
 struct GroupedParams {
     uint32_t split, experts;
     uint32_t rows, cols, nblk;     // rows of ONE matrix, K, super-blocks per row
     uint32_t row_blocks;           // rows / 128
     uint32_t merged;               // both matrices of an expert arrive with one copy per plane
+    // optional dense shared expert processed by the same launch after the routed tiles: every one of sh_tokens rows, in
+    // row order (position = token = route id), its own activation rows and output rows
+    uint32_t sh_tiles, sh_tokens, sh_merged;
+    void* sh_out; uint64_t sh_out_stride_bytes;
     // routes
     const uint32_t* tasks;         // {tiles, routes, (expert, start)...} with tiles of kTileRoutes
     const uint32_t* counts;
@@ -129,8 +134,18 @@ __device__ __forceinline__ bool gwait(uint64_t* bar, uint32_t parity) { return m
 
 struct GTile { uint32_t expert, start, count, row0, ncols; };
 
+// A tile of the shared expert carries the expert id p.experts (one past the routed ids).
 __device__ __forceinline__ GTile gtile(const GroupedParams& p, uint32_t tile) {
     GTile t;
+    const uint32_t routed = p.tasks[0];
+    if (tile >= routed) {
+        t.expert = p.experts;
+        t.start = (tile - routed) * kTileRoutes;
+        t.count = t.start < p.sh_tokens ? min(p.sh_tokens - t.start, kTileRoutes) : 0u;
+        t.row0 = t.start;
+        t.ncols = t.count <= 32 ? 32u : (t.count <= 64 ? 64u : 128u);
+        return t;
+    }
     t.expert = p.tasks[2 + 2 * tile];
     t.start = p.tasks[3 + 2 * tile];
     if (t.expert >= p.experts) { t.expert = 0; t.start = 0; t.count = 0; t.row0 = 0; t.ncols = 32; return t; }
@@ -151,6 +166,7 @@ __device__ __forceinline__ void tma_load_5d_g(void* smem_dst, const CUtensorMap*
 // otherwise one matrix and FP32 rows scattered to their route ids.
 template <bool GATEUP>
 __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
+    pdl_launch_dependents();
     extern __shared__ uint8_t gsm_raw[];
     uint8_t* gsm = gsm_raw + ((1024u - (smem_u32(gsm_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(gsm);
@@ -179,13 +195,13 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();   // everything above touched shared and tensor memory only
 
-    const uint32_t n_tiles = p.tasks[0];
+    const uint32_t n_tiles = p.tasks[0] + p.sh_tiles;
     const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.row_blocks;
     const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
     const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
     const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64
-    const uint32_t ncopy = (NMAT == 1 || p.merged) ? 1u : NMAT;
 
     if (warp == 0) {
         // =========================== TMA producer of the quantised planes ===========================
@@ -196,14 +212,18 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
             for (uint32_t item = item0; item < item1 && ok; ++item) {
                 if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
                 const int r0 = static_cast<int>((item % p.row_blocks) * kRowsM);
-                const bool hi = t.expert >= p.split;
-                const int el = static_cast<int>(hi ? t.expert - p.split : t.expert);
+                const bool shared = t.expert >= p.experts;
+                const bool hi = !shared && t.expert >= p.split;
+                const int el = shared ? 0 : static_cast<int>(hi ? t.expert - p.split : t.expert);
+                const uint32_t mi = shared ? 4u : (hi ? 1u : 0u);                 // map of matrix A; matrix B's is `ms` further
+                const uint32_t ms = shared ? 1u : 2u;
+                const uint32_t ncopy = (NMAT == 1 || (shared ? p.sh_merged : p.merged)) ? 1u : NMAT;
                 // the (d, dmin) pairs of the item's rows over the whole K
                 ok = gwait(&dempty[ds], dph ^ 1u);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&dfull[ds], NMAT * p.dm_mat_bytes);
                 for (uint32_t m = 0; m < ncopy; ++m)
-                    tma_load_4d_g(gsm + p.off_d + ds * p.d_stage_bytes + m * p.dm_mat_bytes, &maps.d[2 * m + (hi ? 1 : 0)], 0,
+                    tma_load_4d_g(gsm + p.off_d + ds * p.d_stage_bytes + m * p.dm_mat_bytes, &maps.d[mi + ms * m], 0,
                                   static_cast<int>((item % p.row_blocks) * 2 * p.nblk), 0, el, &dfull[ds]);
                 if (++ds == 2) { ds = 0; dph ^= 1u; }
                 for (uint32_t sb = 0; sb < p.nblk && ok; ++sb) {
@@ -213,8 +233,8 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
                     uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
                     mbar_arrive_expect_tx(&qfull[qs], NMAT * (kRowsM * 128u + kRowsM * 16u));
                     for (uint32_t m = 0; m < ncopy; ++m) {
-                        tma_load_5d_g(q + m * 16384u, &maps.q[2 * m + (hi ? 1 : 0)], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
-                        tma_load_4d_g(q + NMAT * 16384u + m * 2048u, &maps.f[2 * m + (hi ? 1 : 0)], static_cast<int>(sb * 16), r0, 0, el, &qfull[qs]);
+                        tma_load_5d_g(q + m * 16384u, &maps.q[mi + ms * m], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
+                        tma_load_4d_g(q + NMAT * 16384u + m * 2048u, &maps.f[mi + ms * m], static_cast<int>(sb * 16), r0, 0, el, &qfull[qs]);
                     }
                     if (++qs == 2) { qs = 0; qph ^= 1u; }
                 }
@@ -229,7 +249,7 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
             GTile t{};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
                 if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
-                const CUtensorMap* xmap = t.ncols == 32 ? &maps.x[0] : (t.ncols == 64 ? &maps.x[1] : &maps.x[2]);
+                const CUtensorMap* xmap = &maps.x[(t.expert >= p.experts ? 3 : 0) + (t.ncols == 32 ? 0 : (t.ncols == 64 ? 1 : 2))];
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
                     ok = gwait(&bempty[bs], bph ^ 1u);
                     if (!ok) break;
@@ -375,7 +395,7 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
             if (!GATEUP) {
 #pragma unroll
                 for (uint32_t qd = 0; qd < 4; ++qd)
-                    if (qd * 32 + lane < t.count) rt[qd] = p.pos_route[t.row0 + qd * 32 + lane];
+                    if (qd * 32 + lane < t.count) rt[qd] = t.expert >= p.experts ? t.row0 + qd * 32 + lane : p.pos_route[t.row0 + qd * 32 + lane];
             }
             if (ok) ok = gwait(&acc_full[ab], accph);
             if (ok) {
@@ -384,7 +404,9 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * 256u;
                 // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weight tiles use
                 const uint32_t hcol = (wrow & ~7u) | ((wrow & 4u) | ((wrow & 1u) << 1) | ((wrow & 2u) >> 1));
-                char* hrow = reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(t.row0) * p.out_stride_bytes + (GATEUP ? hcol * 2 : 0);
+                char* const obase = reinterpret_cast<char*>(t.expert >= p.experts ? p.sh_out : p.out);
+                const uint64_t ostride = t.expert >= p.experts ? p.sh_out_stride_bytes : p.out_stride_bytes;
+                char* hrow = obase + static_cast<uint64_t>(t.row0) * ostride + (GATEUP ? hcol * 2 : 0);
                 bool bad = false;
                 for (uint32_t j0 = ehalf * 32; j0 < t.ncols && j0 < t.count; j0 += 32 * EH) {
                     uint32_t g[32], u[GATEUP ? 32 : 1];
@@ -401,14 +423,14 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
                                 const float v = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[GATEUP ? i : 0]);   // silu(g) * u
                                 const __half hv = __float2half_rn(v);
                                 bad |= !finite_f32(__half2float(hv));
-                                *reinterpret_cast<__half*>(hrow + static_cast<uint64_t>(j) * p.out_stride_bytes) = hv;
+                                *reinterpret_cast<__half*>(hrow + static_cast<uint64_t>(j) * ostride) = hv;
                             }
                         } else {
                             const uint32_t route = __shfl_sync(0xffffffffu, rq, j & 31u);
                             if (j < t.count) {
                                 const float v = __uint_as_float(g[i]);
                                 bad |= !finite_f32(v);
-                                reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(route) * p.out_stride_bytes)[wrow] = v;
+                                reinterpret_cast<float*>(obase + static_cast<uint64_t>(route) * ostride)[wrow] = v;
                             }
                         }
                     }
@@ -433,6 +455,8 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
 // helpers: route offsets, gather of the routed rows into permuted order
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) route_offsets_kernel(const uint32_t* __restrict__ counts, uint32_t experts, uint32_t* __restrict__ offsets) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ uint32_t warp_sum[8];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint32_t carry = 0;
@@ -458,14 +482,20 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const float* __restrict__ x, uint64_t x_stride, uint32_t in_div, const uint32_t* __restrict__ token_map,
                    const uint32_t* __restrict__ offsets, uint32_t experts, uint32_t tokens, uint32_t cols, __half* __restrict__ xp,
                    uint64_t xp_stride, uint32_t* __restrict__ pos_route, uint32_t* error) {
-    const uint32_t total = offsets[experts];
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t pos = blockIdx.x * 4 + (threadIdx.x >> 6);
-    if (pos >= total) return;
-    uint32_t lo = 0, hi = experts;   // largest e with offsets[e] <= pos
-    while (hi - lo > 1) { const uint32_t mid = (lo + hi) >> 1; if (offsets[mid] <= pos) lo = mid; else hi = mid; }
-    const uint32_t rid = token_map[static_cast<uint64_t>(lo) * tokens + (pos - offsets[lo])];
+    uint32_t rid = pos;   // no tables: every row in its own position (a dense expert)
+    if (token_map) {
+        if (pos >= offsets[experts]) return;
+        uint32_t lo = 0, hi = experts;   // largest e with offsets[e] <= pos
+        while (hi - lo > 1) { const uint32_t mid = (lo + hi) >> 1; if (offsets[mid] <= pos) lo = mid; else hi = mid; }
+        rid = token_map[static_cast<uint64_t>(lo) * tokens + (pos - offsets[lo])];
+    } else if (pos >= tokens) {
+        return;
+    }
     const uint32_t t64 = threadIdx.x & 63;
-    if (t64 == 0) pos_route[pos] = rid;
+    if (t64 == 0 && pos_route) pos_route[pos] = rid;
     const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(x) + static_cast<uint64_t>(rid / in_div) * x_stride);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(xp) + static_cast<uint64_t>(pos) * xp_stride);
     bool bad = false;
@@ -481,16 +511,14 @@ gather_rows_kernel(const float* __restrict__ x, uint64_t x_stride, uint32_t in_d
 }
 
 int launch_route_offsets(const uint32_t* counts, uint32_t experts, uint32_t* offsets, cudaStream_t st) {
-    route_offsets_kernel<<<1, 256, 0, st>>>(counts, experts, offsets);
-    TSP_CUDA(cudaGetLastError());
+    TSP_CUDA(launch_pdl(route_offsets_kernel, dim3(1), dim3(256), 0, st, counts, experts, offsets));
     return TSP_OK;
 }
 
 int launch_gather_rows(const float* x, uint64_t x_stride, uint32_t in_div, const uint32_t* token_map, const uint32_t* offsets, uint32_t experts,
                        uint32_t tokens, uint32_t max_routes, uint32_t cols, void* xp, uint64_t xp_stride, uint32_t* pos_route, uint32_t* error,
                        cudaStream_t st) {
-    gather_rows_kernel<<<(max_routes + 3) / 4, 256, 0, st>>>(x, x_stride, in_div, token_map, offsets, experts, tokens, cols,
-                                                             static_cast<__half*>(xp), xp_stride, pos_route, error);
+    TSP_CUDA(launch_pdl(gather_rows_kernel, dim3((max_routes + 3) / 4), dim3(256), 0, st, x, x_stride, in_div, token_map, offsets, experts, tokens, cols, static_cast<__half*>(xp), xp_stride, pos_route, error));
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -506,8 +534,7 @@ static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    kernel<<<grid, g_warps(GATEUP) * 32, smem, st>>>(m, p);
-    TSP_CUDA(cudaGetLastError());
+    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(g_warps(GATEUP) * 32), smem, st, m, p));
     return TSP_OK;
 }
 
@@ -515,7 +542,7 @@ static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t
 // `cols` values, 16-byte aligned stride); out: gate-up -> binary16 rows [positions x rows] in permuted order, down -> FP32 rows by route id.
 int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const void* act, uint64_t act_stride, uint32_t max_positions,
                    const uint32_t* tasks, const uint32_t* counts, const uint32_t* offsets, const uint32_t* pos_route, void* out,
-                   uint64_t out_stride, uint32_t* error, cudaStream_t st) {
+                   uint64_t out_stride, uint32_t* error, cudaStream_t st, const GroupedShared* sh) {
     if (a->type != TSP_TYPE_Q4_K || a->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "grouped GEMM: only Q4_K Pack v3 planar weights have a tensor-core kernel");
     TSP_REQUIRE(a->rows % kRowsM == 0 && a->cols % 256 == 0, "grouped GEMM: rows must be a multiple of 128 and columns of 256");
     GroupedParams p{};
@@ -589,6 +616,37 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
         const uint64_t dims[2] = {uint64_t(a->cols) * 2, max_positions}, strides[1] = {act_stride};
         const uint32_t box[2] = {128, ns[i]};
         if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[i])) return rc;
+        maps.x[3 + i] = maps.x[i];
+    }
+    for (int i = 4; i < 6; ++i) { maps.q[i] = maps.q[0]; maps.f[i] = maps.f[0]; maps.d[i] = maps.d[0]; }
+    if (sh) {   // the layer's dense shared expert: same shape, one expert, its own rows
+        const uint8_t* sa = static_cast<const uint8_t*>(sh->a->base);
+        const uint8_t* sb = gateup ? static_cast<const uint8_t*>(sh->b->base) : nullptr;
+        TSP_REQUIRE(reinterpret_cast<uintptr_t>(sa) % 16 == 0 && reinterpret_cast<uintptr_t>(sb) % 16 == 0, "grouped GEMM: expert images must be 16-byte aligned");
+        uint64_t sdelta = 0;
+        p.sh_merged = gateup && mergeable(sa, sb, &sdelta);
+        p.sh_tokens = sh->tokens;
+        p.sh_tiles = (sh->tokens + kTileRoutes - 1) / kTileRoutes;
+        p.sh_out = sh->out; p.sh_out_stride_bytes = sh->out_stride;
+        const uint32_t smats = p.sh_merged ? 2 : 1;
+        const uint64_t sds = p.sh_merged ? sdelta : 16;
+        for (uint32_t m = 0; m < (gateup && !p.sh_merged ? 2u : 1u); ++m) {
+            const uint8_t* bp = m == 0 ? sa : sb;
+            const uint64_t dq[5] = {128, a->rows, nblk, smats, 1}, sq[4] = {uint64_t(nblk) * 128, 128, sds, 16};
+            const uint32_t bq[5] = {128, kRowsM, 1, smats, 1};
+            if (int rc = get_tensor_map_bytes(bp, 5, dq, sq, bq, true, &maps.q[4 + m])) return rc;
+            const uint64_t df[4] = {uint64_t(nblk) * 16, a->rows, smats, 1}, sf[3] = {uint64_t(nblk) * 16, sds, 16};
+            const uint32_t bf[4] = {16, kRowsM, smats, 1};
+            if (int rc = get_tensor_map_bytes(bp + sm_off, 4, df, sf, bf, false, &maps.f[4 + m])) return rc;
+            const uint64_t dd[4] = {256, total_units * 4 / 256, smats, 1}, sd[3] = {256, sds, 16};
+            const uint32_t bd[4] = {256, 2 * nblk, smats, 1};
+            if (int rc = get_tensor_map_bytes(bp + dm_off, 4, dd, sd, bd, false, &maps.d[4 + m])) return rc;
+        }
+        for (int i = 0; i < 3; ++i) {
+            const uint64_t dims[2] = {uint64_t(a->cols) * 2, sh->tokens}, strides[1] = {sh->act_stride};
+            const uint32_t box[2] = {128, ns[i]};
+            if (int rc = get_tensor_map_bytes(sh->act, 2, dims, strides, box, true, &maps.x[3 + i])) return rc;
+        }
     }
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");

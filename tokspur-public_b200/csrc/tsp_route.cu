@@ -92,7 +92,9 @@ __device__ __forceinline__ void route_row(float* row, const float* __restrict__ 
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t tokens, uint32_t experts,
              uint32_t selected, uint32_t mode, int normalize, uint32_t* __restrict__ ids,
-             float* __restrict__ weights, uint32_t* error) {
+             float* __restrict__ weights, uint32_t* error) {    pdl_launch_dependents();
+    pdl_wait();
+
     extern __shared__ float route_smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t token = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -108,7 +110,9 @@ constexpr int kPermuteThreads = 128;
 
 __global__ void __launch_bounds__(kPermuteThreads)
 grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t first, int local_only,
-                      uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* error) {
+                      uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* error) {    pdl_launch_dependents();
+    pdl_wait();
+
     __shared__ uint32_t totals[kPermuteThreads / 32];
     const uint32_t expert = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t accumulated = 0;
@@ -142,7 +146,9 @@ grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_
 // tasks = {live_tiles, routes, (expert, start) pairs in ascending expert order, 0xffffffff padding}
 __global__ void __launch_bounds__(256)
 grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint32_t experts, uint32_t selected,
-                     uint32_t tile, uint32_t bound, int local_only, uint32_t* __restrict__ tasks, uint32_t* error) {
+                     uint32_t tile, uint32_t bound, int local_only, uint32_t* __restrict__ tasks, uint32_t* error) {    pdl_launch_dependents();
+    pdl_wait();
+
     extern __shared__ uint32_t offsets[];  // experts + 1
     const uint32_t tid = threadIdx.x;
     __shared__ uint32_t warp_tiles[8], warp_routes[8];
@@ -199,7 +205,9 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
                const float* __restrict__ shared, uint64_t shared_stride, const float* __restrict__ shared_router,
                const float* __restrict__ x, uint64_t x_stride, float* shared_logit, uint32_t channels,
                uint32_t selected, float* __restrict__ out, uint64_t out_stride, __half* __restrict__ out16,
-               uint64_t out16_stride, int vec4, uint32_t* error) {
+               uint64_t out16_stride, int vec4, uint32_t* error) {    pdl_launch_dependents();
+    pdl_wait();
+
     __shared__ float partial[kCombineThreads / 32];
     __shared__ float w_s[64];
     __shared__ float gate_s;
@@ -271,7 +279,9 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 gemv_f32_kernel(const float* __restrict__ w, uint32_t rows, uint32_t cols, const float* __restrict__ x, uint64_t x_stride, uint32_t tokens,
-                float* __restrict__ out, uint64_t out_stride, uint32_t* error) {
+                float* __restrict__ out, uint64_t out_stride, uint32_t* error) {    pdl_launch_dependents();
+    pdl_wait();
+
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= rows * tokens) return;
     const uint32_t token = warp / rows, row = warp % rows;
@@ -289,13 +299,14 @@ gemv_f32_kernel(const float* __restrict__ w, uint32_t rows, uint32_t cols, const
 int launch_gemv_f32(const float* w, uint32_t rows, uint32_t cols, const float* x, uint64_t x_stride, uint32_t tokens, float* out,
                     uint64_t out_stride, uint32_t* error, cudaStream_t st) {
     const uint64_t warps = static_cast<uint64_t>(rows) * tokens;
-    gemv_f32_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(w, rows, cols, x, x_stride, tokens, out, out_stride, error);
-    TSP_CUDA(cudaGetLastError());
+    TSP_CUDA(launch_pdl(gemv_f32_kernel, dim3(static_cast<unsigned>((warps + 7) / 8)), dim3(256), 0, st, w, rows, cols, x, x_stride, tokens, out, out_stride, error));
     return TSP_OK;
 }
 
 __global__ void rows_f16_to_f32_kernel(const __half* __restrict__ in, uint64_t in_stride, float* __restrict__ out,
-                                       uint64_t out_stride, uint32_t rows, uint32_t cols) {
+                                       uint64_t out_stride, uint32_t rows, uint32_t cols) {    pdl_launch_dependents();
+    pdl_wait();
+
     const uint32_t row = blockIdx.y;
     const __half* src = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(in) + row * in_stride);
     float* dst = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + row * out_stride);
@@ -364,18 +375,17 @@ int launch_route(const float* logits, uint64_t stride, uint32_t tokens, uint32_t
                  uint32_t mode, int normalize, uint32_t* ids, float* weights, uint32_t* error, cudaStream_t st) {
     const uint32_t warps = experts > 3072 ? 2 : kRouteWarps;
     const uint32_t blocks = (tokens + warps - 1) / warps;
-    route_kernel<<<blocks, warps * 32, warps * experts * sizeof(float), st>>>(
-        logits, stride, tokens, experts, selected, mode, normalize, ids, weights, error);
+    TSP_CUDA(launch_pdl(route_kernel, dim3(blocks), dim3(warps * 32), warps * experts * sizeof(float), st, logits, stride, tokens, experts, selected, mode, normalize, ids, weights, error));
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
 
 int launch_permute(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile, uint32_t first, int local_only,
                    uint32_t* token_map, uint32_t* counts, uint32_t* tasks, uint32_t* error, cudaStream_t st) {
-    grouped_routes_kernel<<<experts, kPermuteThreads, 0, st>>>(ids, tokens, experts, selected, first, local_only, token_map, counts, error);
+    TSP_CUDA(launch_pdl(grouped_routes_kernel, dim3(experts), dim3(kPermuteThreads), 0, st, ids, tokens, experts, selected, first, local_only, token_map, counts, error));
     TSP_CUDA(cudaGetLastError());
     const uint32_t bound = static_cast<uint32_t>((static_cast<uint64_t>(tokens) * selected) / tile + experts);
-    grouped_tasks_kernel<<<1, 256, (experts + 1) * sizeof(uint32_t), st>>>(counts, tokens, experts, selected, tile, bound, local_only, tasks, error);
+    TSP_CUDA(launch_pdl(grouped_tasks_kernel, dim3(1), dim3(256), (experts + 1) * sizeof(uint32_t), st, counts, tokens, experts, selected, tile, bound, local_only, tasks, error));
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -391,9 +401,7 @@ int launch_combine(const float* routed, uint64_t routed_stride, const float* wei
     auto a16 = [](const void* p, uint64_t stride) { return (reinterpret_cast<uintptr_t>(p) | stride) % 16 == 0; };
     const int vec4 = a16(routed, routed_stride) && a16(shared, shared_stride) && (!out || a16(out, out_stride)) &&
                      (!out16 || (reinterpret_cast<uintptr_t>(out16) | out16_stride) % 8 == 0);
-    combine_kernel<<<dim3(tokens, slices), kCombineThreads, 0, st>>>(routed, routed_stride, weights, shared, shared_stride, shared_router,
-                                                       x, x_stride, shared_logit, channels, selected, out, out_stride,
-                                                       static_cast<__half*>(out16), out16_stride, vec4, error);
+    TSP_CUDA(launch_pdl(combine_kernel, dim3(tokens, slices), dim3(kCombineThreads), 0, st, routed, routed_stride, weights, shared, shared_stride, shared_router, x, x_stride, shared_logit, channels, selected, out, out_stride, static_cast<__half*>(out16), out16_stride, vec4, error));
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -401,8 +409,7 @@ int launch_combine(const float* routed, uint64_t routed_stride, const float* wei
 int launch_f16_to_f32(const void* in, uint64_t in_stride, float* out, uint64_t out_stride, uint32_t rows, uint32_t cols,
                       cudaStream_t st) {
     dim3 grid((cols + 1023) / 1024, rows);
-    rows_f16_to_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(in), in_stride, out, out_stride, rows, cols);
-    TSP_CUDA(cudaGetLastError());
+    TSP_CUDA(launch_pdl(rows_f16_to_f32_kernel, grid, dim3(256), 0, st, static_cast<const __half*>(in), in_stride, out, out_stride, rows, cols));
     return TSP_OK;
 }
 

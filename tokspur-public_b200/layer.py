@@ -260,17 +260,13 @@ class PrefillScratch:
         self.offsets = z(experts + 1, i32)
         self.pos_route = z(routes, i32)
         self.tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, experts, selected, 128)), i32)
-        # the dense shared expert runs through the same kernels as a one-expert set over all token rows
-        self.ids0 = z(capacity, i32)
-        self.s_token_map, self.s_counts, self.s_offsets, self.s_pos = z(capacity, i32), z(1, i32), z(2, i32), z(capacity, i32)
-        self.s_tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, 1, 1, 128)), i32)
+        # the dense shared expert rides in the routed launches: its binary16 input and hidden rows in row order
         self.s_xp = torch.zeros((capacity, channels), dtype=f16, device=device)
         self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)
         base = capi.MoeScratch.from_buffer_copy(self.base.c)
         base.d_tasks = self.tasks.data_ptr()     # tiles of 128 routes
         self.c = capi.MoePrefillScratch(base, self.xp.data_ptr(), self.hp.data_ptr(), self.offsets.data_ptr(), self.pos_route.data_ptr(),
-                                        self.ids0.data_ptr(), self.s_token_map.data_ptr(), self.s_counts.data_ptr(), self.s_offsets.data_ptr(),
-                                        self.s_pos.data_ptr(), self.s_tasks.data_ptr(), self.s_xp.data_ptr(), self.s_hp.data_ptr())
+                                        self.s_xp.data_ptr(), self.s_hp.data_ptr())
 
 
 def moe_layer_prefill(dl, ps: PrefillScratch, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, mode: int = 0, normalize: bool = True) -> None:

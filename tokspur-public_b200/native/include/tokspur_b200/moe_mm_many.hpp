@@ -10,7 +10,7 @@
 namespace tokspur_b200 {
 
 
-constexpr size_t kMoeMmManyViews = 21;
+constexpr size_t kMoeMmManyViews = 15;
 struct MoeMmManyBytes {
     std::array<uint64_t, kMoeMmManyViews> views{};
     uint64_t total = 0;
@@ -22,8 +22,8 @@ struct MoeMmManyScratch {
     GpuView token_map, counts, tasks, offsets, pos_route;
     // binary16 rows in permuted position order: gathered inputs, hidden rows
     GpuView xp, hp;
-    // the dense shared expert as a one-expert set over every row
-    GpuView ids0, s_token_map, s_counts, s_offsets, s_pos, s_tasks, s_xp, s_hp;
+    // the dense shared expert's binary16 input and hidden rows in row order (it rides in the routed launches)
+    GpuView s_xp, s_hp;
     uint32_t capacity = 0;
     [[nodiscard]] std::array<GpuView, kMoeMmManyViews> views() const;
 };

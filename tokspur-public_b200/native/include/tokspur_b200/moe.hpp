@@ -31,4 +31,15 @@ void release_moe_scratch(CudaGraph& graph, const MoeScratch& scratch);
 void encode_moe(CudaGraph& graph, const MoeWeights& weights, const MoeScratch& scratch, GpuView input, GpuView output,
                 MoeShape shape, RouterMode mode, bool normalize_selected);
 
+// Speculative-verify batches (native/include/tokspur/verify_nax.hpp:12-14, 70): `steps` (2..8) token rows, contiguous FP32 rows
+// of `channels` values in and out, through the decode kernels: the experts the rows share are read once per tile of 8 routes.
+// The scratch is the row scratch for `steps` rows (allocate_moe_rows_scratch); the reference's extra scratch type carries no
+// views and is kept for signature parity.
+struct VerifyNaxMoeScratch {
+    [[nodiscard]] std::array<GpuView, 0> views() const { return {}; }
+};
+MoeScratch allocate_moe_rows_scratch(CudaGraph& graph, MoeShape shape, uint32_t rows);
+void encode_verify_nax_moe(CudaGraph& graph, const MoeWeights& weights, const MoeScratch& scratch, const VerifyNaxMoeScratch& nax_moe,
+                           GpuView input, GpuView output, MoeShape shape, RouterMode mode, bool normalize_selected, uint32_t steps);
+
 }  // namespace tokspur_b200

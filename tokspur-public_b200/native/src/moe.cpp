@@ -26,11 +26,13 @@ std::array<GpuView, 13> MoeScratch::views() const {
     return {logits, indices, weights, gate, up, down, shared_gate, shared_up, shared_down, shared_logit, token_map, counts, tasks};
 }
 
-MoeScratch allocate_moe_scratch(CudaGraph& graph, MoeShape s) {
+MoeScratch allocate_moe_rows_scratch(CudaGraph& graph, MoeShape s, uint32_t rows) {
     shape_check(s);
-    const uint64_t tasks_words = tsp_moe_tasks_words(1, s.experts, s.selected, TSP_GEMV_TILE);
-    const std::array<uint64_t, 13> counts{s.experts, s.selected, s.selected, uint64_t(s.hidden) * s.selected, uint64_t(s.hidden) * s.selected,
-                                          uint64_t(s.channels) * s.selected, s.hidden, s.hidden, s.channels, 1, s.experts, s.experts, tasks_words};
+    if (!rows || rows > 64) throw FormatError("invalid row count for the mixture scratch");
+    const uint64_t n = rows, tasks_words = tsp_moe_tasks_words(rows, s.experts, s.selected, TSP_GEMV_TILE);
+    const std::array<uint64_t, 13> counts{n * s.experts, n * s.selected, n * s.selected, n * s.hidden * s.selected, n * s.hidden * s.selected,
+                                          n * s.channels * s.selected, n * s.hidden, n * s.hidden, n * s.channels, n, n * s.experts, s.experts,
+                                          tasks_words};
     std::array<GpuView, 13> v{};
     size_t made = 0;
     try {
@@ -41,6 +43,8 @@ MoeScratch allocate_moe_scratch(CudaGraph& graph, MoeShape s) {
     }
     return {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12]};
 }
+
+MoeScratch allocate_moe_scratch(CudaGraph& graph, MoeShape s) { return allocate_moe_rows_scratch(graph, s, 1); }
 
 void release_moe_scratch(CudaGraph& graph, const MoeScratch& scratch) {
     for (const auto view : scratch.views()) graph.release(view);
@@ -56,10 +60,27 @@ bool is_planar_moe(const CudaGraph& g, const MoeWeights& w, MoeShape s) {
            dn->rows == s.channels && dn->experts == s.experts;
 }
 
+namespace {
+void encode_rows(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView input, GpuView output, MoeShape shape, RouterMode mode,
+                 bool normalize_selected, uint32_t rows);
+}
+
 void encode_moe(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView input, GpuView output, MoeShape shape,
                 RouterMode mode, bool normalize_selected) {
+    encode_rows(g, w, s, input, output, shape, mode, normalize_selected, 1);
+}
+
+void encode_verify_nax_moe(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, const VerifyNaxMoeScratch&, GpuView input, GpuView output,
+                           MoeShape shape, RouterMode mode, bool normalize_selected, uint32_t steps) {
+    if (steps < 2 || steps > 8) throw FormatError("verify batch must hold 2..8 rows");
+    encode_rows(g, w, s, input, output, shape, mode, normalize_selected, steps);
+}
+
+namespace {
+void encode_rows(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView input, GpuView output, MoeShape shape, RouterMode mode,
+                 bool normalize_selected, uint32_t rows) {
     shape_check(shape);
-    if (input.bytes != uint64_t(shape.channels) * 4 || output.bytes != uint64_t(shape.channels) * 4) throw FormatError("mixture shape mismatch");
+    if (input.bytes != uint64_t(shape.channels) * 4 * rows || output.bytes != uint64_t(shape.channels) * 4 * rows) throw FormatError("mixture shape mismatch");
     if (w.router.encoding != 0 || w.shared_router.encoding != 0) throw FormatError("router projections must be F32");
     tsp_moe_weights tw{};
     if (is_planar_moe(g, w, shape)) {
@@ -90,19 +111,23 @@ void encode_moe(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView 
     ts.d_token_map = static_cast<uint32_t*>(g.device_pointer(s.token_map, true));
     ts.d_counts = static_cast<uint32_t*>(g.device_pointer(s.counts, true));
     ts.d_tasks = static_cast<uint32_t*>(g.device_pointer(s.tasks, true));
-    ts.capacity = 1;
-    if (s.token_map.bytes < uint64_t(shape.experts) * 4 || s.counts.bytes < uint64_t(shape.experts) * 4 ||
-        s.tasks.bytes < tsp_moe_tasks_words(1, shape.experts, shape.selected, TSP_GEMV_TILE) * 4 ||
-        s.gate.bytes < uint64_t(shape.hidden) * shape.selected * 4 || s.down.bytes < uint64_t(shape.channels) * shape.selected * 4)
+    ts.capacity = rows;
+    const uint64_t n = rows;
+    if (s.token_map.bytes < n * shape.experts * 4 || s.counts.bytes < uint64_t(shape.experts) * 4 ||
+        s.tasks.bytes < tsp_moe_tasks_words(rows, shape.experts, shape.selected, TSP_GEMV_TILE) * 4 ||
+        s.gate.bytes < n * shape.hidden * shape.selected * 4 || s.down.bytes < n * shape.channels * shape.selected * 4 ||
+        s.logits.bytes < n * shape.experts * 4 || s.indices.bytes < n * shape.selected * 4 || s.weights.bytes < n * shape.selected * 4 ||
+        s.shared_gate.bytes < n * shape.hidden * 4 || s.shared_down.bytes < n * shape.channels * 4 || s.shared_logit.bytes < n * 4)
         throw FormatError("mixture scratch too small");
 
-    g.gemv_f32(w.router.view, input, s.logits, shape.channels, shape.experts);
+    g.gemv_f32_rows(w.router.view, input, uint64_t(shape.channels) * 4, rows, s.logits, uint64_t(shape.experts) * 4, shape.channels, shape.experts);
     const int rc = tsp_moe_layer_decode(&tw, &ts, g.device_pointer(input), uint64_t(shape.channels) * 4, 0,
-                                        static_cast<const float*>(g.device_pointer(s.logits)), uint64_t(shape.experts) * 4, 1, shape.channels,
+                                        static_cast<const float*>(g.device_pointer(s.logits)), uint64_t(shape.experts) * 4, rows, shape.channels,
                                         shape.hidden, shape.experts, shape.selected, uint32_t(mode), normalize_selected,
                                         g.device_pointer(output, true), uint64_t(shape.channels) * 4, 0, g.error_word(), g.stream());
     if (rc != TSP_OK) throw FormatError(tsp_last_error());
     g.count_dispatches(6);   // route, routes+tasks (2), gate-up, down, combine (the shared expert rides in the routed launches)
 }
+}  // namespace
 
 }  // namespace tokspur_b200

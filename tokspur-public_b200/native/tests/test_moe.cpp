@@ -149,6 +149,40 @@ void layer(CudaGraph& g, uint32_t type, bool use_planar, MoeShape shape, uint32_
     (void)g.submit();
     release_moe_scratch(g, scratch);
 }
+// encode_verify_nax_moe: a verify batch of `steps` rows through the decode kernels, every stage against the oracle.
+void verify_rows(CudaGraph& g, uint32_t type, MoeShape shape, uint32_t steps, uint32_t seed) {
+    const uint32_t C = shape.channels, H = shape.hidden, E = shape.experts, K = shape.selected;
+    const auto gate = generated(type, C, H, E, seed + 1), up = generated(type, C, H, E, seed + 2), down = generated(type, H, C, E, seed + 3);
+    const auto sgate = generated(type, C, H, 1, seed + 4), sup = generated(type, C, H, 1, seed + 5), sdown = generated(type, H, C, 1, seed + 6);
+    const auto router = activations(seed + 7, size_t(E) * C, 0.25f), srouter = activations(seed + 8, C, 0.125f);
+    MoeWeights w{};
+    w.router = {g.upload(bytes_of(router), "router"), 0};
+    w.shared_router = {g.upload(bytes_of(srouter), "shared router"), 0};
+    w.shared_gate = {g.upload(bytes(sgate), "sg"), type}; w.shared_up = {g.upload(bytes(sup), "su"), type}; w.shared_down = {g.upload(bytes(sdown), "sd"), type};
+    w.gate = {g.upload(bytes(gate), "gate"), type}; w.up = {g.upload(bytes(up), "up"), type}; w.down = {g.upload(bytes(down), "down"), type};
+    const auto scratch = allocate_moe_rows_scratch(g, shape, steps);
+    const auto input = g.zeros(uint64_t(C) * 4 * steps, "rows in"), output = g.zeros(uint64_t(C) * 4 * steps, "rows out");
+    const auto x = activations(900 + seed, size_t(C) * steps, 8.f);
+    g.write(input, bytes_of(x));
+    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1};
+    std::vector<double> expected(size_t(C) * steps), ew(size_t(K) * steps);
+    std::vector<uint32_t> eids(size_t(K) * steps);
+    tso_layer_stages st{eids.data(), ew.data(), nullptr, nullptr, nullptr, nullptr, nullptr};
+    require(tso_moe_layer(&L, x.data(), nullptr, steps, expected.data(), &st, 2) == TSO_OK, "oracle layer");
+    const VerifyNaxMoeScratch none{};
+    g.begin();
+    encode_verify_nax_moe(g, w, scratch, none, input, output, shape, RouterMode::softmax, true, steps);
+    (void)g.submit();
+    require(read<uint32_t>(g, scratch.indices) == eids, "verify batch: route ids differ");
+    close(read<float>(g, scratch.weights), ew.data(), ew.size());
+    close(read<float>(g, output), expected.data(), expected.size());
+    g.begin();
+    refuses([&] { encode_verify_nax_moe(g, w, scratch, none, input, output, shape, RouterMode::softmax, true, 1); }, "one-row verify batch accepted");
+    refuses([&] { encode_verify_nax_moe(g, w, scratch, none, input, output, shape, RouterMode::softmax, true, steps + 1); }, "rows beyond the views accepted");
+    g.abort();
+    release_moe_scratch(g, scratch);
+}
+
 // encode_moe_mm_many (grouped tensor-core GEMMs): strided row batches longer than the scratch capacity, against the oracle.
 // Operands are binary16 there, so the layer bar is the relative L2 error of 2e-3, not the decode path's 5e-5.
 void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32_t seed) {
@@ -246,6 +280,9 @@ int main() {
         }
     }
     try {
+        CudaGraph gv(0, uint64_t(2) << 30);
+        verify_rows(gv, 12, {256, 256, 8, 4}, 5, 200);
+        verify_rows(gv, 8, {256, 64, 8, 4}, 8, 210);
         CudaGraph g(0, uint64_t(2) << 30);
         many(g, {512, 256, 16, 4}, 40, 24, 300);   // two chunks: 24 + 16 rows
         CudaGraph g2(0, uint64_t(2) << 30);

@@ -16,9 +16,14 @@
 // The reduction index inside one 8-wide run of K is permuted identically for weights and
 // activations (order 0,2,1,3,4,6,5,7): a 32-bit word of codes then splits into MMA register
 // pairs with two masks and one shift, with no cross-lane movement.
+#include <cuda.h>
+
 #include "tsp_common.cuh"
 
 namespace tsp {
+
+int get_tensor_map_elems(const void* base, uint32_t elem_bytes, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                         bool swizzle128, CUtensorMap* out);
 
 constexpr int kConsumerWarps = 8;
 constexpr int kGemvThreads = (kConsumerWarps + 1) * 32;
@@ -40,6 +45,9 @@ struct GemvParams {
     uint32_t items_per_matrix;
     uint32_t nrt;             // MMA row tiles per item
     uint32_t row_bytes;       // bytes copied per row into the quant area (0: one contiguous copy per matrix)
+    uint32_t src_row_pitch;   // bytes between consecutive rows in global memory
+    uint32_t kparts;          // K parts per item (1: a stage holds the rows' whole K extent); > 1 only with one row tile per warp
+    uint32_t units_per_part;  // K units of a row in one stage
     uint32_t row_stride;      // shared-memory stride between rows of the quant area
     uint32_t quant_bytes;     // quant area bytes per stage
     uint32_t sm_bytes_item;   // planar Q4_K: bytes of the sm plane per matrix per full item
@@ -87,7 +95,7 @@ __device__ __forceinline__ TileInfo tile_info(const GemvParams& p, uint32_t tile
 }
 
 template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap part_map) {
     pdl_launch_dependents();
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -118,10 +126,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             const TileInfo ti = tile_info<NC>(p, tile);
             const uint32_t r0 = ri * p.rows_per_item;
             const uint32_t nr = min(p.rows_per_item, p.rows - r0);
+            for (uint32_t kh = 0; kh < p.kparts && ok; ++kh) {
             if (lane == 0) ok = mbar_wait(&empty[stage], phase ^ 1u);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { if (lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT); break; }
             uint8_t* sbase = smem + p.off_stage + stage * p.stage_bytes;
+            if (p.kparts > 1) {
+                // K-part stages of a dense matrix: ONE tensor copy brings this part of all the item's rows ([part bytes][rows]
+                // box; rows past the matrix end are filled with zeros and still count as delivered bytes)
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&full[stage], p.rows_per_item * p.row_bytes);
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                                 ::"r"(smem_u32(sbase)), "l"(reinterpret_cast<uint64_t>(&part_map)), "r"(smem_u32(&full[stage])),
+                                   "r"(static_cast<int>(kh * p.row_bytes / 2)), "r"(static_cast<int>(r0)) : "memory");
+                }
+                if (++stage == NS) { stage = 0; phase ^= 1u; }
+                continue;
+            }
             // bytes this fill will deliver
             uint32_t total = 0;
             if (p.row_bytes) total += NMAT * nr * p.row_bytes; else total += NMAT * nr * p.nunit * 34u;
@@ -136,9 +157,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                                            : expert_ptr(p.b_base, p.b_base_hi, ti.expert, p.split, p.expert_stride);
                 uint8_t* qdst = sbase + m * p.rows_per_item * p.row_stride;
                 if (p.row_bytes) {
-                    const uint8_t* src = eb + static_cast<uint64_t>(r0) * p.row_bytes;
+                    const uint8_t* src = eb + static_cast<uint64_t>(r0) * p.src_row_pitch + kh * p.row_bytes;
                     for (uint32_t r = lane; r < nr; r += 32)
-                        bulk_g2s(qdst + r * p.row_stride, src + static_cast<uint64_t>(r) * p.row_bytes, p.row_bytes, &full[stage]);
+                        bulk_g2s(qdst + r * p.row_stride, src + static_cast<uint64_t>(r) * p.src_row_pitch, p.row_bytes, &full[stage]);
                 } else if (lane == 0) {
                     bulk_g2s(qdst, eb + static_cast<uint64_t>(r0) * p.nunit * 34u, nr * p.nunit * 34u, &full[stage]);
                 }
@@ -155,6 +176,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                 }
             }
             if (++stage == NS) { stage = 0; phase ^= 1u; }
+            }
         }
         return;
     }
@@ -244,25 +266,29 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             cur_tile = tile;
         }
 
-        // ---- wait for the slab ----
-        if (ok) {
-            ok = mbar_wait(&full[stage], phase);
-            if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
-        }
-        const uint8_t* sbase = smem + p.off_stage + stage * p.stage_bytes;
         const uint32_t r0 = ri * p.rows_per_item;
-
-        for (uint32_t rt = (nrt >= kConsumerWarps ? warp : warp % nrt); rt < nrt; rt += kConsumerWarps) {
+        // every consumer warp has exactly one row tile of the item (nrt <= 8): rt = warp, or warp % nrt when several warps
+        // share a tile and split K among them
+        const uint32_t rt = nrt >= kConsumerWarps ? warp : warp % nrt;
+        {
             float total[NC][4];
 #pragma unroll
             for (int c = 0; c < NC; ++c) { total[c][0] = total[c][1] = total[c][2] = total[c][3] = 0.f; }
             // shared-memory rows of this lane's two MMA row slots
             const uint32_t rowA = GATEUP ? rt * 8 + g : rt * 16 + g;
             const uint32_t rowB = GATEUP ? p.rows_per_item + rt * 8 + g : rt * 16 + 8 + g;
+            for (uint32_t kh = 0; kh < p.kparts; ++kh) {
+            // ---- wait for the slab (one K part of the item's rows) ----
+            if (ok) {
+                ok = mbar_wait(&full[stage], phase);
+                if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
+            }
+            const uint8_t* sbase = smem + p.off_stage + stage * p.stage_bytes;
             const uint8_t* qA = sbase + rowA * p.row_stride;
             const uint8_t* qB = sbase + rowB * p.row_stride;
+            const uint32_t kb0 = kh * p.units_per_part;   // first K unit of this part (activation offsets use the global unit index)
             if (ok) {
-                for (uint32_t b = my_kp; b < p.nunit; b += kp_count) {
+                for (uint32_t b = my_kp; b < p.units_per_part; b += kp_count) {
                     if (TYPE == TSP_TYPE_Q4_K) {
                         // ---- header of the super-block for both rows: d, dmin, sc[8], mn[8] ----
                         uint32_t dmA, dmB, scA[2], scB[2], mnA[2], mnB[2];
@@ -376,17 +402,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                         const uint32_t pb2 = __byte_perm(b1, 0u, 0x4240), pb3 = __byte_perm(b1, 0u, 0x4341);
 #pragma unroll
                         for (int c = 0; c < NC; ++c) {
-                            const uint4 xv = lds128(xhi + (c * 8 + g) * p.x_stride + (b * 32 + t * 8) * 2);
+                            const uint4 xv = lds128(xhi + (c * 8 + g) * p.x_stride + ((kb0 + b) * 32 + t * 8) * 2);
                             float acc[4] = {0.f, 0.f, 0.f, 0.f};
                             mma_f16_16816(acc, pa0, pb0, pa1, pb1, xv.x, xv.y);
                             mma_f16_16816(acc, pa2, pb2, pa3, pb3, xv.z, xv.w);
                             if (p.split_lo) {
-                                const uint4 yv = lds128(xlo + (c * 8 + g) * p.x_stride + (b * 32 + t * 8) * 2);
+                                const uint4 yv = lds128(xlo + (c * 8 + g) * p.x_stride + ((kb0 + b) * 32 + t * 8) * 2);
                                 mma_f16_16816(acc, pa0, pb0, pa1, pb1, yv.x, yv.y);
                                 mma_f16_16816(acc, pa2, pb2, pa3, pb3, yv.z, yv.w);
                             }
-                            const float s0 = *reinterpret_cast<const float*>(sxb + (c * 8 + 2 * t) * p.sx_stride + b * 4);
-                            const float s1 = *reinterpret_cast<const float*>(sxb + (c * 8 + 2 * t + 1) * p.sx_stride + b * 4);
+                            const float s0 = *reinterpret_cast<const float*>(sxb + (c * 8 + 2 * t) * p.sx_stride + (kb0 + b) * 4);
+                            const float s1 = *reinterpret_cast<const float*>(sxb + (c * 8 + 2 * t + 1) * p.sx_stride + (kb0 + b) * 4);
                             total[c][0] = fmaf(fA, acc[0], fmaf(oA, s0, total[c][0]));
                             total[c][1] = fmaf(fA, acc[1], fmaf(oA, s1, total[c][1]));
                             total[c][2] = fmaf(fB, acc[2], fmaf(oB, s0, total[c][2]));
@@ -394,6 +420,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                         }
                     }
                 }
+            }
+            if (kh + 1 < p.kparts) {   // more parts of this item follow: hand the stage back and move on (kparts > 1 implies kp_count == 1)
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&empty[stage]);
+                if (++stage == NS) { stage = 0; phase ^= 1u; }
+            }
             }
             // ---- cross-warp reduction over the K parts (only when one row tile is shared by several warps) ----
             if (kp_count > 1) {
@@ -469,14 +501,14 @@ static uint32_t pad_row(uint32_t row_bytes) {
 }
 
 template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC>
-static int launch_one(const GemvParams& p, size_t smem, int grid, cudaStream_t st) {
+static int launch_one(const GemvParams& p, const CUtensorMap& map, size_t smem, int grid, cudaStream_t st) {
     auto kernel = gemv_kernel<TYPE, LAYOUT, GATEUP, NC>;
     static thread_local size_t configured = 0;
     if (smem > configured) {
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGemvThreads), smem, st, p));
+    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGemvThreads), smem, st, p, map));
     return TSP_OK;
 }
 
@@ -515,8 +547,20 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
     if (layout == TSP_LAYOUT_PLANAR) row_bytes = q4 ? p.nunit * 128 : p.nunit * 32;
     else row_bytes = q4 ? p.nunit * 144 : p.nunit * 34;
     const bool contiguous = (row_bytes % 16) != 0;  // GGUF Q8_0 rows that are not 16-byte multiples
+    p.src_row_pitch = row_bytes;
+    p.kparts = 1;
+    p.units_per_part = p.nunit;
+    // A dense GGUF Q8_0 matrix (the vocabulary head) is walked in K parts of 8 blocks (272 bytes per row): a stage then holds
+    // 128 rows, every warp owns a 16-row tile of its own and no cross-warp reduction is needed (with whole rows per stage
+    // only 16 or 32 rows fit, the eight warps split K and reduce through shared memory after every stage).
+    if (!q4 && layout == TSP_LAYOUT_GGUF && !gateup && a->experts == 1 && !contiguous && p.nunit % 8 == 0 && p.nunit > 8 && a->rows >= 128) {
+        p.units_per_part = 8;
+        p.kparts = p.nunit / 8;
+        row_bytes = 8 * 34;
+    }
     p.row_bytes = contiguous ? 0 : row_bytes;
-    p.row_stride = contiguous ? row_bytes : pad_row(row_bytes);
+    // a tensor copy lays the rows of a K part down densely; per-row copies pad the rows against bank conflicts
+    p.row_stride = contiguous || p.kparts > 1 ? row_bytes : pad_row(row_bytes);
     // rows per stage: as many as fit ~40 KB, in MMA tiles of 16 rows
     const uint32_t per_row_total = p.row_stride + (layout == TSP_LAYOUT_PLANAR ? (q4 ? p.nunit * 20 : p.nunit * 2) : 0);
     uint32_t stage_rows = 128;
@@ -561,11 +605,17 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
     p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
+    CUtensorMap map{};
+    if (p.kparts > 1) {   // [row bytes][rows] as 16-bit elements: a box of one K part (272 bytes) of 128 rows
+        const uint64_t dims[2] = {p.src_row_pitch / 2, a->rows}, strides[1] = {p.src_row_pitch};
+        const uint32_t box[2] = {p.row_bytes / 2, p.rows_per_item};
+        if (int rc = get_tensor_map_elems(a->base, 2, 2, dims, strides, box, false, &map)) return rc;
+    }
 
 #define TSP_DISPATCH(T, L)                                                                           \
     if (type == T && layout == L) {                                                                   \
-        if (gateup) return nc == 1 ? launch_one<T, L, true, 1>(p, smem, grid, st) : launch_one<T, L, true, 2>(p, smem, grid, st); \
-        return nc == 1 ? launch_one<T, L, false, 1>(p, smem, grid, st) : launch_one<T, L, false, 2>(p, smem, grid, st);           \
+        if (gateup) return nc == 1 ? launch_one<T, L, true, 1>(p, map, smem, grid, st) : launch_one<T, L, true, 2>(p, map, smem, grid, st); \
+        return nc == 1 ? launch_one<T, L, false, 1>(p, map, smem, grid, st) : launch_one<T, L, false, 2>(p, map, smem, grid, st);           \
     }
     TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR)
     TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_GGUF)

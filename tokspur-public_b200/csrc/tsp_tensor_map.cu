@@ -44,14 +44,16 @@ struct GenKeyHash {
     }
 };
 
-// dims/box in bytes for dimension 0 (element type is UINT8); strides are the byte strides of dimensions 1..rank-1.
-int get_tensor_map_bytes(const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+// dims/box of dimension 0 in elements of `elem_bytes` (1, 2 or 4: a box may hold at most 256 elements per dimension, so wider
+// elements allow wider boxes); strides are the byte strides of dimensions 1..rank-1.
+int get_tensor_map_elems(const void* base, uint32_t elem_bytes, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
                          bool swizzle128, CUtensorMap* out) {
     static std::mutex mu;
     static std::unordered_map<GenKey, CUtensorMap, GenKeyHash> cache;
     GenKey k{};
-    k.base = base; k.rank = rank; k.swizzle = swizzle128 ? 1u : 0u;
+    k.base = base; k.rank = rank; k.swizzle = (swizzle128 ? 1u : 0u) | (elem_bytes << 4);
     if (rank < 1 || rank > 5) return fail(TSP_E_ARG, "tensor map rank %u out of range", rank);
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return fail(TSP_E_ARG, "tensor map element size %u not supported", elem_bytes);
     for (uint32_t i = 0; i < 5; ++i) { k.dims[i] = i < rank ? dims[i] : 1; k.box[i] = i < rank ? box[i] : 1; }
     for (uint32_t i = 0; i < 4; ++i) k.strides[i] = i + 1 < rank ? strides[i] : 0;
     std::lock_guard<std::mutex> lock(mu);
@@ -63,8 +65,9 @@ int get_tensor_map_bytes(const void* base, uint32_t rank, const uint64_t* dims, 
     cuuint32_t b[5], es[5] = {1, 1, 1, 1, 1};
     for (uint32_t i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
     for (uint32_t i = 0; i + 1 < rank; ++i) st[i] = strides[i];
+    const CUtensorMapDataType type = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
     CUtensorMap m;
-    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const CUresult r = enc(&m, type, rank, const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TSP_E_CUDA, "cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
@@ -72,6 +75,12 @@ int get_tensor_map_bytes(const void* base, uint32_t rank, const uint64_t* dims, 
     cache.emplace(k, m);
     *out = m;
     return TSP_OK;
+}
+
+// the same with byte elements
+int get_tensor_map_bytes(const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                         bool swizzle128, CUtensorMap* out) {
+    return get_tensor_map_elems(base, 1, rank, dims, strides, box, swizzle128, out);
 }
 
 }  // namespace tsp

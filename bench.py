@@ -181,7 +181,11 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     T = args.tokens
     layout = formats.PLANAR if args.layout == "planar" else formats.GGUF
-    layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, formats.Q4_K, layout, dev, keep_gguf=(i == 0))
+    etype = formats.Q8_0 if args.experts == "q8_0" else formats.Q4_K   # q8_0: the MTP block of BASELINE configs[3]
+    blk_bytes, blk_cols = (34, 32) if etype == formats.Q8_0 else (144, 256)
+    expert_gate_up = 2 * HIDDEN * (CHANNELS // blk_cols) * blk_bytes
+    expert_down = CHANNELS * (HIDDEN // blk_cols) * blk_bytes
+    layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, etype, layout, dev, keep_gguf=(i == 0))
               for i in range(args.layers)]
     scratch = L.Scratch(CHANNELS, HIDDEN, EXPERTS, SELECTED, T, dev)
     nb = 8
@@ -236,14 +240,15 @@ def run_ours(args):
     hbm_peak, _, peak_kind = peaks()
     U = stages["unique_experts"]
     # the launch covers the routed experts that were hit plus the shared expert; activations in (binary16), hidden rows out (FP32)
-    gu_bytes = (U + 1) * GGUF_EXPERT_GATE_UP + T * CHANNELS * 2 + T * (SELECTED + 1) * HIDDEN * 4
-    layer_bytes = (U + 1) * (GGUF_EXPERT_GATE_UP + GGUF_EXPERT_DOWN) + T * (CHANNELS * 2 * 2) + T * EXPERTS * 4
+    gu_bytes = (U + 1) * expert_gate_up + T * CHANNELS * 2 + T * (SELECTED + 1) * HIDDEN * 4
+    layer_bytes = (U + 1) * (expert_gate_up + expert_down) + T * (CHANNELS * 2 * 2) + T * EXPERTS * 4
     achieved = gu_bytes / (stages["gate_up_ms"] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "gemv3_kernel<planar, gate-up+SwiGLU> (routed experts + shared expert, one launch)", "achieved": achieved, "peak": hbm_peak,
                 "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (361 experts: 457.2 MB) scaled to the
                 # experts this run's batches hit; traffic grows with the experts touched, the activations stay in L2
-                "traffic": NCU_GATE_UP_DRAM_BYTES_PER_EXPERT * (U + 1), "traffic_source": "ncu capture scaled by experts hit",
+                "traffic": NCU_GATE_UP_DRAM_BYTES_PER_EXPERT * (U + 1) if etype == formats.Q4_K else None,
+                "traffic_source": "ncu capture scaled by experts hit" if etype == formats.Q4_K else None,
                 "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": stages["gate_up_ms"]}
 
     # CPU baseline on the same first layer and batch 0, and an in-run parity figure
@@ -270,8 +275,8 @@ def run_ours(args):
     line = {"metric": "moe_q4k_expert_gemm_tokens_per_s", "value": tokens_s, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"moe_layer_decode_T{T} (BASELINE configs[1])", "hidden": CHANNELS, "experts": EXPERTS, "expert_ffn": HIDDEN,
-                       "top_k": SELECTED, "weights": "Q4_K " + ("Pack-v3 planar" if layout == formats.PLANAR else "GGUF"),
+            "config": {"workload": f"moe_layer_decode_T{T} (BASELINE configs[1])" if etype == formats.Q4_K else f"q8_0_mtp_moe_block_T{T} (BASELINE configs[3])", "hidden": CHANNELS, "experts": EXPERTS, "expert_ffn": HIDDEN,
+                       "top_k": SELECTED, "weights": ("Q8_0 " if etype == formats.Q8_0 else "Q4_K ") + ("Pack-v3 planar" if layout == formats.PLANAR else "GGUF"),
                        "activations": "binary16 in/out, FP32 accumulate", "layers_rotated": len(layers),
                        "l2_policy": "inputs larger than L2: each step streams ~650 MB of distinct expert weights"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -544,6 +549,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=64, help="token rows per step (decode batch)")
     ap.add_argument("--layers", type=int, default=4, help="independently seeded weight sets rotated over")
     ap.add_argument("--layout", default="planar", choices=["planar", "gguf"])
+    ap.add_argument("--experts", default="q4_k", choices=["q4_k", "q8_0"], help="expert encoding of the decode workload (q8_0: the MTP block)")
     ap.add_argument("--cpu-tokens", type=int, default=None, help="tokens of the batch timed on the CPU baseline (0 = skip)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "head"])
     ap.add_argument("--ep-scheme", default="gather", choices=["gather", "alltoall"], help="multi-GPU exchange: all-gather/reduce-scatter or all-to-all")

@@ -92,7 +92,8 @@ __device__ __forceinline__ void route_row(float* row, const float* __restrict__ 
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t tokens, uint32_t experts,
              uint32_t selected, uint32_t mode, int normalize, uint32_t* __restrict__ ids,
-             float* __restrict__ weights, uint32_t* error) {    pdl_launch_dependents();
+             float* __restrict__ weights, uint32_t* error) {
+    pdl_launch_dependents();
     pdl_wait();
 
     extern __shared__ float route_smem[];
@@ -110,7 +111,8 @@ constexpr int kPermuteThreads = 128;
 
 __global__ void __launch_bounds__(kPermuteThreads)
 grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t first, int local_only,
-                      uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* error) {    pdl_launch_dependents();
+                      uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* error) {
+    pdl_launch_dependents();
     pdl_wait();
 
     __shared__ uint32_t totals[kPermuteThreads / 32];
@@ -146,7 +148,8 @@ grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_
 // tasks = {live_tiles, routes, (expert, start) pairs in ascending expert order, 0xffffffff padding}
 __global__ void __launch_bounds__(256)
 grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint32_t experts, uint32_t selected,
-                     uint32_t tile, uint32_t bound, int local_only, uint32_t* __restrict__ tasks, uint32_t* error) {    pdl_launch_dependents();
+                     uint32_t tile, uint32_t bound, int local_only, uint32_t* __restrict__ tasks, uint32_t* error) {
+    pdl_launch_dependents();
     pdl_wait();
 
     extern __shared__ uint32_t offsets[];  // experts + 1
@@ -205,7 +208,8 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
                const float* __restrict__ shared, uint64_t shared_stride, const float* __restrict__ shared_router,
                const float* __restrict__ x, uint64_t x_stride, float* shared_logit, uint32_t channels,
                uint32_t selected, float* __restrict__ out, uint64_t out_stride, __half* __restrict__ out16,
-               uint64_t out16_stride, int vec4, uint32_t* error) {    pdl_launch_dependents();
+               uint64_t out16_stride, int vec4, uint32_t* error) {
+    pdl_launch_dependents();
     pdl_wait();
 
     __shared__ float partial[kCombineThreads / 32];
@@ -279,7 +283,8 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 gemv_f32_kernel(const float* __restrict__ w, uint32_t rows, uint32_t cols, const float* __restrict__ x, uint64_t x_stride, uint32_t tokens,
-                float* __restrict__ out, uint64_t out_stride, uint32_t* error) {    pdl_launch_dependents();
+                float* __restrict__ out, uint64_t out_stride, uint32_t* error) {
+    pdl_launch_dependents();
     pdl_wait();
 
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -304,7 +309,8 @@ int launch_gemv_f32(const float* w, uint32_t rows, uint32_t cols, const float* x
 }
 
 __global__ void rows_f16_to_f32_kernel(const __half* __restrict__ in, uint64_t in_stride, float* __restrict__ out,
-                                       uint64_t out_stride, uint32_t rows, uint32_t cols) {    pdl_launch_dependents();
+                                       uint64_t out_stride, uint32_t rows, uint32_t cols) {
+    pdl_launch_dependents();
     pdl_wait();
 
     const uint32_t row = blockIdx.y;

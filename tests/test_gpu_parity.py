@@ -192,7 +192,7 @@ def test_config1_single_q4k_matmul(oracle, layout, M):
 
 @pytest.mark.parametrize("type_,layout,rows,cols", [(8, formats.GGUF, 512, 2048), (8, formats.PLANAR, 512, 2048), (8, formats.GGUF, 64, 64),
                                                     (8, formats.PLANAR, 256, 64), (12, formats.GGUF, 48, 256), (12, formats.PLANAR, 2048, 512),
-                                                    (12, formats.GGUF, 2048, 512), (8, formats.GGUF, 16, 2560)])
+                                                    (12, formats.GGUF, 2048, 512), (8, formats.GGUF, 16, 2560), (8, formats.GGUF, 208, 512)])
 def test_dense_projection_shapes(oracle, type_, layout, rows, cols):
     w = fixtures.bounded_weights(type_, cols, rows, 1, seed=rows + cols)[0]
     for M, exact in ((1, False), (3, False), (11, False)):

@@ -25,8 +25,7 @@ namespace tsp {
 int get_tensor_map_elems(const void* base, uint32_t elem_bytes, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
                          bool swizzle128, CUtensorMap* out);
 
-constexpr int kConsumerWarps = 8;
-constexpr int kGemvThreads = (kConsumerWarps + 1) * 32;
+constexpr int kConsumerWarps = 8;     // consumer warps of most shapes; the K-part mode of a dense matrix runs 16
 constexpr uint32_t kMaxStages = 6;
 
 struct GemvParams {
@@ -94,8 +93,8 @@ __device__ __forceinline__ TileInfo tile_info(const GemvParams& p, uint32_t tile
     return t;
 }
 
-template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap part_map) {
+template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC, int CW>
+__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap part_map) {
     pdl_launch_dependents();
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -105,7 +104,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     const uint32_t NS = p.n_stages;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < NS; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kConsumerWarps); }
+        for (uint32_t s = 0; s < NS; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
         mbar_fence_init();
     }
     __syncthreads();
@@ -117,7 +116,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
 
-    if (warp == kConsumerWarps) {
+    if (warp == CW) {
         // ------------------------------ producer warp ------------------------------
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -183,11 +182,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 
     // -------------------------------- consumer warps --------------------------------
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t ctid = threadIdx.x;  // 0..255
-    constexpr uint32_t CTHREADS = kConsumerWarps * 32;
+    const uint32_t ctid = threadIdx.x;  // 0 .. 32 CW - 1
+    constexpr uint32_t CTHREADS = CW * 32;
     const uint32_t nrt = p.nrt;
-    const uint32_t kp_count = nrt >= kConsumerWarps ? 1u : kConsumerWarps / nrt;
-    const uint32_t my_kp = nrt >= kConsumerWarps ? 0u : warp / nrt;
+    const uint32_t kp_count = nrt >= CW ? 1u : CW / nrt;
+    const uint32_t my_kp = nrt >= CW ? 0u : warp / nrt;
+    const uint32_t red_slots = nrt >= CW ? 0u : CW - nrt;   // warps that hand partial sums to the first nrt warps
     uint8_t* xhi = smem + p.off_xhi;
     uint8_t* xlo = smem + p.off_xlo;
     uint8_t* sxb = smem + p.off_sx;
@@ -267,9 +267,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         }
 
         const uint32_t r0 = ri * p.rows_per_item;
-        // every consumer warp has exactly one row tile of the item (nrt <= 8): rt = warp, or warp % nrt when several warps
+        // every consumer warp has exactly one row tile of the item (nrt <= CW): rt = warp, or warp % nrt when several warps
         // share a tile and split K among them
-        const uint32_t rt = nrt >= kConsumerWarps ? warp : warp % nrt;
+        const uint32_t rt = nrt >= CW ? warp : warp % nrt;
         {
             float total[NC][4];
 #pragma unroll
@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                     }
                 }
             }
-            if (kh + 1 < p.kparts) {   // more parts of this item follow: hand the stage back and move on (kparts > 1 implies kp_count == 1)
+            if (kh + 1 < p.kparts) {   // more parts of this item follow: hand the stage back and move on
                 __syncwarp();
                 if (lane == 0 && ok) mbar_arrive(&empty[stage]);
                 if (++stage == NS) { stage = 0; phase ^= 1u; }
@@ -429,7 +429,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             }
             // ---- cross-warp reduction over the K parts (only when one row tile is shared by several warps) ----
             if (kp_count > 1) {
-                float* slot = red + ((parity * kConsumerWarps + warp) * 32 + lane) * (4 * NC);
+                float* slot = red + ((parity * red_slots + (my_kp != 0 ? warp - nrt : 0u)) * 32 + lane) * (4 * NC);
                 if (my_kp != 0) {
 #pragma unroll
                     for (int c = 0; c < NC; ++c) *reinterpret_cast<float4*>(slot + 4 * c) = make_float4(total[c][0], total[c][1], total[c][2], total[c][3]);
@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                 named_bar_sync(1, CTHREADS);
                 if (my_kp == 0) {
                     for (uint32_t kp = 1; kp < kp_count; ++kp) {
-                        const float* other = red + ((parity * kConsumerWarps + kp * nrt + rt) * 32 + lane) * (4 * NC);
+                        const float* other = red + ((parity * red_slots + (kp - 1) * nrt + rt) * 32 + lane) * (4 * NC);
 #pragma unroll
                         for (int c = 0; c < NC; ++c) {
                             const float4 v = *reinterpret_cast<const float4*>(other + 4 * c);
@@ -500,15 +500,15 @@ static uint32_t pad_row(uint32_t row_bytes) {
     return row_bytes + 32;
 }
 
-template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC>
+template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC, int CW = kConsumerWarps>
 static int launch_one(const GemvParams& p, const CUtensorMap& map, size_t smem, int grid, cudaStream_t st) {
-    auto kernel = gemv_kernel<TYPE, LAYOUT, GATEUP, NC>;
+    auto kernel = gemv_kernel<TYPE, LAYOUT, GATEUP, NC, CW>;
     static thread_local size_t configured = 0;
     if (smem > configured) {
         TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGemvThreads), smem, st, p, map));
+    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3((CW + 1) * 32), smem, st, p, map));
     return TSP_OK;
 }
 
@@ -592,7 +592,10 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
     p.off_xlo = off; if (p.split_lo) off += tok * p.x_stride;
     p.off_sx = off; off += (q4 ? 2 : 1) * tok * p.sx_stride;
     off = (off + 15u) & ~15u;
-    p.off_red = off; off += 2 * kConsumerWarps * 32 * 4 * nc * 4;
+    // consumer warps: 16 in the K-part mode (two warps per 16-row tile, each half of a part's blocks, one reduction per item: with
+    // eight the warps were bound by their own dependent-instruction latency at half the issue rate), 8 otherwise
+    const uint32_t cw = p.kparts > 1 ? 16u : static_cast<uint32_t>(kConsumerWarps);
+    p.off_red = off; off += 2 * (cw > p.nrt ? cw - p.nrt : 0u) * 32 * 4 * nc * 4;
     off = (off + 127u) & ~127u;
     p.off_stage = off;
     const uint32_t budget = 227 * 1024;
@@ -617,6 +620,9 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
         if (gateup) return nc == 1 ? launch_one<T, L, true, 1>(p, map, smem, grid, st) : launch_one<T, L, true, 2>(p, map, smem, grid, st); \
         return nc == 1 ? launch_one<T, L, false, 1>(p, map, smem, grid, st) : launch_one<T, L, false, 2>(p, map, smem, grid, st);           \
     }
+    if (p.kparts > 1)   // dense GGUF Q8_0 matrix in K parts
+        return nc == 1 ? launch_one<TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF, false, 1, 16>(p, map, smem, grid, st)
+                       : launch_one<TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF, false, 2, 16>(p, map, smem, grid, st);
     TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR)
     TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_GGUF)
     TSP_DISPATCH(TSP_TYPE_Q8_0, TSP_LAYOUT_PLANAR)

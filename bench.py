@@ -180,7 +180,9 @@ def run_ours(args):
         return run_head(args, local)
     dev = torch.device("cuda", local)
     T = args.tokens
-    layout = formats.PLANAR if args.layout == "planar" else formats.GGUF
+    # Q4_K experts default to the Pack-v3 planar layout, Q8_0 experts (the MTP block) stay GGUF blocks
+    lname = args.layout or ("gguf" if args.experts == "q8_0" else "planar")
+    layout = formats.PLANAR if lname == "planar" else formats.GGUF
     etype = formats.Q8_0 if args.experts == "q8_0" else formats.Q4_K   # q8_0: the MTP block of BASELINE configs[3]
     blk_bytes, blk_cols = (34, 32) if etype == formats.Q8_0 else (144, 256)
     expert_gate_up = 2 * HIDDEN * (CHANNELS // blk_cols) * blk_bytes
@@ -548,7 +550,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=64, help="token rows per step (decode batch)")
     ap.add_argument("--layers", type=int, default=4, help="independently seeded weight sets rotated over")
-    ap.add_argument("--layout", default="planar", choices=["planar", "gguf"])
+    ap.add_argument("--layout", default=None, choices=["planar", "gguf"], help="weight layout (default: Pack-v3 planar for Q4_K experts, GGUF blocks for Q8_0 experts)")
     ap.add_argument("--experts", default="q4_k", choices=["q4_k", "q8_0"], help="expert encoding of the decode workload (q8_0: the MTP block)")
     ap.add_argument("--cpu-tokens", type=int, default=None, help="tokens of the batch timed on the CPU baseline (0 = skip)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "head"])

@@ -243,7 +243,7 @@ def test_layer_matches_reference_outputs(oracle, type_, layout):
 
 
 @pytest.mark.parametrize("T", [1, 2, 8, 9, 29, 64])
-@pytest.mark.parametrize("type_,layout", [(12, formats.PLANAR), (12, formats.GGUF), (8, formats.PLANAR)])
+@pytest.mark.parametrize("type_,layout", [(12, formats.PLANAR), (12, formats.GGUF), (8, formats.PLANAR), (8, formats.GGUF)])
 def test_layer_synthetic_quantised(oracle, T, type_, layout):
     """N(0, 0.02) weights through this build's encoders, binary16 N(0,1) activations in and binary16 out, top-k of 16 experts
     (so that several tokens share an expert and tiles of more than 8 routes occur)."""
@@ -258,6 +258,21 @@ def test_layer_synthetic_quantised(oracle, T, type_, layout):
     assert scaled_error(s.routed.cpu().numpy()[:T * K * Cn].reshape(T, K, Cn), st["routed"]) <= 5e-5
     assert rel_l2(out16.astype(np.float32), want) <= 2e-3      # the benchmark's bar, output rounded to binary16
     out32, s2, _ = run_layer(host, layout, x16.astype(np.float32), logits)  # FP32 rows in/out: the reference API's dtype
+    assert rel_l2(out32, want) <= 1e-5 and scaled_error(out32, want) <= 5e-5
+
+
+@pytest.mark.parametrize("T", [3, 29])
+def test_layer_q8_0_gguf_k_part_stages(oracle, T):
+    """Q8_0 experts kept as GGUF blocks with rows of 16 blocks: gate-up [512 x 512] and down [512 x 512] both take the K-part
+    stages (eight blocks of 128 rows per tensor copy, sixteen consumer warps, one reduction per item)."""
+    Cn, H, E, K = 512, 512, 16, 4
+    host = L.synth_host_layer(13, Cn, H, E, K, expert_type=8)
+    x16 = synth.activations_f16(7, T, Cn)
+    logits = synth.router_logits(8, T, E)
+    out32, s, _ = run_layer(host, formats.GGUF, x16.astype(np.float32), logits)
+    assert s.error_word() == 0
+    want, st = oracle.moe_layer(host.oracle_dict(), x16.astype(np.float32), logits, threads=4, stages=True)
+    assert scaled_error(s.routed.cpu().numpy()[:T * K * Cn].reshape(T, K, Cn), st["routed"]) <= 5e-5
     assert rel_l2(out32, want) <= 1e-5 and scaled_error(out32, want) <= 5e-5
 
 

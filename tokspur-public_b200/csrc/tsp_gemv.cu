@@ -28,6 +28,9 @@ int get_tensor_map_elems(const void* base, uint32_t elem_bytes, uint32_t rank, c
 constexpr int kConsumerWarps = 8;     // consumer warps of most shapes; the K-part mode of a dense matrix runs 16
 constexpr uint32_t kMaxStages = 6;
 
+// Tensor maps of the K-part mode: [part bytes as 16-bit elements][rows][experts] of matrix set A (low ids, high ids) and B (same)
+struct alignas(64) GemvPartMaps { CUtensorMap m[4]; };
+
 struct GemvParams {
     // weights
     const uint8_t* a_base; const uint8_t* a_base_hi;   // matrix set A (gate, or the only matrix)
@@ -94,7 +97,7 @@ __device__ __forceinline__ TileInfo tile_info(const GemvParams& p, uint32_t tile
 }
 
 template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC, int CW>
-__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap part_map) {
+__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams p, const __grid_constant__ GemvPartMaps part_maps) {
     pdl_launch_dependents();
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -131,13 +134,18 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
             if (!ok) { if (lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT); break; }
             uint8_t* sbase = smem + p.off_stage + stage * p.stage_bytes;
             if (p.kparts > 1) {
-                // K-part stages of a dense matrix: ONE tensor copy brings this part of all the item's rows ([part bytes][rows]
-                // box; rows past the matrix end are filled with zeros and still count as delivered bytes)
+                // K-part stages of GGUF Q8_0 rows: ONE tensor copy per matrix brings this part of all the item's rows ([part bytes]
+                // [rows][expert] box; rows past the matrix end are filled with zeros and still count as delivered bytes)
                 if (lane == 0) {
-                    mbar_arrive_expect_tx(&full[stage], p.rows_per_item * p.row_bytes);
-                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                                 ::"r"(smem_u32(sbase)), "l"(reinterpret_cast<uint64_t>(&part_map)), "r"(smem_u32(&full[stage])),
-                                   "r"(static_cast<int>(kh * p.row_bytes / 2)), "r"(static_cast<int>(r0)) : "memory");
+                    mbar_arrive_expect_tx(&full[stage], NMAT * p.rows_per_item * p.row_bytes);
+                    const bool hi = ti.expert >= p.split;
+                    const int el = static_cast<int>(hi ? ti.expert - p.split : ti.expert);
+#pragma unroll
+                    for (uint32_t m = 0; m < NMAT; ++m)
+                        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                                     ::"r"(smem_u32(sbase + m * p.rows_per_item * p.row_stride)),
+                                       "l"(reinterpret_cast<uint64_t>(&part_maps.m[2 * m + (hi ? 1 : 0)])), "r"(smem_u32(&full[stage])),
+                                       "r"(static_cast<int>(kh * p.row_bytes / 2)), "r"(static_cast<int>(r0)), "r"(el) : "memory");
                 }
                 if (++stage == NS) { stage = 0; phase ^= 1u; }
                 continue;
@@ -501,7 +509,7 @@ static uint32_t pad_row(uint32_t row_bytes) {
 }
 
 template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC, int CW = kConsumerWarps>
-static int launch_one(const GemvParams& p, const CUtensorMap& map, size_t smem, int grid, cudaStream_t st) {
+static int launch_one(const GemvParams& p, const GemvPartMaps& map, size_t smem, int grid, cudaStream_t st) {
     auto kernel = gemv_kernel<TYPE, LAYOUT, GATEUP, NC, CW>;
     static thread_local size_t configured = 0;
     if (smem > configured) {
@@ -550,10 +558,10 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
     p.src_row_pitch = row_bytes;
     p.kparts = 1;
     p.units_per_part = p.nunit;
-    // A dense GGUF Q8_0 matrix (the vocabulary head) is walked in K parts of 8 blocks (272 bytes per row): a stage then holds
-    // 128 rows, every warp owns a 16-row tile of its own and no cross-warp reduction is needed (with whole rows per stage
-    // only 16 or 32 rows fit, the eight warps split K and reduce through shared memory after every stage).
-    if (!q4 && layout == TSP_LAYOUT_GGUF && !gateup && a->experts == 1 && !contiguous && p.nunit % 8 == 0 && p.nunit > 8 && a->rows >= 128) {
+    // GGUF Q8_0 matrices (the vocabulary head, the experts of the MTP block) are walked in K parts of 8 blocks (272 bytes per
+    // row): a stage then holds 128 rows (gate-up: 64 + 64) and the partial sums of a row tile are reduced once per item (with
+    // whole rows per stage only 16 or 32 rows fit, and the warps reduce through shared memory after every stage).
+    if (!q4 && layout == TSP_LAYOUT_GGUF && !contiguous && p.nunit % 8 == 0 && p.nunit > 8 && a->rows >= 128) {
         p.units_per_part = 8;
         p.kparts = p.nunit / 8;
         row_bytes = 8 * 34;
@@ -608,11 +616,17 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
     p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
-    CUtensorMap map{};
-    if (p.kparts > 1) {   // [row bytes][rows] as 16-bit elements: a box of one K part (272 bytes) of 128 rows
-        const uint64_t dims[2] = {p.src_row_pitch / 2, a->rows}, strides[1] = {p.src_row_pitch};
-        const uint32_t box[2] = {p.row_bytes / 2, p.rows_per_item};
-        if (int rc = get_tensor_map_elems(a->base, 2, 2, dims, strides, box, false, &map)) return rc;
+    GemvPartMaps map{};
+    if (p.kparts > 1) {   // [row bytes][rows][experts] as 16-bit elements: a box of one K part (272 bytes) of the item's rows
+        if (p.expert_stride % 16 != 0 && a->experts > 1) return fail(TSP_E_ARG, "project: expert stride must be a multiple of 16 bytes");
+        const uint32_t box[3] = {p.row_bytes / 2, p.rows_per_item, 1};
+        const uint64_t n_lo = p.split ? p.split : 1, n_hi = p.experts > p.split ? p.experts - p.split : 1;
+        const uint64_t strides[2] = {p.src_row_pitch, p.expert_stride ? p.expert_stride : static_cast<uint64_t>(a->rows) * p.src_row_pitch};
+        for (uint32_t m = 0; m < nmat; ++m) {
+            const uint64_t d_lo[3] = {p.src_row_pitch / 2, a->rows, n_lo}, d_hi[3] = {p.src_row_pitch / 2, a->rows, n_hi};
+            if (int rc = get_tensor_map_elems(m ? p.b_base : p.a_base, 2, 3, d_lo, strides, box, false, &map.m[2 * m])) return rc;
+            if (int rc = get_tensor_map_elems(m ? p.b_base_hi : p.a_base_hi, 2, 3, d_hi, strides, box, false, &map.m[2 * m + 1])) return rc;
+        }
     }
 
 #define TSP_DISPATCH(T, L)                                                                           \
@@ -620,9 +634,12 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
         if (gateup) return nc == 1 ? launch_one<T, L, true, 1>(p, map, smem, grid, st) : launch_one<T, L, true, 2>(p, map, smem, grid, st); \
         return nc == 1 ? launch_one<T, L, false, 1>(p, map, smem, grid, st) : launch_one<T, L, false, 2>(p, map, smem, grid, st);           \
     }
-    if (p.kparts > 1)   // dense GGUF Q8_0 matrix in K parts
+    if (p.kparts > 1) {   // GGUF Q8_0 in K parts
+        if (gateup) return nc == 1 ? launch_one<TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF, true, 1, 16>(p, map, smem, grid, st)
+                                   : launch_one<TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF, true, 2, 16>(p, map, smem, grid, st);
         return nc == 1 ? launch_one<TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF, false, 1, 16>(p, map, smem, grid, st)
                        : launch_one<TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF, false, 2, 16>(p, map, smem, grid, st);
+    }
     TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR)
     TSP_DISPATCH(TSP_TYPE_Q4_K, TSP_LAYOUT_GGUF)
     TSP_DISPATCH(TSP_TYPE_Q8_0, TSP_LAYOUT_PLANAR)

@@ -245,7 +245,9 @@ def run_ours(args):
     gu_bytes = (U + 1) * expert_gate_up + T * CHANNELS * 2 + T * (SELECTED + 1) * HIDDEN * 4
     layer_bytes = (U + 1) * (expert_gate_up + expert_down) + T * (CHANNELS * 2 * 2) + T * EXPERTS * 4
     achieved = gu_bytes / (stages["gate_up_ms"] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gemv3_kernel<planar, gate-up+SwiGLU> (routed experts + shared expert, one launch)", "achieved": achieved, "peak": hbm_peak,
+    kname = ("gemv3_kernel<planar, gate-up+SwiGLU> (routed experts + shared expert, one launch)" if etype == formats.Q4_K else
+             "gemv_kernel<Q8_0, gate-up+SwiGLU> (routed experts, then the shared expert: two launches timed together)")
+    roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": hbm_peak,
                 "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (361 experts: 457.2 MB) scaled to the
                 # experts this run's batches hit; traffic grows with the experts touched, the activations stay in L2

@@ -7,10 +7,13 @@
 //   * one producer warp streams the slab's bytes global -> shared with bulk asynchronous copies
 //     (TMA, untiled form) into a ring of stages guarded by full/empty mbarriers, so the bytes in
 //     flight per SM do not depend on registers or occupancy;
-//   * eight consumer warps dequantise in registers and feed warp-level tensor-core MMAs
+//   * eight (K parts: sixteen) consumer warps dequantise in registers and feed warp-level tensor-core MMAs
 //     (m16n8k16, f16 x f16 -> f32): weight codes enter as *exact* small integers (binary16
 //     subnormals q*2^-24), activations as binary16 high (+ optional low) halves, and the per-group
 //     scales/mins are applied to the FP32 partial sums, so the result carries FP32-level error only;
+//   * GGUF Q8_0 matrices whose rows hold a multiple of 8 blocks are walked in K parts instead: a stage is 8 blocks
+//     (272 bytes) of 128 rows brought by one tensor copy per matrix, sixteen consumer warps work on it (two per
+//     16-row tile, each half of the part's blocks) and reduce their partial sums once per item;
 //   * every wait is bounded; a timeout sets TSP_ERR_TIMEOUT in the sticky error word.
 //
 // The reduction index inside one 8-wide run of K is permuted identically for weights and

@@ -285,7 +285,7 @@ def run_ours(args):
                        "l2_policy": "inputs larger than L2: each step streams ~650 MB of distinct expert weights"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2},
-            "gpu_launches": 7 * args.steps, "clocks": clk, "roofline": roofline, "cpu_baseline": cpu,
+            "gpu_launches": 4 * args.steps, "clocks": clk, "roofline": roofline, "cpu_baseline": cpu,
             "extra": {"layer_hbm_gbs": layer_bytes / (ms * 1e-3) / 1e9, "layer_hbm_frac": layer_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
                       "layer_algorithmic_bytes": layer_bytes, "unique_experts": U, "stage_ms": stages, "parity_rel_l2_vs_cpu": parity,
                       "layer_tflops": T * (SELECTED + 1) * FLOPS_PER_ROUTE / (ms * 1e-3) / 1e12}}
@@ -308,7 +308,6 @@ def run_prefill(args, local):
     host_lg = [torch.from_numpy(synth.router_logits(2000 + b, T, EXPERTS, bias)).pin_memory() for b in range(nb)]
     dev_x = [t.to(dev) for t in host_x]
     dev_lg = [t.to(dev) for t in host_lg]
-    x32 = torch.zeros((T, CHANNELS), dtype=torch.float32, device=dev)
     out = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
     host_out = torch.zeros((T, CHANNELS), dtype=torch.float16).pin_memory()
     sx, slg = torch.zeros_like(dev_x[0]), torch.zeros_like(dev_lg[0])
@@ -341,34 +340,29 @@ def run_prefill(args, local):
         return e0.elapsed_time(e1) / steps
 
     def stage_pass(steps):
-        """CUDA-event time of each launch of the prefill layer."""
+        """CUDA-event time of each launch of the prefill layer, issued exactly as tsp_moe_layer_prefill issues them."""
         s, st = ps.base, L.stream_ptr()
-        names = ["convert", "route", "permute", "offsets", "gather", "gate_up", "down", "combine"]
+        names = ["rows_f16k", "route", "permute", "offsets", "gate_up", "down", "combine"]
         acc = dict.fromkeys(names, 0.0)
-        C4, E, K = CHANNELS * 4, EXPERTS, SELECTED
+        C2, C4, H2, E, K = CHANNELS * 2, CHANNELS * 4, HIDDEN * 2, EXPERTS, SELECTED
         for i in range(steps):
             w = layers[i % len(layers)].weights
             x, lg = dev_x[i % nb], dev_lg[i % nb]
             e = s.error.data_ptr()
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
             ev[0].record()
-            capi.check(lib.tsp_rows_f16_to_f32(x.data_ptr(), CHANNELS * 2, x32.data_ptr(), C4, T, CHANNELS, st)); ev[1].record()
+            capi.check(lib.tsp_moe_rows_f16k(x.data_ptr(), C2, 1, T, CHANNELS, ps.xk.data_ptr(), C2, e, st)); ev[1].record()
             capi.check(lib.tsp_moe_route(lg.data_ptr(), E * 4, T, E, K, 0, 1, s.ids.data_ptr(), s.weights.data_ptr(), e, st)); ev[2].record()
-            capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, E, K, 128, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), e, st)); ev[3].record()
+            capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, E, K, ps.tile, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), e, st)); ev[3].record()
             capi.check(lib.tsp_moe_route_offsets(s.counts.data_ptr(), E, ps.offsets.data_ptr(), st)); ev[4].record()
-            capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), C4, K, s.token_map.data_ptr(), ps.offsets.data_ptr(), E, T, K, CHANNELS,
-                                               ps.xp.data_ptr(), CHANNELS * 2, ps.pos_route.data_ptr(), e, st))
-            capi.check(lib.tsp_moe_gather_rows(x32.data_ptr(), C4, 1, None, None, 1, T, 1, CHANNELS, ps.s_xp.data_ptr(), CHANNELS * 2, None, e, st)); ev[5].record()
-            # routed experts + shared expert in one launch each, exactly as tsp_moe_layer_prefill issues them
-            capi.check(lib.tsp_moe_grouped_gate_up_shared(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up), ps.xp.data_ptr(),
-                                                          CHANNELS * 2, T * K, ps.tasks.data_ptr(), s.counts.data_ptr(), ps.offsets.data_ptr(),
-                                                          ps.hp.data_ptr(), HIDDEN * 2, ps.s_xp.data_ptr(), CHANNELS * 2, T, ps.s_hp.data_ptr(),
-                                                          HIDDEN * 2, e, st)); ev[6].record()
-            capi.check(lib.tsp_moe_grouped_down_shared(C.byref(w.down), C.byref(w.shared_down), ps.hp.data_ptr(), HIDDEN * 2, T * K, ps.tasks.data_ptr(),
-                                                       s.counts.data_ptr(), ps.offsets.data_ptr(), ps.pos_route.data_ptr(), s.routed.data_ptr(), C4,
-                                                       ps.s_hp.data_ptr(), HIDDEN * 2, T, s.shared_out.data_ptr(), C4, e, st)); ev[7].record()
-            capi.check(lib.tsp_moe_combine(s.routed.data_ptr(), C4, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
-                                           x32.data_ptr(), C4, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), CHANNELS * 2, e, st)); ev[8].record()
+            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up), ps.xk.data_ptr(), C2, T, K,
+                                                   s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), ps.offsets.data_ptr(),
+                                                   ps.hp.data_ptr(), H2, ps.s_hp.data_ptr(), H2, e, st)); ev[5].record()
+            capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), C.byref(w.shared_down), ps.hp.data_ptr(), H2, T, K, s.token_map.data_ptr(),
+                                                s.counts.data_ptr(), ps.tasks.data_ptr(), ps.offsets.data_ptr(), ps.routed16.data_ptr(), C2, 1,
+                                                ps.s_hp.data_ptr(), H2, s.shared_out.data_ptr(), C4, e, st)); ev[6].record()
+            capi.check(lib.tsp_moe_combine(ps.routed16.data_ptr(), C2, 1, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
+                                           x.data_ptr(), C2, 1, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), C2, e, st)); ev[7].record()
             torch.cuda.synchronize()
             for k_, n in enumerate(names):
                 acc[n] += ev[k_].elapsed_time(ev[k_ + 1])
@@ -407,7 +401,7 @@ def run_prefill(args, local):
                        "l2_policy": "inputs larger than L2: 0.93 GB of weights and 0.5 GB of intermediates per step"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2},
-            "gpu_launches": 11 * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": 8 * args.steps, "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "kernel": "grouped_mma_kernel<gate-up> (routed experts + shared expert, tcgen05)", "achieved": achieved, "peak": tf_peak,
                          "unit": "TFLOP/s", "frac": achieved / tf_peak, "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_flops_per_launch": gu_flops, "launch_ms": stages["gate_up_ms"]},
@@ -531,8 +525,8 @@ def stage_times(L, capi, layers, s, dev_x, dev_lg, out, steps, warmup, T):
         capi.check(lib.tsp_moe_project_shared(C.byref(w.down), C.byref(w.shared_down), s.hidden.data_ptr(), H4, s.shared_hidden.data_ptr(), H4,
                                               T, SELECTED, s.token_map.data_ptr(), s.counts.data_ptr(), s.tasks.data_ptr(),
                                               s.routed.data_ptr(), C4, s.shared_out.data_ptr(), C4, e, st)); ev[5].record()
-        capi.check(lib.tsp_moe_combine(s.routed.data_ptr(), C4, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
-                                       s.x32.data_ptr(), C4, s.shared_logit.data_ptr(), T, CHANNELS, SELECTED, None, 0, out.data_ptr(),
+        capi.check(lib.tsp_moe_combine(s.routed.data_ptr(), C4, 0, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
+                                       s.x32.data_ptr(), C4, 0, s.shared_logit.data_ptr(), T, CHANNELS, SELECTED, None, 0, out.data_ptr(),
                                        CHANNELS * 2, e, st)); ev[6].record()
         torch.cuda.synchronize()
         if i >= warmup:

@@ -165,10 +165,11 @@ int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared
  *   out[t][c] = sigmoid(s_t) * shared[t][c] + sum_{r<selected} w[t][r] * routed[t*selected+r][c]
  * accumulated in route-rank order starting from the shared term. s_t = dot(d_shared_router, x[t]) when
  * d_shared_router != NULL (and is stored to d_shared_logit when that is non-NULL), else d_shared_logit[t].
+ * routed_dtype / x_dtype: 0 = FP32 rows, 1 = binary16 rows (the prefill path keeps its route rows as binary16).
  * d_out_f16 (optional) receives the same rows rounded to binary16. */
-int tsp_moe_combine(const float* d_routed, uint64_t routed_stride_bytes, const float* d_weights,
+int tsp_moe_combine(const void* d_routed, uint64_t routed_stride_bytes, uint32_t routed_dtype, const float* d_weights,
                     const float* d_shared, uint64_t shared_stride_bytes,
-                    const float* d_shared_router, const float* d_x, uint64_t x_stride_bytes,
+                    const float* d_shared_router, const void* d_x, uint64_t x_stride_bytes, uint32_t x_dtype,
                     float* d_shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected,
                     float* d_out, uint64_t out_stride_bytes, void* d_out_f16, uint64_t out_f16_stride_bytes,
                     uint32_t* d_error, void* stream);
@@ -233,63 +234,57 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
 /* ---- prefill-size path: grouped per-expert GEMMs on the tcgen05 tensor cores --------------------------
  * Replaces `planar_nax_grouped_moe` (graph.mm:9293-9420) = `graph_grouped_routes` -> `nax_grouped_tasks_indirect` ->
  * `nax_moe_gather_bf16_v3` -> `nax_grouped_moe_gate_up_swiglu_v3` -> `nax_grouped_moe_down_v3`
- * (planar_moe_v3.metal:2406-2621). Weights: Q4_K Pack v3 planar, rows a multiple of 128.
- *   1. tsp_moe_permute(..., tile = TSP_GROUPED_TILE)          token_map / counts / tasks (tiles of 128 routes)
- *   2. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e (experts+1 words)
- *   3. tsp_moe_gather_rows                                     binary16 rows in permuted order + the route id of each position
+ * (planar_moe_v3.metal:2406-2621). Weights: Q4_K Pack v3 planar; hidden a multiple of 64, channels of 256.
+ *   1. tsp_moe_rows_f16k                                       binary16 copy of the input rows in the K order the tensor-core tiles use
+ *   2. tsp_moe_permute(..., tile = TSP_GROUPED_TILE)           token_map / counts / tasks (tasks of 256 routes = two sub-tiles of 128)
+ *   3. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e (experts+1 words)
  *   4. tsp_moe_grouped_gate_up                                 H[pos][hidden] binary16, SwiGLU applied, FP32 accumulate in tensor memory
- *   5. tsp_moe_grouped_down                                    routed[route][channel] FP32, scattered by route id
- * Row buffers in permuted order (d_xp, d_hp) hold max_positions = tokens*selected rows. Values inside each aligned run of 8
- * along the row are stored in the order 0,2,1,3,4,6,5,7 (the order the dequantised weight tiles use), which only these
- * kernels read. Operands are binary16, accumulation FP32.
- * tsp_moe_gather_rows with d_token_map = d_offsets = NULL (then selected = in_div = 1, d_pos_route may be NULL) converts the
- * `tokens` rows in place order: the input rows of a dense expert. */
-#define TSP_GROUPED_TILE 128u
+ *   5. tsp_moe_grouped_down                                    routed[route][channel], FP32 or binary16, scattered by route id
+ * The reference's gather of the routed rows (`nax_moe_gather_bf16_v3`) has no launch here: the gate-up kernel fetches each
+ * token's row by id from the copy of step 1 (TMA row gather). Hidden rows (d_hp) are kept in permuted position order,
+ * tokens*selected rows. Values inside each aligned run of 8 along a row of d_xk / d_hp are stored in the order
+ * 0,2,1,3,4,6,5,7 (the order the dequantised weight tiles use), which only these kernels read. Operands are binary16,
+ * accumulation FP32. The route id of a route is row*selected + slot; its input row is `row` of d_xk.
+ *
+ * Both GEMMs take the layer's dense shared expert in the same launch when shared_* is non-NULL (same shape, encoding and
+ * layout as a routed expert): its tasks cover every one of `tokens` rows in row order and follow the routed ones, as
+ * `encode_moe_mm_many` runs the shared expert's dense projections right after the routed ones (moe_mm_many.cpp:189-214).
+ * d_s_hp: the shared expert's binary16 hidden rows [tokens x hidden]; d_shared_out: FP32 [tokens x channels]. */
+#define TSP_GROUPED_TILE 256u
 int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* d_offsets, void* stream);
-int tsp_moe_gather_rows(const float* d_x, uint64_t x_stride_bytes, uint32_t in_div, const uint32_t* d_token_map,
-                        const uint32_t* d_offsets, uint32_t experts, uint32_t tokens, uint32_t selected, uint32_t cols,
-                        void* d_xp, uint64_t xp_stride_bytes, uint32_t* d_pos_route, uint32_t* d_error, void* stream);
-int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const void* d_xp, uint64_t xp_stride_bytes,
-                            uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
-                            void* d_hp, uint64_t hp_stride_bytes, uint32_t* d_error, void* stream);
-int tsp_moe_grouped_down(const tsp_matrix_set* down, const void* d_hp, uint64_t hp_stride_bytes, uint32_t max_positions,
-                         const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, const uint32_t* d_pos_route,
-                         float* d_routed, uint64_t routed_stride_bytes, uint32_t* d_error, void* stream);
+int tsp_moe_rows_f16k(const void* d_x, uint64_t x_stride_bytes, uint32_t x_dtype, uint32_t rows, uint32_t cols, void* d_xk,
+                      uint64_t xk_stride_bytes, uint32_t* d_error, void* stream);
+int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                            const tsp_matrix_set* shared_up, const void* d_xk, uint64_t xk_stride_bytes, uint32_t tokens, uint32_t selected,
+                            const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, const uint32_t* d_offsets,
+                            void* d_hp, uint64_t hp_stride_bytes, void* d_s_hp, uint64_t s_hp_stride_bytes, uint32_t* d_error, void* stream);
+int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride_bytes,
+                         uint32_t tokens, uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks,
+                         const uint32_t* d_offsets, void* d_routed, uint64_t routed_stride_bytes, uint32_t routed_dtype, const void* d_s_hp,
+                         uint64_t s_hp_stride_bytes, float* d_shared_out, uint64_t shared_out_stride_bytes, uint32_t* d_error, void* stream);
 
-/* The two grouped GEMMs with the layer's dense shared expert in the same launch: its token tiles (every one of `tokens`
- * rows in row order; position = token = route id) follow the routed tiles, as `encode_moe_mm_many` runs the shared
- * expert's dense projections right after the routed ones (moe_mm_many.cpp:189-214). The shared matrix sets must have the
- * routed experts' shape, encoding and layout. d_s_xp: binary16 rows [tokens x channels] in the K order of
- * tsp_moe_gather_rows (call it with NULL tables); d_s_hp: binary16 rows [tokens x hidden]; d_shared_out: FP32 [tokens x channels]. */
-int tsp_moe_grouped_gate_up_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
-                                   const tsp_matrix_set* shared_up, const void* d_xp, uint64_t xp_stride_bytes, uint32_t max_positions,
-                                   const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, void* d_hp,
-                                   uint64_t hp_stride_bytes, const void* d_s_xp, uint64_t s_xp_stride_bytes, uint32_t tokens, void* d_s_hp,
-                                   uint64_t s_hp_stride_bytes, uint32_t* d_error, void* stream);
-int tsp_moe_grouped_down_shared(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride_bytes,
-                                uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
-                                const uint32_t* d_pos_route, float* d_routed, uint64_t routed_stride_bytes, const void* d_s_hp,
-                                uint64_t s_hp_stride_bytes, uint32_t tokens, float* d_shared_out, uint64_t shared_out_stride_bytes,
-                                uint32_t* d_error, void* stream);
+/* Test hook: the binary16 values the grouped kernels stage for one Q4_K planar expert, [rows x cols] in natural K order.
+ * Per weight this is RN16((q - 8) * RN16(d*sc) + RN16(8*d*sc - dmin*mn)), three roundings instead of the one rounding of
+ * the exact value the reference's tensor-op path stages (planar_moe_v3.metal:165); the tests bound the deviation. */
+int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, void* stream);
 
-/* One whole MoE FFN sub-layer at prefill size: route -> permute (tiles of TSP_GROUPED_TILE) -> offsets -> gather ->
+/* One whole MoE FFN sub-layer at prefill size: K-ordered rows -> route -> permute (tasks of TSP_GROUPED_TILE) -> offsets ->
  * grouped gate-up + SwiGLU -> grouped down (the dense shared expert rides in both launches) -> gated mixture.
  * Replaces `encode_moe_mm_many` after its router projection (moe_mm_many.cpp:126-220) on the `planar_nax_grouped_moe`
- * path (graph.mm:9293-9420). Weights: Q4_K Pack v3 planar, hidden and channels multiples of 256; the shared expert in the
- * same form. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
+ * path (graph.mm:9293-9420). Weights: Q4_K Pack v3 planar, hidden a multiple of 64 and channels of 256; the shared expert
+ * in the same form. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
  * Caller-owned scratch, all device memory, nothing has to start at zero:
  *   base: as for the decode layer, except d_tasks sized tsp_moe_tasks_words(capacity, experts, selected, TSP_GROUPED_TILE);
- *         d_hidden and d_shared_hidden are not used and may be NULL;
- *   d_xp / d_hp: binary16 rows in permuted position order, [capacity*selected x channels] / [capacity*selected x hidden];
- *   d_offsets [experts + 1], d_pos_route [capacity*selected];
- *   d_s_xp / d_s_hp: the shared expert's binary16 input and hidden rows in row order, [capacity x channels] / [capacity x hidden]. */
+ *         d_routed is used as binary16 rows [capacity*selected x channels]; d_hidden, d_shared_hidden and d_x32 are not
+ *         used and may be NULL;
+ *   d_xk: binary16 copy of the input rows in tile K order, [capacity x channels];
+ *   d_hp: binary16 hidden rows in permuted position order, [capacity*selected x hidden];
+ *   d_offsets [experts + 1]; d_s_hp: the shared expert's binary16 hidden rows, [capacity x hidden]. */
 typedef struct tsp_moe_prefill_scratch {
     tsp_moe_scratch base;
-    void* d_xp;
+    void* d_xk;
     void* d_hp;
     uint32_t* d_offsets;
-    uint32_t* d_pos_route;
-    void* d_s_xp;
     void* d_s_hp;
 } tsp_moe_prefill_scratch;
 int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratch* s, const void* d_x, uint64_t x_stride_bytes,

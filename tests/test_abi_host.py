@@ -28,6 +28,20 @@ def test_library_exports_every_declared_symbol():
         assert name in capi.SIGNATURES, f"{name} has no ctypes signature"
 
 
+def test_prefill_entries_refuse_bad_arguments():
+    lib = capi.lib()
+    buf = (C.c_uint8 * 64)()
+    p = C.addressof(buf) & ~15
+    g = capi.MatrixSet(p + 16, None, 0, 1, 1, 64, 256, 8, 1)      # Q8_0: the tensor-core path takes Q4_K planar only
+    assert lib.tsp_moe_staged_f16(C.byref(g), 0, p, None) == capi.E_TYPE
+    assert lib.tsp_moe_rows_f16k(p, 8, 0, 1, 12, p, 32, p, None) == capi.E_ARG                      # columns not a multiple of 8
+    assert lib.tsp_moe_rows_f16k(p, 64, 2, 1, 16, p, 32, p, None) == capi.E_ARG                     # unknown dtype
+    q = capi.MatrixSet(p + 16, None, 0, 1, 1, 64, 256, 12, 1)
+    assert lib.tsp_moe_grouped_gate_up(C.byref(q), C.byref(q), C.byref(q), None, p, 512, 1, 1, p, p, p, p, p, 128, None, 0, p, None) == capi.E_ARG
+    assert "go together" in capi.last_error()
+    assert lib.tsp_moe_grouped_down(C.byref(q), None, p, 512, 1, 1, p, p, p, p, p, 128, 3, None, 0, None, 0, p, None) == capi.E_ARG   # row dtype 3
+
+
 def test_expert_byte_constants():
     lib = capi.lib()
     assert lib.tsp_expert_bytes(12, 0, 1024, 2048) == 1179648
@@ -57,7 +71,7 @@ def test_contract_violations_are_refused_before_any_launch():
     u = capi.MatrixSet(p + 16, None, 0, 1, 1, 32, 256, 12, 0)
     assert lib.tsp_moe_gate_up_swiglu(C.byref(g), C.byref(u), p, 1024, 1, 1, None, None, None, p + 4096, 256, 0, p, None) == capi.E_ARG
     with pytest.raises(capi.TspError):
-        capi.call("tsp_moe_combine", None, 0, None, None, 0, None, None, 0, None, 1, 8, 2, None, 0, None, 0, None, None)
+        capi.call("tsp_moe_combine", None, 0, 0, None, None, 0, None, None, 0, 0, None, 1, 8, 2, None, 0, None, 0, None, None)
 
 
 @pytest.mark.parametrize("type_", [8, 12])

@@ -17,7 +17,7 @@ def rel_l2(a, b):
     return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
 
 
-@pytest.mark.parametrize("T,E,K,skew", [(3, 4, 2, False), (40, 4, 2, False), (200, 8, 3, True), (700, 8, 2, True)])
+@pytest.mark.parametrize("T,E,K,skew", [(3, 4, 2, False), (40, 4, 2, False), (200, 8, 3, True), (700, 8, 2, True), (1300, 4, 1, True)])
 def test_prefill_layer_against_oracle(oracle, T, E, K, skew):
     Cn, H = 256, 256
     host = L.synth_host_layer(5, Cn, H, E, K, expert_type=formats.Q4_K)
@@ -35,8 +35,32 @@ def test_prefill_layer_against_oracle(oracle, T, E, K, skew):
     want, st = oracle.moe_layer(host.oracle_dict(), x16[sample].astype(np.float32), logits[sample], threads=4, stages=True)
     ids = ps.base.ids.cpu().numpy().view(np.uint32)[:T * K].reshape(T, K)
     assert np.array_equal(ids[sample], st["indices"])
-    routed = ps.base.routed.cpu().numpy()[:T * K * Cn].reshape(T, K, Cn)
+    routed = ps.routed_rows(T).reshape(T, K, Cn)
     assert rel_l2(routed[sample], st["routed"]) <= 2e-3
-    shared = ps.base.shared_out.cpu().numpy()[:T * Cn].reshape(T, Cn)
+    shared = ps.shared_out_rows(T)
     assert rel_l2(shared[sample], st["shared_out"]) <= 2e-3
     assert rel_l2(out.cpu().numpy()[sample], want) <= 2e-3
+
+
+def test_staged_weight_values_against_rounded_reference(oracle):
+    """The binary16 weight values the tensor-core kernels multiply, against RN16 of the reference's dequantised value.
+    The kernels stage RN16((q - 8) * RN16(d*sc) + RN16(8*d*sc - dmin*mn)): three roundings of small quantities instead of one
+    rounding of the exact value. Bound checked here: relative L2 deviation from the exact values <= 4e-4 (one rounding alone
+    gives about 2.1e-4), no value further than 2^-10 of its group's largest magnitude from the once-rounded value."""
+    rows, cols = 128, 2048
+    w = formats.quantize_q4_k(synth.normal(17, (rows, cols), 0.02)).reshape(-1)
+    planar = formats.pack_planar(formats.Q4_K, w, rows, cols)
+    t = torch.from_numpy(planar).cuda()
+    ms = L.matrix_set(t, formats.Q4_K, formats.PLANAR, rows, cols, 1)
+    out = torch.zeros((rows, cols), dtype=torch.float16, device="cuda")
+    capi.call("tsp_moe_staged_f16", C.byref(ms), 0, out.data_ptr(), L.stream_ptr())
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().astype(np.float64)
+    exact = oracle.dequantize(formats.Q4_K, w, rows * cols).reshape(rows, cols).astype(np.float64)
+    once = exact.astype(np.float16).astype(np.float64)
+    rel = np.linalg.norm(got - exact) / np.linalg.norm(exact)
+    rel_once = np.linalg.norm(once - exact) / np.linalg.norm(exact)
+    group_max = np.abs(exact).reshape(rows, cols // 32, 32).max(axis=2, keepdims=True)
+    dev = (np.abs(got - once).reshape(rows, cols // 32, 32) / np.maximum(group_max, 1e-30)).max()
+    print(f"staged weights: rel-L2 vs exact {rel:.3e} (one rounding: {rel_once:.3e}), worst deviation from RN16 {dev:.3e} of the group maximum")
+    assert rel <= 4e-4 and dev <= 2.0 ** -10

@@ -41,8 +41,7 @@ class MoeScratch(C.Structure):
 
 
 class MoePrefillScratch(C.Structure):
-    _fields_ = [("base", MoeScratch), ("d_xp", C.c_void_p), ("d_hp", C.c_void_p), ("d_offsets", C.c_void_p), ("d_pos_route", C.c_void_p),
-                ("d_s_xp", C.c_void_p), ("d_s_hp", C.c_void_p)]
+    _fields_ = [("base", MoeScratch), ("d_xk", C.c_void_p), ("d_hp", C.c_void_p), ("d_offsets", C.c_void_p), ("d_s_hp", C.c_void_p)]
 
 
 class MoeWeights(C.Structure):
@@ -68,7 +67,7 @@ SIGNATURES = {
     "tsp_moe_project": (_i, [_MS, _vp, _u64, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _i, _vp, _vp]),
     "tsp_moe_gate_up_swiglu_shared": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _i, _vp, _vp]),
     "tsp_moe_project_shared": (_i, [_MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
-    "tsp_moe_combine": (_i, [_vp, _u64, _vp, _vp, _u64, _vp, _vp, _u64, _vp, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp, _vp]),
+    "tsp_moe_combine": (_i, [_vp, _u64, _u32, _vp, _vp, _u64, _vp, _vp, _u64, _u32, _vp, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp, _vp]),
     "tsp_synth_weights": (_i, [_u32, _u64, _u64, _u64, C.c_float, _vp, _vp]),
     "tsp_pack_planar": (_i, [_u32, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),
     "tsp_gemv_f32": (_i, [_vp, _u32, _u32, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
@@ -78,11 +77,10 @@ SIGNATURES = {
     "tsp_moe_layer_prefill": (_i, [C.POINTER(MoeWeights), C.POINTER(MoePrefillScratch), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32,
                                    _u32, _u32, _u32, _i, _vp, _u64, _u32, _vp, _vp]),
     "tsp_moe_route_offsets": (_i, [_vp, _u32, _vp, _vp]),
-    "tsp_moe_gather_rows": (_i, [_vp, _u64, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp, _vp, _vp]),
-    "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
-    "tsp_moe_grouped_down": (_i, [_MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
-    "tsp_moe_grouped_gate_up_shared": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
-    "tsp_moe_grouped_down_shared": (_i, [_MS, _MS, _vp, _u64, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
+    "tsp_moe_rows_f16k": (_i, [_vp, _u64, _u32, _u32, _u32, _vp, _u64, _vp, _vp]),
+    "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
+    "tsp_moe_grouped_down": (_i, [_MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _vp, _u64, _vp, _u64, _vp, _vp]),
+    "tsp_moe_staged_f16": (_i, [_MS, _u32, _vp, _vp]),
     "tsp_moe_layer_decode_static_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
     "tsp_moe_layer_decode_static": (_i, [C.POINTER(MoeWeights), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u32, _i,
                                          _vp, _u64, _u32, _vp, _vp]),

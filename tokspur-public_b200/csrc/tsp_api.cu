@@ -39,18 +39,20 @@ int sm_count() {
 // launchers implemented in the kernel files
 int launch_route(const float*, uint64_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, float*, uint32_t*, cudaStream_t);
 int launch_permute(const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, uint32_t*, uint32_t*, uint32_t*, cudaStream_t);
-int launch_combine(const float*, uint64_t, const float*, const float*, uint64_t, const float*, const float*, uint64_t, float*,
+int launch_combine(const void*, uint64_t, uint32_t, const float*, const float*, uint64_t, const float*, const void*, uint64_t, uint32_t, float*,
                    uint32_t, uint32_t, uint32_t, float*, uint64_t, void*, uint64_t, uint32_t*, cudaStream_t);
+int launch_decode_prologue(const float*, uint64_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t, uint32_t*, float*, uint32_t*, uint32_t*,
+                           uint32_t*, const void*, uint64_t, float*, uint64_t, uint32_t, uint32_t*, cudaStream_t);
 int launch_f16_to_f32(const void*, uint64_t, float*, uint64_t, uint32_t, uint32_t, cudaStream_t);
 int launch_dequant(uint32_t, uint32_t, const uint8_t*, uint64_t, float*, uint32_t*, cudaStream_t);
 int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*, uint64_t, uint32_t, uint32_t,
                 const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t, const GemvShared* = nullptr);
 
 int launch_route_offsets(const uint32_t*, uint32_t, uint32_t*, cudaStream_t);
-int launch_gather_rows(const float*, uint64_t, uint32_t, const uint32_t*, const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, void*, uint64_t,
-                       uint32_t*, uint32_t*, cudaStream_t);
-int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, const uint32_t*, const uint32_t*,
-                   const uint32_t*, const uint32_t*, void*, uint64_t, uint32_t*, cudaStream_t, const GroupedShared* = nullptr);
+int launch_rows_f16k(const void*, uint64_t, uint32_t, uint32_t, uint32_t, void*, uint64_t, uint32_t*, cudaStream_t);
+int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, uint32_t, uint32_t, const uint32_t*,
+                   const uint32_t*, const uint32_t*, const uint32_t*, void*, uint64_t, uint32_t, uint32_t*, cudaStream_t, const GroupedShared* = nullptr);
+int launch_staged_f16(const uint8_t*, uint32_t, uint32_t, void*, cudaStream_t);
 int launch_gemv_f32(const float*, uint32_t, uint32_t, const float*, uint64_t, uint32_t, float*, uint64_t, uint32_t*, cudaStream_t);
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
@@ -229,20 +231,22 @@ int tsp_moe_project(const tsp_matrix_set* w, const float* d_in, uint64_t in_stri
                        d_out, out_stride, f16_exact, nc, d_error, static_cast<cudaStream_t>(stream));
 }
 
-int tsp_moe_combine(const float* d_routed, uint64_t routed_stride, const float* d_weights, const float* d_shared,
-                    uint64_t shared_stride, const float* d_shared_router, const float* d_x, uint64_t x_stride,
+int tsp_moe_combine(const void* d_routed, uint64_t routed_stride, uint32_t routed_dtype, const float* d_weights, const float* d_shared,
+                    uint64_t shared_stride, const float* d_shared_router, const void* d_x, uint64_t x_stride, uint32_t x_dtype,
                     float* d_shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected, float* d_out,
                     uint64_t out_stride, void* d_out_f16, uint64_t out_f16_stride, uint32_t* d_error, void* stream) {
     TSP_REQUIRE(d_routed && d_weights && d_shared && (d_out || d_out_f16), "combine: null buffer");
     TSP_REQUIRE(tokens >= 1 && channels >= 1 && channels <= 65536 && selected >= 1 && selected <= 64, "combine: mixture shape mismatch");
-    TSP_REQUIRE(routed_stride >= channels * 4ull && shared_stride >= channels * 4ull && routed_stride % 4 == 0 &&
+    TSP_REQUIRE(routed_dtype <= 1 && x_dtype <= 1, "combine: row dtype must be 0 (FP32) or 1 (binary16)");
+    const uint64_t relem = routed_dtype ? 2 : 4, xelem = x_dtype ? 2 : 4;
+    TSP_REQUIRE(routed_stride >= channels * relem && shared_stride >= channels * 4ull && routed_stride % relem == 0 &&
                 shared_stride % 4 == 0, "combine: row stride too small");
     if (d_out) TSP_REQUIRE(out_stride >= channels * 4ull && out_stride % 4 == 0, "combine: output row stride too small");
-    if (d_shared_router) TSP_REQUIRE(d_x && x_stride >= channels * 4ull && x_stride % 4 == 0, "combine: the shared router needs the input rows");
+    if (d_shared_router) TSP_REQUIRE(d_x && x_stride >= channels * xelem && x_stride % xelem == 0, "combine: the shared router needs the input rows");
     if (d_out_f16) TSP_REQUIRE(out_f16_stride >= channels * 2ull && out_f16_stride % 2 == 0, "combine: binary16 output stride too small");
     if (d_out) TSP_REQUIRE(!overlap(d_out, tokens * out_stride, d_routed, static_cast<uint64_t>(tokens) * selected * routed_stride) &&
                            !overlap(d_out, tokens * out_stride, d_shared, tokens * shared_stride), "combine: output overlaps an input");
-    return launch_combine(d_routed, routed_stride, d_weights, d_shared, shared_stride, d_shared_router, d_x, x_stride,
+    return launch_combine(d_routed, routed_stride, routed_dtype, d_weights, d_shared, shared_stride, d_shared_router, d_x, x_stride, x_dtype,
                           d_shared_logit, tokens, channels, selected, d_out, out_stride, d_out_f16, out_f16_stride, d_error,
                           static_cast<cudaStream_t>(stream));
 }
@@ -349,16 +353,22 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
                 s->d_token_map && s->d_counts && s->d_tasks, "layer: incomplete scratch");
     TSP_REQUIRE(x_dtype == 0 || s->d_x32, "layer: binary16 input needs the d_x32 staging rows");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    TSP_REQUIRE(experts >= 1 && experts <= 4096 && selected >= 1 && selected <= 64 && selected <= experts && mode <= 1, "layer: invalid router shape/mode");
+    TSP_REQUIRE(logits_stride >= static_cast<uint64_t>(experts) * 4 && logits_stride % 4 == 0, "layer: logits stride too small");
     const float* x32 = static_cast<const float*>(d_x);
     uint64_t x32_stride = x_stride;
-    if (x_dtype == 1) {
-        if (int rc = tsp_rows_f16_to_f32(d_x, x_stride, s->d_x32, channels * 4ull, tokens, channels, st)) return rc;
-        x32 = s->d_x32;
-        x32_stride = channels * 4ull;
-    }
+    if (x_dtype == 1) { x32 = s->d_x32; x32_stride = channels * 4ull; }
     const int exact = x_dtype == 1;
-    if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
-    if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GEMV_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
+    // small batches: route, permutation, tile table and the binary16 -> FP32 copy of the rows in ONE launch
+    int fused = launch_decode_prologue(d_logits, logits_stride, tokens, experts, selected, mode, normalize, TSP_GEMV_TILE, s->d_ids, s->d_weights,
+                                       s->d_token_map, s->d_counts, s->d_tasks, x_dtype == 1 ? d_x : nullptr, x_stride, s->d_x32, channels * 4ull,
+                                       channels, d_error, st);
+    if (fused < 0) return fused;
+    if (fused == 1) {
+        if (x_dtype == 1) { if (int rc = tsp_rows_f16_to_f32(d_x, x_stride, s->d_x32, channels * 4ull, tokens, channels, st)) return rc; }
+        if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
+        if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GEMV_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
+    }
     if (int rc = tsp_moe_gate_up_swiglu_shared(&w->gate, &w->up, &w->shared_gate, &w->shared_up, x32, x32_stride, x_dtype == 1 ? d_x : nullptr,
                                                x_dtype == 1 ? x_stride : 0, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks, s->d_hidden,
                                                hidden * 4ull, s->d_shared_hidden, hidden * 4ull, exact, d_error, stream)) return rc;
@@ -366,8 +376,8 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
                                         s->d_token_map, s->d_counts, s->d_tasks, s->d_routed, channels * 4ull, s->d_shared_out, channels * 4ull,
                                         d_error, stream)) return rc;
     // binary16 output rows are written straight from the FP32 mixture; no FP32 copy of the output is kept
-    return tsp_moe_combine(s->d_routed, channels * 4ull, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32,
-                           x32_stride, s->d_shared_logit, tokens, channels, selected,
+    return tsp_moe_combine(s->d_routed, channels * 4ull, 0, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32,
+                           x32_stride, 0, s->d_shared_logit, tokens, channels, selected,
                            out_dtype == 0 ? static_cast<float*>(d_out) : nullptr, out_dtype == 0 ? out_stride : 0,
                            out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
 }
@@ -380,45 +390,15 @@ int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* 
     return launch_route_offsets(d_counts, experts, d_offsets, static_cast<cudaStream_t>(stream));
 }
 
-int tsp_moe_gather_rows(const float* d_x, uint64_t x_stride, uint32_t in_div, const uint32_t* d_token_map, const uint32_t* d_offsets,
-                        uint32_t experts, uint32_t tokens, uint32_t selected, uint32_t cols, void* d_xp, uint64_t xp_stride,
-                        uint32_t* d_pos_route, uint32_t* d_error, void* stream) {
-    TSP_REQUIRE((d_token_map != nullptr) == (d_offsets != nullptr), "gather: token map and offsets go together");
-    TSP_REQUIRE(d_token_map ? d_pos_route != nullptr : (selected == 1 && in_div == 1), "gather: a routed gather needs the position table; a dense one has selected = in_div = 1");
-    TSP_REQUIRE(tokens >= 1 && selected >= 1 && selected <= 64 && in_div >= 1 && cols >= 8 && cols % 8 == 0, "gather: invalid shape");
-    if (int rc = check_rows(d_x, x_stride, cols, 4, "gather input")) return rc;
-    if (int rc = check_rows(d_xp, xp_stride, cols, 2, "gather output")) return rc;
-    return launch_gather_rows(d_x, x_stride, in_div, d_token_map, d_offsets, experts, tokens, tokens * selected, cols, d_xp, xp_stride,
-                              d_pos_route, d_error, static_cast<cudaStream_t>(stream));
+int tsp_moe_rows_f16k(const void* d_x, uint64_t x_stride, uint32_t x_dtype, uint32_t rows, uint32_t cols, void* d_xk, uint64_t xk_stride,
+                      uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(x_dtype <= 1 && rows >= 1 && cols >= 8 && cols % 8 == 0, "K-ordered rows: invalid shape or dtype");
+    if (int rc = check_rows(d_x, x_stride, cols, x_dtype ? 2 : 4, "K-ordered rows input")) return rc;
+    if (int rc = check_rows(d_xk, xk_stride, cols, 2, "K-ordered rows output")) return rc;
+    TSP_REQUIRE(!overlap(d_x, rows * x_stride, d_xk, rows * xk_stride), "K-ordered rows: input and output overlap");
+    return launch_rows_f16k(d_x, x_stride, x_dtype, rows, cols, d_xk, xk_stride, d_error, static_cast<cudaStream_t>(stream));
 }
 
-int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const void* d_xp, uint64_t xp_stride,
-                            uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
-                            void* d_hp, uint64_t hp_stride, uint32_t* d_error, void* stream) {
-    if (int rc = check_matrix(gate, "gate")) return rc;
-    if (int rc = check_matrix(up, "up")) return rc;
-    TSP_REQUIRE(gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
-                gate->experts == up->experts && gate->expert_stride == up->expert_stride && gate->split == up->split,
-                "gate/up matrix sets must share shape, encoding, layout and addressing");
-    TSP_REQUIRE(d_tasks && d_counts && d_offsets && max_positions >= 1, "grouped gate-up: null table");
-    if (int rc = check_rows(d_xp, xp_stride, gate->cols, 2, "grouped gate-up input")) return rc;
-    if (int rc = check_rows(d_hp, hp_stride, gate->rows, 2, "grouped gate-up output")) return rc;
-    return launch_grouped(gate, up, true, d_xp, xp_stride, max_positions, d_tasks, d_counts, d_offsets, nullptr, d_hp, hp_stride, d_error,
-                          static_cast<cudaStream_t>(stream));
-}
-
-int tsp_moe_grouped_down(const tsp_matrix_set* down, const void* d_hp, uint64_t hp_stride, uint32_t max_positions,
-                         const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, const uint32_t* d_pos_route,
-                         float* d_routed, uint64_t routed_stride, uint32_t* d_error, void* stream) {
-    if (int rc = check_matrix(down, "down")) return rc;
-    TSP_REQUIRE(d_tasks && d_counts && d_offsets && d_pos_route && max_positions >= 1, "grouped down: null table");
-    if (int rc = check_rows(d_hp, hp_stride, down->cols, 2, "grouped down input")) return rc;
-    if (int rc = check_rows(d_routed, routed_stride, down->rows, 4, "grouped down output")) return rc;
-    return launch_grouped(down, nullptr, false, d_hp, hp_stride, max_positions, d_tasks, d_counts, d_offsets, d_pos_route, d_routed,
-                          routed_stride, d_error, static_cast<cudaStream_t>(stream));
-}
-
-// The grouped GEMMs with the layer's dense shared expert in the same launch (its token tiles follow the routed tiles).
 static int check_shared_set(const tsp_matrix_set* s, const tsp_matrix_set* like, const char* name) {
     if (int rc = check_matrix(s, name)) return rc;
     TSP_REQUIRE(s->experts == 1 && s->type == like->type && s->layout == like->layout && s->rows == like->rows && s->cols == like->cols,
@@ -426,42 +406,60 @@ static int check_shared_set(const tsp_matrix_set* s, const tsp_matrix_set* like,
     return TSP_OK;
 }
 
-int tsp_moe_grouped_gate_up_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
-                                   const tsp_matrix_set* shared_up, const void* d_xp, uint64_t xp_stride, uint32_t max_positions,
-                                   const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets, void* d_hp, uint64_t hp_stride,
-                                   const void* d_s_xp, uint64_t s_xp_stride, uint32_t tokens, void* d_s_hp, uint64_t s_hp_stride,
-                                   uint32_t* d_error, void* stream) {
+int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate, const tsp_matrix_set* shared_up,
+                            const void* d_xk, uint64_t xk_stride, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                            const uint32_t* d_counts, const uint32_t* d_tasks, const uint32_t* d_offsets, void* d_hp, uint64_t hp_stride,
+                            void* d_s_hp, uint64_t s_hp_stride, uint32_t* d_error, void* stream) {
     if (int rc = check_matrix(gate, "gate")) return rc;
     if (int rc = check_matrix(up, "up")) return rc;
     TSP_REQUIRE(gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
                 gate->experts == up->experts && gate->expert_stride == up->expert_stride && gate->split == up->split,
                 "gate/up matrix sets must share shape, encoding, layout and addressing");
+    TSP_REQUIRE(d_token_map && d_tasks && d_counts && d_offsets && tokens >= 1 && selected >= 1 && selected <= 64, "grouped gate-up: null table or empty batch");
+    TSP_REQUIRE((shared_gate != nullptr) == (shared_up != nullptr), "grouped gate-up: shared gate and up go together");
+    if (int rc = check_rows(d_xk, xk_stride, gate->cols, 2, "grouped gate-up input")) return rc;
+    if (int rc = check_rows(d_hp, hp_stride, gate->rows, 2, "grouped gate-up output")) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!shared_gate)
+        return launch_grouped(gate, up, true, d_xk, xk_stride, tokens, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets, d_hp, hp_stride, 0,
+                              d_error, st);
     if (int rc = check_shared_set(shared_gate, gate, "shared gate")) return rc;
     if (int rc = check_shared_set(shared_up, gate, "shared up")) return rc;
-    TSP_REQUIRE(d_tasks && d_counts && d_offsets && max_positions >= 1 && tokens >= 1, "grouped gate-up: null table");
-    if (int rc = check_rows(d_xp, xp_stride, gate->cols, 2, "grouped gate-up input")) return rc;
-    if (int rc = check_rows(d_hp, hp_stride, gate->rows, 2, "grouped gate-up output")) return rc;
-    if (int rc = check_rows(d_s_xp, s_xp_stride, gate->cols, 2, "shared gate-up input")) return rc;
     if (int rc = check_rows(d_s_hp, s_hp_stride, gate->rows, 2, "shared gate-up output")) return rc;
-    const GroupedShared sh{shared_gate, shared_up, d_s_xp, s_xp_stride, tokens, d_s_hp, s_hp_stride};
-    return launch_grouped(gate, up, true, d_xp, xp_stride, max_positions, d_tasks, d_counts, d_offsets, nullptr, d_hp, hp_stride, d_error,
-                          static_cast<cudaStream_t>(stream), &sh);
+    const GroupedShared sh{shared_gate, shared_up, d_xk, xk_stride, tokens, d_s_hp, s_hp_stride};
+    return launch_grouped(gate, up, true, d_xk, xk_stride, tokens, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets, d_hp, hp_stride, 0,
+                          d_error, st, &sh);
 }
 
-int tsp_moe_grouped_down_shared(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride,
-                                uint32_t max_positions, const uint32_t* d_tasks, const uint32_t* d_counts, const uint32_t* d_offsets,
-                                const uint32_t* d_pos_route, float* d_routed, uint64_t routed_stride, const void* d_s_hp, uint64_t s_hp_stride,
-                                uint32_t tokens, float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
+int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride, uint32_t tokens,
+                         uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, const uint32_t* d_offsets,
+                         void* d_routed, uint64_t routed_stride, uint32_t routed_dtype, const void* d_s_hp, uint64_t s_hp_stride,
+                         float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
     if (int rc = check_matrix(down, "down")) return rc;
-    if (int rc = check_shared_set(shared_down, down, "shared down")) return rc;
-    TSP_REQUIRE(d_tasks && d_counts && d_offsets && d_pos_route && max_positions >= 1 && tokens >= 1, "grouped down: null table");
+    TSP_REQUIRE(d_token_map && d_tasks && d_counts && d_offsets && tokens >= 1 && selected >= 1 && selected <= 64 && routed_dtype <= 1,
+                "grouped down: null table, empty batch or bad row dtype");
+    TSP_REQUIRE(static_cast<uint64_t>(tokens) * selected < (1ull << 31), "grouped down: too many routes");
     if (int rc = check_rows(d_hp, hp_stride, down->cols, 2, "grouped down input")) return rc;
-    if (int rc = check_rows(d_routed, routed_stride, down->rows, 4, "grouped down output")) return rc;
+    if (int rc = check_rows(d_routed, routed_stride, down->rows, routed_dtype ? 2 : 4, "grouped down output")) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!shared_down)
+        return launch_grouped(down, nullptr, false, d_hp, hp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets,
+                              d_routed, routed_stride, routed_dtype, d_error, st);
+    if (int rc = check_shared_set(shared_down, down, "shared down")) return rc;
     if (int rc = check_rows(d_s_hp, s_hp_stride, down->cols, 2, "shared down input")) return rc;
     if (int rc = check_rows(d_shared_out, shared_out_stride, down->rows, 4, "shared down output")) return rc;
     const GroupedShared sh{shared_down, nullptr, d_s_hp, s_hp_stride, tokens, d_shared_out, shared_out_stride};
-    return launch_grouped(down, nullptr, false, d_hp, hp_stride, max_positions, d_tasks, d_counts, d_offsets, d_pos_route, d_routed,
-                          routed_stride, d_error, static_cast<cudaStream_t>(stream), &sh);
+    return launch_grouped(down, nullptr, false, d_hp, hp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets,
+                          d_routed, routed_stride, routed_dtype, d_error, st, &sh);
+}
+
+int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, void* stream) {
+    if (int rc = check_matrix(m, "staged tile")) return rc;
+    if (m->type != TSP_TYPE_Q4_K || m->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "staged tile: only Q4_K Pack v3 planar weights go through the tensor-core kernels");
+    TSP_REQUIRE(expert < m->experts && d_out, "staged tile: expert out of range or null output");
+    const uint8_t* base = static_cast<const uint8_t*>(expert < m->split ? m->base : m->base_hi);
+    const uint32_t local = expert < m->split ? expert : expert - m->split;
+    return launch_staged_f16(base + local * m->expert_stride, m->rows, m->cols, d_out, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -516,33 +514,20 @@ int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratc
                 w->shared_gate.rows == hidden && w->shared_gate.cols == channels && w->shared_gate.experts == 1 &&
                 w->shared_up.experts == 1 && w->shared_down.rows == channels && w->shared_down.cols == hidden &&
                 w->shared_down.experts == 1, "prefill layer: weight shapes do not match the layer shape");
-    TSP_REQUIRE(s->d_ids && s->d_weights && s->d_routed && s->d_shared_out && s->d_token_map && s->d_counts && s->d_tasks && ps->d_xp &&
-                ps->d_hp && ps->d_offsets && ps->d_pos_route && ps->d_s_xp && ps->d_s_hp, "prefill layer: incomplete scratch");
-    TSP_REQUIRE(x_dtype == 0 || s->d_x32, "prefill layer: binary16 input needs the d_x32 staging rows");
+    TSP_REQUIRE(s->d_ids && s->d_weights && s->d_routed && s->d_shared_out && s->d_token_map && s->d_counts && s->d_tasks && ps->d_xk &&
+                ps->d_hp && ps->d_offsets && ps->d_s_hp, "prefill layer: incomplete scratch");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const float* x32 = static_cast<const float*>(d_x);
-    uint64_t x32_stride = x_stride;
-    if (x_dtype == 1) {
-        if (int rc = tsp_rows_f16_to_f32(d_x, x_stride, s->d_x32, channels * 4ull, tokens, channels, st)) return rc;
-        x32 = s->d_x32;
-        x32_stride = channels * 4ull;
-    }
-    const uint32_t routes = tokens * selected;
+    if (int rc = tsp_moe_rows_f16k(d_x, x_stride, x_dtype, tokens, channels, ps->d_xk, channels * 2ull, d_error, st)) return rc;
     if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
     if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GROUPED_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
     if (int rc = tsp_moe_route_offsets(s->d_counts, experts, ps->d_offsets, st)) return rc;
-    if (int rc = tsp_moe_gather_rows(x32, x32_stride, selected, s->d_token_map, ps->d_offsets, experts, tokens, selected, channels, ps->d_xp,
-                                     channels * 2ull, ps->d_pos_route, d_error, st)) return rc;
-    // the dense shared expert rides in the routed launches: its rows need no tables, only the binary16 copy in the K order
-    // the tensor-core tiles use
-    if (int rc = tsp_moe_gather_rows(x32, x32_stride, 1, nullptr, nullptr, 1, tokens, 1, channels, ps->d_s_xp, channels * 2ull, nullptr, d_error, st)) return rc;
-    if (int rc = tsp_moe_grouped_gate_up_shared(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xp, channels * 2ull, routes, s->d_tasks,
-                                                s->d_counts, ps->d_offsets, ps->d_hp, hidden * 2ull, ps->d_s_xp, channels * 2ull, tokens, ps->d_s_hp,
-                                                hidden * 2ull, d_error, st)) return rc;
-    if (int rc = tsp_moe_grouped_down_shared(&w->down, &w->shared_down, ps->d_hp, hidden * 2ull, routes, s->d_tasks, s->d_counts, ps->d_offsets,
-                                             ps->d_pos_route, s->d_routed, channels * 4ull, ps->d_s_hp, hidden * 2ull, tokens, s->d_shared_out,
-                                             channels * 4ull, d_error, st)) return rc;
-    return tsp_moe_combine(s->d_routed, channels * 4ull, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, x32, x32_stride,
+    // the dense shared expert rides in both launches; the route rows are kept as binary16 (half the traffic of the mixture)
+    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xk, channels * 2ull, tokens, selected, s->d_token_map,
+                                         s->d_counts, s->d_tasks, ps->d_offsets, ps->d_hp, hidden * 2ull, ps->d_s_hp, hidden * 2ull, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_down(&w->down, &w->shared_down, ps->d_hp, hidden * 2ull, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
+                                      ps->d_offsets, s->d_routed, channels * 2ull, 1, ps->d_s_hp, hidden * 2ull, s->d_shared_out, channels * 4ull,
+                                      d_error, st)) return rc;
+    return tsp_moe_combine(s->d_routed, channels * 2ull, 1, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, d_x, x_stride, x_dtype,
                            s->d_shared_logit, tokens, channels, selected, out_dtype == 0 ? static_cast<float*>(d_out) : nullptr,
                            out_dtype == 0 ? out_stride : 0, out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
 }

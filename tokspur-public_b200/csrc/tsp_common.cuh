@@ -49,6 +49,26 @@ struct GroupedShared {
     void* out; uint64_t out_stride;
 };
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-DEVICE property of a kernel: what has been set on one device says
+// nothing about the next one. Every launcher keeps one of these per kernel instantiation and asks it before a launch.
+struct SmemAttrCache {
+    static constexpr int kDevices = 64;
+    size_t bytes[kDevices] = {};
+    // true when `smem` exceeds what is known to be configured for `device` (the caller then sets the attribute and calls note())
+    bool needs(int device, size_t smem) const { return device < 0 || device >= kDevices || smem > bytes[device]; }
+    void note(int device, size_t smem) { if (device >= 0 && device < kDevices && smem > bytes[device]) bytes[device] = smem; }
+};
+template <typename Kernel>
+static inline cudaError_t ensure_dynamic_smem(Kernel kernel, SmemAttrCache& cache, size_t smem) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (!cache.needs(dev, smem)) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e == cudaSuccess) cache.note(dev, smem);
+    return e;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------------------------

@@ -514,11 +514,8 @@ static uint32_t pad_row(uint32_t row_bytes) {
 template <uint32_t TYPE, uint32_t LAYOUT, bool GATEUP, int NC, int CW = kConsumerWarps>
 static int launch_one(const GemvParams& p, const GemvPartMaps& map, size_t smem, int grid, cudaStream_t st) {
     auto kernel = gemv_kernel<TYPE, LAYOUT, GATEUP, NC, CW>;
-    static thread_local size_t configured = 0;
-    if (smem > configured) {
-        TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured = smem;
-    }
+    static thread_local SmemAttrCache configured;   // per kernel instantiation, keyed by device
+    TSP_CUDA(ensure_dynamic_smem(kernel, configured, smem));
     TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3((CW + 1) * 32), smem, st, p, map));
     return TSP_OK;
 }

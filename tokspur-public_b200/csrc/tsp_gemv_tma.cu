@@ -596,11 +596,8 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
 template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, int KB, bool SPLIT>
 static int launch3(const Gemv3Maps& maps, const Gemv3Params& p, size_t smem, int grid, cudaStream_t st) {
     auto kernel = gemv3_kernel<LAYOUT, GATEUP, NC, NT, KB, SPLIT>;
-    static thread_local size_t configured = 0;
-    if (smem > configured) {
-        TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured = smem;
-    }
+    static thread_local SmemAttrCache configured;   // per kernel instantiation, keyed by device
+    TSP_CUDA(ensure_dynamic_smem(kernel, configured, smem));
     TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads3), smem, st, maps, p));
     return TSP_OK;
 }

@@ -1,23 +1,34 @@
 // Prefill-size grouped expert GEMMs on the 5th-generation tensor cores (tcgen05) for sm_100a.
 //
-// One launch computes, for every tile of <= 128 routes of one expert, either
-//   gate-up:  H[pos][h]  = silu(W_gate[h] . x[pos]) * (W_up[h] . x[pos])     (two accumulators sharing the activation tile)
+// One launch computes, for every task of <= 256 routes of one expert (two sub-tiles of <= 128 token columns), either
+//   gate-up:  H[pos][h]   = silu(W_gate[h] . x[token]) * (W_up[h] . x[token])
 //   down:     Y[route][c] = W_down[c] . H[pos]
-// with the weights as the M operand (128 weight rows per CTA tile fill the MMA's M extent whatever the number of
-// tokens), the tokens as the N operand (32, 64 or 128 columns) and K walked in chunks of 64.
+// with the weights as the M operand (128 weight rows per item fill the MMA's M extent whatever the number of tokens), the
+// tokens as the N operand (32, 64 or 128 columns per sub-tile) and K walked in chunks of 64.
+//
+//   * A dequantised weight chunk is used for BOTH sub-tiles of a task before it is released: an expert with many routes
+//     pays the dequantisation once per 256 routes. Each sub-tile has its own accumulator (128 columns of tensor memory);
+//     two such pairs are double-buffered (512 columns), so the epilogue of an item runs under the MMAs of the next.
+//   * Gate-up items hold 64 hidden units as 128 A rows: inside every group of 32 rows (one tensor-memory lane quarter)
+//     rows 0..15 are gate rows and rows 16..31 the up rows of the same 16 units, so SwiGLU is a lane exchange inside one
+//     warp and one accumulator serves both matrices (a 16 KB A stage per chunk, four stages).
+//   * Gate-up activation tiles are fetched by token id straight from the K-ordered binary16 copy of the layer input
+//     (`cp.async.bulk.tensor ... tile::gather4`: four rows per instruction, one instruction per lane of the producer warp):
+//     no routed copy of the input rows is ever written. Down activation tiles are plain tile copies of the hidden rows.
 //
 // Roles inside a CTA (one persistent CTA per SM):
-//   warp 0      TMA producer of the quantised planes: Pack v3 planar code boxes + 6-bit factor boxes of one super-block
-//               (256 columns of K) per quant stage, gate and up in one copy each; the (d, dmin) pairs once per item.
+//   warp 0      TMA producer of the quantised planes: Pack v3 planar code lines + 6-bit factor bytes of one super-block
+//               (256 columns of K) per quant stage; the (d, dmin) pairs once per item.
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers.
-//   warps 2..9  dequantise (two warps per SM sub-partition, a thread per half row of a K chunk): read 4-bit codes +
-//               6-bit factors from the quant stage, write binary16 weights in the K-major 128-byte-swizzled operand layout.
-//   warp 10     TMA producer of the activation tiles (tokens x 64 binary16, 128-byte swizzled) of every K chunk.
-//   warps 11..18 epilogue (two per tensor-memory lane quarter): tcgen05.ld of their 32 accumulator lanes, SwiGLU / store. The accumulators are double-buffered
-//               in tensor memory (2 x 256 columns), so the epilogue of an item runs under the MMAs of the next one.
+//   warps 2..9  dequantise: a thread owns one weight row and every other K chunk (threads 0..127 the even chunks, 128..255
+//               the odd ones): 32 code bytes -> 64 binary16 weights written as one 128-byte row of the K-major,
+//               128-byte-swizzled operand tile. Per group of 32 weights the value staged is
+//               RN16((q - 8) * RN16(d*sc) + RN16(8*d*sc - dmin*mn)): the centred code keeps the products small, so the three
+//               roundings cost about 1.5x the error of rounding the exact value once (measured by the tile hook below).
+//   warp 10     activation producer.
+//   warps 11..18 epilogue (two per tensor-memory lane quarter): tcgen05.ld of their 32 accumulator lanes, SwiGLU / store.
 // Accumulation is FP32 in tensor memory. Operands are binary16 (kind::f16, f16 inputs): the activations of this path are
-// binary16-exact, and Q4_K values keep 11 significant bits instead of bf16's 8, which keeps the two chained GEMMs well
-// inside the 2e-3 relative-L2 bar that bf16 operands would only just meet.
+// binary16-exact, and Q4_K values keep 11 significant bits instead of bf16's 8.
 // Every mbarrier wait is bounded; a timeout sets TSP_ERR_TIMEOUT, and every path still frees the tensor memory.
 #include <cuda.h>
 
@@ -53,13 +64,6 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// 32 lanes x 16 consecutive columns of 32-bit accumulators -> 16 registers per thread
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-}
 // 32 lanes x 32 consecutive columns -> 32 registers per thread
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -75,9 +79,20 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
+// four rows of a 2-D tensor, named one by one, land as four consecutive box rows in shared memory (box = {bytes, 1})
+__device__ __forceinline__ void tma_gather4(void* smem_dst, const CUtensorMap* map, int c0, int r0, int r1, int r2, int r3, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_4d_g(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_5d_g(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
                  : "memory");
 }
 
@@ -93,37 +108,40 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-constexpr uint32_t kDqWarps = 8;           // dequantise warps: two per SM sub-partition, each thread half a row of a K chunk
-// epilogue warps: two per tensor-memory lane quarter, taking the 32-column batches in turn (with one per quarter the down
-// GEMM, whose items are only 8 K chunks long, was bound by its epilogue: 0.39 ms against 0.26 ms)
-__host__ __device__ constexpr uint32_t ep_warps(bool) { return 8u; }
-__host__ __device__ constexpr uint32_t g_warps(bool gateup) { return 3 + kDqWarps + ep_warps(gateup); }   // weight producer, MMA, dequant warps, activation producer, epilogue warps
+constexpr uint32_t kDqWarps = 8;           // dequantise warps: 256 threads = 128 weight rows x {even, odd} K chunks
+constexpr uint32_t kEpWarps = 8;           // epilogue warps: two per tensor-memory lane quarter, taking the 32-column batches in turn
+constexpr uint32_t kGWarps = 3 + kDqWarps + kEpWarps;   // weight producer, MMA, dequant warps, activation producer, epilogue warps
 constexpr uint32_t kMaxBStages = 8;
-constexpr uint32_t kTileRoutes = 128;      // routes per tile (N extent at most)
-constexpr uint32_t kRowsM = 128;           // weight rows per CTA tile (M)
-constexpr uint32_t kChunkK = 64;           // K per pipeline step: 64 binary16 = one 128-byte swizzled row
+constexpr uint32_t kTaskRoutes = TSP_GROUPED_TILE;      // routes per task (two sub-tiles)
+constexpr uint32_t kSub = 128;             // token columns per sub-tile (N extent at most)
+constexpr uint32_t kRowsM = 128;           // A rows per item (M)
+constexpr uint32_t kAStages = 4;           // dequantised weight chunks in flight: the four K chunks of a super-block
+static_assert(kTaskRoutes == 2 * kSub, "a task is two sub-tiles");
 
-// Tensor maps of one launch: codes (low ids, high ids; second matrix low, high), factors (same four), (d, dmin) pairs (same four),
-// activation tiles of 32 / 64 / 128 token rows.
-// Indices 4, 5 of q / f / d and 3..5 of x belong to the optional dense shared expert of the layer (sh_tiles != 0).
+// Tensor maps of one launch: codes / factor bytes / (d, dmin) pairs with index 0 matrix A low ids, 1 A high ids, 2 B low ids,
+// 3 B high ids, 4 shared-expert A, 5 shared-expert B. Activations: gate-up uses x[0] only (row-gather map over the K-ordered
+// input rows, routed and shared tiles alike); down uses x[0..2] (tiles of 32 / 64 / 128 hidden rows) and x[3..5] (the same
+// over the shared expert's hidden rows).
 struct alignas(64) GroupedMaps { CUtensorMap q[6], f[6], d[6], x[6]; };
 
 struct GroupedParams {
     uint32_t split, experts;
-    uint32_t rows, cols, nblk;     // rows of ONE matrix, K, super-blocks per row
-    uint32_t row_blocks;           // rows / 128
-    uint32_t merged;               // both matrices of an expert arrive with one copy per plane
-    // optional dense shared expert processed by the same launch after the routed tiles: every one of sh_tokens rows, in
-    // row order (position = token = route id), its own activation rows and output rows
-    uint32_t sh_tiles, sh_tokens, sh_merged;
+    uint32_t nblk;                 // super-blocks per weight row (K / 256)
+    uint32_t row_blocks;           // items per task: hidden / 64 (gate-up) or rows / 128 (down)
+    uint32_t merged, sh_merged;    // both matrices of an expert arrive with one copy per plane (routed experts; shared expert)
+    // optional dense shared expert processed by the same launch after the routed tasks: every one of sh_tokens rows, in
+    // row order (position = token = route id)
+    uint32_t sh_tasks, sh_tokens;
     void* sh_out; uint64_t sh_out_stride_bytes;
     // routes
-    const uint32_t* tasks;         // {tiles, routes, (expert, start)...} with tiles of kTileRoutes
+    uint32_t tokens, selected;     // rows of token_map per expert; routes per token row (route id = row * selected + slot)
+    const uint32_t* tasks;         // {tasks, routes, (expert, start)...} with tasks of kTaskRoutes routes
     const uint32_t* counts;
-    const uint32_t* offsets;       // first permuted position of each expert
-    const uint32_t* pos_route;     // route id (token*selected + slot) of each permuted position
+    const uint32_t* offsets;       // first permuted position of each expert (hidden rows are kept in this order)
+    const uint32_t* token_map;     // [expert][tokens] route ids in ascending order
     // output
     void* out; uint64_t out_stride_bytes;
+    uint32_t out_f16;              // down: binary16 instead of FP32 route rows
     uint32_t* error;
     // shared-memory plan
     uint32_t off_q, q_stage_bytes, off_d, d_stage_bytes, dm_mat_bytes, off_a, off_b, nb_stages;
@@ -132,73 +150,112 @@ struct GroupedParams {
 // bounded wait with a short limit: a stalled pipeline ends in tens of milliseconds, never hangs
 __device__ __forceinline__ bool gwait(uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity, 1u << 21); }
 
-struct GTile { uint32_t expert, start, count, row0, ncols; };
+struct GTask { uint32_t expert, start, count, row0; };
 
-// A tile of the shared expert carries the expert id p.experts (one past the routed ids).
-__device__ __forceinline__ GTile gtile(const GroupedParams& p, uint32_t tile) {
-    GTile t;
+// A task of the shared expert carries the expert id p.experts (one past the routed ids).
+__device__ __forceinline__ GTask gtask(const GroupedParams& p, uint32_t task) {
+    GTask t;
     const uint32_t routed = p.tasks[0];
-    if (tile >= routed) {
+    if (task >= routed) {
         t.expert = p.experts;
-        t.start = (tile - routed) * kTileRoutes;
-        t.count = t.start < p.sh_tokens ? min(p.sh_tokens - t.start, kTileRoutes) : 0u;
+        t.start = (task - routed) * kTaskRoutes;
+        t.count = t.start < p.sh_tokens ? min(p.sh_tokens - t.start, kTaskRoutes) : 0u;
         t.row0 = t.start;
-        t.ncols = t.count <= 32 ? 32u : (t.count <= 64 ? 64u : 128u);
         return t;
     }
-    t.expert = p.tasks[2 + 2 * tile];
-    t.start = p.tasks[3 + 2 * tile];
-    if (t.expert >= p.experts) { t.expert = 0; t.start = 0; t.count = 0; t.row0 = 0; t.ncols = 32; return t; }
+    t.expert = p.tasks[2 + 2 * task];
+    t.start = p.tasks[3 + 2 * task];
+    if (t.expert >= p.experts) { t.expert = 0; t.start = 0; t.count = 0; t.row0 = 0; return t; }
     const uint32_t c = p.counts[t.expert];
-    t.count = c > t.start ? min(c - t.start, kTileRoutes) : 0u;
+    t.count = c > t.start ? min(c - t.start, kTaskRoutes) : 0u;
     t.row0 = p.offsets[t.expert] + t.start;
-    t.ncols = t.count <= 32 ? 32u : (t.count <= 64 ? 64u : 128u);
     return t;
 }
+__device__ __forceinline__ uint32_t sub_count(const GTask& t, uint32_t g) { return g == 0 ? min(t.count, kSub) : (t.count > kSub ? t.count - kSub : 0u); }
+__device__ __forceinline__ uint32_t sub_cols(uint32_t count) { return count <= 32 ? 32u : (count <= 64 ? 64u : 128u); }
+__device__ __forceinline__ uint32_t sub_tiles(const GTask& t) { return t.count > kSub ? 2u : 1u; }
 
-__device__ __forceinline__ void tma_load_5d_g(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-                 : "memory");
+// ---------------------------------------------------------------------------------------------
+// dequantisation of one 64-wide K chunk of one weight row (shared by the GEMM kernel and the tile hook)
+// ---------------------------------------------------------------------------------------------
+struct ChunkScale { __half2 s_lo, c_lo, s_hi, c_hi; };
+
+// d, dmin: the super-block's binary16 pair as floats; scw / mnw: four scale / min bytes of which bytes `b`, `b + 1` belong to
+// this chunk's two groups (low nibbles: group 2c, high nibbles: group 2c + 1). d*sc and dmin*mn are exact in FP32.
+__device__ __forceinline__ ChunkScale chunk_scale(float d, float dmin, uint32_t scw, uint32_t mnw, uint32_t b) {
+    // byte -> float through the 2^23 magic number (0x4B0000bb = 2^23 + bb), folded into one FMA each
+    const uint32_t sel_lo = 0x7440u + b, sel_hi = sel_lo + 1u;
+    const float dn = d * -8388608.f, mn = dmin * -8388608.f;
+    const float s_lo = fmaf(d, __uint_as_float(__byte_perm(scw, 0x4b000000u, sel_lo)), dn);
+    const float s_hi = fmaf(d, __uint_as_float(__byte_perm(scw, 0x4b000000u, sel_hi)), dn);
+    const float m_lo = fmaf(dmin, __uint_as_float(__byte_perm(mnw, 0x4b000000u, sel_lo)), mn);
+    const float m_hi = fmaf(dmin, __uint_as_float(__byte_perm(mnw, 0x4b000000u, sel_hi)), mn);
+    ChunkScale cs;
+    cs.s_lo = __float2half2_rn(s_lo); cs.c_lo = __float2half2_rn(fmaf(8.f, s_lo, -m_lo));
+    cs.s_hi = __float2half2_rn(s_hi); cs.c_hi = __float2half2_rn(fmaf(8.f, s_hi, -m_hi));
+    return cs;
 }
 
-// GATEUP: two weight matrices (gate, up) and the SwiGLU epilogue writing binary16 hidden rows in permuted position order;
-// otherwise one matrix and FP32 rows scattered to their route ids.
+// Eight code bytes (words a, b = bytes 8qq..8qq+7 of the chunk's 32) -> the 8 weights of their low nibbles (`lo`: K positions
+// 8qq..8qq+7 of the chunk) and the 8 of their high nibbles (`hi`: K positions 32+8qq..). Inside each run of 8 the values sit
+// in the order 0,2,1,3,4,6,5,7, the order every K-major operand of these kernels uses: a 32-bit word of codes splits into
+// binary16 pairs without byte shuffles.
+__device__ __forceinline__ void dequant8(uint32_t a, uint32_t b, const ChunkScale& cs, uint4& lo, uint4& hi) {
+    const __half2 k1032 = __float2half2_rn(1032.f), k72 = __float2half2_rn(72.f);
+    const uint32_t src[4] = {a, a >> 8, b, b >> 8};
+    uint32_t l[4], h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lw = (src[i] & 0x000f000fu) | 0x64006400u;     // 1024 + q
+        const uint32_t hw = (src[i] & 0x00f000f0u) | 0x54005400u;     //   64 + q
+        const __half2 ql = __hsub2(*reinterpret_cast<const __half2*>(&lw), k1032);   // q - 8, exact
+        const __half2 qh = __hsub2(*reinterpret_cast<const __half2*>(&hw), k72);
+        const __half2 wl = __hfma2(ql, cs.s_lo, cs.c_lo), wh = __hfma2(qh, cs.s_hi, cs.c_hi);
+        l[i] = *reinterpret_cast<const uint32_t*>(&wl);
+        h[i] = *reinterpret_cast<const uint32_t*>(&wh);
+    }
+    lo = make_uint4(l[0], l[1], l[2], l[3]);
+    hi = make_uint4(h[0], h[1], h[2], h[3]);
+}
+
+// GATEUP: two weight matrices (gate, up) interleaved 16 + 16 rows per lane quarter and the SwiGLU epilogue writing binary16
+// hidden rows in permuted position order; otherwise one matrix and route rows scattered to their route ids.
 template <bool GATEUP>
-__global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
+__global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
     pdl_launch_dependents();
     extern __shared__ uint8_t gsm_raw[];
     uint8_t* gsm = gsm_raw + ((1024u - (smem_u32(gsm_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(gsm);
-    // rings: quantised super-blocks (2 stages, TMA), the (d, dmin) pairs of an item (2 stages, TMA), dequantised weight tiles
-    // (2 stages, filled by the dequant warps) and activation tiles (nb_stages, TMA); the activation ring is deep because its
-    // loads see full memory latency while a weight tile is produced on chip
-    uint64_t *qfull = bars, *qempty = bars + 2, *afull = bars + 4, *aempty = bars + 6, *dfull = bars + 8, *dempty = bars + 10,
-             *bfull = bars + 12, *bempty = bars + 12 + kMaxBStages, *acc_full = bars + 12 + 2 * kMaxBStages, *acc_empty = acc_full + 2;
+    // rings: quantised super-blocks (2 stages, TMA), the (d, dmin) pairs of an item (2 stages, TMA), dequantised weight chunks
+    // (4 stages, filled by the dequant warps) and activation tiles (nb_stages, TMA); the activation ring is deep because its
+    // loads see full memory latency while a weight chunk is produced on chip
+    uint64_t *qfull = bars, *qempty = bars + 2, *dfull = bars + 4, *dempty = bars + 6, *afull = bars + 8, *aempty = bars + 8 + kAStages,
+             *bfull = bars + 8 + 2 * kAStages, *bempty = bfull + kMaxBStages, *acc_full = bempty + kMaxBStages, *acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gsm + 512);
     const uint32_t NB = p.nb_stages;
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
+    constexpr uint32_t RM = GATEUP ? 64 : 128;    // rows of ONE matrix in an item
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
             mbar_init(&qfull[s], 1); mbar_init(&qempty[s], kDqWarps);
-            mbar_init(&afull[s], kDqWarps); mbar_init(&aempty[s], 1);
             mbar_init(&dfull[s], 1); mbar_init(&dempty[s], kDqWarps);
+            mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kEpWarps);
         }
+        for (uint32_t s = 0; s < kAStages; ++s) { mbar_init(&afull[s], kDqWarps / 2); mbar_init(&aempty[s], 1); }
         for (uint32_t s = 0; s < NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], ep_warps(GATEUP)); }
         mbar_fence_init();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }   // two accumulator sets of 256 columns: the epilogue of an item overlaps the MMAs of the next
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }   // two sets of two 128-column accumulators
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();   // everything above touched shared and tensor memory only
 
-    const uint32_t n_tiles = p.tasks[0] + p.sh_tiles;
-    const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.row_blocks;
+    const uint32_t n_tasks = p.tasks[0] + p.sh_tasks;
+    const uint64_t n_items = static_cast<uint64_t>(n_tasks) * p.row_blocks;
     const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
     const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
     const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64
@@ -207,34 +264,35 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
         // =========================== TMA producer of the quantised planes ===========================
         if (lane == 0) {
             bool ok = true;
-            uint32_t qs = 0, qph = 0, ds = 0, dph = 0, cur_tile = 0xffffffffu;
-            GTile t{};
+            uint32_t qs = 0, qph = 0, ds = 0, dph = 0, cur = 0xffffffffu;
+            GTask t{};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
-                if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
-                const int r0 = static_cast<int>((item % p.row_blocks) * kRowsM);
+                if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }   // consecutive items share the task
+                const uint32_t rb = item % p.row_blocks;
+                const int r0 = static_cast<int>(rb * RM);
                 const bool shared = t.expert >= p.experts;
                 const bool hi = !shared && t.expert >= p.split;
                 const int el = shared ? 0 : static_cast<int>(hi ? t.expert - p.split : t.expert);
                 const uint32_t mi = shared ? 4u : (hi ? 1u : 0u);                 // map of matrix A; matrix B's is `ms` further
                 const uint32_t ms = shared ? 1u : 2u;
                 const uint32_t ncopy = (NMAT == 1 || (shared ? p.sh_merged : p.merged)) ? 1u : NMAT;
-                // the (d, dmin) pairs of the item's rows over the whole K
+                // the (d, dmin) pairs of the item's rows over the whole K: RM * nblk * 4 bytes per matrix = lines of 256 bytes
                 ok = gwait(&dempty[ds], dph ^ 1u);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&dfull[ds], NMAT * p.dm_mat_bytes);
                 for (uint32_t m = 0; m < ncopy; ++m)
                     tma_load_4d_g(gsm + p.off_d + ds * p.d_stage_bytes + m * p.dm_mat_bytes, &maps.d[mi + ms * m], 0,
-                                  static_cast<int>((item % p.row_blocks) * 2 * p.nblk), 0, el, &dfull[ds]);
+                                  static_cast<int>(rb * (p.dm_mat_bytes / 256u)), 0, el, &dfull[ds]);
                 if (++ds == 2) { ds = 0; dph ^= 1u; }
                 for (uint32_t sb = 0; sb < p.nblk && ok; ++sb) {
-                    // quant stage: code boxes and factor boxes of this super-block
+                    // quant stage: code lines [matrix][RM][128 B], then factor bytes [matrix][RM][16 B]
                     ok = gwait(&qempty[qs], qph ^ 1u);
                     if (!ok) break;
                     uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
-                    mbar_arrive_expect_tx(&qfull[qs], NMAT * (kRowsM * 128u + kRowsM * 16u));
+                    mbar_arrive_expect_tx(&qfull[qs], kRowsM * 128u + kRowsM * 16u);
                     for (uint32_t m = 0; m < ncopy; ++m) {
-                        tma_load_5d_g(q + m * 16384u, &maps.q[mi + ms * m], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
-                        tma_load_4d_g(q + NMAT * 16384u + m * 2048u, &maps.f[mi + ms * m], static_cast<int>(sb * 16), r0, 0, el, &qfull[qs]);
+                        tma_load_5d_g(q + m * (RM * 128u), &maps.q[mi + ms * m], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
+                        tma_load_4d_g(q + kRowsM * 128u + m * (RM * 16u), &maps.f[mi + ms * m], static_cast<int>(sb * 16), r0, 0, el, &qfull[qs]);
                     }
                     if (++qs == 2) { qs = 0; qph ^= 1u; }
                 }
@@ -243,52 +301,88 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
         }
     } else if (warp == 2 + kDqWarps) {
         // =========================== activation-tile producer ===========================
-        if (lane == 0) {
-            bool ok = true;
-            uint32_t bs = 0, bph = 0, cur_tile = 0xffffffffu;
-            GTile t{};
-            for (uint32_t item = item0; item < item1 && ok; ++item) {
-                if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
-                const CUtensorMap* xmap = &maps.x[(t.expert >= p.experts ? 3 : 0) + (t.ncols == 32 ? 0 : (t.ncols == 64 ? 1 : 2))];
-                for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
-                    ok = gwait(&bempty[bs], bph ^ 1u);
+        bool ok = true;
+        uint32_t bs = 0, bph = 0, cur = 0xffffffffu;
+        GTask t{};
+        uint32_t nsub = 1, ncols[2] = {32, 32};
+        int rows[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};   // gate-up: the four input rows this lane fetches in each sub-tile
+        for (uint32_t item = item0; item < item1 && ok; ++item) {
+            if (item / p.row_blocks != cur) {
+                cur = item / p.row_blocks; t = gtask(p, cur);
+                nsub = sub_tiles(t);
+                for (uint32_t g = 0; g < 2; ++g) {
+                    const uint32_t cnt = sub_count(t, g);
+                    ncols[g] = sub_cols(cnt);
+                    if (GATEUP) {
+#pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k) {
+                            const uint32_t j = 4 * lane + k;     // column of the sub-tile
+                            uint32_t row = 0;                    // columns past the count fetch row 0: their results are never stored
+                            if (j < cnt) {
+                                const uint32_t at = t.start + g * kSub + j;
+                                row = t.expert >= p.experts ? at : p.token_map[static_cast<uint64_t>(t.expert) * p.tokens + at] / p.selected;
+                            }
+                            rows[g][k] = static_cast<int>(row);
+                        }
+                    }
+                }
+            }
+            const bool shared = t.expert >= p.experts;
+            for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
+                for (uint32_t g = 0; g < nsub && ok; ++g) {
+                    ok = __all_sync(0xffffffffu, gwait(&bempty[bs], bph ^ 1u));   // the whole warp gives up together
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&bfull[bs], t.ncols * 128u);
-                    // byte coordinate: the map's element is a byte
-                    tma_load_2d(gsm + p.off_b + bs * 16384u, xmap, static_cast<int>(c * 128), static_cast<int>(t.row0), &bfull[bs]);
+                    uint8_t* dst = gsm + p.off_b + bs * 16384u;
+                    if (GATEUP) {
+                        if (lane == 0) mbar_arrive_expect_tx(&bfull[bs], ncols[g] * 128u);
+                        __syncwarp();
+                        // byte coordinate: the map's element is a byte
+                        if (4 * lane < ncols[g])
+                            tma_gather4(dst + lane * 512u, &maps.x[0], static_cast<int>(c * 128), rows[g][0], rows[g][1], rows[g][2], rows[g][3], &bfull[bs]);
+                    } else if (lane == 0) {
+                        const CUtensorMap* xmap = &maps.x[(shared ? 3 : 0) + (ncols[g] == 32 ? 0 : (ncols[g] == 64 ? 1 : 2))];
+                        mbar_arrive_expect_tx(&bfull[bs], ncols[g] * 128u);
+                        tma_load_2d(dst, xmap, static_cast<int>(c * 128), static_cast<int>(t.row0 + g * kSub), &bfull[bs]);
+                    }
                     if (++bs == NB) { bs = 0; bph ^= 1u; }
                 }
             }
-            if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
         }
+        if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
             bool ok = true;
-            uint32_t ms = 0, mph = 0, bs = 0, bph = 0, ab = 0, accph = 0, cur_tile = 0xffffffffu;
-            GTile t{};
+            uint32_t aph = 0, bs = 0, bph = 0, ab = 0, accph = 0, cur = 0xffffffffu;
+            GTask t{};
+            uint32_t nsub = 1, idesc[2] = {0, 0};
             for (uint32_t item = item0; item < item1 && ok; ++item) {
-                if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
-                const uint32_t idesc = umma_idesc_f16(kRowsM, t.ncols);
+                if (item / p.row_blocks != cur) {
+                    cur = item / p.row_blocks; t = gtask(p, cur);
+                    nsub = sub_tiles(t);
+                    for (uint32_t g = 0; g < 2; ++g) idesc[g] = umma_idesc_f16(kRowsM, sub_cols(sub_count(t, g)));
+                }
                 ok = gwait(&acc_empty[ab], accph ^ 1u);   // the epilogue has drained this accumulator set (used two items ago)
                 if (!ok) break;
                 tc_fence_after();
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
-                    ok = gwait(&afull[ms], mph) && gwait(&bfull[bs], bph);
+                    const uint32_t as = c & (kAStages - 1);
+                    ok = gwait(&afull[as], aph);
                     if (!ok) break;
-                    tc_fence_after();
-                    const uint64_t bdesc = umma_desc_k128(gsm + p.off_b + bs * 16384u);
-#pragma unroll
-                    for (uint32_t m = 0; m < NMAT; ++m) {
-                        const uint64_t adesc = umma_desc_k128(gsm + p.off_a + ms * NMAT * 16384u + m * 16384u);
+                    const uint64_t adesc = umma_desc_k128(gsm + p.off_a + as * 16384u);
+                    for (uint32_t g = 0; g < nsub && ok; ++g) {
+                        ok = gwait(&bfull[bs], bph);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t bdesc = umma_desc_k128(gsm + p.off_b + bs * 16384u);
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; ++kk)
-                            umma_f16(tmem_base + ab * 256u + m * 128u, adesc + kk * 2, bdesc + kk * 2, idesc, (c | kk) != 0 ? 1u : 0u);
+                            umma_f16(tmem_base + ab * 256u + g * kSub, adesc + kk * 2, bdesc + kk * 2, idesc[g], (c | kk) != 0 ? 1u : 0u);
+                        umma_commit(&bempty[bs]);   // the stage is free once the MMAs above have read it
+                        if (++bs == NB) { bs = 0; bph ^= 1u; }
                     }
-                    umma_commit(&aempty[ms]);   // both rings' stages are free once the MMAs above have read them
-                    umma_commit(&bempty[bs]);
-                    if (++ms == 2) { ms = 0; mph ^= 1u; }
-                    if (++bs == NB) { bs = 0; bph ^= 1u; }
+                    if (ok) umma_commit(&aempty[as]);
+                    if (as == kAStages - 1) aph ^= 1u;
                 }
                 if (ok) umma_commit(&acc_full[ab]);
                 if (++ab == 2) { ab = 0; accph ^= 1u; }
@@ -297,77 +391,52 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
         }
     } else if (warp < 2 + kDqWarps) {
         // =========================== dequantise (warps 2 .. 2 + kDqWarps - 1) ===========================
-        const uint32_t dw = warp - 2;                         // 0..7
-        const uint32_t row = (dw & 3u) * 32 + lane;           // weight row of the tile this thread dequantises ...
-        const uint32_t kh = dw >> 2;                          // ... and which half of every 64-wide K chunk (code bytes 16 kh .. 16 kh + 15)
-        const uint32_t sw = row & 7u;
+        const uint32_t dt = threadIdx.x - 64;                 // 0..255
+        const uint32_t half = dt >> 7;                        // which K chunks of every super-block: half, half + 2
+        const uint32_t r = dt & 127u;                         // A row of the item
+        // the row's line in the quant stage: gate-up interleaves 16 gate + 16 up rows per lane quarter
+        const uint32_t mat = GATEUP ? ((r >> 4) & 1u) : 0u;
+        const uint32_t mrow = GATEUP ? ((r >> 5) * 16u + (r & 15u)) : r;          // row inside the matrix's RM rows
+        const uint32_t line = mat * RM + mrow;
+        const uint32_t sw = r & 7u;                           // == line & 7
         bool ok = true;
-        uint32_t qs = 0, qph = 0, ms = 0, mph = 0, ds = 0, dph = 0;
+        uint32_t qs = 0, qph = 0, ds = 0, dph = 0, aph = 0;
         for (uint32_t item = item0; item < item1; ++item) {
             if (ok) ok = gwait(&dfull[ds], dph);
-            const uint8_t* dmp = gsm + p.off_d + ds * p.d_stage_bytes;
+            const uint8_t* dmp = gsm + p.off_d + ds * p.d_stage_bytes + mat * p.dm_mat_bytes + mrow * p.nblk * 4u;
             for (uint32_t sb = 0; sb < p.nblk; ++sb) {
                 if (ok) ok = gwait(&qfull[qs], qph);
                 const uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
-                // per matrix: d, dmin and the sixteen 6-bit factors of this row's super-block
-                float dd[NMAT], dmn[NMAT];
-                uint4 fac[NMAT];
+                // d, dmin and the sixteen 6-bit factors of this row's super-block
+                const uint4 fac = *reinterpret_cast<const uint4*>(q + kRowsM * 128u + line * 16u);
+                const uint32_t dmw = *reinterpret_cast<const uint32_t*>(dmp + sb * 4u);
+                const float dd = half_bits_to_float(dmw & 0xffffu), dmn = half_bits_to_float(dmw >> 16);
+                if (ok && (!finite_f32(dd) || !finite_f32(dmn))) raise_error(p.error, TSP_ERR_NONFINITE);
+                const uint8_t* codes = q + line * 128u;
 #pragma unroll
-                for (uint32_t m = 0; m < NMAT; ++m) {
-                    fac[m] = *reinterpret_cast<const uint4*>(q + NMAT * 16384u + m * 2048u + row * 16u);
-                    const uint32_t dmw = *reinterpret_cast<const uint32_t*>(dmp + m * p.dm_mat_bytes + (row * p.nblk + sb) * 4u);
-                    dd[m] = half_bits_to_float(dmw & 0xffffu);
-                    dmn[m] = half_bits_to_float(dmw >> 16);
-                    if (ok && (!finite_f32(dd[m]) || !finite_f32(dmn[m]))) raise_error(p.error, TSP_ERR_NONFINITE);
-                }
-                for (uint32_t c = 0; c < 4; ++c) {
-                    if (ok) ok = gwait(&aempty[ms], mph ^ 1u);   // the MMAs that read this A tile two chunks ago are done
+                for (uint32_t pp = 0; pp < 2; ++pp) {
+                    const uint32_t c = 2 * pp + half;          // chunk of the super-block = stage of the A ring
+                    if (ok) ok = gwait(&aempty[c], aph ^ 1u);  // the MMAs that read this stage one super-block ago are done
                     if (ok) {
-#pragma unroll
-                        for (uint32_t m = 0; m < NMAT; ++m) {
-                            const uint8_t* line = q + m * 16384u + row * 128u;
-                            const uint4 w0 = *reinterpret_cast<const uint4*>(line + (((2 * c + kh) ^ sw) << 4));
-                            const uint32_t scw = c < 2 ? fac[m].x : fac[m].y, mnw = c < 2 ? fac[m].z : fac[m].w;
-                            // factor byte -> float through the 2^23 magic number (0x4B0000bb = 2^23 + bb), folded into one FMA each
-                            const uint32_t selL = 0x7440u + 2u * (c & 1u), selH = selL + 1u;
-                            const float s_lo = fmaf(dd[m], __uint_as_float(__byte_perm(scw, 0x4b000000u, selL)), dd[m] * -8388608.f);
-                            const float s_hi = fmaf(dd[m], __uint_as_float(__byte_perm(scw, 0x4b000000u, selH)), dd[m] * -8388608.f);
-                            const float m_lo = fmaf(dmn[m], __uint_as_float(__byte_perm(mnw, 0x4b000000u, selL)), dmn[m] * -8388608.f);
-                            const float m_hi = fmaf(dmn[m], __uint_as_float(__byte_perm(mnw, 0x4b000000u, selH)), dmn[m] * -8388608.f);
-                            const __half2 sL = __float2half2_rn(s_lo), sH = __float2half2_rn(s_hi);
-                            const __half2 nL = __float2half2_rn(-m_lo), nH = __float2half2_rn(-m_hi);
-                            const __half2 k1024 = __float2half2_rn(1024.f), k16th = __float2half2_rn(0.0625f), kn64 = __float2half2_rn(-64.f);
-                            uint8_t* arow = gsm + p.off_a + ms * NMAT * 16384u + m * 16384u + row * 128u;
-                            const uint32_t words[4] = {w0.x, w0.y, w0.z, w0.w};
-                            // output chunk qq (8 binary16 = K positions 8qq..8qq+7 of this 64-wide slice, in the shared 0,2,1,3,4,6,5,7 order):
-                            // qq < 4 from the low nibbles of code bytes 8qq..8qq+7, qq >= 4 from the high nibbles of bytes 8(qq-4)..; this
-                            // thread has bytes 16 kh .. 16 kh + 15, i.e. qq = 2 kh, 2 kh + 1 and their high-nibble partners
-#pragma unroll
-                            for (uint32_t q2 = 0; q2 < 2; ++q2) {
-                                const uint32_t qq = 2 * kh + q2;
-                                const uint32_t a = words[2 * q2], b = words[2 * q2 + 1];
-                                uint32_t lo[4], hi4[4];
-                                const uint32_t src[4] = {a, a >> 8, b, b >> 8};
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    const uint32_t l = (src[i] & 0x000f000fu) | 0x64006400u;     // 1024 + q
-                                    const uint32_t h = (src[i] & 0x00f000f0u) | 0x64006400u;     // 1024 + 16 q
-                                    const __half2 ql = __hsub2(*reinterpret_cast<const __half2*>(&l), k1024);
-                                    const __half2 qh = __hfma2(*reinterpret_cast<const __half2*>(&h), k16th, kn64);
-                                    const __half2 wl = __hfma2(ql, sL, nL), wh = __hfma2(qh, sH, nH);
-                                    lo[i] = *reinterpret_cast<const uint32_t*>(&wl);
-                                    hi4[i] = *reinterpret_cast<const uint32_t*>(&wh);
-                                }
-                                *reinterpret_cast<uint4*>(arow + ((qq ^ sw) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                                *reinterpret_cast<uint4*>(arow + (((qq + 4) ^ sw) << 4)) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-                            }
-                        }
+                        const ChunkScale cs = chunk_scale(dd, dmn, pp ? fac.y : fac.x, pp ? fac.w : fac.z, 2u * half);
+                        const uint4 w0 = *reinterpret_cast<const uint4*>(codes + (((2 * c) ^ sw) << 4));
+                        const uint4 w1 = *reinterpret_cast<const uint4*>(codes + (((2 * c + 1) ^ sw) << 4));
+                        uint8_t* arow = gsm + p.off_a + c * 16384u + r * 128u;
+                        uint4 lo, hi;
+                        dequant8(w0.x, w0.y, cs, lo, hi);
+                        *reinterpret_cast<uint4*>(arow + ((0u ^ sw) << 4)) = lo; *reinterpret_cast<uint4*>(arow + ((4u ^ sw) << 4)) = hi;
+                        dequant8(w0.z, w0.w, cs, lo, hi);
+                        *reinterpret_cast<uint4*>(arow + ((1u ^ sw) << 4)) = lo; *reinterpret_cast<uint4*>(arow + ((5u ^ sw) << 4)) = hi;
+                        dequant8(w1.x, w1.y, cs, lo, hi);
+                        *reinterpret_cast<uint4*>(arow + ((2u ^ sw) << 4)) = lo; *reinterpret_cast<uint4*>(arow + ((6u ^ sw) << 4)) = hi;
+                        dequant8(w1.z, w1.w, cs, lo, hi);
+                        *reinterpret_cast<uint4*>(arow + ((3u ^ sw) << 4)) = lo; *reinterpret_cast<uint4*>(arow + ((7u ^ sw) << 4)) = hi;
                         fence_async_smem();   // make the generic-proxy writes visible to the tensor-core (async) proxy
                     }
                     __syncwarp();
-                    if (lane == 0 && ok) mbar_arrive(&afull[ms]);
-                    if (++ms == 2) { ms = 0; mph ^= 1u; }
+                    if (lane == 0 && ok) mbar_arrive(&afull[c]);
                 }
+                aph ^= 1u;
                 __syncwarp();
                 if (lane == 0 && ok) mbar_arrive(&qempty[qs]);
                 if (++qs == 2) { qs = 0; qph ^= 1u; }
@@ -378,59 +447,81 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else {
-        // =========================== epilogue (the last ep_warps warps) ===========================
+        // =========================== epilogue (the last kEpWarps warps) ===========================
         const uint32_t quarter = warp & 3u;                   // tensor-memory lane quarter this warp may read
-        constexpr uint32_t EH = ep_warps(GATEUP) / 4;         // warps per quarter: they take the 32-column batches in turn
-        const uint32_t ehalf = (warp - (3 + kDqWarps)) >> 2;
+        const uint32_t ehalf = (warp - (3 + kDqWarps)) >> 2;  // the two warps of a quarter take the 32-column batches in turn
         bool ok = true;
-        uint32_t ab = 0, accph = 0, cur_tile = 0xffffffffu;
-        GTile t{};
+        uint32_t ab = 0, accph = 0, cur = 0xffffffffu;
+        GTask t{};
         for (uint32_t item = item0; item < item1; ++item) {
-            if (item / p.row_blocks != cur_tile) { cur_tile = item / p.row_blocks; t = gtile(p, cur_tile); }   // consecutive items share the tile
+            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }   // consecutive items share the task
             const uint32_t rb = item % p.row_blocks;
-            // this warp's 32 accumulator lanes = weight rows rb*128 + quarter*32 + lane, all token columns
-            // route ids of the tile's positions, fetched before the wait so their latency hides behind the MMAs:
-            // lane l keeps positions l, 32 + l, 64 + l, 96 + l
-            uint32_t rt[4] = {0, 0, 0, 0};
+            const bool shared = t.expert >= p.experts;
+            const uint32_t nsub = sub_tiles(t);
+            // down: route ids of this lane's columns (column j0 + lane of each batch), fetched before the wait so their latency
+            // hides behind the MMAs: slot [g][b] = batch j0 = ehalf * 32 + 64 * b of sub-tile g
+            uint32_t rt[2][2] = {{0, 0}, {0, 0}};
             if (!GATEUP) {
 #pragma unroll
-                for (uint32_t qd = 0; qd < 4; ++qd)
-                    if (qd * 32 + lane < t.count) rt[qd] = t.expert >= p.experts ? t.row0 + qd * 32 + lane : p.pos_route[t.row0 + qd * 32 + lane];
+                for (uint32_t g = 0; g < 2; ++g)
+#pragma unroll
+                    for (uint32_t b = 0; b < 2; ++b) {
+                        const uint32_t j = ehalf * 32 + 64 * b + lane;
+                        if (j < sub_count(t, g)) {
+                            const uint32_t at = t.start + g * kSub + j;
+                            rt[g][b] = shared ? at : p.token_map[static_cast<uint64_t>(t.expert) * p.tokens + at];
+                        }
+                    }
             }
             if (ok) ok = gwait(&acc_full[ab], accph);
             if (ok) {
                 tc_fence_after();
-                const uint32_t wrow = rb * kRowsM + quarter * 32 + lane;
-                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * 256u;
-                // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weight tiles use
-                const uint32_t hcol = (wrow & ~7u) | ((wrow & 4u) | ((wrow & 1u) << 1) | ((wrow & 2u) >> 1));
-                char* const obase = reinterpret_cast<char*>(t.expert >= p.experts ? p.sh_out : p.out);
-                const uint64_t ostride = t.expert >= p.experts ? p.sh_out_stride_bytes : p.out_stride_bytes;
-                char* hrow = obase + static_cast<uint64_t>(t.row0) * ostride + (GATEUP ? hcol * 2 : 0);
+                char* const obase = reinterpret_cast<char*>(shared ? p.sh_out : p.out);
+                const uint64_t ostride = shared ? p.sh_out_stride_bytes : p.out_stride_bytes;
                 bool bad = false;
-                for (uint32_t j0 = ehalf * 32; j0 < t.ncols && j0 < t.count; j0 += 32 * EH) {
-                    uint32_t g[32], u[GATEUP ? 32 : 1];
-                    const uint32_t rq = j0 < 32 ? rt[0] : (j0 < 64 ? rt[1] : (j0 < 96 ? rt[2] : rt[3]));   // this lane's route id in the 32-wide group of j0
-                    tmem_ld32(taddr + j0, g);
-                    if constexpr (GATEUP) tmem_ld32(taddr + 128u + j0, u);
-                    tmem_ld_wait();
+                for (uint32_t g = 0; g < nsub; ++g) {
+                    const uint32_t cnt = sub_count(t, g), nc = sub_cols(cnt);
+                    const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * 256u + g * kSub;
+                    for (uint32_t j0 = ehalf * 32; j0 < nc && j0 < cnt; j0 += 64) {
+                        uint32_t v[32];
+                        tmem_ld32(taddr + j0, v);
+                        tmem_ld_wait();
+                        if constexpr (GATEUP) {
+                            // lanes 0..15 hold the gate rows of 16 hidden units, lanes 16..31 the up rows of the same units. For each
+                            // pair of token columns the low half-warp finishes the even column and the high half-warp the odd one.
+                            const uint32_t unit = rb * 64u + quarter * 16u + (lane & 15u);
+                            // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weight tiles use
+                            const uint32_t hcol = (unit & ~7u) | ((unit & 4u) | ((unit & 1u) << 1) | ((unit & 2u) >> 1));
+                            char* hrow = obase + static_cast<uint64_t>(t.row0 + g * kSub) * ostride + hcol * 2;
+                            const bool low = lane < 16;
 #pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i) {
-                        const uint32_t j = j0 + i;
-                        if (GATEUP) {
-                            if (j < t.count) {
-                                const float gv = __uint_as_float(g[i]);
-                                const float v = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[GATEUP ? i : 0]);   // silu(g) * u
-                                const __half hv = __float2half_rn(v);
-                                bad |= !finite_f32(__half2float(hv));
-                                *reinterpret_cast<__half*>(hrow + static_cast<uint64_t>(j) * ostride) = hv;
+                            for (uint32_t a = 0; a < 16; ++a) {
+                                const uint32_t send = low ? v[2 * a + 1] : v[2 * a];
+                                const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
+                                const float gv = __uint_as_float(low ? v[2 * a] : recv);
+                                const float uv = __uint_as_float(low ? recv : v[2 * a + 1]);
+                                const uint32_t j = j0 + 2 * a + (low ? 0u : 1u);
+                                if (j < cnt) {
+                                    const float val = __fdividef(gv, 1.f + __expf(-gv)) * uv;   // silu(g) * u
+                                    const __half hv = __float2half_rn(val);
+                                    bad |= !finite_f32(__half2float(hv));
+                                    *reinterpret_cast<__half*>(hrow + static_cast<uint64_t>(j) * ostride) = hv;
+                                }
                             }
                         } else {
-                            const uint32_t route = __shfl_sync(0xffffffffu, rq, j & 31u);
-                            if (j < t.count) {
-                                const float v = __uint_as_float(g[i]);
-                                bad |= !finite_f32(v);
-                                reinterpret_cast<float*>(obase + static_cast<uint64_t>(route) * ostride)[wrow] = v;
+                            const uint32_t wrow = rb * kRowsM + quarter * 32 + lane;   // output channel of this lane
+                            const uint32_t rq = rt[g][j0 >> 6];
+                            const bool f16 = !shared && p.out_f16;
+#pragma unroll
+                            for (uint32_t i = 0; i < 32; ++i) {
+                                const uint32_t route = __shfl_sync(0xffffffffu, rq, i);
+                                if (j0 + i < cnt) {
+                                    const float val = __uint_as_float(v[i]);
+                                    bad |= !finite_f32(val);
+                                    char* orow = obase + static_cast<uint64_t>(route) * ostride;
+                                    if (f16) reinterpret_cast<__half*>(orow)[wrow] = __float2half_rn(val);
+                                    else reinterpret_cast<float*>(orow)[wrow] = val;
+                                }
                             }
                         }
                     }
@@ -450,9 +541,45 @@ __global__ void __launch_bounds__(g_warps(GATEUP) * 32, 1) grouped_mma_kernel(co
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+// ---------------------------------------------------------------------------------------------
+// test hook: the binary16 values the GEMM kernel stages for one planar Q4_K expert, in natural K order
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) staged_f16_kernel(const uint8_t* __restrict__ expert, uint32_t rows, uint32_t nblk, __half* __restrict__ out) {
+    const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const uint64_t units = static_cast<uint64_t>(rows) * nblk;
+    for (uint32_t u = threadIdx.x & 31u; u < nblk * 4; u += 32) {   // (super-block, chunk) of this row
+        const uint32_t sb = u >> 2, c = u & 3u;
+        const uint64_t blk = static_cast<uint64_t>(row) * nblk + sb;
+        const uint4 fac = *reinterpret_cast<const uint4*>(expert + units * 128 + blk * 16);
+        const uint32_t dmw = *reinterpret_cast<const uint32_t*>(expert + units * 144 + blk * 4);
+        const ChunkScale cs = chunk_scale(half_bits_to_float(dmw & 0xffffu), half_bits_to_float(dmw >> 16), (c & 2u) ? fac.y : fac.x,
+                                          (c & 2u) ? fac.w : fac.z, 2u * (c & 1u));
+        const uint32_t* codes = reinterpret_cast<const uint32_t*>(expert + blk * 128 + c * 32);
+        __half* dst = out + static_cast<uint64_t>(row) * nblk * 256 + sb * 256 + c * 64;
+#pragma unroll
+        for (uint32_t qq = 0; qq < 4; ++qq) {
+            uint4 lo, hi;
+            dequant8(codes[2 * qq], codes[2 * qq + 1], cs, lo, hi);
+            const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+            const int pos[8] = {0, 2, 1, 3, 4, 6, 5, 7};   // stored position i holds K element pos[i] of the run
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                dst[8 * qq + pos[i]] = __ushort_as_half(static_cast<unsigned short>((lw[i >> 1] >> (16 * (i & 1))) & 0xffffu));
+                dst[32 + 8 * qq + pos[i]] = __ushort_as_half(static_cast<unsigned short>((hw[i >> 1] >> (16 * (i & 1))) & 0xffffu));
+            }
+        }
+    }
+}
+
+int launch_staged_f16(const uint8_t* expert, uint32_t rows, uint32_t cols, void* out, cudaStream_t st) {
+    staged_f16_kernel<<<(rows + 3) / 4, 128, 0, st>>>(expert, rows, cols / 256, static_cast<__half*>(out));
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
 
 // ---------------------------------------------------------------------------------------------
-// helpers: route offsets, gather of the routed rows into permuted order
+// helpers: route offsets, the K-ordered binary16 copy of the input rows
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) route_offsets_kernel(const uint32_t* __restrict__ counts, uint32_t experts, uint32_t* __restrict__ offsets) {
     pdl_launch_dependents();
@@ -476,35 +603,35 @@ __global__ void __launch_bounds__(256) route_offsets_kernel(const uint32_t* __re
     if (tid == 0) offsets[experts] = carry;
 }
 
-// position p of the permuted order belongs to the expert e with offsets[e] <= p < offsets[e+1]; its route id is
-// token_map[e*tokens + p - offsets[e]]. Rows are written as binary16 with the K order 0,2,1,3,4,6,5,7 inside each run of 8.
+// Rows (FP32 or binary16) -> binary16 rows with the K order 0,2,1,3,4,6,5,7 inside each run of 8: the B operand of the
+// gate-up GEMM, fetched from here by token id. 64 threads per row, four rows per CTA.
+template <bool IN16>
 __global__ void __launch_bounds__(256)
-gather_rows_kernel(const float* __restrict__ x, uint64_t x_stride, uint32_t in_div, const uint32_t* __restrict__ token_map,
-                   const uint32_t* __restrict__ offsets, uint32_t experts, uint32_t tokens, uint32_t cols, __half* __restrict__ xp,
-                   uint64_t xp_stride, uint32_t* __restrict__ pos_route, uint32_t* error) {
+rows_f16k_kernel(const void* __restrict__ x, uint64_t x_stride, uint32_t rows, uint32_t cols, __half* __restrict__ xk, uint64_t xk_stride, uint32_t* error) {
     pdl_launch_dependents();
     pdl_wait();
-    const uint32_t pos = blockIdx.x * 4 + (threadIdx.x >> 6);
-    uint32_t rid = pos;   // no tables: every row in its own position (a dense expert)
-    if (token_map) {
-        if (pos >= offsets[experts]) return;
-        uint32_t lo = 0, hi = experts;   // largest e with offsets[e] <= pos
-        while (hi - lo > 1) { const uint32_t mid = (lo + hi) >> 1; if (offsets[mid] <= pos) lo = mid; else hi = mid; }
-        rid = token_map[static_cast<uint64_t>(lo) * tokens + (pos - offsets[lo])];
-    } else if (pos >= tokens) {
-        return;
-    }
+    const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 6);
+    if (row >= rows) return;
     const uint32_t t64 = threadIdx.x & 63;
-    if (t64 == 0 && pos_route) pos_route[pos] = rid;
-    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(x) + static_cast<uint64_t>(rid / in_div) * x_stride);
-    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(xp) + static_cast<uint64_t>(pos) * xp_stride);
+    const char* src = reinterpret_cast<const char*>(x) + static_cast<uint64_t>(row) * x_stride;
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(xk) + static_cast<uint64_t>(row) * xk_stride);
     bool bad = false;
     for (uint32_t k8 = t64; k8 < cols / 8; k8 += 64) {
-        const float4 a = src[2 * k8], b = src[2 * k8 + 1];
-        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         uint32_t h[8];
+        if (IN16) {
+            const uint4 v = reinterpret_cast<const uint4*>(src)[k8];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { const __half hv = __float2half_rn(v[i]); bad |= !finite_f32(__half2float(hv)); h[i] = __half_as_ushort(hv); }
+            for (int i = 0; i < 4; ++i) {
+                h[2 * i] = w[i] & 0xffffu; h[2 * i + 1] = w[i] >> 16;
+                bad |= (w[i] & 0x7c00u) == 0x7c00u || (w[i] & 0x7c000000u) == 0x7c000000u;
+            }
+        } else {
+            const float4 a = reinterpret_cast<const float4*>(src)[2 * k8], b = reinterpret_cast<const float4*>(src)[2 * k8 + 1];
+            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { const __half hv = __float2half_rn(v[i]); bad |= !finite_f32(__half2float(hv)); h[i] = __half_as_ushort(hv); }
+        }
         dst[k8] = make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
     }
     if (bad) raise_error(error, TSP_ERR_NONFINITE);
@@ -515,11 +642,12 @@ int launch_route_offsets(const uint32_t* counts, uint32_t experts, uint32_t* off
     return TSP_OK;
 }
 
-int launch_gather_rows(const float* x, uint64_t x_stride, uint32_t in_div, const uint32_t* token_map, const uint32_t* offsets, uint32_t experts,
-                       uint32_t tokens, uint32_t max_routes, uint32_t cols, void* xp, uint64_t xp_stride, uint32_t* pos_route, uint32_t* error,
-                       cudaStream_t st) {
-    TSP_CUDA(launch_pdl(gather_rows_kernel, dim3((max_routes + 3) / 4), dim3(256), 0, st, x, x_stride, in_div, token_map, offsets, experts, tokens, cols, static_cast<__half*>(xp), xp_stride, pos_route, error));
-    TSP_CUDA(cudaGetLastError());
+int launch_rows_f16k(const void* x, uint64_t x_stride, uint32_t x_dtype, uint32_t rows, uint32_t cols, void* xk, uint64_t xk_stride, uint32_t* error,
+                     cudaStream_t st) {
+    if (x_dtype == 1)
+        TSP_CUDA(launch_pdl(rows_f16k_kernel<true>, dim3((rows + 3) / 4), dim3(256), 0, st, x, x_stride, rows, cols, static_cast<__half*>(xk), xk_stride, error));
+    else
+        TSP_CUDA(launch_pdl(rows_f16k_kernel<false>, dim3((rows + 3) / 4), dim3(256), 0, st, x, x_stride, rows, cols, static_cast<__half*>(xk), xk_stride, error));
     return TSP_OK;
 }
 
@@ -529,28 +657,30 @@ int launch_gather_rows(const float* x, uint64_t x_stride, uint32_t in_div, const
 template <bool GATEUP>
 static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t smem, int grid, cudaStream_t st) {
     auto kernel = grouped_mma_kernel<GATEUP>;
-    static thread_local size_t configured = 0;
-    if (smem > configured) {
-        TSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured = smem;
-    }
-    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(g_warps(GATEUP) * 32), smem, st, m, p));
+    static thread_local SmemAttrCache configured;   // per kernel instantiation, keyed by device
+    TSP_CUDA(ensure_dynamic_smem(kernel, configured, smem));
+    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGWarps * 32), smem, st, m, p));
     return TSP_OK;
 }
 
-// a/b: Q4_K Pack v3 planar matrix sets [rows x cols]; act: binary16 rows in permuted position order ([max_positions] rows of
-// `cols` values, 16-byte aligned stride); out: gate-up -> binary16 rows [positions x rows] in permuted order, down -> FP32 rows by route id.
-int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const void* act, uint64_t act_stride, uint32_t max_positions,
-                   const uint32_t* tasks, const uint32_t* counts, const uint32_t* offsets, const uint32_t* pos_route, void* out,
-                   uint64_t out_stride, uint32_t* error, cudaStream_t st, const GroupedShared* sh) {
+// a/b: Q4_K Pack v3 planar matrix sets [rows x cols].
+// gate-up: act = K-ordered binary16 copy of the `act_rows` input rows (fetched by token id = route id / selected);
+//          out = binary16 hidden rows [positions x rows] in permuted position order; shared expert: sh->out rows by token.
+// down:    act = hidden rows in permuted position order (act_rows of them); out = route rows by route id, FP32 or binary16;
+//          shared expert: sh->act hidden rows by token, sh->out FP32 rows by token.
+int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const void* act, uint64_t act_stride, uint32_t act_rows,
+                   uint32_t tokens, uint32_t selected, const uint32_t* token_map, const uint32_t* tasks, const uint32_t* counts,
+                   const uint32_t* offsets, void* out, uint64_t out_stride, uint32_t out_f16, uint32_t* error, cudaStream_t st,
+                   const GroupedShared* sh) {
     if (a->type != TSP_TYPE_Q4_K || a->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "grouped GEMM: only Q4_K Pack v3 planar weights have a tensor-core kernel");
-    TSP_REQUIRE(a->rows % kRowsM == 0 && a->cols % 256 == 0, "grouped GEMM: rows must be a multiple of 128 and columns of 256");
+    const uint32_t rm = gateup ? 64u : 128u;
+    TSP_REQUIRE(a->rows % rm == 0 && a->cols % 256 == 0, "grouped GEMM: rows must be a multiple of %u and columns of 256", rm);
     GroupedParams p{};
     const uint32_t nblk = a->cols / 256;
     TSP_REQUIRE(nblk <= 32, "grouped GEMM: K extent too large");
     p.split = a->split < a->experts ? a->split : a->experts;
     p.experts = a->experts;
-    p.rows = a->rows; p.cols = a->cols; p.nblk = nblk; p.row_blocks = a->rows / kRowsM;
+    p.nblk = nblk; p.row_blocks = a->rows / rm;
     const uint64_t total_units = static_cast<uint64_t>(a->rows) * nblk;
     const uint64_t sm_off = total_units * 128, dm_off = total_units * 144;
     const uint8_t* base[4] = {static_cast<const uint8_t*>(a->base), static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base), nullptr, nullptr};
@@ -559,17 +689,18 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
         base[3] = static_cast<const uint8_t*>(b->base_hi ? b->base_hi : b->base);
     }
     for (int i = 0; i < (gateup ? 4 : 2); ++i) TSP_REQUIRE(reinterpret_cast<uintptr_t>(base[i]) % 16 == 0, "grouped GEMM: expert images must be 16-byte aligned");
-    p.tasks = tasks; p.counts = counts; p.offsets = offsets; p.pos_route = pos_route;
-    p.out = out; p.out_stride_bytes = out_stride; p.error = error;
+    p.tokens = tokens; p.selected = selected; p.token_map = token_map;
+    p.tasks = tasks; p.counts = counts; p.offsets = offsets;
+    p.out = out; p.out_stride_bytes = out_stride; p.out_f16 = out_f16; p.error = error;
     const uint32_t nmat = gateup ? 2 : 1;
-    p.dm_mat_bytes = kRowsM * nblk * 4u;
+    p.dm_mat_bytes = rm * nblk * 4u;                  // a multiple of 256: rm >= 64
     p.off_q = 1024;
-    p.q_stage_bytes = nmat * (16384u + 2048u);
+    p.q_stage_bytes = kRowsM * (128u + 16u);
     p.off_d = p.off_q + 2 * p.q_stage_bytes;
     p.d_stage_bytes = (nmat * p.dm_mat_bytes + 1023u) & ~1023u;
     p.off_a = p.off_d + 2 * p.d_stage_bytes;
-    p.off_b = p.off_a + 2 * nmat * 16384u;
-    TSP_REQUIRE(p.off_b + 2 * 16384u + 1024 <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
+    p.off_b = p.off_a + kAStages * 16384u;
+    TSP_REQUIRE(p.off_b + 3 * 16384u + 1024 <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
     p.nb_stages = (227 * 1024 - 1024 - p.off_b) / 16384u;
     if (p.nb_stages > kMaxBStages) p.nb_stages = kMaxBStages;
     const size_t smem = p.off_b + p.nb_stages * 16384u + 1024;
@@ -582,43 +713,53 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     };
     uint64_t delta = 0, delta_hi = 0;
     p.merged = gateup && mergeable(base[0], base[2], &delta) && mergeable(base[1], base[3], &delta_hi) && delta == delta_hi;
+    GroupedMaps maps;
+    auto plane_maps = [&](const uint8_t* bp, uint32_t mats, uint64_t ds, uint32_t n, uint64_t stride, uint32_t at) -> int {
+        {   // codes: [128 B of a super-block][row][super-block][matrix][expert], 128-byte swizzle
+            const uint64_t dims[5] = {128, a->rows, nblk, mats, n}, strides[4] = {uint64_t(nblk) * 128, 128, ds, stride};
+            const uint32_t box[5] = {128, rm, 1, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp, 5, dims, strides, box, true, &maps.q[at])) return rc;
+        }
+        {   // factors: [16 B x super-blocks][row][matrix][expert]
+            const uint64_t dims[4] = {uint64_t(nblk) * 16, a->rows, mats, n}, strides[3] = {uint64_t(nblk) * 16, ds, stride};
+            const uint32_t box[4] = {16, rm, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp + sm_off, 4, dims, strides, box, false, &maps.f[at])) return rc;
+        }
+        {   // (d, dmin) pairs: the plane in lines of 256 bytes, [256 B][line][matrix][expert]; an item's rows are dm_mat_bytes / 256 lines
+            const uint64_t dims[4] = {256, total_units * 4 / 256, mats, n}, strides[3] = {256, ds, stride};
+            const uint32_t box[4] = {256, p.dm_mat_bytes / 256u, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp + dm_off, 4, dims, strides, box, false, &maps.d[at])) return rc;
+        }
+        return TSP_OK;
+    };
     const uint32_t mats = p.merged ? 2 : 1;
     const uint64_t ds = p.merged ? delta : 16;
-    GroupedMaps maps;
     const uint64_t stride = a->experts > 1 ? a->expert_stride : 16;
     TSP_REQUIRE(stride % 16 == 0, "grouped GEMM: expert stride must be a multiple of 16");
+    TSP_REQUIRE(total_units * 4 % 256 == 0, "grouped GEMM: the (d, dmin) plane must be a whole number of 256-byte lines");
     const uint32_t n_lo = p.split, n_hi = a->experts - p.split;
     for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t m = i >> 1;
         const bool hi = i & 1;
         if (m == 1 && (!gateup || p.merged)) { maps.q[i] = maps.q[i - 2]; maps.f[i] = maps.f[i - 2]; maps.d[i] = maps.d[i - 2]; continue; }
         if (hi && n_hi == 0) { maps.q[i] = maps.q[i - 1]; maps.f[i] = maps.f[i - 1]; maps.d[i] = maps.d[i - 1]; continue; }
-        const uint32_t n = hi ? n_hi : (n_lo ? n_lo : 1);
-        const uint8_t* bp = base[i];
-        {   // codes: [128 B of a super-block][row][super-block][matrix][expert], 128-byte swizzle
-            const uint64_t dims[5] = {128, a->rows, nblk, mats, n}, strides[4] = {uint64_t(nblk) * 128, 128, ds, stride};
-            const uint32_t box[5] = {128, kRowsM, 1, mats, 1};
-            if (int rc = get_tensor_map_bytes(bp, 5, dims, strides, box, true, &maps.q[i])) return rc;
-        }
-        {   // factors: [16 B x super-blocks][row][matrix][expert]
-            const uint64_t dims[4] = {uint64_t(nblk) * 16, a->rows, mats, n}, strides[3] = {uint64_t(nblk) * 16, ds, stride};
-            const uint32_t box[4] = {16, kRowsM, mats, 1};
-            if (int rc = get_tensor_map_bytes(bp + sm_off, 4, dims, strides, box, false, &maps.f[i])) return rc;
-        }
-        {   // (d, dmin) pairs: the plane in lines of 256 bytes, [256 B][line][matrix][expert]; a row block of 128 rows is 2 * nblk lines
-            const uint64_t dims[4] = {256, total_units * 4 / 256, mats, n}, strides[3] = {256, ds, stride};
-            const uint32_t box[4] = {256, 2 * nblk, mats, 1};
-            if (int rc = get_tensor_map_bytes(bp + dm_off, 4, dims, strides, box, false, &maps.d[i])) return rc;
-        }
-    }
-    const uint32_t ns[3] = {32, 64, 128};
-    for (int i = 0; i < 3; ++i) {
-        const uint64_t dims[2] = {uint64_t(a->cols) * 2, max_positions}, strides[1] = {act_stride};
-        const uint32_t box[2] = {128, ns[i]};
-        if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[i])) return rc;
-        maps.x[3 + i] = maps.x[i];
+        if (int rc = plane_maps(base[i], mats, ds, hi ? n_hi : (n_lo ? n_lo : 1), stride, i)) return rc;
     }
     for (int i = 4; i < 6; ++i) { maps.q[i] = maps.q[0]; maps.f[i] = maps.f[0]; maps.d[i] = maps.d[0]; }
+    const uint32_t ns[3] = {32, 64, 128};
+    if (gateup) {   // rows fetched one by one: box of one row
+        const uint64_t dims[2] = {uint64_t(a->cols) * 2, act_rows}, strides[1] = {act_stride};
+        const uint32_t box[2] = {128, 1};
+        if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[0])) return rc;
+        for (int i = 1; i < 6; ++i) maps.x[i] = maps.x[0];
+    } else {
+        for (int i = 0; i < 3; ++i) {
+            const uint64_t dims[2] = {uint64_t(a->cols) * 2, act_rows}, strides[1] = {act_stride};
+            const uint32_t box[2] = {128, ns[i]};
+            if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[i])) return rc;
+            maps.x[3 + i] = maps.x[i];
+        }
+    }
     if (sh) {   // the layer's dense shared expert: same shape, one expert, its own rows
         const uint8_t* sa = static_cast<const uint8_t*>(sh->a->base);
         const uint8_t* sb = gateup ? static_cast<const uint8_t*>(sh->b->base) : nullptr;
@@ -626,26 +767,18 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
         uint64_t sdelta = 0;
         p.sh_merged = gateup && mergeable(sa, sb, &sdelta);
         p.sh_tokens = sh->tokens;
-        p.sh_tiles = (sh->tokens + kTileRoutes - 1) / kTileRoutes;
+        p.sh_tasks = (sh->tokens + kTaskRoutes - 1) / kTaskRoutes;
         p.sh_out = sh->out; p.sh_out_stride_bytes = sh->out_stride;
-        const uint32_t smats = p.sh_merged ? 2 : 1;
-        const uint64_t sds = p.sh_merged ? sdelta : 16;
-        for (uint32_t m = 0; m < (gateup && !p.sh_merged ? 2u : 1u); ++m) {
-            const uint8_t* bp = m == 0 ? sa : sb;
-            const uint64_t dq[5] = {128, a->rows, nblk, smats, 1}, sq[4] = {uint64_t(nblk) * 128, 128, sds, 16};
-            const uint32_t bq[5] = {128, kRowsM, 1, smats, 1};
-            if (int rc = get_tensor_map_bytes(bp, 5, dq, sq, bq, true, &maps.q[4 + m])) return rc;
-            const uint64_t df[4] = {uint64_t(nblk) * 16, a->rows, smats, 1}, sf[3] = {uint64_t(nblk) * 16, sds, 16};
-            const uint32_t bf[4] = {16, kRowsM, smats, 1};
-            if (int rc = get_tensor_map_bytes(bp + sm_off, 4, df, sf, bf, false, &maps.f[4 + m])) return rc;
-            const uint64_t dd[4] = {256, total_units * 4 / 256, smats, 1}, sd[3] = {256, sds, 16};
-            const uint32_t bd[4] = {256, 2 * nblk, smats, 1};
-            if (int rc = get_tensor_map_bytes(bp + dm_off, 4, dd, sd, bd, false, &maps.d[4 + m])) return rc;
-        }
-        for (int i = 0; i < 3; ++i) {
-            const uint64_t dims[2] = {uint64_t(a->cols) * 2, sh->tokens}, strides[1] = {sh->act_stride};
-            const uint32_t box[2] = {128, ns[i]};
-            if (int rc = get_tensor_map_bytes(sh->act, 2, dims, strides, box, true, &maps.x[3 + i])) return rc;
+        if (int rc = plane_maps(sa, p.sh_merged ? 2 : 1, p.sh_merged ? sdelta : 16, 1, 16, 4)) return rc;
+        if (gateup && !p.sh_merged) { if (int rc = plane_maps(sb, 1, 16, 1, 16, 5)) return rc; }
+        if (gateup) {
+            TSP_REQUIRE(sh->act == act && sh->tokens <= act_rows, "grouped gate-up: the shared expert reads the same K-ordered input rows");
+        } else {
+            for (int i = 0; i < 3; ++i) {
+                const uint64_t dims[2] = {uint64_t(a->cols) * 2, sh->tokens}, strides[1] = {sh->act_stride};
+                const uint32_t box[2] = {128, ns[i]};
+                if (int rc = get_tensor_map_bytes(sh->act, 2, dims, strides, box, true, &maps.x[3 + i])) return rc;
+            }
         }
     }
     const int grid = sm_count();

@@ -198,15 +198,113 @@ grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint3
 }
 
 // ---------------------------------------------------------------------------------------------
+// Decode-size prologue: route + permutation + tile table of a batch of <= 64 token rows in ONE launch (block 0), with the
+// binary16 -> FP32 copy of the input rows done by the remaining blocks of the same launch. The tables are the ones the
+// separate kernels above produce, bit for bit: the per-expert token order comes from a 64-bit mask of the tokens that
+// name the expert (bit t set = token t routes here), so position = number of lower set bits: no atomics decide an order.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPrologueThreads = 1024;
+constexpr uint32_t kPrologueTokens = 64, kPrologueExperts = 1024;
+
+__global__ void __launch_bounds__(kPrologueThreads)
+decode_prologue_kernel(const float* __restrict__ logits, uint64_t logits_stride, uint32_t tokens, uint32_t experts, uint32_t selected,
+                       uint32_t mode, int normalize, uint32_t tile, uint32_t* __restrict__ ids, float* __restrict__ weights,
+                       uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* __restrict__ tasks,
+                       const __half* __restrict__ x16, uint64_t x16_stride, float* __restrict__ x32, uint64_t x32_stride, uint32_t channels,
+                       uint32_t* error) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (blockIdx.x > 0) {   // the conversion blocks: binary16 rows -> FP32 rows (exact)
+        const uint32_t per_row = channels / 4;   // four values per thread step
+        for (uint32_t i = (blockIdx.x - 1) * blockDim.x + threadIdx.x; i < tokens * per_row; i += (gridDim.x - 1) * blockDim.x) {
+            const uint32_t row = i / per_row, c4 = i - row * per_row;
+            const uint2 h = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(x16) + row * x16_stride + c4 * 8ull);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+            *reinterpret_cast<float4*>(reinterpret_cast<char*>(x32) + row * x32_stride + c4 * 16ull) = make_float4(a.x, a.y, b.x, b.y);
+        }
+        return;
+    }
+    extern __shared__ float pro_smem[];          // [warps][experts] routing rows, reused afterwards
+    __shared__ unsigned long long mask[kPrologueExperts];
+    __shared__ uint32_t tile_off[kPrologueExperts + 1];
+    __shared__ uint32_t warp_tiles[32], warp_routes[32];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+    for (uint32_t e = tid; e < experts; e += blockDim.x) mask[e] = 0ull;
+    for (uint32_t t = warp; t < tokens; t += nwarps)
+        route_row(pro_smem + warp * experts, reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + t * logits_stride), t, experts,
+                  selected, mode, normalize, ids, weights, error, lane);
+    __syncthreads();   // ids are complete (and visible to this block)
+    const uint32_t routes = tokens * selected;
+    for (uint32_t i = tid; i < routes; i += blockDim.x) {
+        const uint32_t t = i / selected, e = ids[i];
+        if (e >= experts) { raise_error(error, TSP_ERR_INDEX); continue; }
+        const unsigned long long bit = 1ull << t;
+        if (atomicOr(&mask[e], bit) & bit) raise_error(error, TSP_ERR_INDEX);   // an expert named twice by one token
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < routes; i += blockDim.x) {
+        const uint32_t t = i / selected, e = ids[i];
+        if (e >= experts) continue;
+        const uint32_t j = __popcll(mask[e] & ((1ull << t) - 1ull));
+        token_map[static_cast<uint64_t>(e) * tokens + j] = i;
+    }
+    // tile table: exclusive scan of tiles per expert over the block (experts <= blockDim.x)
+    uint32_t c = 0, n = 0;
+    if (tid < experts) { c = __popcll(mask[tid]); n = (c + tile - 1) / tile; counts[tid] = c; }
+    uint32_t incl_n = n, incl_c = c;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t tn = __shfl_up_sync(0xffffffffu, incl_n, o), tc = __shfl_up_sync(0xffffffffu, incl_c, o);
+        if (lane >= static_cast<uint32_t>(o)) { incl_n += tn; incl_c += tc; }
+    }
+    if (lane == 31) { warp_tiles[warp] = incl_n; warp_routes[warp] = incl_c; }
+    __syncthreads();
+    uint32_t before = 0, total_n = 0, total_c = 0;
+    for (uint32_t i = 0; i < nwarps; ++i) { if (i < warp) before += warp_tiles[i]; total_n += warp_tiles[i]; total_c += warp_routes[i]; }
+    if (tid < experts) tile_off[tid] = before + incl_n - n;
+    const uint32_t bound = routes / tile + experts;
+    if (tid == 0) {
+        tasks[0] = min(total_n, bound);
+        tasks[1] = total_c;
+        if (total_n > bound || total_c != routes) raise_error(error, TSP_ERR_INDEX);
+    }
+    for (uint32_t i = tid; i < bound; i += blockDim.x) { tasks[2 + 2 * i] = 0xffffffffu; tasks[3 + 2 * i] = 0xffffffffu; }
+    __syncthreads();
+    if (tid < experts)
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint32_t at = tile_off[tid] + i;
+            if (at < bound) { tasks[2 + 2 * at] = tid; tasks[3 + 2 * at] = i * tile; }
+        }
+}
+
+// Returns 1 when the batch does not fit the one-launch prologue (the caller then issues the separate launches).
+int launch_decode_prologue(const float* logits, uint64_t logits_stride, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t mode,
+                           int normalize, uint32_t tile, uint32_t* ids, float* weights, uint32_t* token_map, uint32_t* counts, uint32_t* tasks,
+                           const void* x16, uint64_t x16_stride, float* x32, uint64_t x32_stride, uint32_t channels, uint32_t* error, cudaStream_t st) {
+    if (tokens > kPrologueTokens || experts > kPrologueExperts || experts > static_cast<uint32_t>(kPrologueThreads)) return 1;
+    if (x16 && (channels % 4 || x16_stride % 8 || x32_stride % 16 || reinterpret_cast<uintptr_t>(x16) % 8 || reinterpret_cast<uintptr_t>(x32) % 16)) return 1;
+    const size_t smem = static_cast<size_t>(kPrologueThreads / 32) * experts * sizeof(float);
+    static thread_local SmemAttrCache configured;
+    TSP_CUDA(ensure_dynamic_smem(decode_prologue_kernel, configured, smem));
+    // conversion blocks: enough to cover the rows in one pass
+    const uint32_t conv = x16 ? min(64u, (tokens * (channels / 4) + kPrologueThreads - 1) / kPrologueThreads) : 0u;
+    TSP_CUDA(launch_pdl(decode_prologue_kernel, dim3(1 + conv), dim3(kPrologueThreads), smem, st, logits, logits_stride, tokens, experts, selected, mode,
+                        normalize, tile, ids, weights, token_map, counts, tasks, static_cast<const __half*>(x16), x16_stride, x32, x32_stride, channels, error));
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // combine: one block per token. Optional shared-router dot (FP32 tree sum), then the mixture in
 // route-rank order starting from the gated shared term (routing.cpp:49-58).
 // ---------------------------------------------------------------------------------------------
 constexpr int kCombineThreads = 256;
 
+// R16: the route rows are binary16 (the prefill path keeps them so); X16: the input rows of the shared-router dot are binary16.
+template <bool R16, bool X16>
 __global__ void __launch_bounds__(kCombineThreads)
-combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const float* __restrict__ weights,
+combine_kernel(const void* __restrict__ routed, uint64_t routed_stride, const float* __restrict__ weights,
                const float* __restrict__ shared, uint64_t shared_stride, const float* __restrict__ shared_router,
-               const float* __restrict__ x, uint64_t x_stride, float* shared_logit, uint32_t channels,
+               const void* __restrict__ x, uint64_t x_stride, float* shared_logit, uint32_t channels,
                uint32_t selected, float* __restrict__ out, uint64_t out_stride, __half* __restrict__ out16,
                uint64_t out16_stride, int vec4, uint32_t* error) {
     pdl_launch_dependents();
@@ -219,9 +317,10 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
     if (tid < selected) w_s[tid] = weights[static_cast<uint64_t>(token) * selected + tid];
     float gate = 1.f;
     if (shared_router) {
-        const float* xr = reinterpret_cast<const float*>(reinterpret_cast<const char*>(x) + token * x_stride);
+        const char* xr = reinterpret_cast<const char*>(x) + token * x_stride;
         float acc = 0.f;
-        for (uint32_t c = tid; c < channels; c += kCombineThreads) acc = fmaf(shared_router[c], xr[c], acc);
+        for (uint32_t c = tid; c < channels; c += kCombineThreads)
+            acc = fmaf(shared_router[c], X16 ? __half2float(reinterpret_cast<const __half*>(xr)[c]) : reinterpret_cast<const float*>(xr)[c], acc);
         for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if ((tid & 31) == 0) partial[tid >> 5] = acc;
         __syncthreads();
@@ -253,7 +352,14 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
             for (uint32_t r = 0; r < selected; ++r) {
                 const float wr = w_s[r];
                 if (wr != 0.f) {   // a zero weight marks a route that is not present in `routed` (expert parallelism)
-                    const float4 y = *reinterpret_cast<const float4*>(y0 + r * routed_stride + c * 4ull);
+                    float4 y;
+                    if (R16) {
+                        const uint2 h = *reinterpret_cast<const uint2*>(y0 + r * routed_stride + c * 2ull);
+                        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+                        y = make_float4(a.x, a.y, b.x, b.y);
+                    } else {
+                        y = *reinterpret_cast<const float4*>(y0 + r * routed_stride + c * 4ull);
+                    }
                     v[0] = fmaf(wr, y.x, v[0]); v[1] = fmaf(wr, y.y, v[1]); v[2] = fmaf(wr, y.z, v[2]); v[3] = fmaf(wr, y.w, v[3]);
                 }
             }
@@ -268,7 +374,10 @@ combine_kernel(const float* __restrict__ routed, uint64_t routed_stride, const f
             for (uint32_t cc = c; cc < min(c + 4, c_end); ++cc) {   // a row tail shorter than four channels, or rows that are not 16-byte aligned
                 float v = gate * sh[cc];
                 for (uint32_t r = 0; r < selected; ++r)
-                    if (w_s[r] != 0.f) v = fmaf(w_s[r], reinterpret_cast<const float*>(y0 + r * routed_stride)[cc], v);
+                    if (w_s[r] != 0.f) {
+                        const char* yr = y0 + r * routed_stride;
+                        v = fmaf(w_s[r], R16 ? __half2float(reinterpret_cast<const __half*>(yr)[cc]) : reinterpret_cast<const float*>(yr)[cc], v);
+                    }
                 bad |= !finite_f32(v);
                 if (out) o[cc] = v;
                 if (out16) reinterpret_cast<__half*>(reinterpret_cast<char*>(out16) + token * out16_stride)[cc] = __float2half_rn(v);
@@ -396,8 +505,8 @@ int launch_permute(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint3
     return TSP_OK;
 }
 
-int launch_combine(const float* routed, uint64_t routed_stride, const float* weights, const float* shared,
-                   uint64_t shared_stride, const float* shared_router, const float* x, uint64_t x_stride,
+int launch_combine(const void* routed, uint64_t routed_stride, uint32_t routed_f16, const float* weights, const float* shared,
+                   uint64_t shared_stride, const float* shared_router, const void* x, uint64_t x_stride, uint32_t x_f16,
                    float* shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected, float* out,
                    uint64_t out_stride, void* out16, uint64_t out16_stride, uint32_t* error, cudaStream_t st) {
     // about four CTAs per SM in total: 8 slices of a 2048-wide row at 64 tokens, one slice from a few hundred tokens on
@@ -405,9 +514,14 @@ int launch_combine(const float* routed, uint64_t routed_stride, const float* wei
     const uint32_t want = (4u * 148u + tokens - 1) / tokens;
     if (slices > want) slices = want;
     auto a16 = [](const void* p, uint64_t stride) { return (reinterpret_cast<uintptr_t>(p) | stride) % 16 == 0; };
-    const int vec4 = a16(routed, routed_stride) && a16(shared, shared_stride) && (!out || a16(out, out_stride)) &&
-                     (!out16 || (reinterpret_cast<uintptr_t>(out16) | out16_stride) % 8 == 0);
-    TSP_CUDA(launch_pdl(combine_kernel, dim3(tokens, slices), dim3(kCombineThreads), 0, st, routed, routed_stride, weights, shared, shared_stride, shared_router, x, x_stride, shared_logit, channels, selected, out, out_stride, static_cast<__half*>(out16), out16_stride, vec4, error));
+    const int vec4 = (routed_f16 ? (reinterpret_cast<uintptr_t>(routed) | routed_stride) % 8 == 0 : a16(routed, routed_stride)) && a16(shared, shared_stride) &&
+                     (!out || a16(out, out_stride)) && (!out16 || (reinterpret_cast<uintptr_t>(out16) | out16_stride) % 8 == 0);
+    const dim3 grid(tokens, slices), block(kCombineThreads);
+#define TSP_COMBINE(R, X) TSP_CUDA(launch_pdl(combine_kernel<R, X>, grid, block, 0, st, routed, routed_stride, weights, shared, shared_stride, shared_router, \
+                                              x, x_stride, shared_logit, channels, selected, out, out_stride, static_cast<__half*>(out16), out16_stride, vec4, error))
+    if (routed_f16) { if (x_f16) TSP_COMBINE(true, true); else TSP_COMBINE(true, false); }
+    else { if (x_f16) TSP_COMBINE(false, true); else TSP_COMBINE(false, false); }
+#undef TSP_COMBINE
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }

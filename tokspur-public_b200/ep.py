@@ -148,8 +148,8 @@ class EpLayer:
                                               self.shared_hidden.data_ptr(), H * 4, 1, e, st))
         capi.check(lib.tsp_moe_project(C.byref(w.shared_down), self.shared_hidden.data_ptr(), H * 4, 1, T, 1, None, None, None,
                                        self.shared_out.data_ptr(), Cn * 4, 0, e, st))
-        capi.check(lib.tsp_moe_combine(self.routed.data_ptr(), Cn * 4, self.weights.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
-                                       w.d_shared_router, self.x32.data_ptr(), Cn * 4, self.shared_logit.data_ptr(), T, Cn, K, None, 0,
+        capi.check(lib.tsp_moe_combine(self.routed.data_ptr(), Cn * 4, 0, self.weights.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
+                                       w.d_shared_router, self.x32.data_ptr(), Cn * 4, 0, self.shared_logit.data_ptr(), T, Cn, K, None, 0,
                                        out16.data_ptr(), out16.stride(0) * 2, e, st))
 
     def step_gathered(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
@@ -181,7 +181,7 @@ class EpLayer:
                                        self.g_tasks.data_ptr(), self.g_routed.data_ptr(), Cn * 4, 0, e, st))
         local = (self.g_ids >= self.rank * per) & (self.g_ids < (self.rank + 1) * per)
         w_local = torch.where(local, self.g_weights, torch.zeros_like(self.g_weights))   # zero weight = route not computed here
-        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, None,
+        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, 0, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, 0, None,
                                        G, Cn, K, self.g_partial.data_ptr(), Cn * 4, None, 0, e, st))
         dist.reduce_scatter_tensor(self.rs_out, self.g_partial)
         x_local = self.g_x32.data_ptr() + self.rank * T * Cn * 4
@@ -189,8 +189,8 @@ class EpLayer:
                                               self.shared_hidden.data_ptr(), H * 4, 1, e, st))
         capi.check(lib.tsp_moe_project(C.byref(w.shared_down), self.shared_hidden.data_ptr(), H * 4, 1, T, 1, None, None, None,
                                        self.shared_out.data_ptr(), Cn * 4, 0, e, st))
-        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
-                                       w.d_shared_router, x_local, Cn * 4, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
+        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, 0, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
+                                       w.d_shared_router, x_local, Cn * 4, 0, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
                                        out16.data_ptr(), out16.stride(0) * 2, e, st))
 
     def step_gathered_prefill(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
@@ -223,7 +223,7 @@ class EpLayer:
                                             self.p_offsets.data_ptr(), self.p_pos_route.data_ptr(), self.g_routed.data_ptr(), Cn * 4, e, st))
         local = (self.g_ids >= self.rank * per) & (self.g_ids < (self.rank + 1) * per)
         w_local = torch.where(local, self.g_weights, torch.zeros_like(self.g_weights))   # zero weight = route not computed here
-        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, None,
+        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, 0, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, 0, None,
                                        G, Cn, K, self.g_partial.data_ptr(), Cn * 4, None, 0, e, st))
         dist.reduce_scatter_tensor(self.rs_out, self.g_partial)
         x_local = self.g_x32.data_ptr() + self.rank * T * Cn * 4
@@ -236,8 +236,8 @@ class EpLayer:
                                                self.s_counts.data_ptr(), self.s_offsets.data_ptr(), self.s_hp.data_ptr(), H * 2, e, st))
         capi.check(lib.tsp_moe_grouped_down(C.byref(w.shared_down), self.s_hp.data_ptr(), H * 2, T, self.s_tasks.data_ptr(), self.s_counts.data_ptr(),
                                             self.s_offsets.data_ptr(), self.s_pos.data_ptr(), self.shared_out.data_ptr(), Cn * 4, e, st))
-        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
-                                       w.d_shared_router, x_local, Cn * 4, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
+        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, 0, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
+                                       w.d_shared_router, x_local, Cn * 4, 0, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
                                        out16.data_ptr(), out16.stride(0) * 2, e, st))
 
     def error_word(self) -> int:

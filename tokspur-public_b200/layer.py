@@ -122,19 +122,20 @@ class DeviceLayer:
 class Scratch:
     """Caller-owned scratch for `capacity` token rows (MoeScratch / MoeMmManyScratch)."""
 
-    def __init__(self, channels: int, hidden: int, experts: int, selected: int, capacity: int, device="cuda"):
+    def __init__(self, channels: int, hidden: int, experts: int, selected: int, capacity: int, device="cuda", decode_buffers: bool = True):
         f32, u32 = torch.float32, torch.int32  # int32 storage holds uint32 bit patterns
         z = lambda n, dt: torch.zeros(max(int(n), 1), dtype=dt, device=device)
+        big = (lambda n, dt: z(n, dt)) if decode_buffers else (lambda n, dt: z(1, dt))   # the prefill path keeps its own forms of these
         self.capacity = capacity
         self.shape = (channels, hidden, experts, selected)
         self.ids = z(capacity * selected, u32)
         self.weights = z(capacity * selected, f32)
-        self.hidden = z(capacity * selected * hidden, f32)
-        self.routed = z(capacity * selected * channels, f32)
-        self.shared_hidden = z(capacity * hidden, f32)
+        self.hidden = big(capacity * selected * hidden, f32)
+        self.routed = big(capacity * selected * channels, f32)
+        self.shared_hidden = big(capacity * hidden, f32)
         self.shared_out = z(capacity * channels, f32)
         self.shared_logit = z(capacity, f32)
-        self.x32 = z(capacity * channels, f32)
+        self.x32 = big(capacity * channels, f32)
         self.token_map = z(experts * capacity, u32)
         self.counts = z(experts, u32)
         self.tasks = z(capacity * selected + 2 * experts + 2, u32)  # covers every tile size >= 2
@@ -254,19 +255,28 @@ class PrefillScratch:
         i32, f16 = torch.int32, torch.float16
         z = lambda n, dt: torch.zeros(max(int(n), 1), dtype=dt, device=device)
         routes = capacity * selected
-        self.base = Scratch(channels, hidden, experts, selected, capacity, device)
-        self.xp = torch.zeros((routes, channels), dtype=f16, device=device)     # routed rows, permuted order
-        self.hp = torch.zeros((routes, hidden), dtype=f16, device=device)       # hidden rows, permuted order
+        self.tile = 256   # routes per task of the table the layer call builds (TSP_GROUPED_TILE)
+        self.base = Scratch(channels, hidden, experts, selected, capacity, device, decode_buffers=False)
+        self.routed16 = torch.zeros((routes, channels), dtype=f16, device=device)   # per-route expert outputs, binary16
+        self.xk = torch.zeros((capacity, channels), dtype=f16, device=device)       # input rows, tile K order
+        self.hp = torch.zeros((routes, hidden), dtype=f16, device=device)           # hidden rows, permuted position order
         self.offsets = z(experts + 1, i32)
-        self.pos_route = z(routes, i32)
-        self.tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, experts, selected, 128)), i32)
-        # the dense shared expert rides in the routed launches: its binary16 input and hidden rows in row order
-        self.s_xp = torch.zeros((capacity, channels), dtype=f16, device=device)
-        self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)
+        self.tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, experts, selected, self.tile)), i32)
+        self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)       # the shared expert's hidden rows
         base = capi.MoeScratch.from_buffer_copy(self.base.c)
-        base.d_tasks = self.tasks.data_ptr()     # tiles of 128 routes
-        self.c = capi.MoePrefillScratch(base, self.xp.data_ptr(), self.hp.data_ptr(), self.offsets.data_ptr(), self.pos_route.data_ptr(),
-                                        self.s_xp.data_ptr(), self.s_hp.data_ptr())
+        base.d_tasks = self.tasks.data_ptr()
+        base.d_routed = self.routed16.data_ptr()
+        self.c = capi.MoePrefillScratch(base, self.xk.data_ptr(), self.hp.data_ptr(), self.offsets.data_ptr(), self.s_hp.data_ptr())
+
+    def routed_rows(self, tokens: int):
+        """Per-route expert outputs [tokens*selected, channels] of the last layer call (binary16 on this path) as float32."""
+        K = self.base.shape[3]
+        return self.routed16[: tokens * K].float().cpu().numpy()
+
+    def shared_out_rows(self, tokens: int):
+        """The shared expert's output rows [tokens, channels] of the last layer call as float32."""
+        Cn = self.base.shape[0]
+        return self.base.shared_out.cpu().numpy()[: tokens * Cn].reshape(tokens, Cn)
 
 
 def moe_layer_prefill(dl, ps: PrefillScratch, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, mode: int = 0, normalize: bool = True) -> None:

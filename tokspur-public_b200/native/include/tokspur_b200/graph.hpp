@@ -84,6 +84,7 @@ private:
     struct Planar { size_t slot; uint64_t offset; PlanarMatrixShape shape; };
     const Buffer& checked(GpuView view) const;
     void require_idle() const;
+    void select_device() const;
     void check(int rc) const;
 
     uint64_t owner_;

@@ -10,20 +10,19 @@
 namespace tokspur_b200 {
 
 
-constexpr size_t kMoeMmManyViews = 15;
+constexpr size_t kMoeMmManyViews = 13;   // as many views as the reference's scratch (moe_mm_many.hpp:47-51)
 struct MoeMmManyBytes {
     std::array<uint64_t, kMoeMmManyViews> views{};
     uint64_t total = 0;
 };
 struct MoeMmManyScratch {
-    // router logits and routing results of the rows, FP32 route outputs, shared expert output and gate logit
+    // router logits and routing results of the rows, binary16 route outputs, shared expert output and gate logit
     GpuView logits, indices, weights, routed, shared_out, shared_logit;
-    // stable per-expert permutation (tiles of 128 routes), first position of every expert, route id of every position
-    GpuView token_map, counts, tasks, offsets, pos_route;
-    // binary16 rows in permuted position order: gathered inputs, hidden rows
-    GpuView xp, hp;
-    // the dense shared expert's binary16 input and hidden rows in row order (it rides in the routed launches)
-    GpuView s_xp, s_hp;
+    // stable per-expert permutation (tasks of 256 routes) and the first permuted position of every expert
+    GpuView token_map, counts, tasks, offsets;
+    // binary16 rows: the input rows in tile K order (fetched by token id), the hidden rows in permuted position order, and the
+    // dense shared expert's hidden rows in row order (it rides in the routed launches)
+    GpuView xk, hp, s_hp;
     uint32_t capacity = 0;
     [[nodiscard]] std::array<GpuView, kMoeMmManyViews> views() const;
 };

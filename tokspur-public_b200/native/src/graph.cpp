@@ -22,13 +22,15 @@ CudaGraph::CudaGraph(int device, uint64_t byte_budget) : owner_(next_owner++), d
     cuda(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreate");
     stream_ = st;
     cuda(cudaMalloc(reinterpret_cast<void**>(&error_), sizeof(uint32_t)), "error word");
-    cuda(cudaMemset(error_, 0, sizeof(uint32_t)), "error word");
+    cuda(cudaMemsetAsync(error_, 0, sizeof(uint32_t), st), "error word");
+    cuda(cudaStreamSynchronize(st), "error word");
     cudaEvent_t a, b;
     cuda(cudaEventCreate(&a), "event"); cuda(cudaEventCreate(&b), "event");
     ev0_ = a; ev1_ = b;
 }
 
 CudaGraph::~CudaGraph() {
+    cudaSetDevice(device_);
     cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
     for (auto& b : buffers_) if (b.live) cudaFree(b.ptr);
     cudaFree(error_);
@@ -37,8 +39,13 @@ CudaGraph::~CudaGraph() {
     cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
 }
 
+// one host thread may own graphs on several devices: every entry that touches the device selects this graph's own first
+void CudaGraph::select_device() const { cuda(cudaSetDevice(device_), "cudaSetDevice"); }
 void CudaGraph::require_idle() const { if (in_batch_) throw FormatError("operation is permitted only between batches"); }
-void CudaGraph::require_batch() const { if (!in_batch_) throw FormatError("no batch is open"); }
+void CudaGraph::require_batch() const {
+    if (!in_batch_) throw FormatError("no batch is open");
+    select_device();   // every operator and composed encoder passes here before its launches
+}
 void CudaGraph::check(int rc) const { if (rc != TSP_OK) throw FormatError(tsp_last_error()); }
 
 const CudaGraph::Buffer& CudaGraph::checked(GpuView v) const {
@@ -52,8 +59,12 @@ GpuView CudaGraph::zeros(uint64_t bytes, std::string label) {
     require_idle();
     if (!bytes || bytes > budget_ - live_bytes_) throw FormatError("allocation exceeds the graph's byte budget");
     void* p = nullptr;
+    select_device();
     cuda(cudaMalloc(&p, bytes), "cudaMalloc");
-    cuda(cudaMemset(p, 0, bytes), "cudaMemset");
+    // fills and copies run on the graph's own (non-blocking) stream and are waited for: a non-blocking stream does not
+    // order itself after the legacy default stream, so a fill issued there could still be in flight at the first launch
+    cuda(cudaMemsetAsync(p, 0, bytes, static_cast<cudaStream_t>(stream_)), "cudaMemset");
+    cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)), "cudaMemset");
     buffers_.push_back({p, bytes, false, true, std::move(label)});
     live_bytes_ += bytes; ++allocations_;
     return {owner_, buffers_.size() - 1, 0, bytes};
@@ -61,7 +72,8 @@ GpuView CudaGraph::zeros(uint64_t bytes, std::string label) {
 
 GpuView CudaGraph::upload(std::span<const std::byte> data, std::string label, bool immutable) {
     const auto v = zeros(data.size(), std::move(label));
-    cuda(cudaMemcpy(buffers_[v.slot].ptr, data.data(), data.size(), cudaMemcpyHostToDevice), "upload");
+    cuda(cudaMemcpyAsync(buffers_[v.slot].ptr, data.data(), data.size(), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream_)), "upload");
+    cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)), "upload");
     buffers_[v.slot].immutable = immutable;
     return v;
 }
@@ -76,20 +88,25 @@ void CudaGraph::write(GpuView dst, std::span<const std::byte> data) {
     require_idle();
     const auto& b = checked(dst);
     if (b.immutable || data.size() != dst.bytes) throw FormatError("write to an immutable buffer or size mismatch");
-    cuda(cudaMemcpy(static_cast<char*>(b.ptr) + dst.offset, data.data(), data.size(), cudaMemcpyHostToDevice), "write");
+    select_device();
+    cuda(cudaMemcpyAsync(static_cast<char*>(b.ptr) + dst.offset, data.data(), data.size(), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream_)), "write");
+    cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)), "write");
 }
 
 std::vector<std::byte> CudaGraph::read(GpuView src) const {
     require_idle();
     const auto& b = checked(src);
     std::vector<std::byte> out(src.bytes);
-    cuda(cudaMemcpy(out.data(), static_cast<const char*>(b.ptr) + src.offset, src.bytes, cudaMemcpyDeviceToHost), "read");
+    select_device();
+    cuda(cudaMemcpyAsync(out.data(), static_cast<const char*>(b.ptr) + src.offset, src.bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream_)), "read");
+    cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)), "read");
     return out;
 }
 
 void CudaGraph::release(GpuView full) {
     require_idle();
     const auto& b = checked(full);
+    select_device();
     if (full.offset || full.bytes != b.bytes) throw FormatError("release needs the full buffer view");
     for (const auto& p : planar_) if (p.slot == full.slot) throw FormatError("a registered planar matrix cannot be released");
     cuda(cudaFree(b.ptr), "cudaFree");
@@ -124,12 +141,13 @@ std::optional<PlanarMatrixShape> CudaGraph::planar_matrix_shape(GpuView matrix) 
 
 void CudaGraph::begin() {
     require_idle();
+    select_device();
     frozen_ = true;
-    in_batch_ = true;
     dispatches_ = 0;
     batch_start_ = now_ms();
     check(tsp_error_word_reset(error_, stream_));
     cuda(cudaEventRecord(static_cast<cudaEvent_t>(ev0_), static_cast<cudaStream_t>(stream_)), "event record");
+    in_batch_ = true;   // only once everything that can throw has succeeded
 }
 
 void CudaGraph::abort() {
@@ -140,10 +158,11 @@ void CudaGraph::abort() {
 
 BatchResult CudaGraph::submit() {
     require_batch();
+    in_batch_ = false;   // whatever happens below, the batch is over: a throwing submit must not leave the graph stuck in a batch
+    select_device();
     cuda(cudaEventRecord(static_cast<cudaEvent_t>(ev1_), static_cast<cudaStream_t>(stream_)), "event record");
     uint32_t word = 0;
     const int rc = tsp_error_word_read(error_, stream_, &word);
-    in_batch_ = false;
     if (rc == TSP_E_DEVICE) throw FormatError(tsp_last_error());
     check(rc);
     float gpu_ms = 0;

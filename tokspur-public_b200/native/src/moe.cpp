@@ -126,7 +126,7 @@ void encode_rows(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView
                                         shape.hidden, shape.experts, shape.selected, uint32_t(mode), normalize_selected,
                                         g.device_pointer(output, true), uint64_t(shape.channels) * 4, 0, g.error_word(), g.stream());
     if (rc != TSP_OK) throw FormatError(tsp_last_error());
-    g.count_dispatches(6);   // route, routes+tasks (2), gate-up, down, combine (the shared expert rides in the routed launches)
+    g.count_dispatches(4);   // route + permutation + tile table (one launch), gate-up, down, combine (the shared expert rides in the routed launches)
 }
 }  // namespace
 

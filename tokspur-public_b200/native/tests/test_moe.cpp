@@ -119,7 +119,7 @@ void layer(CudaGraph& g, uint32_t type, bool use_planar, MoeShape shape, uint32_
             g.begin();
             encode_moe(g, w, scratch, input, output, shape, RouterMode::softmax, true);
             const auto batch = g.submit();
-            require(batch.dispatches >= 7 && g.allocations() == allocations, "dispatch / allocation invariant");
+            require(batch.dispatches >= 5 && g.allocations() == allocations, "dispatch / allocation invariant");
             require(read<uint32_t>(g, scratch.indices) == eids, "route ids differ");
             close(read<float>(g, scratch.weights), ew.data(), K);
             close(read<float>(g, scratch.gate), act.data(), act.size());
@@ -232,7 +232,7 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
         g.begin();
         encode_moe_mm_many(g, w, scratch, {input, rows, C, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true);
         const auto batch = g.submit();
-        require(batch.dispatches >= 10 && g.allocations() == allocations, "dispatch / allocation invariant");
+        require(batch.dispatches >= 9 && g.allocations() == allocations, "dispatch / allocation invariant");
         const auto raw = g.read(output);
         double num = 0, den = 0;
         for (uint32_t r = 0; r < rows; ++r)

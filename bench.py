@@ -342,7 +342,7 @@ def run_prefill(args, local):
     def stage_pass(steps):
         """CUDA-event time of each launch of the prefill layer, issued exactly as tsp_moe_layer_prefill issues them."""
         s, st = ps.base, L.stream_ptr()
-        names = ["rows_f16k", "route", "permute", "offsets", "gate_up", "down", "combine"]
+        names = ["rows_f16k", "route", "permute", "offsets", "gather", "gate_up", "down", "combine"]
         acc = dict.fromkeys(names, 0.0)
         C2, C4, H2, E, K = CHANNELS * 2, CHANNELS * 4, HIDDEN * 2, EXPERTS, SELECTED
         for i in range(steps):
@@ -355,14 +355,15 @@ def run_prefill(args, local):
             capi.check(lib.tsp_moe_route(lg.data_ptr(), E * 4, T, E, K, 0, 1, s.ids.data_ptr(), s.weights.data_ptr(), e, st)); ev[2].record()
             capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, E, K, ps.tile, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), e, st)); ev[3].record()
             capi.check(lib.tsp_moe_route_offsets(s.counts.data_ptr(), E, ps.offsets.data_ptr(), st)); ev[4].record()
-            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up), ps.xk.data_ptr(), C2, T, K,
-                                                   s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), ps.offsets.data_ptr(),
-                                                   ps.hp.data_ptr(), H2, ps.s_hp.data_ptr(), H2, e, st)); ev[5].record()
+            capi.check(lib.tsp_moe_gather_rows16(ps.xk.data_ptr(), C2, s.token_map.data_ptr(), ps.offsets.data_ptr(), E, T, K, CHANNELS, ps.xp.data_ptr(), C2, st)); ev[5].record()
+            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up), ps.xp.data_ptr(), C2,
+                                                   ps.xk.data_ptr(), C2, T, K, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(),
+                                                   ps.offsets.data_ptr(), ps.hp.data_ptr(), H2, ps.s_hp.data_ptr(), H2, e, st)); ev[6].record()
             capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), C.byref(w.shared_down), ps.hp.data_ptr(), H2, T, K, s.token_map.data_ptr(),
                                                 s.counts.data_ptr(), ps.tasks.data_ptr(), ps.offsets.data_ptr(), ps.routed16.data_ptr(), C2, 1,
-                                                ps.s_hp.data_ptr(), H2, s.shared_out.data_ptr(), C4, e, st)); ev[6].record()
+                                                ps.s_hp.data_ptr(), H2, s.shared_out.data_ptr(), C4, e, st)); ev[7].record()
             capi.check(lib.tsp_moe_combine(ps.routed16.data_ptr(), C2, 1, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
-                                           x.data_ptr(), C2, 1, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), C2, e, st)); ev[7].record()
+                                           x.data_ptr(), C2, 1, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), C2, e, st)); ev[8].record()
             torch.cuda.synchronize()
             for k_, n in enumerate(names):
                 acc[n] += ev[k_].elapsed_time(ev[k_ + 1])
@@ -401,7 +402,7 @@ def run_prefill(args, local):
                        "l2_policy": "inputs larger than L2: 0.93 GB of weights and 0.5 GB of intermediates per step"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2},
-            "gpu_launches": 8 * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": 9 * args.steps, "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "kernel": "grouped_mma_kernel<gate-up> (routed experts + shared expert, tcgen05)", "achieved": achieved, "peak": tf_peak,
                          "unit": "TFLOP/s", "frac": achieved / tf_peak, "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_flops_per_launch": gu_flops, "launch_ms": stages["gate_up_ms"]},

@@ -100,6 +100,23 @@ int tsp_moe_route(const float* d_logits, uint64_t logits_stride_bytes, uint32_t 
                   uint32_t selected, uint32_t mode, int normalize_selected,
                   uint32_t* d_ids, float* d_weights, uint32_t* d_error, void* stream);
 
+/* The same with the router-margin audit (graph.hpp:162-172, moe_route_rows' margin buffer graph.mm:5877): d_margins[t] = logit of the
+ * last selected expert minus the best logit left out, i.e. how large a perturbation of the FP32 logits the selection of
+ * row t survives (+inf when every expert is selected, 0 for a row with a non-finite logit).
+ * tsp_router_margin_evaluate replaces `evaluate_router_margin` (graph.mm:4931-4985): it synchronises `stream`, reads the
+ * margins back and folds them into the running telemetry; a row counts as a violation when its margin is <= 2*epsilon, and
+ * *fallback (optional) tells whether this batch had any (the reference then re-projects the batch on its exact path). */
+typedef struct tsp_router_margin_telemetry {
+    float min_margin;          /* valid once total_tokens > 0 */
+    double sum_margin;
+    uint64_t total_tokens, violation_count, fallback_layers, total_layers;
+} tsp_router_margin_telemetry;
+int tsp_moe_route_audit(const float* d_logits, uint64_t logits_stride_bytes, uint32_t tokens, uint32_t experts, uint32_t selected,
+                        uint32_t mode, int normalize_selected, uint32_t* d_ids, float* d_weights, float* d_margins,
+                        uint32_t* d_error, void* stream);
+int tsp_router_margin_evaluate(const float* d_margins, uint32_t tokens, float epsilon, void* stream, tsp_router_margin_telemetry* telemetry,
+                               int* fallback);
+
 /* Replaces `graph_grouped_routes` + `graph_grouped_tasks` (grouped_mpp.metal:12-66; host
  * grouped_mm_routes, graph.mm:4608). Builds the stable per-expert token permutation:
  *   d_token_map[e*tokens + j] = token*selected + slot of the j-th (ascending) token routed to e,
@@ -190,6 +207,13 @@ int tsp_pack_planar(uint32_t type, uint32_t rows, uint32_t cols, uint32_t expert
  * shared-router projections, out[t][r] = sum_c W[r][c] x[t][c], W row-major F32 [rows x cols], FP32 accumulation. */
 int tsp_gemv_f32(const float* d_w, uint32_t rows, uint32_t cols, const float* d_x, uint64_t x_stride_bytes, uint32_t tokens,
                  float* d_out, uint64_t out_stride_bytes, uint32_t* d_error, void* stream);
+/* Replaces `moe_router_f32_window` + `moe_shared_router_rows` (graph.mm:5812, 5884): the router projection of a batch with the
+ * shared-router vector as one extra matrix row of the same pass, d_extra_out[t] = sum_c d_extra_row[c] x[t][c] (both NULL: none).
+ * From 32 token rows on this is a tiled FP32 GEMM that reads W once per 64 rows; FP32 FMA only (no reduced-precision tensor
+ * path: the ids chosen from these logits have to follow the reference's double-precision logits; tsp_moe_route_audit tells
+ * how close each row's selection is to changing). */
+int tsp_router_project(const float* d_w, uint32_t rows, uint32_t cols, const float* d_extra_row, const float* d_x, uint64_t x_stride_bytes,
+                       uint32_t tokens, float* d_out, uint64_t out_stride_bytes, float* d_extra_out, uint32_t* d_error, void* stream);
 
 /* binary16 rows -> FP32 rows (exact) and back (round to nearest even); activation edge of the layer. */
 int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride_bytes, float* d_out, uint64_t out_stride_bytes,
@@ -237,30 +261,35 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
  * (planar_moe_v3.metal:2406-2621). Weights: Q4_K Pack v3 planar; hidden a multiple of 64, channels of 256.
  *   1. tsp_moe_rows_f16k                                       binary16 copy of the input rows in the K order the tensor-core tiles use
  *   2. tsp_moe_permute(..., tile = TSP_GROUPED_TILE)           token_map / counts / tasks (tasks of 256 routes = two sub-tiles of 128)
- *   3. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e (experts+1 words)
- *   4. tsp_moe_grouped_gate_up                                 H[pos][hidden] binary16, SwiGLU applied, FP32 accumulate in tensor memory
- *   5. tsp_moe_grouped_down                                    routed[route][channel], FP32 or binary16, scattered by route id
- * The reference's gather of the routed rows (`nax_moe_gather_bf16_v3`) has no launch here: the gate-up kernel fetches each
- * token's row by id from the copy of step 1 (TMA row gather). Hidden rows (d_hp) are kept in permuted position order,
- * tokens*selected rows. Values inside each aligned run of 8 along a row of d_xk / d_hp are stored in the order
- * 0,2,1,3,4,6,5,7 (the order the dequantised weight tiles use), which only these kernels read. Operands are binary16,
- * accumulation FP32. The route id of a route is row*selected + slot; its input row is `row` of d_xk.
+ *   3. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e; experts+3 words: the last
+ *                                                              two are the item counters of steps 5 and 6, cleared here
+ *   4. tsp_moe_gather_rows16                                   the routed copy of the rows of step 1, in permuted position order
+ *   5. tsp_moe_grouped_gate_up                                 H[pos][hidden] binary16, SwiGLU applied, FP32 accumulate in tensor memory
+ *   6. tsp_moe_grouped_down                                    routed[route][channel], FP32 or binary16, scattered by route id
+ * Steps 5 and 6 hand their work items out through the counters step 3 cleared: run step 3 before every pair of them.
+ * Row buffers in permuted position order (d_xp, d_hp) hold tokens*selected rows. Values inside each aligned run of 8 along a
+ * row of d_xk / d_xp / d_hp are stored in the order 0,2,1,3,4,6,5,7 (the order the dequantised weight tiles use), which only
+ * these kernels read. Operands are binary16, accumulation FP32. The route id of a route is row*selected + slot.
  *
  * Both GEMMs take the layer's dense shared expert in the same launch when shared_* is non-NULL (same shape, encoding and
  * layout as a routed expert): its tasks cover every one of `tokens` rows in row order and follow the routed ones, as
  * `encode_moe_mm_many` runs the shared expert's dense projections right after the routed ones (moe_mm_many.cpp:189-214).
- * d_s_hp: the shared expert's binary16 hidden rows [tokens x hidden]; d_shared_out: FP32 [tokens x channels]. */
+ * It reads the rows of step 1 (d_xk) directly; d_s_hp: its binary16 hidden rows [tokens x hidden]; d_shared_out: FP32
+ * [tokens x channels]. */
 #define TSP_GROUPED_TILE 256u
 int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* d_offsets, void* stream);
 int tsp_moe_rows_f16k(const void* d_x, uint64_t x_stride_bytes, uint32_t x_dtype, uint32_t rows, uint32_t cols, void* d_xk,
                       uint64_t xk_stride_bytes, uint32_t* d_error, void* stream);
+int tsp_moe_gather_rows16(const void* d_xk, uint64_t xk_stride_bytes, const uint32_t* d_token_map, const uint32_t* d_offsets, uint32_t experts,
+                          uint32_t tokens, uint32_t selected, uint32_t cols, void* d_xp, uint64_t xp_stride_bytes, void* stream);
 int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
-                            const tsp_matrix_set* shared_up, const void* d_xk, uint64_t xk_stride_bytes, uint32_t tokens, uint32_t selected,
-                            const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, const uint32_t* d_offsets,
-                            void* d_hp, uint64_t hp_stride_bytes, void* d_s_hp, uint64_t s_hp_stride_bytes, uint32_t* d_error, void* stream);
+                            const tsp_matrix_set* shared_up, const void* d_xp, uint64_t xp_stride_bytes, const void* d_xk,
+                            uint64_t xk_stride_bytes, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                            const uint32_t* d_counts, const uint32_t* d_tasks, uint32_t* d_offsets, void* d_hp, uint64_t hp_stride_bytes,
+                            void* d_s_hp, uint64_t s_hp_stride_bytes, uint32_t* d_error, void* stream);
 int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride_bytes,
                          uint32_t tokens, uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks,
-                         const uint32_t* d_offsets, void* d_routed, uint64_t routed_stride_bytes, uint32_t routed_dtype, const void* d_s_hp,
+                         uint32_t* d_offsets, void* d_routed, uint64_t routed_stride_bytes, uint32_t routed_dtype, const void* d_s_hp,
                          uint64_t s_hp_stride_bytes, float* d_shared_out, uint64_t shared_out_stride_bytes, uint32_t* d_error, void* stream);
 
 /* Test hook: the binary16 values the grouped kernels stage for one Q4_K planar expert, [rows x cols] in natural K order.
@@ -269,7 +298,7 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* share
 int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, void* stream);
 
 /* One whole MoE FFN sub-layer at prefill size: K-ordered rows -> route -> permute (tasks of TSP_GROUPED_TILE) -> offsets ->
- * grouped gate-up + SwiGLU -> grouped down (the dense shared expert rides in both launches) -> gated mixture.
+ * routed copy of the rows -> grouped gate-up + SwiGLU -> grouped down (the dense shared expert rides in both launches) -> gated mixture.
  * Replaces `encode_moe_mm_many` after its router projection (moe_mm_many.cpp:126-220) on the `planar_nax_grouped_moe`
  * path (graph.mm:9293-9420). Weights: Q4_K Pack v3 planar, hidden a multiple of 64 and channels of 256; the shared expert
  * in the same form. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
@@ -278,11 +307,12 @@ int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, vo
  *         d_routed is used as binary16 rows [capacity*selected x channels]; d_hidden, d_shared_hidden and d_x32 are not
  *         used and may be NULL;
  *   d_xk: binary16 copy of the input rows in tile K order, [capacity x channels];
- *   d_hp: binary16 hidden rows in permuted position order, [capacity*selected x hidden];
- *   d_offsets [experts + 1]; d_s_hp: the shared expert's binary16 hidden rows, [capacity x hidden]. */
+ *   d_xp / d_hp: binary16 rows in permuted position order, [capacity*selected x channels] / [capacity*selected x hidden];
+ *   d_offsets [experts + 3]; d_s_hp: the shared expert's binary16 hidden rows, [capacity x hidden]. */
 typedef struct tsp_moe_prefill_scratch {
     tsp_moe_scratch base;
     void* d_xk;
+    void* d_xp;
     void* d_hp;
     uint32_t* d_offsets;
     void* d_s_hp;

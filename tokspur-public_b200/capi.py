@@ -41,7 +41,13 @@ class MoeScratch(C.Structure):
 
 
 class MoePrefillScratch(C.Structure):
-    _fields_ = [("base", MoeScratch), ("d_xk", C.c_void_p), ("d_hp", C.c_void_p), ("d_offsets", C.c_void_p), ("d_s_hp", C.c_void_p)]
+    _fields_ = [("base", MoeScratch), ("d_xk", C.c_void_p), ("d_xp", C.c_void_p), ("d_hp", C.c_void_p), ("d_offsets", C.c_void_p),
+                ("d_s_hp", C.c_void_p)]
+
+
+class RouterMarginTelemetry(C.Structure):
+    _fields_ = [("min_margin", C.c_float), ("sum_margin", C.c_double), ("total_tokens", C.c_uint64), ("violation_count", C.c_uint64),
+                ("fallback_layers", C.c_uint64), ("total_layers", C.c_uint64)]
 
 
 class MoeWeights(C.Structure):
@@ -71,6 +77,9 @@ SIGNATURES = {
     "tsp_synth_weights": (_i, [_u32, _u64, _u64, _u64, C.c_float, _vp, _vp]),
     "tsp_pack_planar": (_i, [_u32, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),
     "tsp_gemv_f32": (_i, [_vp, _u32, _u32, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
+    "tsp_router_project": (_i, [_vp, _u32, _u32, _vp, _vp, _u64, _u32, _vp, _u64, _vp, _vp, _vp]),
+    "tsp_moe_route_audit": (_i, [_vp, _u64, _u32, _u32, _u32, _u32, _i, _vp, _vp, _vp, _vp, _vp]),
+    "tsp_router_margin_evaluate": (_i, [_vp, _u32, C.c_float, _vp, C.POINTER(RouterMarginTelemetry), C.POINTER(_i)]),
     "tsp_rows_f16_to_f32": (_i, [_vp, _u64, _vp, _u64, _u32, _u32, _vp]),
     "tsp_moe_layer_decode": (_i, [C.POINTER(MoeWeights), C.POINTER(MoeScratch), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32,
                                   _u32, _u32, _u32, _i, _vp, _u64, _u32, _vp, _vp]),
@@ -78,7 +87,8 @@ SIGNATURES = {
                                    _u32, _u32, _u32, _i, _vp, _u64, _u32, _vp, _vp]),
     "tsp_moe_route_offsets": (_i, [_vp, _u32, _vp, _vp]),
     "tsp_moe_rows_f16k": (_i, [_vp, _u64, _u32, _u32, _u32, _vp, _u64, _vp, _vp]),
-    "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
+    "tsp_moe_gather_rows16": (_i, [_vp, _u64, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp]),
+    "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
     "tsp_moe_grouped_down": (_i, [_MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _vp, _u64, _vp, _u64, _vp, _vp]),
     "tsp_moe_staged_f16": (_i, [_MS, _u32, _vp, _vp]),
     "tsp_moe_layer_decode_static_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),

@@ -37,7 +37,7 @@ int sm_count() {
 }
 
 // launchers implemented in the kernel files
-int launch_route(const float*, uint64_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, float*, uint32_t*, cudaStream_t);
+int launch_route(const float*, uint64_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, float*, uint32_t*, cudaStream_t, float* = nullptr);
 int launch_permute(const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, int, uint32_t*, uint32_t*, uint32_t*, uint32_t*, cudaStream_t);
 int launch_combine(const void*, uint64_t, uint32_t, const float*, const float*, uint64_t, const float*, const void*, uint64_t, uint32_t, float*,
                    uint32_t, uint32_t, uint32_t, float*, uint64_t, void*, uint64_t, uint32_t*, cudaStream_t);
@@ -51,9 +51,10 @@ int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*
 int launch_route_offsets(const uint32_t*, uint32_t, uint32_t*, cudaStream_t);
 int launch_rows_f16k(const void*, uint64_t, uint32_t, uint32_t, uint32_t, void*, uint64_t, uint32_t*, cudaStream_t);
 int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, uint32_t, uint32_t, const uint32_t*,
-                   const uint32_t*, const uint32_t*, const uint32_t*, void*, uint64_t, uint32_t, uint32_t*, cudaStream_t, const GroupedShared* = nullptr);
+                   const uint32_t*, const uint32_t*, const uint32_t*, uint32_t*, void*, uint64_t, uint32_t, uint32_t*, cudaStream_t, const GroupedShared* = nullptr);
+int launch_gather_rows16(const void*, uint64_t, const uint32_t*, const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, void*, uint64_t, cudaStream_t);
 int launch_staged_f16(const uint8_t*, uint32_t, uint32_t, void*, cudaStream_t);
-int launch_gemv_f32(const float*, uint32_t, uint32_t, const float*, uint64_t, uint32_t, float*, uint64_t, uint32_t*, cudaStream_t);
+int launch_gemv_f32(const float*, uint32_t, uint32_t, const float*, const float*, uint64_t, uint32_t, float*, uint64_t, float*, uint32_t*, cudaStream_t);
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
 
@@ -161,6 +162,47 @@ int tsp_moe_route(const float* d_logits, uint64_t stride, uint32_t tokens, uint3
     TSP_REQUIRE(stride >= static_cast<uint64_t>(experts) * 4 && stride % 4 == 0, "route: logits stride too small");
     return launch_route(d_logits, stride, tokens, experts, selected, mode, normalize, d_ids, d_weights, d_error,
                         static_cast<cudaStream_t>(stream));
+}
+
+int tsp_moe_route_audit(const float* d_logits, uint64_t stride, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t mode,
+                        int normalize, uint32_t* d_ids, float* d_weights, float* d_margins, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_logits && d_ids && d_weights && d_margins, "route: null buffer");
+    TSP_REQUIRE(tokens >= 1, "route: no token rows");
+    TSP_REQUIRE(experts >= 1 && experts <= 4096 && selected >= 1 && selected <= 64 && selected <= experts && mode <= 1,
+                "route: invalid router shape/mode");
+    TSP_REQUIRE(stride >= static_cast<uint64_t>(experts) * 4 && stride % 4 == 0, "route: logits stride too small");
+    return launch_route(d_logits, stride, tokens, experts, selected, mode, normalize, d_ids, d_weights, d_error,
+                        static_cast<cudaStream_t>(stream), d_margins);
+}
+
+int tsp_router_margin_evaluate(const float* d_margins, uint32_t tokens, float epsilon, void* stream, tsp_router_margin_telemetry* t, int* fallback) {
+    TSP_REQUIRE(d_margins && t && tokens >= 1 && tokens <= (1u << 20), "margin audit: null buffer or row count out of range");
+    TSP_REQUIRE(epsilon > 0.f && epsilon < 1e30f, "margin audit: epsilon must be positive and finite");
+    static thread_local float host[4096];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float min_m = t->total_tokens ? t->min_margin : INFINITY;
+    double sum = 0;
+    uint64_t violations = 0;
+    const float threshold = 2.f * epsilon;
+    for (uint32_t at = 0; at < tokens; at += 4096) {
+        const uint32_t n = tokens - at < 4096 ? tokens - at : 4096;
+        TSP_CUDA(cudaMemcpyAsync(host, d_margins + at, n * sizeof(float), cudaMemcpyDeviceToHost, st));
+        TSP_CUDA(cudaStreamSynchronize(st));
+        for (uint32_t i = 0; i < n; ++i) {
+            const float m = host[i];
+            if (m < min_m) min_m = m;
+            sum += m;
+            if (!(m > threshold)) ++violations;
+        }
+    }
+    t->min_margin = min_m;
+    t->sum_margin += sum;
+    t->total_tokens += tokens;
+    t->violation_count += violations;
+    t->total_layers += 1;
+    if (violations) t->fallback_layers += 1;
+    if (fallback) *fallback = violations != 0;
+    return TSP_OK;
 }
 
 uint64_t tsp_moe_tasks_words(uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile) {
@@ -271,10 +313,17 @@ int tsp_pack_planar(uint32_t type, uint32_t rows, uint32_t cols, uint32_t expert
 
 int tsp_gemv_f32(const float* d_w, uint32_t rows, uint32_t cols, const float* d_x, uint64_t x_stride, uint32_t tokens, float* d_out,
                  uint64_t out_stride, uint32_t* d_error, void* stream) {
+    return tsp_router_project(d_w, rows, cols, nullptr, d_x, x_stride, tokens, d_out, out_stride, nullptr, d_error, stream);
+}
+
+int tsp_router_project(const float* d_w, uint32_t rows, uint32_t cols, const float* d_extra_row, const float* d_x, uint64_t x_stride,
+                       uint32_t tokens, float* d_out, uint64_t out_stride, float* d_extra_out, uint32_t* d_error, void* stream) {
     TSP_REQUIRE(d_w && d_x && d_out, "gemv: null buffer");
+    TSP_REQUIRE((d_extra_row != nullptr) == (d_extra_out != nullptr), "gemv: the extra row and its output go together");
     TSP_REQUIRE(rows >= 1 && cols >= 1 && tokens >= 1 && static_cast<uint64_t>(rows) * tokens < (1ull << 28), "GEMV shape mismatch");
     TSP_REQUIRE(x_stride >= cols * 4ull && x_stride % 4 == 0 && out_stride >= rows * 4ull && out_stride % 4 == 0, "gemv: row stride too small");
-    return launch_gemv_f32(d_w, rows, cols, d_x, x_stride, tokens, d_out, out_stride, d_error, static_cast<cudaStream_t>(stream));
+    return launch_gemv_f32(d_w, rows, cols, d_extra_row, d_x, x_stride, tokens, d_out, out_stride, d_extra_out, d_error,
+                           static_cast<cudaStream_t>(stream));
 }
 
 int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride, float* d_out, uint64_t out_stride, uint32_t rows,
@@ -406,33 +455,46 @@ static int check_shared_set(const tsp_matrix_set* s, const tsp_matrix_set* like,
     return TSP_OK;
 }
 
+int tsp_moe_gather_rows16(const void* d_xk, uint64_t xk_stride, const uint32_t* d_token_map, const uint32_t* d_offsets, uint32_t experts,
+                          uint32_t tokens, uint32_t selected, uint32_t cols, void* d_xp, uint64_t xp_stride, void* stream) {
+    TSP_REQUIRE(d_token_map && d_offsets && experts >= 1 && experts <= 4096 && tokens >= 1 && selected >= 1 && selected <= 64 && cols >= 8 && cols % 8 == 0,
+                "gather: null table or invalid shape");
+    TSP_REQUIRE(static_cast<uint64_t>(tokens) * selected < (1ull << 31), "gather: too many routes");
+    if (int rc = check_rows(d_xk, xk_stride, cols, 2, "gather input")) return rc;
+    if (int rc = check_rows(d_xp, xp_stride, cols, 2, "gather output")) return rc;
+    return launch_gather_rows16(d_xk, xk_stride, d_token_map, d_offsets, experts, tokens, selected, cols, d_xp, xp_stride, static_cast<cudaStream_t>(stream));
+}
+
 int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate, const tsp_matrix_set* shared_up,
-                            const void* d_xk, uint64_t xk_stride, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
-                            const uint32_t* d_counts, const uint32_t* d_tasks, const uint32_t* d_offsets, void* d_hp, uint64_t hp_stride,
-                            void* d_s_hp, uint64_t s_hp_stride, uint32_t* d_error, void* stream) {
+                            const void* d_xp, uint64_t xp_stride, const void* d_xk, uint64_t xk_stride, uint32_t tokens, uint32_t selected,
+                            const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, uint32_t* d_offsets, void* d_hp,
+                            uint64_t hp_stride, void* d_s_hp, uint64_t s_hp_stride, uint32_t* d_error, void* stream) {
     if (int rc = check_matrix(gate, "gate")) return rc;
     if (int rc = check_matrix(up, "up")) return rc;
     TSP_REQUIRE(gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
                 gate->experts == up->experts && gate->expert_stride == up->expert_stride && gate->split == up->split,
                 "gate/up matrix sets must share shape, encoding, layout and addressing");
     TSP_REQUIRE(d_token_map && d_tasks && d_counts && d_offsets && tokens >= 1 && selected >= 1 && selected <= 64, "grouped gate-up: null table or empty batch");
+    TSP_REQUIRE(static_cast<uint64_t>(tokens) * selected < (1ull << 31), "grouped gate-up: too many routes");
     TSP_REQUIRE((shared_gate != nullptr) == (shared_up != nullptr), "grouped gate-up: shared gate and up go together");
-    if (int rc = check_rows(d_xk, xk_stride, gate->cols, 2, "grouped gate-up input")) return rc;
+    if (int rc = check_rows(d_xp, xp_stride, gate->cols, 2, "grouped gate-up input")) return rc;
     if (int rc = check_rows(d_hp, hp_stride, gate->rows, 2, "grouped gate-up output")) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t* counter = d_offsets + gate->experts + 1;
     if (!shared_gate)
-        return launch_grouped(gate, up, true, d_xk, xk_stride, tokens, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets, d_hp, hp_stride, 0,
-                              d_error, st);
+        return launch_grouped(gate, up, true, d_xp, xp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets, counter,
+                              d_hp, hp_stride, 0, d_error, st);
     if (int rc = check_shared_set(shared_gate, gate, "shared gate")) return rc;
     if (int rc = check_shared_set(shared_up, gate, "shared up")) return rc;
+    if (int rc = check_rows(d_xk, xk_stride, gate->cols, 2, "shared gate-up input")) return rc;
     if (int rc = check_rows(d_s_hp, s_hp_stride, gate->rows, 2, "shared gate-up output")) return rc;
     const GroupedShared sh{shared_gate, shared_up, d_xk, xk_stride, tokens, d_s_hp, s_hp_stride};
-    return launch_grouped(gate, up, true, d_xk, xk_stride, tokens, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets, d_hp, hp_stride, 0,
-                          d_error, st, &sh);
+    return launch_grouped(gate, up, true, d_xp, xp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets, counter,
+                          d_hp, hp_stride, 0, d_error, st, &sh);
 }
 
 int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride, uint32_t tokens,
-                         uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, const uint32_t* d_offsets,
+                         uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, uint32_t* d_offsets,
                          void* d_routed, uint64_t routed_stride, uint32_t routed_dtype, const void* d_s_hp, uint64_t s_hp_stride,
                          float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
     if (int rc = check_matrix(down, "down")) return rc;
@@ -442,15 +504,16 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* share
     if (int rc = check_rows(d_hp, hp_stride, down->cols, 2, "grouped down input")) return rc;
     if (int rc = check_rows(d_routed, routed_stride, down->rows, routed_dtype ? 2 : 4, "grouped down output")) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t* counter = d_offsets + down->experts + 2;
     if (!shared_down)
         return launch_grouped(down, nullptr, false, d_hp, hp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets,
-                              d_routed, routed_stride, routed_dtype, d_error, st);
+                              counter, d_routed, routed_stride, routed_dtype, d_error, st);
     if (int rc = check_shared_set(shared_down, down, "shared down")) return rc;
     if (int rc = check_rows(d_s_hp, s_hp_stride, down->cols, 2, "shared down input")) return rc;
     if (int rc = check_rows(d_shared_out, shared_out_stride, down->rows, 4, "shared down output")) return rc;
     const GroupedShared sh{shared_down, nullptr, d_s_hp, s_hp_stride, tokens, d_shared_out, shared_out_stride};
     return launch_grouped(down, nullptr, false, d_hp, hp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets,
-                          d_routed, routed_stride, routed_dtype, d_error, st, &sh);
+                          counter, d_routed, routed_stride, routed_dtype, d_error, st, &sh);
 }
 
 int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, void* stream) {
@@ -515,14 +578,16 @@ int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratc
                 w->shared_up.experts == 1 && w->shared_down.rows == channels && w->shared_down.cols == hidden &&
                 w->shared_down.experts == 1, "prefill layer: weight shapes do not match the layer shape");
     TSP_REQUIRE(s->d_ids && s->d_weights && s->d_routed && s->d_shared_out && s->d_token_map && s->d_counts && s->d_tasks && ps->d_xk &&
-                ps->d_hp && ps->d_offsets && ps->d_s_hp, "prefill layer: incomplete scratch");
+                ps->d_xp && ps->d_hp && ps->d_offsets && ps->d_s_hp, "prefill layer: incomplete scratch");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (int rc = tsp_moe_rows_f16k(d_x, x_stride, x_dtype, tokens, channels, ps->d_xk, channels * 2ull, d_error, st)) return rc;
     if (int rc = tsp_moe_route(d_logits, logits_stride, tokens, experts, selected, mode, normalize, s->d_ids, s->d_weights, d_error, st)) return rc;
     if (int rc = tsp_moe_permute(s->d_ids, tokens, experts, selected, TSP_GROUPED_TILE, s->d_token_map, s->d_counts, s->d_tasks, d_error, st)) return rc;
     if (int rc = tsp_moe_route_offsets(s->d_counts, experts, ps->d_offsets, st)) return rc;
+    if (int rc = tsp_moe_gather_rows16(ps->d_xk, channels * 2ull, s->d_token_map, ps->d_offsets, experts, tokens, selected, channels, ps->d_xp,
+                                       channels * 2ull, st)) return rc;
     // the dense shared expert rides in both launches; the route rows are kept as binary16 (half the traffic of the mixture)
-    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xk, channels * 2ull, tokens, selected, s->d_token_map,
+    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xp, channels * 2ull, ps->d_xk, channels * 2ull, tokens, selected, s->d_token_map,
                                          s->d_counts, s->d_tasks, ps->d_offsets, ps->d_hp, hidden * 2ull, ps->d_s_hp, hidden * 2ull, d_error, st)) return rc;
     if (int rc = tsp_moe_grouped_down(&w->down, &w->shared_down, ps->d_hp, hidden * 2ull, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
                                       ps->d_offsets, s->d_routed, channels * 2ull, 1, ps->d_s_hp, hidden * 2ull, s->d_shared_out, channels * 4ull,

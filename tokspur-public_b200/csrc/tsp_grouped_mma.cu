@@ -12,9 +12,13 @@
 //   * Gate-up items hold 64 hidden units as 128 A rows: inside every group of 32 rows (one tensor-memory lane quarter)
 //     rows 0..15 are gate rows and rows 16..31 the up rows of the same 16 units, so SwiGLU is a lane exchange inside one
 //     warp and one accumulator serves both matrices (a 16 KB A stage per chunk, four stages).
-//   * Gate-up activation tiles are fetched by token id straight from the K-ordered binary16 copy of the layer input
-//     (`cp.async.bulk.tensor ... tile::gather4`: four rows per instruction, one instruction per lane of the producer warp):
-//     no routed copy of the input rows is ever written. Down activation tiles are plain tile copies of the hidden rows.
+//   * Activation tiles are plain tile copies (one `cp.async.bulk.tensor` per tile and K chunk) of rows kept in permuted
+//     position order: the routed copy of the input rows for gate-up (written once per layer by `gather_rows16_kernel`; the
+//     shared expert's tasks read the input rows themselves), the hidden rows for down. Fetching rows by token id inside the
+//     GEMM (`tile::gather4`, four rows per instruction) was measured and dropped: one such instruction costs the issuing
+//     warp about 200 cycles, so a 128-column tile needs 6400 cycles of issue per K chunk against 256 cycles of MMA.
+//   * Items (task x block of weight rows) are handed out at run time: one thread takes the next index from a global counter
+//     and publishes it to the CTA's roles through a small ring, so CTAs whose items are heavy (256 routes) simply take fewer.
 //
 // Roles inside a CTA (one persistent CTA per SM):
 //   warp 0      TMA producer of the quantised planes: Pack v3 planar code lines + 6-bit factor bytes of one super-block
@@ -79,12 +83,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
-// four rows of a 2-D tensor, named one by one, land as four consecutive box rows in shared memory (box = {bytes, 1})
-__device__ __forceinline__ void tma_gather4(void* smem_dst, const CUtensorMap* map, int c0, int r0, int r1, int r2, int r3, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-                 : "memory");
-}
 __device__ __forceinline__ void tma_load_4d_g(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
@@ -119,9 +117,8 @@ constexpr uint32_t kAStages = 4;           // dequantised weight chunks in fligh
 static_assert(kTaskRoutes == 2 * kSub, "a task is two sub-tiles");
 
 // Tensor maps of one launch: codes / factor bytes / (d, dmin) pairs with index 0 matrix A low ids, 1 A high ids, 2 B low ids,
-// 3 B high ids, 4 shared-expert A, 5 shared-expert B. Activations: gate-up uses x[0] only (row-gather map over the K-ordered
-// input rows, routed and shared tiles alike); down uses x[0..2] (tiles of 32 / 64 / 128 hidden rows) and x[3..5] (the same
-// over the shared expert's hidden rows).
+// 3 B high ids, 4 shared-expert A, 5 shared-expert B. Activations: x[0..2] = tiles of 32 / 64 / 128 rows of the routed rows in
+// permuted position order, x[3..5] the same over the shared expert's rows (row = token).
 struct alignas(64) GroupedMaps { CUtensorMap q[6], f[6], d[6], x[6]; };
 
 struct GroupedParams {
@@ -143,6 +140,7 @@ struct GroupedParams {
     void* out; uint64_t out_stride_bytes;
     uint32_t out_f16;              // down: binary16 instead of FP32 route rows
     uint32_t* error;
+    uint32_t* work_counter;        // next item index; zero when the launch starts (tsp_moe_route_offsets clears it)
     // shared-memory plan
     uint32_t off_q, q_stage_bytes, off_d, d_stage_bytes, dm_mat_bytes, off_a, off_b, nb_stages;
 };
@@ -218,6 +216,24 @@ __device__ __forceinline__ void dequant8(uint32_t a, uint32_t b, const ChunkScal
     hi = make_uint4(h[0], h[1], h[2], h[3]);
 }
 
+// Item hand-out. One thread (the weight producer) takes the next item index from the global counter and publishes it in a ring
+// of kSched slots; the other 18 warps read it (one arrival per warp frees the slot). An index >= n_items ends every role.
+constexpr uint32_t kSched = 4;
+constexpr uint32_t kSchedReaders = 2 + kDqWarps + kEpWarps;   // MMA issuer, activation producer, dequant warps, epilogue warps
+struct SchedReader {
+    uint64_t* full; uint64_t* empty; const volatile uint32_t* slot;
+    uint32_t s = 0, ph = 0;
+    // every lane of the warp calls this; returns 0xffffffff when a bounded wait expired
+    __device__ __forceinline__ uint32_t next(uint32_t lane) {
+        const bool ok = mbar_wait(&full[s], ph, 1u << 21);
+        const uint32_t item = ok ? slot[s] : 0xffffffffu;
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(&empty[s]);
+        if (++s == kSched) { s = 0; ph ^= 1u; }
+        return item;
+    }
+};
+
 // GATEUP: two weight matrices (gate, up) interleaved 16 + 16 rows per lane quarter and the SwiGLU epilogue writing binary16
 // hidden rows in permuted position order; otherwise one matrix and route rows scattered to their route ids.
 template <bool GATEUP>
@@ -230,8 +246,10 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
     // (4 stages, filled by the dequant warps) and activation tiles (nb_stages, TMA); the activation ring is deep because its
     // loads see full memory latency while a weight chunk is produced on chip
     uint64_t *qfull = bars, *qempty = bars + 2, *dfull = bars + 4, *dempty = bars + 6, *afull = bars + 8, *aempty = bars + 8 + kAStages,
-             *bfull = bars + 8 + 2 * kAStages, *bempty = bfull + kMaxBStages, *acc_full = bempty + kMaxBStages, *acc_empty = acc_full + 2;
+             *bfull = bars + 8 + 2 * kAStages, *bempty = bfull + kMaxBStages, *acc_full = bempty + kMaxBStages, *acc_empty = acc_full + 2,
+             *sfull = acc_empty + 2, *sempty = sfull + kSched;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gsm + 512);
+    volatile uint32_t* sched_slot = reinterpret_cast<volatile uint32_t*>(gsm + 528);
     const uint32_t NB = p.nb_stages;
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
     constexpr uint32_t RM = GATEUP ? 64 : 128;    // rows of ONE matrix in an item
@@ -245,6 +263,7 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         }
         for (uint32_t s = 0; s < kAStages; ++s) { mbar_init(&afull[s], kDqWarps / 2); mbar_init(&aempty[s], 1); }
         for (uint32_t s = 0; s < NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], 1); }
+        for (uint32_t s = 0; s < kSched; ++s) { mbar_init(&sfull[s], 1); mbar_init(&sempty[s], kSchedReaders); }
         mbar_fence_init();
     }
     if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }   // two sets of two 128-column accumulators
@@ -255,19 +274,26 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
     pdl_wait();   // everything above touched shared and tensor memory only
 
     const uint32_t n_tasks = p.tasks[0] + p.sh_tasks;
-    const uint64_t n_items = static_cast<uint64_t>(n_tasks) * p.row_blocks;
-    const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
-    const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t n_items = n_tasks * p.row_blocks;
     const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64
+    SchedReader sched{sfull, sempty, sched_slot};
 
     if (warp == 0) {
-        // =========================== TMA producer of the quantised planes ===========================
+        // =========================== item hand-out + TMA producer of the quantised planes ===========================
         if (lane == 0) {
             bool ok = true;
-            uint32_t qs = 0, qph = 0, ds = 0, dph = 0, cur = 0xffffffffu;
+            uint32_t qs = 0, qph = 0, ds = 0, dph = 0, cur = 0xffffffffu, ss = 0, sph = 0;
             GTask t{};
-            for (uint32_t item = item0; item < item1 && ok; ++item) {
-                if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }   // consecutive items share the task
+            while (ok) {
+                ok = gwait(&sempty[ss], sph ^ 1u);
+                if (!ok) break;
+                uint32_t item = atomicAdd(p.work_counter, 1u);
+                if (item >= n_items) item = 0xfffffffeu;            // the end marker (0xffffffff is reserved for an expired wait)
+                sched_slot[ss] = item;
+                mbar_arrive(&sfull[ss]);
+                if (++ss == kSched) { ss = 0; sph ^= 1u; }
+                if (item >= n_items) break;
+                if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }   // consecutive items often share the task
                 const uint32_t rb = item % p.row_blocks;
                 const int r0 = static_cast<int>(rb * RM);
                 const bool shared = t.expert >= p.experts;
@@ -304,67 +330,45 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         bool ok = true;
         uint32_t bs = 0, bph = 0, cur = 0xffffffffu;
         GTask t{};
-        uint32_t nsub = 1, ncols[2] = {32, 32};
-        int rows[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};   // gate-up: the four input rows this lane fetches in each sub-tile
-        for (uint32_t item = item0; item < item1 && ok; ++item) {
-            if (item / p.row_blocks != cur) {
-                cur = item / p.row_blocks; t = gtask(p, cur);
-                nsub = sub_tiles(t);
-                for (uint32_t g = 0; g < 2; ++g) {
-                    const uint32_t cnt = sub_count(t, g);
-                    ncols[g] = sub_cols(cnt);
-                    if (GATEUP) {
-#pragma unroll
-                        for (uint32_t k = 0; k < 4; ++k) {
-                            const uint32_t j = 4 * lane + k;     // column of the sub-tile
-                            uint32_t row = 0;                    // columns past the count fetch row 0: their results are never stored
-                            if (j < cnt) {
-                                const uint32_t at = t.start + g * kSub + j;
-                                row = t.expert >= p.experts ? at : p.token_map[static_cast<uint64_t>(t.expert) * p.tokens + at] / p.selected;
-                            }
-                            rows[g][k] = static_cast<int>(row);
-                        }
-                    }
-                }
-            }
-            const bool shared = t.expert >= p.experts;
-            for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
-                for (uint32_t g = 0; g < nsub && ok; ++g) {
-                    ok = __all_sync(0xffffffffu, gwait(&bempty[bs], bph ^ 1u));   // the whole warp gives up together
-                    if (!ok) break;
-                    uint8_t* dst = gsm + p.off_b + bs * 16384u;
-                    if (GATEUP) {
-                        if (lane == 0) mbar_arrive_expect_tx(&bfull[bs], ncols[g] * 128u);
-                        __syncwarp();
+        for (;;) {
+            const uint32_t item = sched.next(lane);
+            if (item >= n_items) { ok = item != 0xffffffffu; break; }
+            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }
+            if (lane == 0) {
+                const bool shared = t.expert >= p.experts;
+                const uint32_t nsub = sub_tiles(t);
+                const uint32_t nc0 = sub_cols(sub_count(t, 0)), nc1 = sub_cols(sub_count(t, 1));
+                for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
+                    for (uint32_t g = 0; g < nsub && ok; ++g) {
+                        ok = gwait(&bempty[bs], bph ^ 1u);
+                        if (!ok) break;
+                        const uint32_t nc = g ? nc1 : nc0;
+                        const CUtensorMap* xmap = &maps.x[(shared ? 3 : 0) + (nc == 32 ? 0 : (nc == 64 ? 1 : 2))];
+                        mbar_arrive_expect_tx(&bfull[bs], nc * 128u);
                         // byte coordinate: the map's element is a byte
-                        if (4 * lane < ncols[g])
-                            tma_gather4(dst + lane * 512u, &maps.x[0], static_cast<int>(c * 128), rows[g][0], rows[g][1], rows[g][2], rows[g][3], &bfull[bs]);
-                    } else if (lane == 0) {
-                        const CUtensorMap* xmap = &maps.x[(shared ? 3 : 0) + (ncols[g] == 32 ? 0 : (ncols[g] == 64 ? 1 : 2))];
-                        mbar_arrive_expect_tx(&bfull[bs], ncols[g] * 128u);
-                        tma_load_2d(dst, xmap, static_cast<int>(c * 128), static_cast<int>(t.row0 + g * kSub), &bfull[bs]);
+                        tma_load_2d(gsm + p.off_b + bs * 16384u, xmap, static_cast<int>(c * 128), static_cast<int>(t.row0 + g * kSub), &bfull[bs]);
+                        if (++bs == NB) { bs = 0; bph ^= 1u; }
                     }
-                    if (++bs == NB) { bs = 0; bph ^= 1u; }
                 }
             }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
-        if (lane == 0) {
-            bool ok = true;
-            uint32_t aph = 0, bs = 0, bph = 0, ab = 0, accph = 0, cur = 0xffffffffu;
-            GTask t{};
-            uint32_t nsub = 1, idesc[2] = {0, 0};
-            for (uint32_t item = item0; item < item1 && ok; ++item) {
-                if (item / p.row_blocks != cur) {
-                    cur = item / p.row_blocks; t = gtask(p, cur);
-                    nsub = sub_tiles(t);
-                    for (uint32_t g = 0; g < 2; ++g) idesc[g] = umma_idesc_f16(kRowsM, sub_cols(sub_count(t, g)));
-                }
+        bool ok = true;
+        uint32_t aph = 0, bs = 0, bph = 0, ab = 0, accph = 0, cur = 0xffffffffu;
+        GTask t{};
+        for (;;) {
+            const uint32_t item = sched.next(lane);
+            if (item >= n_items) { ok = item != 0xffffffffu; break; }
+            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }
+            if (lane == 0) {
+                const uint32_t nsub = sub_tiles(t);
+                const uint32_t id0 = umma_idesc_f16(kRowsM, sub_cols(sub_count(t, 0))), id1 = umma_idesc_f16(kRowsM, sub_cols(sub_count(t, 1)));
                 ok = gwait(&acc_empty[ab], accph ^ 1u);   // the epilogue has drained this accumulator set (used two items ago)
-                if (!ok) break;
-                tc_fence_after();
+                if (ok) tc_fence_after();
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
                     const uint32_t as = c & (kAStages - 1);
                     ok = gwait(&afull[as], aph);
@@ -377,7 +381,7 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                         const uint64_t bdesc = umma_desc_k128(gsm + p.off_b + bs * 16384u);
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; ++kk)
-                            umma_f16(tmem_base + ab * 256u + g * kSub, adesc + kk * 2, bdesc + kk * 2, idesc[g], (c | kk) != 0 ? 1u : 0u);
+                            umma_f16(tmem_base + ab * 256u + g * kSub, adesc + kk * 2, bdesc + kk * 2, g ? id1 : id0, (c | kk) != 0 ? 1u : 0u);
                         umma_commit(&bempty[bs]);   // the stage is free once the MMAs above have read it
                         if (++bs == NB) { bs = 0; bph ^= 1u; }
                     }
@@ -387,8 +391,10 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                 if (ok) umma_commit(&acc_full[ab]);
                 if (++ab == 2) { ab = 0; accph ^= 1u; }
             }
-            if (!ok) raise_error(p.error, TSP_ERR_TIMEOUT);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
         }
+        if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else if (warp < 2 + kDqWarps) {
         // =========================== dequantise (warps 2 .. 2 + kDqWarps - 1) ===========================
         const uint32_t dt = threadIdx.x - 64;                 // 0..255
@@ -401,7 +407,9 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         const uint32_t sw = r & 7u;                           // == line & 7
         bool ok = true;
         uint32_t qs = 0, qph = 0, ds = 0, dph = 0, aph = 0;
-        for (uint32_t item = item0; item < item1; ++item) {
+        for (;;) {
+            const uint32_t item = sched.next(lane);
+            if (item >= n_items) { ok = item != 0xffffffffu; break; }
             if (ok) ok = gwait(&dfull[ds], dph);
             const uint8_t* dmp = gsm + p.off_d + ds * p.d_stage_bytes + mat * p.dm_mat_bytes + mrow * p.nblk * 4u;
             for (uint32_t sb = 0; sb < p.nblk; ++sb) {
@@ -444,6 +452,8 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(&dempty[ds]);
             if (++ds == 2) { ds = 0; dph ^= 1u; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else {
@@ -453,8 +463,10 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         bool ok = true;
         uint32_t ab = 0, accph = 0, cur = 0xffffffffu;
         GTask t{};
-        for (uint32_t item = item0; item < item1; ++item) {
-            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }   // consecutive items share the task
+        for (;;) {
+            const uint32_t item = sched.next(lane);
+            if (item >= n_items) { ok = item != 0xffffffffu; break; }
+            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }
             const uint32_t rb = item % p.row_blocks;
             const bool shared = t.expert >= p.experts;
             const uint32_t nsub = sub_tiles(t);
@@ -473,16 +485,21 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                         }
                     }
             }
-            if (ok) ok = gwait(&acc_full[ab], accph);
+            ok = gwait(&acc_full[ab], accph);
             if (ok) {
                 tc_fence_after();
                 char* const obase = reinterpret_cast<char*>(shared ? p.sh_out : p.out);
                 const uint64_t ostride = shared ? p.sh_out_stride_bytes : p.out_stride_bytes;
                 bool bad = false;
-                for (uint32_t g = 0; g < nsub; ++g) {
+#pragma unroll
+                for (uint32_t g = 0; g < 2; ++g) {
+                    if (g >= nsub) break;
                     const uint32_t cnt = sub_count(t, g), nc = sub_cols(cnt);
                     const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * 256u + g * kSub;
-                    for (uint32_t j0 = ehalf * 32; j0 < nc && j0 < cnt; j0 += 64) {
+#pragma unroll
+                    for (uint32_t b = 0; b < 2; ++b) {
+                        const uint32_t j0 = ehalf * 32 + 64 * b;
+                        if (j0 >= nc || j0 >= cnt) break;
                         uint32_t v[32];
                         tmem_ld32(taddr + j0, v);
                         tmem_ld_wait();
@@ -510,7 +527,7 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                             }
                         } else {
                             const uint32_t wrow = rb * kRowsM + quarter * 32 + lane;   // output channel of this lane
-                            const uint32_t rq = rt[g][j0 >> 6];
+                            const uint32_t rq = rt[g][b];
                             const bool f16 = !shared && p.out_f16;
 #pragma unroll
                             for (uint32_t i = 0; i < 32; ++i) {
@@ -532,6 +549,8 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(&acc_empty[ab]);
             if (++ab == 2) { ab = 0; accph ^= 1u; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     }
@@ -600,7 +619,11 @@ __global__ void __launch_bounds__(256) route_offsets_kernel(const uint32_t* __re
         carry += total;
         __syncthreads();
     }
-    if (tid == 0) offsets[experts] = carry;
+    if (tid == 0) {
+        offsets[experts] = carry;
+        offsets[experts + 1] = 0;   // the item counters of the two grouped GEMM launches that follow
+        offsets[experts + 2] = 0;
+    }
 }
 
 // Rows (FP32 or binary16) -> binary16 rows with the K order 0,2,1,3,4,6,5,7 inside each run of 8: the B operand of the
@@ -637,6 +660,31 @@ rows_f16k_kernel(const void* __restrict__ x, uint64_t x_stride, uint32_t rows, u
     if (bad) raise_error(error, TSP_ERR_NONFINITE);
 }
 
+// Routed copy of the K-ordered input rows: position p of the permuted order belongs to the expert e with
+// offsets[e] <= p < offsets[e+1]; its route id is token_map[e*tokens + p - offsets[e]], its input row route / selected.
+__global__ void __launch_bounds__(256)
+gather_rows16_kernel(const uint4* __restrict__ xk, uint64_t xk_stride, const uint32_t* __restrict__ token_map, const uint32_t* __restrict__ offsets,
+                     uint32_t experts, uint32_t tokens, uint32_t selected, uint32_t cols, uint4* __restrict__ xp, uint64_t xp_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t pos = blockIdx.x * 4 + (threadIdx.x >> 6);
+    if (pos >= offsets[experts]) return;
+    uint32_t lo = 0, hi = experts;   // largest e with offsets[e] <= pos
+    while (hi - lo > 1) { const uint32_t mid = (lo + hi) >> 1; if (offsets[mid] <= pos) lo = mid; else hi = mid; }
+    const uint32_t row = token_map[static_cast<uint64_t>(lo) * tokens + (pos - offsets[lo])] / selected;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(xk) + static_cast<uint64_t>(row) * xk_stride);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(xp) + static_cast<uint64_t>(pos) * xp_stride);
+    for (uint32_t k8 = threadIdx.x & 63u; k8 < cols / 8; k8 += 64) dst[k8] = src[k8];
+}
+
+int launch_gather_rows16(const void* xk, uint64_t xk_stride, const uint32_t* token_map, const uint32_t* offsets, uint32_t experts, uint32_t tokens,
+                         uint32_t selected, uint32_t cols, void* xp, uint64_t xp_stride, cudaStream_t st) {
+    const uint32_t routes = tokens * selected;
+    TSP_CUDA(launch_pdl(gather_rows16_kernel, dim3((routes + 3) / 4), dim3(256), 0, st, static_cast<const uint4*>(xk), xk_stride, token_map, offsets,
+                        experts, tokens, selected, cols, static_cast<uint4*>(xp), xp_stride));
+    return TSP_OK;
+}
+
 int launch_route_offsets(const uint32_t* counts, uint32_t experts, uint32_t* offsets, cudaStream_t st) {
     TSP_CUDA(launch_pdl(route_offsets_kernel, dim3(1), dim3(256), 0, st, counts, experts, offsets));
     return TSP_OK;
@@ -664,13 +712,14 @@ static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t
 }
 
 // a/b: Q4_K Pack v3 planar matrix sets [rows x cols].
-// gate-up: act = K-ordered binary16 copy of the `act_rows` input rows (fetched by token id = route id / selected);
-//          out = binary16 hidden rows [positions x rows] in permuted position order; shared expert: sh->out rows by token.
+// gate-up: act = the routed copy of the K-ordered input rows in permuted position order (act_rows of them);
+//          out = binary16 hidden rows [positions x rows] in permuted position order; shared expert: sh->act = the K-ordered
+//          input rows by token, sh->out hidden rows by token.
 // down:    act = hidden rows in permuted position order (act_rows of them); out = route rows by route id, FP32 or binary16;
 //          shared expert: sh->act hidden rows by token, sh->out FP32 rows by token.
 int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, const void* act, uint64_t act_stride, uint32_t act_rows,
                    uint32_t tokens, uint32_t selected, const uint32_t* token_map, const uint32_t* tasks, const uint32_t* counts,
-                   const uint32_t* offsets, void* out, uint64_t out_stride, uint32_t out_f16, uint32_t* error, cudaStream_t st,
+                   const uint32_t* offsets, uint32_t* work_counter, void* out, uint64_t out_stride, uint32_t out_f16, uint32_t* error, cudaStream_t st,
                    const GroupedShared* sh) {
     if (a->type != TSP_TYPE_Q4_K || a->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "grouped GEMM: only Q4_K Pack v3 planar weights have a tensor-core kernel");
     const uint32_t rm = gateup ? 64u : 128u;
@@ -691,7 +740,7 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     for (int i = 0; i < (gateup ? 4 : 2); ++i) TSP_REQUIRE(reinterpret_cast<uintptr_t>(base[i]) % 16 == 0, "grouped GEMM: expert images must be 16-byte aligned");
     p.tokens = tokens; p.selected = selected; p.token_map = token_map;
     p.tasks = tasks; p.counts = counts; p.offsets = offsets;
-    p.out = out; p.out_stride_bytes = out_stride; p.out_f16 = out_f16; p.error = error;
+    p.out = out; p.out_stride_bytes = out_stride; p.out_f16 = out_f16; p.error = error; p.work_counter = work_counter;
     const uint32_t nmat = gateup ? 2 : 1;
     p.dm_mat_bytes = rm * nblk * 4u;                  // a multiple of 256: rm >= 64
     p.off_q = 1024;
@@ -747,18 +796,11 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     }
     for (int i = 4; i < 6; ++i) { maps.q[i] = maps.q[0]; maps.f[i] = maps.f[0]; maps.d[i] = maps.d[0]; }
     const uint32_t ns[3] = {32, 64, 128};
-    if (gateup) {   // rows fetched one by one: box of one row
+    for (int i = 0; i < 3; ++i) {
         const uint64_t dims[2] = {uint64_t(a->cols) * 2, act_rows}, strides[1] = {act_stride};
-        const uint32_t box[2] = {128, 1};
-        if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[0])) return rc;
-        for (int i = 1; i < 6; ++i) maps.x[i] = maps.x[0];
-    } else {
-        for (int i = 0; i < 3; ++i) {
-            const uint64_t dims[2] = {uint64_t(a->cols) * 2, act_rows}, strides[1] = {act_stride};
-            const uint32_t box[2] = {128, ns[i]};
-            if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[i])) return rc;
-            maps.x[3 + i] = maps.x[i];
-        }
+        const uint32_t box[2] = {128, ns[i]};
+        if (int rc = get_tensor_map_bytes(act, 2, dims, strides, box, true, &maps.x[i])) return rc;
+        maps.x[3 + i] = maps.x[i];
     }
     if (sh) {   // the layer's dense shared expert: same shape, one expert, its own rows
         const uint8_t* sa = static_cast<const uint8_t*>(sh->a->base);
@@ -771,14 +813,10 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
         p.sh_out = sh->out; p.sh_out_stride_bytes = sh->out_stride;
         if (int rc = plane_maps(sa, p.sh_merged ? 2 : 1, p.sh_merged ? sdelta : 16, 1, 16, 4)) return rc;
         if (gateup && !p.sh_merged) { if (int rc = plane_maps(sb, 1, 16, 1, 16, 5)) return rc; }
-        if (gateup) {
-            TSP_REQUIRE(sh->act == act && sh->tokens <= act_rows, "grouped gate-up: the shared expert reads the same K-ordered input rows");
-        } else {
-            for (int i = 0; i < 3; ++i) {
-                const uint64_t dims[2] = {uint64_t(a->cols) * 2, sh->tokens}, strides[1] = {sh->act_stride};
-                const uint32_t box[2] = {128, ns[i]};
-                if (int rc = get_tensor_map_bytes(sh->act, 2, dims, strides, box, true, &maps.x[3 + i])) return rc;
-            }
+        for (int i = 0; i < 3; ++i) {
+            const uint64_t dims[2] = {uint64_t(a->cols) * 2, sh->tokens}, strides[1] = {sh->act_stride};
+            const uint32_t box[2] = {128, ns[i]};
+            if (int rc = get_tensor_map_bytes(sh->act, 2, dims, strides, box, true, &maps.x[3 + i])) return rc;
         }
     }
     const int grid = sm_count();

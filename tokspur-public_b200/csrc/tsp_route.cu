@@ -21,9 +21,11 @@ __device__ __forceinline__ double sigmoid_f64(double v) {
 }
 
 // One warp routes one token row; `row` is the warp's scratch of `experts` floats in shared memory.
+// `margins` (optional): margins[token] = logit of the last selected expert - logit of the best expert left out (+inf when every
+// expert is selected): how far the selection is from changing under a perturbation of the logits.
 __device__ __forceinline__ void route_row(float* row, const float* __restrict__ src, uint32_t token, uint32_t experts, uint32_t selected,
                                           uint32_t mode, int normalize, uint32_t* __restrict__ ids, float* __restrict__ weights,
-                                          uint32_t* error, uint32_t lane) {
+                                          uint32_t* error, uint32_t lane, float* __restrict__ margins = nullptr) {
     bool bad = false;
     for (uint32_t e = lane; e < experts; e += 32) {
         const float v = src[e];
@@ -37,6 +39,7 @@ __device__ __forceinline__ void route_row(float* row, const float* __restrict__ 
     if (bad) {  // reference: FormatError("nonfinite router logit"); here: flag and publish a harmless row
         if (lane == 0) raise_error(error, TSP_ERR_NONFINITE);
         for (uint32_t r = lane; r < selected; r += 32) { out_ids[r] = r; out_w[r] = 0.f; }
+        if (margins && lane == 0) margins[token] = 0.f;
         return;
     }
     // full-softmax denominator (only when not renormalising over the selection)
@@ -68,6 +71,14 @@ __device__ __forceinline__ void route_row(float* row, const float* __restrict__ 
         if (lane == 0) { out_ids[r] = best_id; row[best_id] = -INFINITY; }
         __syncwarp();
     }
+    if (margins) {   // one more round: the best logit among the experts left out
+        float next = -INFINITY;
+        for (uint32_t e = lane; e < experts; e += 32) next = fmaxf(next, row[e]);
+        for (int o = 16; o; o >>= 1) next = fmaxf(next, __shfl_xor_sync(0xffffffffu, next, o));
+        const uint32_t last = selected - 1;
+        const float last_logit = __shfl_sync(0xffffffffu, last < 32 ? my_logit : my_logit_hi, last & 31u);
+        if (lane == 0) margins[token] = selected < experts ? last_logit - next : INFINITY;
+    }
     const double mx = row_max;
     auto activate = [&](float logit) -> double {
         const double l = logit;
@@ -89,10 +100,74 @@ __device__ __forceinline__ void route_row(float* row, const float* __restrict__ 
     if (lane + 32 < selected) out_w[lane + 32] = static_cast<float>(my_act_hi / denominator);
 }
 
+// The same selection for rows of at most 512 logits kept in registers (expert e = lane + 32 i in slot i), used where one block
+// routes a whole decode batch: about a fifth of the instructions of the shared-memory form. Same total order (value descending,
+// id ascending), same double-precision weights. Full-softmax weights without renormalisation need the serial ascending-id sum
+// and stay with route_row.
+__device__ __forceinline__ void route_row_regs(const float* __restrict__ src, uint32_t token, uint32_t experts, uint32_t selected,
+                                               uint32_t mode, uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* error,
+                                               uint32_t lane) {
+    float v[16];
+    bool bad = false;
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+        const uint32_t e = lane + 32 * i;
+        v[i] = e < experts ? src[e] : -INFINITY;
+        bad |= e < experts && !finite_f32(v[i]);
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    uint32_t* out_ids = ids + static_cast<uint64_t>(token) * selected;
+    float* out_w = weights + static_cast<uint64_t>(token) * selected;
+    if (bad) {
+        if (lane == 0) raise_error(error, TSP_ERR_NONFINITE);
+        for (uint32_t r = lane; r < selected; r += 32) { out_ids[r] = r; out_w[r] = 0.f; }
+        return;
+    }
+    float row_max = -INFINITY;
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) row_max = fmaxf(row_max, v[i]);
+    for (int o = 16; o; o >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, o));
+    float my_logit = 0.f, my_logit_hi = 0.f;
+    for (uint32_t r = 0; r < selected; ++r) {
+        float best = -INFINITY;
+        uint32_t best_id = 0xffffffffu;
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i)
+            if (v[i] > best) { best = v[i]; best_id = lane + 32 * i; }   // ascending scan keeps the lowest id on ties
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+            if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+        }
+        if ((r & 31u) == lane) { if (r < 32) my_logit = best; else my_logit_hi = best; }
+        if (lane == 0) out_ids[r] = best_id;
+        if ((best_id & 31u) == lane) {
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i) if ((best_id >> 5) == i) v[i] = -INFINITY;
+        }
+    }
+    const double mx = row_max;
+    auto activate = [&](float logit) -> double {
+        const double l = logit;
+        if (mode == TSP_ROUTER_SOFTMAX) return exp(l - mx);
+        return exp(-softplus_f64(-l) + softplus_f64(-mx));
+    };
+    const double my_act = lane < selected ? activate(my_logit) : 0.0;
+    const double my_act_hi = lane + 32 < selected ? activate(my_logit_hi) : 0.0;
+    double denominator = my_act + my_act_hi;   // renormalised over the selection: same butterfly order as route_row
+    for (int o = 16; o; o >>= 1) denominator += __shfl_xor_sync(0xffffffffu, denominator, o);
+    if (!(denominator > 0) || isinf(denominator)) {
+        if (lane == 0) raise_error(error, TSP_ERR_NONFINITE);
+        denominator = 1.0;
+    }
+    if (lane < selected) out_w[lane] = static_cast<float>(my_act / denominator);
+    if (lane + 32 < selected) out_w[lane + 32] = static_cast<float>(my_act_hi / denominator);
+}
+
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t tokens, uint32_t experts,
              uint32_t selected, uint32_t mode, int normalize, uint32_t* __restrict__ ids,
-             float* __restrict__ weights, uint32_t* error) {
+             float* __restrict__ weights, uint32_t* error, float* __restrict__ margins) {
     pdl_launch_dependents();
     pdl_wait();
 
@@ -101,7 +176,8 @@ route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t t
     const uint32_t token = blockIdx.x * (blockDim.x >> 5) + warp;
     if (token >= tokens) return;
     const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + token * stride_bytes);
-    route_row(route_smem + warp * experts, src, token, experts, selected, mode, normalize, ids, weights, error, lane);
+    if (experts <= 512 && normalize && !margins) route_row_regs(src, token, experts, selected, mode, ids, weights, error, lane);
+    else route_row(route_smem + warp * experts, src, token, experts, selected, mode, normalize, ids, weights, error, lane, margins);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -230,9 +306,11 @@ decode_prologue_kernel(const float* __restrict__ logits, uint64_t logits_stride,
     __shared__ uint32_t warp_tiles[32], warp_routes[32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
     for (uint32_t e = tid; e < experts; e += blockDim.x) mask[e] = 0ull;
-    for (uint32_t t = warp; t < tokens; t += nwarps)
-        route_row(pro_smem + warp * experts, reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + t * logits_stride), t, experts,
-                  selected, mode, normalize, ids, weights, error, lane);
+    for (uint32_t t = warp; t < tokens; t += nwarps) {
+        const float* row = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + t * logits_stride);
+        if (experts <= 512 && normalize) route_row_regs(row, t, experts, selected, mode, ids, weights, error, lane);
+        else route_row(pro_smem + warp * experts, row, t, experts, selected, mode, normalize, ids, weights, error, lane);
+    }
     __syncthreads();   // ids are complete (and visible to this block)
     const uint32_t routes = tokens * selected;
     for (uint32_t i = tid; i < routes; i += blockDim.x) {
@@ -410,10 +488,94 @@ gemv_f32_kernel(const float* __restrict__ w, uint32_t rows, uint32_t cols, const
     }
 }
 
-int launch_gemv_f32(const float* w, uint32_t rows, uint32_t cols, const float* x, uint64_t x_stride, uint32_t tokens, float* out,
-                    uint64_t out_stride, uint32_t* error, cudaStream_t st) {
+// ---------------------------------------------------------------------------------------------
+// F32 router projection for batches: logits[t][e] = sum_c W[e][c] * x[t][c] as a register-tiled FP32 GEMM (FP32 FMA only: the
+// ids chosen from these logits must follow the reference's double-precision logits, so no reduced-precision tensor path).
+// W is read once per tile of 64 token rows. Every output is one FMA chain in ascending c, i.e. the plain sequential FP32 dot
+// product. An optional extra row `extra` (the shared-router vector) is projected in the same pass into `extra_out[t]`.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRgM = 64, kRgN = 128, kRgK = 16, kRgThreads = 256;
+
+__global__ void __launch_bounds__(kRgThreads)
+router_gemm_kernel(const float* __restrict__ w, uint32_t rows, uint32_t cols, const float* __restrict__ extra, const float* __restrict__ x,
+                   uint64_t x_stride, uint32_t tokens, float* __restrict__ out, uint64_t out_stride, float* __restrict__ extra_out, uint32_t* error) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float xs[kRgK][kRgM + 4];
+    __shared__ float ws[kRgK][kRgN + 4];
+    const uint32_t tid = threadIdx.x;
+    const uint32_t t0 = blockIdx.y * kRgM, r0 = blockIdx.x * kRgN;
+    const uint32_t all_rows = rows + (extra ? 1u : 0u);
+    // thread -> 4 token rows x 8 matrix rows of the tile
+    const uint32_t tm = (tid >> 4) * 4, tn = (tid & 15u) * 8;
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    // loaders: x tile = 64 rows x 16 columns = 256 float4 (one per thread); w tile = 128 x 16 = 512 float4 (two per thread)
+    const uint32_t lx_row = tid >> 2, lx_c4 = (tid & 3u) * 4;
+    for (uint32_t k0 = 0; k0 < cols; k0 += kRgK) {
+        {
+            const uint32_t t = t0 + lx_row, c = k0 + lx_c4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < tokens) {
+                const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(x) + t * x_stride) + c;
+                if (c + 4 <= cols && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) v = *reinterpret_cast<const float4*>(src);
+                else { if (c < cols) v.x = src[0]; if (c + 1 < cols) v.y = src[1]; if (c + 2 < cols) v.z = src[2]; if (c + 3 < cols) v.w = src[3]; }
+            }
+            xs[lx_c4][lx_row] = v.x; xs[lx_c4 + 1][lx_row] = v.y; xs[lx_c4 + 2][lx_row] = v.z; xs[lx_c4 + 3][lx_row] = v.w;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t lr = (tid >> 2) + h * 64, r = r0 + lr, c = k0 + lx_c4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < all_rows) {
+                const float* src = (r < rows ? w + static_cast<uint64_t>(r) * cols : extra) + c;
+                if (c + 4 <= cols && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) v = *reinterpret_cast<const float4*>(src);
+                else { if (c < cols) v.x = src[0]; if (c + 1 < cols) v.y = src[1]; if (c + 2 < cols) v.z = src[2]; if (c + 3 < cols) v.w = src[3]; }
+            }
+            ws[lx_c4][lr] = v.x; ws[lx_c4 + 1][lr] = v.y; ws[lx_c4 + 2][lr] = v.z; ws[lx_c4 + 3][lr] = v.w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kRgK; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&xs[k][tm]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&ws[k][tn]), b1 = *reinterpret_cast<const float4*>(&ws[k][tn + 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(bv[j], av[i], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t t = t0 + tm + i;
+        if (t >= tokens) continue;
+        float* orow = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + t * out_stride);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t r = r0 + tn + j;
+            if (r < rows) { bad |= !finite_f32(acc[i][j]); orow[r] = acc[i][j]; }
+            else if (r == rows && extra) { bad |= !finite_f32(acc[i][j]); extra_out[t] = acc[i][j]; }
+        }
+    }
+    if (bad) raise_error(error, TSP_ERR_NONFINITE);
+}
+
+int launch_gemv_f32(const float* w, uint32_t rows, uint32_t cols, const float* extra, const float* x, uint64_t x_stride, uint32_t tokens, float* out,
+                    uint64_t out_stride, float* extra_out, uint32_t* error, cudaStream_t st) {
+    if (tokens >= 32) {   // batches: W is read once per 64 token rows
+        const dim3 grid((rows + (extra ? 1 : 0) + kRgN - 1) / kRgN, (tokens + kRgM - 1) / kRgM);
+        TSP_CUDA(launch_pdl(router_gemm_kernel, grid, dim3(kRgThreads), 0, st, w, rows, cols, extra, x, x_stride, tokens, out, out_stride, extra_out, error));
+        return TSP_OK;
+    }
     const uint64_t warps = static_cast<uint64_t>(rows) * tokens;
     TSP_CUDA(launch_pdl(gemv_f32_kernel, dim3(static_cast<unsigned>((warps + 7) / 8)), dim3(256), 0, st, w, rows, cols, x, x_stride, tokens, out, out_stride, error));
+    if (extra) TSP_CUDA(launch_pdl(gemv_f32_kernel, dim3(static_cast<unsigned>((tokens + 7) / 8)), dim3(256), 0, st, extra, 1u, cols, x, x_stride, tokens, extra_out, sizeof(float), error));
     return TSP_OK;
 }
 
@@ -487,10 +649,10 @@ __global__ void dequant_q8_kernel(const uint8_t* __restrict__ expert, uint32_t l
 // host launchers (called by the C ABI layer in tsp_api.cu after validation)
 // ---------------------------------------------------------------------------------------------
 int launch_route(const float* logits, uint64_t stride, uint32_t tokens, uint32_t experts, uint32_t selected,
-                 uint32_t mode, int normalize, uint32_t* ids, float* weights, uint32_t* error, cudaStream_t st) {
+                 uint32_t mode, int normalize, uint32_t* ids, float* weights, uint32_t* error, cudaStream_t st, float* margins) {
     const uint32_t warps = experts > 3072 ? 2 : kRouteWarps;
     const uint32_t blocks = (tokens + warps - 1) / warps;
-    TSP_CUDA(launch_pdl(route_kernel, dim3(blocks), dim3(warps * 32), warps * experts * sizeof(float), st, logits, stride, tokens, experts, selected, mode, normalize, ids, weights, error));
+    TSP_CUDA(launch_pdl(route_kernel, dim3(blocks), dim3(warps * 32), warps * experts * sizeof(float), st, logits, stride, tokens, experts, selected, mode, normalize, ids, weights, error, margins));
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }

@@ -259,14 +259,15 @@ class PrefillScratch:
         self.base = Scratch(channels, hidden, experts, selected, capacity, device, decode_buffers=False)
         self.routed16 = torch.zeros((routes, channels), dtype=f16, device=device)   # per-route expert outputs, binary16
         self.xk = torch.zeros((capacity, channels), dtype=f16, device=device)       # input rows, tile K order
+        self.xp = torch.zeros((routes, channels), dtype=f16, device=device)         # their routed copy, permuted position order
         self.hp = torch.zeros((routes, hidden), dtype=f16, device=device)           # hidden rows, permuted position order
-        self.offsets = z(experts + 1, i32)
+        self.offsets = z(experts + 3, i32)   # first position of every expert, total, and the two item counters
         self.tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, experts, selected, self.tile)), i32)
         self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)       # the shared expert's hidden rows
         base = capi.MoeScratch.from_buffer_copy(self.base.c)
         base.d_tasks = self.tasks.data_ptr()
         base.d_routed = self.routed16.data_ptr()
-        self.c = capi.MoePrefillScratch(base, self.xk.data_ptr(), self.hp.data_ptr(), self.offsets.data_ptr(), self.s_hp.data_ptr())
+        self.c = capi.MoePrefillScratch(base, self.xk.data_ptr(), self.xp.data_ptr(), self.hp.data_ptr(), self.offsets.data_ptr(), self.s_hp.data_ptr())
 
     def routed_rows(self, tokens: int):
         """Per-route expert outputs [tokens*selected, channels] of the last layer call (binary16 on this path) as float32."""

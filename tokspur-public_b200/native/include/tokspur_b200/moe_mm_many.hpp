@@ -10,7 +10,7 @@
 namespace tokspur_b200 {
 
 
-constexpr size_t kMoeMmManyViews = 13;   // as many views as the reference's scratch (moe_mm_many.hpp:47-51)
+constexpr size_t kMoeMmManyViews = 14;
 struct MoeMmManyBytes {
     std::array<uint64_t, kMoeMmManyViews> views{};
     uint64_t total = 0;
@@ -20,9 +20,9 @@ struct MoeMmManyScratch {
     GpuView logits, indices, weights, routed, shared_out, shared_logit;
     // stable per-expert permutation (tasks of 256 routes) and the first permuted position of every expert
     GpuView token_map, counts, tasks, offsets;
-    // binary16 rows: the input rows in tile K order (fetched by token id), the hidden rows in permuted position order, and the
+    // binary16 rows: the input rows in tile K order, their routed copy and the hidden rows in permuted position order, and the
     // dense shared expert's hidden rows in row order (it rides in the routed launches)
-    GpuView xk, hp, s_hp;
+    GpuView xk, xp, hp, s_hp;
     uint32_t capacity = 0;
     [[nodiscard]] std::array<GpuView, kMoeMmManyViews> views() const;
 };

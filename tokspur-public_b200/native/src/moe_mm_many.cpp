@@ -10,7 +10,7 @@ void need(bool ok, const char* what) { if (!ok) throw FormatError(what); }
 }
 
 std::array<GpuView, kMoeMmManyViews> MoeMmManyScratch::views() const {
-    return {logits, indices, weights, routed, shared_out, shared_logit, token_map, counts, tasks, offsets, xk, hp, s_hp};
+    return {logits, indices, weights, routed, shared_out, shared_logit, token_map, counts, tasks, offsets, xk, xp, hp, s_hp};
 }
 
 MoeMmManyBytes moe_mm_many_bytes(MoeShape s, uint32_t capacity) {
@@ -18,10 +18,10 @@ MoeMmManyBytes moe_mm_many_bytes(MoeShape s, uint32_t capacity) {
     const uint64_t n = capacity, r = n * s.selected;
     MoeMmManyBytes b;
     // logits, indices, weights, binary16 route rows, FP32 shared-expert rows, gate logits | token_map, counts, tasks, offsets |
-    // binary16 input rows in tile K order, binary16 hidden rows in permuted order, the shared expert's binary16 hidden rows
+    // binary16 input rows in tile K order, their routed copy and the hidden rows in permuted order, the shared expert's hidden rows
     b.views = {n * s.experts * 4, r * 4, r * 4, r * s.channels * 2, n * s.channels * 4, n * 4,
                uint64_t(s.experts) * n * 4, uint64_t(s.experts) * 4, tsp_moe_tasks_words(capacity, s.experts, s.selected, TSP_GROUPED_TILE) * 4,
-               (uint64_t(s.experts) + 1) * 4, n * s.channels * 2, r * s.hidden * 2, n * s.hidden * 2};
+               (uint64_t(s.experts) + 3) * 4, n * s.channels * 2, r * s.channels * 2, r * s.hidden * 2, n * s.hidden * 2};
     for (const auto v : b.views) b.total += v;
     return b;
 }
@@ -36,7 +36,7 @@ MoeMmManyScratch allocate_moe_mm_many_scratch(CudaGraph& graph, MoeShape shape, 
         for (size_t i = 0; i < made; ++i) graph.release(v[i]);
         throw;
     }
-    return {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12], capacity};
+    return {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12], v[13], capacity};
 }
 
 void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scratch) {
@@ -95,7 +95,7 @@ void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratc
     ps.base.d_shared_out = f32p(s.shared_out); ps.base.d_shared_logit = f32p(s.shared_logit);
     ps.base.d_token_map = u32p(s.token_map); ps.base.d_counts = u32p(s.counts); ps.base.d_tasks = u32p(s.tasks);
     ps.base.capacity = s.capacity;
-    ps.d_xk = g.device_pointer(s.xk, true); ps.d_hp = g.device_pointer(s.hp, true);
+    ps.d_xk = g.device_pointer(s.xk, true); ps.d_xp = g.device_pointer(s.xp, true); ps.d_hp = g.device_pointer(s.hp, true);
     ps.d_offsets = u32p(s.offsets); ps.d_s_hp = g.device_pointer(s.s_hp, true);
 
     const uint32_t n = input.rows;
@@ -104,7 +104,7 @@ void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratc
                                          uint64_t(shape.experts) * 4, n, shape.channels, shape.hidden, shape.experts, shape.selected, uint32_t(mode),
                                          normalize_selected, g.device_pointer(output.view, true), output.stride_bytes, 0, g.error_word(), g.stream());
     if (rc != TSP_OK) throw FormatError(tsp_last_error());
-    g.count_dispatches(8);   // K-ordered rows, route, routes, tasks, offsets, gate-up, down (the shared expert rides in both), mixture
+    g.count_dispatches(9);   // K-ordered rows, route, routes, tasks, offsets, routed copy, gate-up, down (the shared expert rides in both), mixture
 }
 
 }  // namespace tokspur_b200

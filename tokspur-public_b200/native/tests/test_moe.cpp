@@ -232,7 +232,7 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
         g.begin();
         encode_moe_mm_many(g, w, scratch, {input, rows, C, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true);
         const auto batch = g.submit();
-        require(batch.dispatches >= 9 && g.allocations() == allocations, "dispatch / allocation invariant");
+        require(batch.dispatches >= 10 && g.allocations() == allocations, "dispatch / allocation invariant");
         const auto raw = g.read(output);
         double num = 0, den = 0;
         for (uint32_t r = 0; r < rows; ++r)

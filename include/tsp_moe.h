@@ -191,6 +191,16 @@ int tsp_moe_combine(const void* d_routed, uint64_t routed_stride_bytes, uint32_t
                     float* d_out, uint64_t out_stride_bytes, void* d_out_f16, uint64_t out_f16_stride_bytes,
                     uint32_t* d_error, void* stream);
 
+/* Hyper-connection residual read / write, the steps either side of the FFN sub-layer in every layer (mtp_head.cpp:206-208).
+ * Replace `MetalGraph::residual_read` / `residual_write` (graph.hpp:1056-1058; CPU: gated_residual_reference's last step and
+ * residual_write_reference, operators.cpp:79-96), batched over `tokens` rows; all buffers FP32, row-major, densely packed:
+ *   read:  output[t][c] = sum_b normalized[t][b][c] * sigmoid(scores[t][b][c]) / branches,  scales[t][b] = 2 sigmoid(inject_logits[t][b] / branches)
+ *   write: destination[t][b][c] = streams[t][b][c] + scales[t][b] * output[t][c]   (destination may be the streams themselves) */
+int tsp_residual_read(const float* d_normalized, const float* d_scores, const float* d_inject_logits, uint32_t branches, uint32_t channels,
+                      uint32_t tokens, float* d_output, float* d_scales, uint32_t* d_error, void* stream);
+int tsp_residual_write(const float* d_streams, const float* d_output, const float* d_scales, uint32_t branches, uint32_t channels,
+                       uint32_t tokens, float* d_destination, uint32_t* d_error, void* stream);
+
 /* ---- data preparation (device side) ----------------------------------------------------------------
  * tsp_synth_weights: seeded N(0, sigma) values quantised to GGUF blocks of `type` (Q4_K, Q8_0) or written
  * as FP32 (type F32, `blocks` = element count), `blocks` blocks starting at stream block `first_block`

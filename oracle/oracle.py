@@ -84,6 +84,8 @@ class Oracle:
         f("gemv_f32").argtypes = [C.c_uint32, u8p, C.c_size_t, C.c_uint32, C.c_uint32, f32p, f64p]
         f("route").argtypes = [f64p, C.c_size_t, C.c_size_t, C.c_uint32, C.c_int, u32p, f64p]
         f("mixture").argtypes = [f64p, f64p, C.c_size_t, f64p, C.c_size_t, C.c_double, f64p]
+        f("gated_residual").argtypes = [f64p, f64p, f64p, f64p, f64p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_double, f64p, f64p, f64p, f64p, f64p]
+        f("residual_write").argtypes = [f64p, f64p, f64p, C.c_size_t, C.c_size_t, f64p]
         if reference:
             L.ref_moe_layer.argtypes = [C.POINTER(_Layer), f32p, f32p, C.c_uint32, f64p, u32p, C.c_uint32]
         else:
@@ -158,6 +160,27 @@ class Oracle:
         out = np.empty(shared.size, dtype=np.float64)
         self._ok(self._f("mixture")(_ptr(experts, f64p), _ptr(weights, f64p), weights.size, _ptr(shared, f64p), shared.size,
                                     float(shared_logit), _ptr(out, f64p)))
+        return out
+
+    def gated_residual(self, streams, gains, down, up, inject, rank: int, epsilon: float, intermediates: bool = False):
+        """Hyper-connection residual read: streams/gains [branches, channels], down [rank, branches*channels],
+        up [branches*channels, rank], inject [branches, branches*channels] -> (input [channels], write_scales [branches])."""
+        streams = np.ascontiguousarray(streams, dtype=np.float64)
+        branches, channels = streams.shape
+        a = [np.ascontiguousarray(v, dtype=np.float64) for v in (gains, down, up, inject)]
+        inp, scales = np.empty(channels), np.empty(branches)
+        norm, scores, logits = (np.empty((branches, channels)), np.empty((branches, channels)), np.empty(branches)) if intermediates and not self.reference else (None, None, None)
+        self._ok(self._f("gated_residual")(_ptr(streams, f64p), _ptr(a[0], f64p), _ptr(a[1], f64p), _ptr(a[2], f64p), _ptr(a[3], f64p), branches,
+                                           channels, rank, float(epsilon), _ptr(inp, f64p), _ptr(scales, f64p), _ptr(norm, f64p),
+                                           _ptr(scores, f64p), _ptr(logits, f64p)))
+        return (inp, scales, norm, scores, logits) if intermediates else (inp, scales)
+
+    def residual_write(self, streams, output, scales):
+        streams = np.ascontiguousarray(streams, dtype=np.float64)
+        branches, channels = streams.shape
+        out = np.empty_like(streams)
+        self._ok(self._f("residual_write")(_ptr(streams, f64p), _ptr(np.ascontiguousarray(output, dtype=np.float64), f64p),
+                                           _ptr(np.ascontiguousarray(scales, dtype=np.float64), f64p), branches, channels, _ptr(out, f64p)))
         return out
 
     # ---- planar (port only) ----

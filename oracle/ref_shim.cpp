@@ -127,4 +127,23 @@ int ref_moe_layer(const RefLayer* L, const float* x, const float* logits, uint32
     return 0;
 }
 
+int ref_gated_residual(const double* streams, const double* gains, const double* down, const double* up, const double* inject,
+                       size_t branches, size_t channels, size_t rank, double epsilon, double* input, double* write_scales,
+                       double*, double*, double*) {
+    return guarded([&] {
+        const size_t width = branches * channels;
+        const auto r = gated_residual_reference({streams, width}, {gains, width}, {down, rank * width}, {up, width * rank}, {inject, branches * width},
+                                                branches, channels, rank, epsilon);
+        std::memcpy(input, r.input.data(), sizeof(double) * channels);
+        std::memcpy(write_scales, r.write_scales.data(), sizeof(double) * branches);
+    });
+}
+
+int ref_residual_write(const double* streams, const double* output, const double* scales, size_t branches, size_t channels, double* out) {
+    return guarded([&] {
+        const auto r = residual_write_reference({streams, branches * channels}, {output, channels}, {scales, branches});
+        std::memcpy(out, r.data(), sizeof(double) * r.size());
+    });
+}
+
 } // extern "C"

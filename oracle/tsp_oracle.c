@@ -202,6 +202,62 @@ int tso_route(const double* logits, size_t experts, size_t selected, uint32_t mo
 }
 
 /* routing.cpp:42-61 */
+/* operators.cpp:42-58 (grouped RMS), 60-89 (gated residual read), 91-96 (residual write) */
+int tso_gated_residual(const double* streams, const double* gains, const double* down, const double* up, const double* inject,
+                       size_t branches, size_t channels, size_t rank, double epsilon, double* input, double* write_scales,
+                       double* normalized_out, double* scores_out, double* inject_out) {
+    if (!branches || branches > 64 || !channels || channels > 65536 || !rank || rank > 4096 || !(epsilon > 0) || !isfinite(epsilon))
+        return TSO_E_SHAPE;
+    const size_t width = branches * channels;
+    double* normalized = (double*)malloc(sizeof(double) * width);
+    double* bottleneck = (double*)malloc(sizeof(double) * rank);
+    if (!normalized || !bottleneck) { free(normalized); free(bottleneck); return TSO_E_SHAPE; }
+    int rc = TSO_OK;
+    for (size_t i = 0; i < width && !rc; ++i) if (!isfinite(streams[i]) || !isfinite(gains[i])) rc = TSO_E_NONFINITE;
+    for (size_t g = 0; g < width && !rc; g += channels) {
+        double squared = 0;
+        for (size_t i = 0; i < channels; ++i) squared += streams[g + i] * streams[g + i];
+        if (!isfinite(squared)) { rc = TSO_E_NONFINITE; break; }
+        const double inverse = 1 / sqrt(squared / (double)channels + epsilon);
+        for (size_t i = 0; i < channels; ++i) normalized[g + i] = streams[g + i] * inverse * gains[g + i];
+    }
+    for (size_t r = 0; r < rank && !rc; ++r) {
+        double acc = 0;
+        for (size_t i = 0; i < width; ++i) acc += down[r * width + i] * normalized[i];
+        bottleneck[r] = tso_silu(acc / (double)branches);
+    }
+    for (size_t i = 0; i < channels && !rc; ++i) input[i] = 0;
+    for (size_t b = 0; b < branches && !rc; ++b) {
+        double scale = 0;
+        for (size_t i = 0; i < width; ++i) scale += inject[b * width + i] * normalized[i];
+        if (inject_out) inject_out[b] = scale;
+        write_scales[b] = 2 * tso_sigmoid(scale / (double)branches);
+    }
+    for (size_t b = 0; b < branches && !rc; ++b)
+        for (size_t c = 0; c < channels; ++c) {
+            const size_t position = b * channels + c;
+            double score = 0;
+            for (size_t r = 0; r < rank; ++r) score += up[position * rank + r] * bottleneck[r];
+            if (scores_out) scores_out[position] = score;
+            input[c] += normalized[position] * tso_sigmoid(score) / (double)branches;
+        }
+    for (size_t i = 0; i < channels && !rc; ++i) if (!isfinite(input[i])) rc = TSO_E_NONFINITE;
+    if (normalized_out && !rc) memcpy(normalized_out, normalized, sizeof(double) * width);
+    free(normalized); free(bottleneck);
+    return rc;
+}
+
+int tso_residual_write(const double* streams, const double* output, const double* scales, size_t branches, size_t channels, double* out) {
+    if (!branches || !channels) return TSO_E_SHAPE;
+    for (size_t b = 0; b < branches; ++b)
+        for (size_t c = 0; c < channels; ++c) {
+            const double v = streams[b * channels + c] + scales[b] * output[c];
+            if (!isfinite(v)) return TSO_E_NONFINITE;
+            out[b * channels + c] = v;
+        }
+    return TSO_OK;
+}
+
 int tso_mixture(const double* experts, const double* weights, size_t selected, const double* shared,
                 size_t channels, double shared_logit, double* out) {
     if (!channels || channels > 65536 || !selected || selected > 64) return TSO_E_SHAPE;

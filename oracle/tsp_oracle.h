@@ -54,6 +54,17 @@ double tso_sigmoid(double v);
 double tso_silu(double v);
 double tso_softplus(double v);
 
+/* Hyper-connection residual read / write around the FFN sub-layer (operators.cpp:42-96).
+ * tso_gated_residual: streams [branches x channels] -> grouped RMS (per branch, gains elementwise) -> bottleneck
+ * silu(down . normalized / branches) [rank] -> scores = up . bottleneck [branches x channels], inject logits =
+ * inject . normalized [branches]; input[c] = sum_b normalized[b][c] * sigmoid(scores[b][c]) / branches,
+ * write_scales[b] = 2 * sigmoid(inject_logit[b] / branches). The intermediates are returned too (any may be NULL).
+ * tso_residual_write: out[b][c] = streams[b][c] + scales[b] * output[c]. */
+int tso_gated_residual(const double* streams, const double* gains, const double* down, const double* up, const double* inject,
+                       size_t branches, size_t channels, size_t rank, double epsilon, double* input, double* write_scales,
+                       double* normalized, double* scores, double* inject_logits);
+int tso_residual_write(const double* streams, const double* output, const double* scales, size_t branches, size_t channels, double* out);
+
 /* Top-k by descending logit, ties to the lower id; mode 0 softmax, 1 sigmoid (routing.cpp:11-40). */
 int tso_route(const double* logits, size_t experts, size_t selected, uint32_t mode, int normalize_selected,
               uint32_t* indices, double* weights);

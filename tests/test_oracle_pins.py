@@ -261,3 +261,15 @@ def test_port_equals_reference_layer(oracle, ref_oracle):
     a, st = oracle.moe_layer(layer, x, logits, threads=2, stages=True)
     b, sb = ref_oracle.moe_layer(layer, x, logits, threads=2, stages=True)
     assert np.array_equal(a, b) and np.array_equal(st["indices"], sb["indices"])
+
+
+def test_residual_read_write_port_equals_reference(oracle, ref_oracle):
+    """operators.cpp:60-96: the port's gated residual read and residual write against the reference's own functions, bit for bit."""
+    rng = np.random.default_rng(5)
+    for B, Cn, R in ((4, 96, 8), (1, 7, 1), (3, 256, 16)):
+        st, g = rng.normal(size=(B, Cn)), rng.normal(size=(B, Cn))
+        dn, up, inj = rng.normal(size=(R, B * Cn)) * 0.1, rng.normal(size=(B * Cn, R)), rng.normal(size=(B, B * Cn)) * 0.1
+        a, b = oracle.gated_residual(st, g, dn, up, inj, R, 1e-6), ref_oracle.gated_residual(st, g, dn, up, inj, R, 1e-6)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+        out = rng.normal(size=Cn)
+        assert np.array_equal(oracle.residual_write(st, out, a[1]), ref_oracle.residual_write(st, out, a[1]))

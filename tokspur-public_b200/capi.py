@@ -80,6 +80,8 @@ SIGNATURES = {
     "tsp_router_project": (_i, [_vp, _u32, _u32, _vp, _vp, _u64, _u32, _vp, _u64, _vp, _vp, _vp]),
     "tsp_moe_route_audit": (_i, [_vp, _u64, _u32, _u32, _u32, _u32, _i, _vp, _vp, _vp, _vp, _vp]),
     "tsp_router_margin_evaluate": (_i, [_vp, _u32, C.c_float, _vp, C.POINTER(RouterMarginTelemetry), C.POINTER(_i)]),
+    "tsp_residual_read": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp]),
+    "tsp_residual_write": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp]),
     "tsp_rows_f16_to_f32": (_i, [_vp, _u64, _vp, _u64, _u32, _u32, _vp]),
     "tsp_moe_layer_decode": (_i, [C.POINTER(MoeWeights), C.POINTER(MoeScratch), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32,
                                   _u32, _u32, _u32, _i, _vp, _u64, _u32, _vp, _vp]),

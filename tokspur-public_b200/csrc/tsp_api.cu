@@ -54,6 +54,8 @@ int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const voi
                    const uint32_t*, const uint32_t*, const uint32_t*, uint32_t*, void*, uint64_t, uint32_t, uint32_t*, cudaStream_t, const GroupedShared* = nullptr);
 int launch_gather_rows16(const void*, uint64_t, const uint32_t*, const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, void*, uint64_t, cudaStream_t);
 int launch_staged_f16(const uint8_t*, uint32_t, uint32_t, void*, cudaStream_t);
+int launch_residual_read(const float*, const float*, const float*, uint32_t, uint32_t, uint32_t, float*, float*, uint32_t*, cudaStream_t);
+int launch_residual_write(const float*, const float*, const float*, uint32_t, uint32_t, uint32_t, float*, uint32_t*, cudaStream_t);
 int launch_gemv_f32(const float*, uint32_t, uint32_t, const float*, const float*, uint64_t, uint32_t, float*, uint64_t, float*, uint32_t*, cudaStream_t);
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
@@ -291,6 +293,26 @@ int tsp_moe_combine(const void* d_routed, uint64_t routed_stride, uint32_t route
     return launch_combine(d_routed, routed_stride, routed_dtype, d_weights, d_shared, shared_stride, d_shared_router, d_x, x_stride, x_dtype,
                           d_shared_logit, tokens, channels, selected, d_out, out_stride, d_out_f16, out_f16_stride, d_error,
                           static_cast<cudaStream_t>(stream));
+}
+
+int tsp_residual_read(const float* d_normalized, const float* d_scores, const float* d_inject_logits, uint32_t branches, uint32_t channels,
+                      uint32_t tokens, float* d_output, float* d_scales, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_normalized && d_scores && d_inject_logits && d_output && d_scales, "residual read: null buffer");
+    TSP_REQUIRE(branches >= 1 && branches <= 64 && channels >= 1 && channels <= 65536 && tokens >= 1 && tokens <= 65535, "residual read shape mismatch");
+    const uint64_t wide = static_cast<uint64_t>(tokens) * branches * channels * 4, narrow = static_cast<uint64_t>(tokens) * channels * 4;
+    TSP_REQUIRE(!overlap(d_output, narrow, d_normalized, wide) && !overlap(d_output, narrow, d_scores, wide), "residual read: output overlaps an input");
+    return launch_residual_read(d_normalized, d_scores, d_inject_logits, branches, channels, tokens, d_output, d_scales, d_error,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int tsp_residual_write(const float* d_streams, const float* d_output, const float* d_scales, uint32_t branches, uint32_t channels, uint32_t tokens,
+                       float* d_destination, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_streams && d_output && d_scales && d_destination, "residual write: null buffer");
+    TSP_REQUIRE(branches >= 1 && branches <= 64 && channels >= 1 && channels <= 65536 && tokens >= 1 && tokens <= 65535, "residual write shape mismatch");
+    const uint64_t wide = static_cast<uint64_t>(tokens) * branches * channels * 4, narrow = static_cast<uint64_t>(tokens) * channels * 4;
+    // in place over the streams is allowed (each element is read once, then written); the FFN output must not be clobbered
+    TSP_REQUIRE(!overlap(d_destination, wide, d_output, narrow), "residual write: destination overlaps the FFN output");
+    return launch_residual_write(d_streams, d_output, d_scales, branches, channels, tokens, d_destination, d_error, static_cast<cudaStream_t>(stream));
 }
 
 int tsp_synth_weights(uint32_t type, uint64_t seed, uint64_t first_block, uint64_t blocks, float sigma, void* d_out, void* stream) {

@@ -9,6 +9,11 @@
 //   * A dequantised weight chunk is used for BOTH sub-tiles of a task before it is released: an expert with many routes
 //     pays the dequantisation once per 256 routes. Each sub-tile has its own accumulator (128 columns of tensor memory);
 //     two such pairs are double-buffered (512 columns), so the epilogue of an item runs under the MMAs of the next.
+//   * One pipeline stage = one K chunk = {dequantised weight chunk, activation tile of sub-tile 0, of sub-tile 1}, filled by
+//     the dequant warps and the activation producer, emptied by ONE commit. The thread that issues the MMAs does one wait,
+//     four MMAs (N = 256 when both sub-tiles are full: their tiles are adjacent) and one commit per chunk: with separate rings
+//     for weights and activations its waits and commits, not the tensor pipe, set the pace (measured: removing the MMAs
+//     altogether made the launch only 30 % shorter).
 //   * Gate-up items hold 64 hidden units as 128 A rows: inside every group of 32 rows (one tensor-memory lane quarter)
 //     rows 0..15 are gate rows and rows 16..31 the up rows of the same 16 units, so SwiGLU is a lane exchange inside one
 //     warp and one accumulator serves both matrices (a 16 KB A stage per chunk, four stages).
@@ -109,11 +114,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
 constexpr uint32_t kDqWarps = 8;           // dequantise warps: 256 threads = 128 weight rows x {even, odd} K chunks
 constexpr uint32_t kEpWarps = 8;           // epilogue warps: two per tensor-memory lane quarter, taking the 32-column batches in turn
 constexpr uint32_t kGWarps = 3 + kDqWarps + kEpWarps;   // weight producer, MMA, dequant warps, activation producer, epilogue warps
-constexpr uint32_t kMaxBStages = 8;
 constexpr uint32_t kTaskRoutes = TSP_GROUPED_TILE;      // routes per task (two sub-tiles)
 constexpr uint32_t kSub = 128;             // token columns per sub-tile (N extent at most)
 constexpr uint32_t kRowsM = 128;           // A rows per item (M)
-constexpr uint32_t kAStages = 4;           // dequantised weight chunks in flight: the four K chunks of a super-block
+constexpr uint32_t kStages = 3;            // K chunks in flight: a stage holds the dequantised weight chunk AND the activation tiles it meets
+constexpr uint32_t kStageBytes = 3 * 16384;   // [A: 128 rows x 128 B][B sub-tile 0][B sub-tile 1]
+constexpr uint32_t kEpTileBytes = 32 * 144;   // per epilogue warp: 32 token rows of 32 FP32 values, rows padded by 16 bytes
 static_assert(kTaskRoutes == 2 * kSub, "a task is two sub-tiles");
 
 // Tensor maps of one launch: codes / factor bytes / (d, dmin) pairs with index 0 matrix A low ids, 1 A high ids, 2 B low ids,
@@ -142,7 +148,7 @@ struct GroupedParams {
     uint32_t* error;
     uint32_t* work_counter;        // next item index; zero when the launch starts (tsp_moe_route_offsets clears it)
     // shared-memory plan
-    uint32_t off_q, q_stage_bytes, off_d, d_stage_bytes, dm_mat_bytes, off_a, off_b, nb_stages;
+    uint32_t off_q, q_stage_bytes, off_d, d_stage_bytes, dm_mat_bytes, off_st, off_ep;
 };
 
 // bounded wait with a short limit: a stalled pipeline ends in tens of milliseconds, never hangs
@@ -216,21 +222,26 @@ __device__ __forceinline__ void dequant8(uint32_t a, uint32_t b, const ChunkScal
     hi = make_uint4(h[0], h[1], h[2], h[3]);
 }
 
-// Item hand-out. One thread (the weight producer) takes the next item index from the global counter and publishes it in a ring
-// of kSched slots; the other 18 warps read it (one arrival per warp frees the slot). An index >= n_items ends every role.
+// Item hand-out. One thread (the weight producer) takes the next item index from the global counter, looks its task up and
+// publishes both in a ring of kSched slots; the other 18 warps read it (one arrival per warp frees the slot). An index
+// >= n_items ends every role.
 constexpr uint32_t kSched = 4;
 constexpr uint32_t kSchedReaders = 2 + kDqWarps + kEpWarps;   // MMA issuer, activation producer, dequant warps, epilogue warps
+struct SchedItem { uint32_t item; GTask t; };
 struct SchedReader {
-    uint64_t* full; uint64_t* empty; const volatile uint32_t* slot;
+    uint64_t* full; uint64_t* empty; const volatile uint32_t* slots;   // 8 words per slot: item, expert, start, count, row0
     uint32_t s = 0, ph = 0;
-    // every lane of the warp calls this; returns 0xffffffff when a bounded wait expired
-    __device__ __forceinline__ uint32_t next(uint32_t lane) {
+    // every lane of the warp calls this; item 0xffffffff when a bounded wait expired
+    __device__ __forceinline__ SchedItem next(uint32_t lane) {
         const bool ok = mbar_wait(&full[s], ph, 1u << 21);
-        const uint32_t item = ok ? slot[s] : 0xffffffffu;
+        SchedItem it;
+        const volatile uint32_t* w = slots + s * 8;
+        it.item = ok ? w[0] : 0xffffffffu;
+        it.t.expert = w[1]; it.t.start = w[2]; it.t.count = w[3]; it.t.row0 = w[4];
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(&empty[s]);
         if (++s == kSched) { s = 0; ph ^= 1u; }
-        return item;
+        return it;
     }
 };
 
@@ -242,15 +253,12 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
     extern __shared__ uint8_t gsm_raw[];
     uint8_t* gsm = gsm_raw + ((1024u - (smem_u32(gsm_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(gsm);
-    // rings: quantised super-blocks (2 stages, TMA), the (d, dmin) pairs of an item (2 stages, TMA), dequantised weight chunks
-    // (4 stages, filled by the dequant warps) and activation tiles (nb_stages, TMA); the activation ring is deep because its
-    // loads see full memory latency while a weight chunk is produced on chip
-    uint64_t *qfull = bars, *qempty = bars + 2, *dfull = bars + 4, *dempty = bars + 6, *afull = bars + 8, *aempty = bars + 8 + kAStages,
-             *bfull = bars + 8 + 2 * kAStages, *bempty = bfull + kMaxBStages, *acc_full = bempty + kMaxBStages, *acc_empty = acc_full + 2,
-             *sfull = acc_empty + 2, *sempty = sfull + kSched;
+    // rings: quantised super-blocks (2 stages, TMA), the (d, dmin) pairs of an item (2 stages, TMA), the K-chunk stages
+    // (weight chunk from the dequant warps + activation tiles by TMA) and the item hand-out
+    uint64_t *qfull = bars, *qempty = bars + 2, *dfull = bars + 4, *dempty = bars + 6, *full = bars + 8, *empty = full + kStages,
+             *acc_full = empty + kStages, *acc_empty = acc_full + 2, *sfull = acc_empty + 2, *sempty = sfull + kSched;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gsm + 512);
-    volatile uint32_t* sched_slot = reinterpret_cast<volatile uint32_t*>(gsm + 528);
-    const uint32_t NB = p.nb_stages;
+    volatile uint32_t* sched_slots = reinterpret_cast<volatile uint32_t*>(gsm + 640);   // kSched x 8 words
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
     constexpr uint32_t RM = GATEUP ? 64 : 128;    // rows of ONE matrix in an item
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -261,8 +269,8 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
             mbar_init(&dfull[s], 1); mbar_init(&dempty[s], kDqWarps);
             mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kEpWarps);
         }
-        for (uint32_t s = 0; s < kAStages; ++s) { mbar_init(&afull[s], kDqWarps / 2); mbar_init(&aempty[s], 1); }
-        for (uint32_t s = 0; s < NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], 1); }
+        // a stage is full when the four dequant warps that own its chunk have written it and the activation bytes have landed
+        for (uint32_t s = 0; s < kStages; ++s) { mbar_init(&full[s], kDqWarps / 2 + 1); mbar_init(&empty[s], 1); }
         for (uint32_t s = 0; s < kSched; ++s) { mbar_init(&sfull[s], 1); mbar_init(&sempty[s], kSchedReaders); }
         mbar_fence_init();
     }
@@ -275,8 +283,9 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
 
     const uint32_t n_tasks = p.tasks[0] + p.sh_tasks;
     const uint32_t n_items = n_tasks * p.row_blocks;
-    const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64
-    SchedReader sched{sfull, sempty, sched_slot};
+    const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64 (a multiple of 4: chunk parity is the same in every item)
+    SchedReader sched{sfull, sempty, sched_slots};
+    uint8_t* const stages = gsm + p.off_st;
 
     if (warp == 0) {
         // =========================== item hand-out + TMA producer of the quantised planes ===========================
@@ -289,11 +298,12 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                 if (!ok) break;
                 uint32_t item = atomicAdd(p.work_counter, 1u);
                 if (item >= n_items) item = 0xfffffffeu;            // the end marker (0xffffffff is reserved for an expired wait)
-                sched_slot[ss] = item;
+                else if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }
+                volatile uint32_t* w = sched_slots + ss * 8;
+                w[0] = item; w[1] = t.expert; w[2] = t.start; w[3] = t.count; w[4] = t.row0;
                 mbar_arrive(&sfull[ss]);
                 if (++ss == kSched) { ss = 0; sph ^= 1u; }
                 if (item >= n_items) break;
-                if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }   // consecutive items often share the task
                 const uint32_t rb = item % p.row_blocks;
                 const int r0 = static_cast<int>(rb * RM);
                 const bool shared = t.expert >= p.experts;
@@ -328,71 +338,73 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
     } else if (warp == 2 + kDqWarps) {
         // =========================== activation-tile producer ===========================
         bool ok = true;
-        uint32_t bs = 0, bph = 0, cur = 0xffffffffu;
-        GTask t{};
+        uint32_t st = 0, sph = 0;   // stage of the next chunk and its phase
         for (;;) {
-            const uint32_t item = sched.next(lane);
-            if (item >= n_items) { ok = item != 0xffffffffu; break; }
-            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }
+            const SchedItem it = sched.next(lane);
+            if (it.item >= n_items) { ok = it.item != 0xffffffffu; break; }
             if (lane == 0) {
+                const GTask& t = it.t;
                 const bool shared = t.expert >= p.experts;
                 const uint32_t nsub = sub_tiles(t);
                 const uint32_t nc0 = sub_cols(sub_count(t, 0)), nc1 = sub_cols(sub_count(t, 1));
+                const CUtensorMap* map0 = &maps.x[(shared ? 3 : 0) + (nc0 == 32 ? 0 : (nc0 == 64 ? 1 : 2))];
+                const CUtensorMap* map1 = &maps.x[(shared ? 3 : 0) + (nc1 == 32 ? 0 : (nc1 == 64 ? 1 : 2))];
+                const uint32_t bytes = (nc0 + (nsub > 1 ? nc1 : 0u)) * 128u;
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
-                    for (uint32_t g = 0; g < nsub && ok; ++g) {
-                        ok = gwait(&bempty[bs], bph ^ 1u);
-                        if (!ok) break;
-                        const uint32_t nc = g ? nc1 : nc0;
-                        const CUtensorMap* xmap = &maps.x[(shared ? 3 : 0) + (nc == 32 ? 0 : (nc == 64 ? 1 : 2))];
-                        mbar_arrive_expect_tx(&bfull[bs], nc * 128u);
-                        // byte coordinate: the map's element is a byte
-                        tma_load_2d(gsm + p.off_b + bs * 16384u, xmap, static_cast<int>(c * 128), static_cast<int>(t.row0 + g * kSub), &bfull[bs]);
-                        if (++bs == NB) { bs = 0; bph ^= 1u; }
-                    }
+                    ok = gwait(&empty[st], sph ^ 1u);
+                    if (!ok) break;
+                    uint8_t* b0 = stages + st * kStageBytes + 16384u;
+                    mbar_arrive_expect_tx(&full[st], bytes);
+                    // byte coordinate: the map's element is a byte
+                    tma_load_2d(b0, map0, static_cast<int>(c * 128), static_cast<int>(t.row0), &full[st]);
+                    if (nsub > 1) tma_load_2d(b0 + 16384u, map1, static_cast<int>(c * 128), static_cast<int>(t.row0 + kSub), &full[st]);
+                    if (++st == kStages) { st = 0; sph ^= 1u; }
                 }
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            st = __shfl_sync(0xffffffffu, st, 0); sph = __shfl_sync(0xffffffffu, sph, 0);
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         bool ok = true;
-        uint32_t aph = 0, bs = 0, bph = 0, ab = 0, accph = 0, cur = 0xffffffffu;
-        GTask t{};
+        uint32_t st = 0, sph = 0, ab = 0, accph = 0;
         for (;;) {
-            const uint32_t item = sched.next(lane);
-            if (item >= n_items) { ok = item != 0xffffffffu; break; }
-            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }
+            const SchedItem it = sched.next(lane);
+            if (it.item >= n_items) { ok = it.item != 0xffffffffu; break; }
             if (lane == 0) {
+                const GTask& t = it.t;
                 const uint32_t nsub = sub_tiles(t);
-                const uint32_t id0 = umma_idesc_f16(kRowsM, sub_cols(sub_count(t, 0))), id1 = umma_idesc_f16(kRowsM, sub_cols(sub_count(t, 1)));
+                const uint32_t nc0 = sub_cols(sub_count(t, 0)), nc1 = sub_cols(sub_count(t, 1));
+                const bool wide = nsub > 1 && nc1 == kSub;          // both sub-tiles full: one N = 256 instruction over the adjacent tiles
+                const uint32_t id0 = umma_idesc_f16(kRowsM, wide ? 256u : nc0), id1 = umma_idesc_f16(kRowsM, nc1);
+                const uint32_t dcol = tmem_base + ab * 256u;
                 ok = gwait(&acc_empty[ab], accph ^ 1u);   // the epilogue has drained this accumulator set (used two items ago)
                 if (ok) tc_fence_after();
                 for (uint32_t c = 0; c < chunks_per_item && ok; ++c) {
-                    const uint32_t as = c & (kAStages - 1);
-                    ok = gwait(&afull[as], aph);
+                    ok = gwait(&full[st], sph);
                     if (!ok) break;
-                    const uint64_t adesc = umma_desc_k128(gsm + p.off_a + as * 16384u);
-                    for (uint32_t g = 0; g < nsub && ok; ++g) {
-                        ok = gwait(&bfull[bs], bph);
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint64_t bdesc = umma_desc_k128(gsm + p.off_b + bs * 16384u);
+                    tc_fence_after();
+                    const uint8_t* sbase = stages + st * kStageBytes;
+                    const uint64_t adesc = umma_desc_k128(sbase), bdesc = umma_desc_k128(sbase + 16384u);
 #pragma unroll
-                        for (uint32_t kk = 0; kk < 4; ++kk)
-                            umma_f16(tmem_base + ab * 256u + g * kSub, adesc + kk * 2, bdesc + kk * 2, g ? id1 : id0, (c | kk) != 0 ? 1u : 0u);
-                        umma_commit(&bempty[bs]);   // the stage is free once the MMAs above have read it
-                        if (++bs == NB) { bs = 0; bph ^= 1u; }
+                    for (uint32_t kk = 0; kk < 4; ++kk) umma_f16(dcol, adesc + kk * 2, bdesc + kk * 2, id0, (c | kk) != 0 ? 1u : 0u);
+                    if (nsub > 1 && !wide) {
+                        const uint64_t bdesc1 = umma_desc_k128(sbase + 32768u);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; ++kk) umma_f16(dcol + kSub, adesc + kk * 2, bdesc1 + kk * 2, id1, (c | kk) != 0 ? 1u : 0u);
                     }
-                    if (ok) umma_commit(&aempty[as]);
-                    if (as == kAStages - 1) aph ^= 1u;
+                    umma_commit(&empty[st]);   // the stage is free once the MMAs above have read it
+                    if (++st == kStages) { st = 0; sph ^= 1u; }
                 }
                 if (ok) umma_commit(&acc_full[ab]);
                 if (++ab == 2) { ab = 0; accph ^= 1u; }
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            st = __shfl_sync(0xffffffffu, st, 0); sph = __shfl_sync(0xffffffffu, sph, 0);
+            ab = __shfl_sync(0xffffffffu, ab, 0); accph = __shfl_sync(0xffffffffu, accph, 0);
         }
         if (!ok && lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT);
     } else if (warp < 2 + kDqWarps) {
@@ -406,10 +418,12 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         const uint32_t line = mat * RM + mrow;
         const uint32_t sw = r & 7u;                           // == line & 7
         bool ok = true;
-        uint32_t qs = 0, qph = 0, ds = 0, dph = 0, aph = 0;
+        uint32_t qs = 0, qph = 0, ds = 0, dph = 0;
+        // this thread's chunks are every other one of the launch-wide chunk sequence: its stage advances by two (mod kStages)
+        uint32_t st = half % kStages, sph = 0;
         for (;;) {
-            const uint32_t item = sched.next(lane);
-            if (item >= n_items) { ok = item != 0xffffffffu; break; }
+            const SchedItem it = sched.next(lane);
+            if (it.item >= n_items) { ok = it.item != 0xffffffffu; break; }
             if (ok) ok = gwait(&dfull[ds], dph);
             const uint8_t* dmp = gsm + p.off_d + ds * p.d_stage_bytes + mat * p.dm_mat_bytes + mrow * p.nblk * 4u;
             for (uint32_t sb = 0; sb < p.nblk; ++sb) {
@@ -423,13 +437,13 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                 const uint8_t* codes = q + line * 128u;
 #pragma unroll
                 for (uint32_t pp = 0; pp < 2; ++pp) {
-                    const uint32_t c = 2 * pp + half;          // chunk of the super-block = stage of the A ring
-                    if (ok) ok = gwait(&aempty[c], aph ^ 1u);  // the MMAs that read this stage one super-block ago are done
+                    const uint32_t c = 2 * pp + half;          // chunk of the super-block
+                    if (ok) ok = gwait(&empty[st], sph ^ 1u);  // the MMAs that read this stage kStages chunks ago are done
                     if (ok) {
                         const ChunkScale cs = chunk_scale(dd, dmn, pp ? fac.y : fac.x, pp ? fac.w : fac.z, 2u * half);
                         const uint4 w0 = *reinterpret_cast<const uint4*>(codes + (((2 * c) ^ sw) << 4));
                         const uint4 w1 = *reinterpret_cast<const uint4*>(codes + (((2 * c + 1) ^ sw) << 4));
-                        uint8_t* arow = gsm + p.off_a + c * 16384u + r * 128u;
+                        uint8_t* arow = stages + st * kStageBytes + r * 128u;
                         uint4 lo, hi;
                         dequant8(w0.x, w0.y, cs, lo, hi);
                         *reinterpret_cast<uint4*>(arow + ((0u ^ sw) << 4)) = lo; *reinterpret_cast<uint4*>(arow + ((4u ^ sw) << 4)) = hi;
@@ -442,9 +456,10 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                         fence_async_smem();   // make the generic-proxy writes visible to the tensor-core (async) proxy
                     }
                     __syncwarp();
-                    if (lane == 0 && ok) mbar_arrive(&afull[c]);
+                    if (lane == 0 && ok) mbar_arrive(&full[st]);
+                    st += 2;
+                    if (st >= kStages) { st -= kStages; sph ^= 1u; }
                 }
-                aph ^= 1u;
                 __syncwarp();
                 if (lane == 0 && ok) mbar_arrive(&qempty[qs]);
                 if (++qs == 2) { qs = 0; qph ^= 1u; }
@@ -460,14 +475,14 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         // =========================== epilogue (the last kEpWarps warps) ===========================
         const uint32_t quarter = warp & 3u;                   // tensor-memory lane quarter this warp may read
         const uint32_t ehalf = (warp - (3 + kDqWarps)) >> 2;  // the two warps of a quarter take the 32-column batches in turn
+        uint8_t* const etile = gsm + p.off_ep + (warp - (3 + kDqWarps)) * kEpTileBytes;   // this warp's transposition tile
         bool ok = true;
-        uint32_t ab = 0, accph = 0, cur = 0xffffffffu;
-        GTask t{};
+        uint32_t ab = 0, accph = 0;
         for (;;) {
-            const uint32_t item = sched.next(lane);
-            if (item >= n_items) { ok = item != 0xffffffffu; break; }
-            if (item / p.row_blocks != cur) { cur = item / p.row_blocks; t = gtask(p, cur); }
-            const uint32_t rb = item % p.row_blocks;
+            const SchedItem it = sched.next(lane);
+            if (it.item >= n_items) { ok = it.item != 0xffffffffu; break; }
+            const GTask& t = it.t;
+            const uint32_t rb = it.item % p.row_blocks;
             const bool shared = t.expert >= p.experts;
             const uint32_t nsub = sub_tiles(t);
             // down: route ids of this lane's columns (column j0 + lane of each batch), fetched before the wait so their latency
@@ -503,43 +518,66 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                         uint32_t v[32];
                         tmem_ld32(taddr + j0, v);
                         tmem_ld_wait();
+                        // Results leave through a per-warp transposition tile in shared memory: the accumulators arrive with a lane per
+                        // weight row and a register per token column, the output rows want a lane per token and a run of weight rows
+                        // (16-byte stores instead of one 2-byte store per value).
                         if constexpr (GATEUP) {
                             // lanes 0..15 hold the gate rows of 16 hidden units, lanes 16..31 the up rows of the same units. For each
                             // pair of token columns the low half-warp finishes the even column and the high half-warp the odd one.
-                            const uint32_t unit = rb * 64u + quarter * 16u + (lane & 15u);
                             // hidden rows feed the down GEMM as its K operand: same order inside each run of 8 as the weight tiles use
-                            const uint32_t hcol = (unit & ~7u) | ((unit & 4u) | ((unit & 1u) << 1) | ((unit & 2u) >> 1));
-                            char* hrow = obase + static_cast<uint64_t>(t.row0 + g * kSub) * ostride + hcol * 2;
+                            const uint32_t u16 = lane & 15u;
+                            const uint32_t hpos = (u16 & 8u) | ((u16 & 4u) | ((u16 & 1u) << 1) | ((u16 & 2u) >> 1));
                             const bool low = lane < 16;
+                            constexpr uint32_t RS = 48;   // tile row: 16 units x 2 B, padded so that the 16-byte reads below spread over the banks
 #pragma unroll
                             for (uint32_t a = 0; a < 16; ++a) {
                                 const uint32_t send = low ? v[2 * a + 1] : v[2 * a];
                                 const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
                                 const float gv = __uint_as_float(low ? v[2 * a] : recv);
                                 const float uv = __uint_as_float(low ? recv : v[2 * a + 1]);
-                                const uint32_t j = j0 + 2 * a + (low ? 0u : 1u);
-                                if (j < cnt) {
-                                    const float val = __fdividef(gv, 1.f + __expf(-gv)) * uv;   // silu(g) * u
-                                    const __half hv = __float2half_rn(val);
-                                    bad |= !finite_f32(__half2float(hv));
-                                    *reinterpret_cast<__half*>(hrow + static_cast<uint64_t>(j) * ostride) = hv;
-                                }
+                                const float val = __fdividef(gv, 1.f + __expf(-gv)) * uv;   // silu(g) * u
+                                const __half hv = __float2half_rn(val);
+                                const uint32_t i = 2 * a + (low ? 0u : 1u);
+                                bad |= (j0 + i < cnt) && !finite_f32(__half2float(hv));
+                                *reinterpret_cast<__half*>(etile + i * RS + hpos * 2) = hv;
                             }
+                            __syncwarp();
+                            if (j0 + lane < cnt) {   // this lane's token: 16 hidden units = 32 bytes
+                                const uint4 o0 = *reinterpret_cast<const uint4*>(etile + lane * RS), o1 = *reinterpret_cast<const uint4*>(etile + lane * RS + 16);
+                                uint4* dst = reinterpret_cast<uint4*>(obase + static_cast<uint64_t>(t.row0 + g * kSub + j0 + lane) * ostride + (rb * 64u + quarter * 16u) * 2);
+                                dst[0] = o0; dst[1] = o1;
+                            }
+                            __syncwarp();
                         } else {
-                            const uint32_t wrow = rb * kRowsM + quarter * 32 + lane;   // output channel of this lane
-                            const uint32_t rq = rt[g][b];
+                            const uint32_t wbase = rb * kRowsM + quarter * 32;   // first output channel of this warp
                             const bool f16 = !shared && p.out_f16;
+                            bool nf = false;
 #pragma unroll
-                            for (uint32_t i = 0; i < 32; ++i) {
-                                const uint32_t route = __shfl_sync(0xffffffffu, rq, i);
-                                if (j0 + i < cnt) {
-                                    const float val = __uint_as_float(v[i]);
-                                    bad |= !finite_f32(val);
-                                    char* orow = obase + static_cast<uint64_t>(route) * ostride;
-                                    if (f16) reinterpret_cast<__half*>(orow)[wrow] = __float2half_rn(val);
-                                    else reinterpret_cast<float*>(orow)[wrow] = val;
+                            for (uint32_t i = 0; i < 32; ++i) nf |= (j0 + i < cnt) && !finite_f32(__uint_as_float(v[i]));
+                            bad |= nf;
+                            char* orow = obase + static_cast<uint64_t>(rt[g][b]) * ostride;   // this lane's token = column j0 + lane
+                            if (f16) {
+                                constexpr uint32_t RS = 80;   // 32 channels x 2 B + 16
+#pragma unroll
+                                for (uint32_t i = 0; i < 32; ++i) *reinterpret_cast<__half*>(etile + i * RS + lane * 2) = __float2half_rn(__uint_as_float(v[i]));
+                                __syncwarp();
+                                if (j0 + lane < cnt) {
+                                    uint4* dst = reinterpret_cast<uint4*>(orow + wbase * 2);
+#pragma unroll
+                                    for (uint32_t k = 0; k < 4; ++k) dst[k] = *reinterpret_cast<const uint4*>(etile + lane * RS + k * 16);
+                                }
+                            } else {
+                                constexpr uint32_t RS = 144;  // 32 channels x 4 B + 16
+#pragma unroll
+                                for (uint32_t i = 0; i < 32; ++i) *reinterpret_cast<uint32_t*>(etile + i * RS + lane * 4) = v[i];
+                                __syncwarp();
+                                if (j0 + lane < cnt) {
+                                    uint4* dst = reinterpret_cast<uint4*>(orow + wbase * 4);
+#pragma unroll
+                                    for (uint32_t k = 0; k < 8; ++k) dst[k] = *reinterpret_cast<const uint4*>(etile + lane * RS + k * 16);
                                 }
                             }
+                            __syncwarp();
                         }
                     }
                 }
@@ -747,12 +785,10 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     p.q_stage_bytes = kRowsM * (128u + 16u);
     p.off_d = p.off_q + 2 * p.q_stage_bytes;
     p.d_stage_bytes = (nmat * p.dm_mat_bytes + 1023u) & ~1023u;
-    p.off_a = p.off_d + 2 * p.d_stage_bytes;
-    p.off_b = p.off_a + kAStages * 16384u;
-    TSP_REQUIRE(p.off_b + 3 * 16384u + 1024 <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
-    p.nb_stages = (227 * 1024 - 1024 - p.off_b) / 16384u;
-    if (p.nb_stages > kMaxBStages) p.nb_stages = kMaxBStages;
-    const size_t smem = p.off_b + p.nb_stages * 16384u + 1024;
+    p.off_st = p.off_d + 2 * p.d_stage_bytes;
+    p.off_ep = p.off_st + kStages * kStageBytes;
+    const size_t smem = p.off_ep + kEpWarps * kEpTileBytes + 1024;
+    TSP_REQUIRE(smem <= 227 * 1024, "grouped GEMM: K extent needs more shared memory than one SM has");
 
     // gate and up of an expert at one constant distance: one copy per plane brings both
     auto mergeable = [](const uint8_t* first, const uint8_t* second, uint64_t* delta) {

@@ -357,11 +357,11 @@ def run_prefill(args, local):
             capi.check(lib.tsp_moe_route_offsets(s.counts.data_ptr(), E, ps.offsets.data_ptr(), st)); ev[4].record()
             capi.check(lib.tsp_moe_gather_rows16(ps.xk.data_ptr(), C2, s.token_map.data_ptr(), ps.offsets.data_ptr(), E, T, K, CHANNELS, ps.xp.data_ptr(), C2, st)); ev[5].record()
             capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up), ps.xp.data_ptr(), C2,
-                                                   ps.xk.data_ptr(), C2, T, K, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(),
+                                                   ps.xk.data_ptr(), C2, T, T, K, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(),
                                                    ps.offsets.data_ptr(), ps.hp.data_ptr(), H2, ps.s_hp.data_ptr(), H2, e, st)); ev[6].record()
             capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), C.byref(w.shared_down), ps.hp.data_ptr(), H2, T, K, s.token_map.data_ptr(),
                                                 s.counts.data_ptr(), ps.tasks.data_ptr(), ps.offsets.data_ptr(), ps.routed16.data_ptr(), C2, 1,
-                                                ps.s_hp.data_ptr(), H2, s.shared_out.data_ptr(), C4, e, st)); ev[7].record()
+                                                ps.s_hp.data_ptr(), H2, T, s.shared_out.data_ptr(), C4, e, st)); ev[7].record()
             capi.check(lib.tsp_moe_combine(ps.routed16.data_ptr(), C2, 1, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
                                            x.data_ptr(), C2, 1, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), C2, e, st)); ev[8].record()
             torch.cuda.synchronize()
@@ -551,7 +551,9 @@ def main():
     ap.add_argument("--experts", default="q4_k", choices=["q4_k", "q8_0"], help="expert encoding of the decode workload (q8_0: the MTP block)")
     ap.add_argument("--cpu-tokens", type=int, default=None, help="tokens of the batch timed on the CPU baseline (0 = skip)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "head"])
-    ap.add_argument("--ep-scheme", default="gather", choices=["gather", "alltoall"], help="multi-GPU exchange: all-gather/reduce-scatter or all-to-all")
+    ap.add_argument("--prefill-tokens", type=int, default=4096, help="token rows per GPU of the prefill sub-record")
+    ap.add_argument("--replicate", type=int, default=32, help="expert-parallel prefill: hot experts held by every rank (0 = none)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill sub-record")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -183,6 +183,8 @@ int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared
  * accumulated in route-rank order starting from the shared term. s_t = dot(d_shared_router, x[t]) when
  * d_shared_router != NULL (and is stored to d_shared_logit when that is non-NULL), else d_shared_logit[t].
  * routed_dtype / x_dtype: 0 = FP32 rows, 1 = binary16 rows (the prefill path keeps its route rows as binary16).
+ * d_shared == NULL leaves the shared term out (partial sums over the routes only: expert parallelism); a route whose weight
+ * is exactly zero is skipped without reading its row.
  * d_out_f16 (optional) receives the same rows rounded to binary16. */
 int tsp_moe_combine(const void* d_routed, uint64_t routed_stride_bytes, uint32_t routed_dtype, const float* d_weights,
                     const float* d_shared, uint64_t shared_stride_bytes,
@@ -284,8 +286,9 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
  * Both GEMMs take the layer's dense shared expert in the same launch when shared_* is non-NULL (same shape, encoding and
  * layout as a routed expert): its tasks cover every one of `tokens` rows in row order and follow the routed ones, as
  * `encode_moe_mm_many` runs the shared expert's dense projections right after the routed ones (moe_mm_many.cpp:189-214).
- * It reads the rows of step 1 (d_xk) directly; d_s_hp: its binary16 hidden rows [tokens x hidden]; d_shared_out: FP32
- * [tokens x channels]. */
+ * It reads the rows of step 1 (d_xk) directly; d_s_hp: its binary16 hidden rows [shared_tokens x hidden]; d_shared_out: FP32
+ * [shared_tokens x channels]. shared_tokens is the layer's own row count (equal to `tokens` on one GPU; under expert
+ * parallelism the routed rows are the rows received from every rank while the shared expert serves this rank's rows). */
 #define TSP_GROUPED_TILE 256u
 int tsp_moe_route_offsets(const uint32_t* d_counts, uint32_t experts, uint32_t* d_offsets, void* stream);
 int tsp_moe_rows_f16k(const void* d_x, uint64_t x_stride_bytes, uint32_t x_dtype, uint32_t rows, uint32_t cols, void* d_xk,
@@ -294,13 +297,14 @@ int tsp_moe_gather_rows16(const void* d_xk, uint64_t xk_stride_bytes, const uint
                           uint32_t tokens, uint32_t selected, uint32_t cols, void* d_xp, uint64_t xp_stride_bytes, void* stream);
 int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
                             const tsp_matrix_set* shared_up, const void* d_xp, uint64_t xp_stride_bytes, const void* d_xk,
-                            uint64_t xk_stride_bytes, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                            uint64_t xk_stride_bytes, uint32_t shared_tokens, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
                             const uint32_t* d_counts, const uint32_t* d_tasks, uint32_t* d_offsets, void* d_hp, uint64_t hp_stride_bytes,
                             void* d_s_hp, uint64_t s_hp_stride_bytes, uint32_t* d_error, void* stream);
 int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride_bytes,
                          uint32_t tokens, uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks,
                          uint32_t* d_offsets, void* d_routed, uint64_t routed_stride_bytes, uint32_t routed_dtype, const void* d_s_hp,
-                         uint64_t s_hp_stride_bytes, float* d_shared_out, uint64_t shared_out_stride_bytes, uint32_t* d_error, void* stream);
+                         uint64_t s_hp_stride_bytes, uint32_t shared_tokens, float* d_shared_out, uint64_t shared_out_stride_bytes,
+                         uint32_t* d_error, void* stream);
 
 /* Test hook: the binary16 values the grouped kernels stage for one Q4_K planar expert, [rows x cols] in natural K order.
  * Per weight this is RN16((q - 8) * RN16(d*sc) + RN16(8*d*sc - dmin*mn)), three roundings instead of the one rounding of

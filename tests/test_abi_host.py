@@ -37,9 +37,9 @@ def test_prefill_entries_refuse_bad_arguments():
     assert lib.tsp_moe_rows_f16k(p, 8, 0, 1, 12, p, 32, p, None) == capi.E_ARG                      # columns not a multiple of 8
     assert lib.tsp_moe_rows_f16k(p, 64, 2, 1, 16, p, 32, p, None) == capi.E_ARG                     # unknown dtype
     q = capi.MatrixSet(p + 16, None, 0, 1, 1, 64, 256, 12, 1)
-    assert lib.tsp_moe_grouped_gate_up(C.byref(q), C.byref(q), C.byref(q), None, p, 512, p, 512, 1, 1, p, p, p, p, p, 128, None, 0, p, None) == capi.E_ARG
+    assert lib.tsp_moe_grouped_gate_up(C.byref(q), C.byref(q), C.byref(q), None, p, 512, p, 512, 1, 1, 1, p, p, p, p, p, 128, None, 0, p, None) == capi.E_ARG
     assert "go together" in capi.last_error()
-    assert lib.tsp_moe_grouped_down(C.byref(q), None, p, 512, 1, 1, p, p, p, p, p, 128, 3, None, 0, None, 0, p, None) == capi.E_ARG   # row dtype 3
+    assert lib.tsp_moe_grouped_down(C.byref(q), None, p, 512, 1, 1, p, p, p, p, p, 128, 3, None, 0, 0, None, 0, p, None) == capi.E_ARG   # row dtype 3
 
 
 def test_expert_byte_constants():

@@ -54,7 +54,7 @@ def test_gate_up_address_order(tokens):
         capi.check(lib.tsp_moe_route_offsets(sc.counts.data_ptr(), E, ps.offsets.data_ptr(), st))
         capi.check(lib.tsp_moe_rows_f16k(x16.data_ptr(), Cn * 2, 1, tokens, Cn, ps.xk.data_ptr(), Cn * 2, e, st))
         capi.check(lib.tsp_moe_gather_rows16(ps.xk.data_ptr(), Cn * 2, sc.token_map.data_ptr(), ps.offsets.data_ptr(), E, tokens, K, Cn, ps.xp.data_ptr(), Cn * 2, st))
-        capi.check(lib.tsp_moe_grouped_gate_up(C.byref(gate), C.byref(upm), None, None, ps.xp.data_ptr(), Cn * 2, None, 0, tokens, K, sc.token_map.data_ptr(),
+        capi.check(lib.tsp_moe_grouped_gate_up(C.byref(gate), C.byref(upm), None, None, ps.xp.data_ptr(), Cn * 2, None, 0, 0, tokens, K, sc.token_map.data_ptr(),
                                                sc.counts.data_ptr(), ps.tasks.data_ptr(), ps.offsets.data_ptr(), ps.hp.data_ptr(), H * 2, None, 0, e, st))
         torch.cuda.synchronize()
         assert sc.error_word() == 0

@@ -72,5 +72,49 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+EP_SRC = os.path.join(PKG, "csrc_ep")
+EP_LIB = os.path.join(PKG, "libtsp_ep.so")
+EP_STAMP = os.path.join(PKG, "build", "libtsp_ep.stamp")
+
+
+def nccl_paths():
+    """Include and library directories of NCCL (the copy that ships with torch), or None when there is none."""
+    try:
+        import nvidia.nccl as n
+        root = os.path.dirname(n.__file__) if getattr(n, "__file__", None) else list(n.__path__)[0]
+    except Exception:
+        return None
+    inc, lib = os.path.join(root, "include"), os.path.join(root, "lib")
+    if os.path.exists(os.path.join(inc, "nccl.h")) and os.path.exists(os.path.join(lib, "libnccl.so.2")):
+        return inc, lib
+    return None
+
+
+def build_ep(force: bool = False) -> str | None:
+    """Compile csrc_ep/ into libtsp_ep.so (expert parallelism: needs NCCL and libtsp_moe.so). Returns the path, or None without NCCL."""
+    paths = nccl_paths()
+    if paths is None:
+        return None
+    build(force=False)
+    srcs = sorted(os.path.join(EP_SRC, f) for f in os.listdir(EP_SRC) if f.endswith(".cu"))
+    h = hashlib.sha256()
+    for path in srcs + [os.path.join(ROOT, "include", "tsp_ep.h"), os.path.join(ROOT, "include", "tsp_moe.h")]:
+        with open(path, "rb") as f:
+            h.update(f.read())
+    digest = h.hexdigest()
+    if not force and os.path.exists(EP_LIB) and os.path.exists(EP_STAMP) and open(EP_STAMP).read().strip() == digest:
+        return EP_LIB
+    inc, lib = paths
+    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    cmd = [_nvcc(), *flags, "-shared", "-I", os.path.join(ROOT, "include"), "-I", inc, "-o", EP_LIB, *srcs, "-L", PKG, "-ltsp_moe", "-L", lib,
+           "-l:libnccl.so.2", "-lcudart", "-Xlinker", "-rpath=$ORIGIN", "-Xlinker", f"-rpath={lib}"]
+    subprocess.run(cmd, check=True)
+    os.makedirs(os.path.dirname(EP_STAMP), exist_ok=True)
+    with open(EP_STAMP, "w") as f:
+        f.write(digest)
+    return EP_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_ep(force="--force" in sys.argv))

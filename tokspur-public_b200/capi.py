@@ -90,8 +90,8 @@ SIGNATURES = {
     "tsp_moe_route_offsets": (_i, [_vp, _u32, _vp, _vp]),
     "tsp_moe_rows_f16k": (_i, [_vp, _u64, _u32, _u32, _u32, _vp, _u64, _vp, _vp]),
     "tsp_moe_gather_rows16": (_i, [_vp, _u64, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp]),
-    "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
-    "tsp_moe_grouped_down": (_i, [_MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _vp, _u64, _vp, _u64, _vp, _vp]),
+    "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
+    "tsp_moe_grouped_down": (_i, [_MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
     "tsp_moe_staged_f16": (_i, [_MS, _u32, _vp, _vp]),
     "tsp_moe_layer_decode_static_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
     "tsp_moe_layer_decode_static": (_i, [C.POINTER(MoeWeights), _vp, _u64, _u32, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u32, _i,

@@ -279,17 +279,17 @@ int tsp_moe_combine(const void* d_routed, uint64_t routed_stride, uint32_t route
                     uint64_t shared_stride, const float* d_shared_router, const void* d_x, uint64_t x_stride, uint32_t x_dtype,
                     float* d_shared_logit, uint32_t tokens, uint32_t channels, uint32_t selected, float* d_out,
                     uint64_t out_stride, void* d_out_f16, uint64_t out_f16_stride, uint32_t* d_error, void* stream) {
-    TSP_REQUIRE(d_routed && d_weights && d_shared && (d_out || d_out_f16), "combine: null buffer");
+    TSP_REQUIRE(d_routed && d_weights && (d_out || d_out_f16), "combine: null buffer");
     TSP_REQUIRE(tokens >= 1 && channels >= 1 && channels <= 65536 && selected >= 1 && selected <= 64, "combine: mixture shape mismatch");
     TSP_REQUIRE(routed_dtype <= 1 && x_dtype <= 1, "combine: row dtype must be 0 (FP32) or 1 (binary16)");
     const uint64_t relem = routed_dtype ? 2 : 4, xelem = x_dtype ? 2 : 4;
-    TSP_REQUIRE(routed_stride >= channels * relem && shared_stride >= channels * 4ull && routed_stride % relem == 0 &&
-                shared_stride % 4 == 0, "combine: row stride too small");
+    TSP_REQUIRE(routed_stride >= channels * relem && routed_stride % relem == 0, "combine: row stride too small");
+    if (d_shared) TSP_REQUIRE(shared_stride >= channels * 4ull && shared_stride % 4 == 0, "combine: shared row stride too small");
     if (d_out) TSP_REQUIRE(out_stride >= channels * 4ull && out_stride % 4 == 0, "combine: output row stride too small");
     if (d_shared_router) TSP_REQUIRE(d_x && x_stride >= channels * xelem && x_stride % xelem == 0, "combine: the shared router needs the input rows");
     if (d_out_f16) TSP_REQUIRE(out_f16_stride >= channels * 2ull && out_f16_stride % 2 == 0, "combine: binary16 output stride too small");
     if (d_out) TSP_REQUIRE(!overlap(d_out, tokens * out_stride, d_routed, static_cast<uint64_t>(tokens) * selected * routed_stride) &&
-                           !overlap(d_out, tokens * out_stride, d_shared, tokens * shared_stride), "combine: output overlaps an input");
+                           (!d_shared || !overlap(d_out, tokens * out_stride, d_shared, tokens * shared_stride)), "combine: output overlaps an input");
     return launch_combine(d_routed, routed_stride, routed_dtype, d_weights, d_shared, shared_stride, d_shared_router, d_x, x_stride, x_dtype,
                           d_shared_logit, tokens, channels, selected, d_out, out_stride, d_out_f16, out_f16_stride, d_error,
                           static_cast<cudaStream_t>(stream));
@@ -488,9 +488,9 @@ int tsp_moe_gather_rows16(const void* d_xk, uint64_t xk_stride, const uint32_t* 
 }
 
 int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate, const tsp_matrix_set* shared_up,
-                            const void* d_xp, uint64_t xp_stride, const void* d_xk, uint64_t xk_stride, uint32_t tokens, uint32_t selected,
-                            const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, uint32_t* d_offsets, void* d_hp,
-                            uint64_t hp_stride, void* d_s_hp, uint64_t s_hp_stride, uint32_t* d_error, void* stream) {
+                            const void* d_xp, uint64_t xp_stride, const void* d_xk, uint64_t xk_stride, uint32_t shared_tokens, uint32_t tokens,
+                            uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, uint32_t* d_offsets,
+                            void* d_hp, uint64_t hp_stride, void* d_s_hp, uint64_t s_hp_stride, uint32_t* d_error, void* stream) {
     if (int rc = check_matrix(gate, "gate")) return rc;
     if (int rc = check_matrix(up, "up")) return rc;
     TSP_REQUIRE(gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
@@ -510,7 +510,8 @@ int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up
     if (int rc = check_shared_set(shared_up, gate, "shared up")) return rc;
     if (int rc = check_rows(d_xk, xk_stride, gate->cols, 2, "shared gate-up input")) return rc;
     if (int rc = check_rows(d_s_hp, s_hp_stride, gate->rows, 2, "shared gate-up output")) return rc;
-    const GroupedShared sh{shared_gate, shared_up, d_xk, xk_stride, tokens, d_s_hp, s_hp_stride};
+    TSP_REQUIRE(shared_tokens >= 1, "grouped gate-up: the shared expert needs at least one row");
+    const GroupedShared sh{shared_gate, shared_up, d_xk, xk_stride, shared_tokens, d_s_hp, s_hp_stride};
     return launch_grouped(gate, up, true, d_xp, xp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets, counter,
                           d_hp, hp_stride, 0, d_error, st, &sh);
 }
@@ -518,7 +519,7 @@ int tsp_moe_grouped_gate_up(const tsp_matrix_set* gate, const tsp_matrix_set* up
 int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* shared_down, const void* d_hp, uint64_t hp_stride, uint32_t tokens,
                          uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, uint32_t* d_offsets,
                          void* d_routed, uint64_t routed_stride, uint32_t routed_dtype, const void* d_s_hp, uint64_t s_hp_stride,
-                         float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
+                         uint32_t shared_tokens, float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
     if (int rc = check_matrix(down, "down")) return rc;
     TSP_REQUIRE(d_token_map && d_tasks && d_counts && d_offsets && tokens >= 1 && selected >= 1 && selected <= 64 && routed_dtype <= 1,
                 "grouped down: null table, empty batch or bad row dtype");
@@ -533,7 +534,8 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* share
     if (int rc = check_shared_set(shared_down, down, "shared down")) return rc;
     if (int rc = check_rows(d_s_hp, s_hp_stride, down->cols, 2, "shared down input")) return rc;
     if (int rc = check_rows(d_shared_out, shared_out_stride, down->rows, 4, "shared down output")) return rc;
-    const GroupedShared sh{shared_down, nullptr, d_s_hp, s_hp_stride, tokens, d_shared_out, shared_out_stride};
+    TSP_REQUIRE(shared_tokens >= 1, "grouped down: the shared expert needs at least one row");
+    const GroupedShared sh{shared_down, nullptr, d_s_hp, s_hp_stride, shared_tokens, d_shared_out, shared_out_stride};
     return launch_grouped(down, nullptr, false, d_hp, hp_stride, tokens * selected, tokens, selected, d_token_map, d_tasks, d_counts, d_offsets,
                           counter, d_routed, routed_stride, routed_dtype, d_error, st, &sh);
 }
@@ -609,10 +611,10 @@ int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratc
     if (int rc = tsp_moe_gather_rows16(ps->d_xk, channels * 2ull, s->d_token_map, ps->d_offsets, experts, tokens, selected, channels, ps->d_xp,
                                        channels * 2ull, st)) return rc;
     // the dense shared expert rides in both launches; the route rows are kept as binary16 (half the traffic of the mixture)
-    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xp, channels * 2ull, ps->d_xk, channels * 2ull, tokens, selected, s->d_token_map,
+    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xp, channels * 2ull, ps->d_xk, channels * 2ull, tokens, tokens, selected, s->d_token_map,
                                          s->d_counts, s->d_tasks, ps->d_offsets, ps->d_hp, hidden * 2ull, ps->d_s_hp, hidden * 2ull, d_error, st)) return rc;
     if (int rc = tsp_moe_grouped_down(&w->down, &w->shared_down, ps->d_hp, hidden * 2ull, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
-                                      ps->d_offsets, s->d_routed, channels * 2ull, 1, ps->d_s_hp, hidden * 2ull, s->d_shared_out, channels * 4ull,
+                                      ps->d_offsets, s->d_routed, channels * 2ull, 1, ps->d_s_hp, hidden * 2ull, tokens, s->d_shared_out, channels * 4ull,
                                       d_error, st)) return rc;
     return tsp_moe_combine(s->d_routed, channels * 2ull, 1, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, d_x, x_stride, x_dtype,
                            s->d_shared_logit, tokens, channels, selected, out_dtype == 0 ? static_cast<float*>(d_out) : nullptr,

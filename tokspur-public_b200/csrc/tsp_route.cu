@@ -415,7 +415,8 @@ combine_kernel(const void* __restrict__ routed, uint64_t routed_stride, const fl
         if (shared_logit) gate = stable_sigmoid(shared_logit[token]);
         __syncthreads();
     }
-    const float* sh = reinterpret_cast<const float*>(reinterpret_cast<const char*>(shared) + token * shared_stride);
+    // shared == nullptr: no shared term (the rows are partial sums that another launch finishes)
+    const float* sh = shared ? reinterpret_cast<const float*>(reinterpret_cast<const char*>(shared) + token * shared_stride) : nullptr;
     float* o = reinterpret_cast<float*>(reinterpret_cast<char*>(out) + token * out_stride);
     bool bad = false;
     // gridDim.y slices of the row per token, so that a small batch still fills the machine while a large one does not repeat
@@ -425,7 +426,7 @@ combine_kernel(const void* __restrict__ routed, uint64_t routed_stride, const fl
     const char* y0 = reinterpret_cast<const char*>(routed) + static_cast<uint64_t>(token) * selected * routed_stride;
     for (uint32_t c = blockIdx.y * per_slice + tid * 4; c < c_end; c += kCombineThreads * 4) {
         if (vec4 && c + 4 <= c_end) {
-            const float4 s4 = *reinterpret_cast<const float4*>(sh + c);
+            const float4 s4 = sh ? *reinterpret_cast<const float4*>(sh + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             float v[4] = {gate * s4.x, gate * s4.y, gate * s4.z, gate * s4.w};
             for (uint32_t r = 0; r < selected; ++r) {
                 const float wr = w_s[r];
@@ -450,7 +451,7 @@ combine_kernel(const void* __restrict__ routed, uint64_t routed_stride, const fl
             }
         } else {
             for (uint32_t cc = c; cc < min(c + 4, c_end); ++cc) {   // a row tail shorter than four channels, or rows that are not 16-byte aligned
-                float v = gate * sh[cc];
+                float v = sh ? gate * sh[cc] : 0.f;
                 for (uint32_t r = 0; r < selected; ++r)
                     if (w_s[r] != 0.f) {
                         const char* yr = y0 + r * routed_stride;
@@ -676,7 +677,7 @@ int launch_combine(const void* routed, uint64_t routed_stride, uint32_t routed_f
     const uint32_t want = (4u * 148u + tokens - 1) / tokens;
     if (slices > want) slices = want;
     auto a16 = [](const void* p, uint64_t stride) { return (reinterpret_cast<uintptr_t>(p) | stride) % 16 == 0; };
-    const int vec4 = (routed_f16 ? (reinterpret_cast<uintptr_t>(routed) | routed_stride) % 8 == 0 : a16(routed, routed_stride)) && a16(shared, shared_stride) &&
+    const int vec4 = (routed_f16 ? (reinterpret_cast<uintptr_t>(routed) | routed_stride) % 8 == 0 : a16(routed, routed_stride)) && (!shared || a16(shared, shared_stride)) &&
                      (!out || a16(out, out_stride)) && (!out16 || (reinterpret_cast<uintptr_t>(out16) | out16_stride) % 8 == 0);
     const dim3 grid(tokens, slices), block(kCombineThreads);
 #define TSP_COMBINE(R, X) TSP_CUDA(launch_pdl(combine_kernel<R, X>, grid, block, 0, st, routed, routed_stride, weights, shared, shared_stride, shared_router, \

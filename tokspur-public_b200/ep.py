@@ -1,323 +1,284 @@
-"""Expert parallelism over the GPUs of one node: experts sharded by contiguous id range, tokens data-parallel by
-source rank, one all-to-all each way (dispatch of routed rows, combine of per-route outputs) over NCCL.
+"""Expert parallelism over the GPUs of one node: a thin harness over libtsp_ep.so (include/tsp_ep.h).
 
-The reference is single-GPU; this is the multi-GPU form of its MoE layer with identical per-route arithmetic: a route's
-expert output is computed on the rank that owns the expert by the same kernels, returned to the token's rank, and mixed
-there in route-rank order with the locally computed shared expert, so the layer output equals the one-GPU output.
-
-`torch.distributed` is the plumbing (process group, all_to_all_single); sort / gather / scatter of route rows use torch
-index ops. No TMA multicast and no peer-memory operand is involved: received rows sit in local HBM before any kernel
-touches them.
+The reference is single-GPU; this is the multi-GPU form of its MoE layer. Experts are sharded by contiguous id range, hot
+experts may be replicated on every rank, tokens are data-parallel by source rank, and one layer step is sequenced by ONE C
+call: route, pack slabs, NCCL all-to-all, the one-GPU kernels on the owners, NCCL exchange of partial sums, local mixture.
+`torch.distributed` is used only to hand the communicator id to the other ranks and for the benchmark's barriers.
 """
 from __future__ import annotations
 
 import ctypes as C
 import json
 import os
-import time
 
 import numpy as np
 import torch
 import torch.distributed as dist
 
+from . import build as _build
+from . import capi
+from .capi import MoeWeights
 
-class RoutePlan:
-    """Where each local route goes and how the returned rows map back. Pure index logic (device-agnostic)."""
-
-    def __init__(self, ids: torch.Tensor, experts: int, world: int, group=None):
-        T, K = ids.shape
-        per = experts // world
-        flat = ids.reshape(-1).to(torch.int64)
-        dest = torch.div(flat, per, rounding_mode="floor")
-        # stable sort by destination keeps (token, slot) order inside each destination: deterministic layouts
-        self.order = torch.sort(dest, stable=True).indices
-        self.send_counts = torch.bincount(dest, minlength=world).to(torch.int64)
-        self.recv_counts = torch.empty_like(self.send_counts)
-        dist.all_to_all_single(self.recv_counts, self.send_counts, group=group)
-        both = torch.stack([self.send_counts, self.recv_counts]).cpu()   # the one host synchronisation of a step
-        self.send_splits = both[0].tolist()
-        self.recv_splits = both[1].tolist()
-        self.token_of_route = torch.div(self.order, K, rounding_mode="floor")
-        self.local_expert = (flat[self.order] % per).to(torch.int32)
-        self.received = int(sum(self.recv_splits))
-        self.routes = T * K
+REPLICATED = 0xFFFF
 
 
-def dispatch(plan: RoutePlan, rows: torch.Tensor, group=None):
-    """rows: [T, C] on the source. Returns (received rows [R, C], their local expert ids [R])."""
-    send_rows = rows.index_select(0, plan.token_of_route)
-    recv_rows = rows.new_empty((plan.received, rows.shape[1]))
-    dist.all_to_all_single(recv_rows, send_rows, plan.recv_splits, plan.send_splits, group=group)
-    recv_ids = plan.local_expert.new_empty(plan.received)
-    dist.all_to_all_single(recv_ids, plan.local_expert, plan.recv_splits, plan.send_splits, group=group)
-    return recv_rows, recv_ids
+class EpLayerDesc(C.Structure):
+    _fields_ = [("local", MoeWeights), ("local_experts", C.c_uint32), ("d_place", C.c_void_p)]
 
 
-def combine(plan: RoutePlan, outputs: torch.Tensor, routed: torch.Tensor, group=None) -> None:
-    """outputs: [R, C] per received route. Writes routed[token*K + slot] for every local route."""
-    back = outputs.new_empty((plan.routes, outputs.shape[1]))
-    dist.all_to_all_single(back, outputs, plan.send_splits, plan.recv_splits, group=group)
-    routed.index_copy_(0, plan.order, back)
+_vp, _u32, _u64, _i = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int
+EP_SIGNATURES = {
+    "tsp_ep_last_error": (C.c_char_p, []),
+    "tsp_ep_unique_id": (_i, [_vp]),
+    "tsp_ep_create": (_i, [_vp, _i, _i, C.POINTER(_vp)]),
+    "tsp_ep_destroy": (_i, [_vp]),
+    "tsp_ep_scratch_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32, _u32, _u32, _i]),
+    "tsp_ep_slab_header_rows": (_u32, [_u32, _u32, _u32]),
+    "tsp_ep_slab_bytes": (_u64, [_u32, _u32, _u32]),
+    "tsp_ep_pack": (_i, [_vp, _vp, _vp, _u64, _vp, _u32, _u32, _u32, _u32, _u32, _i, _vp, _vp, _vp]),
+    "tsp_ep_unpack": (_i, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp]),
+    "tsp_ep_moe_layer": (_i, [_vp, C.POINTER(EpLayerDesc), _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u32, _i, _i, _vp, _u64,
+                              _vp, _vp]),
+}
+_lib = None
 
 
-# --------------------------------------------------------------------------------------------------
-# CUDA side: one rank's share of a layer
-# --------------------------------------------------------------------------------------------------
+def lib() -> C.CDLL:
+    """Load libtsp_ep.so (built on demand; needs NCCL). Fails loudly when it cannot be built."""
+    global _lib
+    if _lib is None:
+        capi.lib()   # libtsp_moe.so first: the expert-parallel library calls into it
+        path = _build.EP_LIB
+        if not os.path.exists(path):
+            _build.build_ep()
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: NCCL headers / library not found, the expert-parallel library cannot be built")
+        L = C.CDLL(path)
+        for name, (res, args) in EP_SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise capi.TspError(rc, lib().tsp_ep_last_error().decode())
+
+
+def placement(experts: int, world: int, replicated=()) -> np.ndarray:
+    """Placement words (owner << 16 | slot) of a layer: contiguous ranges of experts/world ids per rank; the experts in `replicated`
+    are held by every rank behind its own range."""
+    per = experts // world
+    place = np.empty(experts, dtype=np.uint32)
+    for e in range(experts):
+        place[e] = ((e // per) << 16) | (e % per)
+    for i, e in enumerate(sorted(replicated)):
+        place[e] = (REPLICATED << 16) | (per + i)
+    return place
+
+
+def local_expert_ids(experts: int, world: int, rank: int, replicated=()) -> list[int]:
+    per = experts // world
+    return list(range(rank * per, (rank + 1) * per)) + sorted(replicated)
+
+
+def slab_model(ids: np.ndarray, weights: np.ndarray, place: np.ndarray, rank: int, world: int):
+    """Plain numpy statement of what the pack kernels put into the slab for every destination: (pos [world, tokens], per
+    destination the list of (token, local slots, weights)). The CPU tests compare the protocol against this; the GPU tests compare
+    the kernels against it."""
+    T, K = ids.shape
+    owner = place[ids] >> 16
+    dest = np.where(owner == REPLICATED, rank, owner)
+    pos = np.full((world, T), -1, dtype=np.int32)
+    rows = []
+    for g in range(world):
+        mine = dest == g
+        has = mine.any(axis=1)
+        pos[g, has] = np.arange(int(has.sum()), dtype=np.int32)
+        slots = np.where(mine, place[ids] & 0xFFFF, 0xFFFFFFFF).astype(np.uint32)
+        rows.append((np.nonzero(has)[0], slots[has], np.where(mine, weights, 0.0).astype(np.float32)[has]))
+    return pos, rows
+
+
+class EpContext:
+    """This rank's communicator of libtsp_ep.so; the id travels through torch.distributed (any backend)."""
+
+    def __init__(self, rank: int, world: int, device):
+        L = lib()
+        self.rank, self.world = rank, world
+        idbuf = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            raw = (C.c_uint8 * 128)()
+            check(L.tsp_ep_unique_id(raw))
+            idbuf = torch.tensor(list(raw), dtype=torch.uint8)
+        on_device = dist.get_backend() == "nccl"
+        t = idbuf.to(device) if on_device else idbuf
+        dist.broadcast(t, 0)
+        raw = (C.c_uint8 * 128)(*t.cpu().tolist())
+        h = C.c_void_p()
+        check(L.tsp_ep_create(raw, rank, world, C.byref(h)))
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            lib().tsp_ep_destroy(self.handle)
+            self.handle = None
+
+
 class EpLayer:
-    def __init__(self, seed: int, channels: int, hidden: int, experts: int, selected: int, rank: int, world: int, device, capacity: int,
-                 expert_type: int = 12, layout: int = 1, prefill: bool = False):
+    """One rank's share of a layer: local experts (own range + replicated ones), placement table and step scratch."""
+
+    def __init__(self, ctx: EpContext, seed: int, channels: int, hidden: int, experts: int, selected: int, device, tokens: int,
+                 prefill: bool = False, replicated=(), scratch: torch.Tensor | None = None):
         from . import layer as L
-        assert experts % world == 0
-        self.rank, self.world, self.C, self.H, self.E, self.K = rank, world, channels, hidden, experts, selected
-        per = experts // world
-        self.per = per
-        self.w = L.SynthDeviceLayer(seed, channels, hidden, experts, expert_type, layout, device, expert_range=(rank * per, (rank + 1) * per))
-        self.device = device
-        self.capacity = capacity   # token rows per rank per step
-        max_recv = capacity * selected * world
-        f32, i32 = torch.float32, torch.int32
-        z = lambda n, dt: torch.zeros(max(int(n), 1), dtype=dt, device=device)
-        self.ids = z(capacity * selected, i32)
-        self.weights = z(capacity * selected, f32)
-        self.routed = torch.zeros((capacity * selected, channels), dtype=f32, device=device)
-        self.shared_hidden = z(capacity * hidden, f32)
-        self.shared_out = z(capacity * channels, f32)
-        self.shared_logit = z(capacity, f32)
-        self.x32 = z(capacity * channels, f32)
-        self.recv32 = z(max_recv * channels, f32)
-        self.hid = z(max_recv * hidden, f32)
-        self.y = torch.zeros((max_recv, channels), dtype=f32, device=device)
-        self.token_map = z(per * max_recv, i32)
-        self.counts = z(per, i32)
-        self.tasks = z(max_recv + 2 * per + 2, i32)
-        self.error = z(1, i32)
-        # buffers of the gathered (all-gather / reduce-scatter) scheme: every rank sees all world*capacity token rows
-        G = capacity * world
-        self.pack = torch.zeros((capacity, channels * 2 + experts * 4), dtype=torch.uint8, device=device)
-        self.gathered = torch.zeros((G, channels * 2 + experts * 4), dtype=torch.uint8, device=device)
-        self.g_x32 = z(G * channels, f32)
-        self.g_ids = z(G * selected, i32)
-        self.g_weights = z(G * selected, f32)
-        self.g_hid = z(G * selected * hidden, f32)
-        self.g_routed = torch.zeros((G * selected, channels), dtype=f32, device=device)
-        self.g_token_map = z(per * G, i32)
-        self.g_tasks = z(G * selected + 2 * per + 2, i32)
-        self.g_partial = torch.zeros((G, channels), dtype=f32, device=device)
-        self.g_zero = torch.zeros((G, channels), dtype=f32, device=device)
-        self.rs_out = torch.zeros((capacity, channels), dtype=f32, device=device)
-        self.ones = torch.ones(capacity, dtype=f32, device=device)
-        if prefill:
-            # prefill-size gathered scheme: the local experts' routes of all world*capacity rows through the grouped tensor-core
-            # GEMMs (permuted binary16 rows), the shared expert of the local rows through the same kernels
-            from . import capi
-            f16 = torch.float16
-            R = G * selected
-            self.p_tasks = z(int(capi.lib().tsp_moe_tasks_words(G, per, selected, 128)), i32)
-            self.p_offsets = z(per + 1, i32)
-            self.p_pos_route = z(R, i32)
-            self.p_xp = torch.zeros((R, channels), dtype=f16, device=device)
-            self.p_hp = torch.zeros((R, hidden), dtype=f16, device=device)
-            self.s_ids0 = z(capacity, i32)
-            self.s_token_map, self.s_counts, self.s_offsets, self.s_pos = z(capacity, i32), z(1, i32), z(2, i32), z(capacity, i32)
-            self.s_tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, 1, 1, 128)), i32)
-            self.s_xp = torch.zeros((capacity, channels), dtype=f16, device=device)
-            self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)
+        assert experts % ctx.world == 0
+        self.ctx, self.C, self.H, self.E, self.K, self.T, self.prefill = ctx, channels, hidden, experts, selected, tokens, prefill
+        ids = local_expert_ids(experts, ctx.world, ctx.rank, replicated)
+        self.w = L.SynthDeviceLayer(seed, channels, hidden, experts, 12, 1, device, expert_ids=ids)
+        self.place = torch.from_numpy(placement(experts, ctx.world, replicated).view(np.int32)).to(device)
+        self.desc = EpLayerDesc(self.w.weights, len(ids), self.place.data_ptr())
+        need = int(lib().tsp_ep_scratch_bytes(tokens, channels, hidden, experts, len(ids), selected, ctx.world, int(prefill)))
+        self.scratch = scratch if scratch is not None and scratch.numel() >= need else torch.zeros(need, dtype=torch.uint8, device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
 
     def step(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
-        from . import capi
         from . import layer as L
-        lib, st, e = capi.lib(), L.stream_ptr(), self.error.data_ptr()
-        T, Cn, H, K = x16.shape[0], self.C, self.H, self.K
-        w = self.w.weights
-        capi.check(lib.tsp_moe_route(logits.data_ptr(), logits.stride(0) * 4, T, self.E, K, 0, 1, self.ids.data_ptr(), self.weights.data_ptr(), e, st))
-        plan = RoutePlan(self.ids[: T * K].view(T, K), self.E, self.world)
-        rows, lids = dispatch(plan, x16)
-        R = plan.received
-        if R:
-            capi.check(lib.tsp_rows_f16_to_f32(rows.data_ptr(), Cn * 2, self.recv32.data_ptr(), Cn * 4, R, Cn, st))
-            capi.check(lib.tsp_moe_permute(lids.data_ptr(), R, self.per, 1, capi.GEMV_TILE, self.token_map.data_ptr(), self.counts.data_ptr(),
-                                           self.tasks.data_ptr(), e, st))
-            capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.gate), C.byref(w.up), self.recv32.data_ptr(), Cn * 4, R, 1, self.token_map.data_ptr(),
-                                                  self.counts.data_ptr(), self.tasks.data_ptr(), self.hid.data_ptr(), H * 4, 1, e, st))
-            capi.check(lib.tsp_moe_project(C.byref(w.down), self.hid.data_ptr(), H * 4, 1, R, 1, self.token_map.data_ptr(), self.counts.data_ptr(),
-                                           self.tasks.data_ptr(), self.y.data_ptr(), Cn * 4, 0, e, st))
-        combine(plan, self.y[:R], self.routed)
-        # local: shared expert and the gated mixture in route-rank order
-        capi.check(lib.tsp_rows_f16_to_f32(x16.data_ptr(), x16.stride(0) * 2, self.x32.data_ptr(), Cn * 4, T, Cn, st))
-        capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.shared_gate), C.byref(w.shared_up), self.x32.data_ptr(), Cn * 4, T, 1, None, None, None,
-                                              self.shared_hidden.data_ptr(), H * 4, 1, e, st))
-        capi.check(lib.tsp_moe_project(C.byref(w.shared_down), self.shared_hidden.data_ptr(), H * 4, 1, T, 1, None, None, None,
-                                       self.shared_out.data_ptr(), Cn * 4, 0, e, st))
-        capi.check(lib.tsp_moe_combine(self.routed.data_ptr(), Cn * 4, 0, self.weights.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
-                                       w.d_shared_router, self.x32.data_ptr(), Cn * 4, 0, self.shared_logit.data_ptr(), T, Cn, K, None, 0,
-                                       out16.data_ptr(), out16.stride(0) * 2, e, st))
-
-    def step_gathered(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
-        """Small-batch scheme without any host synchronisation: all-gather the token rows and router logits (every rank then
-        routes all rows itself), compute the routes that hit local experts, mix them per token into partial sums, and
-        reduce-scatter the partial sums back to the tokens' ranks. For decode batches the bytes moved equal those of the
-        all-to-all form (with top-10 of 8 ranks nearly every row visits most ranks anyway) and both collectives have fixed
-        sizes. The mixture adds the ranks' partial sums instead of walking the routes in rank order, so the result agrees with
-        the one-GPU layer to FP32 rounding, not bit for bit."""
-        from . import capi
-        from . import layer as L
-        lib, st, e = capi.lib(), L.stream_ptr(), self.error.data_ptr()
-        T, Cn, H, K, E, per = x16.shape[0], self.C, self.H, self.K, self.E, self.per
-        assert T == self.capacity, "the gathered scheme runs at the capacity it was built for"
-        G = T * self.world
-        w = self.w.weights
-        rowb = Cn * 2 + E * 4
-        self.pack[:, : Cn * 2].copy_(x16.view(torch.uint8).view(T, Cn * 2))
-        self.pack[:, Cn * 2:].copy_(logits.view(torch.uint8).view(T, E * 4))
-        dist.all_gather_into_tensor(self.gathered, self.pack)
-        gx, glg = self.gathered.data_ptr(), self.gathered.data_ptr() + Cn * 2
-        capi.check(lib.tsp_rows_f16_to_f32(gx, rowb, self.g_x32.data_ptr(), Cn * 4, G, Cn, st))
-        capi.check(lib.tsp_moe_route(glg, rowb, G, E, K, 0, 1, self.g_ids.data_ptr(), self.g_weights.data_ptr(), e, st))
-        capi.check(lib.tsp_moe_permute_local(self.g_ids.data_ptr(), G, self.rank * per, per, K, capi.GEMV_TILE, self.g_token_map.data_ptr(),
-                                             self.counts.data_ptr(), self.g_tasks.data_ptr(), e, st))
-        capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.gate), C.byref(w.up), self.g_x32.data_ptr(), Cn * 4, G, K, self.g_token_map.data_ptr(),
-                                              self.counts.data_ptr(), self.g_tasks.data_ptr(), self.g_hid.data_ptr(), H * 4, 1, e, st))
-        capi.check(lib.tsp_moe_project(C.byref(w.down), self.g_hid.data_ptr(), H * 4, 1, G, K, self.g_token_map.data_ptr(), self.counts.data_ptr(),
-                                       self.g_tasks.data_ptr(), self.g_routed.data_ptr(), Cn * 4, 0, e, st))
-        local = (self.g_ids >= self.rank * per) & (self.g_ids < (self.rank + 1) * per)
-        w_local = torch.where(local, self.g_weights, torch.zeros_like(self.g_weights))   # zero weight = route not computed here
-        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, 0, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, 0, None,
-                                       G, Cn, K, self.g_partial.data_ptr(), Cn * 4, None, 0, e, st))
-        dist.reduce_scatter_tensor(self.rs_out, self.g_partial)
-        x_local = self.g_x32.data_ptr() + self.rank * T * Cn * 4
-        capi.check(lib.tsp_moe_gate_up_swiglu(C.byref(w.shared_gate), C.byref(w.shared_up), x_local, Cn * 4, T, 1, None, None, None,
-                                              self.shared_hidden.data_ptr(), H * 4, 1, e, st))
-        capi.check(lib.tsp_moe_project(C.byref(w.shared_down), self.shared_hidden.data_ptr(), H * 4, 1, T, 1, None, None, None,
-                                       self.shared_out.data_ptr(), Cn * 4, 0, e, st))
-        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, 0, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
-                                       w.d_shared_router, x_local, Cn * 4, 0, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
-                                       out16.data_ptr(), out16.stride(0) * 2, e, st))
-
-    def step_gathered_prefill(self, x16: torch.Tensor, logits: torch.Tensor, out16: torch.Tensor) -> None:
-        """The gathered scheme at prefill size: all-gather rows + logits, route everything on every rank, run the routes that hit
-        local experts through the grouped tcgen05 GEMMs (tiles of 128 routes), mix them per token into partial sums,
-        reduce-scatter the partial sums, then add the local rows' shared expert. No host synchronisation, fixed-size collectives."""
-        from . import capi
-        from . import layer as L
-        lib, st, e = capi.lib(), L.stream_ptr(), self.error.data_ptr()
-        T, Cn, H, K, E, per = x16.shape[0], self.C, self.H, self.K, self.E, self.per
-        assert T == self.capacity, "the gathered scheme runs at the capacity it was built for"
-        G = T * self.world
-        R = G * K
-        w = self.w.weights
-        rowb = Cn * 2 + E * 4
-        self.pack[:, : Cn * 2].copy_(x16.view(torch.uint8).view(T, Cn * 2))
-        self.pack[:, Cn * 2:].copy_(logits.view(torch.uint8).view(T, E * 4))
-        dist.all_gather_into_tensor(self.gathered, self.pack)
-        gx, glg = self.gathered.data_ptr(), self.gathered.data_ptr() + Cn * 2
-        capi.check(lib.tsp_rows_f16_to_f32(gx, rowb, self.g_x32.data_ptr(), Cn * 4, G, Cn, st))
-        capi.check(lib.tsp_moe_route(glg, rowb, G, E, K, 0, 1, self.g_ids.data_ptr(), self.g_weights.data_ptr(), e, st))
-        capi.check(lib.tsp_moe_permute_local(self.g_ids.data_ptr(), G, self.rank * per, per, K, 128, self.g_token_map.data_ptr(),
-                                             self.counts.data_ptr(), self.p_tasks.data_ptr(), e, st))
-        capi.check(lib.tsp_moe_route_offsets(self.counts.data_ptr(), per, self.p_offsets.data_ptr(), st))
-        capi.check(lib.tsp_moe_gather_rows(self.g_x32.data_ptr(), Cn * 4, K, self.g_token_map.data_ptr(), self.p_offsets.data_ptr(), per, G, K, Cn,
-                                           self.p_xp.data_ptr(), Cn * 2, self.p_pos_route.data_ptr(), e, st))
-        capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), self.p_xp.data_ptr(), Cn * 2, R, self.p_tasks.data_ptr(),
-                                               self.counts.data_ptr(), self.p_offsets.data_ptr(), self.p_hp.data_ptr(), H * 2, e, st))
-        capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), self.p_hp.data_ptr(), H * 2, R, self.p_tasks.data_ptr(), self.counts.data_ptr(),
-                                            self.p_offsets.data_ptr(), self.p_pos_route.data_ptr(), self.g_routed.data_ptr(), Cn * 4, e, st))
-        local = (self.g_ids >= self.rank * per) & (self.g_ids < (self.rank + 1) * per)
-        w_local = torch.where(local, self.g_weights, torch.zeros_like(self.g_weights))   # zero weight = route not computed here
-        capi.check(lib.tsp_moe_combine(self.g_routed.data_ptr(), Cn * 4, 0, w_local.data_ptr(), self.g_zero.data_ptr(), Cn * 4, None, None, 0, 0, None,
-                                       G, Cn, K, self.g_partial.data_ptr(), Cn * 4, None, 0, e, st))
-        dist.reduce_scatter_tensor(self.rs_out, self.g_partial)
-        x_local = self.g_x32.data_ptr() + self.rank * T * Cn * 4
-        capi.check(lib.tsp_moe_permute(self.s_ids0.data_ptr(), T, 1, 1, 128, self.s_token_map.data_ptr(), self.s_counts.data_ptr(),
-                                       self.s_tasks.data_ptr(), e, st))
-        capi.check(lib.tsp_moe_route_offsets(self.s_counts.data_ptr(), 1, self.s_offsets.data_ptr(), st))
-        capi.check(lib.tsp_moe_gather_rows(x_local, Cn * 4, 1, self.s_token_map.data_ptr(), self.s_offsets.data_ptr(), 1, T, 1, Cn,
-                                           self.s_xp.data_ptr(), Cn * 2, self.s_pos.data_ptr(), e, st))
-        capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.shared_gate), C.byref(w.shared_up), self.s_xp.data_ptr(), Cn * 2, T, self.s_tasks.data_ptr(),
-                                               self.s_counts.data_ptr(), self.s_offsets.data_ptr(), self.s_hp.data_ptr(), H * 2, e, st))
-        capi.check(lib.tsp_moe_grouped_down(C.byref(w.shared_down), self.s_hp.data_ptr(), H * 2, T, self.s_tasks.data_ptr(), self.s_counts.data_ptr(),
-                                            self.s_offsets.data_ptr(), self.s_pos.data_ptr(), self.shared_out.data_ptr(), Cn * 4, e, st))
-        capi.check(lib.tsp_moe_combine(self.rs_out.data_ptr(), Cn * 4, 0, self.ones.data_ptr(), self.shared_out.data_ptr(), Cn * 4,
-                                       w.d_shared_router, x_local, Cn * 4, 0, self.shared_logit.data_ptr(), T, Cn, 1, None, 0,
-                                       out16.data_ptr(), out16.stride(0) * 2, e, st))
+        T = x16.shape[0]
+        assert T == self.T
+        check(lib().tsp_ep_moe_layer(self.ctx.handle, C.byref(self.desc), self.scratch.data_ptr(), self.scratch.numel(), x16.data_ptr(),
+                                     x16.stride(0) * 2, logits.data_ptr(), logits.stride(0) * 4, T, self.C, self.H, self.E, self.K, 0, 1,
+                                     int(self.prefill), out16.data_ptr(), out16.stride(0) * 2, self.error.data_ptr(), L.stream_ptr()))
 
     def error_word(self) -> int:
         torch.cuda.synchronize()
         return int(self.error.item()) & 0xFFFFFFFF
 
 
-def run_bench(args, rank: int, world: int, local: int) -> None:
-    """`bench.py --gpus N` for N > 1: every rank brings its own batch of `args.tokens` rows (weak scaling), experts are
-    sharded 512/N per GPU; value = all ranks' tokens / max-over-ranks device time."""
+def hot_experts(logits: np.ndarray, selected: int, count: int) -> list[int]:
+    """The `count` experts that receive the most routes of a calibration batch (host side, outside any timed region)."""
+    if count <= 0:
+        return []
+    ids = np.argsort(-logits, axis=1, kind="stable")[:, :selected]
+    loads = np.bincount(ids.ravel(), minlength=logits.shape[1])
+    return sorted(np.argsort(-loads, kind="stable")[:count].tolist())
+
+
+# --------------------------------------------------------------------------------------------------
+# bench.py --gpus N (N > 1)
+# --------------------------------------------------------------------------------------------------
+def _timed(fn, steps, warmup, dev):
+    """`steps` calls of fn between two barriers, CUDA events on the launching stream, maximum over the ranks (ms per step)."""
+    for i in range(warmup):
+        fn(i)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def _phase(ctx, args, rank, world, dev, prefill: bool, T: int, layers_n: int, nb: int, replicate: int, scratch=None):
+    """One workload (decode batch or prefill batch per rank) through the expert-parallel layer: resident and end-to-end timing."""
     from . import synth
-    from bench import CHANNELS, HIDDEN, EXPERTS, SELECTED, ClockSampler
-    dev = torch.device("cuda", local)
-    prefill = getattr(args, "workload", "decode") == "prefill"
-    T = 4096 if prefill and args.tokens == 64 else args.tokens
-    layers = [EpLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, SELECTED, rank, world, dev, T, prefill=prefill) for i in range(2 if prefill else args.layers)]
-    nb = 2 if prefill else 8
+    from bench import CHANNELS, HIDDEN, EXPERTS, SELECTED
     bias = synth.zipf_bias(5, EXPERTS) if prefill else None
+    # the replicated set comes from a calibration batch every rank can generate for itself (same seed everywhere)
+    rep = hot_experts(synth.router_logits(1999, min(T, 1024), EXPERTS, bias), SELECTED, replicate) if replicate else []
+    layers = [EpLayer(ctx, 100 + i, CHANNELS, HIDDEN, EXPERTS, SELECTED, dev, T, prefill=prefill, replicated=rep, scratch=scratch) for i in range(layers_n)]
+    for l in layers[1:]:
+        l.scratch = layers[0].scratch
     host_x = [torch.from_numpy(synth.activations_f16(1000 + rank * 64 + b, T, CHANNELS)).pin_memory() for b in range(nb)]
-    host_lg = [torch.from_numpy(synth.router_logits(2000 + rank * 64 + b, T, EXPERTS, bias) if prefill else synth.router_logits(2000 + rank * 64 + b, T, EXPERTS)).pin_memory()
-               for b in range(nb)]
-    dev_x = [t.to(dev) for t in host_x]
-    dev_lg = [t.to(dev) for t in host_lg]
+    host_lg = [torch.from_numpy(synth.router_logits(2000 + rank * 64 + b, T, EXPERTS, bias)).pin_memory() for b in range(nb)]
+    dev_x, dev_lg = [t.to(dev) for t in host_x], [t.to(dev) for t in host_lg]
     out = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
     host_out = torch.zeros((T, CHANNELS), dtype=torch.float16).pin_memory()
-    sx = torch.zeros((T, CHANNELS), dtype=torch.float16, device=dev)
-    slg = torch.zeros((T, EXPERTS), dtype=torch.float32, device=dev)
+    sx, slg = torch.zeros_like(dev_x[0]), torch.zeros_like(dev_lg[0])
     stream = torch.cuda.current_stream()
-    step = EpLayer.step if getattr(args, "ep_scheme", "gather") == "alltoall" else EpLayer.step_gathered
-    if prefill:
-        step = EpLayer.step_gathered_prefill
 
     def resident(i):
-        step(layers[i % len(layers)], dev_x[i % nb], dev_lg[i % nb], out)
+        layers[i % len(layers)].step(dev_x[i % nb], dev_lg[i % nb], out)
 
     def e2e(i):
         sx.copy_(host_x[i % nb], non_blocking=True)
         slg.copy_(host_lg[i % nb], non_blocking=True)
-        step(layers[i % len(layers)], sx, slg, out)
+        layers[i % len(layers)].step(sx, slg, out)
         host_out.copy_(out, non_blocking=True)
         stream.synchronize()
 
-    def timed(fn):
-        for i in range(args.warmup):
-            fn(i)
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(args.steps):
-            fn(args.warmup + i)
-        e1.record()
-        dist.barrier()
-        torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    with ClockSampler(local) as clocks:
-        ms = timed(resident)
-        ms_e2e = timed(e2e)
+    steps, warmup = (max(3, args.steps // 4), max(3, args.warmup)) if prefill else (args.steps, max(3, args.warmup))
+    ms = _timed(resident, steps, warmup, dev)
+    ms_e2e = _timed(e2e, steps, warmup, dev)
     err = torch.tensor([sum(l.error_word() for l in layers)], device=dev)
     dist.all_reduce(err, op=dist.ReduceOp.MAX)
     assert int(err.item()) == 0, "device error word set during the benchmark"
+    # parity of this rank's rows of batch 0 against the CPU oracle needs the whole layer's weights: done at N = 1 only
+    return {"ms": ms, "ms_e2e": ms_e2e, "tokens_per_rank": T, "replicated_experts": len(rep), "layers": layers, "steps": steps}
+
+
+def run_bench(args, rank: int, world: int, local: int) -> None:
+    """`bench.py --gpus N` for N > 1: every rank brings its own batch (weak scaling), experts are sharded 512/N per GPU, dispatch and
+    combine are NCCL all-to-all exchanges inside one C call per layer step; value = all ranks' tokens / max-over-ranks device time."""
+    from . import synth
+    from bench import CHANNELS, HIDDEN, EXPERTS, SELECTED, ClockSampler, GGUF_EXPERT_GATE_UP, GGUF_EXPERT_DOWN, FLOPS_PER_ROUTE, peaks
+    dev = torch.device("cuda", local)
+    ctx = EpContext(rank, world, dev)
+    T = args.tokens
+    nb = 8
+    with ClockSampler(local) as clocks:
+        dec = _phase(ctx, args, rank, world, dev, False, T, args.layers, nb, 0)
+        scratch = dec["layers"][0].scratch
+        dec["layers"] = None
+        torch.cuda.empty_cache()
+        pre = None
+        if not getattr(args, "no_prefill", False):
+            pre = _phase(ctx, args, rank, world, dev, True, args.prefill_tokens, 1, 2, args.replicate)
+            pre["layers"] = None
     if rank == 0:
+        hbm_peak, tf_peak, peak_kind = peaks()
         total = T * world
-        line = {"metric": "moe_q4k_expert_gemm_tokens_per_s", "value": total / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": (f"moe_layer_prefill_T{T}_per_gpu (BASELINE configs[2] shape and router, expert-parallel as configs[4])" if prefill
-                                        else f"moe_layer_decode_T{T}_per_gpu (BASELINE configs[1] shape, expert-parallel as configs[4])"),
+        # algorithmic bytes of a decode step per GPU: the experts its batch of the step hits among the experts it owns, read once
+        per = EXPERTS // world
+        uniq = []
+        for b in range(nb):
+            ids = np.concatenate([np.argsort(-synth.router_logits(2000 + r * 64 + b, T, EXPERTS), axis=1, kind="stable")[:, :SELECTED].ravel() for r in range(world)])
+            hit = np.unique(ids)
+            uniq.append(max(int(((hit // per) == g).sum()) for g in range(world)))
+        u_max = float(np.mean(uniq))
+        step_bytes = (u_max + 1) * (GGUF_EXPERT_GATE_UP + GGUF_EXPERT_DOWN)
+        line = {"metric": "moe_q4k_expert_gemm_tokens_per_s", "value": total / (dec["ms"] * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": dec["ms"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16 activations, f32 accumulate", "data": "synthetic",
+                "config": {"workload": f"moe_layer_decode_T{T}_per_gpu (BASELINE configs[1] shape, expert-parallel as configs[4])",
                            "hidden": CHANNELS, "experts": EXPERTS, "expert_ffn": HIDDEN, "top_k": SELECTED, "weights": "Q4_K Pack-v3 planar",
                            "parallelism": f"ep{world}", "experts_per_gpu": EXPERTS // world, "tokens_per_gpu": T,
-                           "collectives": ("NCCL all-to-all dispatch (binary16 rows) + all-to-all combine (FP32 rows), one count exchange" if step is EpLayer.step
-                                           else "NCCL all-gather of token rows + logits, reduce-scatter of per-token partial sums (FP32)"),
+                           "collectives": "NCCL all-to-all dispatch (binary16 token rows, each token once per destination rank, fixed-size slabs with a "
+                                          "device-side count) + NCCL all-to-all combine (per-row partial sums); no host synchronisation in a step",
                            "l2_policy": "layers rotate; per step each GPU streams its hit experts once"},
-                "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "e2e": {"value": total / (dec["ms_e2e"] * 1e-3), "unit": "tokens/s", "ms_per_step": dec["ms_e2e"],
                         "h2d_bytes_per_step": world * (T * CHANNELS * 2 + T * EXPERTS * 4), "d2h_bytes_per_step": world * T * CHANNELS * 2},
-                "gpu_launches": (19 if prefill else 10 if step is EpLayer.step else 12) * args.steps, "clocks": clocks.summary(),
-                "roofline": None, "cpu_baseline": None}
+                "gpu_launches": 17 * args.steps, "clocks": clocks.summary(),
+                "roofline": {"bound": "hbm", "kernel": "whole expert-parallel decode step on the busiest GPU (its hit experts + the shared expert, gate-up and down)",
+                             "achieved": step_bytes / (dec["ms"] * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                             "frac": step_bytes / (dec["ms"] * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                             "algorithmic_bytes_per_step": step_bytes, "experts_hit_on_busiest_gpu": u_max},
+                "cpu_baseline": None, "extra": {}}
+        if pre is not None:
+            Tp = pre["tokens_per_rank"]
+            flops = world * Tp * (SELECTED + 1) * FLOPS_PER_ROUTE
+            line["extra"]["prefill"] = {"tokens_per_s": world * Tp / (pre["ms"] * 1e-3), "ms_per_step": pre["ms"], "tokens_per_gpu": Tp,
+                                        "e2e_tokens_per_s": world * Tp / (pre["ms_e2e"] * 1e-3), "tflops": flops / (pre["ms"] * 1e-3) / 1e12,
+                                        "frac_of_bf16_peak_all_gpus": flops / (pre["ms"] * 1e-3) / 1e12 / (tf_peak * world),
+                                        "replicated_experts": pre["replicated_experts"], "router": "N(0,1) + Zipf(1.1) per-expert bias", "scaling": "weak"}
         print(json.dumps(line), flush=True)
     dist.barrier()
+    ctx.close()
     dist.destroy_process_group()

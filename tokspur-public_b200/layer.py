@@ -176,11 +176,15 @@ class SynthDeviceLayer:
 
     def __init__(self, seed: int, channels: int, hidden: int, experts: int, expert_type: int = formats.Q4_K,
                  layout: int = formats.PLANAR, device="cuda", sigma: float = 0.02, expert_range: tuple[int, int] | None = None,
-                 keep_gguf: bool = False):
+                 keep_gguf: bool = False, expert_ids: list[int] | None = None):
         lib = capi.lib()
         lo, hi = expert_range if expert_range else (0, experts)
-        n = hi - lo
-        self.channels, self.hidden, self.experts_global, self.experts_local, self.first_expert = channels, hidden, experts, n, lo
+        # `expert_ids` names the routed experts held one by one (expert parallelism with replicated experts): local slot i holds
+        # global expert expert_ids[i]
+        ids = list(expert_ids) if expert_ids is not None else list(range(lo, hi))
+        n = len(ids)
+        self.channels, self.hidden, self.experts_global, self.experts_local, self.first_expert = channels, hidden, experts, n, ids[0]
+        self.expert_ids = ids
         self.type, self.layout = expert_type, layout
         epb = 256 if expert_type == formats.Q4_K else 32
         gb = int(lib.tsp_expert_bytes(expert_type, formats.GGUF, hidden, channels))
@@ -189,13 +193,21 @@ class SynthDeviceLayer:
         st = stream_ptr()
         u8 = lambda nbytes: torch.empty(int(nbytes), dtype=torch.uint8, device=device)
 
-        def gen(stream_seed, count, first):
-            t = u8(count * gb)
-            capi.call("tsp_synth_weights", expert_type, stream_seed, first * blocks_per_expert, count * blocks_per_expert, sigma, t.data_ptr(), st)
+        def gen(stream_seed, which):
+            """The experts `which` (global ids) of one weight stream; runs of consecutive ids become one call."""
+            t = u8(len(which) * gb)
+            at = 0
+            while at < len(which):
+                run = 1
+                while at + run < len(which) and which[at + run] == which[at] + run:
+                    run += 1
+                capi.call("tsp_synth_weights", expert_type, stream_seed, which[at] * blocks_per_expert, run * blocks_per_expert, sigma,
+                          t.data_ptr() + at * gb, st)
+                at += run
             return t
 
-        g, u, d = gen(seed * 8 + 0, n, lo), gen(seed * 8 + 1, n, lo), gen(seed * 8 + 2, n, lo)
-        sg, su, sd = gen(seed * 8 + 3, 1, 0), gen(seed * 8 + 4, 1, 0), gen(seed * 8 + 5, 1, 0)
+        g, u, d = gen(seed * 8 + 0, ids), gen(seed * 8 + 1, ids), gen(seed * 8 + 2, ids)
+        sg, su, sd = gen(seed * 8 + 3, [0]), gen(seed * 8 + 4, [0]), gen(seed * 8 + 5, [0])
         self.shared_router = torch.empty(channels, dtype=torch.float32, device=device)
         capi.call("tsp_synth_weights", capi.TYPE_F32, seed * 8 + 6, 0, channels, sigma, self.shared_router.data_ptr(), st)
         self.gguf = dict(gate=g, up=u, down=d, shared_gate=sg, shared_up=su, shared_down=sd) if keep_gguf or layout == formats.GGUF else None

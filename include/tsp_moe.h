@@ -346,8 +346,8 @@ int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratc
  * loads the library gives up that much memory until the process exits.
  *
  *  - Limit: the layer shape and token count must fit the array; tsp_moe_layer_decode_static_bytes() tells what
- *    a call needs (0 for an invalid shape). At hidden 2048 / FFN 512 / 512 experts / top-10 that is 32 token
- *    rows. Anything larger is refused with TSP_E_ARG and a message naming both sizes; nothing is launched.
+ *    a call needs (0 for an invalid shape). At hidden 2048 / FFN 512 / 512 experts / top-10 that is 34 token
+ *    rows (4 187 904 of the 4 194 304 bytes; 35 rows need 4 310 784). Anything larger is refused with TSP_E_ARG and a message naming both sizes; nothing is launched.
  *  - The first call on each device looks up the array's device address (with that device current). Make that
  *    first call during start-up, before any stream capture begins.
  *  - No cudaMalloc / cudaFree / allocating library routine is called, on the first call or later.

@@ -47,7 +47,7 @@ def run_ordinary(dl, x, logits, shape):
     return out.cpu().numpy()
 
 
-def test_static_scratch_entry_matches_caller_scratch_entry_twice_in_a_row():
+def test_static_scratch_entry_matches_caller_scratch_entry_twice_in_a_row(oracle):
     shape = (512, 256, 16, 4)
     Cn, H, E, K = shape
     host = L.synth_host_layer(21, Cn, H, E, K, expert_type=formats.Q4_K)
@@ -59,13 +59,44 @@ def test_static_scratch_entry_matches_caller_scratch_entry_twice_in_a_row():
         want = run_ordinary(dl, x, logits, shape)
         assert scaled_error(got.astype(np.float32), want.astype(np.float64)) <= 5e-5
         assert np.array_equal(got, want)   # same kernels, same order of operations: the rows agree bit for bit
+        if dtype == torch.float32:         # and against the CPU oracle directly, not only through the other entry point
+            truth, _ = oracle.moe_layer(host.oracle_dict(), x.cpu().numpy(), logits.cpu().numpy(), threads=4, stages=True)
+            assert scaled_error(got, truth) <= 5e-5
+
+
+def test_static_scratch_entry_leaves_device_memory_alone():
+    """Free device memory as the driver reports it (cudaMemGetInfo) is the same before and after calls of the entry point.
+    Inputs and outputs are allocated up front. One call is made before the first reading: with lazy module loading the CUDA
+    driver places a library's kernel image, of which the built-in array is a part, on the device when the first kernel of the
+    image launches; that is the cost of loading the library, paid once, and not an allocation the entry point makes."""
+    shape = (512, 256, 16, 4)
+    Cn, H, E, K = shape
+    host = L.synth_host_layer(22, Cn, H, E, K, expert_type=formats.Q4_K)
+    dl = L.DeviceLayer(host, formats.PLANAR, "cuda")
+    T = 8
+    x = torch.from_numpy(synth.activations_f16(50, T, Cn)).cuda().float()
+    logits = torch.from_numpy(synth.router_logits(51, T, E)).cuda()
+    out = torch.zeros((T, Cn), dtype=torch.float32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = (C.byref(dl.weights), x.data_ptr(), Cn * 4, 0, logits.data_ptr(), E * 4, T, Cn, H, E, K, 0, 1, out.data_ptr(), Cn * 4, 0,
+            err.data_ptr(), L.stream_ptr())
+    capi.call("tsp_moe_layer_decode_static", *args)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        capi.call("tsp_moe_layer_decode_static", *args)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, f"free device memory moved by {free_before - free_after} bytes across the call"
+    assert int(err.item()) == 0
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit():
     lib = capi.lib()
     limit = 4 << 20
-    assert 0 < lib.tsp_moe_layer_decode_static_bytes(32, 2048, 512, 512, 10) <= limit
-    assert lib.tsp_moe_layer_decode_static_bytes(64, 2048, 512, 512, 10) > limit
+    # the benchmark layer shape: 34 token rows are the most the array holds
+    assert lib.tsp_moe_layer_decode_static_bytes(34, 2048, 512, 512, 10) == 4187904 <= limit
+    assert lib.tsp_moe_layer_decode_static_bytes(35, 2048, 512, 512, 10) == 4310784 > limit
     shape = (512, 256, 16, 4)
     host = L.synth_host_layer(21, *shape, expert_type=formats.Q4_K)
     dl = L.DeviceLayer(host, formats.PLANAR, "cuda")

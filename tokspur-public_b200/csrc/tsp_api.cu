@@ -1,6 +1,7 @@
 // C ABI of the MoE hot path: argument validation (refused before any launch, as the reference's
 // FormatError checks are), then the launches. No entry point allocates, frees or reads results back
 // except tsp_error_word_read, which is the once-per-batch readback of the sticky error word.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -560,7 +561,7 @@ namespace {
 // The array's name is only a host-side handle; kernels need its device address, which is looked up once per
 // device (with that device current) and remembered here.
 constexpr int kMaxDevices = 64;
-unsigned char* g_static_scratch_addr[kMaxDevices] = {};
+std::atomic<unsigned char*> g_static_scratch_addr[kMaxDevices] = {};   // two host threads may make a device's first call at once
 
 struct StaticPlan {
     uint64_t ids, weights, hidden, routed, shared_hidden, shared_out, shared_logit, x32, token_map, counts, tasks, total;
@@ -640,13 +641,12 @@ int tsp_moe_layer_decode_static(const tsp_moe_weights* w, const void* d_x, uint6
     int dev = 0;
     TSP_CUDA(cudaGetDevice(&dev));
     TSP_REQUIRE(dev >= 0 && dev < kMaxDevices, "static layer: device ordinal %d out of range", dev);
-    if (!g_static_scratch_addr[dev]) {   // first call on this device: resolve the array's device address
-        unsigned char* addr = nullptr;
-        TSP_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_static_scratch));
-        TSP_REQUIRE(addr != nullptr, "static layer: the scratch array has no device address");
-        g_static_scratch_addr[dev] = addr;
+    unsigned char* base = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!base) {   // first call on this device: resolve the array's device address (every racing thread resolves the same value)
+        TSP_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_static_scratch));
+        TSP_REQUIRE(base != nullptr, "static layer: the scratch array has no device address");
+        g_static_scratch_addr[dev].store(base, std::memory_order_release);
     }
-    unsigned char* base = g_static_scratch_addr[dev];
     tsp_moe_scratch s{};
     s.d_ids = reinterpret_cast<uint32_t*>(base + pl.ids);
     s.d_weights = reinterpret_cast<float*>(base + pl.weights);

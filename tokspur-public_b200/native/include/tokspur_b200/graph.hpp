@@ -71,6 +71,35 @@ public:
     void gemv_f32_rows(GpuView matrix, GpuView input, uint64_t in_stride_bytes, uint32_t tokens, GpuView output, uint64_t out_stride_bytes,
                        uint32_t columns, uint32_t rows);
     void route(GpuView logits, GpuView indices, GpuView weights, uint32_t selected, RouterMode mode, bool normalize_selected);
+    // Dense projections through the decode-size kernels (graph.hpp:730-746, 780): encoding 0 (F32 rows), 8 (Q8_0) or 12 (Q4_K); a
+    // quantised matrix is GGUF rows unless it was registered as a planar matrix. out[t][r] = sum_c W[r][c] in[t][c].
+    void gemv(uint32_t encoding, GpuView matrix, GpuView input, GpuView output, uint32_t columns, uint32_t rows);
+    void gemv_rows(uint32_t encoding, GpuView matrix, GpuRowsF32 input, GpuRowsF32 output);
+    // `width` token-major input rows of `columns` values, output rows of `rows` values, both densely packed (q8_many.cpp:20-29)
+    void q8_matvec_many(GpuView matrix, GpuView input, GpuView output, uint32_t columns, uint32_t rows, uint32_t width);
+    void verify_nax_dense_q8(GpuView matrix, GpuRowsF32 input, GpuRowsF32 output);
+    // Batched routing and mixture (graph.hpp:852-853): `tokens` rows of `experts` logits; expert outputs [tokens*selected x channels]
+    void prefill_route_batch(GpuView logits, GpuView indices, GpuView weights, uint32_t experts, uint32_t selected, uint32_t tokens,
+                             RouterMode mode, bool normalize_selected);
+    void prefill_mixture_batch(GpuView experts, GpuView weights, GpuView shared, GpuView shared_logit, GpuRowsF32 output, uint32_t selected);
+    void mixture(GpuView expert_outputs, GpuView weights, GpuView shared_output, GpuView shared_logit, GpuView output);   // graph.hpp:1102
+    // Router projection of a batch with the shared-router row in the same pass (moe_router_f32_window + moe_shared_router_rows,
+    // graph.mm:5812, 5884) and the router-margin audit (graph.hpp:162-172, graph.mm:4911-4985)
+    void moe_router_rows(GpuView router, GpuView shared_router, GpuRowsF32 input, GpuView logits, GpuView shared_logits, uint32_t experts);
+    void configure_router_margin_audit(bool enabled) { require_idle(); margin_audit_ = enabled; }
+    void configure_router_margin_epsilon(float epsilon);
+    [[nodiscard]] bool router_margin_audit() const noexcept { return margin_audit_; }
+    [[nodiscard]] tsp_router_margin_telemetry router_margin_telemetry() const noexcept { return margin_telemetry_; }
+    void reset_router_margin_telemetry() noexcept { margin_telemetry_ = {}; }
+    // routes `tokens` (<= 2048) rows; with the audit enabled it also records each row's top-k margin into the scratch that
+    // prepare_router_margin_scratch() allocated between batches (encode calls never allocate)
+    void prepare_router_margin_scratch();
+    void moe_route_rows(GpuView logits, GpuView indices, GpuView weights, uint32_t experts, uint32_t selected, uint32_t tokens, RouterMode mode,
+                        bool normalize_selected);
+    [[nodiscard]] bool evaluate_router_margin(uint32_t tokens);   // waits for the stream; true when a row's margin is within 2 epsilon
+    // Hyper-connection residual read / write around the FFN sub-layer (graph.hpp:1056-1058)
+    void residual_read(GpuView normalized, GpuView scores, GpuView inject_logits, GpuView output, GpuView scales, uint32_t branches, uint32_t channels);
+    void residual_write(GpuView streams, GpuView output, GpuView scales, GpuView destination);
 
     // raw access for the composed encoders in moe.cpp
     [[nodiscard]] void* device_pointer(GpuView view, bool for_write = false) const;
@@ -95,7 +124,11 @@ private:
     uint32_t* error_ = nullptr;
     void* stream_ = nullptr;
     void *ev0_ = nullptr, *ev1_ = nullptr;
-    bool in_batch_ = false, frozen_ = false;
+    bool in_batch_ = false, frozen_ = false, margin_audit_ = false;
+    float margin_epsilon_ = 1.0e-4f;
+    float* margins_ = nullptr;            // per-row top-k margins of the last moe_route_rows (2048 rows, as the reference's scratch)
+    tsp_router_margin_telemetry margin_telemetry_{};
+    tsp_matrix_set dense_set(uint32_t encoding, GpuView matrix, uint32_t columns, uint32_t rows) const;
     uint64_t dispatches_ = 0;
     double batch_start_ = 0;
 };

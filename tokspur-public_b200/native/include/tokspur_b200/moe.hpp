@@ -42,4 +42,20 @@ MoeScratch allocate_moe_rows_scratch(CudaGraph& graph, MoeShape shape, uint32_t 
 void encode_verify_nax_moe(CudaGraph& graph, const MoeWeights& weights, const MoeScratch& scratch, const VerifyNaxMoeScratch& nax_moe,
                            GpuView input, GpuView output, MoeShape shape, RouterMode mode, bool normalize_selected, uint32_t steps);
 
+// Known-input FFN over up to 64 densely packed rows through the decode-size kernels (native/include/tokspur/moe_many.hpp:5-19): the
+// scratch is the row scratch for `capacity` rows, encode only; `steps` beyond the capacity or the views is refused.
+struct MoeManyScratch {
+    MoeScratch rows;
+    uint32_t capacity = 0;
+};
+MoeManyScratch allocate_moe_many_scratch(CudaGraph& graph, MoeShape shape, uint32_t capacity);
+void release_moe_many_scratch(CudaGraph& graph, const MoeManyScratch& scratch);
+// Checks the weights against the shape between batches, so that a wrong tensor is refused before the first token (prepare_moe_many,
+// moe_many.hpp:16). Kernels here need no pipeline objects, so nothing else is prepared.
+void prepare_moe_many(CudaGraph& graph, const MoeWeights& weights, MoeShape shape);
+// Launches one encode_moe_many of `steps` rows issues (the figure CommandBatch::dispatches grows by)
+uint64_t moe_many_dispatches(const CudaGraph& graph, const MoeWeights& weights, MoeShape shape, uint32_t steps);
+void encode_moe_many(CudaGraph& graph, const MoeWeights& weights, const MoeManyScratch& scratch, GpuView input, GpuView output, MoeShape shape,
+                     RouterMode mode, bool normalize_selected, uint32_t steps);
+
 }  // namespace tokspur_b200

@@ -10,6 +10,15 @@
 namespace tokspur_b200 {
 
 
+// Registered identity of each weight tensor on the prefill path (native/include/tokspur/moe_mm_many.hpp:7-10). The grouped tensor-core
+// GEMMs read the Pack v3 planar form only, so every member must say `planar` and match a registered planar matrix; raw GGUF bytes
+// are refused, never repacked behind the caller's back.
+enum class PrefillWeightLayout : uint32_t { gguf = 0, planar = 1 };
+struct MoeMmLayouts {
+    PrefillWeightLayout gate = PrefillWeightLayout::planar, up = PrefillWeightLayout::planar, down = PrefillWeightLayout::planar;
+    PrefillWeightLayout shared_gate = PrefillWeightLayout::planar, shared_up = PrefillWeightLayout::planar, shared_down = PrefillWeightLayout::planar;
+};
+
 constexpr size_t kMoeMmManyViews = 14;
 struct MoeMmManyBytes {
     std::array<uint64_t, kMoeMmManyViews> views{};
@@ -33,6 +42,12 @@ void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scrat
 // Encode only. The caller owns allocation, the batch and the committed state. Weights must be the registered planar tensors
 // (is_planar_moe) with a Q4_K planar shared expert; anything else is refused before the first launch.
 void encode_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, const MoeMmManyScratch& scratch, GpuRowsF32 input, GpuRowsF32 output,
-                        MoeShape shape, RouterMode mode, bool normalize_selected);
+                        MoeShape shape, RouterMode mode, bool normalize_selected, MoeMmLayouts layouts = {});
+// The weight checks of the encoder, run between batches (prepare_moe_mm_many, moe_mm_many.hpp:59): a tensor of the wrong form or
+// extent is refused before the first token instead of in the middle of a prompt.
+void prepare_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, MoeShape shape, MoeMmLayouts layouts = {});
+// Launches one encode_moe_mm_many of `rows` rows issues with a scratch of `capacity` rows (moe_mm_many_dispatches, moe_mm_many.hpp:60;
+// the reference's chunk is fixed, here it is the scratch capacity).
+uint64_t moe_mm_many_dispatches(const CudaGraph& graph, const MoeWeights& weights, MoeShape shape, uint32_t rows, uint32_t capacity);
 
 }  // namespace tokspur_b200

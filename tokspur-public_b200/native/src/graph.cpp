@@ -34,6 +34,7 @@ CudaGraph::~CudaGraph() {
     cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
     for (auto& b : buffers_) if (b.live) cudaFree(b.ptr);
     cudaFree(error_);
+    if (margins_) cudaFree(margins_);
     cudaEventDestroy(static_cast<cudaEvent_t>(ev0_));
     cudaEventDestroy(static_cast<cudaEvent_t>(ev1_));
     cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
@@ -203,6 +204,142 @@ void CudaGraph::route(GpuView logits, GpuView indices, GpuView weights, uint32_t
     if (logits.bytes % 4 || indices.bytes != uint64_t(selected) * 4 || weights.bytes != uint64_t(selected) * 4) throw FormatError("invalid router shape/mode");
     check(tsp_moe_route(static_cast<const float*>(device_pointer(logits)), logits.bytes, 1, experts, selected, uint32_t(mode), normalize_selected,
                         static_cast<uint32_t*>(device_pointer(indices, true)), static_cast<float*>(device_pointer(weights, true)), error_, stream_));
+    ++dispatches_;
+}
+
+
+// ---- dense projections --------------------------------------------------------------------------------------------------
+tsp_matrix_set CudaGraph::dense_set(uint32_t encoding, GpuView matrix, uint32_t columns, uint32_t rows) const {
+    if (encoding != TSP_TYPE_Q8_0 && encoding != TSP_TYPE_Q4_K) throw FormatError("unsupported GEMV encoding");
+    const auto planar = planar_matrix_shape(matrix);
+    const uint32_t layout = planar ? TSP_LAYOUT_PLANAR : TSP_LAYOUT_GGUF;
+    const uint64_t bytes = tsp_expert_bytes(encoding, layout, rows, columns);
+    if (!bytes || matrix.bytes != bytes) throw FormatError("GEMV shape mismatch");
+    return tsp_matrix_set{device_pointer(matrix), nullptr, bytes, 1, 1, rows, columns, encoding, layout};
+}
+
+void CudaGraph::gemv(uint32_t encoding, GpuView matrix, GpuView input, GpuView output, uint32_t columns, uint32_t rows) {
+    gemv_rows(encoding, matrix, {input, 1, columns, uint64_t(columns) * 4}, {output, 1, rows, uint64_t(rows) * 4});
+}
+
+void CudaGraph::gemv_rows(uint32_t encoding, GpuView matrix, GpuRowsF32 input, GpuRowsF32 output) {
+    require_batch();
+    if (!input.rows || input.rows != output.rows || input.view.bytes < uint64_t(input.rows - 1) * input.stride_bytes + uint64_t(input.columns) * 4 ||
+        output.view.bytes < uint64_t(output.rows - 1) * output.stride_bytes + uint64_t(output.columns) * 4)
+        throw FormatError("GEMV shape mismatch");
+    if (encoding == 0) { gemv_f32_rows(matrix, input.view, input.stride_bytes, input.rows, output.view, output.stride_bytes, input.columns, output.columns); return; }
+    const auto set = dense_set(encoding, matrix, input.columns, output.columns);
+    check(tsp_moe_project(&set, static_cast<const float*>(device_pointer(input.view)), input.stride_bytes, 1, input.rows, 1, nullptr, nullptr, nullptr,
+                          static_cast<float*>(device_pointer(output.view, true)), output.stride_bytes, 0, error_, stream_));
+    ++dispatches_;
+}
+
+void CudaGraph::q8_matvec_many(GpuView matrix, GpuView input, GpuView output, uint32_t columns, uint32_t rows, uint32_t width) {
+    if (!width || width > 64 || input.bytes != uint64_t(columns) * width * 4 || output.bytes != uint64_t(rows) * width * 4) throw FormatError("Q8 many-row shape mismatch");
+    gemv_rows(TSP_TYPE_Q8_0, matrix, {input, width, columns, uint64_t(columns) * 4}, {output, width, rows, uint64_t(rows) * 4});
+}
+
+void CudaGraph::verify_nax_dense_q8(GpuView matrix, GpuRowsF32 input, GpuRowsF32 output) {
+    if (input.rows < 1 || input.rows > 16) throw FormatError("verify batch must hold 1..16 rows");
+    gemv_rows(TSP_TYPE_Q8_0, matrix, input, output);
+}
+
+// ---- batched routing, mixture, router projection with the margin audit -----------------------------------------------------
+void CudaGraph::prefill_route_batch(GpuView logits, GpuView indices, GpuView weights, uint32_t experts, uint32_t selected, uint32_t tokens,
+                                    RouterMode mode, bool normalize_selected) {
+    require_batch();
+    if (!tokens || logits.bytes != uint64_t(tokens) * experts * 4 || indices.bytes != uint64_t(tokens) * selected * 4 || weights.bytes != indices.bytes)
+        throw FormatError("invalid router shape/mode");
+    check(tsp_moe_route(static_cast<const float*>(device_pointer(logits)), uint64_t(experts) * 4, tokens, experts, selected, uint32_t(mode), normalize_selected,
+                        static_cast<uint32_t*>(device_pointer(indices, true)), static_cast<float*>(device_pointer(weights, true)), error_, stream_));
+    ++dispatches_;
+}
+
+void CudaGraph::prefill_mixture_batch(GpuView experts, GpuView weights, GpuView shared, GpuView shared_logit, GpuRowsF32 output, uint32_t selected) {
+    require_batch();
+    const uint32_t tokens = output.rows, channels = output.columns;
+    if (!tokens || !selected || experts.bytes != uint64_t(tokens) * selected * channels * 4 || weights.bytes != uint64_t(tokens) * selected * 4 ||
+        shared.bytes != uint64_t(tokens) * channels * 4 || shared_logit.bytes != uint64_t(tokens) * 4 ||
+        output.view.bytes < uint64_t(tokens - 1) * output.stride_bytes + uint64_t(channels) * 4)
+        throw FormatError("mixture shape mismatch");
+    check(tsp_moe_combine(device_pointer(experts), uint64_t(channels) * 4, 0, static_cast<const float*>(device_pointer(weights)),
+                          static_cast<const float*>(device_pointer(shared)), uint64_t(channels) * 4, nullptr, nullptr, 0, 0,
+                          static_cast<float*>(device_pointer(shared_logit)), tokens, channels, selected, static_cast<float*>(device_pointer(output.view, true)),
+                          output.stride_bytes, nullptr, 0, error_, stream_));
+    ++dispatches_;
+}
+
+void CudaGraph::mixture(GpuView expert_outputs, GpuView weights, GpuView shared_output, GpuView shared_logit, GpuView output) {
+    const uint32_t channels = static_cast<uint32_t>(output.bytes / 4), selected = static_cast<uint32_t>(weights.bytes / 4);
+    if (output.bytes % 4 || !channels) throw FormatError("mixture shape mismatch");
+    prefill_mixture_batch(expert_outputs, weights, shared_output, shared_logit, {output, 1, channels, uint64_t(channels) * 4}, selected);
+}
+
+void CudaGraph::moe_router_rows(GpuView router, GpuView shared_router, GpuRowsF32 input, GpuView logits, GpuView shared_logits, uint32_t experts) {
+    require_batch();
+    const uint32_t tokens = input.rows, columns = input.columns;
+    if (!tokens || router.bytes != uint64_t(experts) * columns * 4 || shared_router.bytes != uint64_t(columns) * 4 ||
+        logits.bytes != uint64_t(tokens) * experts * 4 || shared_logits.bytes != uint64_t(tokens) * 4 ||
+        input.view.bytes < uint64_t(tokens - 1) * input.stride_bytes + uint64_t(columns) * 4)
+        throw FormatError("router projection shape mismatch");
+    check(tsp_router_project(static_cast<const float*>(device_pointer(router)), experts, columns, static_cast<const float*>(device_pointer(shared_router)),
+                             static_cast<const float*>(device_pointer(input.view)), input.stride_bytes, tokens, static_cast<float*>(device_pointer(logits, true)),
+                             uint64_t(experts) * 4, static_cast<float*>(device_pointer(shared_logits, true)), error_, stream_));
+    ++dispatches_;
+}
+
+void CudaGraph::configure_router_margin_epsilon(float epsilon) {
+    require_idle();
+    if (!(epsilon > 0) || epsilon > 1e30f) throw FormatError("router margin epsilon must be positive finite");
+    margin_epsilon_ = epsilon;
+}
+
+void CudaGraph::moe_route_rows(GpuView logits, GpuView indices, GpuView weights, uint32_t experts, uint32_t selected, uint32_t tokens, RouterMode mode,
+                               bool normalize_selected) {
+    if (!margin_audit_) { prefill_route_batch(logits, indices, weights, experts, selected, tokens, mode, normalize_selected); return; }
+    require_batch();
+    if (!tokens || tokens > 2048 || logits.bytes != uint64_t(tokens) * experts * 4 || indices.bytes != uint64_t(tokens) * selected * 4 || weights.bytes != indices.bytes)
+        throw FormatError("router row top-k geometry/mode mismatch");
+    if (!margins_) throw FormatError("router margin audit: enable it and call prepare_router_margin_scratch() between batches first");
+    check(tsp_moe_route_audit(static_cast<const float*>(device_pointer(logits)), uint64_t(experts) * 4, tokens, experts, selected, uint32_t(mode), normalize_selected,
+                              static_cast<uint32_t*>(device_pointer(indices, true)), static_cast<float*>(device_pointer(weights, true)), margins_, error_, stream_));
+    ++dispatches_;
+}
+
+void CudaGraph::prepare_router_margin_scratch() {
+    require_idle();
+    select_device();
+    if (!margins_) cuda(cudaMalloc(reinterpret_cast<void**>(&margins_), 2048 * sizeof(float)), "router margin scratch");
+}
+
+bool CudaGraph::evaluate_router_margin(uint32_t tokens) {
+    if (!margins_ || !tokens) return false;
+    select_device();
+    int fallback = 0;
+    check(tsp_router_margin_evaluate(margins_, tokens, margin_epsilon_, stream_, &margin_telemetry_, &fallback));
+    return fallback != 0;
+}
+
+// ---- residual read / write ---------------------------------------------------------------------------------------------------
+void CudaGraph::residual_read(GpuView normalized, GpuView scores, GpuView inject_logits, GpuView output, GpuView scales, uint32_t branches, uint32_t channels) {
+    require_batch();
+    const uint64_t wide = uint64_t(branches) * channels * 4;
+    if (!branches || !channels || normalized.bytes != wide || scores.bytes != wide || inject_logits.bytes != uint64_t(branches) * 4 ||
+        output.bytes != uint64_t(channels) * 4 || scales.bytes != uint64_t(branches) * 4) throw FormatError("residual read shape mismatch");
+    check(tsp_residual_read(static_cast<const float*>(device_pointer(normalized)), static_cast<const float*>(device_pointer(scores)),
+                            static_cast<const float*>(device_pointer(inject_logits)), branches, channels, 1, static_cast<float*>(device_pointer(output, true)),
+                            static_cast<float*>(device_pointer(scales, true)), error_, stream_));
+    ++dispatches_;
+}
+
+void CudaGraph::residual_write(GpuView streams, GpuView output, GpuView scales, GpuView destination) {
+    require_batch();
+    const uint64_t channels = output.bytes / 4, branches = scales.bytes / 4;
+    if (!channels || !branches || output.bytes % 4 || scales.bytes % 4 || streams.bytes != branches * channels * 4 || destination.bytes != streams.bytes)
+        throw FormatError("residual write shape mismatch");
+    check(tsp_residual_write(static_cast<const float*>(device_pointer(streams)), static_cast<const float*>(device_pointer(output)),
+                             static_cast<const float*>(device_pointer(scales)), uint32_t(branches), uint32_t(channels), 1,
+                             static_cast<float*>(device_pointer(destination, true)), error_, stream_));
     ++dispatches_;
 }
 

@@ -70,6 +70,39 @@ void encode_moe(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView 
     encode_rows(g, w, s, input, output, shape, mode, normalize_selected, 1);
 }
 
+MoeManyScratch allocate_moe_many_scratch(CudaGraph& graph, MoeShape shape, uint32_t capacity) {
+    return {allocate_moe_rows_scratch(graph, shape, capacity), capacity};
+}
+
+void release_moe_many_scratch(CudaGraph& graph, const MoeManyScratch& scratch) { release_moe_scratch(graph, scratch.rows); }
+
+void prepare_moe_many(CudaGraph& g, const MoeWeights& w, MoeShape shape) {
+    shape_check(shape);
+    if (w.router.encoding != 0 || w.shared_router.encoding != 0) throw FormatError("router projections must be F32");
+    if (w.router.view.bytes != uint64_t(shape.channels) * shape.experts * 4 || w.shared_router.view.bytes != uint64_t(shape.channels) * 4)
+        throw FormatError("router shape mismatch");
+    if (!is_planar_moe(g, w, shape)) {
+        (void)matrix_set(g, w.gate, shape.hidden, shape.channels, shape.experts);
+        (void)matrix_set(g, w.up, shape.hidden, shape.channels, shape.experts);
+    }
+    (void)matrix_set(g, w.down, shape.channels, shape.hidden, shape.experts);
+    (void)matrix_set(g, w.shared_gate, shape.hidden, shape.channels, 1);
+    (void)matrix_set(g, w.shared_up, shape.hidden, shape.channels, 1);
+    (void)matrix_set(g, w.shared_down, shape.channels, shape.hidden, 1);
+}
+
+uint64_t moe_many_dispatches(const CudaGraph&, const MoeWeights&, MoeShape shape, uint32_t steps) {
+    shape_check(shape);
+    if (!steps || steps > 64) throw FormatError("invalid row count for the mixture");
+    return 5;   // router GEMV, prologue (routing + permutation + row conversion), gate-up, down, mixture
+}
+
+void encode_moe_many(CudaGraph& g, const MoeWeights& w, const MoeManyScratch& s, GpuView input, GpuView output, MoeShape shape, RouterMode mode,
+                     bool normalize_selected, uint32_t steps) {
+    if (!steps || steps > s.capacity) throw FormatError("mixture rows beyond the scratch capacity");
+    encode_rows(g, w, s.rows, input, output, shape, mode, normalize_selected, steps);
+}
+
 void encode_verify_nax_moe(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, const VerifyNaxMoeScratch&, GpuView input, GpuView output,
                            MoeShape shape, RouterMode mode, bool normalize_selected, uint32_t steps) {
     if (steps < 2 || steps > 8) throw FormatError("verify batch must hold 2..8 rows");

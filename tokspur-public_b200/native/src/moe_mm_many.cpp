@@ -43,27 +43,11 @@ void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scrat
     for (const auto view : scratch.views()) graph.release(view);
 }
 
-void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratch& s, GpuRowsF32 input, GpuRowsF32 output, MoeShape shape,
-                        RouterMode mode, bool normalize_selected) {
-    need(s.capacity > 0 && input.rows > 0 && input.rows == output.rows && input.columns == shape.channels && output.columns == shape.channels &&
-         uint32_t(mode) <= 1, "tiled MoE active rows/router mode");
-    for (const auto r : {input, output})
-        need(r.stride_bytes >= uint64_t(shape.channels) * 4 && r.stride_bytes % 16 == 0 &&
-             r.view.bytes >= uint64_t(r.rows - 1) * r.stride_bytes + uint64_t(shape.channels) * 4, "tiled MoE strided row extent");
-    if (input.rows > s.capacity) {   // longer batches: chunks of `capacity` rows
-        for (uint32_t r0 = 0; r0 < input.rows; r0 += s.capacity) {
-            const uint32_t n = std::min(s.capacity, input.rows - r0);
-            const uint64_t span_in = uint64_t(n - 1) * input.stride_bytes + uint64_t(input.columns) * 4;
-            const uint64_t span_out = uint64_t(n - 1) * output.stride_bytes + uint64_t(output.columns) * 4;
-            encode_moe_mm_many(g, w, s, {g.slice(input.view, uint64_t(r0) * input.stride_bytes, span_in), n, input.columns, input.stride_bytes},
-                               {g.slice(output.view, uint64_t(r0) * output.stride_bytes, span_out), n, output.columns, output.stride_bytes}, shape,
-                               mode, normalize_selected);
-        }
-        return;
-    }
-    const auto bytes = moe_mm_many_bytes(shape, s.capacity);
-    const auto all = s.views();
-    for (size_t i = 0; i < all.size(); ++i) need(all[i].bytes == bytes.views[i], "tiled MoE scratch capacity extent");
+namespace {
+constexpr uint64_t kLaunchesPerChunk = 10;   // router GEMM, K-ordered rows, route, routes, tasks, offsets, routed copy, gate-up, down, mixture
+tsp_moe_weights checked_weights(const CudaGraph& g, const MoeWeights& w, MoeShape shape, MoeMmLayouts l) {
+    for (const auto layout : {l.gate, l.up, l.down, l.shared_gate, l.shared_up, l.shared_down})
+        need(layout == PrefillWeightLayout::planar, "tiled MoE reads registered planar tensors only");
     need(w.router.encoding == 0 && w.shared_router.encoding == 0, "router projections must be F32");
     need(is_planar_moe(g, w, shape), "tiled MoE needs the registered planar expert tensors");
     need(w.router.view.bytes == uint64_t(shape.channels) * shape.experts * 4 && w.shared_router.view.bytes == uint64_t(shape.channels) * 4,
@@ -88,6 +72,44 @@ void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratc
     tw.shared_down = dense(w.shared_down, shape.channels, shape.hidden);
     tw.d_shared_router = static_cast<const float*>(g.device_pointer(w.shared_router.view));
 
+    return tw;
+}
+}  // namespace
+
+void prepare_moe_mm_many(CudaGraph& g, const MoeWeights& w, MoeShape shape, MoeMmLayouts layouts) {
+    (void)moe_mm_many_bytes(shape, 1);
+    (void)checked_weights(g, w, shape, layouts);
+}
+
+uint64_t moe_mm_many_dispatches(const CudaGraph& g, const MoeWeights& w, MoeShape shape, uint32_t rows, uint32_t capacity) {
+    (void)moe_mm_many_bytes(shape, capacity);
+    need(rows > 0, "tiled MoE active rows");
+    (void)checked_weights(g, w, shape, {});
+    return kLaunchesPerChunk * ((uint64_t(rows) + capacity - 1) / capacity);
+}
+
+void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratch& s, GpuRowsF32 input, GpuRowsF32 output, MoeShape shape,
+                        RouterMode mode, bool normalize_selected, MoeMmLayouts layouts) {
+    need(s.capacity > 0 && input.rows > 0 && input.rows == output.rows && input.columns == shape.channels && output.columns == shape.channels &&
+         uint32_t(mode) <= 1, "tiled MoE active rows/router mode");
+    for (const auto r : {input, output})
+        need(r.stride_bytes >= uint64_t(shape.channels) * 4 && r.stride_bytes % 16 == 0 &&
+             r.view.bytes >= uint64_t(r.rows - 1) * r.stride_bytes + uint64_t(shape.channels) * 4, "tiled MoE strided row extent");
+    if (input.rows > s.capacity) {   // longer batches: chunks of `capacity` rows
+        for (uint32_t r0 = 0; r0 < input.rows; r0 += s.capacity) {
+            const uint32_t n = std::min(s.capacity, input.rows - r0);
+            const uint64_t span_in = uint64_t(n - 1) * input.stride_bytes + uint64_t(input.columns) * 4;
+            const uint64_t span_out = uint64_t(n - 1) * output.stride_bytes + uint64_t(output.columns) * 4;
+            encode_moe_mm_many(g, w, s, {g.slice(input.view, uint64_t(r0) * input.stride_bytes, span_in), n, input.columns, input.stride_bytes},
+                               {g.slice(output.view, uint64_t(r0) * output.stride_bytes, span_out), n, output.columns, output.stride_bytes}, shape,
+                               mode, normalize_selected, layouts);
+        }
+        return;
+    }
+    const auto bytes = moe_mm_many_bytes(shape, s.capacity);
+    const auto all = s.views();
+    for (size_t i = 0; i < all.size(); ++i) need(all[i].bytes == bytes.views[i], "tiled MoE scratch capacity extent");
+    const tsp_moe_weights tw = checked_weights(g, w, shape, layouts);
     auto u32p = [&](GpuView v) { return static_cast<uint32_t*>(g.device_pointer(v, true)); };
     auto f32p = [&](GpuView v) { return static_cast<float*>(g.device_pointer(v, true)); };
     tsp_moe_prefill_scratch ps{};
@@ -104,7 +126,7 @@ void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratc
                                          uint64_t(shape.experts) * 4, n, shape.channels, shape.hidden, shape.experts, shape.selected, uint32_t(mode),
                                          normalize_selected, g.device_pointer(output.view, true), output.stride_bytes, 0, g.error_word(), g.stream());
     if (rc != TSP_OK) throw FormatError(tsp_last_error());
-    g.count_dispatches(9);   // K-ordered rows, route, routes, tasks, offsets, routed copy, gate-up, down (the shared expert rides in both), mixture
+    g.count_dispatches(kLaunchesPerChunk - 1);   // the router GEMM counted itself
 }
 
 }  // namespace tokspur_b200

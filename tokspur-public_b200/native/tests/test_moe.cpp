@@ -1,6 +1,7 @@
 // encode_moe and encode_moe_mm_many on the CUDA graph against the CPU oracle, in the style of the reference's native/tests/test_moe.cpp:
 // generated weights, route ids bit-equal, every stage within 5e-5 scaled error, refusals before encoding, sticky-error
 // recovery, allocation invariants. The oracle (oracle/tsp_oracle.h) is test infrastructure and is linked only here.
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <functional>
@@ -176,6 +177,20 @@ void verify_rows(CudaGraph& g, uint32_t type, MoeShape shape, uint32_t steps, ui
     require(read<uint32_t>(g, scratch.indices) == eids, "verify batch: route ids differ");
     close(read<float>(g, scratch.weights), ew.data(), ew.size());
     close(read<float>(g, output), expected.data(), expected.size());
+    // the same rows through encode_moe_many with its own capacity scratch
+    prepare_moe_many(g, w, shape);
+    const auto ms = allocate_moe_many_scratch(g, shape, steps);
+    g.write(output, std::vector<std::byte>(output.bytes));
+    g.begin();
+    encode_moe_many(g, w, ms, input, output, shape, RouterMode::softmax, true, steps);
+    const auto batch = g.submit();
+    require(batch.dispatches == moe_many_dispatches(g, w, shape, steps), "known-input FFN dispatch count");
+    require(read<uint32_t>(g, ms.rows.indices) == eids, "known-input FFN: route ids differ");
+    close(read<float>(g, output), expected.data(), expected.size());
+    g.begin();
+    refuses([&] { encode_moe_many(g, w, ms, input, output, shape, RouterMode::softmax, true, steps + 1); }, "rows beyond the scratch capacity accepted");
+    g.abort();
+    release_moe_many_scratch(g, ms);
     g.begin();
     refuses([&] { encode_verify_nax_moe(g, w, scratch, none, input, output, shape, RouterMode::softmax, true, 1); }, "one-row verify batch accepted");
     refuses([&] { encode_verify_nax_moe(g, w, scratch, none, input, output, shape, RouterMode::softmax, true, steps + 1); }, "rows beyond the views accepted");
@@ -228,11 +243,16 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
     tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1};
     std::vector<double> expected(size_t(rows) * C);
     require(tso_moe_layer(&L, x.data(), nullptr, rows, expected.data(), nullptr, 4) == TSO_OK, "oracle layer");
+    prepare_moe_mm_many(g, w, shape);
+    MoeMmLayouts raw;
+    raw.down = PrefillWeightLayout::gguf;
+    refuses([&] { prepare_moe_mm_many(g, w, shape, raw); }, "a raw GGUF identity was accepted by the tiled path");
+    refuses([&] { prepare_moe_mm_many(g, w, {C, H, E, E + 1}); }, "selected > experts accepted by prepare");
     for (int run = 0; run < 2; ++run) {
         g.begin();
         encode_moe_mm_many(g, w, scratch, {input, rows, C, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true);
         const auto batch = g.submit();
-        require(batch.dispatches >= 10 && g.allocations() == allocations, "dispatch / allocation invariant");
+        require(batch.dispatches == moe_mm_many_dispatches(g, w, shape, rows, capacity) && g.allocations() == allocations, "dispatch / allocation invariant");
         const auto raw = g.read(output);
         double num = 0, den = 0;
         for (uint32_t r = 0; r < rows; ++r)
@@ -253,6 +273,120 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
     refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows + 1, C, in_stride}, {output, rows + 1, C, out_stride}, shape, RouterMode::softmax, true); }, "rows beyond the views accepted");
     g.abort();
     release_moe_mm_many_scratch(g, scratch);
+}
+// The stand-alone operators of the graph (dense GEMV forms, batched routing with the margin audit, mixture, residual read / write)
+// against the oracle's functions.
+void operators(CudaGraph& g, uint32_t seed) {
+    const uint32_t C = 256, R = 96, T = 5, E = 16, K = 4, B = 4;
+    for (uint32_t type : {8u, 12u}) {
+        const auto m = generated(type, C, R, 1, seed + type);
+        const auto mv = g.upload(bytes(m), "dense matrix");
+        const auto x = activations(seed + 3, size_t(C) * T, 4.f);
+        const auto in = g.upload(bytes_of(x), "dense in"), out = g.zeros(uint64_t(R) * 4 * T, "dense out");
+        g.begin();
+        if (type == 8) g.q8_matvec_many(mv, in, out, C, R, T);
+        else g.gemv_rows(type, mv, {in, T, C, uint64_t(C) * 4}, {out, T, R, uint64_t(R) * 4});
+        (void)g.submit();
+        std::vector<double> expected(size_t(R) * T);
+        for (uint32_t t = 0; t < T; ++t) require(tso_gemv_f32(type, m.data(), m.size(), C, R, x.data() + size_t(t) * C, expected.data() + size_t(t) * R) == TSO_OK, "oracle gemv");
+        close(read<float>(g, out), expected.data(), expected.size());
+        if (type == 8) {
+            g.begin();
+            g.verify_nax_dense_q8(mv, {in, T, C, uint64_t(C) * 4}, {out, T, R, uint64_t(R) * 4});
+            g.gemv(type, mv, g.slice(in, 0, uint64_t(C) * 4), g.slice(out, 0, uint64_t(R) * 4), C, R);
+            (void)g.submit();
+            close(read<float>(g, out), expected.data(), expected.size());
+            g.begin();
+            refuses([&] { g.q8_matvec_many(mv, in, out, C, R, T + 1); }, "width beyond the views accepted");
+            refuses([&] { g.verify_nax_dense_q8(mv, {in, 17, C, uint64_t(C) * 4}, {out, 17, R, uint64_t(R) * 4}); }, "17-row verify batch accepted");
+            refuses([&] { g.gemv(5, mv, in, out, C, R); }, "unknown encoding accepted");
+            g.abort();
+        }
+    }
+    // router projection -> audited routing -> mixture
+    const auto router = activations(seed + 7, size_t(E) * C, 0.25f), srouter = activations(seed + 8, C, 0.125f);
+    const auto x = activations(seed + 9, size_t(C) * T, 1.f);
+    const auto rv = g.upload(bytes_of(router), "router"), sv = g.upload(bytes_of(srouter), "shared router"), xv = g.upload(bytes_of(x), "x");
+    const auto logits = g.zeros(uint64_t(T) * E * 4, "logits"), slog = g.zeros(T * 4, "shared logits");
+    const auto ids = g.zeros(T * K * 4, "ids"), wts = g.zeros(T * K * 4, "weights");
+    const auto ex = activations(seed + 10, size_t(T) * K * C, 2.f), sh = activations(seed + 11, size_t(T) * C, 2.f);
+    const auto exv = g.upload(bytes_of(ex), "expert rows"), shv = g.upload(bytes_of(sh), "shared rows"), mix = g.zeros(uint64_t(T) * C * 4, "mixture");
+    g.configure_router_margin_audit(true);
+    g.configure_router_margin_epsilon(1e-4f);
+    g.prepare_router_margin_scratch();
+    const auto allocations = g.allocations();
+    g.begin();
+    g.moe_router_rows(rv, sv, {xv, T, C, uint64_t(C) * 4}, logits, slog, E);
+    g.moe_route_rows(logits, ids, wts, E, K, T, RouterMode::softmax, true);
+    g.prefill_mixture_batch(exv, wts, shv, slog, {mix, T, C, uint64_t(C) * 4}, K);
+    (void)g.submit();
+    require(g.allocations() == allocations, "operators allocated while encoding");
+    const auto gl = read<float>(g, logits), gs = read<float>(g, slog), gw = read<float>(g, wts);
+    const auto gi = read<uint32_t>(g, ids);
+    std::vector<double> el(size_t(T) * E), es(T), emix(size_t(T) * C);
+    for (uint32_t t = 0; t < T; ++t) {
+        require(tso_gemv_f32(0, reinterpret_cast<const uint8_t*>(router.data()), router.size() * 4, C, E, x.data() + size_t(t) * C, el.data() + size_t(t) * E) == TSO_OK, "oracle router");
+        require(tso_gemv_f32(0, reinterpret_cast<const uint8_t*>(srouter.data()), srouter.size() * 4, C, 1, x.data() + size_t(t) * C, &es[t]) == TSO_OK, "oracle shared router");
+    }
+    close(gl, el.data(), el.size());
+    close(gs, es.data(), T);
+    double min_margin = 1e30;
+    for (uint32_t t = 0; t < T; ++t) {
+        // routing is checked on the logits the device produced, so a near-tie cannot flip an id between the two
+        std::vector<double> row(gl.begin() + size_t(t) * E, gl.begin() + size_t(t + 1) * E), ew(K), dex(size_t(K) * C), dsh(C);
+        std::vector<uint32_t> ei(K);
+        require(tso_route(row.data(), E, K, 0, 1, ei.data(), ew.data()) == TSO_OK, "oracle route");
+        require(std::equal(ei.begin(), ei.end(), gi.begin() + size_t(t) * K), "audited route ids differ");
+        close(std::vector<float>(gw.begin() + size_t(t) * K, gw.begin() + size_t(t + 1) * K), ew.data(), K);
+        std::vector<double> sorted(row);
+        std::sort(sorted.begin(), sorted.end(), std::greater<>());
+        min_margin = std::min(min_margin, sorted[K - 1] - sorted[K]);
+        for (size_t i = 0; i < dex.size(); ++i) dex[i] = ex[size_t(t) * K * C + i];
+        for (uint32_t c = 0; c < C; ++c) dsh[c] = sh[size_t(t) * C + c];
+        std::vector<double> w64(gw.begin() + size_t(t) * K, gw.begin() + size_t(t + 1) * K);
+        require(tso_mixture(dex.data(), w64.data(), K, dsh.data(), C, gs[t], emix.data() + size_t(t) * C) == TSO_OK, "oracle mixture");
+    }
+    close(read<float>(g, mix), emix.data(), emix.size());
+    const bool fallback = g.evaluate_router_margin(T);
+    const auto tel = g.router_margin_telemetry();
+    require(tel.total_layers == 1 && tel.total_tokens == T && std::abs(tel.min_margin - min_margin) <= 1e-6 * std::max(1.0, std::abs(min_margin)), "margin telemetry");
+    require(fallback == (min_margin <= 2e-4) && tel.fallback_layers == (fallback ? 1u : 0u), "margin fallback decision");
+    g.begin();
+    g.mixture(g.slice(exv, 0, uint64_t(K) * C * 4), g.slice(wts, 0, K * 4), g.slice(shv, 0, uint64_t(C) * 4), g.slice(slog, 0, 4), g.slice(mix, 0, uint64_t(C) * 4));
+    (void)g.submit();
+    close(read<float>(g, g.slice(mix, 0, uint64_t(C) * 4)), emix.data(), C);
+    g.begin();
+    refuses([&] { g.prefill_mixture_batch(exv, wts, shv, slog, {mix, T + 1, C, uint64_t(C) * 4}, K); }, "mixture rows beyond the views accepted");
+    refuses([&] { g.moe_route_rows(logits, ids, wts, E, K, 4096, RouterMode::softmax, true); }, "audited batch beyond 2048 rows accepted");
+    g.abort();
+    refuses([&] { g.configure_router_margin_epsilon(0.f); }, "zero margin epsilon accepted");
+
+    // residual read / write on one token
+    std::vector<double> dn(size_t(B) * C), dsc(size_t(B) * C), dinj(B), dstreams(size_t(B) * C), dout(C);
+    const auto fn = activations(seed + 20, size_t(B) * C, 1.5f), fsc = activations(seed + 21, size_t(B) * C, 3.f), finj = activations(seed + 22, B, 2.f);
+    const auto fst = activations(seed + 23, size_t(B) * C, 5.f), fo = activations(seed + 24, C, 5.f);
+    const auto nv = g.upload(bytes_of(fn), "normalized"), scv = g.upload(bytes_of(fsc), "scores"), iv = g.upload(bytes_of(finj), "inject");
+    const auto stv = g.upload(bytes_of(fst), "streams"), ov = g.upload(bytes_of(fo), "ffn out");
+    const auto rin = g.zeros(C * 4, "ffn in"), scl = g.zeros(B * 4, "write scales"), dst = g.zeros(uint64_t(B) * C * 4, "streams out");
+    g.begin();
+    g.residual_read(nv, scv, iv, rin, scl, B, C);
+    g.residual_write(stv, ov, scl, dst);
+    (void)g.submit();
+    std::vector<double> ein(C, 0.0), esc(B), edst(size_t(B) * C);
+    for (uint32_t b = 0; b < B; ++b) {
+        esc[b] = 2.0 * tso_sigmoid(double(finj[b]) / B);
+        for (uint32_t c = 0; c < C; ++c) ein[c] += double(fn[size_t(b) * C + c]) * tso_sigmoid(fsc[size_t(b) * C + c]);
+    }
+    for (auto& v : ein) v /= B;
+    const auto gsc = read<float>(g, scl);
+    for (uint32_t b = 0; b < B; ++b) for (uint32_t c = 0; c < C; ++c) edst[size_t(b) * C + c] = double(fst[size_t(b) * C + c]) + double(gsc[b]) * fo[c];
+    close(read<float>(g, rin), ein.data(), C);
+    close(gsc, esc.data(), B);
+    close(read<float>(g, dst), edst.data(), edst.size());
+    g.begin();
+    refuses([&] { g.residual_read(nv, scv, iv, rin, scl, B + 1, C); }, "residual branch mismatch accepted");
+    refuses([&] { g.residual_write(stv, ov, scl, g.slice(dst, 0, uint64_t(C) * 4)); }, "short residual destination accepted");
+    g.abort();
 }
 }  // namespace
 
@@ -287,6 +421,8 @@ int main() {
         many(g, {512, 256, 16, 4}, 40, 24, 300);   // two chunks: 24 + 16 rows
         CudaGraph g2(0, uint64_t(2) << 30);
         many(g2, {512, 256, 8, 2}, 200, 256, 400); // one chunk, tiles of more than 32 routes
+        CudaGraph g3(0, uint64_t(1) << 30);
+        operators(g3, 500);
     } catch (const std::exception& e) {
         std::cerr << "tiled MoE check failed after " << checks << " checks: " << e.what() << '\n';
         return 1;

@@ -178,7 +178,7 @@ def timed_median(fn, steps, warmup, min_seconds=0.5, max_repeats=400):
     """Repeats the timed loop of exactly `steps` calls until the timed regions add up to `min_seconds`; returns the median ms per
     call and the number of repeats."""
     vals, total = [], 0.0
-    while total < min_seconds * 1e3 and len(vals) < max_repeats:
+    while not vals or (total < min_seconds * 1e3 and len(vals) < max_repeats):
         ms = timed(fn, steps, warmup if not vals else 0)
         vals.append(ms)
         total += ms * steps

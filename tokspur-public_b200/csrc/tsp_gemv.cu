@@ -31,7 +31,7 @@ int get_tensor_map_elems(const void* base, uint32_t elem_bytes, uint32_t rank, c
 constexpr int kConsumerWarps = 8;     // consumer warps of most shapes; the K-part mode of a dense matrix runs 16
 constexpr uint32_t kMaxStages = 6;
 
-// Tensor maps of the K-part mode: [part bytes as 16-bit elements][rows][experts] of matrix set A (low ids, high ids) and B (same)
+// Tensor maps of the K-part mode: [part bytes as 32-bit elements][rows][experts] of matrix set A (low ids, high ids) and B (same)
 struct alignas(64) GemvPartMaps { CUtensorMap m[4]; };
 
 struct GemvParams {
@@ -67,6 +67,8 @@ struct GemvParams {
     uint32_t tokens;          // token rows (token_map row length); dense: number of rows
     float* out; uint64_t out_stride_bytes;
     int split_lo;
+    int balance;              // K-part mode of a dense plain projection: CTAs split the (item, K part) sequence evenly; an item shared by
+                              // two CTAs is summed with atomic adds into output rows the launcher zeroed
     uint32_t* error;
 };
 
@@ -77,6 +79,81 @@ __device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_
 __device__ __forceinline__ const uint8_t* expert_ptr(const uint8_t* base, const uint8_t* base_hi, uint32_t e,
                                                      uint32_t split, uint64_t stride) {
     return e < split ? base + static_cast<uint64_t>(e) * stride : base_hi + static_cast<uint64_t>(e - split) * stride;
+}
+
+// Shared-memory loads by 32-bit shared-space address (the compiler keeps the constant part of an address as the instruction's offset)
+__device__ __forceinline__ uint32_t lds32a(uint32_t a) { uint32_t v; asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds16a(uint32_t a) { uint16_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
+__device__ __forceinline__ float2 lds64fa(uint32_t a) { float2 v; asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ uint4 lds128a(uint32_t a) {
+    uint4 v; asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v;
+}
+
+// (d0, d1) += f * (a0, a1) as one packed FP32 instruction (each half rounds like fmaf)
+__device__ __forceinline__ void fma2(float& d0, float& d1, float f, float a0, float a1) {
+    asm("{\n\t.reg .b64 dd, ff, aa;\n\t"
+        "mov.b64 dd, {%0, %1};\n\tmov.b64 ff, {%2, %2};\n\tmov.b64 aa, {%3, %4};\n\t"
+        "fma.rn.f32x2 dd, ff, aa, dd;\n\t"
+        "mov.b64 {%0, %1}, dd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(f), "f"(a0), "f"(a1));
+}
+
+// Eight Q8_0 codes of one row of a 34-byte block as four MMA register pairs of exact binary16 subnormals (code + 128) * 2^-24.
+// Lane t of a row takes the aligned words t and t + 4 of the block (the 32 lanes of a warp then read 32 different banks: rows are
+// 68 words apart), `a` = block address + 4t. In an odd block the codes start on a word boundary: the words hold codes 4t .. 4t+3
+// and 16+4t .. 16+4t+3. In an even block they start 2 bytes off one: the words hold codes 4t-2 .. 4t+1 and 4t+14 .. 4t+17, and
+// lane 0, whose first word begins with the block's scale, takes codes 0, 1 from it and 30, 31 from word 8 at `blk` + 32 (`sel` =
+// 0x5432 for lane 0, 0x3210 otherwise). Pairs are (byte 0, byte 2) and (byte 1, byte 3) of each word; the activation runs are staged in the
+// same order.
+template <bool ALIGNED>
+__device__ __forceinline__ void q8_pairs(uint32_t blk, uint32_t a, uint32_t sel, uint32_t (&out)[4]) {
+    uint32_t w0, w1;
+    if (ALIGNED) {
+        w0 = lds32a(a + 2); w1 = lds32a(a + 18);
+    } else {
+        w0 = __byte_perm(lds32a(a), lds32a(blk + 32), sel); w1 = lds32a(a + 16);
+    }
+    w0 ^= 0x80808080u; w1 ^= 0x80808080u;
+    out[0] = __byte_perm(w0, 0u, 0x4240); out[1] = __byte_perm(w0, 0u, 0x4341);
+    out[2] = __byte_perm(w1, 0u, 0x4240); out[3] = __byte_perm(w1, 0u, 0x4341);
+}
+
+// One block of a warp's four blocks of a K-part stage (GGUF Q8_0, rows 272 bytes apart). aA / aB: shared addresses of the first of
+// the four blocks in this lane's two weight rows; xa[c]: this lane's 16 bytes of the first block in the activation rows of token
+// group c (+ x_lo_off: the low halves); sa[c]: the pair of pre-scaled block sums of tokens 2t, 2t+1 of the first block, blocks
+// `s_step` bytes apart. Everything else is a compile-time offset.
+template <int NC, bool LO, int J>
+__device__ __forceinline__ void q8_block(uint32_t aA, uint32_t aB, uint32_t t4, const uint32_t (&xa)[NC], uint32_t x_lo_off, const uint32_t (&sa)[NC],
+                                         uint32_t s_step, float (&total)[NC][4]) {
+    uint32_t A[4], B[4];
+    const uint32_t sel = t4 ? 0x3210u : 0x5432u;
+    q8_pairs<(J & 1) != 0>(aA + J * 34, aA + J * 34 + t4, sel, A);
+    q8_pairs<(J & 1) != 0>(aB + J * 34, aB + J * 34 + t4, sel, B);
+    const float fA = half_bits_to_float(lds16a(aA + J * 34));   // the 2^24 of the subnormal codes is applied once per item
+    const float fB = half_bits_to_float(lds16a(aB + J * 34));
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+        const uint4 xv = lds128a(xa[c] + J * 64);
+        const float2 sv = lds64fa(sa[c] + J * s_step);
+        float acc[4] = {sv.x, sv.y, sv.x, sv.y};
+        mma_f16_16816(acc, A[0], B[0], A[1], B[1], xv.x, xv.y);
+        mma_f16_16816(acc, A[2], B[2], A[3], B[3], xv.z, xv.w);
+        if (LO) {
+            const uint4 yv = lds128a(xa[c] + x_lo_off + J * 64);
+            mma_f16_16816(acc, A[0], B[0], A[1], B[1], yv.x, yv.y);
+            mma_f16_16816(acc, A[2], B[2], A[3], B[3], yv.z, yv.w);
+        }
+        fma2(total[c][0], total[c][1], fA, acc[0], acc[1]);
+        fma2(total[c][2], total[c][3], fB, acc[2], acc[3]);
+    }
+}
+template <int NC, bool LO>
+__device__ __forceinline__ void q8_part(uint32_t aA, uint32_t aB, uint32_t t4, const uint32_t (&xa)[NC], uint32_t x_lo_off, const uint32_t (&sa)[NC],
+                                        uint32_t s_step, float (&total)[NC][4]) {
+    q8_block<NC, LO, 0>(aA, aB, t4, xa, x_lo_off, sa, s_step, total);
+    q8_block<NC, LO, 1>(aA, aB, t4, xa, x_lo_off, sa, s_step, total);
+    q8_block<NC, LO, 2>(aA, aB, t4, xa, x_lo_off, sa, s_step, total);
+    q8_block<NC, LO, 3>(aA, aB, t4, xa, x_lo_off, sa, s_step, total);
 }
 
 // Work item -> (expert, first route of the tile, routes in the tile)
@@ -118,9 +195,16 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
 
     const uint32_t n_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
     const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.items_per_matrix;
-    const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
-    const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
+    // work units of this CTA: whole items, or with p.balance any run of (item, K part) pairs
+    const uint64_t n_units = p.balance ? n_items * p.kparts : n_items;
+    const uint64_t unit0 = n_units * blockIdx.x / gridDim.x, unit1 = n_units * (blockIdx.x + 1) / gridDim.x;
+    const uint32_t upi = p.balance ? p.kparts : 1u;   // units per item
+    const uint32_t item0 = static_cast<uint32_t>(unit0 / upi), item1 = static_cast<uint32_t>((unit1 + upi - 1) / upi);
+    const uint32_t k_first = p.balance ? static_cast<uint32_t>(unit0 % upi) : 0u;                        // first K part of item0
+    const uint32_t k_last = p.balance && unit1 % upi ? static_cast<uint32_t>(unit1 % upi) : p.kparts;   // end K part of item1 - 1
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
+    // K-part mode of GGUF Q8_0 (sixteen consumer warps): stages of eight blocks of 128 rows, rows 272 bytes apart
+    constexpr bool KPART = TYPE == TSP_TYPE_Q8_0 && LAYOUT == TSP_LAYOUT_GGUF && CW == 16;
 
     if (warp == CW) {
         // ------------------------------ producer warp ------------------------------
@@ -131,7 +215,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
             const TileInfo ti = tile_info<NC>(p, tile);
             const uint32_t r0 = ri * p.rows_per_item;
             const uint32_t nr = min(p.rows_per_item, p.rows - r0);
-            for (uint32_t kh = 0; kh < p.kparts && ok; ++kh) {
+            const uint32_t kbeg = item == item0 ? k_first : 0u, kend = item + 1 == item1 ? k_last : p.kparts;
+            for (uint32_t kh = kbeg; kh < kend && ok; ++kh) {
             if (lane == 0) ok = mbar_wait(&empty[stage], phase ^ 1u);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { if (lane == 0) raise_error(p.error, TSP_ERR_TIMEOUT); break; }
@@ -148,7 +233,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                         asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                                      ::"r"(smem_u32(sbase + m * p.rows_per_item * p.row_stride)),
                                        "l"(reinterpret_cast<uint64_t>(&part_maps.m[2 * m + (hi ? 1 : 0)])), "r"(smem_u32(&full[stage])),
-                                       "r"(static_cast<int>(kh * p.row_bytes / 2)), "r"(static_cast<int>(r0)), "r"(el) : "memory");
+                                       "r"(static_cast<int>(kh * p.row_bytes / 4)), "r"(static_cast<int>(r0)), "r"(el) : "memory");
                 }
                 if (++stage == NS) { stage = 0; phase ^= 1u; }
                 continue;
@@ -229,9 +314,20 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                 if (active) {
                     j = u / per_row; k8 = u % per_row;
                     const uint32_t in_row = rids[j] / p.in_div;
-                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + k8 * 2;
-                    const float4 v0 = src[0], v1 = src[1];
-                    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    float v[8];
+                    if (KPART) {
+                        // destination run (block b, lane t): the eight activations this MMA lane multiplies with its code pairs (q8_pairs)
+                        const uint32_t b = k8 >> 2, tq = k8 & 3u;
+                        const float* xr = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + b * 32;
+                        const uint32_t second = 4 * tq + ((b & 1u) ? 16u : 14u);   // first code of the lane's second word
+                        if (!(b & 1u) && tq == 0) { v[0] = xr[0]; v[1] = xr[30]; v[2] = xr[1]; v[3] = xr[31]; }
+                        else { const uint32_t first = second - 16; v[0] = xr[first]; v[1] = xr[first + 2]; v[2] = xr[first + 1]; v[3] = xr[first + 3]; }
+                        v[4] = xr[second]; v[5] = xr[second + 2]; v[6] = xr[second + 1]; v[7] = xr[second + 3];
+                    } else {
+                        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.x) + in_row * p.x_stride_bytes) + k8 * 2;
+                        const float4 v0 = src[0], v1 = src[1];
+                        v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
+                    }
                     __half h[8], l[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -241,18 +337,20 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                         l[i] = __float2half_rn(v[i] - hf);
                         s += v[i];
                     }
-                    // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7
+                    // permuted order inside the run of 8: positions hold elements 0,2,1,3,4,6,5,7 (the K-part mode gathered its runs
+                    // in pair order already)
+                    const int o1 = KPART ? 1 : 2, o2 = KPART ? 2 : 1, o3 = 3, o4 = 4, o5 = KPART ? 5 : 6, o6 = KPART ? 6 : 5;
                     uint4 ph, pl;
-                    ph.x = __half_as_ushort(h[0]) | (uint32_t(__half_as_ushort(h[2])) << 16);
-                    ph.y = __half_as_ushort(h[1]) | (uint32_t(__half_as_ushort(h[3])) << 16);
-                    ph.z = __half_as_ushort(h[4]) | (uint32_t(__half_as_ushort(h[6])) << 16);
-                    ph.w = __half_as_ushort(h[5]) | (uint32_t(__half_as_ushort(h[7])) << 16);
+                    ph.x = __half_as_ushort(h[0]) | (uint32_t(__half_as_ushort(h[o1])) << 16);
+                    ph.y = __half_as_ushort(h[o2]) | (uint32_t(__half_as_ushort(h[o3])) << 16);
+                    ph.z = __half_as_ushort(h[o4]) | (uint32_t(__half_as_ushort(h[o5])) << 16);
+                    ph.w = __half_as_ushort(h[o6]) | (uint32_t(__half_as_ushort(h[7])) << 16);
                     *reinterpret_cast<uint4*>(xhi + j * p.x_stride + k8 * 16) = ph;
                     if (p.split_lo) {
-                        pl.x = __half_as_ushort(l[0]) | (uint32_t(__half_as_ushort(l[2])) << 16);
-                        pl.y = __half_as_ushort(l[1]) | (uint32_t(__half_as_ushort(l[3])) << 16);
-                        pl.z = __half_as_ushort(l[4]) | (uint32_t(__half_as_ushort(l[6])) << 16);
-                        pl.w = __half_as_ushort(l[5]) | (uint32_t(__half_as_ushort(l[7])) << 16);
+                        pl.x = __half_as_ushort(l[0]) | (uint32_t(__half_as_ushort(l[o1])) << 16);
+                        pl.y = __half_as_ushort(l[o2]) | (uint32_t(__half_as_ushort(l[o3])) << 16);
+                        pl.z = __half_as_ushort(l[o4]) | (uint32_t(__half_as_ushort(l[o5])) << 16);
+                        pl.w = __half_as_ushort(l[o6]) | (uint32_t(__half_as_ushort(l[7])) << 16);
                         *reinterpret_cast<uint4*>(xlo + j * p.x_stride + k8 * 16) = pl;
                     }
                 }
@@ -268,7 +366,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                         *reinterpret_cast<__half*>(sxb + (8u * NC + j) * p.sx_stride + grp * 2) = sl;
                     } else {
                         bad |= !finite_f32(s);
-                        *reinterpret_cast<float*>(sxb + j * p.sx_stride + grp * 4) = s;
+                        // K-part mode: the accumulators start at -128 * 2^-24 * (sum of the block's activations), which takes the
+                        // +128 of the unsigned codes out again inside the MMA
+                        if (KPART) *reinterpret_cast<float*>(sxb + (grp * (8u * NC) + j) * 4) = s * -7.62939453125e-6f;   // [block][token]
+                        else *reinterpret_cast<float*>(sxb + j * p.sx_stride + grp * 4) = s;
                     }
                 }
             }
@@ -288,7 +389,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
             // shared-memory rows of this lane's two MMA row slots
             const uint32_t rowA = GATEUP ? rt * 8 + g : rt * 16 + g;
             const uint32_t rowB = GATEUP ? p.rows_per_item + rt * 8 + g : rt * 16 + 8 + g;
-            for (uint32_t kh = 0; kh < p.kparts; ++kh) {
+            const uint32_t kbeg = item == item0 ? k_first : 0u, kend = item + 1 == item1 ? k_last : p.kparts;
+            const bool partial = kend - kbeg != p.kparts;   // the rest of the item's K extent belongs to a neighbouring CTA
+            for (uint32_t kh = kbeg; kh < kend; ++kh) {
             // ---- wait for the slab (one K part of the item's rows) ----
             if (ok) {
                 ok = mbar_wait(&full[stage], phase);
@@ -298,7 +401,22 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
             const uint8_t* qA = sbase + rowA * p.row_stride;
             const uint8_t* qB = sbase + rowB * p.row_stride;
             const uint32_t kb0 = kh * p.units_per_part;   // first K unit of this part (activation offsets use the global unit index)
-            if (ok) {
+            if (KPART && ok) {
+                // This warp's four blocks of the part: 4 my_kp .. 4 my_kp + 3 (the even ones 2 bytes off a word boundary, the odd ones
+                // on one: resolved at compile time)
+                const uint32_t sb32 = smem_u32(sbase);
+                const uint32_t x_lo_off = smem_u32(xlo) - smem_u32(xhi);
+                const uint32_t aA = sb32 + rowA * 272u + my_kp * 136u, aB = sb32 + rowB * 272u + my_kp * 136u;
+                const uint32_t kb = kb0 + my_kp * 4u;
+                uint32_t xa[NC], sa[NC];
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    xa[c] = smem_u32(xhi) + (c * 8 + g) * p.x_stride + (kb * 32 + t * 8) * 2;
+                    sa[c] = smem_u32(sxb) + (kb * (8u * NC) + c * 8 + 2 * t) * 4;
+                }
+                if (p.split_lo) q8_part<NC, true>(aA, aB, t * 4u, xa, x_lo_off, sa, 8u * NC * 4u, total);
+                else q8_part<NC, false>(aA, aB, t * 4u, xa, x_lo_off, sa, 8u * NC * 4u, total);
+            } else if (ok) {
                 for (uint32_t b = my_kp; b < p.units_per_part; b += kp_count) {
                     if (TYPE == TSP_TYPE_Q4_K) {
                         // ---- header of the super-block for both rows: d, dmin, sc[8], mn[8] ----
@@ -432,11 +550,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                     }
                 }
             }
-            if (kh + 1 < p.kparts) {   // more parts of this item follow: hand the stage back and move on
+            if (kh + 1 < kend) {   // more parts of this item follow: hand the stage back and move on
                 __syncwarp();
                 if (lane == 0 && ok) mbar_arrive(&empty[stage]);
                 if (++stage == NS) { stage = 0; phase ^= 1u; }
             }
+            }
+            if (KPART) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) { total[c][0] *= 16777216.f; total[c][1] *= 16777216.f; total[c][2] *= 16777216.f; total[c][3] *= 16777216.f; }
             }
             // ---- cross-warp reduction over the K parts (only when one row tile is shared by several warps) ----
             if (kp_count > 1) {
@@ -478,6 +600,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                             }
                         } else {
                             const uint32_t r = r0 + rt * 16 + g;
+                            if (partial) {   // two CTAs share the item: each adds its part onto the zeroed rows (two addends: order-free)
+                                if (r < p.rows) { bad |= !finite_f32(total[c][q]); atomicAdd(orow + r, total[c][q]); }
+                                if (r + 8 < p.rows) { bad |= !finite_f32(total[c][2 + q]); atomicAdd(orow + r + 8, total[c][2 + q]); }
+                                continue;
+                            }
                             if (r < p.rows) { bad |= !finite_f32(total[c][q]); orow[r] = total[c][q]; }
                             if (r + 8 < p.rows) { bad |= !finite_f32(total[c][2 + q]); orow[r + 8] = total[c][2 + q]; }
                         }
@@ -562,9 +689,9 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
     // row): a stage then holds 128 rows (gate-up: 64 + 64) and the partial sums of a row tile are reduced once per item (with
     // whole rows per stage only 16 or 32 rows fit, and the warps reduce through shared memory after every stage).
     if (!q4 && layout == TSP_LAYOUT_GGUF && !contiguous && p.nunit % 8 == 0 && p.nunit > 8 && a->rows >= 128) {
-        p.units_per_part = 8;
-        p.kparts = p.nunit / 8;
-        row_bytes = 8 * 34;
+        p.units_per_part = 8;   // parts of 16 blocks leave room for two stages only and measured slower (0.108 against 0.094 ms)
+        p.kparts = p.nunit / p.units_per_part;
+        row_bytes = p.units_per_part * 34;
     }
     p.row_bytes = contiguous ? 0 : row_bytes;
     // a tensor copy lays the rows of a K part down densely; per-row copies pad the rows against bank conflicts
@@ -616,16 +743,20 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
     p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
+    // A dense plain projection in K parts (the vocabulary head): 1187 items of 128 rows over 148 CTAs leave three CTAs a ninth item
+    // while the rest idle. Splitting the (item, K part) sequence evenly instead costs one pass of zeros over the output rows.
+    p.balance = (p.kparts > 1 && !gateup && !token_map && a->experts == 1 && p.items_per_matrix >= static_cast<uint32_t>(grid)) ? 1 : 0;
+    if (p.balance) TSP_CUDA(cudaMemset2DAsync(out, out_stride_bytes, 0, static_cast<size_t>(a->rows) * 4, tokens, st));
     GemvPartMaps map{};
-    if (p.kparts > 1) {   // [row bytes][rows][experts] as 16-bit elements: a box of one K part (272 bytes) of the item's rows
+    if (p.kparts > 1) {   // [row bytes][rows][experts] as 32-bit elements: a box of one K part (272 or 544 bytes) of the item's rows
         if (p.expert_stride % 16 != 0 && a->experts > 1) return fail(TSP_E_ARG, "project: expert stride must be a multiple of 16 bytes");
-        const uint32_t box[3] = {p.row_bytes / 2, p.rows_per_item, 1};
+        const uint32_t box[3] = {p.row_bytes / 4, p.rows_per_item, 1};
         const uint64_t n_lo = p.split ? p.split : 1, n_hi = p.experts > p.split ? p.experts - p.split : 1;
         const uint64_t strides[2] = {p.src_row_pitch, p.expert_stride ? p.expert_stride : static_cast<uint64_t>(a->rows) * p.src_row_pitch};
         for (uint32_t m = 0; m < nmat; ++m) {
-            const uint64_t d_lo[3] = {p.src_row_pitch / 2, a->rows, n_lo}, d_hi[3] = {p.src_row_pitch / 2, a->rows, n_hi};
-            if (int rc = get_tensor_map_elems(m ? p.b_base : p.a_base, 2, 3, d_lo, strides, box, false, &map.m[2 * m])) return rc;
-            if (int rc = get_tensor_map_elems(m ? p.b_base_hi : p.a_base_hi, 2, 3, d_hi, strides, box, false, &map.m[2 * m + 1])) return rc;
+            const uint64_t d_lo[3] = {p.src_row_pitch / 4, a->rows, n_lo}, d_hi[3] = {p.src_row_pitch / 4, a->rows, n_hi};
+            if (int rc = get_tensor_map_elems(m ? p.b_base : p.a_base, 4, 3, d_lo, strides, box, false, &map.m[2 * m])) return rc;
+            if (int rc = get_tensor_map_elems(m ? p.b_base_hi : p.a_base_hi, 4, 3, d_hi, strides, box, false, &map.m[2 * m + 1])) return rc;
         }
     }
 

@@ -274,25 +274,28 @@ grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint3
 }
 
 // ---------------------------------------------------------------------------------------------
-// Decode-size prologue: route + permutation + tile table of a batch of <= 64 token rows in ONE launch (block 0), with the
-// binary16 -> FP32 copy of the input rows done by the remaining blocks of the same launch. The tables are the ones the
-// separate kernels above produce, bit for bit: the per-expert token order comes from a 64-bit mask of the tokens that
-// name the expert (bit t set = token t routes here), so position = number of lower set bits: no atomics decide an order.
+// Decode-size prologue of a batch of <= 64 token rows in TWO launches: (1) routing, one warp per token over as many blocks
+// as that takes, with the binary16 -> FP32 copy of the input rows done by the remaining blocks of the same launch (one block
+// routing 64 rows alone is bound by its own issue rate: measured 25.7 us); (2) permutation + tile table in one block. The
+// tables are the ones the separate kernels above produce, bit for bit: the per-expert token order comes from a 64-bit mask
+// of the tokens that name the expert (bit t set = token t routes here), so position = number of lower set bits: no atomics
+// decide an order.
 // ---------------------------------------------------------------------------------------------
 constexpr int kPrologueThreads = 1024;
+constexpr int kPrologueRouteWarps = 4;
 constexpr uint32_t kPrologueTokens = 64, kPrologueExperts = 1024;
 
-__global__ void __launch_bounds__(kPrologueThreads)
-decode_prologue_kernel(const float* __restrict__ logits, uint64_t logits_stride, uint32_t tokens, uint32_t experts, uint32_t selected,
-                       uint32_t mode, int normalize, uint32_t tile, uint32_t* __restrict__ ids, float* __restrict__ weights,
-                       uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* __restrict__ tasks,
-                       const __half* __restrict__ x16, uint64_t x16_stride, float* __restrict__ x32, uint64_t x32_stride, uint32_t channels,
-                       uint32_t* error) {
+__global__ void __launch_bounds__(kPrologueRouteWarps * 32)
+decode_route_kernel(const float* __restrict__ logits, uint64_t logits_stride, uint32_t tokens, uint32_t experts, uint32_t selected,
+                    uint32_t mode, int normalize, uint32_t route_blocks, uint32_t* __restrict__ ids, float* __restrict__ weights,
+                    const __half* __restrict__ x16, uint64_t x16_stride, float* __restrict__ x32, uint64_t x32_stride, uint32_t channels,
+                    uint32_t* error) {
     pdl_launch_dependents();
     pdl_wait();
-    if (blockIdx.x > 0) {   // the conversion blocks: binary16 rows -> FP32 rows (exact)
+    if (blockIdx.x >= route_blocks) {   // the conversion blocks: binary16 rows -> FP32 rows (exact)
         const uint32_t per_row = channels / 4;   // four values per thread step
-        for (uint32_t i = (blockIdx.x - 1) * blockDim.x + threadIdx.x; i < tokens * per_row; i += (gridDim.x - 1) * blockDim.x) {
+        const uint32_t nconv = gridDim.x - route_blocks;
+        for (uint32_t i = (blockIdx.x - route_blocks) * blockDim.x + threadIdx.x; i < tokens * per_row; i += nconv * blockDim.x) {
             const uint32_t row = i / per_row, c4 = i - row * per_row;
             const uint2 h = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(x16) + row * x16_stride + c4 * 8ull);
             const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
@@ -300,28 +303,39 @@ decode_prologue_kernel(const float* __restrict__ logits, uint64_t logits_stride,
         }
         return;
     }
-    extern __shared__ float pro_smem[];          // [warps][experts] routing rows, reused afterwards
+    extern __shared__ float pro_smem[];          // [warps][experts] routing rows of the shared-memory form
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t t = blockIdx.x * kPrologueRouteWarps + warp;
+    if (t >= tokens) return;
+    const float* row = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + t * logits_stride);
+    if (experts <= 512 && normalize) route_row_regs(row, t, experts, selected, mode, ids, weights, error, lane);
+    else route_row(pro_smem + warp * experts, row, t, experts, selected, mode, normalize, ids, weights, error, lane);
+}
+
+__global__ void __launch_bounds__(kPrologueThreads)
+decode_tables_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile,
+                     uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* __restrict__ tasks, uint32_t* error) {
+    pdl_launch_dependents();
     __shared__ unsigned long long mask[kPrologueExperts];
-    __shared__ uint32_t tile_off[kPrologueExperts + 1];
     __shared__ uint32_t warp_tiles[32], warp_routes[32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
     for (uint32_t e = tid; e < experts; e += blockDim.x) mask[e] = 0ull;
-    for (uint32_t t = warp; t < tokens; t += nwarps) {
-        const float* row = reinterpret_cast<const float*>(reinterpret_cast<const char*>(logits) + t * logits_stride);
-        if (experts <= 512 && normalize) route_row_regs(row, t, experts, selected, mode, ids, weights, error, lane);
-        else route_row(pro_smem + warp * experts, row, t, experts, selected, mode, normalize, ids, weights, error, lane);
-    }
-    __syncthreads();   // ids are complete (and visible to this block)
     const uint32_t routes = tokens * selected;
-    for (uint32_t i = tid; i < routes; i += blockDim.x) {
+    const uint32_t bound = routes / tile + experts;
+    pdl_wait();   // the ids come from the previous launch; everything above touched shared memory only
+    __syncthreads();
+    uint32_t my_e[2] = {0xffffffffu, 0xffffffffu};   // routes <= 64 * 64 = 4096: at most four per thread, two in registers
+    for (uint32_t i = tid, n = 0; i < routes; i += blockDim.x, ++n) {
         const uint32_t t = i / selected, e = ids[i];
+        if (n < 2) my_e[n] = e;
         if (e >= experts) { raise_error(error, TSP_ERR_INDEX); continue; }
         const unsigned long long bit = 1ull << t;
         if (atomicOr(&mask[e], bit) & bit) raise_error(error, TSP_ERR_INDEX);   // an expert named twice by one token
     }
+    for (uint32_t i = tid; i < bound; i += blockDim.x) { tasks[2 + 2 * i] = 0xffffffffu; tasks[3 + 2 * i] = 0xffffffffu; }
     __syncthreads();
-    for (uint32_t i = tid; i < routes; i += blockDim.x) {
-        const uint32_t t = i / selected, e = ids[i];
+    for (uint32_t i = tid, n = 0; i < routes; i += blockDim.x, ++n) {
+        const uint32_t t = i / selected, e = n < 2 ? my_e[n] : ids[i];
         if (e >= experts) continue;
         const uint32_t j = __popcll(mask[e] & ((1ull << t) - 1ull));
         token_map[static_cast<uint64_t>(e) * tokens + j] = i;
@@ -335,38 +349,39 @@ decode_prologue_kernel(const float* __restrict__ logits, uint64_t logits_stride,
         if (lane >= static_cast<uint32_t>(o)) { incl_n += tn; incl_c += tc; }
     }
     if (lane == 31) { warp_tiles[warp] = incl_n; warp_routes[warp] = incl_c; }
-    __syncthreads();
+    __syncthreads();   // also orders the padding of the tile table above before the entries below
     uint32_t before = 0, total_n = 0, total_c = 0;
     for (uint32_t i = 0; i < nwarps; ++i) { if (i < warp) before += warp_tiles[i]; total_n += warp_tiles[i]; total_c += warp_routes[i]; }
-    if (tid < experts) tile_off[tid] = before + incl_n - n;
-    const uint32_t bound = routes / tile + experts;
     if (tid == 0) {
         tasks[0] = min(total_n, bound);
         tasks[1] = total_c;
         if (total_n > bound || total_c != routes) raise_error(error, TSP_ERR_INDEX);
     }
-    for (uint32_t i = tid; i < bound; i += blockDim.x) { tasks[2 + 2 * i] = 0xffffffffu; tasks[3 + 2 * i] = 0xffffffffu; }
-    __syncthreads();
-    if (tid < experts)
+    if (tid < experts) {
+        const uint32_t first = before + incl_n - n;
         for (uint32_t i = 0; i < n; ++i) {
-            const uint32_t at = tile_off[tid] + i;
+            const uint32_t at = first + i;
             if (at < bound) { tasks[2 + 2 * at] = tid; tasks[3 + 2 * at] = i * tile; }
         }
+    }
 }
 
-// Returns 1 when the batch does not fit the one-launch prologue (the caller then issues the separate launches).
+// Returns 1 when the batch does not fit the short prologue (the caller then issues the separate launches).
 int launch_decode_prologue(const float* logits, uint64_t logits_stride, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t mode,
                            int normalize, uint32_t tile, uint32_t* ids, float* weights, uint32_t* token_map, uint32_t* counts, uint32_t* tasks,
                            const void* x16, uint64_t x16_stride, float* x32, uint64_t x32_stride, uint32_t channels, uint32_t* error, cudaStream_t st) {
     if (tokens > kPrologueTokens || experts > kPrologueExperts || experts > static_cast<uint32_t>(kPrologueThreads)) return 1;
     if (x16 && (channels % 4 || x16_stride % 8 || x32_stride % 16 || reinterpret_cast<uintptr_t>(x16) % 8 || reinterpret_cast<uintptr_t>(x32) % 16)) return 1;
-    const size_t smem = static_cast<size_t>(kPrologueThreads / 32) * experts * sizeof(float);
+    const size_t smem = (experts <= 512 && normalize) ? 0 : static_cast<size_t>(kPrologueRouteWarps) * experts * sizeof(float);
     static thread_local SmemAttrCache configured;
-    TSP_CUDA(ensure_dynamic_smem(decode_prologue_kernel, configured, smem));
-    // conversion blocks: enough to cover the rows in one pass
-    const uint32_t conv = x16 ? min(64u, (tokens * (channels / 4) + kPrologueThreads - 1) / kPrologueThreads) : 0u;
-    TSP_CUDA(launch_pdl(decode_prologue_kernel, dim3(1 + conv), dim3(kPrologueThreads), smem, st, logits, logits_stride, tokens, experts, selected, mode,
-                        normalize, tile, ids, weights, token_map, counts, tasks, static_cast<const __half*>(x16), x16_stride, x32, x32_stride, channels, error));
+    TSP_CUDA(ensure_dynamic_smem(decode_route_kernel, configured, smem));
+    const uint32_t route_blocks = (tokens + kPrologueRouteWarps - 1) / kPrologueRouteWarps;
+    // conversion blocks: enough to cover the rows in two passes
+    const uint32_t conv = x16 ? min(128u, (tokens * (channels / 4) + 2 * kPrologueRouteWarps * 32 - 1) / (2 * kPrologueRouteWarps * 32)) : 0u;
+    TSP_CUDA(launch_pdl(decode_route_kernel, dim3(route_blocks + conv), dim3(kPrologueRouteWarps * 32), smem, st, logits, logits_stride, tokens, experts,
+                        selected, mode, normalize, route_blocks, ids, weights, static_cast<const __half*>(x16), x16_stride, x32, x32_stride, channels, error));
+    TSP_CUDA(launch_pdl(decode_tables_kernel, dim3(1), dim3(kPrologueThreads), 0, st, static_cast<const uint32_t*>(ids), tokens, experts, selected, tile,
+                        token_map, counts, tasks, error));
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -428,18 +443,25 @@ combine_kernel(const void* __restrict__ routed, uint64_t routed_stride, const fl
         if (vec4 && c + 4 <= c_end) {
             const float4 s4 = sh ? *reinterpret_cast<const float4*>(sh + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             float v[4] = {gate * s4.x, gate * s4.y, gate * s4.z, gate * s4.w};
-            for (uint32_t r = 0; r < selected; ++r) {
-                const float wr = w_s[r];
-                if (wr != 0.f) {   // a zero weight marks a route that is not present in `routed` (expert parallelism)
-                    float4 y;
+            // A zero weight marks a route that is not present in `routed` (expert parallelism): its row is still inside the
+            // buffer, so it is loaded like the others (four rows in flight) and only the sum skips it.
+            for (uint32_t r0 = 0; r0 < selected; r0 += 4) {
+                float4 y[4];
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const uint32_t r = min(r0 + i, selected - 1);
                     if (R16) {
                         const uint2 h = *reinterpret_cast<const uint2*>(y0 + r * routed_stride + c * 2ull);
                         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
-                        y = make_float4(a.x, a.y, b.x, b.y);
+                        y[i] = make_float4(a.x, a.y, b.x, b.y);
                     } else {
-                        y = *reinterpret_cast<const float4*>(y0 + r * routed_stride + c * 4ull);
+                        y[i] = *reinterpret_cast<const float4*>(y0 + r * routed_stride + c * 4ull);
                     }
-                    v[0] = fmaf(wr, y.x, v[0]); v[1] = fmaf(wr, y.y, v[1]); v[2] = fmaf(wr, y.z, v[2]); v[3] = fmaf(wr, y.w, v[3]);
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const float wr = r0 + i < selected ? w_s[r0 + i] : 0.f;
+                    if (wr != 0.f) { v[0] = fmaf(wr, y[i].x, v[0]); v[1] = fmaf(wr, y[i].y, v[1]); v[2] = fmaf(wr, y[i].z, v[2]); v[3] = fmaf(wr, y[i].w, v[3]); }
                 }
             }
             bad |= !finite_f32(v[0]) | !finite_f32(v[1]) | !finite_f32(v[2]) | !finite_f32(v[3]);

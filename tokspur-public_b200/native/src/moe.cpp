@@ -94,7 +94,7 @@ void prepare_moe_many(CudaGraph& g, const MoeWeights& w, MoeShape shape) {
 uint64_t moe_many_dispatches(const CudaGraph&, const MoeWeights&, MoeShape shape, uint32_t steps) {
     shape_check(shape);
     if (!steps || steps > 64) throw FormatError("invalid row count for the mixture");
-    return 5;   // router GEMV, prologue (routing + permutation + row conversion), gate-up, down, mixture
+    return 6;   // router GEMV, routing (+ row conversion), permutation + tile table, gate-up, down, mixture
 }
 
 void encode_moe_many(CudaGraph& g, const MoeWeights& w, const MoeManyScratch& s, GpuView input, GpuView output, MoeShape shape, RouterMode mode,
@@ -159,7 +159,7 @@ void encode_rows(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView
                                         shape.hidden, shape.experts, shape.selected, uint32_t(mode), normalize_selected,
                                         g.device_pointer(output, true), uint64_t(shape.channels) * 4, 0, g.error_word(), g.stream());
     if (rc != TSP_OK) throw FormatError(tsp_last_error());
-    g.count_dispatches(4);   // route + permutation + tile table (one launch), gate-up, down, combine (the shared expert rides in the routed launches)
+    g.count_dispatches(5);   // routing (+ row conversion), permutation + tile table, gate-up, down, combine (the shared expert rides in the routed launches)
 }
 }  // namespace
 

@@ -440,6 +440,30 @@ def head_record(args, dev, M):
     rec = {"rows": M, "ms_per_step": ms, "tokens_per_s": M / (ms * 1e-3), "e2e_ms_per_step": ms_e2e, "timed_repeats": repeats,
            "hbm_gbs": bytes_launch / (ms * 1e-3) / 1e9, "hbm_frac": bytes_launch / (ms * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind,
            "algorithmic_bytes_per_launch": bytes_launch, "h2d_bytes_per_step": M * CHANNELS * 4, "d2h_bytes_per_step": M * VOCAB * 4}
+    # the sampler's top-64 rows of the same logits (the step that follows the head in the verify pass): head + top-k per step
+    topk_scratch = torch.empty(lib.tsp_logit_topk_scratch_bytes(M, VOCAB), dtype=torch.uint8, device=dev)
+    topk_rows = torch.empty(lib.tsp_logit_topk_output_bytes(M), dtype=torch.uint8, device=dev)
+    host_rows = torch.empty(topk_rows.numel(), dtype=torch.uint8).pin_memory()
+
+    def topk():
+        capi.check(lib.tsp_logit_topk(out.data_ptr(), VOCAB * 4, M, VOCAB, topk_scratch.data_ptr(), topk_scratch.numel(), topk_rows.data_ptr(),
+                                      topk_rows.numel(), st))
+
+    def resident_topk(i):
+        project(i, dev_x[i % nb])
+        topk()
+
+    def e2e_topk(i):   # what the verify pass needs back is the 528-byte rows, not the logits
+        sx.copy_(host_x[i % nb], non_blocking=True)
+        project(i, sx)
+        topk()
+        host_rows.copy_(topk_rows, non_blocking=True)
+        stream.synchronize()
+
+    ms_tk, _ = timed_median(resident_topk, args.steps, args.warmup, args.min_seconds / 4)
+    ms_tk_e2e, _ = timed_median(e2e_topk, max(4, args.steps // 4), args.warmup, args.min_seconds / 4)
+    rec["with_logit_topk"] = {"ms_per_step": ms_tk, "e2e_ms_per_step": ms_tk_e2e, "d2h_bytes_per_step": M * 528,
+                              "launches_per_step": 4, "note": "head (zeroing pass + kernel) + two top-k launches; only the top-64 rows return to the host"}
     cpu = None
     if args.cpu_tokens != 0:
         orc, kind = cpu_oracle()

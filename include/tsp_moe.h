@@ -193,6 +193,21 @@ int tsp_moe_combine(const void* d_routed, uint64_t routed_stride_bytes, uint32_t
                     float* d_out, uint64_t out_stride_bytes, void* d_out_f16, uint64_t out_f16_stride_bytes,
                     uint32_t* d_error, void* stream);
 
+/* Top-64 rows of the sampler behind the vocabulary head. Replaces `MetalGraph::logit_topk` (graph.hpp:1030-1033, graph.mm:9443-9478)
+ * and its size helpers; one output row per logits row in the layout of `GpuLogitTopKRow` (sampling.hpp:21-29, 528 bytes):
+ * u32 vocabulary, count, first_nonfinite_col, first_subnormal_col (0xffffffff: none), u32 ids[64], f32 logits[64].
+ * Order as `cpu_logit_topk_row` (sampling.cpp:473-515): value descending with -0 == +0, ties to the lower column; non-finite
+ * logits are left out, subnormal ones compete; raw bits are returned; unused slots hold id 0 and -infinity.
+ * d_logits: FP32 rows [rows x vocabulary] with a byte stride; d_partial: scratch of tsp_logit_topk_scratch_bytes() (one row per
+ * tile of 4096 columns); both buffers 4-byte aligned and disjoint from the logits. rows 1..2048, vocabulary 1..2^20. */
+#define TSP_TOPK_CAPACITY 64u
+#define TSP_TOPK_TILE_SPAN 4096u
+#define TSP_TOPK_ROW_BYTES 528u
+uint64_t tsp_logit_topk_scratch_bytes(uint32_t rows, uint32_t vocabulary);
+uint64_t tsp_logit_topk_output_bytes(uint32_t rows);
+int tsp_logit_topk(const float* d_logits, uint64_t logits_stride_bytes, uint32_t rows, uint32_t vocabulary, void* d_partial,
+                   uint64_t partial_bytes, void* d_rows_out, uint64_t out_bytes, void* stream);
+
 /* Hyper-connection residual read / write, the steps either side of the FFN sub-layer in every layer (mtp_head.cpp:206-208).
  * Replace `MetalGraph::residual_read` / `residual_write` (graph.hpp:1056-1058; CPU: gated_residual_reference's last step and
  * residual_write_reference, operators.cpp:79-96), batched over `tokens` rows; all buffers FP32, row-major, densely packed:

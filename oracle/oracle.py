@@ -153,6 +153,16 @@ class Oracle:
             ids[t], w[t] = self.route(logits[t], selected, mode, normalize)
         return ids, w
 
+    def logit_topk_row(self, logits: np.ndarray):
+        """Top-64 row of the sampler (port only: the reference's sampling.cpp needs arm_neon.h and does not build here).
+        Returns a dict: vocabulary, count, first_nonfinite_col, first_subnormal_col, ids [64] uint32, logits [64] float32."""
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        raw = np.zeros(132, dtype=np.uint32)   # 528 bytes
+        self.lib.tso_logit_topk_row.argtypes = [f32p, C.c_size_t, u32p]
+        self._ok(self.lib.tso_logit_topk_row(_ptr(logits, f32p), logits.size, _ptr(raw, u32p)))
+        return {"vocabulary": int(raw[0]), "count": int(raw[1]), "first_nonfinite_col": int(raw[2]), "first_subnormal_col": int(raw[3]),
+                "ids": raw[4:68].copy(), "logits": raw[68:132].view(np.float32).copy()}
+
     def mixture(self, experts: np.ndarray, weights: np.ndarray, shared: np.ndarray, shared_logit: float) -> np.ndarray:
         experts = np.ascontiguousarray(experts, dtype=np.float64)
         weights = np.ascontiguousarray(weights, dtype=np.float64)

@@ -278,6 +278,43 @@ int tso_mixture(const double* experts, const double* weights, size_t selected, c
     return TSO_OK;
 }
 
+/* sampling.cpp:473-515 */
+static int topk_beats(float va, uint32_t ida, float vb, uint32_t idb) {
+    const float ca = va == 0.0f ? 0.0f : va, cb = vb == 0.0f ? 0.0f : vb;   /* -0 and +0 compare as one value */
+    return ca > cb || (ca == cb && ida < idb);
+}
+
+int tso_logit_topk_row(const float* logits, size_t vocabulary, tso_topk_row* out) {
+    if (!vocabulary || vocabulary > ((size_t)1 << 20)) return TSO_E_SHAPE;
+    memset(out, 0, sizeof *out);
+    out->vocabulary = (uint32_t)vocabulary;
+    out->first_nonfinite_col = out->first_subnormal_col = 0xffffffffu;
+    for (int i = 0; i < TSO_TOPK_CAPACITY; ++i) out->logits[i] = -INFINITY;
+    uint32_t count = 0;
+    for (size_t i = 0; i < vocabulary; ++i) {
+        const float raw = logits[i];
+        uint32_t bits;
+        memcpy(&bits, &raw, 4);
+        const uint32_t exponent = bits & 0x7f800000u, mantissa = bits & 0x007fffffu, col = (uint32_t)i;
+        if (exponent == 0x7f800000u) {
+            if (out->first_nonfinite_col == 0xffffffffu) out->first_nonfinite_col = col;
+            continue;
+        }
+        if (exponent == 0 && mantissa != 0 && out->first_subnormal_col == 0xffffffffu) out->first_subnormal_col = col;
+        if (count == TSO_TOPK_CAPACITY && !topk_beats(raw, col, out->logits[count - 1], out->ids[count - 1])) continue;
+        uint32_t pos = count < TSO_TOPK_CAPACITY ? count++ : TSO_TOPK_CAPACITY - 1;
+        while (pos > 0 && topk_beats(raw, col, out->logits[pos - 1], out->ids[pos - 1])) {
+            out->logits[pos] = out->logits[pos - 1];
+            out->ids[pos] = out->ids[pos - 1];
+            --pos;
+        }
+        out->logits[pos] = raw;
+        out->ids[pos] = col;
+    }
+    out->count = count;
+    return TSO_OK;
+}
+
 /* ---- Pack v3 planar layout ---- */
 
 /* planar_pack_v3.cpp:601-650 (Q4_K and Q8_0 rows of the table) */

@@ -73,6 +73,18 @@ int tso_route(const double* logits, size_t experts, size_t selected, uint32_t mo
 int tso_mixture(const double* experts, const double* weights, size_t selected, const double* shared,
                 size_t channels, double shared_logit, double* out);
 
+/* Top-64 of a row of logits for the sampler (sampling.cpp:473-515; row type sampling.hpp:21-29, 528 bytes). Non-finite values
+ * are left out and the first such column is recorded; the first subnormal column is recorded too (the value still competes).
+ * Order: value descending with -0 == +0, ties to the lower column; the raw bits of the logits are kept. Unused slots hold
+ * -infinity and id 0. */
+#define TSO_TOPK_CAPACITY 64
+typedef struct {
+    uint32_t vocabulary, count, first_nonfinite_col, first_subnormal_col;
+    uint32_t ids[TSO_TOPK_CAPACITY];
+    float logits[TSO_TOPK_CAPACITY];
+} tso_topk_row;
+int tso_logit_topk_row(const float* logits, size_t vocabulary, tso_topk_row* out);
+
 /* ---- Pack v3 planar expert layout (planar_pack_v3.cpp:601-896) ---- */
 typedef struct {
     uint32_t source_type, columns, rows, blocks_per_row;

@@ -273,3 +273,55 @@ def test_residual_read_write_port_equals_reference(oracle, ref_oracle):
         assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
         out = rng.normal(size=Cn)
         assert np.array_equal(oracle.residual_write(st, out, a[1]), ref_oracle.residual_write(st, out, a[1]))
+
+
+def _topk_brute(row):
+    """Independent statement of the order: finite values, -0 as +0, value descending, column ascending."""
+    row = np.asarray(row, dtype=np.float32)
+    finite = np.isfinite(row)
+    cols = np.nonzero(finite)[0]
+    canon = np.where(row[cols] == 0, np.float32(0), row[cols])
+    order = np.lexsort((cols, -canon.astype(np.float64)))[:64]
+    return cols[order], row[cols[order]]
+
+
+def test_logit_topk_known_answers_of_the_reference_test(oracle):
+    """The rows native/tests/test_logit_topk.cpp:104-155 and :197-222 build, with the answers that test states: ties at 17.5 to
+    the lower column, -0 before +0 by column with its sign bit kept, bad-value columns recorded. (The reference's sampling.cpp
+    includes arm_neon.h and cannot be compiled here: this pin is by known answers and by an independent ordering.)"""
+    for vocab in (32, 64, 5000, 248320):
+        rows = 4 if vocab == 248320 else 3
+        rng = np.random.default_rng(0x51A70000 ^ vocab)
+        logits = (rng.standard_normal((rows, vocab)) * 3.25).astype(np.float32)
+        logits[0, [3, 19, 31]] = 17.5
+        if vocab >= 64:
+            logits[0, vocab - 2], logits[0, vocab - 1] = -0.0, 0.0
+            c = np.arange(vocab - 2)
+            keep = np.isin(c, [3, 19, 31])
+            logits[0, :vocab - 2] = np.where(keep, logits[0, :vocab - 2], -100.0 - (c % 11))
+        for r in range(rows):
+            got = oracle.logit_topk_row(logits[r])
+            assert got["vocabulary"] == vocab and got["count"] == min(vocab, 64)
+            assert got["first_nonfinite_col"] == 0xFFFFFFFF and got["first_subnormal_col"] == 0xFFFFFFFF
+            ids, vals = _topk_brute(logits[r])
+            assert np.array_equal(got["ids"][:got["count"]], ids)
+            assert np.array_equal(got["logits"][:got["count"]].view(np.uint32), vals.view(np.uint32))
+        first = oracle.logit_topk_row(logits[0])
+        assert list(first["ids"][:3]) == [3, 19, 31]
+        if vocab >= 64:
+            assert first["ids"][3] == vocab - 2 and first["logits"][3:4].view(np.uint32)[0] == 0x80000000
+            assert first["ids"][4] == vocab - 1 and first["logits"][4:5].view(np.uint32)[0] == 0
+    vocab = 8192
+    bad = np.full((2, vocab), -1.0, dtype=np.float32)
+    bad.view(np.uint32)[0, 5] = 1
+    bad[0, 5000] = np.nan
+    bad[1, 17] = -np.inf
+    bad.view(np.uint32)[1, 99] = 0x80000001
+    a, b = oracle.logit_topk_row(bad[0]), oracle.logit_topk_row(bad[1])
+    assert (a["first_subnormal_col"], a["first_nonfinite_col"]) == (5, 5000)
+    assert (b["first_nonfinite_col"], b["first_subnormal_col"]) == (17, 99)
+    assert a["ids"][0] == 5 and a["count"] == 64   # the positive subnormal beats every -1 and still competes
+    short = oracle.logit_topk_row(np.array([np.nan, 2.0, np.inf, 1.0], dtype=np.float32))
+    assert short["count"] == 2 and list(short["ids"][:3]) == [1, 3, 0] and np.isneginf(short["logits"][2])
+    with pytest.raises(Exception):
+        oracle.logit_topk_row(np.zeros(0, dtype=np.float32))

@@ -50,6 +50,7 @@ int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*
                 const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t, const GemvShared* = nullptr);
 
 int launch_route_offsets(const uint32_t*, uint32_t, uint32_t*, cudaStream_t);
+int launch_logit_topk(const float*, uint64_t, uint32_t, uint32_t, uint32_t*, uint32_t*, cudaStream_t);
 int launch_rows_f16k(const void*, uint64_t, uint32_t, uint32_t, uint32_t, void*, uint64_t, uint32_t*, cudaStream_t);
 int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, uint32_t, uint32_t, const uint32_t*,
                    const uint32_t*, const uint32_t*, const uint32_t*, uint32_t*, void*, uint64_t, uint32_t, uint32_t*, cudaStream_t, const GroupedShared* = nullptr);
@@ -452,6 +453,28 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
                            x32_stride, 0, s->d_shared_logit, tokens, channels, selected,
                            out_dtype == 0 ? static_cast<float*>(d_out) : nullptr, out_dtype == 0 ? out_stride : 0,
                            out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
+}
+
+uint64_t tsp_logit_topk_scratch_bytes(uint32_t rows, uint32_t vocabulary) {
+    if (!rows || rows > 2048 || !vocabulary || vocabulary > (1u << 20)) return 0;
+    return static_cast<uint64_t>(rows) * ((vocabulary + TSP_TOPK_TILE_SPAN - 1) / TSP_TOPK_TILE_SPAN) * TSP_TOPK_ROW_BYTES;
+}
+uint64_t tsp_logit_topk_output_bytes(uint32_t rows) { return rows && rows <= 2048 ? static_cast<uint64_t>(rows) * TSP_TOPK_ROW_BYTES : 0; }
+
+int tsp_logit_topk(const float* d_logits, uint64_t stride, uint32_t rows, uint32_t vocabulary, void* d_partial, uint64_t partial_bytes,
+                   void* d_rows_out, uint64_t out_bytes, void* stream) {
+    TSP_REQUIRE(d_logits && d_partial && d_rows_out, "logit top-k: null buffer");
+    TSP_REQUIRE(rows >= 1 && rows <= 2048 && vocabulary >= 1 && vocabulary <= (1u << 20) && stride >= static_cast<uint64_t>(vocabulary) * 4 && stride % 4 == 0,
+                "logit top-k geometry mismatch");
+    const uint64_t need_partial = tsp_logit_topk_scratch_bytes(rows, vocabulary), need_out = tsp_logit_topk_output_bytes(rows);
+    const uint64_t in_bytes = static_cast<uint64_t>(rows - 1) * stride + static_cast<uint64_t>(vocabulary) * 4;
+    TSP_REQUIRE(partial_bytes >= need_partial && out_bytes >= need_out && reinterpret_cast<uintptr_t>(d_logits) % 4 == 0 &&
+                reinterpret_cast<uintptr_t>(d_partial) % 4 == 0 && reinterpret_cast<uintptr_t>(d_rows_out) % 4 == 0,
+                "logit top-k buffer span or alignment mismatch");
+    TSP_REQUIRE(!overlap(d_logits, in_bytes, d_partial, need_partial) && !overlap(d_logits, in_bytes, d_rows_out, need_out) &&
+                !overlap(d_partial, need_partial, d_rows_out, need_out), "logit top-k buffers overlap");
+    return launch_logit_topk(d_logits, stride, rows, vocabulary, static_cast<uint32_t*>(d_partial), static_cast<uint32_t*>(d_rows_out),
+                             static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

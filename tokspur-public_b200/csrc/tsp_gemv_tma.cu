@@ -658,7 +658,7 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     const uint32_t nt = (!gateup && nblk <= 2 && a->rows % 32 == 0) ? 2 : 1;
     const uint32_t R = (gateup ? 8 : 16) * nt;
     const uint32_t nmat = gateup ? 2 : 1;
-    const uint32_t kb = (nblk % 4 == 0 && nblk >= 8) ? 4 : (nblk % 2 == 0 && nblk >= 4) ? 2 : 1;
+    const uint32_t kb = (nblk % 4 == 0 && nblk >= 8) ? 4 : (nblk % 2 == 0 && (nblk >= 4 || nt == 2)) ? 2 : 1;
     if (R * nblk > 2048) return 1;   // header boxes are limited to 256 lines
     p.upi = nblk / kb;
     p.groups = a->rows / R;
@@ -758,7 +758,7 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
 #define TSP_D2(L)                                                                  \
     if (a->layout == L) {                                                          \
         if (gateup) { if (nc == 1) TSP_D3(L, true, 1, 1); TSP_D3(L, true, 2, 1); } \
-        if (nt == 2) { if (nc == 1) TSP_D4(L, false, 1, 2, 1); TSP_D4(L, false, 2, 2, 1); } \
+        if (nt == 2) { if (kb == 2) { if (nc == 1) TSP_D4(L, false, 1, 2, 2); TSP_D4(L, false, 2, 2, 2); } if (nc == 1) TSP_D4(L, false, 1, 2, 1); TSP_D4(L, false, 2, 2, 1); } \
         if (nc == 1) TSP_D3(L, false, 1, 1);                                       \
         TSP_D3(L, false, 2, 1);                                                    \
     }

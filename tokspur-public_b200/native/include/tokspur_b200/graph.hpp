@@ -97,6 +97,11 @@ public:
     void moe_route_rows(GpuView logits, GpuView indices, GpuView weights, uint32_t experts, uint32_t selected, uint32_t tokens, RouterMode mode,
                         bool normalize_selected);
     [[nodiscard]] bool evaluate_router_margin(uint32_t tokens);   // waits for the stream; true when a row's margin is within 2 epsilon
+    // The sampler's top-64 rows of a batch of logits rows (graph.hpp:1030-1033): scratch of logit_topk_scratch_bytes(), one
+    // 528-byte row (GpuLogitTopKRow, sampling.hpp:21-29) per logits row in `out_rows`
+    static uint64_t logit_topk_scratch_bytes(uint32_t max_rows, uint32_t max_vocabulary = 1u << 20) { return tsp_logit_topk_scratch_bytes(max_rows, max_vocabulary); }
+    static uint64_t logit_topk_output_bytes(uint32_t max_rows) { return tsp_logit_topk_output_bytes(max_rows); }
+    void logit_topk(GpuRowsF32 logits, GpuView partial_scratch, GpuView out_rows);
     // Hyper-connection residual read / write around the FFN sub-layer (graph.hpp:1056-1058)
     void residual_read(GpuView normalized, GpuView scores, GpuView inject_logits, GpuView output, GpuView scales, uint32_t branches, uint32_t channels);
     void residual_write(GpuView streams, GpuView output, GpuView scales, GpuView destination);

@@ -320,6 +320,19 @@ bool CudaGraph::evaluate_router_margin(uint32_t tokens) {
     return fallback != 0;
 }
 
+void CudaGraph::logit_topk(GpuRowsF32 logits, GpuView partial_scratch, GpuView out_rows) {
+    require_batch();
+    if (!logits.rows || logits.rows > 2048 || !logits.columns || logits.columns > (1u << 20) || logits.stride_bytes < uint64_t(logits.columns) * 4 ||
+        logits.stride_bytes % 4)
+        throw FormatError("GPU logit top-k geometry mismatch");
+    if (logits.view.bytes < uint64_t(logits.rows - 1) * logits.stride_bytes + uint64_t(logits.columns) * 4 ||
+        partial_scratch.bytes < tsp_logit_topk_scratch_bytes(logits.rows, logits.columns) || out_rows.bytes < tsp_logit_topk_output_bytes(logits.rows))
+        throw FormatError("GPU logit top-k buffer span or alignment mismatch");
+    check(tsp_logit_topk(static_cast<const float*>(device_pointer(logits.view)), logits.stride_bytes, logits.rows, logits.columns,
+                         device_pointer(partial_scratch, true), partial_scratch.bytes, device_pointer(out_rows, true), out_rows.bytes, stream_));
+    dispatches_ += 2;
+}
+
 // ---- residual read / write ---------------------------------------------------------------------------------------------------
 void CudaGraph::residual_read(GpuView normalized, GpuView scores, GpuView inject_logits, GpuView output, GpuView scales, uint32_t branches, uint32_t channels) {
     require_batch();

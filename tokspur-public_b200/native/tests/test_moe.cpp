@@ -361,6 +361,22 @@ void operators(CudaGraph& g, uint32_t seed) {
     g.abort();
     refuses([&] { g.configure_router_margin_epsilon(0.f); }, "zero margin epsilon accepted");
 
+    // top-64 rows of the logits just produced, against the oracle's row, bit for bit
+    {
+        const auto scratch = g.zeros(CudaGraph::logit_topk_scratch_bytes(T, E), "topk scratch"), rows = g.zeros(CudaGraph::logit_topk_output_bytes(T), "topk rows");
+        g.begin();
+        g.logit_topk({logits, T, E, uint64_t(E) * 4}, scratch, rows);
+        (void)g.submit();
+        const auto raw = g.read(rows);
+        for (uint32_t t = 0; t < T; ++t) {
+            tso_topk_row want;
+            require(tso_logit_topk_row(gl.data() + size_t(t) * E, E, &want) == TSO_OK, "oracle top-k");
+            require(std::memcmp(raw.data() + size_t(t) * sizeof want, &want, sizeof want) == 0, "logit top-k row differs from the oracle");
+        }
+        g.begin();
+        refuses([&] { g.logit_topk({logits, T, E, uint64_t(E) * 4}, g.slice(scratch, 0, 528), rows); }, "short top-k scratch accepted");
+        g.abort();
+    }
     // residual read / write on one token
     std::vector<double> dn(size_t(B) * C), dsc(size_t(B) * C), dinj(B), dstreams(size_t(B) * C), dout(C);
     const auto fn = activations(seed + 20, size_t(B) * C, 1.5f), fsc = activations(seed + 21, size_t(B) * C, 3.f), finj = activations(seed + 22, B, 2.f);

@@ -183,7 +183,8 @@ route_kernel(const float* __restrict__ logits, uint64_t stride_bytes, uint32_t t
 // ---------------------------------------------------------------------------------------------
 // permutation: one block per expert compacts, in ascending token order, the routes that name it.
 // ---------------------------------------------------------------------------------------------
-constexpr int kPermuteThreads = 128;
+constexpr int kPermuteThreads = 512;
+constexpr uint32_t kPermuteExperts = 2;   // experts per block: a token's ids are read once for all of them
 
 __global__ void __launch_bounds__(kPermuteThreads)
 grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t first, int local_only,
@@ -191,34 +192,52 @@ grouped_routes_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_
     pdl_launch_dependents();
     pdl_wait();
 
-    __shared__ uint32_t totals[kPermuteThreads / 32];
-    const uint32_t expert = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint32_t accumulated = 0;
+    __shared__ uint32_t totals[kPermuteExperts][kPermuteThreads / 32];
+    const uint32_t e0 = blockIdx.x * kPermuteExperts, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t accumulated[kPermuteExperts];
+#pragma unroll
+    for (uint32_t q = 0; q < kPermuteExperts; ++q) accumulated[q] = 0;
     for (uint32_t base = 0; base < tokens; base += kPermuteThreads) {
         const uint32_t token = base + tid;
-        uint32_t slot = 0xffffffffu, matches = 0;
+        uint32_t slot[kPermuteExperts], matches[kPermuteExperts];
+#pragma unroll
+        for (uint32_t q = 0; q < kPermuteExperts; ++q) { slot[q] = 0; matches[q] = 0; }
         if (token < tokens) {
             for (uint32_t i = 0; i < selected; ++i) {
                 // ids are global; this launch owns experts [first, first + experts). With local_only, routes to other
                 // owners are simply not this rank's business; without it they are an index error.
                 const uint32_t id = ids[static_cast<uint64_t>(token) * selected + i] - first;
-                if (id >= experts && expert == 0 && !local_only) raise_error(error, TSP_ERR_INDEX);
-                if (id == expert) { slot = i; ++matches; }
+                if (id >= experts && blockIdx.x == 0 && !local_only) raise_error(error, TSP_ERR_INDEX);
+#pragma unroll
+                for (uint32_t q = 0; q < kPermuteExperts; ++q)
+                    if (id == e0 + q) { slot[q] = i; ++matches[q]; }
             }
         }
-        if (matches > 1) raise_error(error, TSP_ERR_INDEX);
-        const bool found = matches == 1;
-        const uint32_t ballot = __ballot_sync(0xffffffffu, found);
-        const uint32_t prefix = __popc(ballot & ((1u << lane) - 1u));
-        if (lane == 0) totals[warp] = __popc(ballot);
+        uint32_t prefix[kPermuteExperts];
+#pragma unroll
+        for (uint32_t q = 0; q < kPermuteExperts; ++q) {
+            if (matches[q] > 1) raise_error(error, TSP_ERR_INDEX);
+            const uint32_t ballot = __ballot_sync(0xffffffffu, matches[q] == 1);
+            prefix[q] = __popc(ballot & ((1u << lane) - 1u));
+            if (lane == 0) totals[q][warp] = __popc(ballot);
+        }
         __syncthreads();
-        uint32_t before = 0, chunk = 0;
-        for (uint32_t i = 0; i < kPermuteThreads / 32; ++i) { if (i < warp) before += totals[i]; chunk += totals[i]; }
-        if (found) token_map[static_cast<uint64_t>(expert) * tokens + accumulated + before + prefix] = token * selected + slot;
-        accumulated += chunk;
+#pragma unroll
+        for (uint32_t q = 0; q < kPermuteExperts; ++q) {
+            uint32_t before = 0, chunk = 0;
+            for (uint32_t i = 0; i < kPermuteThreads / 32; ++i) { if (i < warp) before += totals[q][i]; chunk += totals[q][i]; }
+            if (matches[q] == 1 && e0 + q < experts)
+                token_map[static_cast<uint64_t>(e0 + q) * tokens + accumulated[q] + before + prefix[q]] = token * selected + slot[q];
+            accumulated[q] += chunk;
+        }
         __syncthreads();
     }
-    if (tid == 0) counts[expert] = accumulated;
+    if (tid < kPermuteExperts && e0 + tid < experts) {
+        uint32_t c = 0;
+#pragma unroll
+        for (uint32_t q = 0; q < kPermuteExperts; ++q) if (q == tid) c = accumulated[q];
+        counts[e0 + tid] = c;
+    }
 }
 
 // tasks = {live_tiles, routes, (expert, start) pairs in ascending expert order, 0xffffffff padding}
@@ -439,6 +458,47 @@ combine_kernel(const void* __restrict__ routed, uint64_t routed_stride, const fl
     const uint32_t per_slice = ((channels + gridDim.y - 1) / gridDim.y + 3u) & ~3u;
     const uint32_t c_end = min(channels, (blockIdx.y + 1) * per_slice);
     const char* y0 = reinterpret_cast<const char*>(routed) + static_cast<uint64_t>(token) * selected * routed_stride;
+    if (R16 && vec4 == 2 && (channels & 7u) == 0 && gridDim.y == 1) {   // vec4 == 2: every row of every buffer starts on a 16-byte boundary
+        // binary16 route rows (prefill): eight channels per thread step, one 16-byte load per route row, five rows in flight
+        for (uint32_t c = tid * 8; c < channels; c += kCombineThreads * 8) {
+            float v[8];
+            if (sh) {
+                const float4 a = *reinterpret_cast<const float4*>(sh + c), b = *reinterpret_cast<const float4*>(sh + c + 4);
+                v[0] = gate * a.x; v[1] = gate * a.y; v[2] = gate * a.z; v[3] = gate * a.w; v[4] = gate * b.x; v[5] = gate * b.y; v[6] = gate * b.z; v[7] = gate * b.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.f;
+            }
+            for (uint32_t r0 = 0; r0 < selected; r0 += 5) {
+                uint4 y[5];
+#pragma unroll
+                for (uint32_t i = 0; i < 5; ++i) y[i] = *reinterpret_cast<const uint4*>(y0 + min(r0 + i, selected - 1) * routed_stride + c * 2ull);
+#pragma unroll
+                for (uint32_t i = 0; i < 5; ++i) {
+                    const float wr = r0 + i < selected ? w_s[r0 + i] : 0.f;
+                    if (wr != 0.f) {
+                        const uint32_t w4[4] = {y[i].x, y[i].y, y[i].z, y[i].w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[q]));
+                            v[2 * q] = fmaf(wr, f.x, v[2 * q]); v[2 * q + 1] = fmaf(wr, f.y, v[2 * q + 1]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bad |= !finite_f32(v[i]);
+            if (out) { *reinterpret_cast<float4*>(o + c) = make_float4(v[0], v[1], v[2], v[3]); *reinterpret_cast<float4*>(o + c + 4) = make_float4(v[4], v[5], v[6], v[7]); }
+            if (out16) {
+                uint32_t h[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { const __half2 t2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]); h[q] = *reinterpret_cast<const uint32_t*>(&t2); }
+                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out16) + token * out16_stride + c * 2ull) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+        }
+        if (bad) raise_error(error, TSP_ERR_NONFINITE);
+        return;
+    }
     for (uint32_t c = blockIdx.y * per_slice + tid * 4; c < c_end; c += kCombineThreads * 4) {
         if (vec4 && c + 4 <= c_end) {
             const float4 s4 = sh ? *reinterpret_cast<const float4*>(sh + c) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -682,7 +742,7 @@ int launch_route(const float* logits, uint64_t stride, uint32_t tokens, uint32_t
 
 int launch_permute(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile, uint32_t first, int local_only,
                    uint32_t* token_map, uint32_t* counts, uint32_t* tasks, uint32_t* error, cudaStream_t st) {
-    TSP_CUDA(launch_pdl(grouped_routes_kernel, dim3(experts), dim3(kPermuteThreads), 0, st, ids, tokens, experts, selected, first, local_only, token_map, counts, error));
+    TSP_CUDA(launch_pdl(grouped_routes_kernel, dim3((experts + kPermuteExperts - 1) / kPermuteExperts), dim3(kPermuteThreads), 0, st, ids, tokens, experts, selected, first, local_only, token_map, counts, error));
     TSP_CUDA(cudaGetLastError());
     const uint32_t bound = static_cast<uint32_t>((static_cast<uint64_t>(tokens) * selected) / tile + experts);
     TSP_CUDA(launch_pdl(grouped_tasks_kernel, dim3(1), dim3(256), (experts + 1) * sizeof(uint32_t), st, counts, tokens, experts, selected, tile, bound, local_only, tasks, error));
@@ -701,9 +761,10 @@ int launch_combine(const void* routed, uint64_t routed_stride, uint32_t routed_f
     auto a16 = [](const void* p, uint64_t stride) { return (reinterpret_cast<uintptr_t>(p) | stride) % 16 == 0; };
     const int vec4 = (routed_f16 ? (reinterpret_cast<uintptr_t>(routed) | routed_stride) % 8 == 0 : a16(routed, routed_stride)) && (!shared || a16(shared, shared_stride)) &&
                      (!out || a16(out, out_stride)) && (!out16 || (reinterpret_cast<uintptr_t>(out16) | out16_stride) % 8 == 0);
+    const int vec8 = vec4 && routed_f16 && a16(routed, routed_stride) && (!out16 || a16(out16, out16_stride));
     const dim3 grid(tokens, slices), block(kCombineThreads);
 #define TSP_COMBINE(R, X) TSP_CUDA(launch_pdl(combine_kernel<R, X>, grid, block, 0, st, routed, routed_stride, weights, shared, shared_stride, shared_router, \
-                                              x, x_stride, shared_logit, channels, selected, out, out_stride, static_cast<__half*>(out16), out16_stride, vec4, error))
+                                              x, x_stride, shared_logit, channels, selected, out, out_stride, static_cast<__half*>(out16), out16_stride, vec8 ? 2 : vec4, error))
     if (routed_f16) { if (x_f16) TSP_COMBINE(true, true); else TSP_COMBINE(true, false); }
     else { if (x_f16) TSP_COMBINE(false, true); else TSP_COMBINE(false, false); }
 #undef TSP_COMBINE

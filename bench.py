@@ -277,7 +277,7 @@ def decode_record(args, dev, T, layers, etype, layout, full: bool):
                 "peak_kind": peak_kind, "timing": "average of a back-to-back loop of this launch alone over the rotating layers (CUDA events)",
                 # measured DRAM bytes of one captured launch (profiles/gemv3_gate_up_and_down_decode_T64.md: 457.2 MB for 361 experts),
                 # scaled to the experts this launch touches: traffic grows with the experts touched, the activations stay in L2
-                "traffic": 457.2e6 / 361 * (U0 + 1) if etype == formats.Q4_K and layout == formats.PLANAR else None,
+                "traffic": 463.2e6 / 359 * (U0 + 1) if etype == formats.Q4_K and layout == formats.PLANAR else None,
                 "traffic_source": "profiles/gemv3_gate_up_and_down_decode_T64.md (ncu), scaled by experts hit",
                 "algorithmic_bytes_per_launch": gu_bytes, "launch_ms": gu_ms, "unique_experts": U0}
     rec["stage_ms"] = {"gate_up_launch_ms": gu_ms, "down_launch_ms": dn_ms, "rest_of_step_ms": ms - gu_ms - dn_ms,
@@ -579,7 +579,9 @@ def run_ours(args):
                                  "h2d_bytes_per_step": rec["h2d_bytes_per_step"], "d2h_bytes_per_step": rec["d2h_bytes_per_step"]},
                          "gpu_launches": args.steps,
                          "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q8_0> (dense head)", "achieved": rec["hbm_gbs"], "peak": hbm_peak, "unit": "GB/s",
-                                      "frac": rec["hbm_frac"], "peak_kind": peak_kind, "traffic": None, "algorithmic_bytes_per_launch": rec["algorithmic_bytes_per_launch"]},
+                                      "frac": rec["hbm_frac"], "peak_kind": peak_kind, "traffic": 348.1e6 if M == 16 else None,
+                                      "traffic_source": "profiles/gemv_q8_0_head_M16.md (ncu: DRAM throughput x duration of one launch at 16 rows)",
+                                      "algorithmic_bytes_per_launch": rec["algorithmic_bytes_per_launch"]},
                          "cpu_baseline": cpu, "extra": {"head": rec}})
         elif args.workload == "config1":
             rec = config1_record(args, dev)
@@ -597,7 +599,8 @@ def run_ours(args):
                                  "h2d_bytes_per_step": rec["h2d_bytes_per_step"], "d2h_bytes_per_step": rec["d2h_bytes_per_step"]},
                          "gpu_launches": 9 * max(4, args.steps // 4),
                          "roofline": {"bound": "tensor", "kernel": "grouped_mma_kernel<gate-up> (routed experts + shared expert, tcgen05)", "achieved": rec["gate_up_launch_tflops"],
-                                      "peak": tf_peak, "unit": "TFLOP/s", "frac": rec["gate_up_launch_frac_of_bf16_peak"], "peak_kind": peak_kind, "traffic": None,
+                                      "peak": tf_peak, "unit": "TFLOP/s", "frac": rec["gate_up_launch_frac_of_bf16_peak"], "peak_kind": peak_kind, "traffic": 478.4e6 if Tp == 4096 else None,
+                                      "traffic_source": "profiles/grouped_mma_prefill_T4096.md (ncu: DRAM throughput x duration of the gate-up launch)",
                                       "launch_ms": rec["stage_ms"]["gate_up_ms"]},
                          "cpu_baseline": cpu, "extra": {"prefill": rec}})
         else:

@@ -193,6 +193,11 @@ int tsp_moe_combine(const void* d_routed, uint64_t routed_stride_bytes, uint32_t
                     float* d_out, uint64_t out_stride_bytes, void* d_out_f16, uint64_t out_f16_stride_bytes,
                     uint32_t* d_error, void* stream);
 
+/* Self test of the bounded waits (no reference counterpart): one thread waits at most `polls` (1..65536) polls on a barrier
+ * that nothing arrives on, then sets TSP_ERR_TIMEOUT in *d_error and the kernel returns normally; the context stays usable.
+ * Every pipeline wait of the library gives up the same way (after 2^24 polls). */
+int tsp_selftest_bounded_wait(uint32_t polls, uint32_t* d_error, void* stream);
+
 /* Top-64 rows of the sampler behind the vocabulary head. Replaces `MetalGraph::logit_topk` (graph.hpp:1030-1033, graph.mm:9443-9478)
  * and its size helpers; one output row per logits row in the layout of `GpuLogitTopKRow` (sampling.hpp:21-29, 528 bytes):
  * u32 vocabulary, count, first_nonfinite_col, first_subnormal_col (0xffffffff: none), u32 ids[64], f32 logits[64].

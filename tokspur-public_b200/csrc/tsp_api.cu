@@ -50,6 +50,7 @@ int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*
                 const uint32_t*, const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t, const GemvShared* = nullptr);
 
 int launch_route_offsets(const uint32_t*, uint32_t, uint32_t*, cudaStream_t);
+int launch_bounded_wait_selftest(uint32_t, uint32_t*, cudaStream_t);
 int launch_logit_topk(const float*, uint64_t, uint32_t, uint32_t, uint32_t*, uint32_t*, cudaStream_t);
 int launch_rows_f16k(const void*, uint64_t, uint32_t, uint32_t, uint32_t, void*, uint64_t, uint32_t*, cudaStream_t);
 int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, uint32_t, uint32_t, const uint32_t*,
@@ -453,6 +454,11 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
                            x32_stride, 0, s->d_shared_logit, tokens, channels, selected,
                            out_dtype == 0 ? static_cast<float*>(d_out) : nullptr, out_dtype == 0 ? out_stride : 0,
                            out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
+}
+
+int tsp_selftest_bounded_wait(uint32_t polls, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(d_error && polls >= 1 && polls <= (1u << 16), "bounded-wait self test: null error word or poll limit outside 1..65536");
+    return launch_bounded_wait_selftest(polls, d_error, static_cast<cudaStream_t>(stream));
 }
 
 uint64_t tsp_logit_topk_scratch_bytes(uint32_t rows, uint32_t vocabulary) {

@@ -772,6 +772,22 @@ int launch_combine(const void* routed, uint64_t routed_stride, uint32_t routed_f
     return TSP_OK;
 }
 
+// One thread waits on a barrier that nothing ever arrives on, with a small poll limit: the wait gives up, the kernel reports
+// TSP_ERR_TIMEOUT through the error word and returns normally. This is the path every bounded wait of the library takes when
+// an arrival is lost; it is exercised here without making any real pipeline misbehave.
+__global__ void bounded_wait_selftest_kernel(uint32_t polls, uint32_t* error) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait(&bar, 0, polls)) raise_error(error, TSP_ERR_TIMEOUT);
+}
+
+int launch_bounded_wait_selftest(uint32_t polls, uint32_t* error, cudaStream_t st) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(polls, error);
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
 int launch_f16_to_f32(const void* in, uint64_t in_stride, float* out, uint64_t out_stride, uint32_t rows, uint32_t cols,
                       cudaStream_t st) {
     dim3 grid((cols + 1023) / 1024, rows);

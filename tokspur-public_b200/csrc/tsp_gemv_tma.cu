@@ -33,10 +33,15 @@ namespace tsp {
 int get_tensor_map_bytes(const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
                          bool swizzle128, CUtensorMap* out);
 
-constexpr int kW3 = 8;                  // consumer warps per CTA, one private pipeline each
+constexpr int kW3 = 8;                  // consumer warps per CTA, one private pipeline each (plain short-K projections run 16)
 constexpr int kProd3 = 4;               // producer warps per CTA (one warpgroup); each feeds kW3 / kProd3 pipelines
 constexpr int kThreads3 = (kW3 + kProd3) * 32;
 constexpr int kConsRegs = 232, kProdRegs = 40;   // (kW3 * kConsRegs + kProd3 * kProdRegs) * 32 <= 65536
+// Registers a consumer thread asks for with setmaxnreg.inc. The request is served from what the producer warps of the same
+// CTA give back and blocks until it is: W * (consumer - launch) <= kProd3 * (launch - kProdRegs) must hold for the
+// register count the kernel is launched with (168 for 12 warps, 96 for 20), or the consumers would wait for ever.
+// launch3() checks this against the compiled kernel before the first launch.
+__host__ __device__ constexpr int cons_regs(int w) { return w == kW3 ? kConsRegs : 104; }
 constexpr uint32_t kMaxStages3 = 8;     // per pipeline
 constexpr uint32_t kMaxHeaders3 = 4;    // per pipeline
 constexpr uint32_t kTableTiles = 32;    // token tiles whose routing data a CTA caches in shared memory
@@ -118,28 +123,29 @@ __device__ __forceinline__ Tile3 tile3(const Gemv3Params& p, uint32_t tile, uint
 // LAYOUT: TSP_LAYOUT_PLANAR (code lines + scale / (d, dmin) planes) or TSP_LAYOUT_GGUF (whole 144-byte blocks, unswizzled)
 // KB: super-blocks per unit. SPLIT: also run the low-half pass of the activations (needed unless every
 // activation is exactly a binary16 value).
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, int KB, bool SPLIT>
-__global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_constant__ Gemv3Maps maps, const Gemv3Params p) {
+// W: consumer warps (pipelines) per CTA. Every launch uses eight (232 registers each); the parameter exists for experiments.
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, int KB, bool SPLIT, int W = kW3>
+__global__ void __launch_bounds__((W + kProd3) * 32, 1) gemv3_kernel(const __grid_constant__ Gemv3Maps maps, const Gemv3Params p) {
     pdl_launch_dependents();
     extern __shared__ uint8_t smem3_raw[];
     // the 128-byte swizzle is a function of the shared-memory address: box bases must sit on 1024-byte boundaries
     uint8_t* smem3 = smem3_raw + ((1024u - (smem_u32(smem3_raw) & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem3);             // [kW3][S]
-    uint64_t* empty = reinterpret_cast<uint64_t*>(smem3 + 512);      // [kW3][S]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem3);             // [W][S]
+    uint64_t* empty = reinterpret_cast<uint64_t*>(smem3 + 512);      // [W][S]
     uint32_t* tt = reinterpret_cast<uint32_t*>(smem3 + 1024);        // [kTableTiles][4] expert, first route, count
     uint32_t* trid = reinterpret_cast<uint32_t*>(smem3 + 1536);      // [kTableTiles][16] route ids (output rows)
     uint32_t* tin = trid + kTableTiles * 16;                         // [kTableTiles][16] input rows
     uint32_t* rids = reinterpret_cast<uint32_t*>(smem3 + 5632);      // the same two for a tile beyond the cached window
     uint32_t* rins = rids + 16;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t warp = threadIdx.x >> 5;   // consumers: pipeline index; producers: kW3 + producer index
+    const uint32_t warp = threadIdx.x >> 5;   // consumers: pipeline index; producers: W + producer index
     const uint32_t S = p.n_stages, HB = p.n_hdr, UPI = p.upi;
     constexpr uint32_t NMAT = GATEUP ? 2 : 1;
     constexpr uint32_t R = (GATEUP ? 8 : 16) * NT;       // rows of one matrix in an item
     constexpr bool PLANAR = LAYOUT == TSP_LAYOUT_PLANAR;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < S * kW3; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (uint32_t s = 0; s < S * W; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_fence_init();
     }
     pdl_wait();   // everything above touched shared memory only
@@ -170,17 +176,17 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
         return tile3<NC>(p, tile, routed_tiles);
     };
     // pipeline w's items are item0 + w + 8n, each of UPI units
-    auto units_of = [&](uint32_t w) { return item0 + w < item1 ? (item1 - item0 - w + kW3 - 1) / kW3 * UPI : 0u; };
+    auto units_of = [&](uint32_t w) { return item0 + w < item1 ? (item1 - item0 - w + W - 1) / W * UPI : 0u; };
 
-    if (warp >= kW3) {
+    if (warp >= W) {
         // ---------------- producer warps: lane i < PER of producer q feeds the pipeline of consumer warp PER q + i ----------------
         // The lanes run one instruction stream: a pass issues the next unit of every pipeline whose stage is free, so a
         // pipeline waits at most one pass (a few hundred cycles) for its copy, whatever the other pipelines do.
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProdRegs));
-        constexpr uint32_t PER = kW3 / kProd3;
+        constexpr uint32_t PER = W / kProd3;
         if (lane >= PER) return;
         constexpr uint32_t mask = (1u << PER) - 1u;
-        const uint32_t w = (warp - kW3) * PER + lane;
+        const uint32_t w = (warp - W) * PER + lane;
         // Units of a pipeline are issued strictly in order, so its stage, unit, header buffer, row group and tile advance
         // incrementally; nothing here divides.
         uint32_t f_tile = (item0 + w) / p.groups, f_grp = (item0 + w) % p.groups, f_u = 0, f_s = 0, f_h = 0, f_issued = 0, f_wrap = 0;
@@ -234,7 +240,7 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
                 if (++f_u == UPI) {
                     f_u = 0;
                     if (++f_h == HB) f_h = 0;
-                    f_grp += kW3;
+                    f_grp += W;
                     while (f_grp >= p.groups) { f_grp -= p.groups; ++f_tile; }
                 }
             }
@@ -243,7 +249,7 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
     }
 
     // ---------------- consumer warps ----------------
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsRegs));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(cons_regs(W)));
     const uint32_t my_units = units_of(warp);
     (void)my_units;
     const uint8_t* my_hdr0 = smem3 + p.off_warp + warp * p.warp_bytes;
@@ -253,7 +259,7 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
 
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t ctid = threadIdx.x;
-    constexpr uint32_t CT = kW3 * 32;   // consumer threads: they alone meet at the tile-change barriers (named barrier 1)
+    constexpr uint32_t CT = W * 32;   // consumer threads: they alone meet at the tile-change barriers (named barrier 1)
     uint8_t* xhi = smem3 + p.off_xhi;
     uint8_t* xlo = smem3 + p.off_xlo;
     uint8_t* sxb = smem3 + p.off_sx;
@@ -439,9 +445,9 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
             }
 
         // ---- this warp's row groups of the segment ----
-        for (; my_it < seg_end; my_it += kW3) {
+        for (; my_it < seg_end; my_it += W) {
             const uint32_t r0 = my_grp * R;
-            my_grp += kW3;
+            my_grp += W;
             while (my_grp >= p.groups) my_grp -= p.groups;
             float total[NT][NC][4];
 #pragma unroll
@@ -593,12 +599,19 @@ __global__ void __launch_bounds__(kThreads3, 1) gemv3_kernel(const __grid_consta
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, int KB, bool SPLIT>
+template <uint32_t LAYOUT, bool GATEUP, int NC, int NT, int KB, bool SPLIT, int W = kW3>
 static int launch3(const Gemv3Maps& maps, const Gemv3Params& p, size_t smem, int grid, cudaStream_t st) {
-    auto kernel = gemv3_kernel<LAYOUT, GATEUP, NC, NT, KB, SPLIT>;
+    auto kernel = gemv3_kernel<LAYOUT, GATEUP, NC, NT, KB, SPLIT, W>;
+    static thread_local int regs_ok = -1;   // the register hand-over between producer and consumer warps adds up for this build
+    if (regs_ok < 0) {
+        cudaFuncAttributes fa{};
+        TSP_CUDA(cudaFuncGetAttributes(&fa, kernel));
+        regs_ok = (fa.numRegs >= kProdRegs && W * (cons_regs(W) - fa.numRegs) <= kProd3 * (fa.numRegs - kProdRegs)) ? 1 : 0;
+    }
+    if (!regs_ok) return fail(TSP_E_CUDA, "decode projection kernel: the compiled register count does not allow the producer/consumer register hand-over");
     static thread_local SmemAttrCache configured;   // per kernel instantiation, keyed by device
     TSP_CUDA(ensure_dynamic_smem(kernel, configured, smem));
-    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads3), smem, st, maps, p));
+    TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3((W + kProd3) * 32), smem, st, maps, p));
     return TSP_OK;
 }
 
@@ -658,45 +671,54 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
     const uint32_t nt = (!gateup && nblk <= 2 && a->rows % 32 == 0) ? 2 : 1;
     const uint32_t R = (gateup ? 8 : 16) * nt;
     const uint32_t nmat = gateup ? 2 : 1;
-    const uint32_t kb = (nblk % 4 == 0 && nblk >= 8) ? 4 : (nblk % 2 == 0 && (nblk >= 4 || nt == 2)) ? 2 : 1;
-    if (R * nblk > 2048) return 1;   // header boxes are limited to 256 lines
-    p.upi = nblk / kb;
-    p.groups = a->rows / R;
-    p.code_mat_bytes = R * kb * (planar ? 128 : 144);
-    p.stage_bytes = (nmat * p.code_mat_bytes + 1023u) & ~1023u;
-    p.sm_mat_bytes = planar ? R * nblk * 16 : 0;
-    p.dm_mat_bytes = planar ? R * nblk * 4 : 0;
-    if (nmat == 2 && p.dm_mat_bytes % 128) return 1;   // the second matrix's pairs must start on a 128-byte boundary
-    p.sm_lines = R * nblk / 8;
-    for (p.dm_inner = 256; p.dm_inner > 16 && (R * nblk * 4) % p.dm_inner; p.dm_inner >>= 1) {}
-    p.hdr_bytes = (nmat * (p.sm_mat_bytes + p.dm_mat_bytes) + 1023u) & ~1023u;
+    // Eight pipelines. Sixteen (104 registers per consumer thread, stages of one super-block) were measured on the short-K
+    // plain projection of the decode layer: 0.077 ms against 0.067 ms with eight, so no launch selects them.
+    uint32_t warps = static_cast<uint32_t>(kW3);
     const uint32_t tok = 8u * static_cast<uint32_t>(nc);
     const bool split_lo = !f16_exact;
-    p.x_stride = a->cols * 2 + 64;
-    p.sx_stride = (a->cols / 32) * 2 + 16;
-    uint32_t off = 6144;   // barriers, tile tables, fallback route ids
-    p.off_xhi = off; off += tok * p.x_stride;
-    p.off_xlo = off; if (split_lo) off += tok * p.x_stride;
-    p.off_sx = off; off += 2 * tok * p.sx_stride;
-    off = (off + 1023u) & ~1023u;
-    p.off_warp = off;
-    const uint32_t budget = 226 * 1024;   // 1 KB of the 227 KB is kept for aligning the dynamic base
-    if (off >= budget) return 1;
-    const uint32_t per_warp = ((budget - off) / kW3) & ~1023u;
-    // pipeline depth and header buffers: a header buffer is reused after n_hdr items, so the producer may run at most
-    // (n_hdr - 1) items + 1 unit ahead of the consumer
-    uint32_t best_s = 0, best_h = 0;
-    for (uint32_t h = planar ? 2 : 0; h <= (planar ? kMaxHeaders3 : 0); ++h) {
-        if (h * p.hdr_bytes + 2 * p.stage_bytes > per_warp) break;
-        uint32_t s = (per_warp - h * p.hdr_bytes) / p.stage_bytes;
-        if (s > kMaxStages3) s = kMaxStages3;
-        if (planar && s > (h - 1) * p.upi + 1) s = (h - 1) * p.upi + 1;
-        if (s > best_s) { best_s = s; best_h = h; }
+    uint32_t kb = 1, off = 0, best_s = 0, best_h = 0;
+    for (;;) {
+        kb = warps == 16 ? 1 : (nblk % 4 == 0 && nblk >= 8) ? 4 : (nblk % 2 == 0 && (nblk >= 4 || nt == 2)) ? 2 : 1;
+        if (R * nblk > 2048) return 1;   // header boxes are limited to 256 lines
+        p.upi = nblk / kb;
+        p.groups = a->rows / R;
+        p.code_mat_bytes = R * kb * (planar ? 128 : 144);
+        p.stage_bytes = (nmat * p.code_mat_bytes + 1023u) & ~1023u;
+        p.sm_mat_bytes = planar ? R * nblk * 16 : 0;
+        p.dm_mat_bytes = planar ? R * nblk * 4 : 0;
+        if (nmat == 2 && p.dm_mat_bytes % 128) return 1;   // the second matrix's pairs must start on a 128-byte boundary
+        p.sm_lines = R * nblk / 8;
+        for (p.dm_inner = 256; p.dm_inner > 16 && (R * nblk * 4) % p.dm_inner; p.dm_inner >>= 1) {}
+        p.hdr_bytes = (nmat * (p.sm_mat_bytes + p.dm_mat_bytes) + 1023u) & ~1023u;
+        p.x_stride = a->cols * 2 + 64;
+        p.sx_stride = (a->cols / 32) * 2 + 16;
+        off = 6144;   // barriers, tile tables, fallback route ids
+        p.off_xhi = off; off += tok * p.x_stride;
+        p.off_xlo = off; if (split_lo) off += tok * p.x_stride;
+        p.off_sx = off; off += 2 * tok * p.sx_stride;
+        off = (off + 1023u) & ~1023u;
+        p.off_warp = off;
+        const uint32_t budget = 226 * 1024;   // 1 KB of the 227 KB is kept for aligning the dynamic base
+        if (off >= budget) return 1;
+        const uint32_t per_warp = ((budget - off) / warps) & ~1023u;
+        const uint32_t max_stages = warps == 16 ? 4u : kMaxStages3;   // the barrier arrays hold 64 entries
+        // pipeline depth and header buffers: a header buffer is reused after n_hdr items, so the producer may run at most
+        // (n_hdr - 1) items + 1 unit ahead of the consumer
+        best_s = 0; best_h = 0;
+        for (uint32_t h = planar ? 2 : 0; h <= (planar ? kMaxHeaders3 : 0); ++h) {
+            if (h * p.hdr_bytes + 2 * p.stage_bytes > per_warp) break;
+            uint32_t s = (per_warp - h * p.hdr_bytes) / p.stage_bytes;
+            if (s > max_stages) s = max_stages;
+            if (planar && s > (h - 1) * p.upi + 1) s = (h - 1) * p.upi + 1;
+            if (s > best_s) { best_s = s; best_h = h; }
+        }
+        if (best_s >= 2 || warps == static_cast<uint32_t>(kW3)) break;
+        warps = kW3;
     }
     if (best_s < 2) return 1;   // too little room for a double-buffered pipeline per warp
     p.n_stages = best_s; p.n_hdr = best_h;
     p.warp_bytes = p.n_hdr * p.hdr_bytes + p.n_stages * p.stage_bytes;
-    const size_t smem = off + static_cast<size_t>(kW3) * p.warp_bytes + 1024;
+    const size_t smem = off + static_cast<size_t>(warps) * p.warp_bytes + 1024;
     p.x = x; p.x_stride_bytes = x_stride_bytes; p.in_div = in_div ? in_div : 1;
     p.token_map = token_map; p.counts = counts; p.tasks = tasks; p.tokens = tokens;
     p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;

@@ -193,6 +193,13 @@ int tsp_moe_combine(const void* d_routed, uint64_t routed_stride_bytes, uint32_t
                     float* d_out, uint64_t out_stride_bytes, void* d_out_f16, uint64_t out_f16_stride_bytes,
                     uint32_t* d_error, void* stream);
 
+/* `q8_lanes_v1` rows (the layout the Pack v3 container keeps dense Q8_0 matrices such as the vocabulary head in,
+ * planar_pack_v3.cpp:467-470; `lanes::pack_rows` / `unpack_rows`, expert_lanes.cpp:92-130) to GGUF Q8_0 rows and back. A
+ * lossless re-layout of whole rows (34 bytes per 32 weights either way), meant to run once when the tensor is uploaded: the
+ * projection kernels read GGUF rows. rows x cols weights, cols a multiple of 32; the two buffers must not overlap. */
+int tsp_q8_lanes_unpack(const void* d_lanes, void* d_gguf, uint64_t rows, uint32_t cols, void* stream);
+int tsp_q8_lanes_pack(const void* d_gguf, void* d_lanes, uint64_t rows, uint32_t cols, void* stream);
+
 /* Self test of the bounded waits (no reference counterpart): one thread waits at most `polls` (1..65536) polls on a barrier
  * that nothing arrives on, then sets TSP_ERR_TIMEOUT in *d_error and the kernel returns normally; the context stays usable.
  * Every pipeline wait of the library gives up the same way (after 2^24 polls). */

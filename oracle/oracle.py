@@ -153,6 +153,15 @@ class Oracle:
             ids[t], w[t] = self.route(logits[t], selected, mode, normalize)
         return ids, w
 
+    def lanes_pack_rows(self, type_: int, columns: int, original: np.ndarray, unpack: bool = False) -> np.ndarray:
+        """Whole rows of GGUF blocks -> lane layout (`q8_lanes_v1` for Q8_0), or back with unpack=True. Lossless."""
+        src = np.ascontiguousarray(original, dtype=np.uint8).reshape(-1)
+        out = np.empty_like(src)
+        fn = self._f("lanes_unpack_rows" if unpack else "lanes_pack_rows")
+        fn.argtypes = [C.c_uint32, C.c_uint32, u8p, u8p, C.c_size_t]
+        self._ok(fn(type_, columns, _ptr(src, u8p), _ptr(out, u8p), src.size))
+        return out
+
     def logit_topk_row(self, logits: np.ndarray):
         """Top-64 row of the sampler (port only: the reference's sampling.cpp needs arm_neon.h and does not build here).
         Returns a dict: vocabulary, count, first_nonfinite_col, first_subnormal_col, ids [64] uint32, logits [64] float32."""

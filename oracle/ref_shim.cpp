@@ -3,6 +3,7 @@
 // validate the plain-C restatement in tsp_oracle.c, to generate the golden fixtures
 // under tests/golden/, and as the timed "reference" CPU arm of the benchmark.
 // Nothing here is reference source: it only calls the reference's public functions.
+#include "tokspur/expert_lanes.hpp"
 #include "tokspur/gguf.hpp"
 #include "tokspur/numeric.hpp"
 #include "tokspur/operators.hpp"
@@ -49,6 +50,13 @@ int ref_gemv_f32(uint32_t type, const uint8_t* matrix, size_t nbytes, uint32_t c
         const auto r = reference_gemv(type, bytes(matrix, nbytes), columns, rows, std::span<const float>(input, columns));
         std::memcpy(output, r.data(), sizeof(double) * rows);
     });
+}
+
+int ref_lanes_pack_rows(uint32_t type, uint32_t columns, const uint8_t* original, uint8_t* packed, size_t nbytes) {
+    return guarded([&] { lanes::pack_rows(lanes::row_layout(type, columns), bytes(original, nbytes), {reinterpret_cast<std::byte*>(packed), nbytes}); });
+}
+int ref_lanes_unpack_rows(uint32_t type, uint32_t columns, const uint8_t* packed, uint8_t* original, size_t nbytes) {
+    return guarded([&] { lanes::unpack_rows(lanes::row_layout(type, columns), bytes(packed, nbytes), {reinterpret_cast<std::byte*>(original), nbytes}); });
 }
 
 double ref_sigmoid(double v) { return stable_sigmoid(v); }

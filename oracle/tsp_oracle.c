@@ -315,6 +315,48 @@ int tso_logit_topk_row(const float* logits, size_t vocabulary, tso_topk_row* out
     return TSO_OK;
 }
 
+/* expert_lanes.cpp:75-130 (Q8_0 and Q4_K rows) */
+static int lanes_geometry(uint32_t type, uint32_t columns, uint32_t* blocks, uint32_t* block_bytes, uint32_t* header, uint32_t* run) {
+    if (type == 8u) { if (!columns || columns % 32 || columns > 65536) return TSO_E_SHAPE; *blocks = columns / 32; *block_bytes = 34; *header = 2; *run = 16; return TSO_OK; }
+    if (type == 12u) { if (!columns || columns % 256 || columns > 65536) return TSO_E_SHAPE; *blocks = columns / 256; *block_bytes = 144; *header = 16; *run = 4; return TSO_OK; }
+    return TSO_E_TYPE;
+}
+static uint64_t lanes_quant_offset(uint32_t type, uint32_t blocks, uint32_t meta, uint32_t block, uint32_t index) {
+    if (type == 12u) {
+        const uint32_t run = block / 4, left = blocks - run * 4, width = (left < 4 ? left : 4) * 4;
+        const uint32_t pair = index / 32, lane = index % 32;
+        return (uint64_t)meta + (uint64_t)run * 512 + lane * width + (block % 4) * 4 + pair;
+    }
+    const uint32_t run = block / 16, left = blocks - run * 16, width = left < 16 ? left : 16;
+    return (uint64_t)meta + (uint64_t)run * 512 + index * width + block % 16;
+}
+static int lanes_move(uint32_t type, uint32_t columns, const uint8_t* in, uint8_t* out, size_t nbytes, int pack) {
+    uint32_t blocks, bb, header, run;
+    const int rc = lanes_geometry(type, columns, &blocks, &bb, &header, &run);
+    if (rc) return rc;
+    (void)run;
+    const size_t row_bytes = (size_t)blocks * bb;
+    const uint32_t meta = blocks * header;
+    if (!nbytes || nbytes % row_bytes) return TSO_E_SHAPE;
+    for (size_t row = 0; row < nbytes; row += row_bytes)
+        for (uint32_t b = 0; b < blocks; ++b) {
+            if (pack) memcpy(out + row + (size_t)b * header, in + row + (size_t)b * bb, header);
+            else memcpy(out + row + (size_t)b * bb, in + row + (size_t)b * header, header);
+            for (uint32_t i = 0; i < bb - header; ++i) {
+                const uint64_t at = lanes_quant_offset(type, blocks, meta, b, i);
+                if (pack) out[row + at] = in[row + (size_t)b * bb + header + i];
+                else out[row + (size_t)b * bb + header + i] = in[row + at];
+            }
+        }
+    return TSO_OK;
+}
+int tso_lanes_pack_rows(uint32_t type, uint32_t columns, const uint8_t* original, uint8_t* packed, size_t nbytes) {
+    return lanes_move(type, columns, original, packed, nbytes, 1);
+}
+int tso_lanes_unpack_rows(uint32_t type, uint32_t columns, const uint8_t* packed, uint8_t* original, size_t nbytes) {
+    return lanes_move(type, columns, packed, original, nbytes, 0);
+}
+
 /* ---- Pack v3 planar layout ---- */
 
 /* planar_pack_v3.cpp:601-650 (Q4_K and Q8_0 rows of the table) */

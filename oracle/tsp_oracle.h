@@ -85,6 +85,14 @@ typedef struct {
 } tso_topk_row;
 int tso_logit_topk_row(const float* logits, size_t vocabulary, tso_topk_row* out);
 
+/* Lane layouts of whole rows (expert_lanes.cpp:75-130), lossless: a row keeps its byte count; the block headers move to a leading
+ * run and the quant bytes are regrouped so that one lane's bytes of consecutive blocks are adjacent. type 8 (Q8_0, layout
+ * `q8_lanes_v1`): 2-byte scales first, then runs of up to 16 blocks, byte i of block b at meta + run*512 + i*width + b%16.
+ * type 12 (Q4_K): 16-byte headers first, runs of up to 4 blocks, quant byte (pair p, lane l) at meta + run*512 + l*width*... as
+ * packed_quant_offset states. nbytes must hold whole rows. */
+int tso_lanes_pack_rows(uint32_t type, uint32_t columns, const uint8_t* original, uint8_t* packed, size_t nbytes);
+int tso_lanes_unpack_rows(uint32_t type, uint32_t columns, const uint8_t* packed, uint8_t* original, size_t nbytes);
+
 /* ---- Pack v3 planar expert layout (planar_pack_v3.cpp:601-896) ---- */
 typedef struct {
     uint32_t source_type, columns, rows, blocks_per_row;

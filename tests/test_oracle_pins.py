@@ -325,3 +325,23 @@ def test_logit_topk_known_answers_of_the_reference_test(oracle):
     assert short["count"] == 2 and list(short["ids"][:3]) == [1, 3, 0] and np.isneginf(short["logits"][2])
     with pytest.raises(Exception):
         oracle.logit_topk_row(np.zeros(0, dtype=np.float32))
+
+
+@pytest.mark.parametrize("type_,columns", [(8, 2048), (8, 2560), (8, 32), (8, 32 * 19), (8, 32 * 33), (12, 2048), (12, 256), (12, 256 * 5), (12, 256 * 7)])
+def test_lane_layout_port_equals_reference(oracle, ref_oracle, type_, columns):
+    """`q8_lanes_v1` (and the Q4_K lane rows) against the reference's own pack_rows / unpack_rows (expert_lanes.cpp:92-130) on
+    random bytes, including rows whose last run is short; lossless both ways."""
+    bpb, epb = (34, 32) if type_ == 8 else (144, 256)
+    rows = 5
+    rng = np.random.default_rng(columns * 31 + type_)
+    original = rng.integers(0, 256, rows * (columns // epb) * bpb, dtype=np.uint8)
+    packed = oracle.lanes_pack_rows(type_, columns, original)
+    assert np.array_equal(packed, ref_oracle.lanes_pack_rows(type_, columns, original))
+    assert np.array_equal(oracle.lanes_pack_rows(type_, columns, packed, unpack=True), original)
+    assert np.array_equal(ref_oracle.lanes_pack_rows(type_, columns, packed, unpack=True), original)
+    if columns // epb > 1:
+        assert not np.array_equal(packed, original)
+    with pytest.raises(Exception):
+        oracle.lanes_pack_rows(type_, columns, original[:-1])
+    with pytest.raises(Exception):
+        oracle.lanes_pack_rows(type_, columns + 1, original)

@@ -94,6 +94,8 @@ SIGNATURES = {
     "tsp_moe_grouped_down": (_i, [_MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
     "tsp_moe_staged_f16": (_i, [_MS, _u32, _vp, _vp]),
     "tsp_moe_layer_decode_static_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
+    "tsp_q8_lanes_unpack": (_i, [_vp, _vp, _u64, _u32, _vp]),
+    "tsp_q8_lanes_pack": (_i, [_vp, _vp, _u64, _u32, _vp]),
     "tsp_selftest_bounded_wait": (_i, [_u32, _vp, _vp]),
     "tsp_logit_topk_scratch_bytes": (_u64, [_u32, _u32]),
     "tsp_logit_topk_output_bytes": (_u64, [_u32]),

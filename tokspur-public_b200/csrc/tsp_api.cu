@@ -51,6 +51,7 @@ int launch_gemv(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*
 
 int launch_route_offsets(const uint32_t*, uint32_t, uint32_t*, cudaStream_t);
 int launch_bounded_wait_selftest(uint32_t, uint32_t*, cudaStream_t);
+int launch_q8_lanes(const void*, void*, uint64_t, uint32_t, bool, cudaStream_t);
 int launch_logit_topk(const float*, uint64_t, uint32_t, uint32_t, uint32_t*, uint32_t*, cudaStream_t);
 int launch_rows_f16k(const void*, uint64_t, uint32_t, uint32_t, uint32_t, void*, uint64_t, uint32_t*, cudaStream_t);
 int launch_grouped(const tsp_matrix_set*, const tsp_matrix_set*, bool, const void*, uint64_t, uint32_t, uint32_t, uint32_t, const uint32_t*,
@@ -455,6 +456,16 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, con
                            out_dtype == 0 ? static_cast<float*>(d_out) : nullptr, out_dtype == 0 ? out_stride : 0,
                            out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);
 }
+
+static int q8_lanes(const void* d_in, void* d_out, uint64_t rows, uint32_t cols, bool unpack, void* stream) {
+    TSP_REQUIRE(d_in && d_out && rows >= 1 && cols >= 32 && cols % 32 == 0 && cols <= 65536, "q8 lanes: null buffer or invalid shape");
+    TSP_REQUIRE(reinterpret_cast<uintptr_t>(d_in) % 2 == 0 && reinterpret_cast<uintptr_t>(d_out) % 2 == 0, "q8 lanes: buffers must be 2-byte aligned");
+    const uint64_t bytes = rows * (cols / 32u) * 34ull;
+    TSP_REQUIRE(!overlap(d_in, bytes, d_out, bytes), "q8 lanes: input and output overlap");
+    return launch_q8_lanes(d_in, d_out, rows, cols, unpack, static_cast<cudaStream_t>(stream));
+}
+int tsp_q8_lanes_unpack(const void* d_lanes, void* d_gguf, uint64_t rows, uint32_t cols, void* stream) { return q8_lanes(d_lanes, d_gguf, rows, cols, true, stream); }
+int tsp_q8_lanes_pack(const void* d_gguf, void* d_lanes, uint64_t rows, uint32_t cols, void* stream) { return q8_lanes(d_gguf, d_lanes, rows, cols, false, stream); }
 
 int tsp_selftest_bounded_wait(uint32_t polls, uint32_t* d_error, void* stream) {
     TSP_REQUIRE(d_error && polls >= 1 && polls <= (1u << 16), "bounded-wait self test: null error word or poll limit outside 1..65536");

@@ -141,4 +141,56 @@ int launch_pack_planar(uint32_t type, const void* gguf, uint64_t gguf_stride, vo
     return TSP_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// `q8_lanes_v1` rows <-> GGUF Q8_0 rows (expert_lanes.cpp:75-130), a lossless re-layout done once when a tensor is loaded: the
+// Pack v3 container stores dense Q8_0 matrices (the vocabulary head among them) in the lane layout, the kernels here read
+// GGUF rows. One block of threads per (row, run of up to 16 quant blocks): the run's 512 code bytes pass through shared memory.
+// ---------------------------------------------------------------------------------------------
+template <bool UNPACK>
+__global__ void __launch_bounds__(128) q8_lanes_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t blocks) {
+    __shared__ uint8_t codes[512];
+    const uint64_t row = blockIdx.y;
+    const uint32_t run = blockIdx.x, tid = threadIdx.x;
+    const uint32_t width = min(16u, blocks - run * 16u);           // blocks in this run
+    const uint64_t row_bytes = static_cast<uint64_t>(blocks) * 34u;
+    const uint8_t* src = in + row * row_bytes;
+    uint8_t* dst = out + row * row_bytes;
+    const uint32_t meta = blocks * 2u;
+    if (UNPACK) {
+        // lanes: scales at 2 b, code i of block b at meta + run*512 + i*width + b%16
+        for (uint32_t k = tid; k < width * 32u; k += 128) codes[k] = src[meta + run * 512u + k];
+        __syncthreads();
+        for (uint32_t k = tid; k < width * 17u; k += 128) {        // 17 half-words per GGUF block
+            const uint32_t b = k / 17u, h = k % 17u, blk = run * 16u + b;
+            uint16_t v;
+            if (h == 0) v = *reinterpret_cast<const uint16_t*>(src + blk * 2u);
+            else v = static_cast<uint16_t>(codes[(2 * h - 2) * width + b]) | (static_cast<uint16_t>(codes[(2 * h - 1) * width + b]) << 8);
+            *reinterpret_cast<uint16_t*>(dst + blk * 34u + h * 2u) = v;
+        }
+    } else {
+        for (uint32_t k = tid; k < width * 17u; k += 128) {
+            const uint32_t b = k / 17u, h = k % 17u, blk = run * 16u + b;
+            const uint16_t v = *reinterpret_cast<const uint16_t*>(src + blk * 34u + h * 2u);
+            if (h == 0) *reinterpret_cast<uint16_t*>(dst + blk * 2u) = v;
+            else { codes[(2 * h - 2) * width + b] = static_cast<uint8_t>(v); codes[(2 * h - 1) * width + b] = static_cast<uint8_t>(v >> 8); }
+        }
+        __syncthreads();
+        for (uint32_t k = tid; k < width * 32u; k += 128) dst[meta + run * 512u + k] = codes[k];
+    }
+}
+
+int launch_q8_lanes(const void* in, void* out, uint64_t rows, uint32_t cols, bool unpack, cudaStream_t st) {
+    const uint32_t blocks = cols / 32u;
+    for (uint64_t r0 = 0; r0 < rows; r0 += 65535) {   // grid.y limit
+        const uint32_t n = static_cast<uint32_t>(rows - r0 < 65535 ? rows - r0 : 65535);
+        const dim3 grid((blocks + 15u) / 16u, n);
+        const uint8_t* src = static_cast<const uint8_t*>(in) + r0 * blocks * 34ull;
+        uint8_t* dst = static_cast<uint8_t*>(out) + r0 * blocks * 34ull;
+        if (unpack) q8_lanes_kernel<true><<<grid, 128, 0, st>>>(src, dst, blocks);
+        else q8_lanes_kernel<false><<<grid, 128, 0, st>>>(src, dst, blocks);
+    }
+    TSP_CUDA(cudaGetLastError());
+    return TSP_OK;
+}
+
 }  // namespace tsp

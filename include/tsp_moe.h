@@ -177,6 +177,21 @@ int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared
                            const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, float* d_out,
                            uint64_t out_stride_bytes, float* d_shared_out, uint64_t shared_out_stride_bytes, uint32_t* d_error, void* stream);
 
+/* The same two launches where the dense shared expert works on OTHER rows than the routed experts (no reference counterpart: the
+ * expert-parallel layer runs the routed experts over the rows it received and the shared expert over the rank's own rows).
+ * d_shared_x / d_shared_in: FP32 rows [shared_tokens x cols] of the shared expert. d_x16 may only be given when both row sets
+ * are the same rows. */
+int tsp_moe_gate_up_swiglu_shared_rows(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                                       const tsp_matrix_set* shared_up, const float* d_x, uint64_t x_stride_bytes, const void* d_x16,
+                                       uint64_t x16_stride_bytes, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                                       const uint32_t* d_counts, const uint32_t* d_tasks, float* d_h, uint64_t h_stride_bytes,
+                                       const float* d_shared_x, uint64_t shared_x_stride_bytes, uint32_t shared_tokens, float* d_shared_h,
+                                       uint64_t shared_h_stride_bytes, int x_is_f16_exact, uint32_t* d_error, void* stream);
+int tsp_moe_project_shared_rows(const tsp_matrix_set* w, const tsp_matrix_set* shared_w, const float* d_in, uint64_t in_stride_bytes,
+                                const float* d_shared_in, uint64_t shared_in_stride_bytes, uint32_t shared_tokens, uint32_t tokens,
+                                uint32_t selected, const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, float* d_out,
+                                uint64_t out_stride_bytes, float* d_shared_out, uint64_t shared_out_stride_bytes, uint32_t* d_error, void* stream);
+
 /* Replaces `gemv(shared_router, rows=1)` + `mixture` / `prefill_mixture_batch` (moe.cpp:79-81,
  * graph.mm:8023,5975; CPU mixture_reference, routing.cpp:42-61):
  *   out[t][c] = sigmoid(s_t) * shared[t][c] + sum_{r<selected} w[t][r] * routed[t*selected+r][c]

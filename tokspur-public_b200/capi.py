@@ -73,6 +73,8 @@ SIGNATURES = {
     "tsp_moe_project": (_i, [_MS, _vp, _u64, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _i, _vp, _vp]),
     "tsp_moe_gate_up_swiglu_shared": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _i, _vp, _vp]),
     "tsp_moe_project_shared": (_i, [_MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
+    "tsp_moe_gate_up_swiglu_shared_rows": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _i, _vp, _vp]),
+    "tsp_moe_project_shared_rows": (_i, [_MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
     "tsp_moe_combine": (_i, [_vp, _u64, _u32, _vp, _vp, _u64, _vp, _vp, _u64, _u32, _vp, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp, _vp]),
     "tsp_synth_weights": (_i, [_u32, _u64, _u64, _u64, C.c_float, _vp, _vp]),
     "tsp_pack_planar": (_i, [_u32, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),

@@ -362,12 +362,15 @@ int tsp_rows_f16_to_f32(const void* d_in, uint64_t in_stride, float* d_out, uint
 
 // Routed experts and the layer's dense shared expert in one launch when the shared expert looks like a routed one (same
 // shape, encoding and layout, Q4_K); otherwise the shared expert gets a launch of its own.
-int tsp_moe_gate_up_swiglu_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
-                                  const tsp_matrix_set* shared_up, const float* d_x, uint64_t x_stride, const void* d_x16,
-                                  uint64_t x16_stride, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
-                                  const uint32_t* d_counts, const uint32_t* d_tasks, float* d_h, uint64_t h_stride, float* d_shared_h,
-                                  uint64_t shared_h_stride, int x_is_f16_exact, uint32_t* d_error, void* stream) {
-    TSP_REQUIRE(gate && up && shared_gate && shared_up && d_token_map && d_counts && d_tasks && d_shared_h, "gate-up with shared expert: null argument");
+int tsp_moe_gate_up_swiglu_shared_rows(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                                       const tsp_matrix_set* shared_up, const float* d_x, uint64_t x_stride, const void* d_x16,
+                                       uint64_t x16_stride, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                                       const uint32_t* d_counts, const uint32_t* d_tasks, float* d_h, uint64_t h_stride,
+                                       const float* d_shared_x, uint64_t shared_x_stride, uint32_t shared_tokens, float* d_shared_h,
+                                       uint64_t shared_h_stride, int x_is_f16_exact, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(gate && up && shared_gate && shared_up && d_token_map && d_counts && d_tasks && d_shared_h && d_shared_x && shared_tokens >= 1,
+                "gate-up with shared expert: null argument");
+    TSP_REQUIRE(!d_x16 || (d_shared_x == d_x && shared_tokens == tokens), "gate-up with shared expert: binary16 rows serve both row sets only when they are the same rows");
     const bool same_shape = shared_gate->type == gate->type && shared_gate->layout == gate->layout && shared_up->type == gate->type &&
                             shared_up->layout == gate->layout && shared_gate->rows == gate->rows && shared_gate->cols == gate->cols &&
                             shared_up->rows == gate->rows && shared_up->cols == gate->cols && shared_gate->experts == 1 && shared_up->experts == 1;
@@ -375,10 +378,13 @@ int tsp_moe_gate_up_swiglu_shared(const tsp_matrix_set* gate, const tsp_matrix_s
         check_matrix(shared_up, "shared up") == TSP_OK && gate->type == up->type && gate->layout == up->layout && up->rows == gate->rows &&
         up->cols == gate->cols && up->experts == gate->experts && gate->expert_stride == up->expert_stride && gate->split == up->split &&
         tokens >= 1 && selected >= 1 && selected <= 64 && check_rows(d_x, x_stride, gate->cols, 4, "gate-up input") == TSP_OK &&
+        check_rows(d_shared_x, shared_x_stride, gate->cols, 4, "shared gate-up input") == TSP_OK &&
         check_rows(d_h, h_stride, gate->rows, 4, "gate-up output") == TSP_OK &&
         check_rows(d_shared_h, shared_h_stride, gate->rows, 4, "shared gate-up output") == TSP_OK && aligned16(d_x) && x_stride % 16 == 0 &&
+        aligned16(d_shared_x) && shared_x_stride % 16 == 0 &&
         (!d_x16 || check_rows(d_x16, x16_stride, gate->cols, 2, "binary16 input") == TSP_OK)) {
-        GemvShared sh{shared_gate, shared_up, d_x, x_stride, d_shared_h, shared_h_stride};
+        GemvShared sh{shared_gate, shared_up, d_shared_x, shared_x_stride, d_shared_h, shared_h_stride};
+        sh.tokens = shared_tokens;
         if (d_x16 && x_is_f16_exact) { sh.x16 = d_x16; sh.x16_stride_bytes = x16_stride; }   // the binary16 rows themselves: staged without conversion
         const int rc = launch_gemv(gate, up, true, d_x, x_stride, selected, tokens, d_token_map, d_counts, d_tasks, d_h, h_stride,
                                    x_is_f16_exact, 1, d_error, static_cast<cudaStream_t>(stream), &sh);
@@ -386,15 +392,24 @@ int tsp_moe_gate_up_swiglu_shared(const tsp_matrix_set* gate, const tsp_matrix_s
     }
     if (int rc = tsp_moe_gate_up_swiglu(gate, up, d_x, x_stride, tokens, selected, d_token_map, d_counts, d_tasks, d_h, h_stride, x_is_f16_exact,
                                         d_error, stream)) return rc;
-    return tsp_moe_gate_up_swiglu(shared_gate, shared_up, d_x, x_stride, tokens, 1, nullptr, nullptr, nullptr, d_shared_h, shared_h_stride,
+    return tsp_moe_gate_up_swiglu(shared_gate, shared_up, d_shared_x, shared_x_stride, shared_tokens, 1, nullptr, nullptr, nullptr, d_shared_h, shared_h_stride,
                                   x_is_f16_exact, d_error, stream);
 }
 
-int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared_w, const float* d_in, uint64_t in_stride,
-                           const float* d_shared_in, uint64_t shared_in_stride, uint32_t tokens, uint32_t selected,
-                           const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, float* d_out, uint64_t out_stride,
-                           float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
-    TSP_REQUIRE(w && shared_w && d_token_map && d_counts && d_tasks && d_shared_in && d_shared_out, "project with shared expert: null argument");
+int tsp_moe_gate_up_swiglu_shared(const tsp_matrix_set* gate, const tsp_matrix_set* up, const tsp_matrix_set* shared_gate,
+                                  const tsp_matrix_set* shared_up, const float* d_x, uint64_t x_stride, const void* d_x16,
+                                  uint64_t x16_stride, uint32_t tokens, uint32_t selected, const uint32_t* d_token_map,
+                                  const uint32_t* d_counts, const uint32_t* d_tasks, float* d_h, uint64_t h_stride, float* d_shared_h,
+                                  uint64_t shared_h_stride, int x_is_f16_exact, uint32_t* d_error, void* stream) {
+    return tsp_moe_gate_up_swiglu_shared_rows(gate, up, shared_gate, shared_up, d_x, x_stride, d_x16, x16_stride, tokens, selected, d_token_map, d_counts,
+                                              d_tasks, d_h, h_stride, d_x, x_stride, tokens, d_shared_h, shared_h_stride, x_is_f16_exact, d_error, stream);
+}
+
+int tsp_moe_project_shared_rows(const tsp_matrix_set* w, const tsp_matrix_set* shared_w, const float* d_in, uint64_t in_stride,
+                                const float* d_shared_in, uint64_t shared_in_stride, uint32_t shared_tokens, uint32_t tokens, uint32_t selected,
+                                const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, float* d_out, uint64_t out_stride,
+                                float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
+    TSP_REQUIRE(w && shared_w && d_token_map && d_counts && d_tasks && d_shared_in && d_shared_out && shared_tokens >= 1, "project with shared expert: null argument");
     const bool same_shape = shared_w->type == w->type && shared_w->layout == w->layout && shared_w->rows == w->rows && shared_w->cols == w->cols &&
                             shared_w->experts == 1;
     if (same_shape && w->rows % 16 == 0 && check_matrix(w, "project") == TSP_OK && check_matrix(shared_w, "shared project") == TSP_OK &&
@@ -402,14 +417,23 @@ int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared
         check_rows(d_shared_in, shared_in_stride, w->cols, 4, "shared project input") == TSP_OK &&
         check_rows(d_out, out_stride, w->rows, 4, "project output") == TSP_OK &&
         check_rows(d_shared_out, shared_out_stride, w->rows, 4, "shared project output") == TSP_OK) {
-        const GemvShared sh{shared_w, nullptr, d_shared_in, shared_in_stride, d_shared_out, shared_out_stride};
+        GemvShared sh{shared_w, nullptr, d_shared_in, shared_in_stride, d_shared_out, shared_out_stride};
+        sh.tokens = shared_tokens;
         const int rc = launch_gemv(w, nullptr, false, d_in, in_stride, 1, tokens, d_token_map, d_counts, d_tasks, d_out, out_stride, 0, 1, d_error,
                                    static_cast<cudaStream_t>(stream), &sh);
         if (rc <= 0) return rc;
     }
     if (int rc = tsp_moe_project(w, d_in, in_stride, 1, tokens, selected, d_token_map, d_counts, d_tasks, d_out, out_stride, 0, d_error, stream)) return rc;
-    return tsp_moe_project(shared_w, d_shared_in, shared_in_stride, 1, tokens, 1, nullptr, nullptr, nullptr, d_shared_out, shared_out_stride, 0,
+    return tsp_moe_project(shared_w, d_shared_in, shared_in_stride, 1, shared_tokens, 1, nullptr, nullptr, nullptr, d_shared_out, shared_out_stride, 0,
                            d_error, stream);
+}
+
+int tsp_moe_project_shared(const tsp_matrix_set* w, const tsp_matrix_set* shared_w, const float* d_in, uint64_t in_stride,
+                           const float* d_shared_in, uint64_t shared_in_stride, uint32_t tokens, uint32_t selected,
+                           const uint32_t* d_token_map, const uint32_t* d_counts, const uint32_t* d_tasks, float* d_out, uint64_t out_stride,
+                           float* d_shared_out, uint64_t shared_out_stride, uint32_t* d_error, void* stream) {
+    return tsp_moe_project_shared_rows(w, shared_w, d_in, in_stride, d_shared_in, shared_in_stride, tokens, tokens, selected, d_token_map, d_counts, d_tasks,
+                                       d_out, out_stride, d_shared_out, shared_out_stride, d_error, stream);
 }
 
 int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s, const void* d_x, uint64_t x_stride,

@@ -39,6 +39,7 @@ struct GemvShared {
     float* out; uint64_t out_stride_bytes;
     // optional: the token rows as binary16 (exactly the values of `x`); both the routed and the dense tiles then read these
     const void* x16 = nullptr; uint64_t x16_stride_bytes = 0;
+    uint32_t tokens = 0;   // rows of the dense expert (0: as many as the routed launch has token rows)
 };
 
 // the layer's dense shared expert riding in a routed launch: one-expert matrix sets of the routed experts' shape, binary16

@@ -74,7 +74,7 @@ struct Gemv3Params {
     // same shape/encoding/layout as the routed experts, every token row as input, its own output rows
     const float* sh_x; uint64_t sh_x_stride_bytes;
     float* sh_out; uint64_t sh_out_stride_bytes;
-    uint32_t sh_tiles;
+    uint32_t sh_tiles, sh_tokens;
 };
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
@@ -103,7 +103,7 @@ __device__ __forceinline__ Tile3 tile3(const Gemv3Params& p, uint32_t tile, uint
     if (tile >= routed_tiles && p.sh_tiles) {
         t.expert = p.experts;
         t.start = (tile - routed_tiles) * 8u * NC;
-        t.count = min(p.tokens - t.start, 8u * NC);
+        t.count = min(p.sh_tokens - t.start, 8u * NC);
         return t;
     }
     if (p.token_map) {
@@ -754,7 +754,8 @@ int launch_gemv_q4k_tma(const tsp_matrix_set* a, const tsp_matrix_set* b, bool g
         for (int pl = 0; pl < 3; ++pl) { maps.m[pl * 6 + 2] = maps.m[pl * 6]; maps.m[pl * 6 + 3] = maps.m[pl * 6 + 1]; }
     for (int pl = 0; pl < 3; ++pl) { maps.m[pl * 6 + 4] = maps.m[pl * 6]; maps.m[pl * 6 + 5] = maps.m[pl * 6]; }
     if (shared) {
-        p.sh_tiles = (tokens + 7) / 8;
+        p.sh_tokens = shared->tokens ? shared->tokens : tokens;
+        p.sh_tiles = (p.sh_tokens + 7) / 8;
         p.sh_x = shared->x; p.sh_x_stride_bytes = shared->x_stride_bytes;
         p.sh_out = shared->out; p.sh_out_stride_bytes = shared->out_stride_bytes;
         if (shared->x16 && f16_exact && reinterpret_cast<uintptr_t>(shared->x16) % 16 == 0 && shared->x16_stride_bytes % 16 == 0) {

@@ -340,14 +340,14 @@ int tsp_ep_moe_layer(tsp_ep_ctx* ctx, const tsp_ep_layer* L, void* d_scratch, ui
         // per received row: the weighted sum of its local routes, as binary16 (zero weights mark routes served elsewhere)
         EP_TSP(tsp_moe_combine(p.routed16, rb, 1, p.w_all, nullptr, 0, nullptr, nullptr, 0, 0, nullptr, R, C, K, nullptr, 0, p.partial16, rb, d_error, st));
     } else {
+        // the routed experts work on the received rows, the shared expert on this rank's own rows: both in the same two launches
         EP_TSP(tsp_rows_f16_to_f32(p.recv, rb, p.x32_all, C * 4ull, R, C, st));
-        EP_TSP(tsp_moe_gate_up_swiglu(&w.gate, &w.up, p.x32_all, C * 4ull, R, K, p.token_map, p.counts, p.tasks, p.hidden, H * 4ull, 1, d_error, st));
-        EP_TSP(tsp_moe_project(&w.down, p.hidden, H * 4ull, 1, R, K, p.token_map, p.counts, p.tasks, p.routed, C * 4ull, 0, d_error, st));
-        EP_TSP(tsp_moe_combine(p.routed, C * 4ull, 0, p.w_all, nullptr, 0, nullptr, nullptr, 0, 0, nullptr, R, C, K, p.partial, C * 4ull, nullptr, 0, d_error, st));
-        // the shared expert of this rank's own rows
         EP_TSP(tsp_rows_f16_to_f32(d_x16, x_stride, p.x32_local, C * 4ull, T, C, st));
-        EP_TSP(tsp_moe_gate_up_swiglu(&w.shared_gate, &w.shared_up, p.x32_local, C * 4ull, T, 1, nullptr, nullptr, nullptr, p.shared_hidden, H * 4ull, 1, d_error, st));
-        EP_TSP(tsp_moe_project(&w.shared_down, p.shared_hidden, H * 4ull, 1, T, 1, nullptr, nullptr, nullptr, p.shared_out, C * 4ull, 0, d_error, st));
+        EP_TSP(tsp_moe_gate_up_swiglu_shared_rows(&w.gate, &w.up, &w.shared_gate, &w.shared_up, p.x32_all, C * 4ull, nullptr, 0, R, K, p.token_map, p.counts,
+                                                  p.tasks, p.hidden, H * 4ull, p.x32_local, C * 4ull, T, p.shared_hidden, H * 4ull, 1, d_error, st));
+        EP_TSP(tsp_moe_project_shared_rows(&w.down, &w.shared_down, p.hidden, H * 4ull, p.shared_hidden, H * 4ull, T, R, K, p.token_map, p.counts, p.tasks,
+                                           p.routed, C * 4ull, p.shared_out, C * 4ull, d_error, st));
+        EP_TSP(tsp_moe_combine(p.routed, C * 4ull, 0, p.w_all, nullptr, 0, nullptr, nullptr, 0, 0, nullptr, R, C, K, p.partial, C * 4ull, nullptr, 0, d_error, st));
     }
 
     // ---- combine: the partial sums of slab q's rows go back to rank q

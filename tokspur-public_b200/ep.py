@@ -270,7 +270,9 @@ def run_bench(args, rank: int, world: int, local: int) -> None:
                              "achieved": step_bytes / (dec["ms"] * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                              "frac": step_bytes / (dec["ms"] * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind, "traffic": None,
                              "algorithmic_bytes_per_step": step_bytes, "experts_hit_on_busiest_gpu": u_max},
-                "cpu_baseline": None, "extra": {}}
+                "cpu_baseline": {"value": None, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                                 "sample": "not timed at N > 1: the CPU arm is measured by the one-GPU run (rank 0, N = 1) and by --impl reference"},
+                "extra": {}}
         if pre is not None:
             Tp = pre["tokens_per_rank"]
             flops = world * Tp * (SELECTED + 1) * FLOPS_PER_ROUTE

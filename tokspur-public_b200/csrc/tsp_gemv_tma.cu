@@ -153,8 +153,21 @@ __global__ void __launch_bounds__((W + kProd3) * 32, 1) gemv3_kernel(const __gri
     const uint32_t routed_tiles = p.token_map ? p.tasks[0] : (p.tokens + 8u * NC - 1) / (8u * NC);
     const uint32_t n_tiles = routed_tiles + p.sh_tiles;
     const uint64_t n_items = static_cast<uint64_t>(n_tiles) * p.groups;   // item = (tile, row group)
-    const uint32_t item0 = static_cast<uint32_t>(n_items * blockIdx.x / gridDim.x);
-    const uint32_t item1 = static_cast<uint32_t>(n_items * (blockIdx.x + 1) / gridDim.x);
+    // Static split by cost, not by item count: besides its items a token tile costs the staging of its activation rows, about
+    // 0.8 items per row of 2048 columns. Routed tiles carry routes / tiles rows on average, the dense expert's tiles eight: with
+    // an even split the CTAs that get the dense expert's tiles (the last ones) finished 9-14 us after the rest of a 100 us launch.
+    // Cost per item in 1/256 item units: 256 + rows of the tile * row cost / groups, piecewise constant over the two kinds of tile.
+    const uint64_t row_cost = 200ull * p.cols / 2048u;
+    const uint64_t routes = p.token_map ? p.tasks[1] : p.tokens;
+    const uint64_t ci_r = 256ull + (routed_tiles ? routes * row_cost / (static_cast<uint64_t>(routed_tiles) * p.groups) : 0ull);
+    const uint64_t ci_s = 256ull + static_cast<uint64_t>(p.sh_tiles ? (p.sh_tokens + p.sh_tiles - 1) / p.sh_tiles : 0u) * row_cost / p.groups;
+    const uint64_t n_r = static_cast<uint64_t>(routed_tiles) * p.groups, cost_r = n_r * ci_r, cost_all = cost_r + (n_items - n_r) * ci_s;
+    auto boundary = [&](uint32_t b) -> uint32_t {
+        if (b >= gridDim.x) return static_cast<uint32_t>(n_items);
+        const uint64_t c = cost_all * b / gridDim.x;
+        return static_cast<uint32_t>(c < cost_r ? c / ci_r : n_r + (c - cost_r) / ci_s);
+    };
+    const uint32_t item0 = boundary(blockIdx.x), item1 = boundary(blockIdx.x + 1);
     // Tile table: the (expert, first route, route count), route ids and input rows of the first kTableTiles token tiles this
     // CTA touches, fetched once and in parallel, so that the dependent global loads behind them are not paid at every tile.
     const uint32_t t0 = item0 / p.groups;

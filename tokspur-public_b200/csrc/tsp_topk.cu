@@ -32,8 +32,8 @@ struct TopkShared {
 // A lower bound T such that exactly `need` of the block's keys (all distinct, 0 = no key, `bits` wide) are >= T, found digit by
 // digit (8 bits) from the top with a shared-memory histogram; the walk stops as soon as the digit's bucket is needed whole,
 // which for spread-out values is after two or three digits. Measured alternatives on 4096-column tiles: one warp-aggregated
-// atomic per distinct digit (`match.any`) and a bit-by-bit walk without atomics were both slower (40 / 39 us against 28 us for
-// 16 rows of 151 936 logits). each(f) calls f(key) for every key of the calling thread. All threads return the same value.
+// atomic per distinct digit (`match.any`), a bit-by-bit walk without atomics and a start below the keys' common prefix (an extra
+// max / min reduction) were all slower (40 / 39 / 32 us against 28 us for 16 rows of 151 936 logits). each(f) calls f(key) for every key of the calling thread. All threads return the same value.
 // sh.hist must be zero on entry and is zero again on return.
 template <class Each>
 __device__ unsigned long long topk_select(TopkShared& sh, Each each, uint32_t need, int bits) {
@@ -74,6 +74,19 @@ __device__ unsigned long long topk_select(TopkShared& sh, Each each, uint32_t ne
     return prefix << (bits - done);
 }
 
+// Appends the keys at or above the bound to sh.sel: one shared-memory atomic per warp and call instead of one per key (the
+// per-key form serialised 64 atomics on one counter: 2.2 k cycles). Must be called by whole warps.
+__device__ __forceinline__ void topk_take(TopkShared& sh, unsigned long long key, unsigned long long threshold) {
+    const bool take = key >= threshold && key != 0;
+    const uint32_t votes = __ballot_sync(0xffffffffu, take);
+    if (!votes) return;
+    const uint32_t lane = threadIdx.x & 31, leader = __ffs(votes) - 1;
+    uint32_t at = 0;
+    if (lane == leader) at = atomicAdd(&sh.taken, static_cast<uint32_t>(__popc(votes)));
+    at = __shfl_sync(0xffffffffu, at, leader);
+    if (take) sh.sel[at + __popc(votes & ((1u << lane) - 1u))] = key;
+}
+
 // Ranks the sh.taken (<= 64) selected keys by counting and returns this thread's key for output slot tid (0 if none).
 __device__ unsigned long long topk_ranked(TopkShared& sh, unsigned long long* ranked) {
     const uint32_t tid = threadIdx.x;
@@ -104,12 +117,18 @@ logit_topk_tiles_kernel(const float* __restrict__ logits, uint64_t stride, uint3
     // 16 columns per thread, key = value image above 12 bits of inverted position inside the tile (44 bits)
     unsigned long long k[16];
     uint32_t valid = 0, nonfinite = 0xffffffffu, subnormal = 0xffffffffu;
+    float vals[16];
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {   // all loads first: sixteen dependent round trips otherwise (measured 6.8 k cycles of a 19 k block)
+        const uint32_t col = base + i * kTopkThreads + tid;
+        vals[i] = src[min(col, vocabulary - 1)];
+    }
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i) {
         const uint32_t local = i * kTopkThreads + tid, col = base + local;
         k[i] = 0;
         if (col < vocabulary) {
-            const float v = src[col];
+            const float v = vals[i];
             const uint32_t b = __float_as_uint(v);
             if ((b & 0x7f800000u) == 0x7f800000u) { nonfinite = min(nonfinite, col); continue; }
             if ((b & 0x7f800000u) == 0 && (b & 0x007fffffu)) subnormal = min(subnormal, col);
@@ -128,7 +147,7 @@ logit_topk_tiles_kernel(const float* __restrict__ logits, uint64_t stride, uint3
     };
     if (count) {
         const unsigned long long threshold = topk_select(sh, each, count, 44);
-        each([&](unsigned long long key) { if (key >= threshold && key != 0) sh.sel[atomicAdd(&sh.taken, 1u)] = key; });
+        each([&](unsigned long long key) { topk_take(sh, key, threshold); });
         __syncthreads();
     }
     const unsigned long long mine = topk_ranked(sh, ranked);
@@ -170,8 +189,9 @@ logit_topk_merge_kernel(const uint32_t* __restrict__ partial, uint32_t vocabular
     auto key_at = [&](uint32_t i) -> unsigned long long {
         const uint32_t t = i / kTopkCap, s = i % kTopkCap;
         const uint32_t* h = src + static_cast<uint64_t>(t) * kTopkRowWords;
-        if (s >= min(h[1], kTopkCap)) return 0ull;
-        return (static_cast<unsigned long long>(topk_mono(__uint_as_float(h[4 + kTopkCap + s]))) << 32) | (0xffffffffu - h[4 + s]);
+        const uint32_t live = h[1], id = h[4 + s], bits = h[4 + kTopkCap + s];   // three independent loads (every slot of a row exists)
+        if (s >= min(live, kTopkCap)) return 0ull;
+        return (static_cast<unsigned long long>(topk_mono(__uint_as_float(bits))) << 32) | (0xffffffffu - id);
     };
     if (REGS) {   // up to 64 tiles: the candidates are read once, 16 per thread, and the digit walk runs out of registers
         unsigned long long k[16];
@@ -183,14 +203,14 @@ logit_topk_merge_kernel(const uint32_t* __restrict__ partial, uint32_t vocabular
         };
         if (count) {
             const unsigned long long threshold = topk_select(sh, each, count, 64);
-            each([&](unsigned long long key) { if (key >= threshold && key != 0) sh.sel[atomicAdd(&sh.taken, 1u)] = key; });
+            each([&](unsigned long long key) { topk_take(sh, key, threshold); });
             __syncthreads();
         }
     } else {
         auto each = [&](auto f) { for (uint32_t i = tid; i < cands; i += kTopkThreads) f(key_at(i)); };
         if (count) {
             const unsigned long long threshold = topk_select(sh, each, count, 64);
-            each([&](unsigned long long key) { if (key >= threshold && key != 0) sh.sel[atomicAdd(&sh.taken, 1u)] = key; });
+            each([&](unsigned long long key) { topk_take(sh, key, threshold); });
             __syncthreads();
         }
     }

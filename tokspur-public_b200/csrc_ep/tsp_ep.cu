@@ -124,14 +124,18 @@ ep_unpack_kernel(const uint8_t* __restrict__ slabs, uint64_t slab_bytes, uint32_
 }
 
 // out[t][c] = sigmoid(w_sr . x[t]) * shared[t][c] + sum over ranks g (ascending) of the partial sum g returned for token t
+// `own`: this rank's own partial rows (they never travel); the other ranks' rows are read from `ret`. Eight channels per thread
+// step (16-byte loads of every rank's row), ranks added in ascending order.
 template <bool P16>
 __global__ void __launch_bounds__(256)
-ep_finish_kernel(const uint8_t* __restrict__ ret, uint64_t ret_peer_bytes, const int32_t* __restrict__ pos, uint32_t world, uint32_t tokens,
-                 uint32_t channels, const float* __restrict__ shared, const float* __restrict__ shared_router, const __half* __restrict__ x16,
-                 uint64_t x_stride, __half* __restrict__ out16, uint64_t out_stride, uint32_t* error) {
+ep_finish_kernel(const uint8_t* __restrict__ ret, uint64_t ret_peer_bytes, const uint8_t* __restrict__ own, uint32_t rank, const int32_t* __restrict__ pos,
+                 uint32_t world, uint32_t tokens, uint32_t channels, const float* __restrict__ shared, const float* __restrict__ shared_router,
+                 const __half* __restrict__ x16, uint64_t x_stride, __half* __restrict__ out16, uint64_t out_stride, uint32_t* error) {
     __shared__ float partial[8];
     __shared__ float gate_s;
+    __shared__ int32_t pos_s[64];
     const uint32_t t = blockIdx.x, tid = threadIdx.x;
+    if (tid < world) pos_s[tid] = pos[uint64_t(tid) * tokens + t];
     float gate = 1.f;
     if (shared_router) {
         const __half* xr = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(x16) + t * x_stride);
@@ -148,18 +152,35 @@ ep_finish_kernel(const uint8_t* __restrict__ ret, uint64_t ret_peer_bytes, const
         }
         __syncthreads();
         gate = gate_s;
+    } else {
+        __syncthreads();
     }
     bool bad = false;
-    for (uint32_t c = tid; c < channels; c += 256) {
-        float v = gate * shared[uint64_t(t) * channels + c];
+    for (uint32_t c = tid * 8; c < channels; c += 256 * 8) {   // channels % 8 == 0 (checked by the entry point)
+        const float4 s0 = *reinterpret_cast<const float4*>(shared + uint64_t(t) * channels + c), s1 = *reinterpret_cast<const float4*>(shared + uint64_t(t) * channels + c + 4);
+        float v[8] = {gate * s0.x, gate * s0.y, gate * s0.z, gate * s0.w, gate * s1.x, gate * s1.y, gate * s1.z, gate * s1.w};
         for (uint32_t g = 0; g < world; ++g) {
-            const int32_t j = pos[uint64_t(g) * tokens + t];
+            const int32_t j = pos_s[g];
             if (j < 0) continue;
-            const uint8_t* row = ret + g * ret_peer_bytes + uint64_t(j) * channels * (P16 ? 2 : 4);
-            v += P16 ? __half2float(reinterpret_cast<const __half*>(row)[c]) : reinterpret_cast<const float*>(row)[c];
+            const uint8_t* row = (g == rank ? own : ret + g * ret_peer_bytes) + uint64_t(j) * channels * (P16 ? 2 : 4);
+            if (P16) {
+                const uint4 h = *reinterpret_cast<const uint4*>(row + c * 2ull);
+                const uint32_t w4[4] = {h.x, h.y, h.z, h.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[q])); v[2 * q] += f.x; v[2 * q + 1] += f.y; }
+            } else {
+                const float4 a = *reinterpret_cast<const float4*>(row + c * 4ull), b4 = *reinterpret_cast<const float4*>(row + c * 4ull + 16);
+                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b4.x; v[5] += b4.y; v[6] += b4.z; v[7] += b4.w;
+            }
         }
-        bad |= (__float_as_uint(v) & 0x7f800000u) == 0x7f800000u;
-        reinterpret_cast<__half*>(reinterpret_cast<char*>(out16) + t * out_stride)[c] = __float2half_rn(v);
+        uint32_t h[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            bad |= (__float_as_uint(v[2 * q]) & 0x7f800000u) == 0x7f800000u || (__float_as_uint(v[2 * q + 1]) & 0x7f800000u) == 0x7f800000u;
+            const __half2 t2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+            h[q] = *reinterpret_cast<const uint32_t*>(&t2);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out16) + t * out_stride + c * 2ull) = make_uint4(h[0], h[1], h[2], h[3]);
     }
     if (bad && error) atomicOr(error, TSP_ERR_NONFINITE);
 }
@@ -309,6 +330,7 @@ int tsp_ep_moe_layer(tsp_ep_ctx* ctx, const tsp_ep_layer* L, void* d_scratch, ui
                      uint32_t selected, uint32_t mode, int normalize, int prefill, void* d_out16, uint64_t out_stride, uint32_t* d_error, void* stream) {
     EP_REQUIRE(ctx && L && d_scratch && d_x16 && d_logits && d_out16 && L->d_place, "layer: null argument");
     EP_REQUIRE(tokens >= 1 && channels % 8 == 0 && L->local_experts >= 1, "layer: invalid shape");
+    EP_REQUIRE((reinterpret_cast<uintptr_t>(d_out16) | out_stride) % 16 == 0, "layer: output rows must be 16-byte aligned");
     EP_REQUIRE(reinterpret_cast<uintptr_t>(d_scratch) % 1024 == 0, "layer: the scratch buffer must be 1024-byte aligned");
     const uint32_t N = uint32_t(ctx->world), rank = uint32_t(ctx->rank), T = tokens, C = channels, H = hidden, K = selected, El = L->local_experts;
     const bool pf = prefill != 0;
@@ -361,13 +383,11 @@ int tsp_ep_moe_layer(tsp_ep_ctx* ctx, const tsp_ep_layer* L, void* d_scratch, ui
         EP_NCCL(ncclRecv(p.ret + q * peer_bytes, peer_bytes, ncclUint8, int(q), ctx->comm, st));
     }
     EP_NCCL(ncclGroupEnd());
-    EP_CUDA(cudaMemcpyAsync(p.ret + rank * peer_bytes, partial + (uint64_t(rank) * p.sg.rows + p.sg.header_rows) * C * es, peer_bytes,
-                            cudaMemcpyDeviceToDevice, st));
-
-    // ---- source side: gated shared expert + partial sums in ascending rank order
-    if (pf) ep_finish_kernel<true><<<T, 256, 0, st>>>(p.ret, peer_bytes, p.pos, N, T, C, p.shared_out, w.d_shared_router, static_cast<const __half*>(d_x16),
+    // ---- source side: gated shared expert + partial sums in ascending rank order (this rank's own rows straight from `partial`)
+    const uint8_t* own = partial + (uint64_t(rank) * p.sg.rows + p.sg.header_rows) * C * es;
+    if (pf) ep_finish_kernel<true><<<T, 256, 0, st>>>(p.ret, peer_bytes, own, rank, p.pos, N, T, C, p.shared_out, w.d_shared_router, static_cast<const __half*>(d_x16),
                                                       x_stride, static_cast<__half*>(d_out16), out_stride, d_error);
-    else ep_finish_kernel<false><<<T, 256, 0, st>>>(p.ret, peer_bytes, p.pos, N, T, C, p.shared_out, w.d_shared_router, static_cast<const __half*>(d_x16),
+    else ep_finish_kernel<false><<<T, 256, 0, st>>>(p.ret, peer_bytes, own, rank, p.pos, N, T, C, p.shared_out, w.d_shared_router, static_cast<const __half*>(d_x16),
                                                     x_stride, static_cast<__half*>(d_out16), out_stride, d_error);
     EP_CUDA(cudaGetLastError());
     return TSP_OK;

@@ -293,16 +293,16 @@ grouped_tasks_kernel(const uint32_t* __restrict__ counts, uint32_t tokens, uint3
 }
 
 // ---------------------------------------------------------------------------------------------
-// Decode-size prologue of a batch of <= 64 token rows in TWO launches: (1) routing, one warp per token over as many blocks
+// Decode-size prologue of a batch of <= 1024 token rows in TWO launches: (1) routing, one warp per token over as many blocks
 // as that takes, with the binary16 -> FP32 copy of the input rows done by the remaining blocks of the same launch (one block
 // routing 64 rows alone is bound by its own issue rate: measured 25.7 us); (2) permutation + tile table in one block. The
-// tables are the ones the separate kernels above produce, bit for bit: the per-expert token order comes from a 64-bit mask
-// of the tokens that name the expert (bit t set = token t routes here), so position = number of lower set bits: no atomics
+// tables are the ones the separate kernels above produce, bit for bit: the per-expert token order comes from a bit mask of
+// the tokens that name the expert (bit t set = token t routes here), so position = number of lower set bits: no atomics
 // decide an order.
 // ---------------------------------------------------------------------------------------------
 constexpr int kPrologueThreads = 1024;
 constexpr int kPrologueRouteWarps = 4;
-constexpr uint32_t kPrologueTokens = 64, kPrologueExperts = 1024;
+constexpr uint32_t kPrologueTokens = 1024, kPrologueExperts = 1024;
 
 __global__ void __launch_bounds__(kPrologueRouteWarps * 32)
 decode_route_kernel(const float* __restrict__ logits, uint64_t logits_stride, uint32_t tokens, uint32_t experts, uint32_t selected,
@@ -331,37 +331,44 @@ decode_route_kernel(const float* __restrict__ logits, uint64_t logits_stride, ui
     else route_row(pro_smem + warp * experts, row, t, experts, selected, mode, normalize, ids, weights, error, lane);
 }
 
+// Permutation + tile table of up to 1024 token rows in ONE block: a mask of the rows that name each expert (`words` 32-bit words per
+// expert in shared memory), positions = number of lower set bits. ids are global; this launch owns experts [first, first + experts);
+// with local_only, routes to other owners are skipped, without it they are an index error.
 __global__ void __launch_bounds__(kPrologueThreads)
-decode_tables_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile,
-                     uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* __restrict__ tasks, uint32_t* error) {
+tables_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile, uint32_t first, int local_only,
+              uint32_t words, uint32_t* __restrict__ token_map, uint32_t* __restrict__ counts, uint32_t* __restrict__ tasks, uint32_t* error) {
     pdl_launch_dependents();
-    __shared__ unsigned long long mask[kPrologueExperts];
+    extern __shared__ uint32_t tables_mask[];   // [experts][words]
     __shared__ uint32_t warp_tiles[32], warp_routes[32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-    for (uint32_t e = tid; e < experts; e += blockDim.x) mask[e] = 0ull;
+    for (uint32_t i = tid; i < experts * words; i += blockDim.x) tables_mask[i] = 0u;
     const uint32_t routes = tokens * selected;
     const uint32_t bound = routes / tile + experts;
     pdl_wait();   // the ids come from the previous launch; everything above touched shared memory only
     __syncthreads();
-    uint32_t my_e[2] = {0xffffffffu, 0xffffffffu};   // routes <= 64 * 64 = 4096: at most four per thread, two in registers
-    for (uint32_t i = tid, n = 0; i < routes; i += blockDim.x, ++n) {
-        const uint32_t t = i / selected, e = ids[i];
-        if (n < 2) my_e[n] = e;
-        if (e >= experts) { raise_error(error, TSP_ERR_INDEX); continue; }
-        const unsigned long long bit = 1ull << t;
-        if (atomicOr(&mask[e], bit) & bit) raise_error(error, TSP_ERR_INDEX);   // an expert named twice by one token
+    for (uint32_t i = tid; i < routes; i += blockDim.x) {
+        const uint32_t t = i / selected, e = ids[i] - first;
+        if (e >= experts) { if (!local_only) raise_error(error, TSP_ERR_INDEX); continue; }
+        const uint32_t bit = 1u << (t & 31u);
+        if (atomicOr(&tables_mask[e * words + (t >> 5)], bit) & bit) raise_error(error, TSP_ERR_INDEX);   // an expert named twice by one token
     }
     for (uint32_t i = tid; i < bound; i += blockDim.x) { tasks[2 + 2 * i] = 0xffffffffu; tasks[3 + 2 * i] = 0xffffffffu; }
     __syncthreads();
-    for (uint32_t i = tid, n = 0; i < routes; i += blockDim.x, ++n) {
-        const uint32_t t = i / selected, e = n < 2 ? my_e[n] : ids[i];
+    for (uint32_t i = tid; i < routes; i += blockDim.x) {
+        const uint32_t t = i / selected, e = ids[i] - first;
         if (e >= experts) continue;
-        const uint32_t j = __popcll(mask[e] & ((1ull << t) - 1ull));
+        const uint32_t* m = tables_mask + e * words;
+        uint32_t j = __popc(m[t >> 5] & ((1u << (t & 31u)) - 1u));
+        for (uint32_t w = 0; w < (t >> 5); ++w) j += __popc(m[w]);
         token_map[static_cast<uint64_t>(e) * tokens + j] = i;
     }
     // tile table: exclusive scan of tiles per expert over the block (experts <= blockDim.x)
     uint32_t c = 0, n = 0;
-    if (tid < experts) { c = __popcll(mask[tid]); n = (c + tile - 1) / tile; counts[tid] = c; }
+    if (tid < experts) {
+        for (uint32_t w = 0; w < words; ++w) c += __popc(tables_mask[tid * words + w]);
+        n = (c + tile - 1) / tile;
+        counts[tid] = c;
+    }
     uint32_t incl_n = n, incl_c = c;
     for (int o = 1; o < 32; o <<= 1) {
         const uint32_t tn = __shfl_up_sync(0xffffffffu, incl_n, o), tc = __shfl_up_sync(0xffffffffu, incl_c, o);
@@ -374,22 +381,37 @@ decode_tables_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t
     if (tid == 0) {
         tasks[0] = min(total_n, bound);
         tasks[1] = total_c;
-        if (total_n > bound || total_c != routes) raise_error(error, TSP_ERR_INDEX);
+        if (total_n > bound || (!local_only && total_c != routes) || total_c > routes) raise_error(error, TSP_ERR_INDEX);
     }
     if (tid < experts) {
-        const uint32_t first = before + incl_n - n;
+        const uint32_t at0 = before + incl_n - n;
         for (uint32_t i = 0; i < n; ++i) {
-            const uint32_t at = first + i;
+            const uint32_t at = at0 + i;
             if (at < bound) { tasks[2 + 2 * at] = tid; tasks[3 + 2 * at] = i * tile; }
         }
     }
+}
+
+// The one-block form covers up to 1024 rows and experts whose masks fit 96 KB of shared memory.
+static bool tables_fit(uint32_t tokens, uint32_t experts) {
+    return tokens >= 1 && tokens <= 1024 && experts <= static_cast<uint32_t>(kPrologueThreads) && static_cast<uint64_t>(experts) * ((tokens + 31) / 32) * 4 <= 96 * 1024;
+}
+static int launch_tables(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile, uint32_t first, int local_only,
+                         uint32_t* token_map, uint32_t* counts, uint32_t* tasks, uint32_t* error, cudaStream_t st) {
+    const uint32_t words = (tokens + 31) / 32;
+    const size_t smem = static_cast<size_t>(experts) * words * 4;
+    static thread_local SmemAttrCache configured;
+    TSP_CUDA(ensure_dynamic_smem(tables_kernel, configured, smem));
+    TSP_CUDA(launch_pdl(tables_kernel, dim3(1), dim3(kPrologueThreads), smem, st, ids, tokens, experts, selected, tile, first, local_only, words, token_map, counts,
+                        tasks, error));
+    return TSP_OK;
 }
 
 // Returns 1 when the batch does not fit the short prologue (the caller then issues the separate launches).
 int launch_decode_prologue(const float* logits, uint64_t logits_stride, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t mode,
                            int normalize, uint32_t tile, uint32_t* ids, float* weights, uint32_t* token_map, uint32_t* counts, uint32_t* tasks,
                            const void* x16, uint64_t x16_stride, float* x32, uint64_t x32_stride, uint32_t channels, uint32_t* error, cudaStream_t st) {
-    if (tokens > kPrologueTokens || experts > kPrologueExperts || experts > static_cast<uint32_t>(kPrologueThreads)) return 1;
+    if (tokens > kPrologueTokens || experts > kPrologueExperts || !tables_fit(tokens, experts)) return 1;
     if (x16 && (channels % 4 || x16_stride % 8 || x32_stride % 16 || reinterpret_cast<uintptr_t>(x16) % 8 || reinterpret_cast<uintptr_t>(x32) % 16)) return 1;
     const size_t smem = (experts <= 512 && normalize) ? 0 : static_cast<size_t>(kPrologueRouteWarps) * experts * sizeof(float);
     static thread_local SmemAttrCache configured;
@@ -399,8 +421,7 @@ int launch_decode_prologue(const float* logits, uint64_t logits_stride, uint32_t
     const uint32_t conv = x16 ? min(128u, (tokens * (channels / 4) + 2 * kPrologueRouteWarps * 32 - 1) / (2 * kPrologueRouteWarps * 32)) : 0u;
     TSP_CUDA(launch_pdl(decode_route_kernel, dim3(route_blocks + conv), dim3(kPrologueRouteWarps * 32), smem, st, logits, logits_stride, tokens, experts,
                         selected, mode, normalize, route_blocks, ids, weights, static_cast<const __half*>(x16), x16_stride, x32, x32_stride, channels, error));
-    TSP_CUDA(launch_pdl(decode_tables_kernel, dim3(1), dim3(kPrologueThreads), 0, st, static_cast<const uint32_t*>(ids), tokens, experts, selected, tile,
-                        token_map, counts, tasks, error));
+    if (int rc = launch_tables(ids, tokens, experts, selected, tile, 0, 0, token_map, counts, tasks, error, st)) return rc;
     TSP_CUDA(cudaGetLastError());
     return TSP_OK;
 }
@@ -829,6 +850,7 @@ int launch_route(const float* logits, uint64_t stride, uint32_t tokens, uint32_t
 
 int launch_permute(const uint32_t* ids, uint32_t tokens, uint32_t experts, uint32_t selected, uint32_t tile, uint32_t first, int local_only,
                    uint32_t* token_map, uint32_t* counts, uint32_t* tasks, uint32_t* error, cudaStream_t st) {
+    if (tables_fit(tokens, experts)) return launch_tables(ids, tokens, experts, selected, tile, first, local_only, token_map, counts, tasks, error, st);
     TSP_CUDA(launch_pdl(grouped_routes_kernel, dim3((experts + kPermuteExperts - 1) / kPermuteExperts), dim3(kPermuteThreads), 0, st, ids, tokens, experts, selected, first, local_only, token_map, counts, error));
     TSP_CUDA(cudaGetLastError());
     const uint32_t bound = static_cast<uint32_t>((static_cast<uint64_t>(tokens) * selected) / tile + experts);

@@ -590,10 +590,12 @@ def run_ours(args):
             line.update({"e2e": None, "gpu_launches": 5 * args.steps, "roofline": None, "cpu_baseline": None, "extra": {"config1": rec}})
         elif args.workload == "prefill":
             Tp = args.tokens if args.tokens != 64 else args.prefill_tokens
-            layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, formats.Q4_K, formats.PLANAR, dev, keep_gguf=(i == 0)) for i in range(min(args.layers, 2))]
+            p_layout = formats.GGUF if args.layout == "gguf" else formats.PLANAR
+            layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, formats.Q4_K, p_layout, dev, keep_gguf=(i == 0)) for i in range(min(args.layers, 2))]
             rec, cpu = prefill_record(args, dev, layers, Tp)
             _, tf_peak, peak_kind = peaks()
-            line = base_line(args, rec["tokens_per_s"], rec["ms_per_step"], f"moe_layer_prefill_T{Tp} (BASELINE configs[2])", "Q4_K Pack-v3 planar",
+            line = base_line(args, rec["tokens_per_s"], rec["ms_per_step"], f"moe_layer_prefill_T{Tp} (BASELINE configs[2])",
+                             "Q4_K GGUF" if p_layout == formats.GGUF else "Q4_K Pack-v3 planar",
                              "f16 operands, f32 accumulate", {"router": rec["router"], "l2_policy": "inputs larger than L2: 0.93 GB of weights and 0.4 GB of intermediates per step"})
             line.update({"e2e": {"value": rec["e2e_tokens_per_s"], "unit": "tokens/s", "ms_per_step": rec["e2e_ms_per_step"],
                                  "h2d_bytes_per_step": rec["h2d_bytes_per_step"], "d2h_bytes_per_step": rec["d2h_bytes_per_step"]},

@@ -312,7 +312,9 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
 /* ---- prefill-size path: grouped per-expert GEMMs on the tcgen05 tensor cores --------------------------
  * Replaces `planar_nax_grouped_moe` (graph.mm:9293-9420) = `graph_grouped_routes` -> `nax_grouped_tasks_indirect` ->
  * `nax_moe_gather_bf16_v3` -> `nax_grouped_moe_gate_up_swiglu_v3` -> `nax_grouped_moe_down_v3`
- * (planar_moe_v3.metal:2406-2621). Weights: Q4_K Pack v3 planar; hidden a multiple of 64, channels of 256.
+ * (planar_moe_v3.metal:2406-2621). Weights: Q4_K, Pack v3 planar (one copy per plane) or plain GGUF super-blocks (the tensor
+ * maps then walk the 144-byte blocks: codes from byte 16, the 16-byte header beside them; same staged operands, so the same
+ * result bits); gate, up and their shared expert in one layout; hidden a multiple of 64, channels of 256.
  *   1. tsp_moe_rows_f16k                                       binary16 copy of the input rows in the K order the tensor-core tiles use
  *   2. tsp_moe_permute(..., tile = TSP_GROUPED_TILE)           token_map / counts / tasks (tasks of 256 routes = two sub-tiles of 128)
  *   3. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e; experts+3 words: the last
@@ -356,8 +358,8 @@ int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, vo
 /* One whole MoE FFN sub-layer at prefill size: K-ordered rows -> route -> permute (tasks of TSP_GROUPED_TILE) -> offsets ->
  * routed copy of the rows -> grouped gate-up + SwiGLU -> grouped down (the dense shared expert rides in both launches) -> gated mixture.
  * Replaces `encode_moe_mm_many` after its router projection (moe_mm_many.cpp:126-220) on the `planar_nax_grouped_moe`
- * path (graph.mm:9293-9420). Weights: Q4_K Pack v3 planar, hidden a multiple of 64 and channels of 256; the shared expert
- * in the same form. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
+ * path (graph.mm:9293-9420). Weights: Q4_K, Pack v3 planar or plain GGUF super-blocks, hidden a multiple of 64 and channels
+ * of 256; the shared expert in the same form as the routed experts of its projection. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
  * Caller-owned scratch, all device memory, nothing has to start at zero:
  *   base: as for the decode layer, except d_tasks sized tsp_moe_tasks_words(capacity, experts, selected, TSP_GROUPED_TILE);
  *         d_routed is used as binary16 rows [capacity*selected x channels]; d_hidden, d_shared_hidden and d_x32 are not

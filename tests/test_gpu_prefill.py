@@ -42,6 +42,43 @@ def test_prefill_layer_against_oracle(oracle, T, E, K, skew):
     assert rel_l2(out.cpu().numpy()[sample], want) <= 2e-3
 
 
+@pytest.mark.parametrize("T,E,K,Cn,H,order", [(40, 4, 2, 256, 256, "separate"), (700, 8, 2, 512, 256, "gate_first"), (300, 3, 2, 256, 512, "up_first")])
+def test_prefill_layer_gguf_blocks_against_oracle(oracle, T, E, K, Cn, H, order):
+    """The same layer with the expert and shared tensors left as plain GGUF super-blocks (no planar copy): the code and header
+    maps walk the 144-byte blocks. `order` puts gate and up in one allocation (one copy brings both when up follows gate at a
+    constant distance) or the other way round (two copies), or leaves them as separate allocations."""
+    host = L.synth_host_layer(11, Cn, H, E, K, expert_type=formats.Q4_K)
+    dl = L.DeviceLayer(host, formats.GGUF, "cuda")
+    if order != "separate":
+        pair = np.concatenate([host.gate.reshape(-1), host.up.reshape(-1)] if order == "gate_first" else [host.up.reshape(-1), host.gate.reshape(-1)])
+        both = torch.from_numpy(pair).cuda()
+        dl.tensors.append(both)
+        n = host.gate.size
+        g_off, u_off = (0, n) if order == "gate_first" else (n, 0)
+        dl.weights.gate = L.matrix_set(both, formats.Q4_K, formats.GGUF, H, Cn, E, offset=g_off)
+        dl.weights.up = L.matrix_set(both, formats.Q4_K, formats.GGUF, H, Cn, E, offset=u_off)
+    ps = L.PrefillScratch(Cn, H, E, K, T, "cuda")
+    x16 = synth.activations_f16(12, T, Cn)
+    logits = synth.router_logits(13, T, E, synth.zipf_bias(14, E) * 2)
+    x32 = torch.from_numpy(x16.astype(np.float32)).cuda()
+    out = torch.zeros((T, Cn), dtype=torch.float32, device="cuda")
+    L.moe_layer_prefill(dl, ps, x32, torch.from_numpy(logits).cuda(), out)
+    torch.cuda.synchronize()
+    assert ps.base.error_word() == 0
+    sample = np.unique(np.linspace(0, T - 1, 24).astype(int))
+    want, st = oracle.moe_layer(host.oracle_dict(), x16[sample].astype(np.float32), logits[sample], threads=4, stages=True)
+    routed = ps.routed_rows(T).reshape(T, K, Cn)
+    assert rel_l2(routed[sample], st["routed"]) <= 2e-3
+    assert rel_l2(ps.shared_out_rows(T)[sample], st["shared_out"]) <= 2e-3
+    assert rel_l2(out.cpu().numpy()[sample], want) <= 2e-3
+    # the planar copy of the same weights gives the same bits: both layouts stage identical binary16 operands
+    dp = L.DeviceLayer(host, formats.PLANAR, "cuda")
+    out_p = torch.zeros_like(out)
+    L.moe_layer_prefill(dp, ps, x32, torch.from_numpy(logits).cuda(), out_p)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out_p)
+
+
 def test_staged_weight_values_against_rounded_reference(oracle):
     """The binary16 weight values the tensor-core kernels multiply, against RN16 of the reference's dequantised value.
     The kernels stage RN16((q - 8) * RN16(d*sc) + RN16(8*d*sc - dmin*mn)): three roundings of small quantities instead of one

@@ -247,7 +247,10 @@ struct SchedReader {
 
 // GATEUP: two weight matrices (gate, up) interleaved 16 + 16 rows per lane quarter and the SwiGLU epilogue writing binary16
 // hidden rows in permuted position order; otherwise one matrix and route rows scattered to their route ids.
-template <bool GATEUP>
+// GGUF: the weights are plain 144-byte super-blocks (16-byte header: d, dmin, twelve bytes of packed 6-bit factors; then the 128
+// code bytes). The code map then steps 144 bytes per super-block from the first block's byte 16, the factor map brings the whole
+// header, the (d, dmin) ring is left idle and the dequant warps unpack the factors (numeric.cpp:17-31 states the packing).
+template <bool GATEUP, bool GGUF>
 __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
     pdl_launch_dependents();
     extern __shared__ uint8_t gsm_raw[];
@@ -312,14 +315,16 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                 const uint32_t mi = shared ? 4u : (hi ? 1u : 0u);                 // map of matrix A; matrix B's is `ms` further
                 const uint32_t ms = shared ? 1u : 2u;
                 const uint32_t ncopy = (NMAT == 1 || (shared ? p.sh_merged : p.merged)) ? 1u : NMAT;
-                // the (d, dmin) pairs of the item's rows over the whole K: RM * nblk * 4 bytes per matrix = lines of 256 bytes
-                ok = gwait(&dempty[ds], dph ^ 1u);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&dfull[ds], NMAT * p.dm_mat_bytes);
-                for (uint32_t m = 0; m < ncopy; ++m)
-                    tma_load_4d_g(gsm + p.off_d + ds * p.d_stage_bytes + m * p.dm_mat_bytes, &maps.d[mi + ms * m], 0,
-                                  static_cast<int>(rb * (p.dm_mat_bytes / 256u)), 0, el, &dfull[ds]);
-                if (++ds == 2) { ds = 0; dph ^= 1u; }
+                if (!GGUF) {
+                    // the (d, dmin) pairs of the item's rows over the whole K: RM * nblk * 4 bytes per matrix = lines of 256 bytes
+                    ok = gwait(&dempty[ds], dph ^ 1u);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&dfull[ds], NMAT * p.dm_mat_bytes);
+                    for (uint32_t m = 0; m < ncopy; ++m)
+                        tma_load_4d_g(gsm + p.off_d + ds * p.d_stage_bytes + m * p.dm_mat_bytes, &maps.d[mi + ms * m], 0,
+                                      static_cast<int>(rb * (p.dm_mat_bytes / 256u)), 0, el, &dfull[ds]);
+                    if (++ds == 2) { ds = 0; dph ^= 1u; }
+                }
                 for (uint32_t sb = 0; sb < p.nblk && ok; ++sb) {
                     // quant stage: code lines [matrix][RM][128 B], then factor bytes [matrix][RM][16 B]
                     ok = gwait(&qempty[qs], qph ^ 1u);
@@ -328,7 +333,8 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                     mbar_arrive_expect_tx(&qfull[qs], kRowsM * 128u + kRowsM * 16u);
                     for (uint32_t m = 0; m < ncopy; ++m) {
                         tma_load_5d_g(q + m * (RM * 128u), &maps.q[mi + ms * m], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
-                        tma_load_4d_g(q + kRowsM * 128u + m * (RM * 16u), &maps.f[mi + ms * m], static_cast<int>(sb * 16), r0, 0, el, &qfull[qs]);
+                        if (GGUF) tma_load_5d_g(q + kRowsM * 128u + m * (RM * 16u), &maps.f[mi + ms * m], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
+                        else tma_load_4d_g(q + kRowsM * 128u + m * (RM * 16u), &maps.f[mi + ms * m], static_cast<int>(sb * 16), r0, 0, el, &qfull[qs]);
                     }
                     if (++qs == 2) { qs = 0; qph ^= 1u; }
                 }
@@ -424,14 +430,25 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         for (;;) {
             const SchedItem it = sched.next(lane);
             if (it.item >= n_items) { ok = it.item != 0xffffffffu; break; }
-            if (ok) ok = gwait(&dfull[ds], dph);
+            if (!GGUF && ok) ok = gwait(&dfull[ds], dph);
             const uint8_t* dmp = gsm + p.off_d + ds * p.d_stage_bytes + mat * p.dm_mat_bytes + mrow * p.nblk * 4u;
             for (uint32_t sb = 0; sb < p.nblk; ++sb) {
                 if (ok) ok = gwait(&qfull[qs], qph);
                 const uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
                 // d, dmin and the sixteen 6-bit factors of this row's super-block
-                const uint4 fac = *reinterpret_cast<const uint4*>(q + kRowsM * 128u + line * 16u);
-                const uint32_t dmw = *reinterpret_cast<const uint32_t*>(dmp + sb * 4u);
+                uint4 fac = *reinterpret_cast<const uint4*>(q + kRowsM * 128u + line * 16u);
+                uint32_t dmw;
+                if (GGUF) {
+                    // header word 0 = (d, dmin); bytes 4..15 hold the low 6 bits of factors 0..3 with the top 2 bits of factors
+                    // 4..7 above them (scales, then minima), then the low 4 bits of scales / minima 4..7 as nibble pairs
+                    dmw = fac.x;
+                    const uint32_t s_lo = fac.y & 0x3f3f3f3fu, m_lo = fac.z & 0x3f3f3f3fu;
+                    const uint32_t s_hi = (fac.w & 0x0f0f0f0fu) | ((fac.y >> 2) & 0x30303030u);
+                    const uint32_t m_hi = ((fac.w >> 4) & 0x0f0f0f0fu) | ((fac.z >> 2) & 0x30303030u);
+                    fac = make_uint4(s_lo, s_hi, m_lo, m_hi);
+                } else {
+                    dmw = *reinterpret_cast<const uint32_t*>(dmp + sb * 4u);
+                }
                 const float dd = half_bits_to_float(dmw & 0xffffu), dmn = half_bits_to_float(dmw >> 16);
                 if (ok && (!finite_f32(dd) || !finite_f32(dmn))) raise_error(p.error, TSP_ERR_NONFINITE);
                 const uint8_t* codes = q + line * 128u;
@@ -464,9 +481,11 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                 if (lane == 0 && ok) mbar_arrive(&qempty[qs]);
                 if (++qs == 2) { qs = 0; qph ^= 1u; }
             }
-            __syncwarp();
-            if (lane == 0 && ok) mbar_arrive(&dempty[ds]);
-            if (++ds == 2) { ds = 0; dph ^= 1u; }
+            if (!GGUF) {
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&dempty[ds]);
+                if (++ds == 2) { ds = 0; dph ^= 1u; }
+            }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
         }
@@ -740,16 +759,16 @@ int launch_rows_f16k(const void* x, uint64_t x_stride, uint32_t x_dtype, uint32_
 // ---------------------------------------------------------------------------------------------
 // host launcher of the grouped tensor-core GEMMs
 // ---------------------------------------------------------------------------------------------
-template <bool GATEUP>
+template <bool GATEUP, bool GGUF>
 static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t smem, int grid, cudaStream_t st) {
-    auto kernel = grouped_mma_kernel<GATEUP>;
+    auto kernel = grouped_mma_kernel<GATEUP, GGUF>;
     static thread_local SmemAttrCache configured;   // per kernel instantiation, keyed by device
     TSP_CUDA(ensure_dynamic_smem(kernel, configured, smem));
     TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGWarps * 32), smem, st, m, p));
     return TSP_OK;
 }
 
-// a/b: Q4_K Pack v3 planar matrix sets [rows x cols].
+// a/b: Q4_K matrix sets [rows x cols], Pack v3 planar or plain GGUF super-blocks (both sets in the same layout).
 // gate-up: act = the routed copy of the K-ordered input rows in permuted position order (act_rows of them);
 //          out = binary16 hidden rows [positions x rows] in permuted position order; shared expert: sh->act = the K-ordered
 //          input rows by token, sh->out hidden rows by token.
@@ -759,7 +778,8 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
                    uint32_t tokens, uint32_t selected, const uint32_t* token_map, const uint32_t* tasks, const uint32_t* counts,
                    const uint32_t* offsets, uint32_t* work_counter, void* out, uint64_t out_stride, uint32_t out_f16, uint32_t* error, cudaStream_t st,
                    const GroupedShared* sh) {
-    if (a->type != TSP_TYPE_Q4_K || a->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "grouped GEMM: only Q4_K Pack v3 planar weights have a tensor-core kernel");
+    if (a->type != TSP_TYPE_Q4_K) return fail(TSP_E_TYPE, "grouped GEMM: only Q4_K weights have a tensor-core kernel");
+    const bool gguf = a->layout == TSP_LAYOUT_GGUF;
     const uint32_t rm = gateup ? 64u : 128u;
     TSP_REQUIRE(a->rows % rm == 0 && a->cols % 256 == 0, "grouped GEMM: rows must be a multiple of %u and columns of 256", rm);
     GroupedParams p{};
@@ -800,6 +820,18 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     p.merged = gateup && mergeable(base[0], base[2], &delta) && mergeable(base[1], base[3], &delta_hi) && delta == delta_hi;
     GroupedMaps maps;
     auto plane_maps = [&](const uint8_t* bp, uint32_t mats, uint64_t ds, uint32_t n, uint64_t stride, uint32_t at) -> int {
+        if (gguf) {
+            // codes: bytes 16..143 of every 144-byte super-block, [128 B][row][super-block][matrix][expert], 128-byte swizzle;
+            // headers: bytes 0..15 of the same blocks, same walk
+            const uint64_t dims[5] = {128, a->rows, nblk, mats, n}, strides[4] = {uint64_t(nblk) * 144, 144, ds, stride};
+            const uint32_t box[5] = {128, rm, 1, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp + 16, 5, dims, strides, box, true, &maps.q[at])) return rc;
+            const uint64_t hdims[5] = {16, a->rows, nblk, mats, n};
+            const uint32_t hbox[5] = {16, rm, 1, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp, 5, hdims, strides, hbox, false, &maps.f[at])) return rc;
+            maps.d[at] = maps.f[at];   // not read
+            return TSP_OK;
+        }
         {   // codes: [128 B of a super-block][row][super-block][matrix][expert], 128-byte swizzle
             const uint64_t dims[5] = {128, a->rows, nblk, mats, n}, strides[4] = {uint64_t(nblk) * 128, 128, ds, stride};
             const uint32_t box[5] = {128, rm, 1, mats, 1};
@@ -821,7 +853,7 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     const uint64_t ds = p.merged ? delta : 16;
     const uint64_t stride = a->experts > 1 ? a->expert_stride : 16;
     TSP_REQUIRE(stride % 16 == 0, "grouped GEMM: expert stride must be a multiple of 16");
-    TSP_REQUIRE(total_units * 4 % 256 == 0, "grouped GEMM: the (d, dmin) plane must be a whole number of 256-byte lines");
+    TSP_REQUIRE(gguf || total_units * 4 % 256 == 0, "grouped GEMM: the (d, dmin) plane must be a whole number of 256-byte lines");
     const uint32_t n_lo = p.split, n_hi = a->experts - p.split;
     for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t m = i >> 1;
@@ -857,7 +889,8 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     }
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
-    return gateup ? launch_grouped_t<true>(maps, p, smem, grid, st) : launch_grouped_t<false>(maps, p, smem, grid, st);
+    if (gguf) return gateup ? launch_grouped_t<true, true>(maps, p, smem, grid, st) : launch_grouped_t<false, true>(maps, p, smem, grid, st);
+    return gateup ? launch_grouped_t<true, false>(maps, p, smem, grid, st) : launch_grouped_t<false, false>(maps, p, smem, grid, st);
 }
 
 }  // namespace tsp

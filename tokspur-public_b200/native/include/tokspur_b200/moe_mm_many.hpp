@@ -11,8 +11,10 @@ namespace tokspur_b200 {
 
 
 // Registered identity of each weight tensor on the prefill path (native/include/tokspur/moe_mm_many.hpp:7-10). The grouped tensor-core
-// GEMMs read the Pack v3 planar form only, so every member must say `planar` and match a registered planar matrix; raw GGUF bytes
-// are refused, never repacked behind the caller's back.
+// GEMMs read Q4_K in both forms: Pack v3 planar (a registered planar matrix; the default here, the faster walk) and raw GGUF
+// super-blocks (the reference's default). The declared identity must be the tensor's real one (a registered planar matrix declared
+// `gguf`, or the reverse, is refused), the tensors of one projection (gate, up and the shared gate / up; down and the shared
+// down) share one identity, and nothing is repacked behind the caller's back.
 enum class PrefillWeightLayout : uint32_t { gguf = 0, planar = 1 };
 struct MoeMmLayouts {
     PrefillWeightLayout gate = PrefillWeightLayout::planar, up = PrefillWeightLayout::planar, down = PrefillWeightLayout::planar;
@@ -39,8 +41,9 @@ MoeMmManyBytes moe_mm_many_bytes(MoeShape shape, uint32_t capacity);
 MoeMmManyScratch allocate_moe_mm_many_scratch(CudaGraph& graph, MoeShape shape, uint32_t capacity);
 void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scratch);
 
-// Encode only. The caller owns allocation, the batch and the committed state. Weights must be the registered planar tensors
-// (is_planar_moe) with a Q4_K planar shared expert; anything else is refused before the first launch.
+// Encode only. The caller owns allocation, the batch and the committed state. Weights must be Q4_K in the declared layouts
+// (planar: is_planar_moe plus planar shared matrices; gguf: raw blocks of the layer's extent); anything else is refused before
+// the first launch.
 void encode_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, const MoeMmManyScratch& scratch, GpuRowsF32 input, GpuRowsF32 output,
                         MoeShape shape, RouterMode mode, bool normalize_selected, MoeMmLayouts layouts = {});
 // The weight checks of the encoder, run between batches (prepare_moe_mm_many, moe_mm_many.hpp:59): a tensor of the wrong form or
@@ -48,6 +51,7 @@ void encode_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, const MoeMm
 void prepare_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, MoeShape shape, MoeMmLayouts layouts = {});
 // Launches one encode_moe_mm_many of `rows` rows issues with a scratch of `capacity` rows (moe_mm_many_dispatches, moe_mm_many.hpp:60;
 // the reference's chunk is fixed, here it is the scratch capacity).
-uint64_t moe_mm_many_dispatches(const CudaGraph& graph, const MoeWeights& weights, MoeShape shape, uint32_t rows, uint32_t capacity);
+uint64_t moe_mm_many_dispatches(const CudaGraph& graph, const MoeWeights& weights, MoeShape shape, uint32_t rows, uint32_t capacity,
+                                MoeMmLayouts layouts = {});
 
 }  // namespace tokspur_b200

@@ -46,32 +46,44 @@ void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scrat
 namespace {
 constexpr uint64_t kLaunchesPerChunk = 10;   // router GEMM, K-ordered rows, route, routes, tasks, offsets, routed copy, gate-up, down, mixture
 tsp_moe_weights checked_weights(const CudaGraph& g, const MoeWeights& w, MoeShape shape, MoeMmLayouts l) {
-    for (const auto layout : {l.gate, l.up, l.down, l.shared_gate, l.shared_up, l.shared_down})
-        need(layout == PrefillWeightLayout::planar, "tiled MoE reads registered planar tensors only");
+    // one identity per projection: the gate-up launch reads gate, up and the shared gate / up in one layout, the down launch
+    // down and the shared down in one layout
+    need(l.gate == l.up && l.gate == l.shared_gate && l.gate == l.shared_up && l.down == l.shared_down,
+         "tiled MoE: the routed and shared tensors of one projection must be registered in the same layout");
     need(w.router.encoding == 0 && w.shared_router.encoding == 0, "router projections must be F32");
-    need(is_planar_moe(g, w, shape), "tiled MoE needs the registered planar expert tensors");
     need(w.router.view.bytes == uint64_t(shape.channels) * shape.experts * 4 && w.shared_router.view.bytes == uint64_t(shape.channels) * 4,
          "router shape mismatch");
-    const uint32_t type = w.gate.encoding;
-    const uint64_t pb = tsp_expert_bytes(type, TSP_LAYOUT_PLANAR, shape.hidden, shape.channels);
-    const uint64_t pd = tsp_expert_bytes(w.down.encoding, TSP_LAYOUT_PLANAR, shape.channels, shape.hidden);
-    need(pb && pd && shape.experts % 2 == 0, "tiled MoE weight extent");
-    auto dense = [&](GpuMatrix m, uint32_t rows, uint32_t cols) {
-        const auto shp = g.planar_matrix_shape(m.view);
-        need(shp.has_value() && m.view.bytes == tsp_expert_bytes(m.encoding, TSP_LAYOUT_PLANAR, rows, cols), "tiled MoE shared expert must be a registered planar matrix");
-        return tsp_matrix_set{g.device_pointer(m.view), nullptr, m.view.bytes, 1, 1, rows, cols, m.encoding, TSP_LAYOUT_PLANAR};
+    need(w.gate.encoding == TSP_TYPE_Q4_K && w.up.encoding == TSP_TYPE_Q4_K && w.down.encoding == TSP_TYPE_Q4_K &&
+         w.shared_gate.encoding == TSP_TYPE_Q4_K && w.shared_up.encoding == TSP_TYPE_Q4_K && w.shared_down.encoding == TSP_TYPE_Q4_K,
+         "tiled MoE reads Q4_K tensors only");
+    // a tensor declared `gguf` must be raw blocks of the layer's extent and must not be a registered planar matrix, one declared
+    // `planar` must be registered with the matching shape: the declared identity is checked, never guessed
+    auto set = [&](GpuMatrix m, PrefillWeightLayout layout, uint32_t rows, uint32_t cols, uint32_t experts) {
+        const bool planar = layout == PrefillWeightLayout::planar;
+        need(g.planar_matrix_shape(m.view).has_value() == planar, "tiled MoE explicit registered layout mismatch");
+        const uint32_t tl = planar ? TSP_LAYOUT_PLANAR : TSP_LAYOUT_GGUF;
+        const uint64_t eb = tsp_expert_bytes(m.encoding, tl, rows, cols);
+        need(eb && m.view.bytes == eb * experts, "tiled MoE weight extent");
+        return tsp_matrix_set{g.device_pointer(m.view), nullptr, eb, experts, experts, rows, cols, m.encoding, tl};
     };
     tsp_moe_weights tw{};
-    const auto lo = static_cast<const char*>(g.device_pointer(w.gate.view)), hi = static_cast<const char*>(g.device_pointer(w.up.view));
-    tw.gate = {lo, hi, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, type, TSP_LAYOUT_PLANAR};
-    tw.up = {lo + pb, hi + pb, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, type, TSP_LAYOUT_PLANAR};
-    tw.down = {g.device_pointer(w.down.view), nullptr, pd, shape.experts, shape.experts, shape.channels, shape.hidden, w.down.encoding, TSP_LAYOUT_PLANAR};
-    need(w.down.view.bytes == pd * shape.experts, "tiled MoE down extent");
-    tw.shared_gate = dense(w.shared_gate, shape.hidden, shape.channels);
-    tw.shared_up = dense(w.shared_up, shape.hidden, shape.channels);
-    tw.shared_down = dense(w.shared_down, shape.channels, shape.hidden);
+    if (l.gate == PrefillWeightLayout::planar) {
+        // co-located pairs: the "gate" tensor holds experts [0, E/2) as [gate_e, up_e], the "up" tensor experts [E/2, E)
+        need(is_planar_moe(g, w, shape), "tiled MoE needs the registered planar expert tensors");
+        const uint64_t pb = tsp_expert_bytes(TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR, shape.hidden, shape.channels);
+        need(pb && shape.experts % 2 == 0, "tiled MoE weight extent");
+        const auto lo = static_cast<const char*>(g.device_pointer(w.gate.view)), hi = static_cast<const char*>(g.device_pointer(w.up.view));
+        tw.gate = {lo, hi, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR};
+        tw.up = {lo + pb, hi + pb, 2 * pb, shape.experts / 2, shape.experts, shape.hidden, shape.channels, TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR};
+    } else {
+        tw.gate = set(w.gate, l.gate, shape.hidden, shape.channels, shape.experts);
+        tw.up = set(w.up, l.up, shape.hidden, shape.channels, shape.experts);
+    }
+    tw.down = set(w.down, l.down, shape.channels, shape.hidden, shape.experts);
+    tw.shared_gate = set(w.shared_gate, l.shared_gate, shape.hidden, shape.channels, 1);
+    tw.shared_up = set(w.shared_up, l.shared_up, shape.hidden, shape.channels, 1);
+    tw.shared_down = set(w.shared_down, l.shared_down, shape.channels, shape.hidden, 1);
     tw.d_shared_router = static_cast<const float*>(g.device_pointer(w.shared_router.view));
-
     return tw;
 }
 }  // namespace
@@ -81,10 +93,10 @@ void prepare_moe_mm_many(CudaGraph& g, const MoeWeights& w, MoeShape shape, MoeM
     (void)checked_weights(g, w, shape, layouts);
 }
 
-uint64_t moe_mm_many_dispatches(const CudaGraph& g, const MoeWeights& w, MoeShape shape, uint32_t rows, uint32_t capacity) {
+uint64_t moe_mm_many_dispatches(const CudaGraph& g, const MoeWeights& w, MoeShape shape, uint32_t rows, uint32_t capacity, MoeMmLayouts layouts) {
     (void)moe_mm_many_bytes(shape, capacity);
     need(rows > 0, "tiled MoE active rows");
-    (void)checked_weights(g, w, shape, {});
+    (void)checked_weights(g, w, shape, layouts);
     return kLaunchesPerChunk * ((uint64_t(rows) + capacity - 1) / capacity);
 }
 

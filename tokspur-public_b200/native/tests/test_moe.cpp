@@ -267,6 +267,27 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
         std::cout << "  encode_moe_mm_many rows " << rows << " capacity " << capacity << ": relative L2 error " << rel << "\n";
         require(rel <= 2e-3, "tiled MoE relative L2 tolerance exceeded");
     }
+    {   // the same tensors as raw GGUF super-blocks (the reference's default identity): same staged operands, so the same bits
+        const auto planar_rows = g.read(output);
+        MoeWeights r = w;
+        r.gate = {g.upload(bytes(gate), "gate gguf"), type}; r.up = {g.upload(bytes(up), "up gguf"), type};
+        r.down = {g.upload(bytes(down), "down gguf"), type};
+        r.shared_gate = {g.upload(bytes(sgate), "sg gguf"), type}; r.shared_up = {g.upload(bytes(sup), "su gguf"), type};
+        r.shared_down = {g.upload(bytes(sdown), "sd gguf"), type};
+        MoeMmLayouts all_raw;
+        all_raw.gate = all_raw.up = all_raw.down = all_raw.shared_gate = all_raw.shared_up = all_raw.shared_down = PrefillWeightLayout::gguf;
+        prepare_moe_mm_many(g, r, shape, all_raw);
+        refuses([&] { prepare_moe_mm_many(g, r, shape); }, "raw GGUF tensors declared planar were accepted");
+        refuses([&] { prepare_moe_mm_many(g, w, shape, all_raw); }, "registered planar tensors declared raw GGUF were accepted");
+        const auto before = g.allocations();
+        g.begin();
+        encode_moe_mm_many(g, r, scratch, {input, rows, C, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true, all_raw);
+        const auto batch = g.submit();
+        require(batch.dispatches == moe_mm_many_dispatches(g, r, shape, rows, capacity, all_raw) && g.allocations() == before, "dispatch / allocation invariant (raw GGUF)");
+        require(g.read(output) == planar_rows, "raw GGUF and planar weights gave different rows");
+        std::cout << "  encode_moe_mm_many raw GGUF blocks: rows identical to the planar run\n";
+        for (const auto& m : {r.gate, r.up, r.down, r.shared_gate, r.shared_up, r.shared_down}) g.release(m.view);
+    }
     g.begin();
     refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows, C - 1, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true); }, "column mismatch accepted");
     refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows, C, in_stride - 4}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true); }, "unaligned stride accepted");

@@ -317,8 +317,9 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
  * result bits); gate, up and their shared expert in one layout; hidden a multiple of 64, channels of 256.
  *   1. tsp_moe_rows_f16k                                       binary16 copy of the input rows in the K order the tensor-core tiles use
  *   2. tsp_moe_permute(..., tile = TSP_GROUPED_TILE)           token_map / counts / tasks (tasks of 256 routes = two sub-tiles of 128)
- *   3. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e; experts+3 words: the last
- *                                                              two are the item counters of steps 5 and 6, cleared here
+ *   3. tsp_moe_route_offsets                                   offsets[e] = first permuted position of expert e; experts+5 words: the last
+ *                                                              four are item counters, cleared here (steps 5 and 6, and the
+ *                                                              two dense launches of a shared expert in another encoding)
  *   4. tsp_moe_gather_rows16                                   the routed copy of the rows of step 1, in permuted position order
  *   5. tsp_moe_grouped_gate_up                                 H[pos][hidden] binary16, SwiGLU applied, FP32 accumulate in tensor memory
  *   6. tsp_moe_grouped_down                                    routed[route][channel], FP32 or binary16, scattered by route id
@@ -327,6 +328,7 @@ int tsp_moe_layer_decode(const tsp_moe_weights* w, const tsp_moe_scratch* s,
  * row of d_xk / d_xp / d_hp are stored in the order 0,2,1,3,4,6,5,7 (the order the dequantised weight tiles use), which only
  * these kernels read. Operands are binary16, accumulation FP32. The route id of a route is row*selected + slot.
  *
+ * Weights of steps 5 and 6 may also be Q8_0 GGUF blocks (the Q8_0 expert sets of the MTP block).
  * Both GEMMs take the layer's dense shared expert in the same launch when shared_* is non-NULL (same shape, encoding and
  * layout as a routed expert): its tasks cover every one of `tokens` rows in row order and follow the routed ones, as
  * `encode_moe_mm_many` runs the shared expert's dense projections right after the routed ones (moe_mm_many.cpp:189-214).
@@ -350,6 +352,21 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* share
                          uint64_t s_hp_stride_bytes, uint32_t shared_tokens, float* d_shared_out, uint64_t shared_out_stride_bytes,
                          uint32_t* d_error, void* stream);
 
+/* Dense projections of row batches through the same tensor-core kernel (no routing tables): the shared expert when its
+ * encoding or layout differs from the routed experts', i.e. the reference's dense Q8_0 shared expert beside Q4_K experts.
+ * Replace `nax_dense_q8_swiglu` (gate + up + SwiGLU in one dispatch) and `dense_mm_q8` as `encode_moe_mm_many` uses them
+ * (moe_mm_many.cpp:236-259; kernels nax_prefill.metal:1506-1636). Matrices: single [rows x cols] Q8_0 GGUF blocks or Q4_K
+ * (planar or GGUF), rows a multiple of 64 (gate/up) or 128, cols of 256.
+ *   tsp_dense_mm_swiglu: d_xk binary16 input rows in tile K order (tsp_moe_rows_f16k) -> d_h binary16 silu(gate.x) * (up.x), in
+ *                        the K order the next projection reads;
+ *   tsp_dense_mm:        d_xk binary16 rows in tile K order (e.g. the rows tsp_dense_mm_swiglu wrote) -> d_out FP32 rows.
+ * d_counter: one device word holding 0 when the launch starts (the item hand-out counter; tsp_moe_route_offsets clears words
+ * experts+3 and experts+4 of its buffer for this use). */
+int tsp_dense_mm_swiglu(const tsp_matrix_set* gate, const tsp_matrix_set* up, const void* d_xk, uint64_t xk_stride_bytes, uint32_t rows,
+                        void* d_h, uint64_t h_stride_bytes, uint32_t* d_counter, uint32_t* d_error, void* stream);
+int tsp_dense_mm(const tsp_matrix_set* matrix, const void* d_xk, uint64_t xk_stride_bytes, uint32_t rows, float* d_out,
+                 uint64_t out_stride_bytes, uint32_t* d_counter, uint32_t* d_error, void* stream);
+
 /* Test hook: the binary16 values the grouped kernels stage for one Q4_K planar expert, [rows x cols] in natural K order.
  * Per weight this is RN16((q - 8) * RN16(d*sc) + RN16(8*d*sc - dmin*mn)), three roundings instead of the one rounding of
  * the exact value the reference's tensor-op path stages (planar_moe_v3.metal:165); the tests bound the deviation. */
@@ -359,14 +376,16 @@ int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, vo
  * routed copy of the rows -> grouped gate-up + SwiGLU -> grouped down (the dense shared expert rides in both launches) -> gated mixture.
  * Replaces `encode_moe_mm_many` after its router projection (moe_mm_many.cpp:126-220) on the `planar_nax_grouped_moe`
  * path (graph.mm:9293-9420). Weights: Q4_K, Pack v3 planar or plain GGUF super-blocks, hidden a multiple of 64 and channels
- * of 256; the shared expert in the same form as the routed experts of its projection. Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
+ * of 256. A shared expert in the routed experts' form rides in the routed launches; in another form (dense Q8_0 GGUF blocks
+ * beside Q4_K experts, as the reference's model has it) it is computed by tsp_dense_mm_swiglu / tsp_dense_mm in launches of
+ * its own (11 launches instead of 9). Arguments as tsp_moe_layer_decode; `tokens` <= s->base.capacity.
  * Caller-owned scratch, all device memory, nothing has to start at zero:
  *   base: as for the decode layer, except d_tasks sized tsp_moe_tasks_words(capacity, experts, selected, TSP_GROUPED_TILE);
  *         d_routed is used as binary16 rows [capacity*selected x channels]; d_hidden, d_shared_hidden and d_x32 are not
  *         used and may be NULL;
  *   d_xk: binary16 copy of the input rows in tile K order, [capacity x channels];
  *   d_xp / d_hp: binary16 rows in permuted position order, [capacity*selected x channels] / [capacity*selected x hidden];
- *   d_offsets [experts + 3]; d_s_hp: the shared expert's binary16 hidden rows, [capacity x hidden]. */
+ *   d_offsets [experts + 5]; d_s_hp: the shared expert's binary16 hidden rows, [capacity x hidden]. */
 typedef struct tsp_moe_prefill_scratch {
     tsp_moe_scratch base;
     void* d_xk;

@@ -94,6 +94,8 @@ SIGNATURES = {
     "tsp_moe_gather_rows16": (_i, [_vp, _u64, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp]),
     "tsp_moe_grouped_gate_up": (_i, [_MS, _MS, _MS, _MS, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp, _vp]),
     "tsp_moe_grouped_down": (_i, [_MS, _MS, _vp, _u64, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _vp, _u64, _u32, _vp, _u64, _vp, _vp]),
+    "tsp_dense_mm_swiglu": (_i, [_MS, _MS, _vp, _u64, _u32, _vp, _u64, _vp, _vp, _vp]),
+    "tsp_dense_mm": (_i, [_MS, _vp, _u64, _u32, _vp, _u64, _vp, _vp, _vp]),
     "tsp_moe_staged_f16": (_i, [_MS, _u32, _vp, _vp]),
     "tsp_moe_layer_decode_static_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
     "tsp_q8_lanes_unpack": (_i, [_vp, _vp, _u64, _u32, _vp]),

@@ -605,6 +605,32 @@ int tsp_moe_grouped_down(const tsp_matrix_set* down, const tsp_matrix_set* share
                           counter, d_routed, routed_stride, routed_dtype, d_error, st, &sh);
 }
 
+int tsp_dense_mm_swiglu(const tsp_matrix_set* gate, const tsp_matrix_set* up, const void* d_xk, uint64_t xk_stride, uint32_t rows,
+                        void* d_h, uint64_t h_stride, uint32_t* d_counter, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(gate, "dense gate")) return rc;
+    if (int rc = check_matrix(up, "dense up")) return rc;
+    TSP_REQUIRE(gate->experts == 1 && up->experts == 1 && gate->type == up->type && gate->layout == up->layout && gate->rows == up->rows &&
+                gate->cols == up->cols, "dense gate/up must be single matrices of one shape, encoding and layout");
+    TSP_REQUIRE(rows >= 1 && d_counter, "dense gate-up: no rows or no item counter");
+    if (int rc = check_rows(d_xk, xk_stride, gate->cols, 2, "dense gate-up input")) return rc;
+    if (int rc = check_rows(d_h, h_stride, gate->rows, 2, "dense gate-up output")) return rc;
+    const GroupedShared sh{gate, up, d_xk, xk_stride, rows, d_h, h_stride};
+    return launch_grouped(gate, up, true, d_xk, xk_stride, rows, rows, 1, nullptr, nullptr, nullptr, nullptr, d_counter, d_h, h_stride, 0, d_error,
+                          static_cast<cudaStream_t>(stream), &sh);
+}
+
+int tsp_dense_mm(const tsp_matrix_set* m, const void* d_xk, uint64_t xk_stride, uint32_t rows, float* d_out, uint64_t out_stride,
+                 uint32_t* d_counter, uint32_t* d_error, void* stream) {
+    if (int rc = check_matrix(m, "dense matrix")) return rc;
+    TSP_REQUIRE(m->experts == 1, "dense projection: one matrix");
+    TSP_REQUIRE(rows >= 1 && d_counter, "dense projection: no rows or no item counter");
+    if (int rc = check_rows(d_xk, xk_stride, m->cols, 2, "dense projection input")) return rc;
+    if (int rc = check_rows(d_out, out_stride, m->rows, 4, "dense projection output")) return rc;
+    const GroupedShared sh{m, nullptr, d_xk, xk_stride, rows, d_out, out_stride};
+    return launch_grouped(m, nullptr, false, d_xk, xk_stride, rows, rows, 1, nullptr, nullptr, nullptr, nullptr, d_counter, d_out, out_stride, 0, d_error,
+                          static_cast<cudaStream_t>(stream), &sh);
+}
+
 int tsp_moe_staged_f16(const tsp_matrix_set* m, uint32_t expert, void* d_out, void* stream) {
     if (int rc = check_matrix(m, "staged tile")) return rc;
     if (m->type != TSP_TYPE_Q4_K || m->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "staged tile: only Q4_K Pack v3 planar weights go through the tensor-core kernels");
@@ -675,12 +701,24 @@ int tsp_moe_layer_prefill(const tsp_moe_weights* w, const tsp_moe_prefill_scratc
     if (int rc = tsp_moe_route_offsets(s->d_counts, experts, ps->d_offsets, st)) return rc;
     if (int rc = tsp_moe_gather_rows16(ps->d_xk, channels * 2ull, s->d_token_map, ps->d_offsets, experts, tokens, selected, channels, ps->d_xp,
                                        channels * 2ull, st)) return rc;
-    // the dense shared expert rides in both launches; the route rows are kept as binary16 (half the traffic of the mixture)
-    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, &w->shared_gate, &w->shared_up, ps->d_xp, channels * 2ull, ps->d_xk, channels * 2ull, tokens, tokens, selected, s->d_token_map,
+    // the dense shared expert rides in both launches when it has the routed experts' encoding and layout; in another form (the
+    // reference's dense Q8_0 shared expert beside Q4_K experts) it gets the same kernel in launches of its own.
+    // The route rows are kept as binary16 (half the traffic of the mixture)
+    auto same_form = [](const tsp_matrix_set& a, const tsp_matrix_set& b) { return a.type == b.type && a.layout == b.layout; };
+    const bool ride_up = same_form(w->shared_gate, w->gate) && same_form(w->shared_up, w->gate);
+    const bool ride_down = same_form(w->shared_down, w->down);
+    if (int rc = tsp_moe_grouped_gate_up(&w->gate, &w->up, ride_up ? &w->shared_gate : nullptr, ride_up ? &w->shared_up : nullptr, ps->d_xp, channels * 2ull,
+                                         ps->d_xk, channels * 2ull, tokens, tokens, selected, s->d_token_map,
                                          s->d_counts, s->d_tasks, ps->d_offsets, ps->d_hp, hidden * 2ull, ps->d_s_hp, hidden * 2ull, d_error, st)) return rc;
-    if (int rc = tsp_moe_grouped_down(&w->down, &w->shared_down, ps->d_hp, hidden * 2ull, tokens, selected, s->d_token_map, s->d_counts, s->d_tasks,
-                                      ps->d_offsets, s->d_routed, channels * 2ull, 1, ps->d_s_hp, hidden * 2ull, tokens, s->d_shared_out, channels * 4ull,
-                                      d_error, st)) return rc;
+    if (!ride_up)
+        if (int rc = tsp_dense_mm_swiglu(&w->shared_gate, &w->shared_up, ps->d_xk, channels * 2ull, tokens, ps->d_s_hp, hidden * 2ull,
+                                         ps->d_offsets + experts + 3, d_error, st)) return rc;
+    if (int rc = tsp_moe_grouped_down(&w->down, ride_down ? &w->shared_down : nullptr, ps->d_hp, hidden * 2ull, tokens, selected, s->d_token_map, s->d_counts,
+                                      s->d_tasks, ps->d_offsets, s->d_routed, channels * 2ull, 1, ps->d_s_hp, hidden * 2ull, tokens, s->d_shared_out,
+                                      channels * 4ull, d_error, st)) return rc;
+    if (!ride_down)
+        if (int rc = tsp_dense_mm(&w->shared_down, ps->d_s_hp, hidden * 2ull, tokens, s->d_shared_out, channels * 4ull, ps->d_offsets + experts + 4,
+                                  d_error, st)) return rc;
     return tsp_moe_combine(s->d_routed, channels * 2ull, 1, s->d_weights, s->d_shared_out, channels * 4ull, w->d_shared_router, d_x, x_stride, x_dtype,
                            s->d_shared_logit, tokens, channels, selected, out_dtype == 0 ? static_cast<float*>(d_out) : nullptr,
                            out_dtype == 0 ? out_stride : 0, out_dtype == 1 ? d_out : nullptr, out_dtype == 1 ? out_stride : 0, d_error, st);

@@ -129,7 +129,8 @@ struct alignas(64) GroupedMaps { CUtensorMap q[6], f[6], d[6], x[6]; };
 
 struct GroupedParams {
     uint32_t split, experts;
-    uint32_t nblk;                 // super-blocks per weight row (K / 256)
+    uint32_t nblk;                 // quant-stage loads per item: super-blocks per weight row (K / 256); Q8_0: spans of four blocks (K / 128)
+    uint32_t chunks;               // K chunks of 64 per item
     uint32_t row_blocks;           // items per task: hidden / 64 (gate-up) or rows / 128 (down)
     uint32_t merged, sh_merged;    // both matrices of an expert arrive with one copy per plane (routed experts; shared expert)
     // optional dense shared expert processed by the same launch after the routed tasks: every one of sh_tokens rows, in
@@ -159,7 +160,7 @@ struct GTask { uint32_t expert, start, count, row0; };
 // A task of the shared expert carries the expert id p.experts (one past the routed ids).
 __device__ __forceinline__ GTask gtask(const GroupedParams& p, uint32_t task) {
     GTask t;
-    const uint32_t routed = p.tasks[0];
+    const uint32_t routed = p.tasks ? p.tasks[0] : 0u;
     if (task >= routed) {
         t.expert = p.experts;
         t.start = (task - routed) * kTaskRoutes;
@@ -247,10 +248,47 @@ struct SchedReader {
 
 // GATEUP: two weight matrices (gate, up) interleaved 16 + 16 rows per lane quarter and the SwiGLU epilogue writing binary16
 // hidden rows in permuted position order; otherwise one matrix and route rows scattered to their route ids.
-// GGUF: the weights are plain 144-byte super-blocks (16-byte header: d, dmin, twelve bytes of packed 6-bit factors; then the 128
-// code bytes). The code map then steps 144 bytes per super-block from the first block's byte 16, the factor map brings the whole
-// header, the (d, dmin) ring is left idle and the dequant warps unpack the factors (numeric.cpp:17-31 states the packing).
-template <bool GATEUP, bool GGUF>
+// ENC selects the weight bytes:
+//   kEncPlanar  Q4_K Pack v3 planes (codes, 16-byte factor records, (d, dmin) pairs);
+//   kEncGguf    Q4_K plain 144-byte super-blocks (16-byte header: d, dmin, twelve bytes of packed 6-bit factors; then the 128
+//               code bytes). The code map steps 144 bytes per super-block from the first block's byte 16, the factor map brings
+//               the whole header, the (d, dmin) ring is left idle and the dequant warps unpack the factors (numeric.cpp:17-31);
+//   kEncQ8      Q8_0 plain 34-byte blocks (binary16 scale, 32 signed codes; numeric.cpp:33-45). A quant stage holds four blocks
+//               (136 bytes = two K chunks) of every row in a 144-byte line: 136 * span is 16-byte aligned for even spans only,
+//               so odd spans are fetched from 8 bytes earlier and read from byte 8 of the line.
+constexpr int kEncPlanar = 0, kEncGguf = 1, kEncQ8 = 2;
+
+// One Q8_0 chunk (two blocks = 68 bytes starting at word WS of the 20 words `L`) -> the chunk's 128-byte A row. Block 0 starts on
+// a word boundary (scale in the low half-word, codes two bytes off: realigned with funnel shifts), block 1 two bytes past one
+// (scale in the high half-word, codes word-aligned). A code byte b becomes binary16 through 0x6400 | (b ^ 0x80) = 1152 + q, the
+// subtraction is exact and d * q is rounded once: the staged value is RN16 of the exact weight.
+template <uint32_t WS>
+__device__ __forceinline__ bool q8_chunk_row(const uint32_t (&L)[20], uint8_t* arow, uint32_t sw) {
+    const __half2 k1152 = __float2half2_rn(1152.f);
+    const uint32_t s0 = L[WS] & 0xffffu, s1 = L[WS + 8] >> 16;
+    const bool finite = (s0 & 0x7c00u) != 0x7c00u && (s1 & 0x7c00u) != 0x7c00u;
+    const uint32_t dw0 = s0 | (s0 << 16), dw1 = s1 | (s1 << 16);
+    const __half2 d0 = *reinterpret_cast<const __half2*>(&dw0), d1 = *reinterpret_cast<const __half2*>(&dw1);
+#pragma unroll
+    for (uint32_t u = 0; u < 8; ++u) {          // unit u: K positions 8u .. 8u+7 of the chunk
+        uint32_t a, b;
+        if (u < 4) { a = __funnelshift_r(L[WS + 2 * u], L[WS + 2 * u + 1], 16); b = __funnelshift_r(L[WS + 2 * u + 1], L[WS + 2 * u + 2], 16); }
+        else { a = L[WS + 9 + 2 * (u - 4)]; b = L[WS + 10 + 2 * (u - 4)]; }
+        a ^= 0x80808080u; b ^= 0x80808080u;
+        const __half2 d = u < 4 ? d0 : d1;
+        uint32_t w[4] = {__byte_perm(a, 0x64646464u, 0x4240), __byte_perm(a, 0x64646464u, 0x4341),
+                         __byte_perm(b, 0x64646464u, 0x4240), __byte_perm(b, 0x64646464u, 0x4341)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&w[i]), k1152), d);
+            w[i] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+        *reinterpret_cast<uint4*>(arow + ((u ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    return finite;
+}
+
+template <bool GATEUP, int ENC>
 __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __grid_constant__ GroupedMaps maps, const GroupedParams p) {
     pdl_launch_dependents();
     extern __shared__ uint8_t gsm_raw[];
@@ -284,9 +322,11 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();   // everything above touched shared and tensor memory only
 
-    const uint32_t n_tasks = p.tasks[0] + p.sh_tasks;
+    constexpr bool GGUF = ENC == kEncGguf, Q8 = ENC == kEncQ8;
+    const uint32_t routed_tasks = p.tasks ? p.tasks[0] : 0u;   // no table: a dense launch (the shared expert's tasks only)
+    const uint32_t n_tasks = routed_tasks + p.sh_tasks;
     const uint32_t n_items = n_tasks * p.row_blocks;
-    const uint32_t chunks_per_item = p.nblk * 4;   // K chunks of 64 (a multiple of 4: chunk parity is the same in every item)
+    const uint32_t chunks_per_item = p.chunks;     // K chunks of 64 (an even number: a dequant thread's chunk parity is the same in every item)
     SchedReader sched{sfull, sempty, sched_slots};
     uint8_t* const stages = gsm + p.off_st;
 
@@ -315,7 +355,7 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                 const uint32_t mi = shared ? 4u : (hi ? 1u : 0u);                 // map of matrix A; matrix B's is `ms` further
                 const uint32_t ms = shared ? 1u : 2u;
                 const uint32_t ncopy = (NMAT == 1 || (shared ? p.sh_merged : p.merged)) ? 1u : NMAT;
-                if (!GGUF) {
+                if (ENC == kEncPlanar) {
                     // the (d, dmin) pairs of the item's rows over the whole K: RM * nblk * 4 bytes per matrix = lines of 256 bytes
                     ok = gwait(&dempty[ds], dph ^ 1u);
                     if (!ok) break;
@@ -331,6 +371,12 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                     if (!ok) break;
                     uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
                     mbar_arrive_expect_tx(&qfull[qs], kRowsM * 128u + kRowsM * 16u);
+                    if (Q8) {
+                        // four blocks of every row: [matrix][RM][144 B]; odd spans start 8 bytes early (16-byte aligned x)
+                        const int x = static_cast<int>(sb * 136u - ((sb & 1u) ? 8u : 0u));
+                        for (uint32_t m = 0; m < ncopy; ++m)
+                            tma_load_4d_g(q + m * (RM * 144u), &maps.q[mi + ms * m], x, r0, 0, el, &qfull[qs]);
+                    } else
                     for (uint32_t m = 0; m < ncopy; ++m) {
                         tma_load_5d_g(q + m * (RM * 128u), &maps.q[mi + ms * m], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
                         if (GGUF) tma_load_5d_g(q + kRowsM * 128u + m * (RM * 16u), &maps.f[mi + ms * m], 0, r0, static_cast<int>(sb), 0, el, &qfull[qs]);
@@ -430,11 +476,40 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
         for (;;) {
             const SchedItem it = sched.next(lane);
             if (it.item >= n_items) { ok = it.item != 0xffffffffu; break; }
-            if (!GGUF && ok) ok = gwait(&dfull[ds], dph);
+            if (ENC == kEncPlanar && ok) ok = gwait(&dfull[ds], dph);
             const uint8_t* dmp = gsm + p.off_d + ds * p.d_stage_bytes + mat * p.dm_mat_bytes + mrow * p.nblk * 4u;
             for (uint32_t sb = 0; sb < p.nblk; ++sb) {
                 if (ok) ok = gwait(&qfull[qs], qph);
                 const uint8_t* q = gsm + p.off_q + qs * p.q_stage_bytes;
+                if (Q8) {
+                    // this thread's chunk of the span: blocks 2 * half, 2 * half + 1 of the row's four
+                    if (ok) ok = gwait(&empty[st], sph ^ 1u);
+                    if (ok) {
+                        const uint4* src = reinterpret_cast<const uint4*>(q + line * 144u) + half * 4u;
+                        uint32_t L[20];
+#pragma unroll
+                        for (int i = 0; i < 5; ++i) { const uint4 v = src[i]; L[4 * i] = v.x; L[4 * i + 1] = v.y; L[4 * i + 2] = v.z; L[4 * i + 3] = v.w; }
+                        uint8_t* arow = stages + st * kStageBytes + r * 128u;
+                        bool finite;
+                        // first word of the chunk among the 20: byte (8 if the span is odd) + 68 * half - 64 * half
+                        switch (half + 2u * (sb & 1u)) {
+                            case 0: finite = q8_chunk_row<0>(L, arow, sw); break;
+                            case 1: finite = q8_chunk_row<1>(L, arow, sw); break;
+                            case 2: finite = q8_chunk_row<2>(L, arow, sw); break;
+                            default: finite = q8_chunk_row<3>(L, arow, sw); break;
+                        }
+                        if (!finite) raise_error(p.error, TSP_ERR_NONFINITE);
+                        fence_async_smem();
+                    }
+                    __syncwarp();
+                    if (lane == 0 && ok) mbar_arrive(&full[st]);
+                    st += 2;
+                    if (st >= kStages) { st -= kStages; sph ^= 1u; }
+                    __syncwarp();
+                    if (lane == 0 && ok) mbar_arrive(&qempty[qs]);
+                    if (++qs == 2) { qs = 0; qph ^= 1u; }
+                    continue;
+                }
                 // d, dmin and the sixteen 6-bit factors of this row's super-block
                 uint4 fac = *reinterpret_cast<const uint4*>(q + kRowsM * 128u + line * 16u);
                 uint32_t dmw;
@@ -481,7 +556,7 @@ __global__ void __launch_bounds__(kGWarps * 32, 1) grouped_mma_kernel(const __gr
                 if (lane == 0 && ok) mbar_arrive(&qempty[qs]);
                 if (++qs == 2) { qs = 0; qph ^= 1u; }
             }
-            if (!GGUF) {
+            if (ENC == kEncPlanar) {
                 __syncwarp();
                 if (lane == 0 && ok) mbar_arrive(&dempty[ds]);
                 if (++ds == 2) { ds = 0; dph ^= 1u; }
@@ -678,8 +753,10 @@ __global__ void __launch_bounds__(256) route_offsets_kernel(const uint32_t* __re
     }
     if (tid == 0) {
         offsets[experts] = carry;
-        offsets[experts + 1] = 0;   // the item counters of the two grouped GEMM launches that follow
-        offsets[experts + 2] = 0;
+        offsets[experts + 1] = 0;   // the item counters of the grouped GEMM launches that follow (routed gate-up, routed down, and
+        offsets[experts + 2] = 0;   // the two dense launches of a shared expert in another encoding)
+        offsets[experts + 3] = 0;
+        offsets[experts + 4] = 0;
     }
 }
 
@@ -759,16 +836,18 @@ int launch_rows_f16k(const void* x, uint64_t x_stride, uint32_t x_dtype, uint32_
 // ---------------------------------------------------------------------------------------------
 // host launcher of the grouped tensor-core GEMMs
 // ---------------------------------------------------------------------------------------------
-template <bool GATEUP, bool GGUF>
+template <bool GATEUP, int ENC>
 static int launch_grouped_t(const GroupedMaps& m, const GroupedParams& p, size_t smem, int grid, cudaStream_t st) {
-    auto kernel = grouped_mma_kernel<GATEUP, GGUF>;
+    auto kernel = grouped_mma_kernel<GATEUP, ENC>;
     static thread_local SmemAttrCache configured;   // per kernel instantiation, keyed by device
     TSP_CUDA(ensure_dynamic_smem(kernel, configured, smem));
     TSP_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGWarps * 32), smem, st, m, p));
     return TSP_OK;
 }
 
-// a/b: Q4_K matrix sets [rows x cols], Pack v3 planar or plain GGUF super-blocks (both sets in the same layout).
+// a/b: Q4_K matrix sets [rows x cols], Pack v3 planar or plain GGUF super-blocks, or Q8_0 GGUF blocks (both sets and the shared
+// expert's in the same encoding and layout). tasks == nullptr: a dense launch, only the shared expert's rows (`sh`) are computed
+// and a/b only give the shape.
 // gate-up: act = the routed copy of the K-ordered input rows in permuted position order (act_rows of them);
 //          out = binary16 hidden rows [positions x rows] in permuted position order; shared expert: sh->act = the K-ordered
 //          input rows by token, sh->out hidden rows by token.
@@ -778,16 +857,19 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
                    uint32_t tokens, uint32_t selected, const uint32_t* token_map, const uint32_t* tasks, const uint32_t* counts,
                    const uint32_t* offsets, uint32_t* work_counter, void* out, uint64_t out_stride, uint32_t out_f16, uint32_t* error, cudaStream_t st,
                    const GroupedShared* sh) {
-    if (a->type != TSP_TYPE_Q4_K) return fail(TSP_E_TYPE, "grouped GEMM: only Q4_K weights have a tensor-core kernel");
+    const bool q8 = a->type == TSP_TYPE_Q8_0;
+    if (a->type != TSP_TYPE_Q4_K && !(q8 && a->layout == TSP_LAYOUT_GGUF))
+        return fail(TSP_E_TYPE, "grouped GEMM: the tensor-core kernel reads Q4_K (planar or GGUF blocks) and Q8_0 GGUF blocks");
+    TSP_REQUIRE(tasks || sh, "grouped GEMM: a launch without a task table needs the dense rows");
     const bool gguf = a->layout == TSP_LAYOUT_GGUF;
     const uint32_t rm = gateup ? 64u : 128u;
     TSP_REQUIRE(a->rows % rm == 0 && a->cols % 256 == 0, "grouped GEMM: rows must be a multiple of %u and columns of 256", rm);
     GroupedParams p{};
-    const uint32_t nblk = a->cols / 256;
-    TSP_REQUIRE(nblk <= 32, "grouped GEMM: K extent too large");
+    const uint32_t nblk = q8 ? a->cols / 128 : a->cols / 256;
+    TSP_REQUIRE(a->cols / 256 <= 32, "grouped GEMM: K extent too large");
     p.split = a->split < a->experts ? a->split : a->experts;
     p.experts = a->experts;
-    p.nblk = nblk; p.row_blocks = a->rows / rm;
+    p.nblk = nblk; p.chunks = a->cols / 64; p.row_blocks = a->rows / rm;
     const uint64_t total_units = static_cast<uint64_t>(a->rows) * nblk;
     const uint64_t sm_off = total_units * 128, dm_off = total_units * 144;
     const uint8_t* base[4] = {static_cast<const uint8_t*>(a->base), static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base), nullptr, nullptr};
@@ -800,7 +882,7 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     p.tasks = tasks; p.counts = counts; p.offsets = offsets;
     p.out = out; p.out_stride_bytes = out_stride; p.out_f16 = out_f16; p.error = error; p.work_counter = work_counter;
     const uint32_t nmat = gateup ? 2 : 1;
-    p.dm_mat_bytes = rm * nblk * 4u;                  // a multiple of 256: rm >= 64
+    p.dm_mat_bytes = q8 ? 0u : rm * nblk * 4u;        // a multiple of 256: rm >= 64 (Q8_0: no (d, dmin) ring)
     p.off_q = 1024;
     p.q_stage_bytes = kRowsM * (128u + 16u);
     p.off_d = p.off_q + 2 * p.q_stage_bytes;
@@ -820,6 +902,16 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     p.merged = gateup && mergeable(base[0], base[2], &delta) && mergeable(base[1], base[3], &delta_hi) && delta == delta_hi;
     GroupedMaps maps;
     auto plane_maps = [&](const uint8_t* bp, uint32_t mats, uint64_t ds, uint32_t n, uint64_t stride, uint32_t at) -> int {
+        if (q8) {
+            // rows of 34-byte blocks: [row bytes][row][matrix][expert]; a box is 144 bytes (four blocks + 8) of rm rows. The last
+            // even span's box ends 8 bytes past the row: those bytes arrive as zeros and are not read
+            const uint64_t row_bytes = uint64_t(a->cols / 32) * 34;   // a multiple of 16: columns are a multiple of 256
+            const uint64_t dims[4] = {row_bytes, a->rows, mats, n}, strides[3] = {row_bytes, ds, stride};
+            const uint32_t box[4] = {144, rm, mats, 1};
+            if (int rc = get_tensor_map_bytes(bp, 4, dims, strides, box, false, &maps.q[at])) return rc;
+            maps.f[at] = maps.q[at]; maps.d[at] = maps.q[at];   // not read
+            return TSP_OK;
+        }
         if (gguf) {
             // codes: bytes 16..143 of every 144-byte super-block, [128 B][row][super-block][matrix][expert], 128-byte swizzle;
             // headers: bytes 0..15 of the same blocks, same walk
@@ -853,7 +945,7 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     const uint64_t ds = p.merged ? delta : 16;
     const uint64_t stride = a->experts > 1 ? a->expert_stride : 16;
     TSP_REQUIRE(stride % 16 == 0, "grouped GEMM: expert stride must be a multiple of 16");
-    TSP_REQUIRE(gguf || total_units * 4 % 256 == 0, "grouped GEMM: the (d, dmin) plane must be a whole number of 256-byte lines");
+    TSP_REQUIRE(gguf || q8 || total_units * 4 % 256 == 0, "grouped GEMM: the (d, dmin) plane must be a whole number of 256-byte lines");
     const uint32_t n_lo = p.split, n_hi = a->experts - p.split;
     for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t m = i >> 1;
@@ -889,8 +981,9 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     }
     const int grid = sm_count();
     if (grid <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
-    if (gguf) return gateup ? launch_grouped_t<true, true>(maps, p, smem, grid, st) : launch_grouped_t<false, true>(maps, p, smem, grid, st);
-    return gateup ? launch_grouped_t<true, false>(maps, p, smem, grid, st) : launch_grouped_t<false, false>(maps, p, smem, grid, st);
+    if (q8) return gateup ? launch_grouped_t<true, kEncQ8>(maps, p, smem, grid, st) : launch_grouped_t<false, kEncQ8>(maps, p, smem, grid, st);
+    if (gguf) return gateup ? launch_grouped_t<true, kEncGguf>(maps, p, smem, grid, st) : launch_grouped_t<false, kEncGguf>(maps, p, smem, grid, st);
+    return gateup ? launch_grouped_t<true, kEncPlanar>(maps, p, smem, grid, st) : launch_grouped_t<false, kEncPlanar>(maps, p, smem, grid, st);
 }
 
 }  // namespace tsp

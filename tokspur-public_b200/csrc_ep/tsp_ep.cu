@@ -220,7 +220,7 @@ Plan make_plan(uint8_t* base, uint32_t T, uint32_t C, uint32_t H, uint32_t Eloc,
     p.counts = c.take<uint32_t>(uint64_t(Eloc) * 4);
     const uint32_t tile = prefill ? TSP_GROUPED_TILE : TSP_GEMV_TILE;
     p.tasks = c.take<uint32_t>(tsp_moe_tasks_words(uint32_t(R), Eloc, K, tile) * 4);
-    p.offsets = c.take<uint32_t>((uint64_t(Eloc) + 3) * 4);
+    p.offsets = c.take<uint32_t>((uint64_t(Eloc) + 5) * 4);
     p.shared_out = c.take<float>(uint64_t(T) * C * 4);
     p.ret = c.take<uint8_t>(uint64_t(N) * T * C * (prefill ? 2 : 4));
     if (prefill) {

@@ -273,7 +273,7 @@ class PrefillScratch:
         self.xk = torch.zeros((capacity, channels), dtype=f16, device=device)       # input rows, tile K order
         self.xp = torch.zeros((routes, channels), dtype=f16, device=device)         # their routed copy, permuted position order
         self.hp = torch.zeros((routes, hidden), dtype=f16, device=device)           # hidden rows, permuted position order
-        self.offsets = z(experts + 3, i32)   # first position of every expert, total, and the two item counters
+        self.offsets = z(experts + 5, i32)   # first position of every expert, total, and the four item counters
         self.tasks = z(int(capi.lib().tsp_moe_tasks_words(capacity, experts, selected, self.tile)), i32)
         self.s_hp = torch.zeros((capacity, hidden), dtype=f16, device=device)       # the shared expert's hidden rows
         base = capi.MoeScratch.from_buffer_copy(self.base.c)

@@ -12,9 +12,10 @@ namespace tokspur_b200 {
 
 // Registered identity of each weight tensor on the prefill path (native/include/tokspur/moe_mm_many.hpp:7-10). The grouped tensor-core
 // GEMMs read Q4_K in both forms: Pack v3 planar (a registered planar matrix; the default here, the faster walk) and raw GGUF
-// super-blocks (the reference's default). The declared identity must be the tensor's real one (a registered planar matrix declared
-// `gguf`, or the reverse, is refused), the tensors of one projection (gate, up and the shared gate / up; down and the shared
-// down) share one identity, and nothing is repacked behind the caller's back.
+// super-blocks (the reference's default), and a dense shared expert also as raw Q8_0 blocks (the reference model's form,
+// moe_mm_many.cpp:236-259). The declared identity must be the tensor's real one (a registered planar matrix declared `gguf`, or
+// the reverse, is refused), gate and up share one identity, and nothing is repacked behind the caller's back. A shared expert in
+// the routed experts' encoding and identity rides in their launches; otherwise it costs one more launch per projection.
 enum class PrefillWeightLayout : uint32_t { gguf = 0, planar = 1 };
 struct MoeMmLayouts {
     PrefillWeightLayout gate = PrefillWeightLayout::planar, up = PrefillWeightLayout::planar, down = PrefillWeightLayout::planar;
@@ -41,9 +42,9 @@ MoeMmManyBytes moe_mm_many_bytes(MoeShape shape, uint32_t capacity);
 MoeMmManyScratch allocate_moe_mm_many_scratch(CudaGraph& graph, MoeShape shape, uint32_t capacity);
 void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scratch);
 
-// Encode only. The caller owns allocation, the batch and the committed state. Weights must be Q4_K in the declared layouts
-// (planar: is_planar_moe plus planar shared matrices; gguf: raw blocks of the layer's extent); anything else is refused before
-// the first launch.
+// Encode only. The caller owns allocation, the batch and the committed state. Expert tensors must be Q4_K in the declared layouts
+// (planar: is_planar_moe; gguf: raw blocks of the layer's extent), the shared expert Q4_K in either layout or raw Q8_0 blocks;
+// anything else is refused before the first launch.
 void encode_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, const MoeMmManyScratch& scratch, GpuRowsF32 input, GpuRowsF32 output,
                         MoeShape shape, RouterMode mode, bool normalize_selected, MoeMmLayouts layouts = {});
 // The weight checks of the encoder, run between batches (prepare_moe_mm_many, moe_mm_many.hpp:59): a tensor of the wrong form or

@@ -3,6 +3,7 @@
 #include "tokspur_b200/moe_mm_many.hpp"
 
 #include <algorithm>
+#include <utility>
 
 namespace tokspur_b200 {
 namespace {
@@ -21,7 +22,7 @@ MoeMmManyBytes moe_mm_many_bytes(MoeShape s, uint32_t capacity) {
     // binary16 input rows in tile K order, their routed copy and the hidden rows in permuted order, the shared expert's hidden rows
     b.views = {n * s.experts * 4, r * 4, r * 4, r * s.channels * 2, n * s.channels * 4, n * 4,
                uint64_t(s.experts) * n * 4, uint64_t(s.experts) * 4, tsp_moe_tasks_words(capacity, s.experts, s.selected, TSP_GROUPED_TILE) * 4,
-               (uint64_t(s.experts) + 3) * 4, n * s.channels * 2, r * s.channels * 2, r * s.hidden * 2, n * s.hidden * 2};
+               (uint64_t(s.experts) + 5) * 4, n * s.channels * 2, r * s.channels * 2, r * s.hidden * 2, n * s.hidden * 2};
     for (const auto v : b.views) b.total += v;
     return b;
 }
@@ -45,17 +46,24 @@ void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scrat
 
 namespace {
 constexpr uint64_t kLaunchesPerChunk = 10;   // router GEMM, K-ordered rows, route, routes, tasks, offsets, routed copy, gate-up, down, mixture
+// a shared expert that cannot ride in the routed launches adds one launch per projection
+uint64_t extra_launches(const tsp_moe_weights& tw) {
+    auto same = [](const tsp_matrix_set& a, const tsp_matrix_set& b) { return a.type == b.type && a.layout == b.layout; };
+    return (same(tw.shared_gate, tw.gate) && same(tw.shared_up, tw.gate) ? 0u : 1u) + (same(tw.shared_down, tw.down) ? 0u : 1u);
+}
 tsp_moe_weights checked_weights(const CudaGraph& g, const MoeWeights& w, MoeShape shape, MoeMmLayouts l) {
-    // one identity per projection: the gate-up launch reads gate, up and the shared gate / up in one layout, the down launch
-    // down and the shared down in one layout
-    need(l.gate == l.up && l.gate == l.shared_gate && l.gate == l.shared_up && l.down == l.shared_down,
-         "tiled MoE: the routed and shared tensors of one projection must be registered in the same layout");
+    // gate and up go through one launch: one identity for the pair (routed, and shared). A shared expert whose encoding or
+    // identity differs from the routed experts' gets launches of its own
+    need(l.gate == l.up && l.shared_gate == l.shared_up, "tiled MoE: gate and up must be registered in the same layout");
     need(w.router.encoding == 0 && w.shared_router.encoding == 0, "router projections must be F32");
     need(w.router.view.bytes == uint64_t(shape.channels) * shape.experts * 4 && w.shared_router.view.bytes == uint64_t(shape.channels) * 4,
          "router shape mismatch");
-    need(w.gate.encoding == TSP_TYPE_Q4_K && w.up.encoding == TSP_TYPE_Q4_K && w.down.encoding == TSP_TYPE_Q4_K &&
-         w.shared_gate.encoding == TSP_TYPE_Q4_K && w.shared_up.encoding == TSP_TYPE_Q4_K && w.shared_down.encoding == TSP_TYPE_Q4_K,
-         "tiled MoE reads Q4_K tensors only");
+    need(w.gate.encoding == TSP_TYPE_Q4_K && w.up.encoding == TSP_TYPE_Q4_K && w.down.encoding == TSP_TYPE_Q4_K,
+         "tiled MoE reads Q4_K expert tensors only");
+    need(w.shared_gate.encoding == w.shared_up.encoding, "tiled MoE: shared gate and up must share an encoding");
+    for (const auto& [m, layout] : {std::pair{w.shared_gate, l.shared_gate}, std::pair{w.shared_up, l.shared_up}, std::pair{w.shared_down, l.shared_down}})
+        need(m.encoding == TSP_TYPE_Q4_K || (m.encoding == TSP_TYPE_Q8_0 && layout == PrefillWeightLayout::gguf),
+             "tiled MoE shared expert: Q4_K (planar or raw blocks) or raw Q8_0 blocks");
     // a tensor declared `gguf` must be raw blocks of the layer's extent and must not be a registered planar matrix, one declared
     // `planar` must be registered with the matching shape: the declared identity is checked, never guessed
     auto set = [&](GpuMatrix m, PrefillWeightLayout layout, uint32_t rows, uint32_t cols, uint32_t experts) {
@@ -96,8 +104,8 @@ void prepare_moe_mm_many(CudaGraph& g, const MoeWeights& w, MoeShape shape, MoeM
 uint64_t moe_mm_many_dispatches(const CudaGraph& g, const MoeWeights& w, MoeShape shape, uint32_t rows, uint32_t capacity, MoeMmLayouts layouts) {
     (void)moe_mm_many_bytes(shape, capacity);
     need(rows > 0, "tiled MoE active rows");
-    (void)checked_weights(g, w, shape, layouts);
-    return kLaunchesPerChunk * ((uint64_t(rows) + capacity - 1) / capacity);
+    const tsp_moe_weights tw = checked_weights(g, w, shape, layouts);
+    return (kLaunchesPerChunk + extra_launches(tw)) * ((uint64_t(rows) + capacity - 1) / capacity);
 }
 
 void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratch& s, GpuRowsF32 input, GpuRowsF32 output, MoeShape shape,
@@ -138,7 +146,7 @@ void encode_moe_mm_many(CudaGraph& g, const MoeWeights& w, const MoeMmManyScratc
                                          uint64_t(shape.experts) * 4, n, shape.channels, shape.hidden, shape.experts, shape.selected, uint32_t(mode),
                                          normalize_selected, g.device_pointer(output.view, true), output.stride_bytes, 0, g.error_word(), g.stream());
     if (rc != TSP_OK) throw FormatError(tsp_last_error());
-    g.count_dispatches(kLaunchesPerChunk - 1);   // the router GEMM counted itself
+    g.count_dispatches(kLaunchesPerChunk - 1 + extra_launches(tw));   // the router GEMM counted itself
 }
 
 }  // namespace tokspur_b200

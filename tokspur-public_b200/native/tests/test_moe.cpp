@@ -288,6 +288,39 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
         std::cout << "  encode_moe_mm_many raw GGUF blocks: rows identical to the planar run\n";
         for (const auto& m : {r.gate, r.up, r.down, r.shared_gate, r.shared_up, r.shared_down}) g.release(m.view);
     }
+    {   // the reference model's mix: planar Q4_K experts beside a dense shared expert of raw Q8_0 blocks (launches of its own)
+        const auto q8g = generated(8, C, H, 1, seed + 14), q8u = generated(8, C, H, 1, seed + 15), q8d = generated(8, H, C, 1, seed + 16);
+        MoeWeights m = w;
+        m.shared_gate = {g.upload(bytes(q8g), "sg q8"), 8}; m.shared_up = {g.upload(bytes(q8u), "su q8"), 8}; m.shared_down = {g.upload(bytes(q8d), "sd q8"), 8};
+        MoeMmLayouts mixed;
+        mixed.shared_gate = mixed.shared_up = mixed.shared_down = PrefillWeightLayout::gguf;
+        prepare_moe_mm_many(g, m, shape, mixed);
+        refuses([&] { prepare_moe_mm_many(g, m, shape); }, "raw Q8_0 shared tensors declared planar were accepted");
+        tso_layer LQ{C, H, E, K, type, 8, gate.data(), up.data(), down.data(), q8g.data(), q8u.data(), q8d.data(), srouter.data(), router.data(), 0, 1};
+        std::vector<double> want(size_t(rows) * C);
+        require(tso_moe_layer(&LQ, x.data(), nullptr, rows, want.data(), nullptr, 4) == TSO_OK, "oracle layer (Q8_0 shared)");
+        const auto before = g.allocations();
+        g.begin();
+        encode_moe_mm_many(g, m, scratch, {input, rows, C, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true, mixed);
+        const auto batch = g.submit();
+        const uint64_t chunks = (uint64_t(rows) + capacity - 1) / capacity;
+        require(batch.dispatches == moe_mm_many_dispatches(g, m, shape, rows, capacity, mixed) && batch.dispatches == 12 * chunks && g.allocations() == before,
+                "dispatch / allocation invariant (Q8_0 shared)");
+        const auto got = g.read(output);
+        double num = 0, den = 0;
+        for (uint32_t r = 0; r < rows; ++r)
+            for (uint32_t c = 0; c < C; ++c) {
+                float v;
+                std::memcpy(&v, got.data() + r * out_stride + size_t(c) * 4, 4);
+                const double e = want[size_t(r) * C + c];
+                require(std::isfinite(v), "non-finite row value");
+                num += (v - e) * (v - e); den += e * e;
+            }
+        const double rel = std::sqrt(num / den);
+        std::cout << "  encode_moe_mm_many with a dense Q8_0 shared expert: relative L2 error " << rel << "\n";
+        require(rel <= 2e-3, "tiled MoE (Q8_0 shared) relative L2 tolerance exceeded");
+        for (const auto& t : {m.shared_gate, m.shared_up, m.shared_down}) g.release(t.view);
+    }
     g.begin();
     refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows, C - 1, in_stride}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true); }, "column mismatch accepted");
     refuses([&] { encode_moe_mm_many(g, w, scratch, {input, rows, C, in_stride - 4}, {output, rows, C, out_stride}, shape, RouterMode::softmax, true); }, "unaligned stride accepted");

@@ -337,7 +337,9 @@ def prefill_record(args, dev, layers, T):
     def stage_pass(n):
         """CUDA-event time of each launch of the layer, issued exactly as tsp_moe_layer_prefill issues them."""
         s, st = ps.base, L.stream_ptr()
-        names = ["rows_f16k", "route", "permute", "offsets", "gather", "gate_up", "down", "combine"]
+        mixed = layers[0].shared_type != layers[0].type   # a shared expert in another encoding: launches of its own
+        names = ["rows_f16k", "route", "permute", "offsets", "gather", "gate_up"] + (["shared_gate_up"] if mixed else []) + ["down"] + \
+                (["shared_down"] if mixed else []) + ["combine"]
         acc = dict.fromkeys(names, 0.0)
         C2, C4, H2, E, K = CHANNELS * 2, CHANNELS * 4, HIDDEN * 2, EXPERTS, SELECTED
         for i in range(n):
@@ -351,14 +353,21 @@ def prefill_record(args, dev, layers, T):
             capi.check(lib.tsp_moe_permute(s.ids.data_ptr(), T, E, K, ps.tile, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(), e, st)); ev[3].record()
             capi.check(lib.tsp_moe_route_offsets(s.counts.data_ptr(), E, ps.offsets.data_ptr(), st)); ev[4].record()
             capi.check(lib.tsp_moe_gather_rows16(ps.xk.data_ptr(), C2, s.token_map.data_ptr(), ps.offsets.data_ptr(), E, T, K, CHANNELS, ps.xp.data_ptr(), C2, st)); ev[5].record()
-            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), C.byref(w.shared_gate), C.byref(w.shared_up), ps.xp.data_ptr(), C2,
-                                                   ps.xk.data_ptr(), C2, T, T, K, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(),
-                                                   ps.offsets.data_ptr(), ps.hp.data_ptr(), H2, ps.s_hp.data_ptr(), H2, e, st)); ev[6].record()
-            capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), C.byref(w.shared_down), ps.hp.data_ptr(), H2, T, K, s.token_map.data_ptr(),
+            k_ev = 6
+            capi.check(lib.tsp_moe_grouped_gate_up(C.byref(w.gate), C.byref(w.up), None if mixed else C.byref(w.shared_gate), None if mixed else C.byref(w.shared_up),
+                                                   ps.xp.data_ptr(), C2, ps.xk.data_ptr(), C2, T, T, K, s.token_map.data_ptr(), s.counts.data_ptr(), ps.tasks.data_ptr(),
+                                                   ps.offsets.data_ptr(), ps.hp.data_ptr(), H2, ps.s_hp.data_ptr(), H2, e, st)); ev[k_ev].record(); k_ev += 1
+            if mixed:
+                capi.check(lib.tsp_dense_mm_swiglu(C.byref(w.shared_gate), C.byref(w.shared_up), ps.xk.data_ptr(), C2, T, ps.s_hp.data_ptr(), H2,
+                                                   ps.offsets.data_ptr() + 4 * (E + 3), e, st)); ev[k_ev].record(); k_ev += 1
+            capi.check(lib.tsp_moe_grouped_down(C.byref(w.down), None if mixed else C.byref(w.shared_down), ps.hp.data_ptr(), H2, T, K, s.token_map.data_ptr(),
                                                 s.counts.data_ptr(), ps.tasks.data_ptr(), ps.offsets.data_ptr(), ps.routed16.data_ptr(), C2, 1,
-                                                ps.s_hp.data_ptr(), H2, T, s.shared_out.data_ptr(), C4, e, st)); ev[7].record()
+                                                ps.s_hp.data_ptr(), H2, T, s.shared_out.data_ptr(), C4, e, st)); ev[k_ev].record(); k_ev += 1
+            if mixed:
+                capi.check(lib.tsp_dense_mm(C.byref(w.shared_down), ps.s_hp.data_ptr(), H2, T, s.shared_out.data_ptr(), C4, ps.offsets.data_ptr() + 4 * (E + 4),
+                                            e, st)); ev[k_ev].record(); k_ev += 1
             capi.check(lib.tsp_moe_combine(ps.routed16.data_ptr(), C2, 1, s.weights.data_ptr(), s.shared_out.data_ptr(), C4, w.d_shared_router,
-                                           x.data_ptr(), C2, 1, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), C2, e, st)); ev[8].record()
+                                           x.data_ptr(), C2, 1, s.shared_logit.data_ptr(), T, CHANNELS, K, None, 0, out.data_ptr(), C2, e, st)); ev[k_ev].record()
             torch.cuda.synchronize()
             for k_, nme in enumerate(names):
                 acc[nme] += ev[k_].elapsed_time(ev[k_ + 1])
@@ -373,7 +382,7 @@ def prefill_record(args, dev, layers, T):
            "timed_repeats": repeats, "layer_tflops": layer_flops / (ms * 1e-3) / 1e12, "layer_frac_of_bf16_peak": layer_flops / (ms * 1e-3) / 1e12 / tf_peak,
            "gate_up_launch_tflops": gu_flops / (stages["gate_up_ms"] * 1e-3) / 1e12,
            "gate_up_launch_frac_of_bf16_peak": gu_flops / (stages["gate_up_ms"] * 1e-3) / 1e12 / tf_peak, "peak_tflops": tf_peak, "peak_kind": peak_kind,
-           "stage_ms": stages, "launches_per_step": 9, "router": "N(0,1) + Zipf(1.1) per-expert bias",
+           "stage_ms": stages, "launches_per_step": 9 + 2 * int(layers[0].shared_type != layers[0].type), "router": "N(0,1) + Zipf(1.1) per-expert bias",
            "h2d_bytes_per_step": T * CHANNELS * 2 + T * EXPERTS * 4, "d2h_bytes_per_step": T * CHANNELS * 2}
     cpu = None
     if args.cpu_tokens != 0:
@@ -591,11 +600,13 @@ def run_ours(args):
         elif args.workload == "prefill":
             Tp = args.tokens if args.tokens != 64 else args.prefill_tokens
             p_layout = formats.GGUF if args.layout == "gguf" else formats.PLANAR
-            layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, formats.Q4_K, p_layout, dev, keep_gguf=(i == 0)) for i in range(min(args.layers, 2))]
+            sh_type = formats.Q8_0 if args.shared == "q8_0" else None
+            layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, formats.Q4_K, p_layout, dev, keep_gguf=(i == 0), shared_type=sh_type)
+                      for i in range(min(args.layers, 2))]
             rec, cpu = prefill_record(args, dev, layers, Tp)
             _, tf_peak, peak_kind = peaks()
             line = base_line(args, rec["tokens_per_s"], rec["ms_per_step"], f"moe_layer_prefill_T{Tp} (BASELINE configs[2])",
-                             "Q4_K GGUF" if p_layout == formats.GGUF else "Q4_K Pack-v3 planar",
+                             ("Q4_K GGUF" if p_layout == formats.GGUF else "Q4_K Pack-v3 planar") + (" + dense Q8_0 shared expert" if sh_type else ""),
                              "f16 operands, f32 accumulate", {"router": rec["router"], "l2_policy": "inputs larger than L2: 0.93 GB of weights and 0.4 GB of intermediates per step"})
             line.update({"e2e": {"value": rec["e2e_tokens_per_s"], "unit": "tokens/s", "ms_per_step": rec["e2e_ms_per_step"],
                                  "h2d_bytes_per_step": rec["h2d_bytes_per_step"], "d2h_bytes_per_step": rec["d2h_bytes_per_step"]},
@@ -643,6 +654,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4, help="independently seeded weight sets rotated over")
     ap.add_argument("--layout", default=None, choices=["planar", "gguf"], help="weight layout (default: Pack-v3 planar for Q4_K experts, GGUF blocks for Q8_0 experts)")
     ap.add_argument("--experts", default="q4_k", choices=["q4_k", "q8_0"], help="expert encoding of the decode workload (q8_0: the MTP block)")
+    ap.add_argument("--shared", default=None, choices=["q8_0"], help="prefill workload: the shared expert as dense Q8_0 blocks (launches of its own)")
     ap.add_argument("--cpu-tokens", type=int, default=None, help="tokens of the batch timed on the CPU baseline (0 = skip)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "head", "config1"])
     ap.add_argument("--decode-only", action="store_true", help="decode workload without the extra sub-records")

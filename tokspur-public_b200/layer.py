@@ -176,7 +176,7 @@ class SynthDeviceLayer:
 
     def __init__(self, seed: int, channels: int, hidden: int, experts: int, expert_type: int = formats.Q4_K,
                  layout: int = formats.PLANAR, device="cuda", sigma: float = 0.02, expert_range: tuple[int, int] | None = None,
-                 keep_gguf: bool = False, expert_ids: list[int] | None = None):
+                 keep_gguf: bool = False, expert_ids: list[int] | None = None, shared_type: int | None = None):
         lib = capi.lib()
         lo, hi = expert_range if expert_range else (0, experts)
         # `expert_ids` names the routed experts held one by one (expert parallelism with replicated experts): local slot i holds
@@ -193,8 +193,13 @@ class SynthDeviceLayer:
         st = stream_ptr()
         u8 = lambda nbytes: torch.empty(int(nbytes), dtype=torch.uint8, device=device)
 
-        def gen(stream_seed, which):
+        def gen(stream_seed, which, type_=expert_type):
             """The experts `which` (global ids) of one weight stream; runs of consecutive ids become one call."""
+            if type_ != expert_type:   # a dense shared expert in another encoding: one matrix of raw blocks
+                nb = int(lib.tsp_expert_bytes(type_, formats.GGUF, hidden, channels))
+                t = u8(nb)
+                capi.call("tsp_synth_weights", type_, stream_seed, 0, hidden * channels // (256 if type_ == formats.Q4_K else 32), sigma, t.data_ptr(), st)
+                return t
             t = u8(len(which) * gb)
             at = 0
             while at < len(which):
@@ -207,7 +212,8 @@ class SynthDeviceLayer:
             return t
 
         g, u, d = gen(seed * 8 + 0, ids), gen(seed * 8 + 1, ids), gen(seed * 8 + 2, ids)
-        sg, su, sd = gen(seed * 8 + 3, [0]), gen(seed * 8 + 4, [0]), gen(seed * 8 + 5, [0])
+        self.shared_type = expert_type if shared_type is None else shared_type
+        sg, su, sd = (gen(seed * 8 + 3 + i, [0], self.shared_type) for i in range(3))
         self.shared_router = torch.empty(channels, dtype=torch.float32, device=device)
         capi.call("tsp_synth_weights", capi.TYPE_F32, seed * 8 + 6, 0, channels, sigma, self.shared_router.data_ptr(), st)
         self.gguf = dict(gate=g, up=u, down=d, shared_gate=sg, shared_up=su, shared_down=sd) if keep_gguf or layout == formats.GGUF else None
@@ -234,21 +240,27 @@ class SynthDeviceLayer:
             pd = u8(n * pb)
             pack(d, channels, hidden, n, pd, 0, pb)
             down = matrix_set(pd, expert_type, layout, channels, hidden, n)
-            psg, psu, psd = u8(pb), u8(pb), u8(pb)
-            pack(sg, hidden, channels, 1, psg, 0, pb)
-            pack(su, hidden, channels, 1, psu, 0, pb)
-            pack(sd, channels, hidden, 1, psd, 0, pb)
-            self.tensors += [pd, psg, psu, psd]
-            shared = [matrix_set(psg, expert_type, layout, hidden, channels), matrix_set(psu, expert_type, layout, hidden, channels),
-                      matrix_set(psd, expert_type, layout, channels, hidden)]
+            self.tensors.append(pd)
+            if self.shared_type != expert_type:   # raw blocks of the other encoding, as generated
+                shared = [matrix_set(sg, self.shared_type, formats.GGUF, hidden, channels), matrix_set(su, self.shared_type, formats.GGUF, hidden, channels),
+                          matrix_set(sd, self.shared_type, formats.GGUF, channels, hidden)]
+                self.tensors += [sg, su, sd]
+            else:
+                psg, psu, psd = u8(pb), u8(pb), u8(pb)
+                pack(sg, hidden, channels, 1, psg, 0, pb)
+                pack(su, hidden, channels, 1, psu, 0, pb)
+                pack(sd, channels, hidden, 1, psd, 0, pb)
+                self.tensors += [psg, psu, psd]
+                shared = [matrix_set(psg, expert_type, layout, hidden, channels), matrix_set(psu, expert_type, layout, hidden, channels),
+                          matrix_set(psd, expert_type, layout, channels, hidden)]
             torch.cuda.synchronize()
             if not keep_gguf:
                 del g, u, d, sg, su, sd
         else:
             gate, up = matrix_set(g, expert_type, layout, hidden, channels, n), matrix_set(u, expert_type, layout, hidden, channels, n)
             down = matrix_set(d, expert_type, layout, channels, hidden, n)
-            shared = [matrix_set(sg, expert_type, layout, hidden, channels), matrix_set(su, expert_type, layout, hidden, channels),
-                      matrix_set(sd, expert_type, layout, channels, hidden)]
+            shared = [matrix_set(sg, self.shared_type, layout, hidden, channels), matrix_set(su, self.shared_type, layout, hidden, channels),
+                      matrix_set(sd, self.shared_type, layout, channels, hidden)]
         self.weights = MoeWeights(gate, up, down, shared[0], shared[1], shared[2], self.shared_router.data_ptr())
 
     def host_layer(self, selected: int) -> HostLayer:
@@ -256,7 +268,7 @@ class SynthDeviceLayer:
         assert self.gguf is not None
         h = {k: v.cpu().numpy() for k, v in self.gguf.items()}
         n = self.experts_local
-        return HostLayer(self.channels, self.hidden, n, selected, self.type, self.type, h["gate"].reshape(n, -1), h["up"].reshape(n, -1),
+        return HostLayer(self.channels, self.hidden, n, selected, self.type, self.shared_type, h["gate"].reshape(n, -1), h["up"].reshape(n, -1),
                          h["down"].reshape(n, -1), h["shared_gate"], h["shared_up"], h["shared_down"], self.shared_router.cpu().numpy())
 
 

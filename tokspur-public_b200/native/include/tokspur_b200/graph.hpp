@@ -39,6 +39,9 @@ struct PlanarMatrixShape {
     uint32_t columns = 0, rows = 0, experts = 0;
 };
 enum class RouterMode : uint32_t { softmax, sigmoid };
+// Registered identity of a weight tensor on the prefill path (native/include/tokspur/moe_mm_many.hpp:7-10): raw GGUF blocks or
+// a registered Pack v3 planar matrix.
+enum class PrefillWeightLayout : uint32_t { gguf = 0, planar = 1 };
 struct BatchResult { uint64_t dispatches = 0; double wall_ms = 0, gpu_ms = 0; };
 
 class CudaGraph {
@@ -78,6 +81,13 @@ public:
     // `width` token-major input rows of `columns` values, output rows of `rows` values, both densely packed (q8_many.cpp:20-29)
     void q8_matvec_many(GpuView matrix, GpuView input, GpuView output, uint32_t columns, uint32_t rows, uint32_t width);
     void verify_nax_dense_q8(GpuView matrix, GpuRowsF32 input, GpuRowsF32 output);
+    // Dense Q8_0 projection of a prefill-size row batch on the tensor cores (graph.hpp:859-860, 767): binary16 operands, FP32
+    // accumulate, FP32 rows out. prepare_dense_mm_q8 (between batches) sizes the staging of the binary16 input rows; the encode
+    // call never allocates. `reuse_staged` skips the conversion when the previous dense_mm_q8 staged the same input rows.
+    // Matrix: raw Q8_0 blocks [rows x columns], rows a multiple of 128, columns of 256.
+    void prepare_dense_mm_q8(PrefillWeightLayout layout, uint32_t max_rows, uint32_t max_columns);
+    void dense_mm_q8(PrefillWeightLayout layout, GpuView matrix, GpuRowsF32 input, GpuRowsF32 output, bool reuse_staged = false);
+    [[nodiscard]] static uint32_t dense_mm_q8_dispatches(bool reuse_staged = false) { return reuse_staged ? 1u : 2u; }
     // Batched routing and mixture (graph.hpp:852-853): `tokens` rows of `experts` logits; expert outputs [tokens*selected x channels]
     void prefill_route_batch(GpuView logits, GpuView indices, GpuView weights, uint32_t experts, uint32_t selected, uint32_t tokens,
                              RouterMode mode, bool normalize_selected);
@@ -131,6 +141,9 @@ private:
     void *ev0_ = nullptr, *ev1_ = nullptr;
     bool in_batch_ = false, frozen_ = false, margin_audit_ = false;
     float margin_epsilon_ = 1.0e-4f;
+    void* dense_staging_ = nullptr;       // binary16 input rows of dense_mm_q8 in tile K order, then 256 item-counter words
+    uint64_t dense_staging_rows_ = 0, dense_staging_cols_ = 0;
+    uint32_t dense_counter_ = 0;          // next unused counter word
     float* margins_ = nullptr;            // per-row top-k margins of the last moe_route_rows (2048 rows, as the reference's scratch)
     tsp_router_margin_telemetry margin_telemetry_{};
     tsp_matrix_set dense_set(uint32_t encoding, GpuView matrix, uint32_t columns, uint32_t rows) const;

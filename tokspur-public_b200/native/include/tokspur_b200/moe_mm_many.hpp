@@ -16,7 +16,6 @@ namespace tokspur_b200 {
 // moe_mm_many.cpp:236-259). The declared identity must be the tensor's real one (a registered planar matrix declared `gguf`, or
 // the reverse, is refused), gate and up share one identity, and nothing is repacked behind the caller's back. A shared expert in
 // the routed experts' encoding and identity rides in their launches; otherwise it costs one more launch per projection.
-enum class PrefillWeightLayout : uint32_t { gguf = 0, planar = 1 };
 struct MoeMmLayouts {
     PrefillWeightLayout gate = PrefillWeightLayout::planar, up = PrefillWeightLayout::planar, down = PrefillWeightLayout::planar;
     PrefillWeightLayout shared_gate = PrefillWeightLayout::planar, shared_up = PrefillWeightLayout::planar, shared_down = PrefillWeightLayout::planar;

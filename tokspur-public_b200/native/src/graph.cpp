@@ -35,6 +35,7 @@ CudaGraph::~CudaGraph() {
     for (auto& b : buffers_) if (b.live) cudaFree(b.ptr);
     cudaFree(error_);
     if (margins_) cudaFree(margins_);
+    if (dense_staging_) cudaFree(dense_staging_);
     cudaEventDestroy(static_cast<cudaEvent_t>(ev0_));
     cudaEventDestroy(static_cast<cudaEvent_t>(ev1_));
     cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
@@ -242,6 +243,50 @@ void CudaGraph::q8_matvec_many(GpuView matrix, GpuView input, GpuView output, ui
 void CudaGraph::verify_nax_dense_q8(GpuView matrix, GpuRowsF32 input, GpuRowsF32 output) {
     if (input.rows < 1 || input.rows > 16) throw FormatError("verify batch must hold 1..16 rows");
     gemv_rows(TSP_TYPE_Q8_0, matrix, input, output);
+}
+
+// ---- dense Q8_0 row batches on the tensor cores (dense_mm_q8, graph.mm:5009-5100) -------------------------------------------
+namespace { constexpr uint32_t kDenseCounters = 256; }
+
+void CudaGraph::prepare_dense_mm_q8(PrefillWeightLayout layout, uint32_t max_rows, uint32_t max_columns) {
+    require_idle();
+    select_device();
+    if (layout != PrefillWeightLayout::gguf) throw FormatError("dense Q8_0 GEMM reads raw GGUF blocks only");
+    if (!max_rows || !max_columns || max_columns % 256) throw FormatError("dense Q8_0 GEMM staging shape");
+    if (dense_staging_ && dense_staging_rows_ * dense_staging_cols_ >= uint64_t(max_rows) * max_columns) return;
+    if (dense_staging_) { cuda(cudaFree(dense_staging_), "dense staging"); dense_staging_ = nullptr; }
+    const uint64_t bytes = uint64_t(max_rows) * max_columns * 2 + kDenseCounters * 4;
+    cuda(cudaMalloc(&dense_staging_, bytes), "dense staging");
+    cuda(cudaMemset(dense_staging_, 0, bytes), "dense staging");
+    dense_staging_rows_ = max_rows; dense_staging_cols_ = max_columns; dense_counter_ = 0;
+}
+
+void CudaGraph::dense_mm_q8(PrefillWeightLayout layout, GpuView matrix, GpuRowsF32 input, GpuRowsF32 output, bool reuse_staged) {
+    require_batch();
+    if (layout != PrefillWeightLayout::gguf || planar_matrix_shape(matrix)) throw FormatError("dense Q8_0 GEMM reads raw GGUF blocks only");
+    if (!input.rows || input.rows != output.rows || !input.columns || input.columns % 256 || !output.columns || output.columns % 128 ||
+        input.stride_bytes < uint64_t(input.columns) * 4 || input.stride_bytes % 16 || output.stride_bytes < uint64_t(output.columns) * 4 || output.stride_bytes % 16 ||
+        input.view.bytes < uint64_t(input.rows - 1) * input.stride_bytes + uint64_t(input.columns) * 4 ||
+        output.view.bytes < uint64_t(output.rows - 1) * output.stride_bytes + uint64_t(output.columns) * 4)
+        throw FormatError("dense Q8_0 GEMM shape mismatch");
+    if (!dense_staging_ || uint64_t(input.rows) * input.columns > dense_staging_rows_ * dense_staging_cols_)
+        throw FormatError("dense Q8_0 GEMM: call prepare_dense_mm_q8() between batches with at least this many rows and columns");
+    const uint64_t bytes = tsp_expert_bytes(TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF, output.columns, input.columns);
+    if (!bytes || matrix.bytes != bytes) throw FormatError("dense Q8_0 GEMM matrix extent");
+    const tsp_matrix_set set{device_pointer(matrix), nullptr, bytes, 1, 1, output.columns, input.columns, TSP_TYPE_Q8_0, TSP_LAYOUT_GGUF};
+    const uint64_t xk_stride = uint64_t(input.columns) * 2;
+    auto* counters = reinterpret_cast<uint32_t*>(static_cast<char*>(dense_staging_) + dense_staging_rows_ * dense_staging_cols_ * 2);
+    if (dense_counter_ == kDenseCounters) {   // every word has been used once: clear them in stream order
+        cuda(cudaMemsetAsync(counters, 0, kDenseCounters * 4, static_cast<cudaStream_t>(stream_)), "dense counters");
+        dense_counter_ = 0;
+    }
+    if (!reuse_staged) {
+        check(tsp_moe_rows_f16k(device_pointer(input.view), input.stride_bytes, 0, input.rows, input.columns, dense_staging_, xk_stride, error_, stream_));
+        ++dispatches_;
+    }
+    check(tsp_dense_mm(&set, dense_staging_, xk_stride, input.rows, static_cast<float*>(device_pointer(output.view, true)), output.stride_bytes,
+                       counters + dense_counter_++, error_, stream_));
+    ++dispatches_;
 }
 
 // ---- batched routing, mixture, router projection with the margin audit -----------------------------------------------------

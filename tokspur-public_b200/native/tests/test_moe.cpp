@@ -357,6 +357,47 @@ void operators(CudaGraph& g, uint32_t seed) {
             g.abort();
         }
     }
+    {   // dense Q8_0 row batch on the tensor cores: 300 strided rows, twice (the second call reuses the staged input rows)
+        const uint32_t DC = 512, DR = 256, DT = 300;
+        const auto m = generated(8, DC, DR, 1, seed + 21);
+        const auto mv = g.upload(bytes(m), "dense q8 matrix");
+        std::vector<float> x(size_t(DT) * DC);
+        uint32_t rng = seed * 31u + 9u;
+        for (auto& v : x) { rng = rng * 1664525u + 1013904223u; v = float(int(rng % 1025) - 512) / 64.f; }   // exact in binary16
+        const uint64_t in_stride = uint64_t(DC) * 4 + 16, out_stride = uint64_t(DR) * 4 + 32;
+        std::vector<uint8_t> staged(in_stride * DT, 0);
+        for (uint32_t r = 0; r < DT; ++r) std::memcpy(staged.data() + r * in_stride, x.data() + size_t(r) * DC, size_t(DC) * 4);
+        const auto in = g.upload(bytes(staged), "dense q8 in"), out = g.zeros(out_stride * DT, "dense q8 out");
+        refuses([&] { g.begin(); try { g.dense_mm_q8(PrefillWeightLayout::gguf, mv, {in, DT, DC, in_stride}, {out, DT, DR, out_stride}); } catch (...) { g.abort(); throw; } },
+                "dense Q8_0 GEMM ran without prepared staging");
+        g.prepare_dense_mm_q8(PrefillWeightLayout::gguf, DT, DC);
+        std::vector<double> expected(size_t(DR) * DT);
+        for (uint32_t t = 0; t < DT; ++t) require(tso_gemv_f32(8, m.data(), m.size(), DC, DR, x.data() + size_t(t) * DC, expected.data() + size_t(t) * DR) == TSO_OK, "oracle gemv");
+        for (int run = 0; run < 2; ++run) {
+            g.begin();
+            g.dense_mm_q8(PrefillWeightLayout::gguf, mv, {in, DT, DC, in_stride}, {out, DT, DR, out_stride}, run == 1);
+            const auto batch = g.submit();
+            require(batch.dispatches == CudaGraph::dense_mm_q8_dispatches(run == 1), "dense Q8_0 GEMM dispatch count");
+            const auto raw = g.read(out);
+            double num = 0, den = 0;
+            for (uint32_t t = 0; t < DT; ++t)
+                for (uint32_t r = 0; r < DR; ++r) {
+                    float v;
+                    std::memcpy(&v, raw.data() + t * out_stride + size_t(r) * 4, 4);
+                    const double e = expected[size_t(t) * DR + r];
+                    num += (v - e) * (v - e); den += e * e;
+                }
+            const double rel = std::sqrt(num / den);
+            std::cout << "  dense_mm_q8 " << DT << " rows: relative L2 error " << rel << "\n";
+            require(rel <= 2e-3, "dense Q8_0 GEMM relative L2 tolerance exceeded");
+        }
+        g.begin();
+        refuses([&] { g.dense_mm_q8(PrefillWeightLayout::planar, mv, {in, DT, DC, in_stride}, {out, DT, DR, out_stride}); }, "planar identity accepted by the dense Q8_0 GEMM");
+        refuses([&] { g.dense_mm_q8(PrefillWeightLayout::gguf, mv, {in, DT, DC, in_stride}, {out, DT, DR - 128, out_stride}); }, "matrix extent mismatch accepted");
+        refuses([&] { g.dense_mm_q8(PrefillWeightLayout::gguf, mv, {in, DT + 1, DC, in_stride}, {out, DT + 1, DR, out_stride}); }, "rows beyond the views accepted");
+        g.abort();
+        g.release(mv); g.release(in); g.release(out);
+    }
     // router projection -> audited routing -> mixture
     const auto router = activations(seed + 7, size_t(E) * C, 0.25f), srouter = activations(seed + 8, C, 0.125f);
     const auto x = activations(seed + 9, size_t(C) * T, 1.f);

@@ -43,8 +43,10 @@ extern "C" {
 
 /* GGUF tensor type ids (gguf.cpp:21-32). */
 #define TSP_TYPE_F32 0u
+#define TSP_TYPE_Q5_1 7u   /* decode-size kernels only, GGUF layout (the reference model's down tensors) */
 #define TSP_TYPE_Q8_0 8u
 #define TSP_TYPE_Q4_K 12u
+#define TSP_TYPE_Q5_K 13u  /* decode-size kernels only, GGUF layout (some of the reference model's gate / up tensors) */
 
 /* Weight byte layouts. */
 #define TSP_LAYOUT_GGUF 0u    /* GGUF array-of-blocks rows (144 B / 256 weights Q4_K, 34 B / 32 weights Q8_0) */
@@ -68,7 +70,7 @@ typedef struct tsp_matrix_set {
     uint32_t split;          /* first expert id stored under base_hi; == experts when unused */
     uint32_t experts;
     uint32_t rows, cols;
-    uint32_t type;           /* TSP_TYPE_Q4_K or TSP_TYPE_Q8_0 */
+    uint32_t type;           /* TSP_TYPE_Q4_K or TSP_TYPE_Q8_0; TSP_TYPE_Q5_K / TSP_TYPE_Q5_1 on the decode-size entries */
     uint32_t layout;         /* TSP_LAYOUT_* */
 } tsp_matrix_set;
 

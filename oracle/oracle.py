@@ -41,7 +41,8 @@ class _Layer(C.Structure):
     _fields_ = [("channels", C.c_uint32), ("hidden", C.c_uint32), ("experts", C.c_uint32), ("selected", C.c_uint32),
                 ("expert_type", C.c_uint32), ("shared_type", C.c_uint32),
                 ("gate", u8p), ("up", u8p), ("down", u8p), ("shared_gate", u8p), ("shared_up", u8p), ("shared_down", u8p),
-                ("shared_router", f32p), ("router", f32p), ("mode", C.c_uint32), ("normalize_selected", C.c_int)]
+                ("shared_router", f32p), ("router", f32p), ("mode", C.c_uint32), ("normalize_selected", C.c_int),
+                ("down_type", C.c_uint32)]
 
 
 class _Stages(C.Structure):
@@ -259,7 +260,7 @@ class Oracle:
 
     # ---- whole layer ----
     def moe_layer(self, layer: dict, x: np.ndarray, logits: np.ndarray | None, threads: int = 1, stages: bool = False):
-        """layer: dict with channels, hidden, experts, selected, expert_type, shared_type, gate, up, down,
+        """layer: dict with channels, hidden, experts, selected, expert_type, shared_type (and optionally down_type), gate, up, down,
         shared_gate, shared_up, shared_down (uint8 arrays, GGUF layout), shared_router (f32 or None),
         router (f32 or None), mode, normalize. Returns out [T,C] float64 (and a dict of stages)."""
         keep = []
@@ -279,7 +280,7 @@ class Oracle:
         Ls = _Layer(layer["channels"], layer["hidden"], layer["experts"], layer["selected"],
                     layer["expert_type"], layer["shared_type"], b("gate"), b("up"), b("down"),
                     b("shared_gate"), b("shared_up"), b("shared_down"), fl("shared_router"), fl("router"),
-                    layer.get("mode", 0), int(layer.get("normalize", True)))
+                    layer.get("mode", 0), int(layer.get("normalize", True)), int(layer.get("down_type") or 0))
         x = np.ascontiguousarray(x, dtype=np.float32)
         T, Cn = x.shape
         lg = np.ascontiguousarray(logits, dtype=np.float32) if logits is not None else None

@@ -90,6 +90,7 @@ struct RefLayer {
     const float* router;
     uint32_t mode;
     int normalize_selected;
+    uint32_t down_type;   // 0: expert_type
 };
 
 int ref_moe_layer(const RefLayer* L, const float* x, const float* logits, uint32_t tokens, double* out,
@@ -99,6 +100,8 @@ int ref_moe_layer(const RefLayer* L, const float* x, const float* logits, uint32
     std::vector<int> rcs(threads, 0);
     const uint32_t C = L->channels, H = L->hidden, E = L->experts, K = L->selected;
     const size_t eb = tensor_bytes(L->expert_type, uint64_t(C) * H), sb = tensor_bytes(L->shared_type, uint64_t(C) * H);
+    const uint32_t down_type = L->down_type ? L->down_type : L->expert_type;
+    const size_t db = tensor_bytes(down_type, uint64_t(C) * H);
     auto work = [&](uint32_t id) {
         rcs[id] = guarded([&] {
             for (uint32_t t = uint64_t(tokens) * id / threads; t < uint64_t(tokens) * (id + 1) / threads; ++t) {
@@ -111,7 +114,7 @@ int ref_moe_layer(const RefLayer* L, const float* x, const float* logits, uint32
                     auto g = reference_gemv_doubleinput(L->expert_type, bytes(L->gate + size_t(e) * eb, eb), C, H, xd);
                     const auto u = reference_gemv_doubleinput(L->expert_type, bytes(L->up + size_t(e) * eb, eb), C, H, xd);
                     for (size_t i = 0; i < g.size(); ++i) g[i] = stable_silu(g[i]) * u[i];
-                    const auto d = reference_gemv_doubleinput(L->expert_type, bytes(L->down + size_t(e) * eb, eb), H, C, g);
+                    const auto d = reference_gemv_doubleinput(down_type, bytes(L->down + size_t(e) * db, db), H, C, g);
                     routed.insert(routed.end(), d.begin(), d.end());
                 }
                 auto sg = reference_gemv_doubleinput(L->shared_type, bytes(L->shared_gate, sb), C, H, xd);

@@ -24,8 +24,10 @@ int tso_block_geometry(uint32_t type, uint32_t* epb, uint32_t* bpb) {
         case 0: e = 1; b = 4; break;
         case 1: e = 1; b = 2; break;
         case 30: e = 1; b = 2; break;
+        case 7: e = 32; b = 24; break;
         case 8: e = 32; b = 34; break;
         case 12: e = 256; b = 144; break;
+        case 13: e = 256; b = 176; break;
         default: return TSO_E_TYPE;
     }
     if (epb) *epb = e;
@@ -62,9 +64,16 @@ double tso_value(uint32_t type, const uint8_t* block, uint32_t index) {
         case 0: return bits_f32(rd32(block));
         case 1: return tso_binary16(rd16(block));
         case 30: return bits_f32((uint32_t)rd16(block) << 16);
+        case 7: {   /* Q5_1: d, m, 32 fifth bits, 16 bytes of nibbles (numeric.cpp:38-42) */
+            const uint32_t low = (block[8 + index % 16] >> (4 * (index / 16))) & 15u;
+            const uint32_t high = (rd32(block + 4) >> index) & 1u;
+            return (double)tso_binary16(rd16(block)) * (low | (high << 4)) + tso_binary16(rd16(block + 2));
+        }
         case 8: return (double)tso_binary16(rd16(block)) * (int8_t)block[2 + index];
-        case 12: {
-            const uint32_t q = (block[16 + (index / 64) * 32 + index % 32] >> (4 * ((index % 64) / 32))) & 15u;
+        case 12: case 13: {   /* Q5_K: the Q4_K header, 32 bytes of fifth bits, then the nibbles (numeric.cpp:44-50) */
+            const uint32_t low_offset = type == 12 ? 16u : 48u;
+            uint32_t q = (block[low_offset + (index / 64) * 32 + index % 32] >> (4 * ((index % 64) / 32))) & 15u;
+            if (type == 13) q |= ((block[16 + index % 32] >> (index / 32)) & 1u) << 4;
             return (double)tso_binary16(rd16(block)) * k_group_factor(block, index / 32, 0) * q -
                    (double)tso_binary16(rd16(block + 2)) * k_group_factor(block, index / 32, 1);
         }
@@ -546,6 +555,8 @@ static void* layer_worker(void* arg) {
     const tso_layer* L = j->L;
     const uint32_t C = L->channels, H = L->hidden, E = L->experts, K = L->selected;
     const size_t gu_bytes = tensor_bytes(L->expert_type, (uint64_t)C * H);
+    const uint32_t down_type = L->down_type ? L->down_type : L->expert_type;
+    const size_t dn_bytes = tensor_bytes(down_type, (uint64_t)C * H);
     const size_t sgu_bytes = tensor_bytes(L->shared_type, (uint64_t)C * H);
     double* xd = (double*)malloc(sizeof(double) * C);
     double* lg = (double*)malloc(sizeof(double) * E);
@@ -568,7 +579,7 @@ static void* layer_worker(void* arg) {
             if (rc) break;
             for (uint32_t i = 0; i < H; ++i) g[i] = tso_silu(g[i]) * u[i];
             if (j->st && j->st->activated) memcpy(j->st->activated + ((size_t)t * K + r) * H, g, sizeof(double) * H);
-            rc = tso_gemv_f64(L->expert_type, L->down + (size_t)e * gu_bytes, gu_bytes, H, C, g, routed + (size_t)r * C);
+            rc = tso_gemv_f64(down_type, L->down + (size_t)e * dn_bytes, dn_bytes, H, C, g, routed + (size_t)r * C);
         }
         if (!rc) rc = tso_gemv_f64(L->shared_type, L->shared_gate, sgu_bytes, C, H, xd, g);
         if (!rc) rc = tso_gemv_f64(L->shared_type, L->shared_up, sgu_bytes, C, H, xd, u);

@@ -31,7 +31,7 @@ enum {
     TSO_E_RANGE = -4,     /* index or factor out of range */
 };
 
-/* GGUF type ids handled here: 0 F32, 1 F16, 8 Q8_0, 12 Q4_K, 30 BF16. */
+/* GGUF type ids handled here: 0 F32, 1 F16, 7 Q5_1, 8 Q8_0, 12 Q4_K, 13 Q5_K, 30 BF16. */
 int tso_block_geometry(uint32_t type, uint32_t* elements_per_block, uint32_t* bytes_per_block);
 
 /* binary16 -> binary32, all 65536 patterns (numeric.cpp:81-91). */
@@ -118,7 +118,7 @@ int tso_grouped_tasks(const uint32_t* counts, uint32_t tokens, uint32_t experts,
 /* ---- one whole MoE FFN layer, composed as ffn_check.cpp:104-139 ---- */
 typedef struct {
     uint32_t channels, hidden, experts, selected;
-    uint32_t expert_type;           /* encoding of gate/up/down expert tensors (12 or 8) */
+    uint32_t expert_type;           /* encoding of gate/up/down expert tensors (12, 13, 8 or 7) */
     uint32_t shared_type;           /* encoding of the shared expert tensors */
     const uint8_t* gate;            /* [experts][hidden x channels] GGUF bytes, expert-major */
     const uint8_t* up;
@@ -130,6 +130,7 @@ typedef struct {
     const float* router;            /* F32 [experts x channels] or NULL when logits are supplied */
     uint32_t mode;                  /* 0 softmax, 1 sigmoid */
     int normalize_selected;
+    uint32_t down_type;             /* encoding of the down expert tensors when it differs from gate/up (0: expert_type) */
 } tso_layer;
 
 typedef struct {

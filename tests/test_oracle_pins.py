@@ -45,6 +45,45 @@ def _q4k_fixture_block():
     return block, expected
 
 
+def _q5k_fixture_block():
+    # native/tests/test_numeric.cpp:81-103 for type 13: the Q4_K header, 32 bytes of fifth bits (bit g of byte lane), nibbles at 48
+    block = np.zeros(176, dtype=np.uint8)
+    block[0:2] = [0x00, 0x30]
+    block[2:4] = [0x00, 0x34]
+    expected = np.zeros(256, dtype=np.float32)
+    for group in range(8):
+        scale, minimum = (group * 11 + 3) % 64, (group * 7 + 5) % 64
+        for bit in range(6):
+            scale_byte = 4 + group if group < 4 else (8 + group if bit < 4 else group)
+            min_byte = 8 + group if group < 4 else (8 + group if bit < 4 else 4 + group)
+            scale_bit = bit if (group < 4 or bit < 4) else bit + 2
+            min_bit = bit if group < 4 else (bit + 4 if bit < 4 else bit + 2)
+            block[scale_byte] |= ((scale >> bit) & 1) << scale_bit
+            block[min_byte] |= ((minimum >> bit) & 1) << min_bit
+        for lane in range(32):
+            code = (lane * 3 + group * 5) % 32
+            block[48 + (group // 2) * 32 + lane] |= (code % 16) << ((group % 2) * 4)
+            block[16 + lane] |= (code // 16) << group
+            expected[group * 32 + lane] = np.float32(0.125) * scale * code - np.float32(0.25) * minimum
+    return block, expected
+
+
+def _q51_fixture_block():
+    # native/tests/test_numeric.cpp:62-73: d = 0.5, m = -2, code = (13 i + 7) % 32, fifth bits in the word at byte 4
+    block = np.zeros(24, dtype=np.uint8)
+    block[0:2] = [0x00, 0x38]
+    block[2:4] = [0x00, 0xc0]
+    expected = np.zeros(32, dtype=np.float32)
+    high = 0
+    for i in range(32):
+        code = (i * 13 + 7) % 32
+        high |= (code // 16) << i
+        block[8 + i % 16] |= (code % 16) << ((i // 16) * 4)
+        expected[i] = 0.5 * code - 2
+    block[4:8] = np.frombuffer(int(high).to_bytes(4, "little"), dtype=np.uint8)
+    return block, expected
+
+
 def _q8_fixture_block():
     block = np.zeros(34, dtype=np.uint8)
     block[0:2] = [0x00, 0x34]  # 0.25
@@ -56,7 +95,7 @@ def _q8_fixture_block():
     return block, expected
 
 
-@pytest.mark.parametrize("type_,maker", [(12, _q4k_fixture_block), (8, _q8_fixture_block)])
+@pytest.mark.parametrize("type_,maker", [(12, _q4k_fixture_block), (8, _q8_fixture_block), (13, _q5k_fixture_block), (7, _q51_fixture_block)])
 def test_format_fixture_blocks(oracle, type_, maker):
     block, expected = maker()
     got = oracle.dequantize(type_, block, expected.size)
@@ -223,7 +262,7 @@ def test_permutation_tables(oracle):
 
 # ---- the restatement against the reference's own compiled sources, on random inputs ----
 
-@pytest.mark.parametrize("type_", [8, 12])
+@pytest.mark.parametrize("type_", [8, 12, 13, 7])
 def test_port_equals_reference_decode_and_gemv(oracle, ref_oracle, type_):
     cols, rows = 512, 24
     w = fixtures.lcg_weights(type_, cols, rows, 1)[0]

@@ -14,6 +14,7 @@ from . import build as _build
 LIB_PATH = _build.LIB
 
 TYPE_F32, TYPE_Q8_0, TYPE_Q4_K = 0, 8, 12
+TYPE_Q5_1, TYPE_Q5_K = 7, 13
 LAYOUT_GGUF, LAYOUT_PLANAR = 0, 1
 ROUTER_SOFTMAX, ROUTER_SIGMOID = 0, 1
 ERR_NONFINITE, ERR_INDEX, ERR_TIMEOUT = 2, 4, 8

@@ -62,16 +62,19 @@ int launch_residual_read(const float*, const float*, const float*, uint32_t, uin
 int launch_residual_write(const float*, const float*, const float*, uint32_t, uint32_t, uint32_t, float*, uint32_t*, cudaStream_t);
 int launch_gemv_f32(const float*, uint32_t, uint32_t, const float*, const float*, uint64_t, uint32_t, float*, uint64_t, float*, uint32_t*, cudaStream_t);
 int launch_synth(uint32_t, uint64_t, uint64_t, uint64_t, float, void*, cudaStream_t);
+int launch_dequant_k5(uint32_t, const uint8_t*, uint64_t, float*, uint32_t*, cudaStream_t);
 int launch_pack_planar(uint32_t, const void*, uint64_t, void*, uint64_t, uint64_t, uint32_t, cudaStream_t);
 
 static int check_matrix(const tsp_matrix_set* m, const char* name) {
     TSP_REQUIRE(m != nullptr, "%s: null matrix set", name);
-    if (m->type != TSP_TYPE_Q4_K && m->type != TSP_TYPE_Q8_0) return fail(TSP_E_TYPE, "%s: encoding %u has no kernel", name, m->type);
+    const bool five = m->type == TSP_TYPE_Q5_K || m->type == TSP_TYPE_Q5_1;
+    if (m->type != TSP_TYPE_Q4_K && m->type != TSP_TYPE_Q8_0 && !five) return fail(TSP_E_TYPE, "%s: encoding %u has no kernel", name, m->type);
     if (m->layout != TSP_LAYOUT_GGUF && m->layout != TSP_LAYOUT_PLANAR) return fail(TSP_E_TYPE, "%s: unknown layout %u", name, m->layout);
+    if (five && m->layout != TSP_LAYOUT_GGUF) return fail(TSP_E_TYPE, "%s: the five-bit encodings are read as plain GGUF rows only", name);
     TSP_REQUIRE(m->base && aligned16(m->base), "%s: base must be a 16-byte aligned device pointer", name);
     TSP_REQUIRE(m->experts >= 1 && m->experts <= 4096, "%s: experts out of range", name);
     TSP_REQUIRE(m->rows >= 8 && m->rows % 8 == 0 && m->rows <= 1u << 20, "%s: rows must be a multiple of 8", name);
-    const uint32_t block = m->type == TSP_TYPE_Q4_K ? 256u : 32u;
+    const uint32_t block = (m->type == TSP_TYPE_Q4_K || m->type == TSP_TYPE_Q5_K) ? 256u : 32u;
     TSP_REQUIRE(m->cols >= block && m->cols % block == 0 && m->cols <= 65536, "%s: columns must be a multiple of %u", name, block);
     const uint64_t bytes = tsp_expert_bytes(m->type, m->layout, m->rows, m->cols);
     TSP_REQUIRE(bytes != 0, "%s: shape not representable in this layout", name);
@@ -145,6 +148,9 @@ uint64_t tsp_expert_bytes(uint32_t type, uint32_t layout, uint32_t rows, uint32_
         if (layout == TSP_LAYOUT_PLANAR && (rows % 4 || blocks % 8)) return 0;
         return blocks * 34u;
     }
+    if (layout != TSP_LAYOUT_GGUF) return 0;
+    if (type == TSP_TYPE_Q5_K) return cols % 256 ? 0 : static_cast<uint64_t>(rows) * (cols / 256) * 176u;
+    if (type == TSP_TYPE_Q5_1) return cols % 32 ? 0 : static_cast<uint64_t>(rows) * (cols / 32) * 24u;
     return 0;
 }
 
@@ -154,6 +160,9 @@ int tsp_dequant_f32(const tsp_matrix_set* m, uint32_t expert, float* d_out, uint
     TSP_REQUIRE(d_out, "dequant: null output");
     const uint8_t* base = static_cast<const uint8_t*>(expert < m->split ? m->base : m->base_hi);
     const uint32_t local = expert < m->split ? expert : expert - m->split;
+    if (m->type == TSP_TYPE_Q5_K || m->type == TSP_TYPE_Q5_1)
+        return launch_dequant_k5(m->type, base + local * m->expert_stride, static_cast<uint64_t>(m->rows) * m->cols, d_out, d_error,
+                                 static_cast<cudaStream_t>(stream));
     const uint64_t blocks = static_cast<uint64_t>(m->rows) * (m->cols / (m->type == TSP_TYPE_Q4_K ? 256 : 32));
     TSP_REQUIRE(blocks < (1ull << 31), "dequant: matrix too large");
     return launch_dequant(m->type, m->layout, base + local * m->expert_stride, blocks, d_out, d_error, static_cast<cudaStream_t>(stream));

@@ -622,6 +622,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
     }
 }
 
+int launch_gemv_k5(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*, uint64_t, uint32_t, uint32_t, const uint32_t*, const uint32_t*,
+                   const uint32_t*, float*, uint64_t, int, uint32_t*, cudaStream_t);
 int launch_gemv_q4k_tma(const tsp_matrix_set*, const tsp_matrix_set*, bool, const float*, uint64_t, uint32_t, uint32_t, const uint32_t*,
                         const uint32_t*, const uint32_t*, float*, uint64_t, int, int, uint32_t*, cudaStream_t, const GemvShared*);
 
@@ -652,6 +654,8 @@ int launch_gemv(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup, c
                 float* out, uint64_t out_stride_bytes, int f16_exact, int nc, uint32_t* error, cudaStream_t st, const GemvShared* shared) {
     // `shared` (an extra dense expert in the same launch) is served by the second-generation pipeline only: return 1 = not done
     if (shared && a->type != TSP_TYPE_Q4_K) return 1;
+    if (a->type == TSP_TYPE_Q5_K || a->type == TSP_TYPE_Q5_1)   // the reference model's five-bit encodings: their own plain kernel
+        return launch_gemv_k5(a, b, gateup, x, x_stride_bytes, in_div, tokens, token_map, counts, tasks, out, out_stride_bytes, nc, error, st);
     if (a->type == TSP_TYPE_Q4_K) {   // the second-generation pipeline covers Q4_K; shapes it declines (return 1) fall through
         const int rc = launch_gemv_q4k_tma(a, b, gateup, x, x_stride_bytes, in_div, tokens, token_map, counts, tasks, out,
                                            out_stride_bytes, f16_exact, nc, error, st, shared);

@@ -11,12 +11,13 @@ from __future__ import annotations
 import numpy as np
 
 Q8_0, Q4_K = 8, 12
+Q5_1, Q5_K = 7, 13   # the reference model's down / gate-up encodings beside Q4_K and Q8_0 (decode-size kernels, GGUF rows)
 GGUF, PLANAR = 0, 1
 
 
 def block_geometry(type_: int) -> tuple[int, int]:
     """(elements per block, bytes per block) of a GGUF encoding."""
-    return {Q8_0: (32, 34), Q4_K: (256, 144)}[type_]
+    return {Q8_0: (32, 34), Q4_K: (256, 144), Q5_1: (32, 24), Q5_K: (256, 176)}[type_]
 
 
 def gguf_bytes(type_: int, rows: int, cols: int) -> int:
@@ -83,8 +84,67 @@ def quantize_q4_k(w: np.ndarray) -> np.ndarray:
     return out.reshape(rows, -1)
 
 
+def quantize_q5_k(w: np.ndarray) -> np.ndarray:
+    """[rows, cols] float32 -> uint8 [rows, cols/256*176]: the Q4_K scheme with 32 levels. Block: d, dmin, the twelve factor
+    bytes, 32 bytes of fifth bits (bit g of byte i = weight i of group g), 128 bytes of low nibbles (numeric.cpp:44-50)."""
+    rows, cols = w.shape
+    nb = cols // 256
+    x = w.reshape(rows, nb, 8, 32).astype(np.float32)
+    lo = np.minimum(x.min(axis=3), 0)
+    hi = x.max(axis=3)
+    min_g = -lo
+    scale_g = (hi + min_g) / 31.0
+    d = (scale_g.max(axis=2) / 63.0).astype(np.float16)
+    dmin = (min_g.max(axis=2) / 63.0).astype(np.float16)
+    df, mf = d.astype(np.float32), dmin.astype(np.float32)
+    sc = np.where(df[..., None] > 0, np.rint(scale_g / np.where(df > 0, df, 1)[..., None]), 0)
+    mn = np.where(mf[..., None] > 0, np.rint(min_g / np.where(mf > 0, mf, 1)[..., None]), 0)
+    sc = np.clip(sc, 0, 63).astype(np.uint8)
+    mn = np.clip(mn, 0, 63).astype(np.uint8)
+    dl = df[..., None] * sc
+    ml = mf[..., None] * mn
+    q = np.where(dl[..., None] > 0, np.rint((x + ml[..., None]) / np.where(dl > 0, dl, 1)[..., None]), 0)
+    q = np.clip(q, 0, 31).astype(np.uint8)
+    out = np.zeros((rows, nb, 176), dtype=np.uint8)
+    out[..., 0:2] = d.view(np.uint8).reshape(rows, nb, 2)
+    out[..., 2:4] = dmin.view(np.uint8).reshape(rows, nb, 2)
+    out[..., 4:8] = sc[..., 0:4] | ((sc[..., 4:8] >> 4) << 6)
+    out[..., 8:12] = mn[..., 0:4] | ((mn[..., 4:8] >> 4) << 6)
+    out[..., 12:16] = (sc[..., 4:8] & 15) | ((mn[..., 4:8] & 15) << 4)
+    high = np.zeros((rows, nb, 32), dtype=np.uint8)
+    for g in range(8):
+        high |= (q[:, :, g, :] >> 4) << g
+    out[..., 16:48] = high
+    qp = (q & 15).reshape(rows, nb, 4, 2, 32)
+    out[..., 48:] = (qp[:, :, :, 0, :] | (qp[:, :, :, 1, :] << 4)).reshape(rows, nb, 128)
+    return out.reshape(rows, -1)
+
+
+def quantize_q5_1(w: np.ndarray) -> np.ndarray:
+    """[rows, cols] float32 -> uint8 [rows, cols/32*24]: d = (max - min)/31 and m = min as binary16, q = round((w - m)/d);
+    block: d, m, 32 fifth bits (bit i = weight i), 16 bytes of nibbles (weight i in nibble i/16 of byte i%16; numeric.cpp:38-42)."""
+    rows, cols = w.shape
+    nb = cols // 32
+    x = w.reshape(rows, nb, 32).astype(np.float32)
+    mn, mx = x.min(axis=2), x.max(axis=2)
+    d = ((mx - mn) / 31.0).astype(np.float16)
+    m = mn.astype(np.float16)
+    df, mf = d.astype(np.float32), m.astype(np.float32)
+    q = np.where(df[..., None] > 0, np.rint((x - mf[..., None]) / np.where(df > 0, df, 1)[..., None]), 0)
+    q = np.clip(q, 0, 31).astype(np.uint32)
+    out = np.zeros((rows, nb, 24), dtype=np.uint8)
+    out[..., 0:2] = d.view(np.uint8).reshape(rows, nb, 2)
+    out[..., 2:4] = m.view(np.uint8).reshape(rows, nb, 2)
+    high = np.zeros((rows, nb), dtype=np.uint32)
+    for i in range(32):
+        high |= (q[..., i] >> 4) << np.uint32(i)
+    out[..., 4:8] = high.view(np.uint8).reshape(rows, nb, 4)
+    out[..., 8:24] = ((q[..., 0:16] & 15) | ((q[..., 16:32] & 15) << 4)).astype(np.uint8)
+    return out.reshape(rows, -1)
+
+
 def quantize(type_: int, w: np.ndarray) -> np.ndarray:
-    return quantize_q4_k(w) if type_ == Q4_K else quantize_q8_0(w)
+    return {Q4_K: quantize_q4_k, Q8_0: quantize_q8_0, Q5_K: quantize_q5_k, Q5_1: quantize_q5_1}[type_](w)
 
 
 # --------------------------------------------------------------------------------------------

@@ -50,11 +50,11 @@ class HostLayer:
     down_type: int | None = None  # defaults to expert_type
 
     def oracle_dict(self, mode: int = 0, normalize: bool = True) -> dict:
-        assert self.down_type in (None, self.expert_type), "the oracle layer takes one expert encoding"
         return dict(channels=self.channels, hidden=self.hidden, experts=self.experts, selected=self.selected,
                     expert_type=self.expert_type, shared_type=self.shared_type, gate=self.gate, up=self.up, down=self.down,
                     shared_gate=self.shared_gate, shared_up=self.shared_up, shared_down=self.shared_down,
-                    shared_router=self.shared_router, router=None, mode=mode, normalize=normalize)
+                    shared_router=self.shared_router, router=None, mode=mode, normalize=normalize,
+                    down_type=self.down_type if self.down_type not in (None, self.expert_type) else 0)
 
 
 def synth_host_layer(seed: int, channels: int, hidden: int, experts: int, selected: int, expert_type: int = formats.Q4_K,

@@ -38,18 +38,20 @@ void close(const std::vector<float>& actual, const double* expected, size_t n, d
 }
 // the reference's "bounded nonzero quant domain" generator (native/tests/test_moe_mm_many_gpu.cpp:30-47), Q4_K and Q8_0
 std::vector<uint8_t> generated(uint32_t type, uint32_t k, uint32_t r, uint32_t e, uint32_t seed) {
-    const uint32_t epb = type == 8 ? 32 : 256, bpb = type == 8 ? 34 : 144;
+    // Q5_1 (7): d, m, fifth bits, nibbles; Q5_K (13): the Q4_K header, 32 bytes of fifth bits, 128 bytes of nibbles
+    const uint32_t epb = (type == 8 || type == 7) ? 32 : 256, bpb = type == 8 ? 34 : type == 7 ? 24 : type == 13 ? 176 : 144;
     std::vector<uint8_t> raw(uint64_t(k / epb) * bpb * r * e);
     uint32_t rng = seed;
     for (size_t at = 0; at < raw.size(); at += bpb) {
         for (uint32_t i = 0; i < bpb; ++i) { rng = rng * 1664525u + 1013904223u; raw[at + i] = uint8_t(rng >> 24); }
         raw[at] = 1; raw[at + 1] = 0x0c;
         if (type == 8) { for (unsigned i = 0; i < 32; ++i) { rng = rng * 1664525u + 1013904223u; raw[at + 2 + i] = uint8_t(int(rng % 31) - 15); } }
+        else if (type == 7) { raw[at + 2] = 1; raw[at + 3] = 0x84; }   // m = -0x0401: the 32 codes centre near zero
         else {
             raw[at + 2] = 1; raw[at + 3] = 4;
             for (unsigned i = 0; i < 8; ++i) raw[at + 4 + i] = 1;
             for (unsigned i = 8; i < 12; ++i) raw[at + 4 + i] = 0x11;
-            for (unsigned i = 0; i < 128; ++i) raw[at + 16 + i] &= 0x77;
+            if (type == 12) for (unsigned i = 0; i < 128; ++i) raw[at + 16 + i] &= 0x77;
         }
     }
     return raw;
@@ -72,15 +74,17 @@ std::vector<uint8_t> planar(uint32_t type, const std::vector<uint8_t>& gguf, uin
     return out;
 }
 
-void layer(CudaGraph& g, uint32_t type, bool use_planar, MoeShape shape, uint32_t seed) {
+// down_type / shared_type 0: the encoding of gate and up
+void layer(CudaGraph& g, uint32_t type, bool use_planar, MoeShape shape, uint32_t seed, uint32_t down_type = 0, uint32_t shared_type = 0) {
     const uint32_t C = shape.channels, H = shape.hidden, E = shape.experts, K = shape.selected;
-    const auto gate = generated(type, C, H, E, seed + 1), up = generated(type, C, H, E, seed + 2), down = generated(type, H, C, E, seed + 3);
-    const auto sgate = generated(type, C, H, 1, seed + 4), sup = generated(type, C, H, 1, seed + 5), sdown = generated(type, H, C, 1, seed + 6);
+    const uint32_t dt = down_type ? down_type : type, st = shared_type ? shared_type : type;
+    const auto gate = generated(type, C, H, E, seed + 1), up = generated(type, C, H, E, seed + 2), down = generated(dt, H, C, E, seed + 3);
+    const auto sgate = generated(st, C, H, 1, seed + 4), sup = generated(st, C, H, 1, seed + 5), sdown = generated(st, H, C, 1, seed + 6);
     const auto router = activations(seed + 7, size_t(E) * C, 0.25f), srouter = activations(seed + 8, C, 0.125f);
     MoeWeights w{};
     w.router = {g.upload(bytes_of(router), "router"), 0};
     w.shared_router = {g.upload(bytes_of(srouter), "shared router"), 0};
-    w.shared_gate = {g.upload(bytes(sgate), "sg"), type}; w.shared_up = {g.upload(bytes(sup), "su"), type}; w.shared_down = {g.upload(bytes(sdown), "sd"), type};
+    w.shared_gate = {g.upload(bytes(sgate), "sg"), st}; w.shared_up = {g.upload(bytes(sup), "su"), st}; w.shared_down = {g.upload(bytes(sdown), "sd"), st};
     if (use_planar) {
         // co-located pairs: lo = experts [0, E/2) as [gate_e, up_e], hi = the rest (planar_pack_v3.cpp:1076-1093)
         const auto pg = planar(type, gate, C, H, E), pu = planar(type, up, C, H, E);
@@ -100,14 +104,14 @@ void layer(CudaGraph& g, uint32_t type, bool use_planar, MoeShape shape, uint32_
         g.register_planar_matrix(w.down.view, {type, dk, H, C, E});
         require(is_planar_moe(g, w, shape), "registered pairs are recognised as a planar MoE");
     } else {
-        w.gate = {g.upload(bytes(gate), "gate"), type}; w.up = {g.upload(bytes(up), "up"), type}; w.down = {g.upload(bytes(down), "down"), type};
+        w.gate = {g.upload(bytes(gate), "gate"), type}; w.up = {g.upload(bytes(up), "up"), type}; w.down = {g.upload(bytes(down), "down"), dt};
         require(!is_planar_moe(g, w, shape), "raw GGUF tensors are not planar");
     }
     const auto scratch = allocate_moe_scratch(g, shape);
     const auto input = g.zeros(C * 4, "input"), output = g.zeros(C * 4, "output");
     const auto allocations = g.allocations();
 
-    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1};
+    tso_layer L{C, H, E, K, type, st, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1, dt};
     for (uint32_t token = 0; token < 3; ++token) {
         const auto x = activations(100 + token + seed, C, 8.f);
         std::vector<double> expected(C), ew(K), act(size_t(K) * H), routed(size_t(K) * C), sact(H), sout(C);
@@ -165,7 +169,7 @@ void verify_rows(CudaGraph& g, uint32_t type, MoeShape shape, uint32_t steps, ui
     const auto input = g.zeros(uint64_t(C) * 4 * steps, "rows in"), output = g.zeros(uint64_t(C) * 4 * steps, "rows out");
     const auto x = activations(900 + seed, size_t(C) * steps, 8.f);
     g.write(input, bytes_of(x));
-    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1};
+    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1, 0};
     std::vector<double> expected(size_t(C) * steps), ew(size_t(K) * steps);
     std::vector<uint32_t> eids(size_t(K) * steps);
     tso_layer_stages st{eids.data(), ew.data(), nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -240,7 +244,7 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
     std::vector<uint8_t> staged(in_stride * rows, 0);
     for (uint32_t r = 0; r < rows; ++r) std::memcpy(staged.data() + r * in_stride, x.data() + size_t(r) * C, size_t(C) * 4);
     g.write(input, bytes(staged));
-    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1};
+    tso_layer L{C, H, E, K, type, type, gate.data(), up.data(), down.data(), sgate.data(), sup.data(), sdown.data(), srouter.data(), router.data(), 0, 1, 0};
     std::vector<double> expected(size_t(rows) * C);
     require(tso_moe_layer(&L, x.data(), nullptr, rows, expected.data(), nullptr, 4) == TSO_OK, "oracle layer");
     prepare_moe_mm_many(g, w, shape);
@@ -296,7 +300,7 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
         mixed.shared_gate = mixed.shared_up = mixed.shared_down = PrefillWeightLayout::gguf;
         prepare_moe_mm_many(g, m, shape, mixed);
         refuses([&] { prepare_moe_mm_many(g, m, shape); }, "raw Q8_0 shared tensors declared planar were accepted");
-        tso_layer LQ{C, H, E, K, type, 8, gate.data(), up.data(), down.data(), q8g.data(), q8u.data(), q8d.data(), srouter.data(), router.data(), 0, 1};
+        tso_layer LQ{C, H, E, K, type, 8, gate.data(), up.data(), down.data(), q8g.data(), q8u.data(), q8d.data(), srouter.data(), router.data(), 0, 1, 0};
         std::vector<double> want(size_t(rows) * C);
         require(tso_moe_layer(&LQ, x.data(), nullptr, rows, want.data(), nullptr, 4) == TSO_OK, "oracle layer (Q8_0 shared)");
         const auto before = g.allocations();
@@ -512,13 +516,15 @@ int main() {
         return 1;
     }
     // planar registration is frozen after the first batch of a graph, so every weight form gets its own graph
-    const struct { uint32_t type; bool planar; MoeShape shape; } cases[] = {
-        {12, false, {256, 256, 8, 4}}, {8, true, {256, 64, 8, 4}}, {8, false, {64, 64, 6, 3}}, {12, true, {512, 256, 16, 10}}};
+    // the last case is the reference model's pairing: Q5_K gate / up, Q5_1 down, Q8_0 shared expert (raw GGUF rows)
+    const struct { uint32_t type; bool planar; MoeShape shape; uint32_t down = 0, shared = 0; } cases[] = {
+        {12, false, {256, 256, 8, 4}}, {8, true, {256, 64, 8, 4}}, {8, false, {64, 64, 6, 3}}, {12, true, {512, 256, 16, 10}},
+        {13, false, {512, 256, 8, 4}, 7, 8}};
     uint32_t seed = 50;
     for (const auto& c : cases) {
         try {
             CudaGraph g(0, uint64_t(2) << 30);
-            layer(g, c.type, c.planar, c.shape, seed += 10);
+            layer(g, c.type, c.planar, c.shape, seed += 10, c.down, c.shared);
         } catch (const std::exception& e) {
             std::cerr << "MoE check failed (type " << c.type << ", planar " << c.planar << ") after " << checks << " checks: " << e.what() << '\n';
             return 1;

@@ -10,6 +10,7 @@
 #include "tokspur/routing.hpp"
 
 #include <cstring>
+#include <string>
 #include <thread>
 #include <vector>
 
@@ -155,6 +156,27 @@ int ref_residual_write(const double* streams, const double* output, const double
         const auto r = residual_write_reference({streams, branches * channels}, {output, channels}, {scales, branches});
         std::memcpy(out, r.data(), sizeof(double) * r.size());
     });
+}
+
+// The reference's own GGUF parser on borrowed file bytes (gguf.hpp:97, gguf.cpp): the tensor directory and the pack metadata as
+// text lines, for checking this build's container reader and test writer. Line 1: alignment, version, architecture, recipe,
+// data offset, manifest length; then one line per tensor: name|type|absolute offset|bytes|dimensions.
+long ref_gguf_describe(const uint8_t* file, size_t nbytes, char* out, size_t cap) {
+    std::string text;
+    const int rc = guarded([&] {
+        const Gguf g(bytes(file, nbytes));
+        text = std::to_string(g.unsigned_value("general.alignment")) + "|" + std::to_string(g.unsigned_value("tokspur_pack.version")) + "|" +
+               std::string(g.string_value("general.architecture")) + "|" + std::string(g.string_value("tokspur_pack.recipe")) + "|" +
+               std::to_string(g.data_offset()) + "|" + std::to_string(g.string_value("tokspur_pack.manifest").size()) + "\n";
+        for (const auto& t : g.tensors()) {
+            text += t.name + "|" + std::to_string(t.type) + "|" + std::to_string(t.offset) + "|" + std::to_string(t.bytes) + "|";
+            for (size_t i = 0; i < t.dimensions.size(); ++i) text += (i ? "," : "") + std::to_string(t.dimensions[i]);
+            text += "\n";
+        }
+    });
+    if (rc) return rc;
+    if (out && cap) { const size_t n = text.size() < cap - 1 ? text.size() : cap - 1; std::memcpy(out, text.data(), n); out[n] = 0; }
+    return long(text.size());
 }
 
 } // extern "C"

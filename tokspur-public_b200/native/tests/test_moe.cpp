@@ -1,16 +1,22 @@
 // encode_moe and encode_moe_mm_many on the CUDA graph against the CPU oracle, in the style of the reference's native/tests/test_moe.cpp:
 // generated weights, route ids bit-equal, every stage within 5e-5 scaled error, refusals before encoding, sticky-error
 // recovery, allocation invariants. The oracle (oracle/tsp_oracle.h) is test infrastructure and is linked only here.
+#include <unistd.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <filesystem>
 #include <functional>
 #include <iostream>
+#include <stdexcept>
 #include <vector>
 
 #include "tokspur_b200/moe.hpp"
 #include "tokspur_b200/moe_mm_many.hpp"
+#include "tokspur_b200/pack_v3.hpp"
 #include "tsp_oracle.h"
+#include "pack_v3_writer.hpp"
 
 using namespace tokspur_b200;
 namespace {
@@ -332,6 +338,56 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
     g.abort();
     release_moe_mm_many_scratch(g, scratch);
 }
+// One layer read from a "tokspur-pack-v3" container (written here with the test-side writer in the reference's layouts: co-located
+// planar Q4_K gate / up pairs, planar Q8_0 down, lane-packed dense Q8_0 shared expert, plain F32 routers) and run through
+// encode_moe and encode_moe_many against the oracle on the source GGUF bytes.
+void pack_layer(uint32_t seed) {
+    namespace fs = std::filesystem;
+    const uint32_t C = 256, H = 64, E = 8, K = 4;
+    pack_v3_test::LayerBytes L{C, H, E, 12, generated(12, C, H, E, seed + 1), generated(12, C, H, E, seed + 2), generated(8, H, C, E, seed + 3),
+                               generated(8, C, H, 1, seed + 4), generated(8, C, H, 1, seed + 5), generated(8, H, C, 1, seed + 6),
+                               activations(seed + 7, size_t(E) * C, 0.25f), activations(seed + 8, C, 0.125f)};
+    const fs::path dir = fs::temp_directory_path() / ("tokspur_b200_pack_layer_" + std::to_string(::getpid()));
+    fs::create_directories(dir);
+    const fs::path path = dir / "layer.gguf";
+    pack_v3_test::write(path, pack_v3_test::layer_entries(L, "blk.3."));
+    const PackIndexV3 index = read_pack_v3_index(path);
+    CudaGraph g(0, uint64_t(1) << 30);
+    MoeShape shape{0, 0, 0, K};
+    const MoeWeights w = load_pack_v3_moe_layer(g, path, index, "blk.3.", shape);
+    fs::remove_all(dir);
+    require(shape.channels == C && shape.hidden == H && shape.experts == E && shape.selected == K, "layer shape from the pack directory");
+    require(is_planar_moe(g, w, shape) && w.shared_gate.encoding == 8 && !g.planar_matrix_shape(w.shared_gate.view), "registered forms of the pack tensors");
+    refuses([&] { MoeShape s2{}; (void)load_pack_v3_moe_layer(g, path, index, "blk.4.", s2); }, "a layer that is not in the pack was loaded");
+
+    tso_layer O{C, H, E, K, 12, 8, L.gate.data(), L.up.data(), L.down.data(), L.sgate.data(), L.sup.data(), L.sdown.data(), L.srouter.data(), L.router.data(), 0, 1, 8};
+    const auto scratch = allocate_moe_scratch(g, shape);
+    const auto input = g.zeros(C * 4, "input"), output = g.zeros(C * 4, "output");
+    for (uint32_t token = 0; token < 3; ++token) {
+        const auto x = activations(300 + token + seed, C, 8.f);
+        std::vector<double> expected(C);
+        require(tso_moe_layer(&O, x.data(), nullptr, 1, expected.data(), nullptr, 1) == TSO_OK, "oracle layer");
+        g.write(input, bytes_of(x));
+        g.begin();
+        encode_moe(g, w, scratch, input, output, shape, RouterMode::softmax, true);
+        (void)g.submit();
+        close(read<float>(g, output), expected.data(), C);
+    }
+    const uint32_t rows = 9;
+    const auto many = allocate_moe_many_scratch(g, shape, rows);
+    const auto xin = activations(400 + seed, size_t(rows) * C, 4.f);
+    const auto in = g.zeros(uint64_t(rows) * C * 4, "rows in"), out = g.zeros(uint64_t(rows) * C * 4, "rows out");
+    g.write(in, bytes_of(xin));
+    std::vector<double> expected(size_t(rows) * C);
+    require(tso_moe_layer(&O, xin.data(), nullptr, rows, expected.data(), nullptr, 4) == TSO_OK, "oracle layer rows");
+    g.begin();
+    encode_moe_many(g, w, many, in, out, shape, RouterMode::softmax, true, rows);
+    (void)g.submit();
+    close(read<float>(g, out), expected.data(), expected.size());
+    release_moe_many_scratch(g, many);
+    release_moe_scratch(g, scratch);
+    std::cout << "  layer loaded from a pack v3 container: encode_moe and encode_moe_many agree with the oracle\n";
+}
 // The stand-alone operators of the graph (dense GEMV forms, batched routing with the margin audit, mixture, residual read / write)
 // against the oracle's functions.
 void operators(CudaGraph& g, uint32_t seed) {
@@ -540,6 +596,7 @@ int main() {
         many(g2, {512, 256, 8, 2}, 200, 256, 400); // one chunk, tiles of more than 32 routes
         CudaGraph g3(0, uint64_t(1) << 30);
         operators(g3, 500);
+        pack_layer(600);
     } catch (const std::exception& e) {
         std::cerr << "tiled MoE check failed after " << checks << " checks: " << e.what() << '\n';
         return 1;

@@ -25,6 +25,9 @@ void release_moe_scratch(CudaGraph& graph, const MoeScratch& scratch);
 
 // True when gate/up are registered co-located planar pairs and down a registered planar set of matching shape (moe.hpp:22-35).
 [[nodiscard]] bool is_planar_moe(const CudaGraph& g, const MoeWeights& w, MoeShape s);
+// The gate / up half of that test alone: the "gate" tensor holds experts [0, E/2) as [gate_e, up_e] pairs, the "up" tensor the rest.
+// The encoders address such pairs whatever form the down tensor has (a pack's planar Q8_0 down may be kept as raw rows).
+[[nodiscard]] bool is_planar_gate_up(const CudaGraph& g, const MoeWeights& w, MoeShape s);
 
 // One token row: F32 router projection, top-k, routed gate-up + SwiGLU and down, shared expert, gated mixture.
 // Neither allocates, reads back nor commits; `input`/`output` are FP32 rows of `channels` values.

@@ -41,9 +41,10 @@ MoeMmManyBytes moe_mm_many_bytes(MoeShape shape, uint32_t capacity);
 MoeMmManyScratch allocate_moe_mm_many_scratch(CudaGraph& graph, MoeShape shape, uint32_t capacity);
 void release_moe_mm_many_scratch(CudaGraph& graph, const MoeMmManyScratch& scratch);
 
-// Encode only. The caller owns allocation, the batch and the committed state. Expert tensors must be Q4_K in the declared layouts
-// (planar: is_planar_moe; gguf: raw blocks of the layer's extent), the shared expert Q4_K in either layout or raw Q8_0 blocks;
-// anything else is refused before the first launch.
+// Encode only. The caller owns allocation, the batch and the committed state. Gate / up expert tensors must be Q4_K in the declared
+// layout (planar: the co-located pair tensors; gguf: raw blocks of the layer's extent), the down experts Q4_K in either layout or
+// raw Q8_0 blocks (the reference model's down encoding), the shared expert Q4_K in either layout or raw Q8_0 blocks; anything
+// else is refused before the first launch.
 void encode_moe_mm_many(CudaGraph& graph, const MoeWeights& weights, const MoeMmManyScratch& scratch, GpuRowsF32 input, GpuRowsF32 output,
                         MoeShape shape, RouterMode mode, bool normalize_selected, MoeMmLayouts layouts = {});
 // The weight checks of the encoder, run between batches (prepare_moe_mm_many, moe_mm_many.hpp:59): a tensor of the wrong form or

@@ -62,7 +62,10 @@ struct PackIndexV3 {
 // tensors are registered as planar matrices, lane-packed dense Q8_0 matrices are unpacked to GGUF rows on the device, plain
 // tensors are taken as they are. The shape is read from the directory. Layouts without a kernel here (the Q5_K / Q5_1 planes)
 // are refused. Returns the weights and fills `shape` (selected is left to the caller).
+// q8_down_as_rows: a planar Q8_0 down tensor is re-laid as raw GGUF blocks on the host while loading (lossless) instead of being
+// registered as a planar matrix: the prefill encoder (encode_moe_mm_many) reads Q8_0 experts as raw blocks only.
+struct PackLoadOptions { bool q8_down_as_rows = false; };
 MoeWeights load_pack_v3_moe_layer(CudaGraph& graph, const std::filesystem::path& path, const PackIndexV3& index, std::string_view prefix,
-                                  MoeShape& shape);
+                                  MoeShape& shape, PackLoadOptions options = {});
 
 }  // namespace tokspur_b200

@@ -50,14 +50,18 @@ void release_moe_scratch(CudaGraph& graph, const MoeScratch& scratch) {
     for (const auto view : scratch.views()) graph.release(view);
 }
 
+bool is_planar_gate_up(const CudaGraph& g, const MoeWeights& w, MoeShape s) {
+    const auto lo = g.planar_matrix_shape(w.gate.view), hi = g.planar_matrix_shape(w.up.view);
+    if (!lo || !hi) return false;
+    return (lo->kind == 2u || lo->kind == 6u) && (hi->kind == 3u || hi->kind == 7u) && lo->source_type == w.gate.encoding &&
+           hi->source_type == w.up.encoding && lo->source_type == hi->source_type && lo->columns == s.channels && lo->rows == s.hidden &&
+           lo->experts == s.experts && hi->columns == s.channels && hi->rows == s.hidden && hi->experts == s.experts;
+}
+
 bool is_planar_moe(const CudaGraph& g, const MoeWeights& w, MoeShape s) {
-    const auto lo = g.planar_matrix_shape(w.gate.view), hi = g.planar_matrix_shape(w.up.view), dn = g.planar_matrix_shape(w.down.view);
-    if (!lo || !hi || !dn) return false;
-    return (lo->kind == 2u || lo->kind == 6u) && (hi->kind == 3u || hi->kind == 7u) && (dn->kind == 9u || dn->kind == 10u) &&
-           lo->source_type == w.gate.encoding && hi->source_type == w.up.encoding && dn->source_type == w.down.encoding &&
-           lo->source_type == hi->source_type && lo->columns == s.channels && lo->rows == s.hidden && lo->experts == s.experts &&
-           hi->columns == s.channels && hi->rows == s.hidden && hi->experts == s.experts && dn->columns == s.hidden &&
-           dn->rows == s.channels && dn->experts == s.experts;
+    const auto dn = g.planar_matrix_shape(w.down.view);
+    return is_planar_gate_up(g, w, s) && dn && (dn->kind == 9u || dn->kind == 10u) && dn->source_type == w.down.encoding &&
+           dn->columns == s.hidden && dn->rows == s.channels && dn->experts == s.experts;
 }
 
 namespace {
@@ -81,7 +85,7 @@ void prepare_moe_many(CudaGraph& g, const MoeWeights& w, MoeShape shape) {
     if (w.router.encoding != 0 || w.shared_router.encoding != 0) throw FormatError("router projections must be F32");
     if (w.router.view.bytes != uint64_t(shape.channels) * shape.experts * 4 || w.shared_router.view.bytes != uint64_t(shape.channels) * 4)
         throw FormatError("router shape mismatch");
-    if (!is_planar_moe(g, w, shape)) {
+    if (!is_planar_gate_up(g, w, shape)) {
         (void)matrix_set(g, w.gate, shape.hidden, shape.channels, shape.experts);
         (void)matrix_set(g, w.up, shape.hidden, shape.channels, shape.experts);
     }
@@ -116,7 +120,7 @@ void encode_rows(CudaGraph& g, const MoeWeights& w, const MoeScratch& s, GpuView
     if (input.bytes != uint64_t(shape.channels) * 4 * rows || output.bytes != uint64_t(shape.channels) * 4 * rows) throw FormatError("mixture shape mismatch");
     if (w.router.encoding != 0 || w.shared_router.encoding != 0) throw FormatError("router projections must be F32");
     tsp_moe_weights tw{};
-    if (is_planar_moe(g, w, shape)) {
+    if (is_planar_gate_up(g, w, shape)) {
         // co-located pairs: the "gate" tensor holds experts [0, E/2) as [gate_e, up_e], the "up" tensor experts [E/2, E)
         const uint64_t pb = tsp_expert_bytes(w.gate.encoding, TSP_LAYOUT_PLANAR, shape.hidden, shape.channels);
         const auto lo = static_cast<const char*>(g.device_pointer(w.gate.view)), hi = static_cast<const char*>(g.device_pointer(w.up.view));

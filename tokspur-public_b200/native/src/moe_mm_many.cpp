@@ -58,8 +58,9 @@ tsp_moe_weights checked_weights(const CudaGraph& g, const MoeWeights& w, MoeShap
     need(w.router.encoding == 0 && w.shared_router.encoding == 0, "router projections must be F32");
     need(w.router.view.bytes == uint64_t(shape.channels) * shape.experts * 4 && w.shared_router.view.bytes == uint64_t(shape.channels) * 4,
          "router shape mismatch");
-    need(w.gate.encoding == TSP_TYPE_Q4_K && w.up.encoding == TSP_TYPE_Q4_K && w.down.encoding == TSP_TYPE_Q4_K,
-         "tiled MoE reads Q4_K expert tensors only");
+    need(w.gate.encoding == TSP_TYPE_Q4_K && w.up.encoding == TSP_TYPE_Q4_K, "tiled MoE reads Q4_K gate / up expert tensors only");
+    need(w.down.encoding == TSP_TYPE_Q4_K || (w.down.encoding == TSP_TYPE_Q8_0 && l.down == PrefillWeightLayout::gguf),
+         "tiled MoE down experts: Q4_K (planar or raw blocks) or raw Q8_0 blocks");
     need(w.shared_gate.encoding == w.shared_up.encoding, "tiled MoE: shared gate and up must share an encoding");
     for (const auto& [m, layout] : {std::pair{w.shared_gate, l.shared_gate}, std::pair{w.shared_up, l.shared_up}, std::pair{w.shared_down, l.shared_down}})
         need(m.encoding == TSP_TYPE_Q4_K || (m.encoding == TSP_TYPE_Q8_0 && layout == PrefillWeightLayout::gguf),
@@ -77,7 +78,7 @@ tsp_moe_weights checked_weights(const CudaGraph& g, const MoeWeights& w, MoeShap
     tsp_moe_weights tw{};
     if (l.gate == PrefillWeightLayout::planar) {
         // co-located pairs: the "gate" tensor holds experts [0, E/2) as [gate_e, up_e], the "up" tensor experts [E/2, E)
-        need(is_planar_moe(g, w, shape), "tiled MoE needs the registered planar expert tensors");
+        need(is_planar_gate_up(g, w, shape), "tiled MoE needs the registered co-located gate / up pair tensors");
         const uint64_t pb = tsp_expert_bytes(TSP_TYPE_Q4_K, TSP_LAYOUT_PLANAR, shape.hidden, shape.channels);
         need(pb && shape.experts % 2 == 0, "tiled MoE weight extent");
         const auto lo = static_cast<const char*>(g.device_pointer(w.gate.view)), hi = static_cast<const char*>(g.device_pointer(w.up.view));

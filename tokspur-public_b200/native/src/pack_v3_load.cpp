@@ -3,6 +3,8 @@
 // registered weights.
 #include <cuda_runtime.h>
 
+#include <cstring>
+
 #include "tokspur_b200/moe.hpp"
 #include "tokspur_b200/pack_v3.hpp"
 
@@ -38,7 +40,24 @@ GpuMatrix dense(CudaGraph& g, const std::filesystem::path& path, const PackIndex
 }
 }  // namespace
 
-MoeWeights load_pack_v3_moe_layer(CudaGraph& g, const std::filesystem::path& path, const PackIndexV3& index, std::string_view prefix, MoeShape& shape) {
+namespace {
+// planar Q8_0 experts (per expert: 32-byte code blocks, then the binary16 scales; planar_pack_v3.cpp:611-616) -> GGUF blocks
+std::vector<std::byte> q8_planar_to_rows(const std::vector<std::byte>& planar, uint64_t blocks_per_expert, uint64_t experts) {
+    std::vector<std::byte> out(planar.size());
+    for (uint64_t e = 0; e < experts; ++e) {
+        const std::byte* src = planar.data() + e * blocks_per_expert * 34;
+        std::byte* dst = out.data() + e * blocks_per_expert * 34;
+        for (uint64_t b = 0; b < blocks_per_expert; ++b) {
+            std::memcpy(dst + b * 34, src + blocks_per_expert * 32 + b * 2, 2);
+            std::memcpy(dst + b * 34 + 2, src + b * 32, 32);
+        }
+    }
+    return out;
+}
+}  // namespace
+
+MoeWeights load_pack_v3_moe_layer(CudaGraph& g, const std::filesystem::path& path, const PackIndexV3& index, std::string_view prefix, MoeShape& shape,
+                                  PackLoadOptions options) {
     const std::string p(prefix);
     const auto& gate = index.at(p + "ffn_gate_exps.weight");
     const auto& up = index.at(p + "ffn_up_exps.weight");
@@ -73,7 +92,11 @@ MoeWeights load_pack_v3_moe_layer(CudaGraph& g, const std::filesystem::path& pat
         w.gate = {upload_tensor(g, path, index, gate), gate.source_type};
         w.up = {upload_tensor(g, path, index, up), up.source_type};
     }
-    if (down.kind == PlanarKind::q8_planar_v3) {
+    if (down.kind == PlanarKind::q8_planar_v3 && options.q8_down_as_rows) {
+        need(H % 32 == 0 && down.bytes == C * (H / 32) * 34 * E, "pack v3: planar Q8_0 down extent");
+        const auto rows = q8_planar_to_rows(read_pack_v3_tensor(path, index, down), C * (H / 32), E);
+        w.down = {g.upload(rows, down.name + " (rows)", true), down.source_type};
+    } else if (down.kind == PlanarKind::q8_planar_v3) {
         w.down = {upload_tensor(g, path, index, down), down.source_type};
         g.register_planar_matrix(w.down.view, {down.source_type, uint32_t(down.kind), uint32_t(H), uint32_t(C), uint32_t(E)});
     } else {

@@ -343,7 +343,7 @@ void many(CudaGraph& g, MoeShape shape, uint32_t rows, uint32_t capacity, uint32
 // encode_moe and encode_moe_many against the oracle on the source GGUF bytes.
 void pack_layer(uint32_t seed) {
     namespace fs = std::filesystem;
-    const uint32_t C = 256, H = 64, E = 8, K = 4;
+    const uint32_t C = 256, H = 256, E = 8, K = 4;
     pack_v3_test::LayerBytes L{C, H, E, 12, generated(12, C, H, E, seed + 1), generated(12, C, H, E, seed + 2), generated(8, H, C, E, seed + 3),
                                generated(8, C, H, 1, seed + 4), generated(8, C, H, 1, seed + 5), generated(8, H, C, 1, seed + 6),
                                activations(seed + 7, size_t(E) * C, 0.25f), activations(seed + 8, C, 0.125f)};
@@ -355,7 +355,6 @@ void pack_layer(uint32_t seed) {
     CudaGraph g(0, uint64_t(1) << 30);
     MoeShape shape{0, 0, 0, K};
     const MoeWeights w = load_pack_v3_moe_layer(g, path, index, "blk.3.", shape);
-    fs::remove_all(dir);
     require(shape.channels == C && shape.hidden == H && shape.experts == E && shape.selected == K, "layer shape from the pack directory");
     require(is_planar_moe(g, w, shape) && w.shared_gate.encoding == 8 && !g.planar_matrix_shape(w.shared_gate.view), "registered forms of the pack tensors");
     refuses([&] { MoeShape s2{}; (void)load_pack_v3_moe_layer(g, path, index, "blk.4.", s2); }, "a layer that is not in the pack was loaded");
@@ -387,6 +386,42 @@ void pack_layer(uint32_t seed) {
     release_moe_many_scratch(g, many);
     release_moe_scratch(g, scratch);
     std::cout << "  layer loaded from a pack v3 container: encode_moe and encode_moe_many agree with the oracle\n";
+    {   // the same layer for the prefill encoder: the planar Q8_0 down tensor re-laid as raw blocks while loading
+        CudaGraph gp(0, uint64_t(1) << 30);
+        MoeShape sp{0, 0, 0, K};
+        const MoeWeights wp = load_pack_v3_moe_layer(gp, path, index, "blk.3.", sp, {true});
+        require(is_planar_gate_up(gp, wp, sp) && !is_planar_moe(gp, wp, sp) && !gp.planar_matrix_shape(wp.down.view), "forms of the tensors loaded for prefill");
+        MoeMmLayouts lay;   // gate / up: the registered pairs; down and the shared expert: raw Q8_0 blocks
+        lay.down = lay.shared_gate = lay.shared_up = lay.shared_down = PrefillWeightLayout::gguf;
+        prepare_moe_mm_many(gp, wp, sp, lay);
+        const uint32_t n = 70, capacity = 64;
+        const auto ps = allocate_moe_mm_many_scratch(gp, sp, capacity);
+        std::vector<float> xr(size_t(n) * C);
+        uint32_t rng = seed * 13u + 1u;
+        for (auto& v : xr) { rng = rng * 1664525u + 1013904223u; v = float(int(rng % 1025) - 512) / 64.f; }
+        const auto pin = gp.zeros(uint64_t(n) * C * 4, "prefill in"), pout = gp.zeros(uint64_t(n) * C * 4, "prefill out");
+        gp.write(pin, bytes_of(xr));
+        std::vector<double> want(size_t(n) * C);
+        require(tso_moe_layer(&O, xr.data(), nullptr, n, want.data(), nullptr, 4) == TSO_OK, "oracle layer (prefill rows)");
+        gp.begin();
+        encode_moe_mm_many(gp, wp, ps, {pin, n, C, uint64_t(C) * 4}, {pout, n, C, uint64_t(C) * 4}, sp, RouterMode::softmax, true, lay);
+        (void)gp.submit();
+        const auto got = read<float>(gp, pout);
+        double num = 0, den = 0;
+        for (size_t i = 0; i < got.size(); ++i) { require(std::isfinite(got[i]), "non-finite row value"); num += (got[i] - want[i]) * (got[i] - want[i]); den += want[i] * want[i]; }
+        const double rel = std::sqrt(num / den);
+        std::cout << "  pack layer through encode_moe_mm_many (Q4_K pairs, Q8_0 down rows, Q8_0 shared): relative L2 error " << rel << "\n";
+        require(rel <= 2e-3, "pack layer prefill tolerance exceeded");
+        // one decode row through the same weights (pairs + raw Q8_0 down)
+        const auto s1 = allocate_moe_scratch(gp, sp);
+        const auto i1 = gp.zeros(C * 4, "in"), o1 = gp.zeros(C * 4, "out");
+        gp.write(i1, std::span<const std::byte>(reinterpret_cast<const std::byte*>(xr.data()), size_t(C) * 4));
+        gp.begin();
+        encode_moe(gp, wp, s1, i1, o1, sp, RouterMode::softmax, true);
+        (void)gp.submit();
+        close(read<float>(gp, o1), want.data(), C);
+    }
+    fs::remove_all(dir);
 }
 // The stand-alone operators of the graph (dense GEMV forms, batched routing with the margin audit, mixture, residual read / write)
 // against the oracle's functions.

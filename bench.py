@@ -193,9 +193,9 @@ def decode_record(args, dev, T, layers, etype, layout, full: bool):
     import torch
     from tokspur_public_b200 import capi, formats, synth
     from tokspur_public_b200 import layer as L
-    blk_bytes, blk_cols = (34, 32) if etype == formats.Q8_0 else (144, 256)
-    expert_gate_up = 2 * HIDDEN * (CHANNELS // blk_cols) * blk_bytes
-    expert_down = CHANNELS * (HIDDEN // blk_cols) * blk_bytes
+    down_type = getattr(layers[0], "down_type", etype)
+    expert_gate_up = 2 * formats.gguf_bytes(etype, HIDDEN, CHANNELS)
+    expert_down = formats.gguf_bytes(down_type, CHANNELS, HIDDEN)
     scratch = L.Scratch(CHANNELS, HIDDEN, EXPERTS, SELECTED, T, dev)
     nb = 8
     host_x = [torch.from_numpy(synth.activations_f16(1000 + b, T, CHANNELS)).pin_memory() for b in range(nb)]
@@ -272,6 +272,7 @@ def decode_record(args, dev, T, layers, etype, layout, full: bool):
     dn_bytes = (U0 + 1) * expert_down + T * (SELECTED + 1) * (HIDDEN * 4 + CHANNELS * 4)
     achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
     kname = ("gemv3_kernel<planar, gate-up+SwiGLU> (routed experts + shared expert, one launch)" if etype == formats.Q4_K else
+             "gemv_k5_kernel<Q5_K, gate-up+SwiGLU> (routed experts) + gemv_kernel<Q8_0> (shared expert): two launches timed together" if etype == formats.Q5_K else
              "gemv_kernel<Q8_0, gate-up+SwiGLU> (routed experts, then the shared expert: two launches timed together)")
     roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "peak_kind": peak_kind, "timing": "average of a back-to-back loop of this launch alone over the rotating layers (CUDA events)",
@@ -575,8 +576,12 @@ def run_ours(args):
     # Q4_K experts default to the Pack-v3 planar layout, Q8_0 experts (the MTP block) stay GGUF blocks
     lname = args.layout or ("gguf" if args.experts == "q8_0" else "planar")
     layout = formats.PLANAR if lname == "planar" else formats.GGUF
-    etype = formats.Q8_0 if args.experts == "q8_0" else formats.Q4_K   # q8_0: the MTP block of BASELINE configs[3]
-    wname = ("Q8_0 " if etype == formats.Q8_0 else "Q4_K ") + ("Pack-v3 planar" if layout == formats.PLANAR else "GGUF")
+    # q8_0: the MTP block of BASELINE configs[3]; q5_k: the reference model's other pairing (Q5_K gate / up, Q5_1 down, Q8_0 shared), raw blocks
+    etype = {"q8_0": formats.Q8_0, "q5_k": formats.Q5_K}.get(args.experts, formats.Q4_K)
+    if etype == formats.Q5_K:
+        layout = formats.GGUF
+    wname = {formats.Q8_0: "Q8_0 ", formats.Q5_K: "Q5_K gate/up + Q5_1 down + Q8_0 shared ", formats.Q4_K: "Q4_K "}[etype] + \
+            ("Pack-v3 planar" if layout == formats.PLANAR else "GGUF")
     with ClockSampler(local) as clocks:
         if args.workload == "head":
             M = min(max(args.tokens, 1), 16) if args.tokens != 64 else 16
@@ -617,7 +622,8 @@ def run_ours(args):
                                       "launch_ms": rec["stage_ms"]["gate_up_ms"]},
                          "cpu_baseline": cpu, "extra": {"prefill": rec}})
         else:
-            layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, etype, layout, dev, keep_gguf=(i == 0)) for i in range(args.layers)]
+            extra_types = dict(down_type=formats.Q5_1, shared_type=formats.Q8_0) if etype == formats.Q5_K else {}
+            layers = [L.SynthDeviceLayer(100 + i, CHANNELS, HIDDEN, EXPERTS, etype, layout, dev, keep_gguf=(i == 0), **extra_types) for i in range(args.layers)]
             rec, (roofline, cpu) = decode_record(args, dev, T, layers, etype, layout, True)
             extra = {"decode": rec}
             headline = etype == formats.Q4_K and layout == formats.PLANAR and T == 64 and not args.decode_only
@@ -632,7 +638,9 @@ def run_ours(args):
                 extra["head_M1"] = head_record(args, dev, 1)[0]
                 extra["config1"] = config1_record(args, dev)
             line = base_line(args, rec["tokens_per_s"], rec["ms_per_step"],
-                             f"moe_layer_decode_T{T} (BASELINE configs[1])" if etype == formats.Q4_K else f"q8_0_mtp_moe_block_T{T} (BASELINE configs[3])",
+                             f"moe_layer_decode_T{T} (BASELINE configs[1])" if etype == formats.Q4_K else
+                             f"moe_layer_decode_T{T} (reference model encodings at the BASELINE shape)" if etype == formats.Q5_K else
+                             f"q8_0_mtp_moe_block_T{T} (BASELINE configs[3])",
                              wname, "f16 activations, f32 accumulate",
                              {"activations": "binary16 in/out, FP32 accumulate", "layers_rotated": args.layers,
                               "l2_policy": "inputs larger than L2: each step streams ~650 MB of distinct expert weights",
@@ -653,7 +661,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=64, help="token rows per step (decode batch)")
     ap.add_argument("--layers", type=int, default=4, help="independently seeded weight sets rotated over")
     ap.add_argument("--layout", default=None, choices=["planar", "gguf"], help="weight layout (default: Pack-v3 planar for Q4_K experts, GGUF blocks for Q8_0 experts)")
-    ap.add_argument("--experts", default="q4_k", choices=["q4_k", "q8_0"], help="expert encoding of the decode workload (q8_0: the MTP block)")
+    ap.add_argument("--experts", default="q4_k", choices=["q4_k", "q8_0", "q5_k"],
+                    help="expert encoding of the decode workload (q8_0: the MTP block; q5_k: Q5_K gate/up, Q5_1 down, Q8_0 shared expert)")
     ap.add_argument("--shared", default=None, choices=["q8_0"], help="prefill workload: the shared expert as dense Q8_0 blocks (launches of its own)")
     ap.add_argument("--cpu-tokens", type=int, default=None, help="tokens of the batch timed on the CPU baseline (0 = skip)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "head", "config1"])

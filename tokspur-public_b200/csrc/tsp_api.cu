@@ -329,7 +329,8 @@ int tsp_residual_write(const float* d_streams, const float* d_output, const floa
 }
 
 int tsp_synth_weights(uint32_t type, uint64_t seed, uint64_t first_block, uint64_t blocks, float sigma, void* d_out, void* stream) {
-    if (type != TSP_TYPE_Q4_K && type != TSP_TYPE_Q8_0 && type != TSP_TYPE_F32) return fail(TSP_E_TYPE, "synth: encoding %u has no generator", type);
+    if (type != TSP_TYPE_Q4_K && type != TSP_TYPE_Q8_0 && type != TSP_TYPE_F32 && type != TSP_TYPE_Q5_K && type != TSP_TYPE_Q5_1)
+        return fail(TSP_E_TYPE, "synth: encoding %u has no generator", type);
     TSP_REQUIRE(d_out && blocks >= 1 && blocks < (1ull << 38), "synth: null output or block count out of range");
     TSP_REQUIRE(sigma > 0.f && sigma < 1e4f, "synth: sigma out of range");
     return launch_synth(type, seed, first_block, blocks, sigma, d_out, static_cast<cudaStream_t>(stream));

@@ -1,17 +1,21 @@
 // Decode-size routed / dense projections over the five-bit encodings of the reference's model: Q5_K (176-byte super-blocks of
 // 256 weights; gate and up tensors) and Q5_1 (24-byte blocks of 32 weights; down tensors), plain GGUF rows.
 //
-// One thread owns one weight row (gate-up: the gate row and the up row of one hidden unit) for all token rows of a tile and walks
-// its K extent: it decodes 32-weight groups to the exactly rounded FP32 weights (numeric.cpp:38-50: d * sc * q and dmin * mn
-// are exact in FP32, so one FMA gives the reference's rounded value), multiplies them with the tile's FP32 activation rows (the
-// lanes of a warp read the same activation values: broadcast loads) and keeps one FP32 sum per token. Weight bytes are read once
-// per (tile, row); no shared-memory staging, no copy pipeline: a plain path for the encodings the benchmark configurations do
-// not use.
+// A block takes one token tile and a run of weight rows. It first stages the tile's FP32 activation rows in shared memory
+// (32-value groups padded to 36 values, so that 32 lanes reading 16 bytes each at a group stride touch every bank equally). Then
+// the lanes of a warp spread over the K extent of one weight row (gate-up: the gate row and the up row of one hidden unit): a
+// lane takes one 32-weight group at a time with 16-byte loads that are contiguous across the warp, decodes it to the exactly
+// rounded FP32 weights (numeric.cpp:38-50: d * sc * q and dmin * mn are exact in FP32, so one FMA gives the reference's rounded
+// value), multiplies with the staged activations and keeps one FP32 sum per token; the lanes' sums are added with shuffles.
+// Weight bytes are read once per (tile, row). FP32 FMAs, no tensor cores, no copy pipeline: a plain path for the encodings the
+// benchmark configurations do not use.
 #include "tsp_common.cuh"
 
 namespace tsp {
 
-constexpr uint32_t kK5MaxTokens = 16;  // token rows of a tile (8 per routed tile, 16 for dense row batches)
+constexpr uint32_t kK5MaxTokens = 16;   // token rows of a tile (8 per routed tile, 16 for dense row batches)
+constexpr uint32_t kK5Threads = 256;    // eight warps
+constexpr uint32_t kK5BlockRows = 64;   // weight rows (hidden units) per block and tile
 
 struct K5Params {
     const uint8_t* a_base; const uint8_t* a_base_hi; const uint8_t* b_base; const uint8_t* b_base_hi;
@@ -20,38 +24,35 @@ struct K5Params {
     const float* x; uint64_t x_stride_bytes; uint32_t in_div;
     const uint32_t* token_map; const uint32_t* counts; const uint32_t* tasks;
     uint32_t tokens, tile_tokens;
+    uint32_t lanes_per_row;   // lanes that share one weight row: the largest power of two <= min(32, groups)
     float* out; uint64_t out_stride_bytes;
     uint32_t* error;
 };
-
-// the twelve packed 6-bit factors of a K-quant super-block (numeric.cpp:25-31)
-__device__ __forceinline__ void k_factors(const uint8_t* block, uint32_t group, uint32_t& sc, uint32_t& mn) {
-    const uint32_t lane = group & 3u;
-    if (group < 4) { sc = block[4 + lane] & 63u; mn = block[8 + lane] & 63u; return; }
-    const uint32_t packed = block[12 + lane];
-    sc = (packed & 15u) | ((block[4 + lane] >> 6) << 4);
-    mn = (packed >> 4) | ((block[8 + lane] >> 6) << 4);
-}
 
 // byte k of `q` as a float: 0x4B0000bb is 2^23 + bb, the subtraction is exact (no integer-to-float conversion instruction)
 template <uint32_t K>
 __device__ __forceinline__ float byte_f32(uint32_t q) { return __uint_as_float(__byte_perm(q, 0x4b000000u, 0x7440u + K)) - 8388608.f; }
 
-// One 32-weight group of a row, opened once (scale, offset, code pointers) and then read four weights at a time:
-// get(i4, w) gives weights 4 i4 .. 4 i4 + 3 of the group as the exactly rounded FP32 values.
+// One 32-weight group of a row, fetched with wide loads and then read four weights at a time: get(i4, w) gives weights
+// 4 i4 .. 4 i4 + 3 of the group as the exactly rounded FP32 values.
 template <uint32_t TYPE> struct Group5;
-template <> struct Group5<13u> {   // Q5_K
-    float s, m; const uint32_t* qs; const uint32_t* qh; uint32_t shift, g; bool finite;
+template <> struct Group5<13u> {   // Q5_K: header (d, dmin, twelve factor bytes), 32 bytes of fifth bits, 128 bytes of nibbles
+    float s, m; uint32_t qs[8], qh[8]; uint32_t shift, g; bool finite;
     __device__ __forceinline__ Group5(const uint8_t* row, uint32_t grp) {
         const uint8_t* block = row + (grp >> 3) * 176u;
         g = grp & 7u;
-        const uint32_t dm = *reinterpret_cast<const uint32_t*>(block);
-        const float d = half_bits_to_float(dm & 0xffffu), dmin = half_bits_to_float(dm >> 16);
-        uint32_t sc, mn;
-        k_factors(block, g, sc, mn);
+        const uint4 h = *reinterpret_cast<const uint4*>(block);
+        const uint4 h0 = reinterpret_cast<const uint4*>(block + 16)[0], h1 = reinterpret_cast<const uint4*>(block + 16)[1];
+        const uint4 q0 = reinterpret_cast<const uint4*>(block + 48 + (g >> 1) * 32)[0], q1 = reinterpret_cast<const uint4*>(block + 48 + (g >> 1) * 32)[1];
+        qh[0] = h0.x; qh[1] = h0.y; qh[2] = h0.z; qh[3] = h0.w; qh[4] = h1.x; qh[5] = h1.y; qh[6] = h1.z; qh[7] = h1.w;
+        qs[0] = q0.x; qs[1] = q0.y; qs[2] = q0.z; qs[3] = q0.w; qs[4] = q1.x; qs[5] = q1.y; qs[6] = q1.z; qs[7] = q1.w;
+        // factors of group g from the header words (y, z, w = the twelve packed bytes), numeric.cpp:25-31
+        const uint32_t sh = 8u * (g & 3u);
+        const uint32_t by = (h.y >> sh) & 255u, bz = (h.z >> sh) & 255u, bw = (h.w >> sh) & 255u;
+        const uint32_t sc = g < 4 ? (by & 63u) : ((bw & 15u) | ((by >> 6) << 4));
+        const uint32_t mn = g < 4 ? (bz & 63u) : ((bw >> 4) | ((bz >> 6) << 4));
+        const float d = half_bits_to_float(h.x & 0xffffu), dmin = half_bits_to_float(h.x >> 16);
         s = d * static_cast<float>(sc); m = -(dmin * static_cast<float>(mn));   // both exact
-        qs = reinterpret_cast<const uint32_t*>(block + 48 + (g >> 1) * 32);
-        qh = reinterpret_cast<const uint32_t*>(block + 16);
         shift = 4u * (g & 1u);
         finite = finite_f32(d) && finite_f32(dmin);
     }
@@ -60,7 +61,7 @@ template <> struct Group5<13u> {   // Q5_K
         w[0] = fmaf(s, byte_f32<0>(q), m); w[1] = fmaf(s, byte_f32<1>(q), m); w[2] = fmaf(s, byte_f32<2>(q), m); w[3] = fmaf(s, byte_f32<3>(q), m);
     }
 };
-template <> struct Group5<7u> {    // Q5_1
+template <> struct Group5<7u> {    // Q5_1: d, m, 32 fifth bits, 16 bytes of nibbles
     float d, m; uint32_t qh; uint32_t qs[4]; bool finite;
     __device__ __forceinline__ Group5(const uint8_t* row, uint32_t grp) {
         const uint2* block = reinterpret_cast<const uint2*>(row + grp * 24u);   // 24-byte blocks of 8-byte aligned rows: three 8-byte loads
@@ -79,76 +80,22 @@ template <> struct Group5<7u> {    // Q5_1
     }
 };
 
-// Four lanes own one weight row (gate-up: the gate row and the up row of one hidden unit) of a tile: lane q of the four takes the
-// units of 128 weights q, q + 4, ... of the row and the four add their sums with two shuffles. A warp covers eight rows, and its
-// lanes read four distinct activation addresses per load. MT: token rows of a tile at most (8 routed, 16 dense batches).
-constexpr uint32_t kK5Threads = 128, kK5Lanes = 4, kK5Rows = kK5Threads / kK5Lanes;
-
-// A non-finite activation makes the sums it enters non-finite (0 * inf is NaN), so the finished sums are checked, not the inputs.
-template <bool GATEUP, uint32_t MT>
-struct K5Acc {
-    float a[MT], b[GATEUP ? MT : 1];
-    uint32_t xo[MT];   // the tile's input rows as float4 offsets from the first row buffer
-    // four weights of matrix A (and B) against the tile's activation values at float4 index `at`
-    __device__ __forceinline__ void add(const float (&wa)[4], const float (&wb)[4], const float4* x0, uint32_t at, uint32_t count) {
-#pragma unroll
-        for (uint32_t j = 0; j < MT; ++j) {
-            if (j >= count) break;
-            const float4 v = x0[xo[j] + at];
-            a[j] = fmaf(wa[0], v.x, a[j]); a[j] = fmaf(wa[1], v.y, a[j]); a[j] = fmaf(wa[2], v.z, a[j]); a[j] = fmaf(wa[3], v.w, a[j]);
-            if (GATEUP) { b[j] = fmaf(wb[0], v.x, b[j]); b[j] = fmaf(wb[1], v.y, b[j]); b[j] = fmaf(wb[2], v.z, b[j]); b[j] = fmaf(wb[3], v.w, b[j]); }
-        }
-    }
-};
-
-// factors of group g from the header words (y, z, w = the twelve packed bytes), numeric.cpp:25-31
-__device__ __forceinline__ void k_factors_w(const uint4& h, uint32_t g, uint32_t& sc, uint32_t& mn) {
-    const uint32_t sh = 8u * (g & 3u);
-    const uint32_t by = (h.y >> sh) & 255u, bz = (h.z >> sh) & 255u, bw = (h.w >> sh) & 255u;
-    if (g < 4) { sc = by & 63u; mn = bz & 63u; }
-    else { sc = (bw & 15u) | ((by >> 6) << 4); mn = (bw >> 4) | ((bz >> 6) << 4); }
-}
-
-// group g (a run-time value: one copy of this code serves the eight groups, the unrolled token loops are large)
-template <bool GATEUP, uint32_t MT>
-__device__ __forceinline__ void q5k_group(uint32_t g, const uint8_t* blkA, const uint8_t* blkB, const uint4& hA, const uint4& hB, const uint4 (&qhA)[2],
-                                          const uint4 (&qhB)[2], K5Acc<GATEUP, MT>& acc, const float4* x0, uint32_t at0, uint32_t count) {
-    uint32_t sc, mn;
-    k_factors_w(hA, g, sc, mn);
-    const float sA = half_bits_to_float(hA.x & 0xffffu) * static_cast<float>(sc), mA = -(half_bits_to_float(hA.x >> 16) * static_cast<float>(mn));
-    float sB = 0.f, mB = 0.f;
-    if (GATEUP) {
-        k_factors_w(hB, g, sc, mn);
-        sB = half_bits_to_float(hB.x & 0xffffu) * static_cast<float>(sc); mB = -(half_bits_to_float(hB.x >> 16) * static_cast<float>(mn));
-    }
-    const uint4* qsA = reinterpret_cast<const uint4*>(blkA + 48 + (g >> 1) * 32);
-    const uint4* qsB = reinterpret_cast<const uint4*>(blkB + 48 + (g >> 1) * 32);
-    const uint32_t nib = 4u * (g & 1u);
-#pragma unroll
-    for (uint32_t h = 0; h < 2; ++h) {
-        const uint4 ca = qsA[h], cb = GATEUP ? qsB[h] : make_uint4(0, 0, 0, 0);
-        const uint32_t wa_[4] = {ca.x, ca.y, ca.z, ca.w}, wb_[4] = {cb.x, cb.y, cb.z, cb.w};
-        const uint32_t ha_[4] = {qhA[h].x, qhA[h].y, qhA[h].z, qhA[h].w}, hb_[4] = {qhB[h].x, qhB[h].y, qhB[h].z, qhB[h].w};
-#pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) {
-            const uint32_t qa = ((wa_[k] >> nib) & 0x0f0f0f0fu) | (((ha_[k] >> g) & 0x01010101u) << 4);
-            const uint32_t qb = ((wb_[k] >> nib) & 0x0f0f0f0fu) | (((hb_[k] >> g) & 0x01010101u) << 4);
-            const float wa[4] = {fmaf(sA, byte_f32<0>(qa), mA), fmaf(sA, byte_f32<1>(qa), mA), fmaf(sA, byte_f32<2>(qa), mA), fmaf(sA, byte_f32<3>(qa), mA)};
-            const float wb[4] = {fmaf(sB, byte_f32<0>(qb), mB), fmaf(sB, byte_f32<1>(qb), mB), fmaf(sB, byte_f32<2>(qb), mB), fmaf(sB, byte_f32<3>(qb), mB)};
-            acc.add(wa, wb, x0, at0 + g * 8u + h * 4u + k, count);
-        }
-    }
-}
-
+// MT: token rows of a tile at most (8 for routed tiles, 16 for dense row batches of more than 8 rows).
+// Shared memory: the tile's rows as [token][group][9 float4] (eight of data, one of padding).
 template <uint32_t TYPE, bool GATEUP, uint32_t MT>
 __global__ void __launch_bounds__(kK5Threads) gemv_k5_kernel(const K5Params p) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ uint32_t s_x[kK5MaxTokens];        // the tile's input rows as float4 offsets from p.x
+    extern __shared__ float4 k5_xs[];
+    __shared__ const float4* s_x[kK5MaxTokens];   // the tile's input rows
     __shared__ float* s_out[kK5MaxTokens];        // and its output rows
     __shared__ uint32_t s_tile[3];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t n_tiles = p.token_map ? p.tasks[0] : (p.tokens + p.tile_tokens - 1) / p.tile_tokens;
-    const uint32_t q = threadIdx.x & (kK5Lanes - 1u), r = blockIdx.x * kK5Rows + threadIdx.x / kK5Lanes;
+    const uint32_t groups = p.cols / 32u;
+    const uint32_t lpr = p.lanes_per_row, rpw = 32u / lpr;    // lanes per row, rows per warp
+    const uint32_t sub = lane / lpr, lig = lane & (lpr - 1u); // this lane's row of the warp's rows, its first group
+    const uint32_t row0 = blockIdx.x * kK5BlockRows;
     for (uint32_t tile = blockIdx.y; tile < n_tiles; tile += gridDim.y) {   // uniform over the block
         __syncthreads();   // the previous tile's rows are no longer read
         if (threadIdx.x == 0) {
@@ -163,65 +110,65 @@ __global__ void __launch_bounds__(kK5Threads) gemv_k5_kernel(const K5Params p) {
         }
         __syncthreads();
         const uint32_t expert = s_tile[0], start = s_tile[1], count = min(s_tile[2], MT);
+        if (count == 0) continue;   // uniform
         if (threadIdx.x < count) {
             const uint32_t rid = p.token_map ? p.token_map[static_cast<uint64_t>(expert) * p.tokens + start + threadIdx.x] : start + threadIdx.x;
-            s_x[threadIdx.x] = static_cast<uint32_t>(static_cast<uint64_t>(rid / p.in_div) * p.x_stride_bytes / 16u);
+            s_x[threadIdx.x] = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.x) + static_cast<uint64_t>(rid / p.in_div) * p.x_stride_bytes);
             s_out[threadIdx.x] = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out) + static_cast<uint64_t>(rid) * p.out_stride_bytes);
         }
         __syncthreads();
-        if (count == 0 || r >= p.rows) continue;   // uniform over a warp: its eight rows start at a multiple of eight, and so does rows
+        // stage the activation rows: consecutive threads read consecutive 16-byte pieces of a row
+        for (uint32_t i = threadIdx.x; i < count * groups * 8u; i += kK5Threads) {
+            const uint32_t j = i / (groups * 8u), rem = i - j * groups * 8u;
+            k5_xs[(j * groups + (rem >> 3)) * 9u + (rem & 7u)] = s_x[j][rem];
+        }
+        __syncthreads();
         const bool hi = expert >= p.split;
-        const uint64_t eoff = static_cast<uint64_t>(hi ? expert - p.split : expert) * p.expert_stride + static_cast<uint64_t>(r) * p.row_bytes;
-        const uint8_t* rowA = (hi ? p.a_base_hi : p.a_base) + eoff;
-        const uint8_t* rowB = GATEUP ? (hi ? p.b_base_hi : p.b_base) + eoff : rowA;
-
-        K5Acc<GATEUP, MT> acc;
-#pragma unroll
-        for (uint32_t j = 0; j < MT; ++j) { acc.a[j] = 0.f; if (GATEUP) acc.b[j] = 0.f; acc.xo[j] = j < count ? s_x[j] : 0u; }
-        const float4* x0 = reinterpret_cast<const float4*>(p.x);
+        const uint64_t eoff = static_cast<uint64_t>(hi ? expert - p.split : expert) * p.expert_stride;
+        const uint8_t* baseA = (hi ? p.a_base_hi : p.a_base) + eoff;
+        const uint8_t* baseB = GATEUP ? (hi ? p.b_base_hi : p.b_base) + eoff : baseA;
         bool ok = true;
-        if constexpr (TYPE == 13u) {
-            for (uint32_t unit = q; unit < p.cols / 128u; unit += kK5Lanes) {   // half a super-block: groups 0..3 or 4..7
-                const uint32_t blk = unit >> 1;
-                const uint8_t* bA = rowA + blk * 176u;
-                const uint8_t* bB = rowB + blk * 176u;
-                const uint4 hA = *reinterpret_cast<const uint4*>(bA), hB = *reinterpret_cast<const uint4*>(bB);
-                const uint4 qhA[2] = {reinterpret_cast<const uint4*>(bA + 16)[0], reinterpret_cast<const uint4*>(bA + 16)[1]};
-                const uint4 qhB[2] = {reinterpret_cast<const uint4*>(bB + 16)[0], reinterpret_cast<const uint4*>(bB + 16)[1]};
-                ok &= (hA.x & 0x7c00u) != 0x7c00u && (hA.x & 0x7c000000u) != 0x7c000000u && (hB.x & 0x7c00u) != 0x7c00u && (hB.x & 0x7c000000u) != 0x7c000000u;
-                const uint32_t at0 = blk * 64u;
-                const uint32_t g0 = (unit & 1u) * 4u;
-#pragma unroll 1
-                for (uint32_t g = g0; g < g0 + 4u; ++g) q5k_group<GATEUP, MT>(g, bA, bB, hA, hB, qhA, qhB, acc, x0, at0, count);
-            }
-        } else {
-            for (uint32_t unit = q; unit < (p.cols + 127u) / 128u; unit += kK5Lanes)
-                for (uint32_t grp = unit * 4u; grp < unit * 4u + 4u && grp < p.cols / 32u; ++grp) {
-                    const Group5<7u> ga(rowA, grp), gb(rowB, grp);
-                    ok &= ga.finite & gb.finite;
+        // the warps take the block's rows in turn, `rpw` rows at a time (uniform trip count over the warp: shuffles inside)
+        for (uint32_t rb = row0 + warp * rpw; rb < row0 + kK5BlockRows && rb < p.rows; rb += (kK5Threads / 32u) * rpw) {
+            const uint32_t r = rb + sub;
+            const bool live = r < p.rows && r < row0 + kK5BlockRows;
+            const uint8_t* rowA = baseA + static_cast<uint64_t>(live ? r : rb) * p.row_bytes;
+            const uint8_t* rowB = baseB + static_cast<uint64_t>(live ? r : rb) * p.row_bytes;
+            float accA[MT], accB[GATEUP ? MT : 1];
 #pragma unroll
-                    for (uint32_t i4 = 0; i4 < 8; ++i4) {
-                        float wa[4], wb[4] = {0.f, 0.f, 0.f, 0.f};
-                        ga.get(i4, wa);
-                        if (GATEUP) gb.get(i4, wb);
-                        acc.add(wa, wb, x0, grp * 8u + i4, count);
+            for (uint32_t j = 0; j < MT; ++j) { accA[j] = 0.f; if (GATEUP) accB[j] = 0.f; }
+            for (uint32_t grp = lig; grp < groups; grp += lpr) {
+                const Group5<TYPE> ga(rowA, grp), gb(rowB, grp);
+                ok &= ga.finite & gb.finite;
+#pragma unroll
+                for (uint32_t i4 = 0; i4 < 8; ++i4) {
+                    float wa[4], wb[4] = {0.f, 0.f, 0.f, 0.f};
+                    ga.get(i4, wa);
+                    if (GATEUP) gb.get(i4, wb);
+#pragma unroll
+                    for (uint32_t j = 0; j < MT; ++j) {
+                        if (j >= count) break;
+                        const float4 v = k5_xs[(j * groups + grp) * 9u + i4];
+                        accA[j] = fmaf(wa[0], v.x, accA[j]); accA[j] = fmaf(wa[1], v.y, accA[j]); accA[j] = fmaf(wa[2], v.z, accA[j]); accA[j] = fmaf(wa[3], v.w, accA[j]);
+                        if (GATEUP) { accB[j] = fmaf(wb[0], v.x, accB[j]); accB[j] = fmaf(wb[1], v.y, accB[j]); accB[j] = fmaf(wb[2], v.z, accB[j]); accB[j] = fmaf(wb[3], v.w, accB[j]); }
                     }
                 }
-        }
-        if (!ok) raise_error(p.error, TSP_ERR_NONFINITE);
+            }
+            // A non-finite activation makes the sums it enters non-finite (0 * inf is NaN): the finished sums are checked
 #pragma unroll
-        for (uint32_t j = 0; j < MT; ++j) {
-            if (j >= count) break;
-            float a = acc.a[j], b = GATEUP ? acc.b[j] : 0.f;
-            a += __shfl_xor_sync(0xffffffffu, a, 1); a += __shfl_xor_sync(0xffffffffu, a, 2);
-            if (GATEUP) { b += __shfl_xor_sync(0xffffffffu, b, 1); b += __shfl_xor_sync(0xffffffffu, b, 2); }
-            if (q == 0) {
-                // silu with the branch-stable sigmoid (operators.cpp:28-36)
-                const float v = GATEUP ? (a >= 0.f ? a / (1.f + expf(-a)) : a * expf(a) / (1.f + expf(a))) * b : a;
-                if (!finite_f32(v)) raise_error(p.error, TSP_ERR_NONFINITE);
-                s_out[j][r] = v;
+            for (uint32_t j = 0; j < MT; ++j) {
+                if (j >= count) break;
+                float a = accA[j], b = GATEUP ? accB[j] : 0.f;
+                for (uint32_t o = lpr >> 1; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); if (GATEUP) b += __shfl_xor_sync(0xffffffffu, b, o); }
+                if (lig == 0 && live) {
+                    // silu with the branch-stable sigmoid (operators.cpp:28-36)
+                    const float v = GATEUP ? (a >= 0.f ? a / (1.f + expf(-a)) : a * expf(a) / (1.f + expf(a))) * b : a;
+                    if (!finite_f32(v)) raise_error(p.error, TSP_ERR_NONFINITE);
+                    s_out[j][r] = v;
+                }
             }
         }
+        if (!ok) raise_error(p.error, TSP_ERR_NONFINITE);
     }
 }
 
@@ -251,6 +198,7 @@ int launch_gemv_k5(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
                    uint32_t tokens, const uint32_t* token_map, const uint32_t* counts, const uint32_t* tasks, float* out,
                    uint64_t out_stride_bytes, int nc, uint32_t* error, cudaStream_t st) {
     if (a->layout != TSP_LAYOUT_GGUF) return fail(TSP_E_TYPE, "five-bit encodings are read as plain GGUF rows only");
+    if (nc != 1 && nc != 2) return fail(TSP_E_ARG, "five-bit projection: tiles hold 8 or 16 token rows");
     K5Params p{};
     p.a_base = static_cast<const uint8_t*>(a->base);
     p.a_base_hi = static_cast<const uint8_t*>(a->base_hi ? a->base_hi : a->base);
@@ -267,20 +215,31 @@ int launch_gemv_k5(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     p.token_map = token_map; p.counts = counts; p.tasks = tasks;
     p.tokens = tokens; p.tile_tokens = 8u * static_cast<uint32_t>(nc);
     p.out = out; p.out_stride_bytes = out_stride_bytes; p.error = error;
-    if (nc != 1 && nc != 2) return fail(TSP_E_ARG, "five-bit projection: tiles hold 8 or 16 token rows");
-    // routed launches learn their tile count on the device: a fixed number of block rows walks the tiles
+    const uint32_t groups = a->cols / 32;
+    p.lanes_per_row = 1;
+    while (p.lanes_per_row * 2 <= groups && p.lanes_per_row < 32) p.lanes_per_row *= 2;
+    const size_t smem = static_cast<size_t>(p.tile_tokens) * groups * 9 * sizeof(float4);
+    if (smem > 200 * 1024) return fail(TSP_E_ARG, "five-bit projection: %u columns x %u token rows do not fit the activation staging", a->cols, p.tile_tokens);
+    // routed launches learn their tile count on the device: a fixed number of block rows walks the tiles (a routed launch has at
+    // most 64 routes per token row, one tile each at worst)
     const uint32_t dense_tiles = (tokens + p.tile_tokens - 1) / p.tile_tokens;
     const int sms = sm_count();
     if (sms <= 0) return fail(TSP_E_CUDA, "no usable CUDA device");
-    // a routed launch has at most 64 routes per token row (selected <= 64), one tile each at worst
     const uint64_t routed_cap = static_cast<uint64_t>(tokens) * 64u;
     const uint32_t walkers = static_cast<uint32_t>(routed_cap < 4u * static_cast<uint32_t>(sms) ? routed_cap : 4u * static_cast<uint32_t>(sms));
-    const dim3 grid((a->rows + kK5Rows - 1) / kK5Rows, token_map ? walkers : (dense_tiles < 1024u ? dense_tiles : 1024u)), block(kK5Threads);
-#define TSP_K5(T, G) (nc == 1 ? launch_pdl(gemv_k5_kernel<T, G, 8u>, grid, block, 0, st, p) : launch_pdl(gemv_k5_kernel<T, G, 16u>, grid, block, 0, st, p))
-    if (a->type == TSP_TYPE_Q5_K) TSP_CUDA(gateup ? TSP_K5(13u, true) : TSP_K5(13u, false));
-    else TSP_CUDA(gateup ? TSP_K5(7u, true) : TSP_K5(7u, false));
-#undef TSP_K5
-    return TSP_OK;
+    const dim3 grid((a->rows + kK5BlockRows - 1) / kK5BlockRows, token_map ? walkers : (dense_tiles < 1024u ? dense_tiles : 1024u)), block(kK5Threads);
+    auto go = [&](auto kernel) -> int {
+        static thread_local SmemAttrCache configured;   // per kernel instantiation (one lambda instantiation each), keyed by device
+        TSP_CUDA(ensure_dynamic_smem(kernel, configured, smem));
+        TSP_CUDA(launch_pdl(kernel, grid, block, smem, st, p));
+        return TSP_OK;
+    };
+    if (a->type == TSP_TYPE_Q5_K) {
+        if (gateup) return nc == 1 ? go(gemv_k5_kernel<13u, true, 8u>) : go(gemv_k5_kernel<13u, true, 16u>);
+        return nc == 1 ? go(gemv_k5_kernel<13u, false, 8u>) : go(gemv_k5_kernel<13u, false, 16u>);
+    }
+    if (gateup) return nc == 1 ? go(gemv_k5_kernel<7u, true, 8u>) : go(gemv_k5_kernel<7u, true, 16u>);
+    return nc == 1 ? go(gemv_k5_kernel<7u, false, 8u>) : go(gemv_k5_kernel<7u, false, 16u>);
 }
 
 }  // namespace tsp

@@ -24,6 +24,9 @@ __device__ __forceinline__ float normal_at(uint64_t key, uint64_t i, float sigma
     return sigma * sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
 }
 
+// LEVELS 15: Q4_K (144-byte blocks, nibbles at byte 16); 31: Q5_K (176-byte blocks: the same header, 32 bytes of fifth bits, nibbles
+// at byte 48; numeric.cpp:44-50)
+template <int LEVELS>
 __global__ void synth_q4k_kernel(uint64_t key, uint64_t first_block, uint64_t blocks, float sigma, uint8_t* __restrict__ out) {
     const uint64_t blk = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (blk >= blocks) return;
@@ -38,7 +41,7 @@ __global__ void synth_q4k_kernel(uint64_t key, uint64_t first_block, uint64_t bl
             hi = fmaxf(hi, v);
         }
         minv[g] = -lo;
-        scale[g] = (hi + minv[g]) / 15.0f;
+        scale[g] = (hi + minv[g]) / static_cast<float>(LEVELS);
         max_scale = fmaxf(max_scale, scale[g]);
         max_min = fmaxf(max_min, minv[g]);
     }
@@ -49,7 +52,10 @@ __global__ void synth_q4k_kernel(uint64_t key, uint64_t first_block, uint64_t bl
         sc[g] = d > 0.f ? static_cast<uint8_t>(fminf(fmaxf(rintf(scale[g] / d), 0.f), 63.f)) : 0;
         mn[g] = dmin > 0.f ? static_cast<uint8_t>(fminf(fmaxf(rintf(minv[g] / dmin), 0.f), 63.f)) : 0;
     }
-    uint8_t* b = out + blk * 144;
+    constexpr bool Q5 = LEVELS == 31;
+    uint8_t* b = out + blk * (Q5 ? 176 : 144);
+    uint8_t* qs = b + (Q5 ? 48 : 16);
+    if (Q5) for (int l = 0; l < 32; ++l) b[16 + l] = 0;
     const uint16_t db = __half_as_ushort(dh), mb = __half_as_ushort(mh);
     b[0] = db & 255; b[1] = db >> 8; b[2] = mb & 255; b[3] = mb >> 8;
     for (int g = 0; g < 4; ++g) {
@@ -61,9 +67,10 @@ __global__ void synth_q4k_kernel(uint64_t key, uint64_t first_block, uint64_t bl
         const float dl0 = d * sc[2 * j], ml0 = dmin * mn[2 * j], dl1 = d * sc[2 * j + 1], ml1 = dmin * mn[2 * j + 1];
         for (int l = 0; l < 32; ++l) {
             const float v0 = normal_at(key, e0 + (2 * j) * 32 + l, sigma), v1 = normal_at(key, e0 + (2 * j + 1) * 32 + l, sigma);
-            const uint32_t q0 = dl0 > 0.f ? static_cast<uint32_t>(fminf(fmaxf(rintf((v0 + ml0) / dl0), 0.f), 15.f)) : 0u;
-            const uint32_t q1 = dl1 > 0.f ? static_cast<uint32_t>(fminf(fmaxf(rintf((v1 + ml1) / dl1), 0.f), 15.f)) : 0u;
-            b[16 + j * 32 + l] = static_cast<uint8_t>(q0 | (q1 << 4));
+            const uint32_t q0 = dl0 > 0.f ? static_cast<uint32_t>(fminf(fmaxf(rintf((v0 + ml0) / dl0), 0.f), static_cast<float>(LEVELS))) : 0u;
+            const uint32_t q1 = dl1 > 0.f ? static_cast<uint32_t>(fminf(fmaxf(rintf((v1 + ml1) / dl1), 0.f), static_cast<float>(LEVELS))) : 0u;
+            qs[j * 32 + l] = static_cast<uint8_t>((q0 & 15u) | ((q1 & 15u) << 4));
+            if (Q5) b[16 + l] |= static_cast<uint8_t>(((q0 >> 4) << (2 * j)) | ((q1 >> 4) << (2 * j + 1)));
         }
     }
 }
@@ -84,6 +91,30 @@ __global__ void synth_q8_kernel(uint64_t key, uint64_t first_block, uint64_t blo
         const int q = d > 0.f ? static_cast<int>(fminf(fmaxf(rintf(v / d), -127.f), 127.f)) : 0;
         b[2 + l] = static_cast<uint8_t>(q & 255);
     }
+}
+
+// Q5_1: d = (max - min) / 31 and m = min as binary16, 32 fifth bits, 16 bytes of nibbles (numeric.cpp:38-42)
+__global__ void synth_q51_kernel(uint64_t key, uint64_t first_block, uint64_t blocks, float sigma, uint8_t* __restrict__ out) {
+    const uint64_t blk = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (blk >= blocks) return;
+    const uint64_t e0 = (first_block + blk) * 32;
+    float lo = INFINITY, hi = -INFINITY;
+    for (int l = 0; l < 32; ++l) { const float v = normal_at(key, e0 + l, sigma); lo = fminf(lo, v); hi = fmaxf(hi, v); }
+    const __half dh = __float2half_rn((hi - lo) / 31.0f), mh = __float2half_rn(lo);
+    const float d = __half2float(dh), m = __half2float(mh);
+    uint8_t* b = out + blk * 24;
+    const uint16_t db = __half_as_ushort(dh), mb = __half_as_ushort(mh);
+    b[0] = db & 255; b[1] = db >> 8; b[2] = mb & 255; b[3] = mb >> 8;
+    uint32_t high = 0;
+    uint8_t nib[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    for (int l = 0; l < 32; ++l) {
+        const float v = normal_at(key, e0 + l, sigma);
+        const uint32_t q = d > 0.f ? static_cast<uint32_t>(fminf(fmaxf(rintf((v - m) / d), 0.f), 31.f)) : 0u;
+        high |= (q >> 4) << l;
+        nib[l & 15] |= static_cast<uint8_t>((q & 15u) << (4 * (l >> 4)));
+    }
+    b[4] = high & 255; b[5] = (high >> 8) & 255; b[6] = (high >> 16) & 255; b[7] = high >> 24;
+    for (int i = 0; i < 16; ++i) b[8 + i] = nib[i];
 }
 
 __global__ void synth_f32_kernel(uint64_t key, uint64_t n, float sigma, float* __restrict__ out) {
@@ -125,7 +156,9 @@ __global__ void pack_planar_kernel(uint32_t type, const uint8_t* __restrict__ gg
 int launch_synth(uint32_t type, uint64_t seed, uint64_t first_block, uint64_t blocks, float sigma, void* out, cudaStream_t st) {
     const uint64_t key = seed * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull;
     const unsigned grid = static_cast<unsigned>((blocks + 127) / 128);
-    if (type == TSP_TYPE_Q4_K) synth_q4k_kernel<<<grid, 128, 0, st>>>(key, first_block, blocks, sigma, static_cast<uint8_t*>(out));
+    if (type == TSP_TYPE_Q4_K) synth_q4k_kernel<15><<<grid, 128, 0, st>>>(key, first_block, blocks, sigma, static_cast<uint8_t*>(out));
+    else if (type == TSP_TYPE_Q5_K) synth_q4k_kernel<31><<<grid, 128, 0, st>>>(key, first_block, blocks, sigma, static_cast<uint8_t*>(out));
+    else if (type == TSP_TYPE_Q5_1) synth_q51_kernel<<<grid, 128, 0, st>>>(key, first_block, blocks, sigma, static_cast<uint8_t*>(out));
     else if (type == TSP_TYPE_Q8_0) synth_q8_kernel<<<grid, 128, 0, st>>>(key, first_block, blocks, sigma, static_cast<uint8_t*>(out));
     else synth_f32_kernel<<<grid, 128, 0, st>>>(key, blocks, sigma, static_cast<float*>(out));
     TSP_CUDA(cudaGetLastError());

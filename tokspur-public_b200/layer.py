@@ -176,7 +176,7 @@ class SynthDeviceLayer:
 
     def __init__(self, seed: int, channels: int, hidden: int, experts: int, expert_type: int = formats.Q4_K,
                  layout: int = formats.PLANAR, device="cuda", sigma: float = 0.02, expert_range: tuple[int, int] | None = None,
-                 keep_gguf: bool = False, expert_ids: list[int] | None = None, shared_type: int | None = None):
+                 keep_gguf: bool = False, expert_ids: list[int] | None = None, shared_type: int | None = None, down_type: int | None = None):
         lib = capi.lib()
         lo, hi = expert_range if expert_range else (0, experts)
         # `expert_ids` names the routed experts held one by one (expert parallelism with replicated experts): local slot i holds
@@ -186,19 +186,24 @@ class SynthDeviceLayer:
         self.channels, self.hidden, self.experts_global, self.experts_local, self.first_expert = channels, hidden, experts, n, ids[0]
         self.expert_ids = ids
         self.type, self.layout = expert_type, layout
-        epb = 256 if expert_type == formats.Q4_K else 32
+        epb = formats.block_geometry(expert_type)[0]
         gb = int(lib.tsp_expert_bytes(expert_type, formats.GGUF, hidden, channels))
         pb = int(lib.tsp_expert_bytes(expert_type, formats.PLANAR, hidden, channels))
         blocks_per_expert = hidden * channels // epb
         st = stream_ptr()
         u8 = lambda nbytes: torch.empty(int(nbytes), dtype=torch.uint8, device=device)
 
+        self.down_type = expert_type if down_type is None else down_type
+        assert self.down_type == expert_type or layout == formats.GGUF, "a down encoding of its own is kept as raw GGUF blocks"
+
         def gen(stream_seed, which, type_=expert_type):
             """The experts `which` (global ids) of one weight stream; runs of consecutive ids become one call."""
-            if type_ != expert_type:   # a dense shared expert in another encoding: one matrix of raw blocks
+            if type_ != expert_type:   # tensors in another encoding (a dense shared expert, the down experts): raw blocks
                 nb = int(lib.tsp_expert_bytes(type_, formats.GGUF, hidden, channels))
-                t = u8(nb)
-                capi.call("tsp_synth_weights", type_, stream_seed, 0, hidden * channels // (256 if type_ == formats.Q4_K else 32), sigma, t.data_ptr(), st)
+                per = hidden * channels // formats.block_geometry(type_)[0]
+                t = u8(len(which) * nb)
+                for i, e in enumerate(which):
+                    capi.call("tsp_synth_weights", type_, stream_seed, e * per, per, sigma, t.data_ptr() + i * nb, st)
                 return t
             t = u8(len(which) * gb)
             at = 0
@@ -211,7 +216,7 @@ class SynthDeviceLayer:
                 at += run
             return t
 
-        g, u, d = gen(seed * 8 + 0, ids), gen(seed * 8 + 1, ids), gen(seed * 8 + 2, ids)
+        g, u, d = gen(seed * 8 + 0, ids), gen(seed * 8 + 1, ids), gen(seed * 8 + 2, ids, self.down_type)
         self.shared_type = expert_type if shared_type is None else shared_type
         sg, su, sd = (gen(seed * 8 + 3 + i, [0], self.shared_type) for i in range(3))
         self.shared_router = torch.empty(channels, dtype=torch.float32, device=device)
@@ -258,7 +263,7 @@ class SynthDeviceLayer:
                 del g, u, d, sg, su, sd
         else:
             gate, up = matrix_set(g, expert_type, layout, hidden, channels, n), matrix_set(u, expert_type, layout, hidden, channels, n)
-            down = matrix_set(d, expert_type, layout, channels, hidden, n)
+            down = matrix_set(d, self.down_type, layout, channels, hidden, n)
             shared = [matrix_set(sg, self.shared_type, layout, hidden, channels), matrix_set(su, self.shared_type, layout, hidden, channels),
                       matrix_set(sd, self.shared_type, layout, channels, hidden)]
         self.weights = MoeWeights(gate, up, down, shared[0], shared[1], shared[2], self.shared_router.data_ptr())
@@ -269,7 +274,8 @@ class SynthDeviceLayer:
         h = {k: v.cpu().numpy() for k, v in self.gguf.items()}
         n = self.experts_local
         return HostLayer(self.channels, self.hidden, n, selected, self.type, self.shared_type, h["gate"].reshape(n, -1), h["up"].reshape(n, -1),
-                         h["down"].reshape(n, -1), h["shared_gate"], h["shared_up"], h["shared_down"], self.shared_router.cpu().numpy())
+                         h["down"].reshape(n, -1), h["shared_gate"], h["shared_up"], h["shared_down"], self.shared_router.cpu().numpy(),
+                         down_type=self.down_type)
 
 
 class PrefillScratch:

@@ -383,3 +383,33 @@ def test_full_shape_layer_properties(oracle):
     L.moe_layer_decode(sl, s, dev(x16[perm]), dev(logits[perm]), out2)
     torch.cuda.synchronize()
     assert np.array_equal(out2.cpu().numpy().view(np.uint16), got[perm].view(np.uint16))
+
+
+def test_decode_layer_is_capturable_in_a_cuda_graph(oracle):
+    """The decode layer's launches (programmatic dependent launches included) are recorded into a CUDA graph on a capture stream
+    and replayed: the replay gives the bits of the direct call. (tsp_moe_layer_decode with caller scratch; no allocation and no
+    host synchronisation happens inside the call.)"""
+    Cn, H, E, K, T = 512, 256, 16, 4, 8
+    host = L.synth_host_layer(21, Cn, H, E, K, expert_type=12)
+    dl = L.DeviceLayer(host, formats.PLANAR, DEV)
+    s = L.Scratch(Cn, H, E, K, T, DEV)
+    x = dev(synth.activations_f16(31, T, Cn))
+    lg = dev(synth.router_logits(32, T, E))
+    out = torch.zeros((T, Cn), dtype=torch.float16, device=DEV)
+    L.moe_layer_decode(dl, s, x, lg, out)      # warm-up outside the capture: shared-memory attributes are set here
+    torch.cuda.synchronize()
+    want = out.clone()
+    graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        L.moe_layer_decode(dl, s, x, lg, out)
+        stream.synchronize()
+        out.zero_()
+        with torch.cuda.graph(graph, stream=stream):
+            L.moe_layer_decode(dl, s, x, lg, out)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    assert s.error_word() == 0

@@ -74,7 +74,7 @@ def test_contract_violations_are_refused_before_any_launch():
         capi.call("tsp_moe_combine", None, 0, 0, None, None, 0, None, None, 0, 0, None, 1, 8, 2, None, 0, None, 0, None, None)
 
 
-@pytest.mark.parametrize("type_", [8, 12])
+@pytest.mark.parametrize("type_", [8, 12, 13, 7])
 def test_numpy_formats_agree_with_oracle(oracle, type_):
     rows, cols = 32, 512
     w = synth.normal(3, (rows, cols), 0.02)
@@ -83,7 +83,14 @@ def test_numpy_formats_agree_with_oracle(oracle, type_):
     dec = oracle.dequantize(type_, g, rows * cols).reshape(rows, cols)
     assert np.array_equal(dec, formats.dequantize_gguf(type_, g, rows, cols))
     err = np.abs(dec - w).max()
-    assert err < (0.006 if type_ == 12 else 0.0006)  # the encoder is sane: within a code step of the source
+    assert err < {12: 0.006, 8: 0.0006, 13: 0.003, 7: 0.003}[type_]  # the encoder is sane: within a code step of the source
+    lcg5 = fixtures.lcg_weights(type_, cols, rows, 1)[0]   # every code / factor bit pattern
+    assert np.array_equal(oracle.dequantize(type_, lcg5, rows * cols).reshape(rows, cols).view(np.uint32),
+                          formats.dequantize_gguf(type_, lcg5, rows, cols).view(np.uint32))
+    if type_ in (13, 7):   # no planar form of the five-bit encodings in this build
+        assert capi.lib().tsp_expert_bytes(type_, formats.PLANAR, rows, cols) == 0
+        assert capi.lib().tsp_expert_bytes(type_, formats.GGUF, rows, cols) == g.size
+        return
     spec = oracle.spec(type_, cols, rows)
     assert np.array_equal(formats.pack_planar(type_, g, rows, cols), oracle.pack_expert(spec, g))
     lcg = fixtures.lcg_weights(type_, cols, rows, 1)[0]

@@ -168,6 +168,24 @@ def dequantize_gguf(type_: int, data: np.ndarray, rows: int, cols: int) -> np.nd
         d = b[..., 0:2].copy().view(np.float16).astype(np.float64)
         q = b[..., 2:].view(np.int8).astype(np.float64)
         return (d * q).reshape(rows, cols).astype(np.float32)
+    if type_ == Q5_1:
+        b = data.reshape(rows, cols // 32, 24)
+        d = b[..., 0:2].copy().view(np.float16).astype(np.float64)
+        m = b[..., 2:4].copy().view(np.float16).astype(np.float64)
+        high = b[..., 4:8].copy().view(np.uint32)
+        i = np.arange(32)
+        q = ((b[..., 8 + i % 16] >> (4 * (i // 16))) & 15) | (((high >> i.astype(np.uint32)) & 1) << 4)
+        return (d * q + m).reshape(rows, cols).astype(np.float32)
+    if type_ == Q5_K:
+        b = data.reshape(rows, cols // 256, 176)
+        d = b[..., 0:2].copy().view(np.float16).astype(np.float64)[..., 0]
+        dmin = b[..., 2:4].copy().view(np.float16).astype(np.float64)[..., 0]
+        sm = sm16_from_scales12(b[..., 4:16]).astype(np.float64)
+        qs = b[..., 48:].reshape(rows, cols // 256, 4, 32)
+        q = np.stack([qs & 15, qs >> 4], axis=3).reshape(rows, cols // 256, 8, 32).astype(np.uint32)
+        q |= ((b[..., None, 16:48].astype(np.uint32) >> np.arange(8, dtype=np.uint32)[:, None]) & 1) << 4
+        v = (d[..., None] * sm[..., 0:8])[..., None] * q - (dmin[..., None] * sm[..., 8:16])[..., None]
+        return v.reshape(rows, cols).astype(np.float32)
     b = data.reshape(rows, cols // 256, 144)
     d = b[..., 0:2].copy().view(np.float16).astype(np.float64)[..., 0]
     dmin = b[..., 2:4].copy().view(np.float16).astype(np.float64)[..., 0]

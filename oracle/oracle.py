@@ -54,7 +54,7 @@ class _Spec(C.Structure):
     _fields_ = [("source_type", C.c_uint32), ("columns", C.c_uint32), ("rows", C.c_uint32), ("blocks_per_row", C.c_uint32),
                 ("source_row_bytes", C.c_uint64), ("planar_row_bytes", C.c_uint64),
                 ("source_expert_bytes", C.c_uint64), ("planar_expert_bytes", C.c_uint64),
-                ("qs_offset", C.c_uint64), ("sm_offset", C.c_uint64), ("dm_offset", C.c_uint64)]
+                ("qs_offset", C.c_uint64), ("sm_offset", C.c_uint64), ("dm_offset", C.c_uint64), ("qh_offset", C.c_uint64)]
 
 
 class OracleError(RuntimeError):

@@ -380,6 +380,20 @@ int tso_make_expert_spec(uint32_t type, uint32_t columns, uint32_t rows, tso_pla
         s->source_row_bytes = (uint64_t)s->blocks_per_row * 144;
         s->planar_row_bytes = (uint64_t)s->blocks_per_row * 148;
         s->qs_offset = 0; s->sm_offset = total * 128; s->dm_offset = total * 144;
+    } else if (type == 13) {   /* Q5_K: planes of nibbles, fifth bits, factor records, (d, dmin) pairs: 128 + 32 + 16 + 4 bytes per block */
+        if (columns < 256 || columns % 256) return TSO_E_SHAPE;
+        s->blocks_per_row = columns / 256;
+        const uint64_t total = (uint64_t)rows * s->blocks_per_row;
+        s->source_row_bytes = (uint64_t)s->blocks_per_row * 176;
+        s->planar_row_bytes = (uint64_t)s->blocks_per_row * 180;
+        s->qs_offset = 0; s->qh_offset = total * 128; s->sm_offset = total * 160; s->dm_offset = total * 176;
+    } else if (type == 7) {    /* Q5_1: planes of nibbles, fifth-bit words, (d, m) pairs: 16 + 4 + 4 bytes per block */
+        if (columns < 32 || columns % 32) return TSO_E_SHAPE;
+        s->blocks_per_row = columns / 32;
+        const uint64_t total = (uint64_t)rows * s->blocks_per_row;
+        s->source_row_bytes = (uint64_t)s->blocks_per_row * 24;
+        s->planar_row_bytes = s->source_row_bytes;
+        s->qs_offset = 0; s->qh_offset = total * 16; s->dm_offset = total * 20;
     } else if (type == 8) {
         if (columns < 32 || columns % 32) return TSO_E_SHAPE;
         s->blocks_per_row = columns / 32;
@@ -426,6 +440,21 @@ int tso_pack_expert_planar(const tso_planar_spec* s, const uint8_t* src, uint8_t
             tso_pack_sm16(sb + 4, dst + s->sm_offset + b * 16);
             memcpy(dst + s->dm_offset + b * 4, sb, 4);
         }
+    } else if (s->source_type == 13) {
+        for (uint64_t b = 0; b < total; ++b) {
+            const uint8_t* sb = src + b * 176;
+            memcpy(dst + s->qs_offset + b * 128, sb + 48, 128);
+            memcpy(dst + s->qh_offset + b * 32, sb + 16, 32);
+            tso_pack_sm16(sb + 4, dst + s->sm_offset + b * 16);
+            memcpy(dst + s->dm_offset + b * 4, sb, 4);
+        }
+    } else if (s->source_type == 7) {
+        for (uint64_t b = 0; b < total; ++b) {
+            const uint8_t* sb = src + b * 24;
+            memcpy(dst + s->qs_offset + b * 16, sb + 8, 16);
+            memcpy(dst + s->qh_offset + b * 4, sb + 4, 4);
+            memcpy(dst + s->dm_offset + b * 4, sb, 4);
+        }
     } else if (s->source_type == 8) {
         for (uint64_t b = 0; b < total; ++b) {
             const uint8_t* sb = src + b * 34;
@@ -446,6 +475,22 @@ int tso_unpack_expert_planar(const tso_planar_spec* s, const uint8_t* src, uint8
             const int rc = tso_unpack_sm16(src + s->sm_offset + b * 16, sb + 4);
             if (rc) return rc;
             memcpy(sb + 16, src + s->qs_offset + b * 128, 128);
+        }
+    } else if (s->source_type == 13) {
+        for (uint64_t b = 0; b < total; ++b) {
+            uint8_t* sb = dst + b * 176;
+            memcpy(sb, src + s->dm_offset + b * 4, 4);
+            const int rc = tso_unpack_sm16(src + s->sm_offset + b * 16, sb + 4);
+            if (rc) return rc;
+            memcpy(sb + 16, src + s->qh_offset + b * 32, 32);
+            memcpy(sb + 48, src + s->qs_offset + b * 128, 128);
+        }
+    } else if (s->source_type == 7) {
+        for (uint64_t b = 0; b < total; ++b) {
+            uint8_t* sb = dst + b * 24;
+            memcpy(sb, src + s->dm_offset + b * 4, 4);
+            memcpy(sb + 4, src + s->qh_offset + b * 4, 4);
+            memcpy(sb + 8, src + s->qs_offset + b * 16, 16);
         }
     } else if (s->source_type == 8) {
         for (uint64_t b = 0; b < total; ++b) {
@@ -476,6 +521,41 @@ int tso_dequantize_expert_planar(const tso_planar_spec* s, const uint8_t* base, 
                     if (!isfinite(v)) return TSO_E_NONFINITE;
                     out[b * 256 + g * 32 + l] = v;
                 }
+            }
+        }
+    } else if (s->source_type == 13) {
+        for (uint64_t b = 0; b < total; ++b) {
+            const uint8_t* qs = base + s->qs_offset + b * 128;
+            const uint8_t* qh = base + s->qh_offset + b * 32;
+            const uint8_t* sm = base + s->sm_offset + b * 16;
+            const uint8_t* dm = base + s->dm_offset + b * 4;
+            const double d = tso_binary16(rd16(dm)), dmin = tso_binary16(rd16(dm + 2));
+            if (!isfinite(d) || !isfinite(dmin)) return TSO_E_NONFINITE;
+            for (uint32_t g = 0; g < 8; ++g) {
+                const double dl = d * sm[g], ml = dmin * sm[8 + g];
+                const uint8_t* q = qs + (g >> 1) * 32;
+                const uint32_t shift = (g & 1u) * 4u;
+                for (uint32_t l = 0; l < 32; ++l) {
+                    const uint32_t code = ((q[l] >> shift) & 15u) | (((qh[l] >> g) & 1u) << 4);
+                    const float v = (float)(dl * code - ml);
+                    if (!isfinite(v)) return TSO_E_NONFINITE;
+                    out[b * 256 + g * 32 + l] = v;
+                }
+            }
+        }
+    } else if (s->source_type == 7) {
+        for (uint64_t b = 0; b < total; ++b) {
+            const uint8_t* qs = base + s->qs_offset + b * 16;
+            const uint32_t qh = rd32(base + s->qh_offset + b * 4);
+            const uint8_t* dm = base + s->dm_offset + b * 4;
+            const double d = tso_binary16(rd16(dm));
+            const float m = tso_binary16(rd16(dm + 2));
+            if (!isfinite(d) || !isfinite(m)) return TSO_E_NONFINITE;
+            for (uint32_t i = 0; i < 32; ++i) {
+                const uint32_t code = ((qs[i % 16] >> (4 * (i / 16))) & 15u) | (((qh >> i) & 1u) << 4);
+                const float v = (float)(d * code + m);
+                if (!isfinite(v)) return TSO_E_NONFINITE;
+                out[b * 32 + i] = v;
             }
         }
     } else if (s->source_type == 8) {

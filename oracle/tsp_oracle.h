@@ -93,11 +93,12 @@ int tso_logit_topk_row(const float* logits, size_t vocabulary, tso_topk_row* out
 int tso_lanes_pack_rows(uint32_t type, uint32_t columns, const uint8_t* original, uint8_t* packed, size_t nbytes);
 int tso_lanes_unpack_rows(uint32_t type, uint32_t columns, const uint8_t* packed, uint8_t* original, size_t nbytes);
 
-/* ---- Pack v3 planar expert layout (planar_pack_v3.cpp:601-896) ---- */
+/* ---- Pack v3 planar expert layout (planar_pack_v3.cpp:601-896): types 12 (Q4_K), 8 (Q8_0), 13 (Q5_K), 7 (Q5_1) ---- */
 typedef struct {
     uint32_t source_type, columns, rows, blocks_per_row;
     uint64_t source_row_bytes, planar_row_bytes, source_expert_bytes, planar_expert_bytes;
     uint64_t qs_offset, sm_offset, dm_offset;
+    uint64_t qh_offset;   /* fifth-bit plane of the five-bit encodings (types 13 and 7), 0 otherwise */
 } tso_planar_spec;
 
 int tso_make_expert_spec(uint32_t source_type, uint32_t columns, uint32_t rows, tso_planar_spec* spec);

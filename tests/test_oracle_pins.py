@@ -222,7 +222,7 @@ def test_sm16_bijection_and_refusal(oracle):
         oracle.unpack_sm16(bad)
 
 
-@pytest.mark.parametrize("type_,cols,rows", [(12, 512, 64), (8, 512, 64), (8, 64, 16)])
+@pytest.mark.parametrize("type_,cols,rows", [(12, 512, 64), (8, 512, 64), (8, 64, 16), (13, 512, 64), (7, 512, 64), (7, 64, 16)])
 def test_planar_round_trip_and_zero_difference(oracle, type_, cols, rows):
     # native/tests/test_planar_pack_v3.cpp:236-281: byte-exact round trip, identical FP32 operands
     g = fixtures.lcg_weights(type_, cols, rows, 1)[0]
@@ -239,7 +239,11 @@ def test_planar_spec_byte_constants(oracle):
     assert (s.planar_expert_bytes, s.source_expert_bytes, s.sm_offset, s.dm_offset) == (1212416, 1179648, 1048576, 1179648)
     s = oracle.spec(12, 512, 2048)
     assert (s.planar_expert_bytes, s.source_expert_bytes) == (606208, 589824)
-    for bad in ((12, 2048, 6), (12, 300, 8), (8, 48, 8), (8, 32, 4), (5, 256, 8)):
+    s = oracle.spec(13, 512, 64)     # Q5_K: 128 + 32 + 16 + 4 bytes per super-block, plane after plane
+    assert (s.planar_row_bytes, s.source_row_bytes, s.qh_offset, s.sm_offset, s.dm_offset) == (360, 352, 128 * 128, 128 * 160, 128 * 176)
+    s = oracle.spec(7, 64, 16)       # Q5_1: 16 + 4 + 4 bytes per block
+    assert (s.planar_row_bytes, s.source_row_bytes, s.qh_offset, s.dm_offset) == (48, 48, 32 * 16, 32 * 20)
+    for bad in ((12, 2048, 6), (12, 300, 8), (8, 48, 8), (8, 32, 4), (5, 256, 8), (13, 300, 8), (7, 48, 8)):
         with pytest.raises(Exception):
             oracle.spec(*bad)
 

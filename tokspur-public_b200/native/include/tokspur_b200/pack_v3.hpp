@@ -57,11 +57,24 @@ struct PackIndexV3 {
 // The packed bytes of one tensor
 [[nodiscard]] std::vector<std::byte> read_pack_v3_tensor(const std::filesystem::path& path, const PackIndexV3& index, const PackTensorV3& tensor);
 
+// Planar expert images back to plain GGUF blocks on the host, lossless (the plane order of planar_pack_v3.cpp:601-650: Q4_K nibbles |
+// factor records | (d, dmin); Q5_K nibbles | fifth bits | factor records | (d, dmin); Q5_1 nibbles | fifth-bit words | (d, m);
+// Q8_0 codes | scales). `planar` holds `experts` images of planar_expert_bytes_v3() each, `gguf` receives as many of
+// gguf_expert_bytes_v3(). A factor record with a value above 63 is refused (FormatError).
+[[nodiscard]] uint64_t planar_expert_bytes_v3(uint32_t source_type, uint64_t columns, uint64_t rows);   // 0: no planar form of this shape
+[[nodiscard]] uint64_t gguf_expert_bytes_v3(uint32_t source_type, uint64_t columns, uint64_t rows);
+void unpack_planar_experts_v3(uint32_t source_type, uint64_t columns, uint64_t rows, uint64_t experts, const std::byte* planar, std::byte* gguf);
+// The two tensors of a co-located pair ("gate" = experts [0, E/2) as [gate_e, up_e] images, "up" = the rest; planar_pack_v3.cpp:1076-1093)
+// to separate gate and up tensors of E plain GGUF experts each.
+void split_coloc_pair_v3(uint32_t source_type, uint64_t columns, uint64_t rows, uint64_t experts, const std::byte* pair_lo, const std::byte* pair_hi,
+                         std::byte* gate_gguf, std::byte* up_gguf);
+
 // One layer's FFN tensors (`prefix` + ffn_gate_inp, ffn_gate_inp_shexp, ffn_{gate,up,down}_exps, ffn_{gate,up,down}_shexp,
 // model.cpp:50-57) uploaded as immutable buffers of `graph`, between batches: co-located Q4_K / Q8_0 pairs and planar Q8_0 down
 // tensors are registered as planar matrices, lane-packed dense Q8_0 matrices are unpacked to GGUF rows on the device, plain
-// tensors are taken as they are. The shape is read from the directory. Layouts without a kernel here (the Q5_K / Q5_1 planes)
-// are refused. Returns the weights and fills `shape` (selected is left to the caller).
+// tensors are taken as they are. The five-bit planar forms (co-located Q5_K pairs, planar Q5_1 down) have no planar kernel here: they
+// are re-laid as plain GGUF blocks on the host while loading and then run through the decode-size five-bit kernel. The shape is
+// read from the directory. Returns the weights and fills `shape` (selected is left to the caller).
 // q8_down_as_rows: a planar Q8_0 down tensor is re-laid as raw GGUF blocks on the host while loading (lossless) instead of being
 // registered as a planar matrix: the prefill encoder (encode_moe_mm_many) reads Q8_0 experts as raw blocks only.
 struct PackLoadOptions { bool q8_down_as_rows = false; };

@@ -177,6 +177,79 @@ PlanarKind parse_planar_kind(std::string_view name) {
     throw FormatError("unrecognised planar v3 layout string: " + std::string(name));
 }
 
+namespace {
+struct PlaneSpec { uint32_t per_block, block_bytes, planar_bytes, qs, qh, sm, dm; };   // weights per block; bytes per GGUF / planar block; plane widths
+PlaneSpec plane_spec(uint32_t type) {
+    switch (type) {
+        case 12: return {256, 144, 148, 128, 0, 16, 4};
+        case 13: return {256, 176, 180, 128, 32, 16, 4};
+        case 7: return {32, 24, 24, 16, 4, 0, 4};
+        case 8: return {32, 34, 34, 32, 0, 0, 2};
+        default: throw FormatError("pack v3: encoding without a planar form");
+    }
+}
+// sixteen factor bytes sc[0..7], mn[0..7] -> the twelve packed bytes of a K-quant header (numeric.cpp:25-31 read the other way)
+void factors_to_packed(const unsigned char* sm, unsigned char* s12) {
+    for (int i = 0; i < 16; ++i) need((sm[i] & 0xc0u) == 0, "corrupt planar v3 scale/min factor exceeds 6 bits");
+    for (int k = 0; k < 4; ++k) {
+        s12[k] = (unsigned char)(sm[k] | ((sm[4 + k] >> 4) << 6));
+        s12[4 + k] = (unsigned char)(sm[8 + k] | ((sm[12 + k] >> 4) << 6));
+        s12[8 + k] = (unsigned char)((sm[4 + k] & 15u) | ((sm[12 + k] & 15u) << 4));
+    }
+}
+}  // namespace
+
+uint64_t gguf_expert_bytes_v3(uint32_t type, uint64_t columns, uint64_t rows) {
+    const PlaneSpec s = plane_spec(type);
+    return columns % s.per_block ? 0 : rows * (columns / s.per_block) * s.block_bytes;
+}
+uint64_t planar_expert_bytes_v3(uint32_t type, uint64_t columns, uint64_t rows) {
+    const PlaneSpec s = plane_spec(type);
+    if (!columns || columns % s.per_block || rows < 4 || rows % 4) return 0;
+    const uint64_t blocks = rows * (columns / s.per_block);
+    if (type == 8 && blocks % 8) return 0;
+    const uint64_t bytes = blocks * s.planar_bytes;
+    return bytes % 16 ? 0 : bytes;
+}
+
+void unpack_planar_experts_v3(uint32_t type, uint64_t columns, uint64_t rows, uint64_t experts, const std::byte* planar, std::byte* gguf) {
+    const PlaneSpec s = plane_spec(type);
+    const uint64_t pb = planar_expert_bytes_v3(type, columns, rows), gb = gguf_expert_bytes_v3(type, columns, rows);
+    need(pb && gb, "pack v3: shape without a planar form");
+    const uint64_t n = rows * (columns / s.per_block);
+    const uint64_t at_qh = n * s.qs, at_sm = at_qh + n * s.qh, at_dm = at_sm + n * s.sm;   // planes follow one another
+    for (uint64_t e = 0; e < experts; ++e) {
+        const auto* src = reinterpret_cast<const unsigned char*>(planar) + e * pb;
+        auto* dst = reinterpret_cast<unsigned char*>(gguf) + e * gb;
+        for (uint64_t b = 0; b < n; ++b) {
+            unsigned char* blk = dst + b * s.block_bytes;
+            std::memcpy(blk, src + at_dm + b * s.dm, s.dm);                       // scales first in every GGUF block
+            if (type == 12 || type == 13) {
+                factors_to_packed(src + at_sm + b * 16, blk + 4);
+                if (type == 13) std::memcpy(blk + 16, src + at_qh + b * 32, 32);
+                std::memcpy(blk + (type == 13 ? 48 : 16), src + b * 128, 128);
+            } else if (type == 7) {
+                std::memcpy(blk + 4, src + at_qh + b * 4, 4);
+                std::memcpy(blk + 8, src + b * 16, 16);
+            } else {
+                std::memcpy(blk + 2, src + b * 32, 32);
+            }
+        }
+    }
+}
+
+void split_coloc_pair_v3(uint32_t type, uint64_t columns, uint64_t rows, uint64_t experts, const std::byte* pair_lo, const std::byte* pair_hi,
+                         std::byte* gate_gguf, std::byte* up_gguf) {
+    need(experts >= 2 && experts % 2 == 0, "pack v3: a co-located pair holds an even number of experts");
+    const uint64_t pb = planar_expert_bytes_v3(type, columns, rows), gb = gguf_expert_bytes_v3(type, columns, rows);
+    need(pb && gb, "pack v3: shape without a planar form");
+    for (uint64_t e = 0; e < experts; ++e) {
+        const std::byte* pair = (e < experts / 2 ? pair_lo : pair_hi) + (e % (experts / 2)) * 2 * pb;
+        unpack_planar_experts_v3(type, columns, rows, 1, pair, gate_gguf + e * gb);
+        unpack_planar_experts_v3(type, columns, rows, 1, pair + pb, up_gguf + e * gb);
+    }
+}
+
 const PackTensorV3* PackIndexV3::find(std::string_view name) const {
     for (const auto& t : tensors) if (t.name == name) return &t;
     return nullptr;

@@ -40,22 +40,6 @@ GpuMatrix dense(CudaGraph& g, const std::filesystem::path& path, const PackIndex
 }
 }  // namespace
 
-namespace {
-// planar Q8_0 experts (per expert: 32-byte code blocks, then the binary16 scales; planar_pack_v3.cpp:611-616) -> GGUF blocks
-std::vector<std::byte> q8_planar_to_rows(const std::vector<std::byte>& planar, uint64_t blocks_per_expert, uint64_t experts) {
-    std::vector<std::byte> out(planar.size());
-    for (uint64_t e = 0; e < experts; ++e) {
-        const std::byte* src = planar.data() + e * blocks_per_expert * 34;
-        std::byte* dst = out.data() + e * blocks_per_expert * 34;
-        for (uint64_t b = 0; b < blocks_per_expert; ++b) {
-            std::memcpy(dst + b * 34, src + blocks_per_expert * 32 + b * 2, 2);
-            std::memcpy(dst + b * 34 + 2, src + b * 32, 32);
-        }
-    }
-    return out;
-}
-}  // namespace
-
 MoeWeights load_pack_v3_moe_layer(CudaGraph& g, const std::filesystem::path& path, const PackIndexV3& index, std::string_view prefix, MoeShape& shape,
                                   PackLoadOptions options) {
     const std::string p(prefix);
@@ -80,7 +64,17 @@ MoeWeights load_pack_v3_moe_layer(CudaGraph& g, const std::filesystem::path& pat
     // gate / up: a co-located pair (two tensors of [gate_e, up_e] expert pairs, planar_pack_v3.cpp:1076-1093) or plain GGUF experts
     const bool coloc_q4 = gate.kind == PlanarKind::q4k_coloc_gate_v3 && up.kind == PlanarKind::q4k_coloc_up_v3;
     const bool coloc_q8 = gate.kind == PlanarKind::q8_coloc_gate_v3 && up.kind == PlanarKind::q8_coloc_up_v3;
-    if (coloc_q4 || coloc_q8) {
+    const bool coloc_q5 = gate.kind == PlanarKind::q5k_coloc_gate_v3 && up.kind == PlanarKind::q5k_coloc_up_v3;
+    if (coloc_q5) {
+        // no planar five-bit kernel: the pair tensors become separate gate / up tensors of plain Q5_K blocks on the host
+        need(gate.source_type == TSP_TYPE_Q5_K && gate.partner_name == up.name && up.partner_name == gate.name && gate.bytes == up.bytes &&
+             gate.bytes == planar_expert_bytes_v3(TSP_TYPE_Q5_K, C, H) * E, "pack v3: co-located Q5_K pair extent");
+        const auto lo = read_pack_v3_tensor(path, index, gate), hi = read_pack_v3_tensor(path, index, up);
+        std::vector<std::byte> gg(gguf_expert_bytes_v3(TSP_TYPE_Q5_K, C, H) * E), ug(gg.size());
+        split_coloc_pair_v3(TSP_TYPE_Q5_K, C, H, E, lo.data(), hi.data(), gg.data(), ug.data());
+        w.gate = {g.upload(gg, gate.name + " (rows)", true), TSP_TYPE_Q5_K};
+        w.up = {g.upload(ug, up.name + " (rows)", true), TSP_TYPE_Q5_K};
+    } else if (coloc_q4 || coloc_q8) {
         need(gate.partner_name == up.name && up.partner_name == gate.name && gate.bytes == up.bytes, "pack v3: co-located pair does not name its partner");
         w.gate = {upload_tensor(g, path, index, gate), gate.source_type};
         w.up = {upload_tensor(g, path, index, up), up.source_type};
@@ -92,10 +86,13 @@ MoeWeights load_pack_v3_moe_layer(CudaGraph& g, const std::filesystem::path& pat
         w.gate = {upload_tensor(g, path, index, gate), gate.source_type};
         w.up = {upload_tensor(g, path, index, up), up.source_type};
     }
-    if (down.kind == PlanarKind::q8_planar_v3 && options.q8_down_as_rows) {
-        need(H % 32 == 0 && down.bytes == C * (H / 32) * 34 * E, "pack v3: planar Q8_0 down extent");
-        const auto rows = q8_planar_to_rows(read_pack_v3_tensor(path, index, down), C * (H / 32), E);
-        w.down = {g.upload(rows, down.name + " (rows)", true), down.source_type};
+    if ((down.kind == PlanarKind::q8_planar_v3 && options.q8_down_as_rows) || down.kind == PlanarKind::q51_planar_v3) {
+        // planar Q8_0 on request, planar Q5_1 always (no planar five-bit kernel): plain GGUF blocks, re-laid on the host
+        const uint32_t type = down.kind == PlanarKind::q51_planar_v3 ? TSP_TYPE_Q5_1 : TSP_TYPE_Q8_0;
+        need(down.source_type == type && down.bytes == planar_expert_bytes_v3(type, H, C) * E && down.bytes, "pack v3: planar down extent");
+        std::vector<std::byte> rows(gguf_expert_bytes_v3(type, H, C) * E);
+        unpack_planar_experts_v3(type, H, C, E, read_pack_v3_tensor(path, index, down).data(), rows.data());
+        w.down = {g.upload(rows, down.name + " (rows)", true), type};
     } else if (down.kind == PlanarKind::q8_planar_v3) {
         w.down = {upload_tensor(g, path, index, down), down.source_type};
         g.register_planar_matrix(w.down.view, {down.source_type, uint32_t(down.kind), uint32_t(H), uint32_t(C), uint32_t(E)});

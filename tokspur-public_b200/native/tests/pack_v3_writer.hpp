@@ -106,10 +106,11 @@ inline void colocate(uint32_t type, const std::vector<uint8_t>& gate, const std:
     }
 }
 
-struct LayerBytes {   // GGUF bytes of one layer: experts Q4_K or Q8_0 (gate / up), down Q8_0, shared expert Q8_0, routers F32
+struct LayerBytes {   // GGUF bytes of one layer: experts Q4_K, Q5_K or Q8_0 (gate / up), down Q8_0 or Q5_1, shared expert Q8_0, routers F32
     uint32_t C, H, E, gate_type;
     std::vector<uint8_t> gate, up, down, sgate, sup, sdown;
     std::vector<float> router, srouter;
+    uint32_t down_type = 8;
 };
 
 inline std::vector<Entry> layer_entries(const LayerBytes& L, const std::string& prefix) {
@@ -126,14 +127,15 @@ inline std::vector<Entry> layer_entries(const LayerBytes& L, const std::string& 
         return out;
     };
     auto f32 = [](const std::vector<float>& v) { std::vector<uint8_t> b(v.size() * 4); std::memcpy(b.data(), v.data(), b.size()); return b; };
-    const char* gl = gt == 12 ? "q4k_coloc_gate_v3" : "q8_coloc_gate_v3";
-    const char* ul = gt == 12 ? "q4k_coloc_up_v3" : "q8_coloc_up_v3";
+    const char* gl = gt == 12 ? "q4k_coloc_gate_v3" : gt == 13 ? "q5k_coloc_gate_v3" : "q8_coloc_gate_v3";
+    const char* ul = gt == 12 ? "q4k_coloc_up_v3" : gt == 13 ? "q5k_coloc_up_v3" : "q8_coloc_up_v3";
+    const uint32_t dt = L.down_type;
     return {
         {prefix + "ffn_gate_inp.weight", 0, 0, "plain", {C, E}, {C, E}, uint64_t(C) * E * 4, "", f32(L.router)},
         {prefix + "ffn_gate_inp_shexp.weight", 0, 0, "plain", {C}, {C}, uint64_t(C) * 4, "", f32(L.srouter)},
         {gname, expanded ? 24u : gt, gt, gl, pdims, gdims, L.gate.size(), uname, lo},
         {uname, expanded ? 24u : gt, gt, ul, pdims, gdims, L.up.size(), gname, hi},
-        {prefix + "ffn_down_exps.weight", 8, 8, "q8_planar_v3", {H, C, E}, {H, C, E}, L.down.size(), "", planar_experts(8, L.down, H, C, E)},
+        {prefix + "ffn_down_exps.weight", dt, dt, dt == 7 ? "q51_planar_v3" : "q8_planar_v3", {H, C, E}, {H, C, E}, L.down.size(), "", planar_experts(dt, L.down, H, C, E)},
         {prefix + "ffn_gate_shexp.weight", 8, 8, "q8_lanes_v1", {C, H}, {C, H}, L.sgate.size(), "", lanes(L.sgate, C)},
         {prefix + "ffn_up_shexp.weight", 8, 8, "q8_lanes_v1", {C, H}, {C, H}, L.sup.size(), "", lanes(L.sup, C)},
         {prefix + "ffn_down_shexp.weight", 8, 8, "q8_lanes_v1", {H, C}, {H, C}, L.sdown.size(), "", lanes(L.sdown, H)},

@@ -26,13 +26,13 @@ void refuses(const std::function<void()>& f, const char* what) {
     throw std::runtime_error(what);
 }
 std::vector<uint8_t> blocks(uint32_t type, uint64_t weights, uint32_t seed) {
-    const uint32_t epb = type == 8 ? 32 : 256, bpb = type == 8 ? 34 : 144;
+    const uint32_t epb = (type == 8 || type == 7) ? 32 : 256, bpb = type == 8 ? 34 : type == 7 ? 24 : type == 13 ? 176 : 144;
     std::vector<uint8_t> raw(weights / epb * bpb);
     uint32_t rng = seed;
     for (size_t at = 0; at < raw.size(); at += bpb) {
         for (uint32_t i = 0; i < bpb; ++i) { rng = rng * 1664525u + 1013904223u; raw[at + i] = uint8_t(rng >> 24); }
         raw[at] = 1; raw[at + 1] = 0x0c;
-        if (type == 12) { raw[at + 2] = 1; raw[at + 3] = 4; for (unsigned i = 4; i < 16; ++i) raw[at + i] &= 0x3f; }
+        if (type == 12 || type == 13 || type == 7) { raw[at + 2] = 1; raw[at + 3] = 4; }
     }
     return raw;
 }
@@ -117,6 +117,55 @@ int main(int argc, char** argv) {
             refuses([&] { (void)read_pack_v3_index(bad); }, "foreign recipe accepted");
             pack_v3_test::write(bad, entries, "tokspur-pack-v3-block-7");   // the reference's per-block recipes share the prefix
             require(read_pack_v3_index(bad).recipe == "tokspur-pack-v3-block-7", "per-block recipe");
+        }
+
+        // ---- planar images back to GGUF blocks on the host: every encoding, against the oracle's packer and unpacker ----
+        for (const uint32_t type : {12u, 13u, 7u, 8u}) {
+            const uint32_t cols = 512, rows = 24, experts = 4;
+            const auto src = blocks(type, uint64_t(cols) * rows * experts, 40 + type);
+            const auto planar = pack_v3_test::planar_experts(type, src, cols, rows, experts);
+            require(planar.size() == planar_expert_bytes_v3(type, cols, rows) * experts && src.size() == gguf_expert_bytes_v3(type, cols, rows) * experts, "planar / GGUF extents");
+            std::vector<std::byte> back(src.size());
+            unpack_planar_experts_v3(type, cols, rows, experts, reinterpret_cast<const std::byte*>(planar.data()), back.data());
+            require(std::memcmp(back.data(), src.data(), src.size()) == 0, "planar experts do not come back as their GGUF blocks");
+            tso_planar_spec spec;
+            require(tso_make_expert_spec(type, cols, rows, &spec) == TSO_OK, "oracle spec");
+            std::vector<uint8_t> want(spec.source_expert_bytes);
+            require(tso_unpack_expert_planar(&spec, planar.data() + spec.planar_expert_bytes, want.data()) == TSO_OK &&
+                    std::memcmp(reinterpret_cast<const uint8_t*>(back.data()) + spec.source_expert_bytes, want.data(), want.size()) == 0, "differs from the oracle's unpacker");
+            if (type != 7) {   // co-located pairs exist for Q4_K, Q5_K and Q8_0
+                const auto other = blocks(type, uint64_t(cols) * rows * experts, 50 + type);
+                std::vector<uint8_t> lo, hi;
+                pack_v3_test::colocate(type, src, other, cols, rows, experts, lo, hi);
+                std::vector<std::byte> g2(src.size()), u2(src.size());
+                split_coloc_pair_v3(type, cols, rows, experts, reinterpret_cast<const std::byte*>(lo.data()), reinterpret_cast<const std::byte*>(hi.data()), g2.data(), u2.data());
+                require(std::memcmp(g2.data(), src.data(), src.size()) == 0 && std::memcmp(u2.data(), other.data(), other.size()) == 0, "co-located pair does not split into its gate and up tensors");
+            }
+            if (type == 12 || type == 13) {   // a factor byte above 63 in the factor-record plane
+                auto bad_planar = planar;
+                bad_planar[uint64_t(rows) * (cols / 256) * (type == 13 ? 160 : 128) + 5] |= 0x40;
+                refuses([&] { unpack_planar_experts_v3(type, cols, rows, 1, reinterpret_cast<const std::byte*>(bad_planar.data()), back.data()); }, "a factor above 63 was accepted");
+            }
+        }
+        refuses([&] { (void)planar_expert_bytes_v3(5, 256, 8); }, "an encoding without a planar form was accepted");
+        require(planar_expert_bytes_v3(12, 300, 8) == 0 && planar_expert_bytes_v3(8, 32, 4) == 0 && planar_expert_bytes_v3(13, 512, 6) == 0, "shapes without a planar form");
+        {   // the reference model's other pairing in a pack: co-located Q5_K gate / up, planar Q5_1 down
+            pack_v3_test::LayerBytes L5{C, H, E, 13, blocks(13, uint64_t(C) * H * E, 11), blocks(13, uint64_t(C) * H * E, 12), blocks(7, uint64_t(C) * H * E, 13),
+                                        blocks(8, uint64_t(C) * H, 14), blocks(8, uint64_t(C) * H, 15), blocks(8, uint64_t(C) * H, 16),
+                                        std::vector<float>(size_t(C) * E, 0.5f), std::vector<float>(C, 0.25f), 7};
+            const fs::path p5 = dir / "layer5.gguf";
+            pack_v3_test::write(p5, pack_v3_test::layer_entries(L5, "blk.0."));
+            const PackIndexV3 i5 = read_pack_v3_index(p5);
+            const auto& g5 = i5.at("blk.0.ffn_gate_exps.weight");
+            const auto& d5 = i5.at("blk.0.ffn_down_exps.weight");
+            require(g5.kind == PlanarKind::q5k_coloc_gate_v3 && g5.type == 24 && g5.dimensions == std::vector<uint64_t>{180, H, E} && g5.source_type == 13 &&
+                    d5.kind == PlanarKind::q51_planar_v3 && d5.type == 7 && d5.bytes == d5.source_bytes, "five-bit pack entries");
+            const auto lo = read_pack_v3_tensor(p5, i5, g5), hi = read_pack_v3_tensor(p5, i5, i5.at("blk.0.ffn_up_exps.weight"));
+            std::vector<std::byte> gg(L5.gate.size()), ug(L5.up.size()), dd(L5.down.size());
+            split_coloc_pair_v3(13, C, H, E, lo.data(), hi.data(), gg.data(), ug.data());
+            unpack_planar_experts_v3(7, H, C, E, read_pack_v3_tensor(p5, i5, d5).data(), dd.data());
+            require(std::memcmp(gg.data(), L5.gate.data(), gg.size()) == 0 && std::memcmp(ug.data(), L5.up.data(), ug.size()) == 0 &&
+                    std::memcmp(dd.data(), L5.down.data(), dd.size()) == 0, "five-bit pack tensors do not come back as their GGUF blocks");
         }
 
         // ---- the reference's own GGUF parser on the same bytes ----

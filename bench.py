@@ -240,7 +240,10 @@ def decode_record(args, dev, T, layers, etype, layout, full: bool):
     rec = {"tokens": T, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "e2e_ms_per_step": ms_e2e, "e2e_tokens_per_s": T / (ms_e2e * 1e-3),
            "timed_repeats": repeats, "unique_experts": U, "layer_algorithmic_bytes": layer_bytes,
            "layer_hbm_gbs": layer_bytes / (ms * 1e-3) / 1e9, "layer_hbm_frac": layer_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
-           "layer_tflops": T * (SELECTED + 1) * FLOPS_PER_ROUTE / (ms * 1e-3) / 1e12, "launches_per_step": 5}
+           "layer_tflops": T * (SELECTED + 1) * FLOPS_PER_ROUTE / (ms * 1e-3) / 1e12,
+           # routing, tables, gate-up, down, mixture; experts that cannot take the shared expert into their launches (Q8_0, Q5_K) run it
+           # in a launch of its own beside each projection
+           "launches_per_step": 5 if etype == formats.Q4_K else 7}
     if not full:
         return rec, None
     # ---- the dominant launch alone, back to back over the rotating layers (tables of batch 0; the weights change every launch)

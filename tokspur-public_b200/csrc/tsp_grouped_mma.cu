@@ -903,8 +903,9 @@ int launch_grouped(const tsp_matrix_set* a, const tsp_matrix_set* b, bool gateup
     GroupedMaps maps;
     auto plane_maps = [&](const uint8_t* bp, uint32_t mats, uint64_t ds, uint32_t n, uint64_t stride, uint32_t at) -> int {
         if (q8) {
-            // rows of 34-byte blocks: [row bytes][row][matrix][expert]; a box is 144 bytes (four blocks + 8) of rm rows. The last
-            // even span's box ends 8 bytes past the row: those bytes arrive as zeros and are not read
+            // rows of 34-byte blocks: [row bytes][row][matrix][expert]; a box is 144 bytes (four blocks + 8) of rm rows. Columns are a
+            // multiple of 256, so a row holds an even number of spans and the last one is odd: its box (from 8 bytes before the span)
+            // ends exactly at the end of the row, and every even span's box ends inside it
             const uint64_t row_bytes = uint64_t(a->cols / 32) * 34;   // a multiple of 16: columns are a multiple of 256
             const uint64_t dims[4] = {row_bytes, a->rows, mats, n}, strides[3] = {row_bytes, ds, stride};
             const uint32_t box[4] = {144, rm, mats, 1};

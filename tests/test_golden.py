@@ -11,7 +11,7 @@ import golden_cases
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_outputs.npz"))
 
 
-@pytest.mark.parametrize("type_", [8, 12])
+@pytest.mark.parametrize("type_", [8, 12, 13, 7])
 def test_decode_and_gemv_match_reference_outputs(oracle, type_):
     cols, rows = 512, 16
     w = fixtures.lcg_weights(type_, cols, rows, 2)
@@ -39,3 +39,12 @@ def test_layer_matches_reference_outputs(oracle, type_):
     assert np.array_equal(st["indices"], GOLD[f"layer_ids_{type_}"])
     assert list(st["indices"][1]) == [0, 1, 2]
     assert np.array_equal(y, GOLD[f"layer_out_{type_}"])
+
+
+def test_five_bit_layer_matches_reference_outputs(oracle):
+    """Q5_K gate / up, Q5_1 down, Q8_0 shared expert: the layer the reference's CPU code computed from the same bytes."""
+    layer, x, logits = golden_cases.five_bit_layer()
+    y, st = oracle.moe_layer(layer, x, logits, threads=2, stages=True)
+    assert np.array_equal(st["indices"], GOLD["layer_ids_five_bit"])
+    assert np.array_equal(y, GOLD["layer_out_five_bit"])
+    assert np.isfinite(y).all() and float(np.abs(y).max()) > 0

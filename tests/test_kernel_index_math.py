@@ -80,3 +80,65 @@ def test_q8_span_boxes_of_the_grouped_kernel_are_aligned_and_inside_the_row():
                 assert piece0 * 16 <= start and start + 68 <= (piece0 + 5) * 16 <= 144
                 # the blocks of the chunk inside the row: 2 * half and 2 * half + 1 of the span's four
                 assert x + start == sb * 136 + 68 * half == (sb * 4 + 2 * half) * 34
+
+
+def _funnelshift_r(lo, hi, n):
+    return (((hi << 32) | lo) >> n) & 0xFFFFFFFF
+
+
+def _byte_perm(a, b, sel):
+    src = [(a >> (8 * i)) & 255 for i in range(4)] + [(b >> (8 * i)) & 255 for i in range(4)]
+    return sum(src[(sel >> (4 * i)) & 7] << (8 * i) for i in range(4))
+
+
+def test_q8_chunk_words_give_the_blocks_codes_in_tile_order():
+    """q8_chunk_row of csrc/tsp_grouped_mma.cu replayed with integers: from the five 16-byte pieces a dequantise thread loads, the
+    scale half-words and the realigned code words of the chunk's two blocks, and the 0x6400 | (byte ^ 0x80) operand (1152 + q as
+    binary16 bits) in the order the tiles use inside every run of eight (0, 2, 1, 3, 4, 6, 5, 7)."""
+    import numpy as np
+    rng = np.random.default_rng(7)
+    for parity in (0, 1):
+        blocks = rng.integers(0, 256, size=(4, 34), dtype=np.uint8)          # one span: four Q8_0 blocks
+        line = np.zeros(144, dtype=np.uint8)
+        line[:] = rng.integers(0, 256, size=144, dtype=np.uint8)              # neighbouring bytes are arbitrary
+        off = 8 if parity else 0
+        line[off:off + 136] = blocks.reshape(-1)
+        words = line.view("<u4").astype(np.uint64)
+        for half in (0, 1):
+            L = [int(w) for w in words[half * 4 * 4: half * 4 * 4 + 20]]
+            ws = half + 2 * parity
+            s0, s1 = L[ws] & 0xFFFF, L[ws + 8] >> 16
+            b0, b1 = blocks[2 * half], blocks[2 * half + 1]
+            assert s0 == int(b0[0]) | (int(b0[1]) << 8) and s1 == int(b1[0]) | (int(b1[1]) << 8)
+            for u in range(8):
+                if u < 4:
+                    a = _funnelshift_r(L[ws + 2 * u], L[ws + 2 * u + 1], 16)
+                    b = _funnelshift_r(L[ws + 2 * u + 1], L[ws + 2 * u + 2], 16)
+                else:
+                    a, b = L[ws + 9 + 2 * (u - 4)], L[ws + 10 + 2 * (u - 4)]
+                a ^= 0x80808080
+                b ^= 0x80808080
+                w = [_byte_perm(a, 0x64646464, 0x4240), _byte_perm(a, 0x64646464, 0x4341), _byte_perm(b, 0x64646464, 0x4240), _byte_perm(b, 0x64646464, 0x4341)]
+                halves = [h for x in w for h in (x & 0xFFFF, x >> 16)]       # eight binary16 bit patterns in staged order
+                codes = (b0 if u < 4 else b1)[2 + 8 * (u % 4): 2 + 8 * (u % 4) + 8].astype(np.int8)
+                for pos, k in enumerate((0, 2, 1, 3, 4, 6, 5, 7)):
+                    assert halves[pos] == 0x6400 | ((int(codes[k]) + 128) & 255)       # 1024 + (q + 128) = 1152 + q
+                    assert np.array([halves[pos]], dtype=np.uint16).view(np.float16)[0] == 1152 + int(codes[k])
+
+
+def test_five_bit_code_assembly():
+    """Group5 of csrc/tsp_gemv_k5.cu replayed with integers: Q5_1 spreads four fifth bits to bit 4 of four bytes with one multiply,
+    Q5_K takes bit g of the fifth-bit bytes; byte k of the result converts through the 0x4B000000 magic number."""
+    import numpy as np
+    for hb in range(16):
+        spread = ((hb * 0x00204081) & 0x01010101) << 4
+        assert spread == sum(((hb >> k) & 1) << (8 * k + 4) for k in range(4))
+    rng = np.random.default_rng(11)
+    for _ in range(200):
+        qs, qh, g = int(rng.integers(0, 1 << 32)), int(rng.integers(0, 1 << 32)), int(rng.integers(0, 8))
+        q = ((qs >> (4 * (g & 1))) & 0x0F0F0F0F) | (((qh >> g) & 0x01010101) << 4)
+        for k in range(4):
+            want = (((qs >> (8 * k)) & 255) >> (4 * (g & 1)) & 15) | ((((qh >> (8 * k)) & 255) >> g & 1) << 4)
+            assert (q >> (8 * k)) & 255 == want
+            bits = _byte_perm(q, 0x4B000000, 0x7440 + k)
+            assert np.array([bits], dtype=np.uint32).view(np.float32)[0] - np.float32(8388608.0) == want

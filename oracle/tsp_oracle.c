@@ -28,6 +28,8 @@ int tso_block_geometry(uint32_t type, uint32_t* epb, uint32_t* bpb) {
         case 8: e = 32; b = 34; break;
         case 12: e = 256; b = 144; break;
         case 13: e = 256; b = 176; break;
+        case 14: e = 256; b = 210; break;
+        case 20: e = 32; b = 18; break;
         default: return TSO_E_TYPE;
     }
     if (epb) *epb = e;
@@ -76,6 +78,18 @@ double tso_value(uint32_t type, const uint8_t* block, uint32_t index) {
             if (type == 13) q |= ((block[16 + index % 32] >> (index / 32)) & 1u) << 4;
             return (double)tso_binary16(rd16(block)) * k_group_factor(block, index / 32, 0) * q -
                    (double)tso_binary16(rd16(block + 2)) * k_group_factor(block, index / 32, 1);
+        }
+        case 14: {  /* Q6_K: 128 bytes of low nibbles, 64 bytes of 2-bit tops, 16 signed group scales, d (numeric.cpp:51-58) */
+            const uint32_t within = index % 128, section = index / 128;
+            const uint32_t low = (block[section * 64 + within % 64] >> (4 * (within / 64))) & 15u;
+            const uint32_t high = (block[128 + section * 32 + within % 32] >> (2 * (within / 32))) & 3u;
+            const int scale = (int8_t)block[192 + index / 16];
+            return (double)tso_binary16(rd16(block + 208)) * scale * ((int)(low | (high << 4)) - 32);
+        }
+        case 20: {  /* IQ4_NL: d and 16 bytes of nibbles that index the encoding's fixed 16-value alphabet (numeric.cpp:59-65) */
+            static const int alphabet[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+            const uint32_t code = (block[2 + index % 16] >> (4 * (index / 16))) & 15u;
+            return (double)tso_binary16(rd16(block)) * alphabet[code];
         }
         default: return NAN;
     }

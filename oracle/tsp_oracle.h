@@ -31,7 +31,8 @@ enum {
     TSO_E_RANGE = -4,     /* index or factor out of range */
 };
 
-/* GGUF type ids handled here: 0 F32, 1 F16, 7 Q5_1, 8 Q8_0, 12 Q4_K, 13 Q5_K, 30 BF16. */
+/* GGUF type ids handled here: 0 F32, 1 F16, 7 Q5_1, 8 Q8_0, 12 Q4_K, 13 Q5_K, 14 Q6_K, 20 IQ4_NL, 30 BF16 (every encoding
+ * numeric.cpp decodes; the CUDA kernels cover 7, 8, 12 and 13). */
 int tso_block_geometry(uint32_t type, uint32_t* elements_per_block, uint32_t* bytes_per_block);
 
 /* binary16 -> binary32, all 65536 patterns (numeric.cpp:81-91). */

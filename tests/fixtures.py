@@ -20,18 +20,21 @@ def lcg_stream(seed: int, n: int) -> np.ndarray:
 
 
 def block_bytes(type_: int) -> int:
-    return {7: 24, 8: 34, 12: 144, 13: 176}[type_]
+    return {7: 24, 8: 34, 12: 144, 13: 176, 14: 210, 20: 18}[type_]
 
 
 def lcg_weights(type_: int, cols: int, rows: int, experts: int, seed: int = 44) -> np.ndarray:
     bpb = block_bytes(type_)
-    epb = 32 if type_ in (7, 8) else 256
+    epb = 32 if type_ in (7, 8, 20) else 256
     nblocks = cols // epb * rows * experts
     out = (lcg_stream(seed, nblocks * bpb) >> np.uint32(24)).astype(np.uint8).reshape(nblocks, bpb)
     ds = np.array([0x0401, 0x0568, 0x068e, 0x0ac2, 0x2401, 0x2803, 0xa401, 0x1801], dtype=np.uint16)
     d = ds[np.arange(nblocks) % 8]
     out[:, 0] = d & 255
     out[:, 1] = d >> 8
+    if type_ == 14:        # Q6_K keeps its scale at the end of the block
+        out[:, 208] = d & 255
+        out[:, 209] = d >> 8
     if type_ != 8:
         out[:, 2] = 0x03
         out[:, 3] = 0x1c

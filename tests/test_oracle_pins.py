@@ -84,6 +84,34 @@ def _q51_fixture_block():
     return block, expected
 
 
+def _q6k_fixture_block():
+    # native/tests/test_numeric.cpp:104-114: d = 0.03125, code = (7 i + 1) % 64, group scale = 15 (i / 16) - 120
+    block = np.zeros(210, dtype=np.uint8)
+    block[208:210] = [0x00, 0x28]
+    expected = np.zeros(256, dtype=np.float32)
+    for i in range(256):
+        code = (i * 7 + 1) % 64
+        block[(i // 128) * 64 + (i % 64)] |= (code % 16) << ((i % 128 // 64) * 4)
+        block[128 + (i // 128) * 32 + i % 32] |= (code // 16) << ((i % 128 // 32) * 2)
+        scale = (i // 16) * 15 - 120
+        block[192 + i // 16] = scale & 255
+        expected[i] = np.float32(0.03125) * scale * (code - 32)
+    return block, expected
+
+
+def _iq4nl_fixture_block():
+    # native/tests/test_numeric.cpp:115-123: d = 0.5, code = 7 i % 16 into the encoding's fixed value alphabet
+    alphabet = [-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113]
+    block = np.zeros(18, dtype=np.uint8)
+    block[0:2] = [0x00, 0x38]
+    expected = np.zeros(32, dtype=np.float32)
+    for i in range(32):
+        code = (i * 7) % 16
+        block[2 + i % 16] |= code << ((i // 16) * 4)
+        expected[i] = 0.5 * alphabet[code]
+    return block, expected
+
+
 def _q8_fixture_block():
     block = np.zeros(34, dtype=np.uint8)
     block[0:2] = [0x00, 0x34]  # 0.25
@@ -95,7 +123,8 @@ def _q8_fixture_block():
     return block, expected
 
 
-@pytest.mark.parametrize("type_,maker", [(12, _q4k_fixture_block), (8, _q8_fixture_block), (13, _q5k_fixture_block), (7, _q51_fixture_block)])
+@pytest.mark.parametrize("type_,maker", [(12, _q4k_fixture_block), (8, _q8_fixture_block), (13, _q5k_fixture_block), (7, _q51_fixture_block),
+                                         (14, _q6k_fixture_block), (20, _iq4nl_fixture_block)])
 def test_format_fixture_blocks(oracle, type_, maker):
     block, expected = maker()
     got = oracle.dequantize(type_, block, expected.size)
@@ -266,7 +295,7 @@ def test_permutation_tables(oracle):
 
 # ---- the restatement against the reference's own compiled sources, on random inputs ----
 
-@pytest.mark.parametrize("type_", [8, 12, 13, 7])
+@pytest.mark.parametrize("type_", [8, 12, 13, 7, 14, 20])
 def test_port_equals_reference_decode_and_gemv(oracle, ref_oracle, type_):
     cols, rows = 512, 24
     w = fixtures.lcg_weights(type_, cols, rows, 1)[0]

@@ -16,6 +16,7 @@ namespace tokspur_b200 {
 class CudaGraph;
 struct MoeWeights;
 struct MoeShape;
+struct GpuMatrix;
 
 // planar_pack_v3.hpp:29-40; kind 10 is this build's extension (Q4_K down tensors in planar form), never written by the reference
 enum class PlanarKind : uint32_t {
@@ -54,6 +55,8 @@ struct PackIndexV3 {
 [[nodiscard]] PackIndexV3 read_pack_v3_index(const std::filesystem::path& path);
 // The index as one line of JSON (tests and tools)
 [[nodiscard]] std::string describe_pack_v3(const PackIndexV3& index);
+// The layer prefixes ("blk.0.", "blk.1.", ...) whose routed-expert tensors the pack holds, in ascending layer order
+[[nodiscard]] std::vector<std::string> pack_v3_moe_layers(const PackIndexV3& index);
 // The packed bytes of one tensor
 [[nodiscard]] std::vector<std::byte> read_pack_v3_tensor(const std::filesystem::path& path, const PackIndexV3& index, const PackTensorV3& tensor);
 
@@ -78,6 +81,9 @@ void split_coloc_pair_v3(uint32_t source_type, uint64_t columns, uint64_t rows, 
 // q8_down_as_rows: a planar Q8_0 down tensor is re-laid as raw GGUF blocks on the host while loading (lossless) instead of being
 // registered as a planar matrix: the prefill encoder (encode_moe_mm_many) reads Q8_0 experts as raw blocks only.
 struct PackLoadOptions { bool q8_down_as_rows = false; };
+// One dense two-dimensional tensor (the vocabulary head `output.weight`, a shared-expert matrix, a router) as the projection
+// kernels read it: plain tensors as they are, lane-packed Q8_0 (`q8_lanes_v1`) unpacked to GGUF rows on the device.
+GpuMatrix load_pack_v3_dense_matrix(CudaGraph& graph, const std::filesystem::path& path, const PackIndexV3& index, std::string_view name);
 MoeWeights load_pack_v3_moe_layer(CudaGraph& graph, const std::filesystem::path& path, const PackIndexV3& index, std::string_view prefix,
                                   MoeShape& shape, PackLoadOptions options = {});
 

@@ -354,6 +354,22 @@ PackIndexV3 read_pack_v3_index(const std::filesystem::path& path) {
     return index;
 }
 
+std::vector<std::string> pack_v3_moe_layers(const PackIndexV3& index) {
+    constexpr std::string_view prefix = "blk.", suffix = ".ffn_gate_exps.weight";
+    std::vector<std::pair<uint64_t, std::string>> found;
+    for (const auto& t : index.tensors) {
+        const std::string_view n = t.name;
+        if (n.size() <= prefix.size() + suffix.size() || n.substr(0, prefix.size()) != prefix || n.substr(n.size() - suffix.size()) != suffix) continue;
+        const std::string_view digits = n.substr(prefix.size(), n.size() - prefix.size() - suffix.size());
+        if (digits.empty() || digits.size() > 6 || !std::all_of(digits.begin(), digits.end(), [](char ch) { return ch >= '0' && ch <= '9'; })) continue;
+        found.emplace_back(std::stoull(std::string(digits)), std::string(n.substr(0, n.size() - suffix.size() + 1)));
+    }
+    std::sort(found.begin(), found.end());
+    std::vector<std::string> out;
+    for (auto& f : found) out.push_back(std::move(f.second));
+    return out;
+}
+
 std::string describe_pack_v3(const PackIndexV3& index) {
     std::string out = "{\"version\":" + std::to_string(index.version) + ",\"alignment\":" + std::to_string(index.alignment) + ",\"architecture\":";
     escape_into(out, index.architecture);

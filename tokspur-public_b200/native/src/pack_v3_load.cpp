@@ -40,6 +40,12 @@ GpuMatrix dense(CudaGraph& g, const std::filesystem::path& path, const PackIndex
 }
 }  // namespace
 
+GpuMatrix load_pack_v3_dense_matrix(CudaGraph& g, const std::filesystem::path& path, const PackIndexV3& index, std::string_view name) {
+    const auto& t = index.at(name);
+    need(t.source_dimensions.size() == 2 && t.source_dimensions[0] >= 1 && t.source_dimensions[1] >= 1, "pack v3: not a two-dimensional tensor");
+    return dense(g, path, index, std::string(name), t.source_dimensions[0], t.source_dimensions[1]);
+}
+
 MoeWeights load_pack_v3_moe_layer(CudaGraph& g, const std::filesystem::path& path, const PackIndexV3& index, std::string_view prefix, MoeShape& shape,
                                   PackLoadOptions options) {
     const std::string p(prefix);

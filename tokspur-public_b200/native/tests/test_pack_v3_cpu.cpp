@@ -80,6 +80,15 @@ int main(int argc, char** argv) {
         require(index.at("blk.7.ffn_down_exps.weight").kind == PlanarKind::q8_planar_v3 && index.at("blk.7.ffn_gate_shexp.weight").kind == PlanarKind::q8_lanes_v1 &&
                 index.find("blk.8.ffn_gate_exps.weight") == nullptr, "kinds and lookup");
         refuses([&] { (void)index.at("missing"); }, "lookup of a missing tensor did not throw");
+        require(pack_v3_moe_layers(index) == std::vector<std::string>{"blk.7."}, "layer prefixes of the pack");
+        {   // several layers, written out of order: ascending layer numbers come back
+            auto many = pack_v3_test::layer_entries(L, "blk.12.");
+            for (auto& e : pack_v3_test::layer_entries(L, "blk.3.")) many.push_back(e);
+            for (auto& e : pack_v3_test::layer_entries(L, "blk.48.")) many.push_back(e);
+            const fs::path pm = dir / "layers.gguf";
+            pack_v3_test::write(pm, many);
+            require(pack_v3_moe_layers(read_pack_v3_index(pm)) == std::vector<std::string>{"blk.3.", "blk.12.", "blk.48."}, "layer order");
+        }
         refuses([&] { (void)parse_planar_kind("q4k_planar_v9"); }, "unknown layout string accepted");
         const std::string text = describe_pack_v3(index);
         require(text.find("\"layout\":\"q4k_coloc_up_v3\"") != std::string::npos && text.find("\"alignment\":16384") != std::string::npos, "description text");
